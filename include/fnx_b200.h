@@ -1,0 +1,195 @@
+/* fnx_b200: C ABI of the B200 (sm_100a) speculative-decoding verify path.
+ *
+ * Drop-in boundary: these entry points stand where the reference engine's per-layer operator API stands
+ * (engine/src/kernels.hpp, namespace fnx: free functions on raw device pointers and a stream, called only by the
+ * window scheduler in engine/src/engine.cu and engine_common.cu).  The reference has no FFI of its own; a C ABI
+ * is what a maintainer would bind from C++ (or any other host language) to swap this path in.  Each declaration
+ * names the reference interface it replaces.
+ *
+ * Conventions (as the reference's, engine/src/kernels.hpp:1-2):
+ *   - every pointer is DEVICE memory unless its name starts with h_; the caller owns every buffer;
+ *   - activations are f32 rows; quantised weights are GGML IQ3_S, re-tiled once by fnx_iq3s_retile();
+ *   - window scalars (first position, state slot) live in device memory so that captured graphs replay;
+ *   - no entry point synchronises, allocates or reads results back: all are stream-capture safe, except where
+ *     a comment says otherwise (fnx_engine_* set-up calls, fnx_comm_*);
+ *   - return value: 0 on success, a negative FNX_E_* code otherwise, with text from fnx_last_error();
+ *     device-side conditions are OR-ed into the `err` word (FNX_ERR_* bits, the reference's bit values,
+ *     engine/src/kernels.hpp:373-375), which the caller reads back with the window's results.
+ */
+#ifndef FNX_B200_H
+#define FNX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* fnx_stream;   /* a cudaStream_t */
+
+enum { FNX_OK = 0, FNX_E_ARG = -1, FNX_E_CUDA = -2, FNX_E_STATE = -3, FNX_E_UNAVAILABLE = -4 };
+/* device error bits (engine/src/kernels.hpp:373-375): a wait gave up; a non-finite value; non-finite logits */
+enum { FNX_ERR_TIMEOUT = 1, FNX_ERR_NONFINITE = 2, FNX_ERR_LOGITS = 16 };
+
+enum { FNX_TOPK_N = 64,      /* sampler candidates per row (TOPK_N, engine/src/kernels.hpp:441) */
+       FNX_MAX_ROWS = 32,    /* rows (tree nodes) of one verify window */
+       FNX_JOB_TOK = 4 };    /* activation rows of one expert job */
+
+const char* fnx_last_error(void);
+int fnx_version(void);
+
+/* ---------------------------------------------------------------------------------------------- IQ3_S weights
+ * GGML block_iq3_s <-> the device tile layout (a bit permutation; same size).  Replaces the reference's load-time
+ * re-layout of weights (split Q8_0 layout, engine/src/dense.cuh; expert slicing engine/src/model.cpp:1063-1069).
+ * rows % 16 == 0, cols % 256 == 0. */
+size_t fnx_iq3s_bytes(size_t rows, size_t cols);
+int fnx_iq3s_retile(const void* ggml_blocks, void* tiles, size_t rows, size_t cols, fnx_stream st);
+int fnx_iq3s_untile(const void* tiles, void* ggml_blocks, size_t rows, size_t cols, fnx_stream st);
+/* tiles -> f32 [rows][cols] (tests and tools; fnx::conv::dequantize, engine/src/tensor_convert.hpp:143-326) */
+int fnx_iq3s_dequant_tiles(const void* tiles, float* out, size_t rows, size_t cols, fnx_stream st);
+/* deterministic fixture quantiser f32 -> GGML blocks (ggml's own quantiser is not part of the reference tree) */
+int fnx_iq3s_quantize(const float* w, void* ggml_blocks, size_t n, fnx_stream st);
+/* out[i] = sigma * N(0,1) from Philox4x32-10 keyed by (seed, stream_id), counter i / 4 */
+int fnx_fill_normal(float* out, size_t n, float sigma, uint64_t seed, uint32_t stream_id, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- dense GEMV
+ * y[t][r] (+)= W[r] . xin[t] for t < T (T <= 8 per call), W an IQ3_S tile matrix; xin[t] = x[t], or
+ * rmsnorm(x[t]) * norm_w when norm_w is not null.  Replaces q8s_gemv / mmvq / rms_norm_rows
+ * (engine/src/kernels.hpp:49-52, 405-406).  rows % 32 == 0 (cols 2048), % 16 (cols 4096), % 128 (cols 512). */
+int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps,
+              float* y, int ldy, int accumulate, unsigned* err, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- MoE
+ * One expert job: expert `w` applied to n activation rows (Job, engine/src/kernels.hpp:18-23, with MAXT = 4 rows;
+ * an expert picked by more rows gets several jobs). */
+typedef struct {
+    int w;                    /* expert index */
+    int n;                    /* rows of the job, 1..FNX_JOB_TOK */
+    int y[FNX_JOB_TOK];       /* activation rows (tokens) */
+    int out[FNX_JOB_TOK];     /* output rows: pair t * K + k; the shared expert's T * K + t */
+} fnx_job;
+
+/* router_route (engine/src/kernels.hpp:294-296; simple form route :79): logits [T][E + 1] = Wr . xin (f32 weights,
+ * row E the shared expert's gate), top-K by logit (ties: lower index), weights = softmax over the K; jobs for the
+ * experts in [e_lo, e_hi) in first-pick order, then (add_shared != 0) one job of the shared expert (w = E) per 4
+ * rows; *njobs = their number.  xin = rmsnorm(x) * norm_w when norm_w is not null. */
+int fnx_router_route(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K,
+                     int e_lo, int e_hi, int add_shared, float* logits, int* topi, float* topw, fnx_job* jobs,
+                     int* njobs, unsigned* err, fnx_stream st);
+/* moe_gate_up + SwiGLU (engine/src/kernels.hpp:319, :329; engine/src/moe.cuh:572-608): h[out][F] =
+ * silu(Wg . xin) * (Wu . xin).  Wgu: expert e's [gate (F); up (F)] x H tile matrix at Wgu + (e - e_base) *
+ * expert_stride; the shared expert (w == E) is read from Wsh. */
+int fnx_moe_gate_up(const void* Wgu, size_t expert_stride, int e_base, const void* Wsh, int E, const fnx_job* jobs,
+                    const int* njobs, int njobs_max, const float* x, const float* norm_w, float eps, int H, int F,
+                    float* h, unsigned* err, fnx_stream st);
+/* moe_down (engine/src/kernels.hpp:343): part[out][H] = Wd . h[out] */
+int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, const void* Wsh, int E, const fnx_job* jobs,
+                 const int* njobs, int njobs_max, const float* h, int H, int F, float* part, unsigned* err,
+                 fnx_stream st);
+/* moe_combine (engine/src/kernels.hpp:83; the cross-card addend of ring_sum :396): out[t] (+)= sum over the picks in
+ * [e_lo, e_hi) of topw * part[t K + k], + sigmoid(logits[t][E]) * part[T K + t] when add_shared */
+int fnx_moe_combine(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
+                    int K, int e_lo, int e_hi, int add_shared, float* out, int accumulate, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- attention
+ * attn_prep_append (engine/src/kernels.hpp:259): per-head RMS norm, NEOX rotary on the first nrot dims at position
+ * *pos0 + depth[t] (depth null: t), K and V rows stored as f16 at cache row *pos0 + t.
+ * qg rows [nq][q (hd) | gate (hd)], k and v rows [nkv][hd], with row strides ldq, ldk, ldv floats;
+ * caches [rows][nkv][hd] f16. */
+int fnx_attn_prep_append(float* qg, int ldq, float* k, int ldk, const float* v, int ldv, const float* q_norm,
+                         const float* k_norm, void* kc, void* vc, int T, int nq, int nkv, int hd, int nrot,
+                         const int* pos0, const int* depth, float eps, float rope_base, fnx_stream st);
+/* attn (engine/src/kernels.hpp:238): softmax(q k / sqrt(hd)) v sigmoid(gate) over cache rows [0, *pos0) and the
+ * window rows on row t's path to the root (parent null: a chain, the reference's causal case).
+ * out [T][nq][hd].  scratch: fnx_attn_scratch_bytes(T, nq, hd) bytes (attn_scratch_floats, :131). */
+size_t fnx_attn_scratch_bytes(int T, int nq, int hd);
+int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
+             const int* pos0, const int* parent, void* scratch, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- gated DeltaNet
+ * gdn_core (engine/src/kernels.hpp:97-99).  State and conv-history rings of NS slots replace snap / hsnap + the
+ * commit copy: the window starts from slot *cur; row t starts from its parent's result and writes slot
+ * (*cur + 1 + t) % NS.  S_pool [NS][nv][hs][hs] f32, hist_pool [NS][3][(2 nk + nv) hs] f32; y [T][nv hs].
+ * qkvz rows [q | k | v | z] with stride ldx floats, ab rows [alpha (nv) | beta (nv)] with stride ldab. */
+int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt,
+                 const float* a, const float* nw, float* S_pool, const int* cur, int NS, const int* parent, float* y,
+                 int nk, int nv, int hs, int T, float eps, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- head
+ * argmax (engine/src/kernels.hpp:433): per-row maximum, ties to the lower index; err bit 16 on a non-finite logit */
+int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st);
+/* top_tokens (engine/src/kernels.hpp:445) without penalties: the 64 highest per row, logit descending, id ascending */
+int fnx_top_tokens(const float* logits, int T, int V, float* out_v, int* out_i, fnx_stream st);
+/* embed rows: R[t] = f16 table[tok[t]] (the reference embeds on the host, engine_common.cu:955) */
+int fnx_embed_rows(const void* table_f16, const int* tok, int T, int H, float* R, fnx_stream st);
+/* rms_norm_rows (engine/src/kernels.hpp:406) */
+int fnx_rmsnorm(const float* x, const float* w, float* y, int rows, int n, float eps, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- drafting, acceptance
+ * lookup_drafts (engine/src/session.cpp:428-447) on the GPU: ctx[0 .. *n) tokens; out[0 .. out_n[0]) drafts,
+ * out_n[1] = match start or -1.  d1: device scalar (the draft layer's first token, < 0: any). */
+int fnx_lookup_draft(const int* ctx, const int* n, int lk, const int* d1, int* out, int* out_n, fnx_stream st);
+/* greedy acceptance over a tree (chain rule engine/src/session.cpp:573): result[0] = n, result[1 .. 1 + n) = the
+ * accepted node path, result[1 + FNX_MAX_ROWS ..] = the emitted tokens */
+int fnx_accept_greedy(const int* tok, const int* parent, const int* best, int T, int* result, fnx_stream st);
+typedef struct {
+    float temperature, top_p, min_p;
+    int top_k;
+} fnx_sampling;
+/* speculative sampling over a chain (engine/src/session.cpp:575-612, make_dist :41-75, draw :77-84) with
+ * Philox4x32-10 uniforms addressed (seed, seq, step, slot).  cand_* [T][64] from fnx_top_tokens; q_* the draft
+ * distributions ([T-1][64], q_n[j] = 0: a fixed draft; all null: every draft fixed). result as fnx_accept_greedy's. */
+int fnx_accept_sample(const float* cand_v, const int* cand_i, const int* tok, int T, fnx_sampling s, const int* q_ids,
+                      const double* q_p, const int* q_n, uint64_t seed, uint32_t seq, const uint32_t* step,
+                      int* result, fnx_stream st);
+
+/* ---------------------------------------------------------------------------------------------- engine
+ * The thin window scheduler: Engine::verify / commit / draft (engine/src/engine.hpp:50-229) for the synthetic
+ * Qwen3-Next-style model, one CUDA graph per window shape.  Set-up calls allocate and synchronise. */
+typedef struct {
+    int n_layer, hidden, n_expert, top_k, ffn;          /* 48, 2048, 512, 10, 512 */
+    int n_q_head, n_kv_head, head_dim, n_rot;           /* 16, 2, 256, 64 */
+    int gdn_k_head, gdn_v_head, gdn_head_dim;           /* 16, 32, 128 */
+    int vocab, max_ctx, max_rows;                       /* 151936, context rows, rows per window <= FNX_MAX_ROWS */
+    int attn_every;                                     /* 4: layer l is attention when (l + 1) % 4 == 0 */
+    int ep_rank, ep_size;                               /* expert-parallel shard of this process */
+    int n_seq;                                          /* independent sequences (lanes) held */
+    float eps, rope_base;
+} fnx_model_config;
+typedef struct fnx_engine fnx_engine;
+
+int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out);
+void fnx_engine_destroy(fnx_engine* e);
+/* random-init weights: every matrix N(0, sigma) -> IQ3_S; norm weights 1; router f32 N(0, sigma) */
+int fnx_engine_init_synthetic(fnx_engine* e, uint64_t seed, float sigma);
+/* bytes of weights + state this engine holds on its GPU */
+size_t fnx_engine_device_bytes(const fnx_engine* e);
+/* the engine's tensors by name, for tests and loaders: device pointer and byte size (0 if unknown) */
+void* fnx_engine_tensor(fnx_engine* e, const char* name, size_t* bytes);
+/* resets sequence `seq` to an empty context */
+int fnx_engine_reset(fnx_engine* e, int seq);
+/* Engine::verify: runs the T window rows (h_tok, h_parent host arrays; parent null = chain) of sequence `seq`
+ * through the model; leaves logits, per-row argmax and the acceptance result on the device and, when h_result is
+ * not null, copies the greedy acceptance result back (synchronises).  Does not commit. */
+int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const int* h_parent, int T, int* h_result);
+/* Engine::commit: keeps the n accepted rows h_path[0..n) of the last window of `seq` */
+int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n);
+/* Engine::draft: the MTP layer on the rows kept by the last commit, then k - 1 chained single-row calls;
+ * h_drafts receives k tokens */
+int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts);
+/* the device time of the last verify / draft graph launch in milliseconds (CUDA events on the engine's stream) */
+float fnx_engine_last_ms(const fnx_engine* e);
+int fnx_engine_pos(const fnx_engine* e, int seq);
+fnx_stream fnx_engine_stream(fnx_engine* e);
+
+/* ---------------------------------------------------------------------------------------------- expert-parallel sum
+ * ring_sum (engine/src/kernels.hpp:396) over NCCL: in-place sum of x[count] f32 across the communicator. */
+int fnx_comm_unique_id(void* h_id128);
+int fnx_engine_comm_init(fnx_engine* e, const void* h_id128, int rank, int size);
+int fnx_allreduce(fnx_engine* e, float* x, size_t count, fnx_stream st);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,391 @@
+"""Host-side mirror of the reference engine's operator API over the fnx_b200 C ABI.
+
+The product is ``libfnx_b200.so`` (hand-written sm_100a CUDA behind ``include/fnx_b200.h``); this module only
+binds it with ctypes so that tests and the benchmark can call the same entry points a C++ host would.  PyTorch is
+used for device memory and streams, nothing else.  There is no CPU fallback: if the library has not been built,
+``lib()`` raises.
+
+Names follow the reference's ``engine/src/kernels.hpp`` (router_route, moe_gate_up, moe_down, moe_combine,
+attn_prep_append, attn, gdn_core, argmax, top_tokens) and ``engine/src/engine.hpp`` (verify, commit, draft).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+
+_HERE = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libfnx_b200.so"
+HEADER = _HERE.parent / "include" / "fnx_b200.h"
+_LIB = None
+
+TOPK_N = 64
+MAX_ROWS = 32
+JOB_TOK = 4
+IQ3S_BLOCK = 110
+
+
+class Job(C.Structure):
+    _fields_ = [("w", C.c_int), ("n", C.c_int), ("y", C.c_int * JOB_TOK), ("out", C.c_int * JOB_TOK)]
+
+
+class Sampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("min_p", C.c_float), ("top_k", C.c_int)]
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in (
+        "n_layer", "hidden", "n_expert", "top_k", "ffn", "n_q_head", "n_kv_head", "head_dim", "n_rot", "gdn_k_head",
+        "gdn_v_head", "gdn_head_dim", "vocab", "max_ctx", "max_rows", "attn_every", "ep_rank", "ep_size", "n_seq")] + [
+        ("eps", C.c_float), ("rope_base", C.c_float)]
+
+
+def flash_next_config(**over) -> ModelConfig:
+    """The synthetic Qwen3-Next-style model of the benchmark (48 layers, hidden 2048, 512 experts top-10, ffn 512)."""
+    d = dict(n_layer=48, hidden=2048, n_expert=512, top_k=10, ffn=512, n_q_head=16, n_kv_head=2, head_dim=256, n_rot=64,
+             gdn_k_head=16, gdn_v_head=32, gdn_head_dim=128, vocab=151936, max_ctx=8192, max_rows=8, attn_every=4,
+             ep_rank=0, ep_size=1, n_seq=1, eps=1e-6, rope_base=1e7)
+    d.update(over)
+    return ModelConfig(**d)
+
+
+_P, _I, _F, _Z, _U64, _U32 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_uint64, C.c_uint32
+
+_PROTOS = {
+    "fnx_last_error": (C.c_char_p, []),
+    "fnx_version": (_I, []),
+    "fnx_iq3s_bytes": (_Z, [_Z, _Z]),
+    "fnx_iq3s_retile": (_I, [_P, _P, _Z, _Z, _P]),
+    "fnx_iq3s_untile": (_I, [_P, _P, _Z, _Z, _P]),
+    "fnx_iq3s_dequant_tiles": (_I, [_P, _P, _Z, _Z, _P]),
+    "fnx_iq3s_quantize": (_I, [_P, _P, _Z, _P]),
+    "fnx_fill_normal": (_I, [_P, _Z, _F, _U64, _U32, _P]),
+    "fnx_dense": (_I, [_P, _I, _I, _P, _I, _I, _P, _F, _P, _I, _I, _P, _P]),
+    "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
+    "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
+    "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "fnx_attn_prep_append": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P]),
+    "fnx_attn_scratch_bytes": (_Z, [_I, _I, _I]),
+    "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "fnx_gdn_core": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _P]),
+    "fnx_argmax": (_I, [_P, _I, _I, _P, _P, _P, _P]),
+    "fnx_top_tokens": (_I, [_P, _I, _I, _P, _P, _P]),
+    "fnx_embed_rows": (_I, [_P, _P, _I, _I, _P, _P]),
+    "fnx_rmsnorm": (_I, [_P, _P, _P, _I, _I, _F, _P]),
+    "fnx_lookup_draft": (_I, [_P, _P, _I, _P, _P, _P, _P]),
+    "fnx_accept_greedy": (_I, [_P, _P, _P, _I, _P, _P]),
+    "fnx_accept_sample": (_I, [_P, _P, _P, _I, Sampling, _P, _P, _P, _U64, _U32, _P, _P, _P]),
+    "fnx_engine_create": (_I, [C.POINTER(ModelConfig), C.POINTER(_P)]),
+    "fnx_engine_destroy": (None, [_P]),
+    "fnx_engine_init_synthetic": (_I, [_P, _U64, _F]),
+    "fnx_engine_device_bytes": (_Z, [_P]),
+    "fnx_engine_tensor": (_P, [_P, C.c_char_p, C.POINTER(_Z)]),
+    "fnx_engine_reset": (_I, [_P, _I]),
+    "fnx_engine_verify": (_I, [_P, _I, _P, _P, _I, _P]),
+    "fnx_engine_commit": (_I, [_P, _I, _P, _I]),
+    "fnx_engine_draft": (_I, [_P, _I, _I, _P]),
+    "fnx_engine_last_ms": (_F, [_P]),
+    "fnx_engine_pos": (_I, [_P, _I]),
+    "fnx_engine_stream": (_P, [_P]),
+    "fnx_comm_unique_id": (_I, [_P]),
+    "fnx_engine_comm_init": (_I, [_P, _P, _I, _I]),
+    "fnx_allreduce": (_I, [_P, _P, _Z, _P]),
+}
+EXPORTS = tuple(_PROTOS)
+
+
+def lib() -> C.CDLL:
+    """The C-ABI library.  Raises when it has not been built: there is no other implementation to fall back to."""
+    global _LIB
+    if _LIB is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python {_HERE / 'build.py'}`")
+        L = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in _PROTOS.items():
+            f = getattr(L, name)
+            f.restype = res
+            f.argtypes = args
+        _LIB = L
+    return _LIB
+
+
+class FnxError(RuntimeError):
+    pass
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise FnxError(f"fnx_b200 error {rc}: {lib().fnx_last_error().decode()}")
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor / numpy array, or None."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return C.c_void_p(t.data_ptr())
+    return C.c_void_p(t.ctypes.data)
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# ------------------------------------------------------------------------------------------------ weights
+def iq3s_bytes(rows: int, cols: int) -> int:
+    return rows * (cols // 256) * IQ3S_BLOCK
+
+
+def iq3s_retile(ggml, rows: int, cols: int):
+    """GGML IQ3_S blocks (uint8 cuda tensor) -> the device tile layout."""
+    import torch
+    out = torch.empty(iq3s_bytes(rows, cols), dtype=torch.uint8, device=ggml.device)
+    check(lib().fnx_iq3s_retile(ptr(ggml), ptr(out), rows, cols, _stream()))
+    return out
+
+
+def iq3s_untile(tiles, rows: int, cols: int):
+    import torch
+    out = torch.empty(iq3s_bytes(rows, cols), dtype=torch.uint8, device=tiles.device)
+    check(lib().fnx_iq3s_untile(ptr(tiles), ptr(out), rows, cols, _stream()))
+    return out
+
+
+def iq3s_dequant_tiles(tiles, rows: int, cols: int):
+    import torch
+    out = torch.empty((rows, cols), dtype=torch.float32, device=tiles.device)
+    check(lib().fnx_iq3s_dequant_tiles(ptr(tiles), ptr(out), rows, cols, _stream()))
+    return out
+
+
+def iq3s_quantize(w):
+    """f32 cuda tensor (numel a multiple of 256) -> GGML IQ3_S blocks (fixture quantiser)."""
+    import torch
+    out = torch.empty(w.numel() // 256 * IQ3S_BLOCK, dtype=torch.uint8, device=w.device)
+    check(lib().fnx_iq3s_quantize(ptr(w), ptr(out), w.numel(), _stream()))
+    return out
+
+
+def fill_normal(out, sigma: float, seed: int, stream_id: int):
+    check(lib().fnx_fill_normal(ptr(out), out.numel(), sigma, seed, stream_id, _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ operators
+def new_err(device="cuda"):
+    import torch
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def dense(W, rows: int, cols: int, x, norm_w=None, eps: float = 1e-6, out=None, accumulate: bool = False, err=None):
+    """y[t] (+)= W . x[t] (x optionally RMS-normed with norm_w first): q8s_gemv / mmvq of the reference."""
+    import torch
+    T = x.shape[0]
+    if out is None:
+        out = torch.zeros((T, rows), dtype=torch.float32, device=x.device)
+    err = new_err(x.device) if err is None else err
+    for t0 in range(0, T, 8):
+        nt = min(8, T - t0)
+        check(lib().fnx_dense(ptr(W), rows, cols, ptr(x[t0:]), x.stride(0), nt, ptr(norm_w), eps, ptr(out[t0:]), out.stride(0),
+                              1 if accumulate else 0, ptr(err), _stream()))
+    return out, err
+
+
+def router_route(Wr, x, K: int, norm_w=None, eps: float = 1e-6, e_lo: int = 0, e_hi=None, add_shared: bool = True, err=None):
+    import torch
+    T, H = x.shape
+    E = Wr.shape[0] - 1
+    e_hi = E if e_hi is None else e_hi
+    dev = x.device
+    logits = torch.empty((T, E + 1), dtype=torch.float32, device=dev)
+    topi = torch.empty((T, K), dtype=torch.int32, device=dev)
+    topw = torch.empty((T, K), dtype=torch.float32, device=dev)
+    njobs_max = T * K + (T + JOB_TOK - 1) // JOB_TOK
+    jobs = torch.zeros(njobs_max * C.sizeof(Job), dtype=torch.uint8, device=dev)
+    njobs = torch.zeros(2, dtype=torch.int32, device=dev)
+    err = new_err(dev) if err is None else err
+    check(lib().fnx_router_route(ptr(Wr), ptr(x), ptr(norm_w), eps, T, E, H, K, e_lo, e_hi, 1 if add_shared else 0, ptr(logits), ptr(topi),
+                                 ptr(topw), ptr(jobs), ptr(njobs), ptr(err), _stream()))
+    return dict(logits=logits, topi=topi, topw=topw, jobs=jobs, njobs=njobs, njobs_max=njobs_max, err=err)
+
+
+def moe_experts(Wgu, Wdn, Wsh_gu, Wsh_dn, route, x, F: int, K: int, norm_w=None, eps: float = 1e-6, e_base: int = 0, e_lo: int = 0,
+                e_hi=None, add_shared: bool = True):
+    """gate|up + SwiGLU, down and combine over a routing result: returns (out [T][H], h, part)."""
+    import torch
+    T, H = x.shape
+    E = route["logits"].shape[1] - 1
+    e_hi = E if e_hi is None else e_hi
+    P = T * K + T
+    gu_stride, dn_stride = iq3s_bytes(2 * F, H), iq3s_bytes(H, F)
+    h = torch.zeros((P, F), dtype=torch.float32, device=x.device)
+    part = torch.zeros((P, H), dtype=torch.float32, device=x.device)
+    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    L = lib()
+    check(L.fnx_moe_gate_up(ptr(Wgu), gu_stride, e_base, ptr(Wsh_gu), E, ptr(route["jobs"]), ptr(route["njobs"]), route["njobs_max"], ptr(x),
+                            ptr(norm_w), eps, H, F, ptr(h), ptr(route["err"]), _stream()))
+    check(L.fnx_moe_down(ptr(Wdn), dn_stride, e_base, ptr(Wsh_dn), E, ptr(route["jobs"]), ptr(route["njobs"]), route["njobs_max"], ptr(h), H, F,
+                         ptr(part), ptr(route["err"]), _stream()))
+    check(L.fnx_moe_combine(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, e_lo, e_hi,
+                            1 if add_shared else 0, ptr(out), 0, _stream()))
+    return out, h, part
+
+
+def attn_prep_append(qg, k, v, q_norm, k_norm, kc, vc, pos0, depth=None, nrot: int = 64, eps: float = 1e-6, rope_base: float = 1e7):
+    """In place on qg [T][nq][2 hd] and k [T][nkv][hd]; appends f16 rows to kc / vc [rows][nkv][hd]."""
+    T, nq, hd2 = qg.shape
+    nkv, hd = k.shape[1], k.shape[2]
+    check(lib().fnx_attn_prep_append(ptr(qg), nq * hd2, ptr(k), nkv * hd, ptr(v), nkv * hd, ptr(q_norm), ptr(k_norm), ptr(kc), ptr(vc), T, nq,
+                                     nkv, hd, nrot, ptr(pos0), ptr(depth), eps, rope_base, _stream()))
+
+
+def attn(qg, kc, vc, pos0, parent=None, scratch=None):
+    import torch
+    T, nq, hd2 = qg.shape
+    nkv, hd = kc.shape[1], kc.shape[2]
+    out = torch.empty((T, nq, hd), dtype=torch.float32, device=qg.device)
+    if scratch is None:
+        scratch = torch.empty(lib().fnx_attn_scratch_bytes(T, nq, hd), dtype=torch.uint8, device=qg.device)
+    check(lib().fnx_attn(ptr(qg), nq * hd2, ptr(kc), ptr(vc), ptr(out), T, nq, nkv, hd, ptr(pos0), ptr(parent), ptr(scratch), _stream()))
+    return out
+
+
+def gdn_core(qkvz, ab, hist_pool, convw, dt, a, nw, S_pool, cur, parent, nk: int, nv: int, hs: int = 128, eps: float = 1e-6):
+    import torch
+    T = qkvz.shape[0]
+    y = torch.empty((T, nv * hs), dtype=torch.float32, device=qkvz.device)
+    check(lib().fnx_gdn_core(ptr(qkvz), qkvz.stride(0), ptr(ab), ab.stride(0), ptr(hist_pool), ptr(convw), ptr(dt), ptr(a), ptr(nw), ptr(S_pool),
+                             ptr(cur), S_pool.shape[0], ptr(parent), ptr(y), nk, nv, hs, T, eps, _stream()))
+    return y
+
+
+def argmax(logits, err=None):
+    import torch
+    T, V = logits.shape
+    bi = torch.empty(T, dtype=torch.int32, device=logits.device)
+    bv = torch.empty(T, dtype=torch.float32, device=logits.device)
+    err = new_err(logits.device) if err is None else err
+    check(lib().fnx_argmax(ptr(logits), T, V, ptr(bi), ptr(bv), ptr(err), _stream()))
+    return bi, bv, err
+
+
+def top_tokens(logits):
+    import torch
+    T, V = logits.shape
+    ov = torch.empty((T, TOPK_N), dtype=torch.float32, device=logits.device)
+    oi = torch.empty((T, TOPK_N), dtype=torch.int32, device=logits.device)
+    check(lib().fnx_top_tokens(ptr(logits), T, V, ptr(ov), ptr(oi), _stream()))
+    return ov, oi
+
+
+def lookup_draft(ctx, n, lk: int, d1=None):
+    """ctx int32 cuda tensor, n int32[1] (tokens in ctx), d1 int32[1] or None -> (drafts list, match)."""
+    import torch
+    out = torch.zeros(MAX_ROWS, dtype=torch.int32, device=ctx.device)
+    out_n = torch.zeros(2, dtype=torch.int32, device=ctx.device)
+    check(lib().fnx_lookup_draft(ptr(ctx), ptr(n), lk, ptr(d1), ptr(out), ptr(out_n), _stream()))
+    cnt, match = out_n.tolist()
+    return out[:cnt].tolist(), match
+
+
+def _unpack_result(result):
+    r = result.tolist()
+    n = r[0]
+    return n, r[1:1 + n], r[1 + MAX_ROWS:1 + MAX_ROWS + n]
+
+
+def accept_greedy(tok, parent, best):
+    import torch
+    result = torch.zeros(1 + 2 * MAX_ROWS, dtype=torch.int32, device=tok.device)
+    check(lib().fnx_accept_greedy(ptr(tok), ptr(parent), ptr(best), tok.numel(), ptr(result), _stream()))
+    return _unpack_result(result)
+
+
+def accept_sample(cand_v, cand_i, tok, s: Sampling, seed: int, seq: int, step, q_ids=None, q_p=None, q_n=None):
+    import torch
+    result = torch.zeros(1 + 2 * MAX_ROWS, dtype=torch.int32, device=tok.device)
+    check(lib().fnx_accept_sample(ptr(cand_v), ptr(cand_i), ptr(tok), tok.numel(), s, ptr(q_ids), ptr(q_p), ptr(q_n), seed, seq, ptr(step),
+                                  ptr(result), _stream()))
+    return _unpack_result(result)
+
+
+# ------------------------------------------------------------------------------------------------ engine
+class Engine:
+    """Engine::verify / commit / draft of the reference (engine/src/engine.hpp:50-229) over the C ABI."""
+
+    def __init__(self, cfg: ModelConfig):
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        check(lib().fnx_engine_create(C.byref(cfg), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().fnx_engine_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def init_synthetic(self, seed: int = 0, sigma: float = 0.02):
+        check(lib().fnx_engine_init_synthetic(self._h, seed, sigma))
+
+    def device_bytes(self) -> int:
+        return lib().fnx_engine_device_bytes(self._h)
+
+    def tensor(self, name: str, dtype, shape=None):
+        """A torch view of one of the engine's device tensors (no copy)."""
+        import torch
+        nbytes = C.c_size_t(0)
+        p = lib().fnx_engine_tensor(self._h, name.encode(), C.byref(nbytes))
+        if not p:
+            raise KeyError(name)
+        n = nbytes.value // torch.empty(0, dtype=dtype).element_size()
+
+        class _Holder:
+            pass
+        h = _Holder()
+        h.__cuda_array_interface__ = {"shape": (n,), "typestr": {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1",
+                                                                 torch.float16: "<f2"}[dtype], "data": (p, False), "version": 2}
+        t = torch.as_tensor(h, device="cuda")
+        return t if shape is None else t.view(shape)
+
+    def reset(self, seq: int = 0):
+        check(lib().fnx_engine_reset(self._h, seq))
+
+    def verify(self, tokens, parents=None, seq: int = 0, want_result: bool = True):
+        T = len(tokens)
+        tok = (C.c_int * T)(*tokens)
+        par = (C.c_int * T)(*parents) if parents is not None else None
+        res = (C.c_int * (1 + 2 * MAX_ROWS))() if want_result else None
+        check(lib().fnx_engine_verify(self._h, seq, tok, par, T, res))
+        if not want_result:
+            return None
+        n = res[0]
+        return n, list(res[1:1 + n]), list(res[1 + MAX_ROWS:1 + MAX_ROWS + n])
+
+    def commit(self, path, seq: int = 0):
+        n = len(path)
+        check(lib().fnx_engine_commit(self._h, seq, (C.c_int * n)(*path), n))
+
+    def draft(self, k: int, seq: int = 0):
+        out = (C.c_int * k)()
+        check(lib().fnx_engine_draft(self._h, seq, k, out))
+        return list(out)
+
+    def last_ms(self) -> float:
+        return lib().fnx_engine_last_ms(self._h)
+
+    def pos(self, seq: int = 0) -> int:
+        return lib().fnx_engine_pos(self._h, seq)
+
+    def prefill(self, tokens, seq: int = 0):
+        """Reads a prompt by running it through chained verify windows and keeping every row."""
+        R = self.cfg.max_rows
+        for i in range(0, len(tokens), R):
+            w = list(tokens[i:i + R])
+            self.verify(w, None, seq, want_result=False)
+            self.commit(list(range(len(w))), seq)

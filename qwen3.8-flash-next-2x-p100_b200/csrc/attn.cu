@@ -1,0 +1,239 @@
+// Gated attention for a verify window: per-head norm + rotary + KV append, then tree-masked split-K attention.
+//
+// fnx_attn_prep_append replaces attn_prep_append / k_attn_prep_append (engine/src/kernels.hpp:259,
+// engine/src/kernels.cu:1880-1910; norm_rope :513-530).  fnx_attn replaces attn / k_attn_part + k_attn_local +
+// k_attn_combine (engine/src/kernels.hpp:238, engine/src/kernels.cu:558-667, 786-803): the same online-softmax
+// split over positions, except that one block serves every row of the window for its share of the positions (the
+// K and V rows are read once per window, not once per row), the cache is not split across cards by position, and
+// a row may see only the window rows on its path to the root (the reference's windows are chains).
+#include "fnx_common.cuh"
+
+namespace fnxb {
+
+// ------------------------------------------------------------------------------------------------ prep + append
+__global__ void k_attn_prep_append(float* __restrict__ qg, int ldq, float* __restrict__ k, int ldk, const float* __restrict__ v, int ldv,
+                                   const float* __restrict__ qn, const float* __restrict__ kn, __half* __restrict__ kc,
+                                   __half* __restrict__ vc, int nq, int nkv, int hd, int nrot, const int* __restrict__ pos0p,
+                                   const int* __restrict__ depth, float eps, float rope_base) {
+    extern __shared__ float xrow[];   // hd floats
+    __shared__ float red[32];
+    const int t = blockIdx.y, h = blockIdx.x, i = threadIdx.x, pos0 = *pos0p;
+    const int pos = pos0 + (depth ? depth[t] : t);
+    const size_t crow = (size_t) (pos0 + t) * nkv * hd;
+    if (h >= nq + nkv) {   // a V head: store only
+        const int kvh = h - nq - nkv;
+        vc[crow + (size_t) kvh * hd + i] = __float2half_rn(v[(size_t) t * ldv + (size_t) kvh * hd + i]);
+        return;
+    }
+    float* x = h < nq ? qg + (size_t) t * ldq + (size_t) h * 2 * hd : k + (size_t) t * ldk + (size_t) (h - nq) * hd;
+    const float* w = h < nq ? qn : kn;
+    const float val = x[i];
+    float ss = warp_sum(val * val);
+    if ((i & 31) == 0) red[i >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int j = 0; j < hd / 32; ++j) ss += red[j];
+    xrow[i] = val * rsqrtf(ss / (float) hd + eps) * w[i];
+    __syncthreads();
+    float y = xrow[i];
+    if (i < nrot) {
+        const int pr = i < nrot / 2 ? i : i - nrot / 2;
+        const float fe = powf(rope_base, -2.0f * (float) pr / (float) nrot);
+        float sn, cs;
+        sincosf((float) pos * fe, &sn, &cs);
+        const float x0 = xrow[pr], x1 = xrow[pr + nrot / 2];
+        y = i < nrot / 2 ? x0 * cs - x1 * sn : x0 * sn + x1 * cs;
+    }
+    x[i] = y;
+    if (h >= nq) kc[crow + (size_t) (h - nq) * hd + i] = __float2half_rn(y);
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+constexpr int ATT_CH = 32;        // positions per chunk
+constexpr int ATT_ROWS = 5;       // window rows one block serves
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_MAXQ = 8;       // q heads per KV head
+
+struct AttPartial {   // one (row, head, split)
+    float m, z;
+};
+
+// scratch: acc [T][nq][S][hd] floats, then mz [T][nq][S]
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restrict__ qg, int ldq, const __half* __restrict__ kc,
+                                                           const __half* __restrict__ vc, float* __restrict__ acc_out,
+                                                           AttPartial* __restrict__ mz_out, int T, int nq, int nkv, int hd,
+                                                           const int* __restrict__ pos0p, const int* __restrict__ parent) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int s = blockIdx.x, S = gridDim.x, kvh = blockIdx.y, r0 = blockIdx.z * ATT_ROWS;
+    const int nr = min(ATT_ROWS, T - r0), qpk = nq / nkv, NQ = nr * qpk;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pos0 = *pos0p, ctx = pos0 + T;
+    const int KS = hd + 8;   // padded K row (halves): 16-byte reads by 8 lanes land in 8 different bank groups
+    float* qs = reinterpret_cast<float*>(smem);                        // [ATT_ROWS * ATT_MAXQ][hd]
+    __half* Ks = reinterpret_cast<__half*>(qs + ATT_ROWS * ATT_MAXQ * hd);   // [ATT_CH][KS]
+    __half* Vs = Ks + ATT_CH * KS;                                     // [ATT_CH][hd]
+    float* es = reinterpret_cast<float*>(Vs + ATT_CH * hd);            // [NQ max][ATT_CH]
+    float* fs = es + ATT_ROWS * ATT_MAXQ * ATT_CH;                     // rescale per query
+    float* ms = fs + ATT_ROWS * ATT_MAXQ;                              // running max
+    float* zs = ms + ATT_ROWS * ATT_MAXQ;                              // running sum
+    unsigned* see = reinterpret_cast<unsigned*>(zs + ATT_ROWS * ATT_MAXQ);   // per local row: window rows it sees
+    for (int i = tid; i < NQ * hd; i += ATT_THREADS) {
+        const int qi = i / hd, d = i % hd, r = qi / qpk, hh = qi % qpk;
+        qs[i] = qg[(size_t) (r0 + r) * ldq + (size_t) (kvh * qpk + hh) * 2 * hd + d];
+    }
+    if (tid < NQ) { ms[tid] = -INFINITY; zs[tid] = 0.f; }
+    if (tid < nr) {
+        unsigned m = 0;
+        for (int a = r0 + tid; a >= 0; a = parent ? parent[a] : a - 1) m |= 1u << a;
+        see[tid] = m;
+    }
+    float acc[ATT_ROWS * ATT_MAXQ];
+#pragma unroll
+    for (int i = 0; i < ATT_ROWS * ATT_MAXQ; ++i) acc[i] = 0.f;
+    // this block's chunks: a contiguous share of the ceil(ctx / 32) chunks
+    const int nch = (ctx + ATT_CH - 1) / ATT_CH;
+    const int c0 = (int) ((long long) nch * s / S), c1 = (int) ((long long) nch * (s + 1) / S);
+    const float scale = rsqrtf((float) hd);
+    for (int c = c0; c < c1; ++c) {
+        const int p0 = c * ATT_CH, np = min(ATT_CH, ctx - p0);
+        __syncthreads();
+        // K and V rows of the chunk, 16 bytes per thread per step
+        for (int i = tid; i < ATT_CH * hd / 8; i += ATT_THREADS) {
+            const int pp = i / (hd / 8), d8 = i % (hd / 8);
+            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+            if (pp < np) {
+                const size_t g = ((size_t) (p0 + pp) * nkv + kvh) * hd + d8 * 8;
+                kv4 = *reinterpret_cast<const uint4*>(kc + g);
+                vv4 = *reinterpret_cast<const uint4*>(vc + g);
+            }
+            *reinterpret_cast<uint4*>(Ks + pp * KS + d8 * 8) = kv4;
+            *reinterpret_cast<uint4*>(Vs + pp * hd + d8 * 8) = vv4;
+        }
+        __syncthreads();
+        // scores: warp w takes queries w, w + 8, ...; lane = position
+        for (int qi = warp; qi < NQ; qi += ATT_THREADS / 32) {
+            const float* q = qs + qi * hd;
+            const __half* kr = Ks + lane * KS;
+            float sacc = 0.f;
+            for (int d = 0; d < hd; d += 8) {
+                const uint4 kk = *reinterpret_cast<const uint4*>(kr + d);
+                const float4 q0 = *reinterpret_cast<const float4*>(q + d), q1 = *reinterpret_cast<const float4*>(q + d + 4);
+                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk.x));
+                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
+                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk.z));
+                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk.w));
+                sacc = fmaf(q0.x, k0.x, sacc); sacc = fmaf(q0.y, k0.y, sacc);
+                sacc = fmaf(q0.z, k1.x, sacc); sacc = fmaf(q0.w, k1.y, sacc);
+                sacc = fmaf(q1.x, k2.x, sacc); sacc = fmaf(q1.y, k2.y, sacc);
+                sacc = fmaf(q1.z, k3.x, sacc); sacc = fmaf(q1.w, k3.y, sacc);
+            }
+            const int p = p0 + lane, r = qi / qpk;
+            const bool vis = lane < np && (p < pos0 || ((see[r] >> (p - pos0)) & 1u));
+            const float sv = vis ? sacc * scale : -INFINITY;
+            const float mo = ms[qi], mn = fmaxf(mo, warp_max(sv));
+            const float w = sv == -INFINITY ? 0.f : expf(sv - mn);
+            const float f = mo == -INFINITY ? 0.f : expf(mo - mn);
+            const float zn = zs[qi] * f + warp_sum(w);
+            es[qi * ATT_CH + lane] = w;
+            __syncwarp();
+            if (lane == 0) { ms[qi] = mn; zs[qi] = zn; fs[qi] = f; }
+        }
+        __syncthreads();
+        // values: thread = dimension (hd == ATT_THREADS), all queries
+        for (int d = tid; d < hd; d += ATT_THREADS) {
+#pragma unroll
+            for (int qi = 0; qi < ATT_ROWS * ATT_MAXQ; ++qi)
+                if (qi < NQ) acc[qi] *= fs[qi];
+            for (int pp = 0; pp < ATT_CH; ++pp) {
+                const float vv = __half2float(Vs[pp * hd + d]);
+#pragma unroll
+                for (int qi = 0; qi < ATT_ROWS * ATT_MAXQ; ++qi)
+                    if (qi < NQ) acc[qi] = fmaf(es[qi * ATT_CH + pp], vv, acc[qi]);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < hd) {
+#pragma unroll
+        for (int qi = 0; qi < ATT_ROWS * ATT_MAXQ; ++qi)
+            if (qi < NQ) {
+                const int r = qi / qpk, hh = qi % qpk;
+                const size_t slot = ((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s;
+                acc_out[slot * hd + tid] = acc[qi];
+            }
+    }
+    if (tid < NQ) {
+        const int r = tid / qpk, hh = tid % qpk;
+        mz_out[((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s] = AttPartial{ms[tid], zs[tid]};
+    }
+}
+
+// merge the splits of (row, head): out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) z_s * sigmoid(gate)
+__global__ void k_attn_combine(const float* __restrict__ acc_in, const AttPartial* __restrict__ mz_in, const float* __restrict__ qg, int ldq,
+                               float* __restrict__ out, int nq, int hd, int S) {
+    const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
+    const size_t base = ((size_t) t * nq + h) * S;
+    float mx = -INFINITY;
+    for (int s = 0; s < S; ++s) mx = fmaxf(mx, mz_in[base + s].m);
+    float z = 0.f, acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+        const AttPartial p = mz_in[base + s];
+        if (p.m == -INFINITY) continue;
+        const float w = expf(p.m - mx);
+        z = fmaf(w, p.z, z);
+        acc = fmaf(w, acc_in[(base + s) * hd + i], acc);
+    }
+    const float gate = qg[(size_t) t * ldq + (size_t) h * 2 * hd + hd + i];
+    out[((size_t) t * nq + h) * hd + i] = acc / z * sigmoidf_(gate);
+}
+
+static int attn_splits(int nkv) {
+    const int s = sm_count() / (nkv > 0 ? nkv : 1);
+    return s < 1 ? 1 : s;
+}
+
+}  // namespace fnxb
+
+using namespace fnxb;
+
+extern "C" int fnx_attn_prep_append(float* qg, int ldq, float* k, int ldk, const float* v, int ldv, const float* q_norm, const float* k_norm,
+                                    void* kc, void* vc, int T, int nq, int nkv, int hd, int nrot, const int* pos0, const int* depth, float eps,
+                                    float rope_base, fnx_stream st) {
+    FNX_REQUIRE(qg && k && v && q_norm && k_norm && kc && vc && pos0, "fnx_attn_prep_append: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_attn_prep_append: %d rows", T);
+    FNX_REQUIRE(hd % 32 == 0 && hd <= 1024 && nrot <= hd && nrot % 2 == 0, "fnx_attn_prep_append: head dim %d, rotary %d", hd, nrot);
+    k_attn_prep_append<<<dim3(nq + 2 * nkv, T), hd, hd * sizeof(float), as_stream(st)>>>(qg, ldq, k, ldk, v, ldv, q_norm, k_norm, (__half*) kc, (__half*) vc,
+                                                                                        nq, nkv, hd, nrot, pos0, depth, eps, rope_base);
+    FNX_LAUNCH_OK("fnx_attn_prep_append");
+    return FNX_OK;
+}
+
+extern "C" size_t fnx_attn_scratch_bytes(int T, int nq, int hd) {
+    const size_t S = (size_t) sm_count();   // an upper bound of the splits for any KV-head count
+    return (size_t) T * nq * S * ((size_t) hd * sizeof(float) + sizeof(AttPartial));
+}
+
+extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd, const int* pos0,
+                        const int* parent, void* scratch, fnx_stream st) {
+    FNX_REQUIRE(qg && kc && vc && out && pos0 && scratch, "fnx_attn: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_attn: %d rows", T);
+    FNX_REQUIRE(hd == ATT_THREADS, "fnx_attn: head dim %d (this build: %d)", hd, ATT_THREADS);
+    FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQ, "fnx_attn: %d q heads over %d KV heads", nq, nkv);
+    const int S = attn_splits(nkv);
+    float* acc = (float*) scratch;
+    AttPartial* mz = (AttPartial*) (acc + (size_t) T * nq * S * hd);
+    const size_t smem = (size_t) ATT_ROWS * ATT_MAXQ * hd * sizeof(float) + (size_t) ATT_CH * (hd + 8) * sizeof(__half) +
+                        (size_t) ATT_CH * hd * sizeof(__half) + (size_t) ATT_ROWS * ATT_MAXQ * (ATT_CH + 3) * sizeof(float) +
+                        ATT_ROWS * sizeof(unsigned);
+    static bool configured = false;
+    if (!configured) {
+        FNX_CUDA_OK(cudaFuncSetAttribute(k_attn_part, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+        configured = true;
+    }
+    k_attn_part<<<dim3(S, nkv, (T + ATT_ROWS - 1) / ATT_ROWS), ATT_THREADS, smem, as_stream(st)>>>(qg, ldq, (const __half*) kc, (const __half*) vc,
+                                                                                                   acc, mz, T, nq, nkv, hd, pos0, parent);
+    FNX_LAUNCH_OK("fnx_attn (partials)");
+    k_attn_combine<<<dim3(nq, T), hd, 0, as_stream(st)>>>(acc, mz, qg, ldq, out, nq, hd, S);
+    FNX_LAUNCH_OK("fnx_attn (combine)");
+    return FNX_OK;
+}

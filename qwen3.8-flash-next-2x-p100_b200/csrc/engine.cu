@@ -1,0 +1,723 @@
+// The window scheduler: a thin re-creation of Engine::verify / commit / draft (engine/src/engine.hpp:50-229;
+// enqueue engine/src/engine.cu:1760-1848, ffn_half :1569-1757, mtp_enqueue :2095-2133; verify
+// engine/src/engine_common.cu:913-1056, commit :710-754, draft :1569-1684) for the synthetic Qwen3-Next-style model:
+// pre-norm residual blocks (RMS norm, eps 1e-6) instead of hyper-connections, every attn_every-th layer gated
+// attention and the others gated DeltaNet, a top-k MoE with a sigmoid-gated shared expert in every layer, one
+// MTP draft layer that shares the head.  One host thread drives one GPU; every window shape is captured once
+// into a CUDA graph (the reference captures one graph per row count too, engine_common.cu:994-1003), window
+// scalars live in device memory, and expert-parallel ranks add their partial sums with one all-reduce per layer.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "fnx_common.cuh"
+#include "iq3s_tile.h"
+
+namespace fnxb {
+
+// ---- NCCL through dlopen: the library has no link-time dependency on it; single-GPU use never loads it
+struct NcclId { char b[128]; };
+struct Nccl {
+    void* lib = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, NcclId, int) = nullptr;   // ncclUniqueId: 128 bytes, passed by value
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+
+static Nccl* nccl() {
+    static Nccl n;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        n.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!n.lib) n.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (n.lib) {
+            n.GetUniqueId = (int (*)(void*)) dlsym(n.lib, "ncclGetUniqueId");
+            n.CommInitRank = (int (*)(void**, int, NcclId, int)) dlsym(n.lib, "ncclCommInitRank");
+            n.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t)) dlsym(n.lib, "ncclAllReduce");
+            n.CommDestroy = (int (*)(void*)) dlsym(n.lib, "ncclCommDestroy");
+            n.GetErrorString = (const char* (*) (int) ) dlsym(n.lib, "ncclGetErrorString");
+        }
+    }
+    return n.lib && n.GetUniqueId && n.CommInitRank && n.AllReduce ? &n : nullptr;
+}
+
+struct LayerW {
+    bool attn = false;
+    float *norm1 = nullptr, *norm2 = nullptr;
+    // mixer
+    uint8_t *w_in = nullptr, *w_out = nullptr;   // attention: [q|gate per head; k; v] x H and H x (nq hd); DeltaNet: [q|k|v|z|alpha|beta] x H and H x (nv hs)
+    int in_rows = 0;
+    float *qn = nullptr, *kn = nullptr;          // attention head norms
+    __half *kc = nullptr, *vc = nullptr;         // [n_seq][cache_rows][nkv hd]
+    float *convw = nullptr, *dt = nullptr, *a = nullptr, *gnorm = nullptr;
+    float *S_pool = nullptr, *hist_pool = nullptr;   // [n_seq][NS]...
+    // MoE
+    float* wr = nullptr;
+    uint8_t *wgu = nullptr, *wdn = nullptr, *wsh_gu = nullptr, *wsh_dn = nullptr;
+};
+
+struct SeqState {
+    int pos = 0, cur = 0;
+    int last_T = 0;              // rows of the last verify window
+    int kept = 0;                // rows kept by the last commit
+    int kept_pos0 = 0;           // position of the first kept row
+};
+
+}  // namespace fnxb
+
+using namespace fnxb;
+
+struct fnx_engine {
+    fnx_model_config c{};
+    cudaStream_t st = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+    size_t bytes = 0;
+    std::vector<void*> owned;
+    std::map<std::string, std::pair<void*, size_t>> tensors;
+    std::vector<LayerW> layers;
+    LayerW mtp;
+    float *mtp_hnorm = nullptr, *mtp_enorm = nullptr, *mtp_onorm = nullptr, *out_norm = nullptr;
+    uint8_t *mtp_fc_hid = nullptr, *mtp_fc_emb = nullptr, *head = nullptr;
+    __half* embed = nullptr;
+    std::vector<SeqState> seqs;
+    int NS = 0, cache_rows = 0, E_local = 0, e_lo = 0, e_hi = 0;
+    size_t gu_bytes = 0, dn_bytes = 0;
+    // window buffers
+    float *R = nullptr, *Rm = nullptr, *Rsrc = nullptr, *Emb = nullptr, *proj = nullptr, *mix = nullptr, *logits = nullptr;
+    float *rlogits = nullptr, *topw = nullptr, *hbuf = nullptr, *part = nullptr, *moe_out = nullptr, *best_v = nullptr, *cand_v = nullptr;
+    int *topi = nullptr, *njobs = nullptr, *best_i = nullptr, *result = nullptr, *d_tok = nullptr, *d_parent = nullptr, *d_depth = nullptr;
+    int *d_pos = nullptr, *d_cur = nullptr, *d_ctx = nullptr, *d_ctx_n = nullptr, *d_path = nullptr, *d_mtok = nullptr, *d_mpos = nullptr;
+    int *cand_i = nullptr, *d_draft = nullptr;
+    fnx_job* jobs = nullptr;
+    unsigned* err = nullptr;
+    void* att_scratch = nullptr;
+    int *h_stage = nullptr;      // pinned host staging
+    std::map<uint64_t, cudaGraphExec_t> graphs;
+    std::map<int, std::pair<__half**, __half**>> commit_tables;   // per sequence: device tables of its K and V caches
+    void* comm = nullptr;
+    int proj_ld = 0;
+};
+
+namespace fnxb {
+
+template <typename T>
+static int dalloc(fnx_engine* e, T** p, size_t count, const char* name = nullptr) {
+    void* q = nullptr;
+    const size_t bytes = count * sizeof(T);
+    FNX_CUDA_OK(cudaMalloc(&q, bytes ? bytes : 16));
+    FNX_CUDA_OK(cudaMemset(q, 0, bytes ? bytes : 16));
+    e->owned.push_back(q);
+    e->bytes += bytes;
+    *p = (T*) q;
+    if (name) e->tensors[name] = {q, bytes};
+    return FNX_OK;
+}
+
+#define FNX_TRY(expr)              \
+    do {                           \
+        int rc_ = (expr);          \
+        if (rc_ != FNX_OK) return rc_; \
+    } while (0)
+
+static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+__global__ void k_fill_const(float* p, size_t n, float v) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+__global__ void k_f32_to_f16(const float* x, __half* y, size_t n) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __float2half_rn(x[i]);
+}
+__global__ void k_gdn_params(float* dt, float* a, int nv) {
+    const int h = blockIdx.x * blockDim.x + threadIdx.x;
+    if (h < nv) {
+        dt[h] = 0.1f * (float) ((h % 5) - 2);
+        a[h] = -(0.5f + (float) (h % 8) / 8.0f);
+    }
+}
+// dst[j] = src[idx[j]] rows of n floats
+__global__ void k_gather_rows(float* __restrict__ dst, const float* __restrict__ src, const int* __restrict__ idx, int n) {
+    const int j = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[(size_t) j * n + i] = src[(size_t) idx[j] * n + i];
+}
+__global__ void k_add_rows(float* __restrict__ dst, const float* __restrict__ src, size_t n) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] += src[i];
+}
+// depth of every window row from the parent array (parent null: a chain)
+__global__ void k_depths(const int* __restrict__ parent, int* __restrict__ depth, int T) {
+    const int t = threadIdx.x;
+    if (t >= T) return;
+    int d = 0;
+    for (int a = parent ? parent[t] : t - 1; a >= 0; a = parent ? parent[a] : a - 1) ++d;
+    depth[t] = d;
+}
+// commit: the kept rows' K and V move to consecutive cache rows (a no-op for a chain), the kept rows' tokens join
+// the context followed by the token the window emitted last (the next window's first row, as the reference's ctx
+// keeps it, engine/src/session.cpp:501), the state slot advances.  One block per attention layer + one for the
+// bookkeeping.
+__global__ void k_commit(__half* const* __restrict__ kcs, __half* const* __restrict__ vcs, int nlayer, int row_halves,
+                         const int* __restrict__ path, const int* __restrict__ tok, const int* __restrict__ emitted, int n,
+                         int* __restrict__ pos, int* __restrict__ cur, int NS, int* __restrict__ ctx, int* __restrict__ ctx_n) {
+    const int l = blockIdx.x, p0 = *pos;
+    if (l < nlayer) {
+        for (int j = 0; j < n; ++j) {
+            const int src = path[j];
+            if (src == j) continue;   // path is increasing, so row j's source is never overwritten before it is read
+            for (int i = threadIdx.x; i < row_halves; i += blockDim.x) {
+                kcs[l][(size_t) (p0 + j) * row_halves + i] = kcs[l][(size_t) (p0 + src) * row_halves + i];
+                vcs[l][(size_t) (p0 + j) * row_halves + i] = vcs[l][(size_t) (p0 + src) * row_halves + i];
+            }
+            __syncthreads();
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        const int cn = *ctx_n;
+        for (int j = 0; j < n; ++j) ctx[cn + j] = tok[path[j]];
+        ctx[cn + n] = emitted[n - 1];
+        *ctx_n = cn + n;
+        *cur = (*cur + 1 + path[n - 1]) % NS;
+    }
+}
+__global__ void k_advance_pos(int* pos, int n) { *pos += n; }
+
+struct Dims {
+    int H, E, K, F, nq, nkv, hd, nrot, nk, nv, hs, V, MAXR, q_rows, kv_rows, attn_in, gdn_ch, gdn_in, P;
+};
+static Dims dims(const fnx_model_config& c) {
+    Dims d;
+    d.H = c.hidden; d.E = c.n_expert; d.K = c.top_k; d.F = c.ffn;
+    d.nq = c.n_q_head; d.nkv = c.n_kv_head; d.hd = c.head_dim; d.nrot = c.n_rot;
+    d.nk = c.gdn_k_head; d.nv = c.gdn_v_head; d.hs = c.gdn_head_dim; d.V = c.vocab; d.MAXR = c.max_rows;
+    d.q_rows = d.nq * 2 * d.hd;
+    d.kv_rows = d.nkv * d.hd;
+    const int tile_rows = 16 * (16 / (c.hidden / 256));   // output rows per step of the dense kernel at K = hidden
+    d.attn_in = round_up(d.q_rows + 2 * d.kv_rows, tile_rows);
+    d.gdn_ch = (2 * d.nk + d.nv) * d.hs;
+    d.gdn_in = round_up(d.gdn_ch + d.nv * d.hs + 2 * d.nv, tile_rows);
+    d.P = d.MAXR * d.K + d.MAXR;   // expert output rows: pairs + the shared expert's
+    return d;
+}
+
+// an IQ3_S tile matrix of N(0, sigma) weights: generate, quantise, re-tile, in chunks of whole 16-row tiles
+static int synth_iq3s(fnx_engine* e, uint8_t* dst, size_t rows, size_t cols, float sigma, uint64_t seed, uint32_t stream_id, float* tmp_f,
+                      uint8_t* tmp_g, size_t tmp_weights) {
+    size_t chunk_rows = tmp_weights / cols / 16 * 16;
+    if (chunk_rows == 0) return fail(FNX_E_ARG, "synthetic init: staging buffer too small for %zu columns", cols);
+    uint32_t sub = 0;
+    for (size_t r0 = 0; r0 < rows; r0 += chunk_rows, ++sub) {
+        const size_t nr = rows - r0 < chunk_rows ? rows - r0 : chunk_rows;
+        FNX_TRY(fnx_fill_normal(tmp_f, nr * cols, sigma, seed, stream_id + sub, e->st));
+        FNX_TRY(fnx_iq3s_quantize(tmp_f, tmp_g, nr * cols, e->st));
+        FNX_TRY(fnx_iq3s_retile(tmp_g, dst + iq3s_bytes(r0, cols), nr, cols, e->st));
+    }
+    return FNX_OK;
+}
+
+static int alloc_layer(fnx_engine* e, LayerW& L, bool attn, const std::string& pre) {
+    const Dims d = dims(e->c);
+    const int ns = e->c.n_seq;
+    L.attn = attn;
+    FNX_TRY(dalloc(e, &L.norm1, d.H, (pre + "norm1").c_str()));
+    FNX_TRY(dalloc(e, &L.norm2, d.H, (pre + "norm2").c_str()));
+    if (attn) {
+        L.in_rows = d.attn_in;
+        FNX_TRY(dalloc(e, &L.w_in, iq3s_bytes(d.attn_in, d.H), (pre + "w_in").c_str()));
+        FNX_TRY(dalloc(e, &L.w_out, iq3s_bytes(d.H, d.nq * d.hd), (pre + "w_out").c_str()));
+        FNX_TRY(dalloc(e, &L.qn, d.hd, (pre + "q_norm").c_str()));
+        FNX_TRY(dalloc(e, &L.kn, d.hd, (pre + "k_norm").c_str()));
+        FNX_TRY(dalloc(e, &L.kc, (size_t) ns * e->cache_rows * d.kv_rows, (pre + "k_cache").c_str()));
+        FNX_TRY(dalloc(e, &L.vc, (size_t) ns * e->cache_rows * d.kv_rows, (pre + "v_cache").c_str()));
+    } else {
+        L.in_rows = d.gdn_in;
+        FNX_TRY(dalloc(e, &L.w_in, iq3s_bytes(d.gdn_in, d.H), (pre + "w_in").c_str()));
+        FNX_TRY(dalloc(e, &L.w_out, iq3s_bytes(d.H, d.nv * d.hs), (pre + "w_out").c_str()));
+        FNX_TRY(dalloc(e, &L.convw, (size_t) d.gdn_ch * 4, (pre + "conv_w").c_str()));
+        FNX_TRY(dalloc(e, &L.dt, d.nv, (pre + "dt").c_str()));
+        FNX_TRY(dalloc(e, &L.a, d.nv, (pre + "a").c_str()));
+        FNX_TRY(dalloc(e, &L.gnorm, d.hs, (pre + "g_norm").c_str()));
+        FNX_TRY(dalloc(e, &L.S_pool, (size_t) ns * e->NS * d.nv * d.hs * d.hs, (pre + "state").c_str()));
+        FNX_TRY(dalloc(e, &L.hist_pool, (size_t) ns * e->NS * 3 * d.gdn_ch, (pre + "conv_hist").c_str()));
+    }
+    FNX_TRY(dalloc(e, &L.wr, (size_t) (d.E + 1) * d.H, (pre + "router").c_str()));
+    FNX_TRY(dalloc(e, &L.wgu, e->gu_bytes * e->E_local, (pre + "experts_gu").c_str()));
+    FNX_TRY(dalloc(e, &L.wdn, e->dn_bytes * e->E_local, (pre + "experts_dn").c_str()));
+    FNX_TRY(dalloc(e, &L.wsh_gu, e->gu_bytes, (pre + "shared_gu").c_str()));
+    FNX_TRY(dalloc(e, &L.wsh_dn, e->dn_bytes, (pre + "shared_dn").c_str()));
+    return FNX_OK;
+}
+
+static int fill_const(fnx_engine* e, float* p, size_t n, float v) {
+    k_fill_const<<<(unsigned) ((n + 255) / 256), 256, 0, e->st>>>(p, n, v);
+    FNX_LAUNCH_OK("fill_const");
+    return FNX_OK;
+}
+
+static int init_layer(fnx_engine* e, LayerW& L, int li, uint64_t seed, float sigma, float* tf, uint8_t* tg, size_t tw) {
+    const Dims d = dims(e->c);
+    auto sid = [&](int kind, int ex) { return (uint32_t) (((li * 16 + kind) << 12) | ex); };
+    FNX_TRY(fill_const(e, L.norm1, d.H, 1.0f));
+    FNX_TRY(fill_const(e, L.norm2, d.H, 1.0f));
+    FNX_TRY(synth_iq3s(e, L.w_in, L.in_rows, d.H, sigma, seed, sid(0, 0), tf, tg, tw));
+    if (L.attn) {
+        FNX_TRY(synth_iq3s(e, L.w_out, d.H, d.nq * d.hd, sigma, seed, sid(1, 0), tf, tg, tw));
+        FNX_TRY(fill_const(e, L.qn, d.hd, 1.0f));
+        FNX_TRY(fill_const(e, L.kn, d.hd, 1.0f));
+    } else {
+        FNX_TRY(synth_iq3s(e, L.w_out, d.H, d.nv * d.hs, sigma, seed, sid(1, 0), tf, tg, tw));
+        FNX_TRY(fnx_fill_normal(L.convw, (size_t) d.gdn_ch * 4, 0.5f, seed, sid(2, 0), e->st));
+        k_gdn_params<<<(d.nv + 63) / 64, 64, 0, e->st>>>(L.dt, L.a, d.nv);
+        FNX_LAUNCH_OK("gdn_params");
+        FNX_TRY(fill_const(e, L.gnorm, d.hs, 1.0f));
+    }
+    FNX_TRY(fnx_fill_normal(L.wr, (size_t) (d.E + 1) * d.H, sigma, seed, sid(3, 0), e->st));
+    for (int x = 0; x < e->E_local; ++x) {
+        const int ge = e->e_lo + x;   // the global expert: every rank draws the same weights for it
+        FNX_TRY(synth_iq3s(e, L.wgu + (size_t) x * e->gu_bytes, 2 * d.F, d.H, sigma, seed, sid(4, ge), tf, tg, tw));
+        FNX_TRY(synth_iq3s(e, L.wdn + (size_t) x * e->dn_bytes, d.H, d.F, sigma, seed, sid(5, ge), tf, tg, tw));
+    }
+    FNX_TRY(synth_iq3s(e, L.wsh_gu, 2 * d.F, d.H, sigma, seed, sid(6, 0), tf, tg, tw));
+    FNX_TRY(synth_iq3s(e, L.wsh_dn, d.H, d.F, sigma, seed, sid(7, 0), tf, tg, tw));
+    return FNX_OK;
+}
+
+// ---- one MoE block on T rows of residual R: R += experts(rmsnorm(R))
+static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
+    const Dims d = dims(e->c);
+    const bool ep = e->c.ep_size > 1;
+    FNX_TRY(fnx_router_route(L.wr, R, L.norm2, e->c.eps, T, d.E, d.H, d.K, e->e_lo, e->e_hi, 1, e->rlogits, e->topi, e->topw, e->jobs, e->njobs,
+                             e->err, e->st));
+    const int njobs_max = T * d.K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+    FNX_TRY(fnx_moe_gate_up(L.wgu, e->gu_bytes, e->e_lo, L.wsh_gu, d.E, e->jobs, e->njobs, njobs_max, R, L.norm2, e->c.eps, d.H, d.F, e->hbuf,
+                            e->err, e->st));
+    FNX_TRY(fnx_moe_down(L.wdn, e->dn_bytes, e->e_lo, L.wsh_dn, d.E, e->jobs, e->njobs, njobs_max, e->hbuf, d.H, d.F, e->part, e->err, e->st));
+    if (!ep) return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, d.E, 1, R, 1, e->st);
+    // expert parallel: this rank's routed addend, summed across ranks, then the (replicated) shared expert
+    FNX_TRY(fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, e->e_lo, e->e_hi, 0, e->moe_out, 0, e->st));
+    FNX_TRY(fnx_allreduce(e, e->moe_out, (size_t) T * d.H, e->st));
+    k_add_rows<<<(unsigned) (((size_t) T * d.H + 255) / 256), 256, 0, e->st>>>(R, e->moe_out, (size_t) T * d.H);
+    FNX_LAUNCH_OK("moe add");
+    return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, 0, 1, R, 1, e->st);
+}
+
+// dense projection of up to MAXR rows in calls of 8
+static int enqueue_dense(fnx_engine* e, const uint8_t* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float* y, int ldy,
+                         int accumulate) {
+    for (int t0 = 0; t0 < T; t0 += 8) {
+        const int nt = T - t0 < 8 ? T - t0 : 8;
+        FNX_TRY(fnx_dense(W, rows, cols, x + (size_t) t0 * ldx, ldx, nt, norm_w, e->c.eps, y + (size_t) t0 * ldy, ldy, accumulate, e->err, e->st));
+    }
+    return FNX_OK;
+}
+
+static int enqueue_attention(fnx_engine* e, const LayerW& L, float* R, int T, int seq, const int* d_parent, const int* d_depth, const int* d_pos) {
+    const Dims d = dims(e->c);
+    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0));
+    __half* kc = L.kc + (size_t) seq * e->cache_rows * d.kv_rows;
+    __half* vc = L.vc + (size_t) seq * e->cache_rows * d.kv_rows;
+    float* qg = e->proj;
+    float* k = e->proj + d.q_rows;
+    float* v = k + d.kv_rows;
+    FNX_TRY(fnx_attn_prep_append(qg, e->proj_ld, k, e->proj_ld, v, e->proj_ld, L.qn, L.kn, kc, vc, T, d.nq, d.nkv, d.hd, d.nrot, d_pos, d_depth,
+                                 e->c.eps, e->c.rope_base, e->st));
+    FNX_TRY(fnx_attn(qg, e->proj_ld, kc, vc, e->mix, T, d.nq, d.nkv, d.hd, d_pos, d_parent, e->att_scratch, e->st));
+    return enqueue_dense(e, L.w_out, d.H, d.nq * d.hd, e->mix, d.nq * d.hd, T, nullptr, R, d.H, 1);
+}
+
+static int enqueue_gdn(fnx_engine* e, const LayerW& L, float* R, int T, int seq, const int* d_parent) {
+    const Dims d = dims(e->c);
+    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0));
+    float* S = L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs;
+    float* hist = L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch;
+    FNX_TRY(fnx_gdn_core(e->proj, e->proj_ld, e->proj + d.gdn_ch + d.nv * d.hs, e->proj_ld, hist, L.convw, L.dt, L.a, L.gnorm, S, e->d_cur + seq,
+                         e->NS, d_parent, e->mix, d.nk, d.nv, d.hs, T, e->c.eps, e->st));
+    return enqueue_dense(e, L.w_out, d.H, d.nv * d.hs, e->mix, d.nv * d.hs, T, nullptr, R, d.H, 1);
+}
+
+// the whole verify window: embed, layers, head, argmax, greedy acceptance
+static int enqueue_verify(fnx_engine* e, int seq, int T, bool tree) {
+    const Dims d = dims(e->c);
+    const int* par = tree ? e->d_parent : nullptr;
+    k_depths<<<1, 32, 0, e->st>>>(par, e->d_depth, T);
+    FNX_LAUNCH_OK("depths");
+    FNX_TRY(fnx_embed_rows(e->embed, e->d_tok, T, d.H, e->R, e->st));
+    for (size_t l = 0; l < e->layers.size(); ++l) {
+        const LayerW& L = e->layers[l];
+        if (L.attn) FNX_TRY(enqueue_attention(e, L, e->R, T, seq, par, e->d_depth, e->d_pos + seq));
+        else FNX_TRY(enqueue_gdn(e, L, e->R, T, seq, par));
+        FNX_TRY(enqueue_moe(e, L, e->R, T));
+    }
+    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0));
+    FNX_TRY(fnx_argmax(e->logits, T, d.V, e->best_i, e->best_v, e->err, e->st));
+    return fnx_accept_greedy(e->d_tok, par, e->best_i, T, e->result, e->st);
+}
+
+// one MTP call on T rows: Rm = fc_hid(rms(src)) + fc_emb(rms(emb(tok))), the draft block, the head on the last row
+static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
+    const Dims d = dims(e->c);
+    FNX_TRY(fnx_embed_rows(e->embed, e->d_mtok, T, d.H, e->Emb, e->st));
+    FNX_TRY(enqueue_dense(e, e->mtp_fc_hid, d.H, d.H, src, d.H, T, e->mtp_hnorm, e->Rm, d.H, 0));
+    FNX_TRY(enqueue_dense(e, e->mtp_fc_emb, d.H, d.H, e->Emb, d.H, T, e->mtp_enorm, e->Rm, d.H, 1));
+    FNX_TRY(enqueue_attention(e, e->mtp, e->Rm, T, seq, nullptr, nullptr, e->d_mpos));
+    FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, T));
+    FNX_TRY(fnx_dense(e->head, d.V, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, d.V, 0, e->err, e->st));
+    return fnx_argmax(e->logits, 1, d.V, e->d_draft, nullptr, e->err, e->st);
+}
+
+template <typename F>
+static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        // a first, uncaptured run: it sets the kernels' launch attributes and is harmless, since a window changes no
+        // committed state (cache rows past the position, state slots other than the current one)
+        FNX_TRY(enqueue());
+        FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+        cudaGraph_t g = nullptr;
+        FNX_CUDA_OK(cudaStreamBeginCapture(e->st, cudaStreamCaptureModeRelaxed));
+        const int rc = enqueue();
+        const cudaError_t ce = cudaStreamEndCapture(e->st, &g);
+        if (rc != FNX_OK) {
+            if (g) cudaGraphDestroy(g);
+            return rc;
+        }
+        if (ce != cudaSuccess) return fail(FNX_E_CUDA, "graph capture: %s", cudaGetErrorString(ce));
+        cudaGraphExec_t x = nullptr;
+        FNX_CUDA_OK(cudaGraphInstantiate(&x, g, 0));
+        cudaGraphDestroy(g);
+        it = e->graphs.emplace(key, x).first;
+    }
+    FNX_CUDA_OK(cudaEventRecord(e->ev0, e->st));
+    FNX_CUDA_OK(cudaGraphLaunch(it->second, e->st));
+    FNX_CUDA_OK(cudaEventRecord(e->ev1, e->st));
+    return FNX_OK;
+}
+
+}  // namespace fnxb
+
+extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) {
+    FNX_REQUIRE(cfg && out, "fnx_engine_create: null pointer");
+    const fnx_model_config& c = *cfg;
+    FNX_REQUIRE(c.hidden % 256 == 0 && c.hidden <= 4096 && c.ffn % 256 == 0, "engine: hidden %d / ffn %d must be multiples of 256", c.hidden, c.ffn);
+    FNX_REQUIRE(c.max_rows >= 1 && c.max_rows <= FNX_MAX_ROWS, "engine: max_rows %d (1..%d)", c.max_rows, FNX_MAX_ROWS);
+    FNX_REQUIRE(c.ep_size >= 1 && c.ep_rank >= 0 && c.ep_rank < c.ep_size && c.n_expert % c.ep_size == 0, "engine: expert-parallel rank %d of %d over %d experts",
+                c.ep_rank, c.ep_size, c.n_expert);
+    FNX_REQUIRE(c.n_seq >= 1 && c.n_layer >= 1 && c.attn_every >= 1, "engine: bad sequence / layer counts");
+    FNX_REQUIRE(c.vocab % (16 * (16 / (c.hidden / 256))) == 0, "engine: vocabulary %d is not a whole number of head tiles", c.vocab);
+    fnx_engine* e = new fnx_engine();
+    e->c = c;
+    const Dims d = dims(c);
+    e->NS = c.max_rows + 1;
+    e->cache_rows = c.max_ctx + c.max_rows;
+    e->E_local = c.n_expert / c.ep_size;
+    e->e_lo = c.ep_rank * e->E_local;
+    e->e_hi = e->e_lo + e->E_local;
+    e->gu_bytes = iq3s_bytes((size_t) 2 * d.F, d.H);
+    e->dn_bytes = iq3s_bytes((size_t) d.H, d.F);
+    e->seqs.resize(c.n_seq);
+    int rc = FNX_OK;
+    auto body = [&]() -> int {
+        FNX_CUDA_OK(cudaStreamCreateWithFlags(&e->st, cudaStreamNonBlocking));
+        FNX_CUDA_OK(cudaEventCreate(&e->ev0));
+        FNX_CUDA_OK(cudaEventCreate(&e->ev1));
+        e->layers.resize(c.n_layer);
+        for (int l = 0; l < c.n_layer; ++l) FNX_TRY(alloc_layer(e, e->layers[l], (l + 1) % c.attn_every == 0, "l" + std::to_string(l) + "."));
+        FNX_TRY(alloc_layer(e, e->mtp, true, "mtp."));
+        FNX_TRY(dalloc(e, &e->mtp_hnorm, d.H, "mtp.h_norm"));
+        FNX_TRY(dalloc(e, &e->mtp_enorm, d.H, "mtp.e_norm"));
+        FNX_TRY(dalloc(e, &e->mtp_onorm, d.H, "mtp.out_norm"));
+        FNX_TRY(dalloc(e, &e->out_norm, d.H, "out_norm"));
+        FNX_TRY(dalloc(e, &e->mtp_fc_hid, iq3s_bytes(d.H, d.H), "mtp.fc_hid"));
+        FNX_TRY(dalloc(e, &e->mtp_fc_emb, iq3s_bytes(d.H, d.H), "mtp.fc_emb"));
+        FNX_TRY(dalloc(e, &e->head, iq3s_bytes(d.V, d.H), "head"));
+        FNX_TRY(dalloc(e, &e->embed, (size_t) d.V * d.H, "embed"));
+        e->proj_ld = d.attn_in > d.gdn_in ? d.attn_in : d.gdn_in;
+        const int mixw = d.nq * d.hd > d.nv * d.hs ? d.nq * d.hd : d.nv * d.hs;
+        FNX_TRY(dalloc(e, &e->R, (size_t) d.MAXR * d.H, "buf.R"));
+        FNX_TRY(dalloc(e, &e->Rm, (size_t) d.MAXR * d.H, "buf.Rm"));
+        FNX_TRY(dalloc(e, &e->Rsrc, (size_t) d.MAXR * d.H, "buf.Rsrc"));
+        FNX_TRY(dalloc(e, &e->Emb, (size_t) d.MAXR * d.H, "buf.Emb"));
+        FNX_TRY(dalloc(e, &e->proj, (size_t) d.MAXR * e->proj_ld, "buf.proj"));
+        FNX_TRY(dalloc(e, &e->mix, (size_t) d.MAXR * mixw, "buf.mix"));
+        FNX_TRY(dalloc(e, &e->logits, (size_t) d.MAXR * d.V, "buf.logits"));
+        FNX_TRY(dalloc(e, &e->rlogits, (size_t) d.MAXR * (d.E + 1), "buf.router_logits"));
+        FNX_TRY(dalloc(e, &e->topi, (size_t) d.MAXR * d.K, "buf.topi"));
+        FNX_TRY(dalloc(e, &e->topw, (size_t) d.MAXR * d.K, "buf.topw"));
+        FNX_TRY(dalloc(e, &e->jobs, (size_t) d.P + 8, "buf.jobs"));
+        FNX_TRY(dalloc(e, &e->njobs, 2, "buf.njobs"));
+        FNX_TRY(dalloc(e, &e->hbuf, (size_t) d.P * d.F, "buf.h"));
+        FNX_TRY(dalloc(e, &e->part, (size_t) d.P * d.H, "buf.part"));
+        FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
+        FNX_TRY(dalloc(e, &e->best_i, d.MAXR, "buf.best_i"));
+        FNX_TRY(dalloc(e, &e->best_v, d.MAXR, "buf.best_v"));
+        FNX_TRY(dalloc(e, &e->cand_v, (size_t) d.MAXR * FNX_TOPK_N, "buf.cand_v"));
+        FNX_TRY(dalloc(e, &e->cand_i, (size_t) d.MAXR * FNX_TOPK_N, "buf.cand_i"));
+        FNX_TRY(dalloc(e, &e->result, 1 + 2 * FNX_MAX_ROWS, "buf.result"));
+        FNX_TRY(dalloc(e, &e->d_tok, FNX_MAX_ROWS, "buf.tok"));
+        FNX_TRY(dalloc(e, &e->d_parent, FNX_MAX_ROWS, "buf.parent"));
+        FNX_TRY(dalloc(e, &e->d_depth, FNX_MAX_ROWS, "buf.depth"));
+        FNX_TRY(dalloc(e, &e->d_path, FNX_MAX_ROWS, "buf.path"));
+        FNX_TRY(dalloc(e, &e->d_mtok, FNX_MAX_ROWS, "buf.mtp_tok"));
+        FNX_TRY(dalloc(e, &e->d_mpos, 1, "buf.mtp_pos"));
+        FNX_TRY(dalloc(e, &e->d_draft, 1, "buf.draft"));
+        FNX_TRY(dalloc(e, &e->d_pos, c.n_seq, "seq.pos"));
+        FNX_TRY(dalloc(e, &e->d_cur, c.n_seq, "seq.cur"));
+        FNX_TRY(dalloc(e, &e->d_ctx, (size_t) c.n_seq * e->cache_rows, "seq.ctx"));
+        FNX_TRY(dalloc(e, &e->d_ctx_n, c.n_seq, "seq.ctx_n"));
+        FNX_TRY(dalloc(e, &e->err, 1, "buf.err"));
+        void* sc = nullptr;
+        const size_t sb = fnx_attn_scratch_bytes(d.MAXR, d.nq, d.hd);
+        FNX_TRY(dalloc(e, (uint8_t**) &sc, sb, "buf.attn_scratch"));
+        e->att_scratch = sc;
+        FNX_CUDA_OK(cudaHostAlloc((void**) &e->h_stage, sizeof(int) * 8 * FNX_MAX_ROWS, cudaHostAllocDefault));
+        return FNX_OK;
+    };
+    rc = body();
+    if (rc != FNX_OK) {
+        fnx_engine_destroy(e);
+        return rc;
+    }
+    *out = e;
+    return FNX_OK;
+}
+
+extern "C" void fnx_engine_destroy(fnx_engine* e) {
+    if (!e) return;
+    if (e->st) cudaStreamSynchronize(e->st);
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+    if (e->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(e->comm);
+    for (void* p : e->owned) cudaFree(p);
+    if (e->h_stage) cudaFreeHost(e->h_stage);
+    if (e->ev0) cudaEventDestroy(e->ev0);
+    if (e->ev1) cudaEventDestroy(e->ev1);
+    if (e->st) cudaStreamDestroy(e->st);
+    delete e;
+}
+
+extern "C" int fnx_engine_init_synthetic(fnx_engine* e, uint64_t seed, float sigma) {
+    FNX_REQUIRE(e, "fnx_engine_init_synthetic: null engine");
+    const Dims d = dims(e->c);
+    // staging: one chunk of f32 weights and its GGML blocks
+    const size_t tw = (size_t) 32 << 20;
+    float* tf = nullptr;
+    uint8_t* tg = nullptr;
+    FNX_CUDA_OK(cudaMalloc((void**) &tf, tw * sizeof(float)));
+    FNX_CUDA_OK(cudaMalloc((void**) &tg, tw / 256 * IQ3S_BLOCK_BYTES));
+    int rc = FNX_OK;
+    auto body = [&]() -> int {
+        for (int l = 0; l < e->c.n_layer; ++l) FNX_TRY(init_layer(e, e->layers[l], l, seed, sigma, tf, tg, tw));
+        FNX_TRY(init_layer(e, e->mtp, 60, seed, sigma, tf, tg, tw));
+        FNX_TRY(fill_const(e, e->mtp_hnorm, d.H, 1.0f));
+        FNX_TRY(fill_const(e, e->mtp_enorm, d.H, 1.0f));
+        FNX_TRY(fill_const(e, e->mtp_onorm, d.H, 1.0f));
+        FNX_TRY(fill_const(e, e->out_norm, d.H, 1.0f));
+        FNX_TRY(synth_iq3s(e, e->mtp_fc_hid, d.H, d.H, sigma, seed, (61u * 16 + 0) << 12, tf, tg, tw));
+        FNX_TRY(synth_iq3s(e, e->mtp_fc_emb, d.H, d.H, sigma, seed, (61u * 16 + 1) << 12, tf, tg, tw));
+        FNX_TRY(synth_iq3s(e, e->head, d.V, d.H, sigma, seed, (62u * 16) << 12, tf, tg, tw));
+        // the embedding table: N(0, 1) rounded to f16, in chunks of the staging buffer
+        const size_t n = (size_t) d.V * d.H;
+        uint32_t sub = 0;
+        for (size_t o = 0; o < n; o += tw, ++sub) {
+            const size_t m = n - o < tw ? n - o : tw;
+            FNX_TRY(fnx_fill_normal(tf, m, 1.0f, seed, ((63u * 16) << 12) + sub, e->st));
+            k_f32_to_f16<<<(unsigned) ((m + 255) / 256), 256, 0, e->st>>>(tf, e->embed + o, m);
+            FNX_LAUNCH_OK("embed init");
+        }
+        FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+        return FNX_OK;
+    };
+    rc = body();
+    cudaStreamSynchronize(e->st);
+    cudaFree(tf);
+    cudaFree(tg);
+    return rc;
+}
+
+extern "C" size_t fnx_engine_device_bytes(const fnx_engine* e) { return e ? e->bytes : 0; }
+
+extern "C" void* fnx_engine_tensor(fnx_engine* e, const char* name, size_t* bytes) {
+    if (bytes) *bytes = 0;
+    if (!e || !name) return nullptr;
+    auto it = e->tensors.find(name);
+    if (it == e->tensors.end()) return nullptr;
+    if (bytes) *bytes = it->second.second;
+    return it->second.first;
+}
+
+extern "C" int fnx_engine_reset(fnx_engine* e, int seq) {
+    FNX_REQUIRE(e && seq >= 0 && seq < e->c.n_seq, "fnx_engine_reset: sequence %d", seq);
+    const Dims d = dims(e->c);
+    e->seqs[seq] = SeqState{};
+    FNX_CUDA_OK(cudaMemsetAsync(e->d_pos + seq, 0, sizeof(int), e->st));
+    FNX_CUDA_OK(cudaMemsetAsync(e->d_cur + seq, 0, sizeof(int), e->st));
+    FNX_CUDA_OK(cudaMemsetAsync(e->d_ctx_n + seq, 0, sizeof(int), e->st));
+    for (LayerW& L : e->layers)
+        if (!L.attn) {
+            FNX_CUDA_OK(cudaMemsetAsync(L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs, 0, sizeof(float) * e->NS * d.nv * d.hs * d.hs, e->st));
+            FNX_CUDA_OK(cudaMemsetAsync(L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch, 0, sizeof(float) * e->NS * 3 * d.gdn_ch, e->st));
+        }
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const int* h_parent, int T, int* h_result) {
+    FNX_REQUIRE(e && h_tok && seq >= 0 && seq < e->c.n_seq, "fnx_engine_verify: bad arguments");
+    FNX_REQUIRE(T >= 1 && T <= e->c.max_rows, "fnx_engine_verify: %d rows (1..%d)", T, e->c.max_rows);
+    SeqState& s = e->seqs[seq];
+    FNX_REQUIRE(s.pos + T <= e->c.max_ctx, "fnx_engine_verify: the window runs past the context of %d rows", e->c.max_ctx);
+    for (int t = 0; t < T; ++t) {
+        FNX_REQUIRE(h_tok[t] >= 0 && h_tok[t] < e->c.vocab, "fnx_engine_verify: token %d outside the vocabulary", h_tok[t]);
+        if (h_parent) FNX_REQUIRE(h_parent[t] < t && h_parent[t] >= (t == 0 ? -1 : 0), "fnx_engine_verify: parent[%d] = %d is not an earlier row", t, h_parent[t]);
+    }
+    // the previous call's use of the staging buffer is over: every call that copies results back synchronises
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    int* hs = e->h_stage;
+    memcpy(hs, h_tok, sizeof(int) * T);
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_tok, hs, sizeof(int) * T, cudaMemcpyHostToDevice, e->st));
+    if (h_parent) {
+        memcpy(hs + FNX_MAX_ROWS, h_parent, sizeof(int) * T);
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_parent, hs + FNX_MAX_ROWS, sizeof(int) * T, cudaMemcpyHostToDevice, e->st));
+    }
+    const bool tree = h_parent != nullptr;
+    const uint64_t key = ((uint64_t) 1 << 60) | ((uint64_t) seq << 20) | ((uint64_t) T << 1) | (tree ? 1 : 0);
+    FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
+    s.last_T = T;
+    if (h_result) {
+        FNX_CUDA_OK(cudaMemcpyAsync(hs + 2 * FNX_MAX_ROWS, e->result, sizeof(int) * (1 + 2 * FNX_MAX_ROWS), cudaMemcpyDeviceToHost, e->st));
+        FNX_CUDA_OK(cudaMemcpyAsync(hs + 5 * FNX_MAX_ROWS, e->err, sizeof(unsigned), cudaMemcpyDeviceToHost, e->st));
+        FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+        FNX_CUDA_OK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+        memcpy(h_result, hs + 2 * FNX_MAX_ROWS, sizeof(int) * (1 + 2 * FNX_MAX_ROWS));
+        const unsigned bits = (unsigned) hs[5 * FNX_MAX_ROWS];
+        if (bits) return fail(FNX_E_STATE, "verify: device error bits 0x%x (1: a bounded wait gave up, 2: non-finite value, 16: non-finite logits)", bits);
+    }
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n) {
+    FNX_REQUIRE(e && h_path && seq >= 0 && seq < e->c.n_seq, "fnx_engine_commit: bad arguments");
+    SeqState& s = e->seqs[seq];
+    FNX_REQUIRE(s.last_T > 0, "fnx_engine_commit: no verified window to commit");
+    FNX_REQUIRE(n >= 1 && n <= s.last_T && h_path[0] == 0, "fnx_engine_commit: %d rows of a window of %d (the first kept row is row 0)", n, s.last_T);
+    for (int j = 1; j < n; ++j) FNX_REQUIRE(h_path[j] > h_path[j - 1] && h_path[j] < s.last_T, "fnx_engine_commit: path[%d] = %d is not increasing", j, h_path[j]);
+    const Dims d = dims(e->c);
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    int* hs = e->h_stage;
+    memcpy(hs, h_path, sizeof(int) * n);
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_path, hs, sizeof(int) * n, cudaMemcpyHostToDevice, e->st));
+    // device tables of the attention layers' caches for this sequence (built once per sequence)
+    auto& tables = e->commit_tables;
+    const int key = seq;
+    if (!tables.count(key)) {
+        std::vector<__half*> ks, vs;
+        for (LayerW& L : e->layers)
+            if (L.attn) {
+                ks.push_back(L.kc + (size_t) seq * e->cache_rows * d.kv_rows);
+                vs.push_back(L.vc + (size_t) seq * e->cache_rows * d.kv_rows);
+            }
+        __half **dk = nullptr, **dv = nullptr;
+        FNX_TRY(dalloc(e, &dk, ks.size() + 1));
+        FNX_TRY(dalloc(e, &dv, vs.size() + 1));
+        FNX_CUDA_OK(cudaMemcpy(dk, ks.data(), sizeof(__half*) * ks.size(), cudaMemcpyHostToDevice));
+        FNX_CUDA_OK(cudaMemcpy(dv, vs.data(), sizeof(__half*) * vs.size(), cudaMemcpyHostToDevice));
+        tables[key] = {dk, dv};
+    }
+    int nattn = 0;
+    for (LayerW& L : e->layers) nattn += L.attn;
+    k_commit<<<nattn + 1, 256, 0, e->st>>>(tables[key].first, tables[key].second, nattn, d.kv_rows, e->d_path, e->d_tok, e->result + 1 + FNX_MAX_ROWS, n,
+                                           e->d_pos + seq, e->d_cur + seq, e->NS, e->d_ctx + (size_t) seq * e->cache_rows, e->d_ctx_n + seq);
+    FNX_LAUNCH_OK("commit");
+    k_advance_pos<<<1, 1, 0, e->st>>>(e->d_pos + seq, n);
+    FNX_LAUNCH_OK("commit (position)");
+    s.kept = n;
+    s.kept_pos0 = s.pos;
+    s.cur = (s.cur + 1 + h_path[n - 1]) % e->NS;
+    s.pos += n;
+    s.last_T = 0;
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
+    FNX_REQUIRE(e && h_drafts && seq >= 0 && seq < e->c.n_seq && k >= 1 && k < e->c.max_rows, "fnx_engine_draft: bad arguments");
+    SeqState& s = e->seqs[seq];
+    FNX_REQUIRE(s.kept >= 1, "fnx_engine_draft: nothing committed since the last draft");
+    const Dims d = dims(e->c);
+    const int n = s.kept;
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    int* hs = e->h_stage;
+    float total_ms = 0.f;
+    // first call: the kept rows of the main model (gathered by path) with the tokens the window emitted
+    k_gather_rows<<<dim3((d.H + 255) / 256, n), 256, 0, e->st>>>(e->Rsrc, e->R, e->d_path, d.H);
+    FNX_LAUNCH_OK("draft gather");
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->result + 1 + FNX_MAX_ROWS, sizeof(int) * n, cudaMemcpyDeviceToDevice, e->st));
+    hs[0] = s.kept_pos0;
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    FNX_TRY(run_graph(e, ((uint64_t) 2 << 60) | ((uint64_t) seq << 20) | (uint64_t) n, [&]() { return enqueue_mtp(e, seq, n, e->Rsrc); }));
+    FNX_CUDA_OK(cudaMemcpyAsync(hs + 8, e->d_draft, sizeof(int), cudaMemcpyDeviceToHost, e->st));
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    float ms = 0.f;
+    FNX_CUDA_OK(cudaEventElapsedTime(&ms, e->ev0, e->ev1));
+    total_ms += ms;
+    h_drafts[0] = hs[8];
+    // the chain: each draft from the draft layer's own last row and the previous draft
+    for (int j = 1; j < k; ++j) {
+        const int src_row = j == 1 ? n - 1 : 0;
+        FNX_CUDA_OK(cudaMemcpyAsync(e->Rsrc, e->Rm + (size_t) src_row * d.H, sizeof(float) * d.H, cudaMemcpyDeviceToDevice, e->st));
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->d_draft, sizeof(int), cudaMemcpyDeviceToDevice, e->st));
+        hs[0] = s.kept_pos0 + n - 1 + j;
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
+        FNX_TRY(run_graph(e, ((uint64_t) 2 << 60) | ((uint64_t) seq << 20) | 1u, [&]() { return enqueue_mtp(e, seq, 1, e->Rsrc); }));
+        FNX_CUDA_OK(cudaMemcpyAsync(hs + 8, e->d_draft, sizeof(int), cudaMemcpyDeviceToHost, e->st));
+        FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+        FNX_CUDA_OK(cudaEventElapsedTime(&ms, e->ev0, e->ev1));
+        total_ms += ms;
+        h_drafts[j] = hs[8];
+    }
+    e->last_ms = total_ms;
+    s.kept = 0;
+    return FNX_OK;
+}
+
+extern "C" float fnx_engine_last_ms(const fnx_engine* e) { return e ? e->last_ms : 0.f; }
+extern "C" int fnx_engine_pos(const fnx_engine* e, int seq) { return e && seq >= 0 && seq < e->c.n_seq ? e->seqs[seq].pos : -1; }
+extern "C" fnx_stream fnx_engine_stream(fnx_engine* e) { return e ? (fnx_stream) e->st : nullptr; }
+
+extern "C" int fnx_comm_unique_id(void* h_id128) {
+    FNX_REQUIRE(h_id128, "fnx_comm_unique_id: null pointer");
+    Nccl* n = nccl();
+    if (!n) return fail(FNX_E_UNAVAILABLE, "NCCL (libnccl.so.2) could not be loaded");
+    const int rc = n->GetUniqueId(h_id128);
+    if (rc) return fail(FNX_E_CUDA, "ncclGetUniqueId: %s", n->GetErrorString ? n->GetErrorString(rc) : "error");
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_comm_init(fnx_engine* e, const void* h_id128, int rank, int size) {
+    FNX_REQUIRE(e && h_id128 && rank == e->c.ep_rank && size == e->c.ep_size, "fnx_engine_comm_init: rank %d of %d does not match the engine's shard", rank, size);
+    Nccl* n = nccl();
+    if (!n) return fail(FNX_E_UNAVAILABLE, "NCCL (libnccl.so.2) could not be loaded");
+    NcclId id;
+    memcpy(id.b, h_id128, 128);
+    const int rc = n->CommInitRank(&e->comm, size, id, rank);
+    if (rc) return fail(FNX_E_CUDA, "ncclCommInitRank: %s", n->GetErrorString ? n->GetErrorString(rc) : "error");
+    return FNX_OK;
+}
+
+extern "C" int fnx_allreduce(fnx_engine* e, float* x, size_t count, fnx_stream st) {
+    FNX_REQUIRE(e && x, "fnx_allreduce: null pointer");
+    if (e->c.ep_size == 1) return FNX_OK;
+    Nccl* n = nccl();
+    if (!n || !e->comm) return fail(FNX_E_STATE, "fnx_allreduce: the communicator is not initialised (fnx_engine_comm_init)");
+    // ncclFloat32 = 7, ncclSum = 0
+    const int rc = n->AllReduce(x, x, count, 7, 0, e->comm, as_stream(st));
+    if (rc) return fail(FNX_E_CUDA, "ncclAllReduce: %s", n->GetErrorString ? n->GetErrorString(rc) : "error");
+    return FNX_OK;
+}

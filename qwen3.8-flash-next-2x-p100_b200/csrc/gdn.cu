@@ -1,0 +1,174 @@
+// Gated DeltaNet core for a verify window, one launch.
+//
+// Replaces gdn_core / k_gdn_core (engine/src/kernels.hpp:97-99, engine/src/gdn_core.cuh:20-225; unfused statement
+// engine/src/kernels.cu:422-506): conv4 + SiLU over the q|k|v channels, L2 norms of q and k, the gates, the delta
+// rule on the fp32 state, the gated RMS norm of the output.  Differences by design:
+//   - rows form a tree (parent[t]); row t starts from its parent's state and conv history, not from row t - 1's;
+//   - the state after every row, and the history keeping it would leave, go to ring slot (*cur + 1 + t) % NS
+//     instead of the snap / hsnap buffers, so that a commit is a change of *cur and copies nothing
+//     (engine/src/engine_common.cu:710-754 copies the kept snapshot back);
+//   - the four blocks that share a value head form a thread-block cluster and add up the head's square sums
+//     through distributed shared memory, where the reference uses a global scratch buffer and atomic counters.
+#include <cooperative_groups.h>
+
+#include "fnx_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace fnxb {
+
+constexpr int GDN_HS = 128, GDN_Q = 4, GDN_QC = GDN_HS / GDN_Q, GDN_THREADS = 128;
+
+// value of channel c at the k-th row before window row t on its path (k = 0: row t itself), reaching into the
+// starting history (3 rows, oldest first) past the root
+__device__ __forceinline__ float gdn_src(const float* __restrict__ qkvz, int stride, const float* __restrict__ hin, int ch,
+                                         const int* __restrict__ parent, int t, int k, int c) {
+    int a = t;
+    for (int i = 0; i < k; ++i) {
+        a = parent ? parent[a] : a - 1;
+        if (a < 0) return hin[(size_t) (2 - (k - 1 - i)) * ch + c];
+    }
+    return qkvz[(size_t) a * stride + c];
+}
+
+__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
+    k_gdn_core(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
+               const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
+               const float* __restrict__ nw, float* __restrict__ S_pool, const int* __restrict__ curp, int NS,
+               const int* __restrict__ parent, float* __restrict__ y, int nk, int nv, int T, float eps) {
+    extern __shared__ __align__(16) float sm[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, kh = lv % nk, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int ch = (2 * nk + nv) * GDN_HS, cur = *curp;
+    const size_t hsz = (size_t) 3 * ch, ssz = (size_t) nv * GDN_HS * GDN_HS;
+    float* xq = sm;                              // [T][HS] q after conv, silu, norm
+    float* xk = xq + (size_t) T * GDN_HS;        // [T][HS]
+    float* vs = xk + (size_t) T * GDN_HS;        // [T][QC]
+    float* gates = vs + (size_t) T * GDN_QC;     // [T][2]
+    float* kred = gates + 2 * T;                 // [2][4][QC]
+    float* ared = kred + 2 * 4 * GDN_QC;         // [T][4][QC]
+    float* osum = ared + (size_t) T * 4 * GDN_QC;   // [T] this block's square sums (read by the cluster)
+    float* red = osum + T;                       // [4][2 T]
+    const float* hin = hist_pool + (size_t) cur * hsz;
+    if (tid < T) {
+        const float* abt = ab + (size_t) tid * ldab;
+        const float x = abt[lv] + dt[lv];
+        gates[2 * tid] = expf((x > 20.0f ? x : log1pf(expf(x))) * a_[lv]);
+        gates[2 * tid + 1] = 1.0f / (1.0f + expf(-abt[nv + lv]));
+    }
+    // ---- conv + silu: the head's q and k channels (HS each), this block's QC v channels; histories to the slots
+    for (int e = tid; e < 2 * GDN_HS + GDN_QC; e += GDN_THREADS) {
+        const int part = e < GDN_HS ? 0 : e < 2 * GDN_HS ? 1 : 2, i = part < 2 ? e - part * GDN_HS : e - 2 * GDN_HS;
+        const int c = part == 0 ? kh * GDN_HS + i : part == 1 ? nk * GDN_HS + kh * GDN_HS + i : 2 * nk * GDN_HS + lv * GDN_HS + qq * GDN_QC + i;
+        const float w0 = convw[c * 4], w1 = convw[c * 4 + 1], w2 = convw[c * 4 + 2], w3 = convw[c * 4 + 3];
+        const bool writes = part == 2 || (lv < nk && qq == 0);   // one block per channel writes its history
+        for (int t = 0; t < T; ++t) {
+            const float x3 = gdn_src(qkvz, stride, hin, ch, parent, t, 3, c), x2 = gdn_src(qkvz, stride, hin, ch, parent, t, 2, c);
+            const float x1 = gdn_src(qkvz, stride, hin, ch, parent, t, 1, c), x0 = qkvz[(size_t) t * stride + c];
+            const float x = w0 * x3 + w1 * x2 + w2 * x1 + w3 * x0;
+            const float v = x / (1.0f + expf(-x));
+            if (part == 0) xq[t * GDN_HS + i] = v;
+            else if (part == 1) xk[t * GDN_HS + i] = v;
+            else vs[t * GDN_QC + i] = v;
+            if (writes) {
+                float* hout = hist_pool + (size_t) ((cur + 1 + t) % NS) * hsz;
+                hout[c] = x2;
+                hout[ch + c] = x1;
+                hout[2 * ch + c] = x0;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- L2 norms of q and k per row: thread = element (HS == GDN_THREADS)
+    for (int t = 0; t < T; ++t) {
+        const float qv = xq[t * GDN_HS + tid], kv = xk[t * GDN_HS + tid];
+        const float sq = warp_sum(qv * qv), sk = warp_sum(kv * kv);
+        if (lane == 0) { red[warp * 2 * T + t] = sq; red[warp * 2 * T + T + t] = sk; }
+    }
+    __syncthreads();
+    for (int t = 0; t < T; ++t) {
+        float sq = 0.f, sk = 0.f;
+        for (int w = 0; w < 4; ++w) { sq += red[w * 2 * T + t]; sk += red[w * 2 * T + T + t]; }
+        xq[t * GDN_HS + tid] *= rsqrtf(sq + 1e-6f);
+        xk[t * GDN_HS + tid] *= rsqrtf(sk + 1e-6f);
+    }
+    __syncthreads();
+    // ---- the delta rule: warp `part` holds key rows [32 part, +32) of the block's QC value columns, lane = column
+    const int part = warp, col = qq * GDN_QC + lane;
+    const size_t soff = (size_t) lv * GDN_HS * GDN_HS + (size_t) part * 32 * GDN_HS + col;
+    float s[32];
+    int have = -2;   // the row whose result the registers hold (-1: the starting state)
+    const float scale = rsqrtf((float) GDN_HS);
+#pragma unroll 1
+    for (int t = 0; t < T; ++t) {
+        const int par = parent ? parent[t] : t - 1;
+        if (par != have) {
+            const float* src = S_pool + (size_t) (par < 0 ? cur : (cur + 1 + par) % NS) * ssz + soff;
+#pragma unroll
+            for (int r = 0; r < 32; ++r) s[r] = src[(size_t) r * GDN_HS];
+        }
+        const float gv = gates[2 * t], bv = gates[2 * t + 1];
+        const float* kt = xk + t * GDN_HS + part * 32;
+        const float* qt = xq + t * GDN_HS + part * 32;
+        float kvd = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) kvd = fmaf(s[r], kt[r], kvd);
+        float* kr = kred + (t & 1) * 4 * GDN_QC;
+        kr[part * GDN_QC + lane] = kvd;
+        __syncthreads();
+        const float kvs = (kr[lane] + kr[GDN_QC + lane]) + (kr[2 * GDN_QC + lane] + kr[3 * GDN_QC + lane]);
+        const float delta = (vs[t * GDN_QC + lane] - gv * kvs) * bv;
+        float at = 0.f;
+        float* dst = S_pool + (size_t) ((cur + 1 + t) % NS) * ssz + soff;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            s[r] = fmaf(kt[r], delta, gv * s[r]);
+            at = fmaf(s[r], qt[r], at);
+            dst[(size_t) r * GDN_HS] = s[r];
+        }
+        ared[(t * 4 + part) * GDN_QC + lane] = at;
+        have = t;
+    }
+    __syncthreads();
+    // ---- this block's outputs and their square sums per row
+    float ov[FNX_MAX_ROWS / 4];   // warp w keeps rows w, w + 4, ... of column `lane`
+    for (int t = warp, j = 0; t < T; t += 4, ++j) {
+        const float o = ((ared[(t * 4 + 0) * GDN_QC + lane] + ared[(t * 4 + 1) * GDN_QC + lane]) +
+                         (ared[(t * 4 + 2) * GDN_QC + lane] + ared[(t * 4 + 3) * GDN_QC + lane])) * scale;
+        ov[j] = o;
+        const float sq = warp_sum(o * o);
+        if (lane == 0) osum[t] = sq;
+    }
+    cluster.sync();
+    for (int t = warp, j = 0; t < T; t += 4, ++j) {
+        float ms = 0.f;
+        for (int b = 0; b < GDN_Q; ++b) ms += cluster.map_shared_rank(osum, b)[t];
+        ms /= (float) GDN_HS;
+        const float z = qkvz[(size_t) t * stride + ch + lv * GDN_HS + col];
+        y[(size_t) t * nv * GDN_HS + lv * GDN_HS + col] = ov[j] * rsqrtf(ms + eps) * nw[col] / (1.0f + expf(-z));
+    }
+    cluster.sync();   // no block may leave while a neighbour still reads its shared memory
+}
+
+}  // namespace fnxb
+
+using namespace fnxb;
+
+extern "C" int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt, const float* a,
+                            const float* nw, float* S_pool, const int* cur, int NS, const int* parent, float* y, int nk, int nv, int hs,
+                            int T, float eps, fnx_stream st) {
+    FNX_REQUIRE(qkvz && ab && hist_pool && convw && dt && a && nw && S_pool && cur && y, "fnx_gdn_core: null pointer");
+    FNX_REQUIRE(hs == GDN_HS, "fnx_gdn_core: head dim %d (this build: %d)", hs, GDN_HS);
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && NS >= T + 1, "fnx_gdn_core: %d rows need at least %d state slots, have %d", T, T + 1, NS);
+    FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_core: %d key heads, %d value heads", nk, nv);
+    const size_t smem = sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T);
+    static bool configured = false;
+    if (!configured) {
+        FNX_CUDA_OK(cudaFuncSetAttribute(k_gdn_core, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        configured = true;
+    }
+    k_gdn_core<<<nv * GDN_Q, GDN_THREADS, smem, as_stream(st)>>>(qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps);
+    FNX_LAUNCH_OK("fnx_gdn_core");
+    return FNX_OK;
+}

@@ -1,0 +1,153 @@
+// Head-side kernels: per-row argmax, the sampler's 64 candidates, embedding rows, RMS norm rows.
+//
+// fnx_argmax replaces argmax / k_argmax (engine/src/kernels.hpp:433, engine/src/kernels.cu:1056-1083): the same
+// total order, value first and the lower index on ties.  fnx_top_tokens replaces top_tokens / k_topk_rows
+// (engine/src/kernels.hpp:445, engine/src/topk.cuh:17-155) without penalties or logit bias: a radix select over the
+// 64-bit key (ordered logit bits, ~index), which has no ties, then a rank sort of the 64 survivors.
+#include "fnx_common.cuh"
+
+namespace fnxb {
+
+// float -> uint32 with the same order
+__device__ __forceinline__ uint32_t fkey(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return b & 0x80000000u ? ~b : b | 0x80000000u;
+}
+__device__ __forceinline__ float fkey_inv(uint32_t k) { return __uint_as_float(k & 0x80000000u ? k & 0x7fffffffu : ~k); }
+__device__ __forceinline__ unsigned long long key64(float v, int i) { return ((unsigned long long) fkey(v) << 32) | (uint32_t) ~i; }
+
+__global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logits, int V, int* __restrict__ best_i,
+                                                 float* __restrict__ best_v, unsigned* __restrict__ err) {
+    __shared__ unsigned long long red[32];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* l = logits + (size_t) t * V;
+    unsigned long long best = 0;
+    bool bad = false;
+    for (int i = tid; i < V; i += 1024) {
+        const float v = l[i];
+        bad |= !isfinite(v);
+        const unsigned long long k = key64(v, i);
+        best = k > best ? k : best;
+    }
+    for (int o = 16; o; o >>= 1) {
+        const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
+        best = ok > best ? ok : best;
+    }
+    if ((tid & 31) == 0) red[tid >> 5] = best;
+    if (bad) atomicOr(err, (unsigned) FNX_ERR_LOGITS);
+    __syncthreads();
+    if (tid < 32) {
+        best = red[tid];
+        for (int o = 16; o; o >>= 1) {
+            const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
+            best = ok > best ? ok : best;
+        }
+        if (tid == 0) {
+            best_i[t] = (int) ~(uint32_t) best;
+            if (best_v) best_v[t] = fkey_inv((uint32_t) (best >> 32));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024) k_top_tokens(const float* __restrict__ logits, int V, float* __restrict__ out_v, int* __restrict__ out_i) {
+    __shared__ unsigned hist[256];
+    __shared__ unsigned long long prefix_s, sel[FNX_TOPK_N];
+    __shared__ unsigned need_s, nsel;
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* l = logits + (size_t) t * V;
+    if (tid == 0) { prefix_s = 0; need_s = FNX_TOPK_N; nsel = 0; }
+    __syncthreads();
+    // 8 passes of 8 bits from the top: after pass p the first 8 (p + 1) bits of the 64th largest key are known
+    for (int pass = 0; pass < 8; ++pass) {
+        const int shift = 56 - 8 * pass;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const unsigned long long prefix = prefix_s;
+        const unsigned long long mask = pass == 0 ? 0ull : ~0ull << (shift + 8);
+        for (int i = tid; i < V; i += 1024) {
+            const unsigned long long k = key64(l[i], i);
+            if ((k & mask) == prefix) atomicAdd(&hist[(unsigned) (k >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned need = need_s, b = 255;
+            for (;; --b) {
+                if (hist[b] >= need) break;
+                need -= hist[b];
+                if (b == 0) break;
+            }
+            need_s = need;
+            prefix_s = prefix | ((unsigned long long) b << shift);
+        }
+        __syncthreads();
+    }
+    const unsigned long long thr = prefix_s;   // the 64th largest key (keys are distinct)
+    for (int i = tid; i < V; i += 1024) {
+        const unsigned long long k = key64(l[i], i);
+        if (k >= thr) {
+            const unsigned at = atomicAdd(&nsel, 1u);
+            if (at < FNX_TOPK_N) sel[at] = k;
+        }
+    }
+    __syncthreads();
+    const unsigned n = min(nsel, (unsigned) FNX_TOPK_N);
+    if (tid < (int) n) {
+        const unsigned long long k = sel[tid];
+        unsigned rank = 0;
+        for (unsigned j = 0; j < n; ++j) rank += sel[j] > k;
+        out_v[t * FNX_TOPK_N + rank] = fkey_inv((uint32_t) (k >> 32));
+        out_i[t * FNX_TOPK_N + rank] = (int) ~(uint32_t) k;
+    }
+}
+
+__global__ void k_embed_rows(const __half* __restrict__ table, const int* __restrict__ tok, int H, float* __restrict__ R) {
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < H) R[(size_t) t * H + i] = __half2float(table[(size_t) tok[t] * H + i]);
+}
+
+__global__ void __launch_bounds__(256) k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int n, float eps) {
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* xr = x + (size_t) r * n;
+    float ss = 0.f;
+    for (int i = tid; i < n; i += 256) ss += xr[i] * xr[i];
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int j = 0; j < 8; ++j) ss += red[j];
+    const float sc = rsqrtf(ss / (float) n + eps);
+    for (int i = tid; i < n; i += 256) y[(size_t) r * n + i] = xr[i] * sc * w[i];
+}
+
+}  // namespace fnxb
+
+using namespace fnxb;
+
+extern "C" int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st) {
+    FNX_REQUIRE(logits && best_i && err && T >= 1 && V >= 1, "fnx_argmax: bad arguments");
+    k_argmax<<<T, 1024, 0, as_stream(st)>>>(logits, V, best_i, best_v, err);
+    FNX_LAUNCH_OK("fnx_argmax");
+    return FNX_OK;
+}
+
+extern "C" int fnx_top_tokens(const float* logits, int T, int V, float* out_v, int* out_i, fnx_stream st) {
+    FNX_REQUIRE(logits && out_v && out_i && T >= 1 && V >= FNX_TOPK_N, "fnx_top_tokens: bad arguments (vocabulary of at least %d)", FNX_TOPK_N);
+    k_top_tokens<<<T, 1024, 0, as_stream(st)>>>(logits, V, out_v, out_i);
+    FNX_LAUNCH_OK("fnx_top_tokens");
+    return FNX_OK;
+}
+
+extern "C" int fnx_embed_rows(const void* table_f16, const int* tok, int T, int H, float* R, fnx_stream st) {
+    FNX_REQUIRE(table_f16 && tok && R && T >= 1, "fnx_embed_rows: bad arguments");
+    k_embed_rows<<<dim3((H + 255) / 256, T), 256, 0, as_stream(st)>>>((const __half*) table_f16, tok, H, R);
+    FNX_LAUNCH_OK("fnx_embed_rows");
+    return FNX_OK;
+}
+
+extern "C" int fnx_rmsnorm(const float* x, const float* w, float* y, int rows, int n, float eps, fnx_stream st) {
+    FNX_REQUIRE(x && w && y && rows >= 1 && n >= 1, "fnx_rmsnorm: bad arguments");
+    k_rmsnorm<<<rows, 256, 0, as_stream(st)>>>(x, w, y, n, eps);
+    FNX_LAUNCH_OK("fnx_rmsnorm");
+    return FNX_OK;
+}

@@ -1,0 +1,202 @@
+// MoE routing and combine.
+//
+// fnx_router_route replaces router_route / k_router_route (engine/src/kernels.hpp:294-296, engine/src/moe.cuh:258-515)
+// and its simple form route / k_topk + k_jobs (engine/src/kernels.cu:338-398): one launch computes the router logits
+// (f32 weights, a warp per expert row, fixed summation order), and the last block to finish picks the top K per row,
+// renormalises their softmax and lists the jobs.  fnx_moe_combine replaces k_combine (engine/src/kernels.cu:412-419).
+#include "fnx_common.cuh"
+
+namespace fnxb {
+
+constexpr int RT_WARPS = 4, RT_TOK = 8, RT_MAXE = 1024;
+
+__global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restrict__ Wr, const float* __restrict__ x,
+                                                          const float* __restrict__ norm_w, float eps, int T, int E, int H, int K,
+                                                          int e_lo, int e_hi, int add_shared, float* __restrict__ logits,
+                                                          int* __restrict__ topi, float* __restrict__ topw, fnx_job* __restrict__ jobs,
+                                                          int* __restrict__ njobs, unsigned* __restrict__ err) {
+    extern __shared__ __align__(16) float xs[];   // [RT_TOK][H]
+    __shared__ float rs[RT_TOK];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row = blockIdx.x * RT_WARPS + warp;
+    for (int t0 = 0; t0 < T; t0 += RT_TOK) {
+        const int nt = min(RT_TOK, T - t0);
+        __syncthreads();
+        for (int t = warp; t < nt; t += RT_WARPS) {
+            const float* xr = x + (size_t) (t0 + t) * H;
+            float ss = 0.f;
+            for (int i = lane * 4; i < H; i += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + i);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) rs[t] = norm_w ? rsqrtf(ss / (float) H + eps) : 1.0f;
+        }
+        __syncthreads();
+        for (int i = tid * 4; i < nt * H; i += RT_WARPS * 32 * 4) {
+            const int t = i / H, c = i % H;
+            float4 v = *reinterpret_cast<const float4*>(x + (size_t) (t0 + t) * H + c);
+            if (norm_w) {
+                const float4 w = *reinterpret_cast<const float4*>(norm_w + c);
+                const float r = rs[t];
+                v.x *= r * w.x; v.y *= r * w.y; v.z *= r * w.z; v.w *= r * w.w;
+            }
+            *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v;
+        }
+        __syncthreads();
+        if (row <= E) {
+            float acc[RT_TOK];
+#pragma unroll
+            for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
+            const float* wr = Wr + (size_t) row * H;
+            for (int i = lane * 4; i < H; i += 128) {
+                const float4 w = *reinterpret_cast<const float4*>(wr + i);
+#pragma unroll
+                for (int t = 0; t < RT_TOK; ++t)
+                    if (t < nt) {
+                        const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + i);
+                        acc[t] = fmaf(w.x, v.x, acc[t]);
+                        acc[t] = fmaf(w.y, v.y, acc[t]);
+                        acc[t] = fmaf(w.z, v.z, acc[t]);
+                        acc[t] = fmaf(w.w, v.w, acc[t]);
+                    }
+            }
+#pragma unroll
+            for (int t = 0; t < RT_TOK; ++t)
+                if (t < nt) {
+                    const float s = warp_sum(acc[t]);
+                    if (lane == 0) {
+                        logits[(size_t) (t0 + t) * (E + 1) + row] = s;
+                        if (!isfinite(s)) atomicOr(err, (unsigned) FNX_ERR_NONFINITE);
+                    }
+                }
+        }
+    }
+    // ---- the last block to get here routes
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last = atomicAdd(&njobs[1], 1) == (int) gridDim.x - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    // top K per row: a warp per row, 10 rounds of (value, index) maximum, ties to the lower index
+    for (int t = warp; t < T; t += RT_WARPS) {
+        const volatile float* l = logits + (size_t) t * (E + 1);
+        float v[RT_MAXE / 32];
+#pragma unroll
+        for (int j = 0; j < RT_MAXE / 32; ++j) v[j] = lane + 32 * j < E ? l[lane + 32 * j] : -INFINITY;
+        float top = 0.f, z = 0.f, mine = 0.f;
+        for (int k = 0; k < K; ++k) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < RT_MAXE / 32; ++j)
+                if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (k == 0) top = bv;
+            const float w = expf(bv - top);
+            z += w;
+            if (lane == k) mine = w;
+            if (lane == 0) topi[t * K + k] = bi;
+#pragma unroll
+            for (int j = 0; j < RT_MAXE / 32; ++j)
+                if (lane + 32 * j == bi) v[j] = -INFINITY;
+        }
+        if (lane < K) topw[t * K + lane] = mine / z;
+    }
+    __syncthreads();
+    // jobs in ascending expert order: expert e's rows in row order, 4 per job; then the shared expert's
+    __shared__ int cnt[RT_MAXE], base[RT_MAXE + 1];
+    for (int e = tid; e < E; e += RT_WARPS * 32) {
+        int c = 0;
+        if (e >= e_lo && e < e_hi)
+            for (int i = 0; i < T * K; ++i) c += topi[i] == e;
+        cnt[e] = (c + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int s = 0;
+        for (int e = 0; e < E; ++e) { base[e] = s; s += cnt[e]; }
+        base[E] = s;
+        njobs[0] = s + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
+        njobs[1] = 0;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += RT_WARPS * 32) {
+        if (!cnt[e]) continue;
+        int n = 0;
+        fnx_job* jb = jobs + base[e];
+        for (int i = 0; i < T * K; ++i)
+            if (topi[i] == e) {
+                fnx_job& j = jb[n / FNX_JOB_TOK];
+                j.w = e;
+                j.y[n % FNX_JOB_TOK] = i / K;
+                j.out[n % FNX_JOB_TOK] = i;
+                j.n = n % FNX_JOB_TOK + 1;
+                ++n;
+            }
+    }
+    if (add_shared)
+        for (int t = tid; t < T; t += RT_WARPS * 32) {
+            fnx_job& j = jobs[base[E] + t / FNX_JOB_TOK];
+            j.w = E;
+            j.y[t % FNX_JOB_TOK] = t;
+            j.out[t % FNX_JOB_TOK] = T * K + t;
+            if (t % FNX_JOB_TOK == FNX_JOB_TOK - 1 || t == T - 1) j.n = t % FNX_JOB_TOK + 1;
+        }
+}
+
+__global__ void k_combine(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
+                          const float* __restrict__ logits, int T, int E, int H, int K, int e_lo, int e_hi, int add_shared,
+                          float* __restrict__ out, int accumulate) {
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    float s = 0.f;
+    for (int k = 0; k < K; ++k) {
+        const int e = topi[t * K + k];
+        if (e >= e_lo && e < e_hi) s = fmaf(topw[t * K + k], part[((size_t) t * K + k) * H + i], s);
+    }
+    if (add_shared) s += sigmoidf_(logits[(size_t) t * (E + 1) + E]) * part[((size_t) T * K + t) * H + i];
+    float* o = out + (size_t) t * H + i;
+    *o = accumulate ? *o + s : s;
+}
+
+}  // namespace fnxb
+
+using namespace fnxb;
+
+extern "C" int fnx_router_route(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K, int e_lo,
+                                int e_hi, int add_shared, float* logits, int* topi, float* topw, fnx_job* jobs, int* njobs,
+                                unsigned* err, fnx_stream st) {
+    FNX_REQUIRE(Wr && x && logits && topi && topw && jobs && njobs && err, "fnx_router_route: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_router_route: %d rows (1..%d)", T, FNX_MAX_ROWS);
+    FNX_REQUIRE(E >= K && E <= RT_MAXE && K >= 1 && K <= 32, "fnx_router_route: %d experts, top %d not supported", E, K);
+    FNX_REQUIRE(H % 128 == 0 && H <= 4096, "fnx_router_route: hidden %d not supported", H);
+    FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E, "fnx_router_route: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
+    const size_t smem = (size_t) RT_TOK * H * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        FNX_CUDA_OK(cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        configured = true;
+    }
+    const int blocks = (E + 1 + RT_WARPS - 1) / RT_WARPS;
+    k_router<<<blocks, RT_WARPS * 32, smem, as_stream(st)>>>(Wr, x, norm_w, eps, T, E, H, K, e_lo, e_hi, add_shared, logits, topi, topw, jobs,
+                                                            njobs, err);
+    FNX_LAUNCH_OK("fnx_router_route");
+    return FNX_OK;
+}
+
+extern "C" int fnx_moe_combine(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H, int K,
+                               int e_lo, int e_hi, int add_shared, float* out, int accumulate, fnx_stream st) {
+    FNX_REQUIRE(part && topi && topw && logits && out, "fnx_moe_combine: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_moe_combine: %d rows", T);
+    k_combine<<<dim3((H + 255) / 256, T), 256, 0, as_stream(st)>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
+    FNX_LAUNCH_OK("fnx_moe_combine");
+    return FNX_OK;
+}

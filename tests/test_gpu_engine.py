@@ -1,0 +1,163 @@
+"""GPU tests of the window scheduler (Engine::verify / commit / draft over the C ABI) on a reduced model, against the
+same model run through the CPU oracle, plus the size-independent properties the reference's own `spec` test uses:
+speculative output equals plain greedy output, and a cut-back window leaves the state of a window of the kept rows."""
+import numpy as np
+import pytest
+
+from helpers import OracleModel, rel_err
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def small_cfg(F, **over):
+    # every kernel path at a different shape from the benchmark's: hidden 1024 (4 blocks per row), ffn 256
+    d = dict(n_layer=4, hidden=1024, n_expert=32, top_k=4, ffn=256, n_q_head=8, n_kv_head=1, head_dim=256, n_rot=64, gdn_k_head=2,
+             gdn_v_head=4, gdn_head_dim=128, vocab=2048, max_ctx=512, max_rows=8, attn_every=4)
+    d.update(over)
+    return F.flash_next_config(**d)
+
+
+@pytest.fixture(scope="module")
+def model(F, O):
+    cfg = small_cfg(F)
+    eng = F.Engine(cfg)
+    eng.init_synthetic(seed=0, sigma=0.02)
+    om = OracleModel(F, O, eng, cfg)
+    yield cfg, eng, om
+    eng.close()
+
+
+def _routing_margin_ok(om, K, tol=2e-4):
+    """True when every row's K-th and (K+1)-th router logits are further apart than the kernels' rounding."""
+    for topi, logits in om.routing:
+        for t in range(topi.shape[0]):
+            l = np.sort(logits[t, :-1])[::-1]
+            if l[K - 1] - l[K] < tol * max(1.0, abs(l[0])):
+                return False
+    return True
+
+
+def test_verify_commit_draft_match_oracle(F, O, model):
+    cfg, eng, om = model
+    rng = np.random.default_rng(0)
+    eng.reset()
+    # 1) a prompt of 19 tokens through chained windows
+    prompt = rng.integers(0, cfg.vocab, size=19).tolist()
+    eng.prefill(prompt)
+    for i in range(0, len(prompt), cfg.max_rows):
+        w = prompt[i:i + cfg.max_rows]
+        om.verify(w, None)
+        om.commit(list(range(len(w))))
+    assert eng.pos() == om.pos == 19
+    # 2) a chain window of 5 rows
+    toks = rng.integers(0, cfg.vocab, size=5).tolist()
+    n, path, em = eng.verify(toks)
+    on, opath, oem = om.verify(toks, None)
+    R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:5]
+    logits = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5]
+    topi = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:5]
+    assert _routing_margin_ok(om, cfg.top_k), "pick another seed: a routing near-tie makes the comparison meaningless"
+    assert rel_err(R, om.R) < 1e-2 and rel_err(logits, om.logits) < 1e-2           # the target's bar
+    assert rel_err(R, om.R) < 2e-3                                                   # what the kernels hold
+    assert np.array_equal(topi, om.routing[-1][0])                                   # last layer's routing, bit-exact
+    assert (n, path, em) == (on, list(opath), list(oem))
+    # 3) keep what greedy accepted, draft 3 tokens with the MTP layer
+    eng.commit(path)
+    om.commit(list(opath))
+    d = eng.draft(3)
+    od = om.draft(list(oem), 3)
+    assert d == od
+    # 4) a tree window: the accepted token as root, two branches
+    root = em[-1]
+    toks = [root, d[0], d[1], int(rng.integers(0, cfg.vocab)), d[2], int(rng.integers(0, cfg.vocab))]
+    par = [-1, 0, 1, 0, 2, 3]
+    r1 = eng.verify(toks, par)
+    r2 = om.verify(toks, par)
+    R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:6]
+    assert rel_err(R, om.R) < 2e-3
+    assert r1 == (r2[0], list(r2[1]), list(r2[2]))
+    # keep a path that is not a prefix of the rows, to exercise the cache compaction and the state ring
+    keep = [0, 3, 5]
+    eng.commit(keep)
+    om.commit(keep)
+    toks = rng.integers(0, cfg.vocab, size=3).tolist()
+    r1 = eng.verify(toks)
+    r2 = om.verify(toks, None)
+    R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:3]
+    assert rel_err(R, om.R) < 2e-3
+    assert r1 == (r2[0], list(r2[1]), list(r2[2]))
+
+
+def _greedy_plain(eng, prompt, steps):
+    eng.reset()
+    eng.prefill(prompt[:-1])
+    x, out = prompt[-1], []
+    for _ in range(steps):
+        n, path, em = eng.verify([x])
+        eng.commit([0])
+        x = em[0]
+        out.append(x)
+    return out
+
+
+def test_speculative_output_equals_plain_greedy(F, model):
+    """K perfect drafts, and windows with a corrupted draft: the emitted text must be the plain greedy text (the
+    reference's `spec` mode, engine/tools/fnx_run.cpp:8-9)."""
+    cfg, eng, _ = model
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, cfg.vocab, size=12).tolist()
+    want = _greedy_plain(eng, prompt, 24)
+    eng.reset()
+    eng.prefill(prompt[:-1])
+    x, out, i = prompt[-1], [], 0
+    while len(out) < 24:
+        k = min(4, 24 - len(out) - 1)
+        drafts = list(want[len(out):len(out) + k])
+        if k and i % 3 == 1:
+            j = int(rng.integers(0, k))
+            drafts[j] = (drafts[j] + 1) % cfg.vocab        # one wrong draft: the window is cut back there
+        n, path, em = eng.verify([x] + drafts)
+        assert path == list(range(n))
+        if not (k and i % 3 == 1):
+            assert n == k + 1
+        eng.commit(path)
+        out += em
+        x = em[-1]
+        i += 1
+    assert out[:24] == want
+
+
+def test_tree_verify_equals_chain_verify_of_the_accepted_path(F, model):
+    cfg, eng, _ = model
+    rng = np.random.default_rng(6)
+    prompt = rng.integers(0, cfg.vocab, size=9).tolist()
+    want = _greedy_plain(eng, prompt, 6)
+    eng.reset()
+    eng.prefill(prompt[:-1])
+    # root, a wrong branch first, then the right chain hanging off the root as a second branch
+    wrong = [(want[0] + 7) % cfg.vocab, (want[1] + 7) % cfg.vocab]
+    toks = [prompt[-1], wrong[0], wrong[1], want[0], want[1], want[2]]
+    par = [-1, 0, 1, 0, 3, 4]
+    n, path, em = eng.verify(toks, par)
+    assert path == [0, 3, 4, 5] and em == want[:4]
+    eng.commit(path)
+    n, path, em = eng.verify([em[-1]])
+    assert em[0] == want[4]
+
+
+def test_engine_rejects_bad_calls(F, model):
+    cfg, eng, _ = model
+    eng.reset()
+    with pytest.raises(F.FnxError):
+        eng.verify([1] * (cfg.max_rows + 1))
+    with pytest.raises(F.FnxError):
+        eng.verify([cfg.vocab])
+    with pytest.raises(F.FnxError):
+        eng.verify([1, 2], [-1, 1])       # a parent must be an earlier row
+    with pytest.raises(F.FnxError):
+        eng.commit([0])                   # nothing verified
+    eng.verify([1, 2, 3])
+    with pytest.raises(F.FnxError):
+        eng.commit([0, 2, 1])
+    eng.commit([0])

@@ -1,0 +1,360 @@
+"""GPU parity tests: every operator of the verify path through the C ABI against the CPU oracle.
+
+Bars (from the target): routing indices, accepted counts, greedy tokens and every integer/byte result bit-exact;
+hidden states and logits within 1e-2 relative (the kernels are far inside that: the tolerances below are the
+tighter figures the two-level int8 activations are expected to hold).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import gpu_iq3s_matrix, rel_err
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+TOL_GEMV = 2e-3   # relative to the largest reference magnitude
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+# ------------------------------------------------------------------------------------------------ IQ3_S
+def test_retile_is_a_permutation_and_decodes_like_the_oracle(F, O):
+    rng = np.random.default_rng(10)
+    rows, cols = 64, 1024
+    blk = rng.integers(0, 256, size=(rows * cols // 256, 110), dtype=np.uint8)
+    d = blk[:, :2].view(np.uint16)
+    d[(d & 0x7C00) == 0x7C00] &= 0x3FFF   # keep d finite
+    g = dev(blk.reshape(-1))
+    tiles = F.iq3s_retile(g, rows, cols)
+    assert torch.equal(F.iq3s_untile(tiles, rows, cols), g)
+    got = F.iq3s_dequant_tiles(tiles, rows, cols).cpu().numpy()
+    ref = O.iq3s_dequant(blk).reshape(rows, cols)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    # sorted bytes of a tile equal sorted bytes of its 16 blocks only if nothing was dropped: check sizes too
+    assert tiles.numel() == g.numel() == F.iq3s_bytes(rows, cols)
+
+
+def test_gpu_quantiser_is_bit_identical_to_the_cpu_twin(F, O):
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((96, 2048)) * 0.02).astype(np.float32)
+    w[3, :256] = 0.0          # an all-zero block
+    w[5, 256:288] = 0.0       # an all-zero sub-block
+    got = F.iq3s_quantize(dev(w)).cpu().numpy()
+    ref = O.iq3s_quantize(w).reshape(-1)
+    assert np.array_equal(got, ref)
+    dq = O.iq3s_dequant(got).reshape(w.shape)
+    assert np.sqrt(((dq - w) ** 2).mean()) / w.std() < 0.2
+
+
+# ------------------------------------------------------------------------------------------------ dense GEMV
+@pytest.mark.parametrize("rows,cols,T", [(64, 2048, 1), (64, 2048, 5), (128, 512, 4), (256, 512, 8), (32, 4096, 5), (256, 256, 3),
+                                         (64, 1024, 7), (9216, 2048, 5), (2048, 4096, 5), (128, 2048, 20)])
+def test_dense_matches_oracle(F, O, rows, cols, T):
+    tiles, ggml = gpu_iq3s_matrix(F, rows, cols, seed=3, stream_id=rows + cols)
+    rng = np.random.default_rng(rows + T)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    y, err = F.dense(tiles, rows, cols, dev(x))
+    ref = O.iq3s_gemv(ggml, rows, cols, x)
+    assert int(err.item()) == 0
+    assert rel_err(y.cpu().numpy(), ref) < TOL_GEMV
+
+
+def test_dense_with_norm_accumulate_and_strides(F, O):
+    rows, cols, T = 2048, 2048, 5
+    tiles, ggml = gpu_iq3s_matrix(F, rows, cols, seed=4, stream_id=77)
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((T, cols)) * 3.0).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    base = rng.standard_normal((T, rows + 64)).astype(np.float32)
+    out = dev(base)
+    y, err = F.dense(tiles, rows, cols, dev(x), norm_w=dev(w), eps=1e-6, out=out[:, :rows], accumulate=True)
+    ref = base[:, :rows] + O.iq3s_gemv(ggml, rows, cols, O.rmsnorm(x, w, 1e-6))
+    assert int(err.item()) == 0
+    assert rel_err(out[:, :rows].cpu().numpy(), ref) < TOL_GEMV
+    assert np.array_equal(out[:, rows:].cpu().numpy(), base[:, rows:])   # nothing written past the rows
+
+
+def test_dense_zero_and_huge_inputs(F, O):
+    rows, cols = 64, 2048
+    tiles, ggml = gpu_iq3s_matrix(F, rows, cols, seed=6, stream_id=5)
+    x = np.zeros((2, cols), np.float32)
+    x[1, ::7] = 1e4
+    y, err = F.dense(tiles, rows, cols, dev(x))
+    ref = O.iq3s_gemv(ggml, rows, cols, x)
+    assert np.all(y[0].cpu().numpy() == 0.0)
+    assert rel_err(y.cpu().numpy(), ref) < TOL_GEMV
+
+
+def test_dense_rejects_bad_shapes(F):
+    tiles = torch.zeros(F.iq3s_bytes(64, 2048), dtype=torch.uint8, device="cuda")
+    x = torch.zeros((1, 2048), device="cuda")
+    with pytest.raises(F.FnxError):
+        F.dense(tiles, 48, 2048, x)          # not a whole number of steps
+    with pytest.raises(F.FnxError):
+        F.dense(tiles, 64, 768, x[:, :768])  # unsupported column count
+
+
+# ------------------------------------------------------------------------------------------------ MoE
+def _moe_fixture(F, E, H, Fn, seed):
+    gu_t, gu_g, dn_t, dn_g = [], [], [], []
+    for e in range(E):
+        t, g = gpu_iq3s_matrix(F, 2 * Fn, H, seed, 1000 + e)
+        gu_t.append(t); gu_g.append(g)
+        t, g = gpu_iq3s_matrix(F, H, Fn, seed, 5000 + e)
+        dn_t.append(t); dn_g.append(g)
+    sh_gu_t, sh_gu_g = gpu_iq3s_matrix(F, 2 * Fn, H, seed, 9000)
+    sh_dn_t, sh_dn_g = gpu_iq3s_matrix(F, H, Fn, seed, 9001)
+    wr = torch.empty((E + 1) * H, dtype=torch.float32, device="cuda")
+    F.fill_normal(wr, 0.02, seed, 9002)
+    return dict(gu_t=torch.cat(gu_t), dn_t=torch.cat(dn_t), gu_g=np.concatenate(gu_g), dn_g=np.concatenate(dn_g), sh_gu_t=sh_gu_t,
+                sh_dn_t=sh_dn_t, sh_gu_g=sh_gu_g, sh_dn_g=sh_dn_g, wr=wr.view(E + 1, H))
+
+
+def _check_jobs(F, route, T, K, E, topi, e_lo, e_hi, add_shared):
+    nj = int(route["njobs"][0].item())
+    assert int(route["njobs"][1].item()) == 0
+    raw = route["jobs"].cpu().numpy().tobytes()
+    jobs = (F.Job * route["njobs_max"]).from_buffer_copy(raw)
+    seen = set()
+    shared_rows = set()
+    for j in range(nj):
+        jb = jobs[j]
+        assert 1 <= jb.n <= F.JOB_TOK
+        for i in range(jb.n):
+            if jb.w == E:
+                assert jb.out[i] == T * K + jb.y[i]
+                shared_rows.add(jb.y[i])
+            else:
+                assert e_lo <= jb.w < e_hi
+                t, k = divmod(jb.out[i], K)
+                assert t == jb.y[i] and topi[t, k] == jb.w
+                seen.add(jb.out[i])
+    want = {t * K + k for t in range(T) for k in range(K) if e_lo <= topi[t, k] < e_hi}
+    assert seen == want
+    assert shared_rows == (set(range(T)) if add_shared else set())
+
+
+@pytest.mark.parametrize("E,H,Fn,K,T", [(32, 1024, 256, 4, 3), (64, 2048, 512, 10, 5), (64, 2048, 512, 10, 20)])
+def test_moe_block_matches_oracle(F, O, E, H, Fn, K, T):
+    fx = _moe_fixture(F, E, H, Fn, seed=21)
+    rng = np.random.default_rng(E + T)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    nw = (1.0 + 0.05 * rng.standard_normal(H)).astype(np.float32)
+    xn = O.rmsnorm(x, nw, 1e-6)
+    ref_out, ref_logits, ref_topi, ref_topw = O.moe(fx["wr"].cpu().numpy(), fx["gu_g"], fx["dn_g"], fx["sh_gu_g"], fx["sh_dn_g"], xn, Fn, K)
+    route = F.router_route(fx["wr"], dev(x), K, norm_w=dev(nw))
+    assert np.array_equal(route["topi"].cpu().numpy(), ref_topi)            # routing indices: bit-exact
+    assert rel_err(route["logits"].cpu().numpy(), ref_logits) < 1e-5
+    assert np.abs(route["topw"].cpu().numpy() - ref_topw).max() < 1e-5
+    _check_jobs(F, route, T, K, E, ref_topi, 0, E, True)
+    out, h, part = F.moe_experts(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], route, dev(x), Fn, K, norm_w=dev(nw))
+    assert int(route["err"].item()) == 0
+    assert rel_err(out.cpu().numpy(), ref_out) < TOL_GEMV
+    # expert-parallel shards add up to the whole (2 ranks), the shared expert counted once
+    acc = np.zeros_like(ref_out)
+    for r in range(2):
+        lo, hi = r * E // 2, (r + 1) * E // 2
+        rt = F.router_route(fx["wr"], dev(x), K, norm_w=dev(nw), e_lo=lo, e_hi=hi, add_shared=(r == 0))
+        _check_jobs(F, rt, T, K, E, ref_topi, lo, hi, r == 0)
+        gu_b, dn_b = F.iq3s_bytes(2 * Fn, H), F.iq3s_bytes(H, Fn)
+        o, _, _ = F.moe_experts(fx["gu_t"][lo * gu_b:hi * gu_b], fx["dn_t"][lo * dn_b:hi * dn_b], fx["sh_gu_t"], fx["sh_dn_t"], rt, dev(x), Fn, K,
+                                norm_w=dev(nw), e_base=lo, e_lo=lo, e_hi=hi, add_shared=(r == 0))
+        ref_r, _, _, _ = O.moe(fx["wr"].cpu().numpy(), fx["gu_g"], fx["dn_g"], fx["sh_gu_g"], fx["sh_dn_g"], xn, Fn, K, e_lo=lo, e_hi=hi,
+                               add_shared=(r == 0))
+        assert rel_err(o.cpu().numpy(), ref_r) < TOL_GEMV
+        acc += o.cpu().numpy()
+    assert rel_err(acc, ref_out) < TOL_GEMV
+
+
+def test_router_many_tokens_pick_one_expert(F, O):
+    # every row identical: all rows pick the same experts, so jobs split into groups of 4 rows
+    E, H, K, T = 32, 1024, 4, 9
+    rng = np.random.default_rng(2)
+    wr = (rng.standard_normal((E + 1, H)) * 0.02).astype(np.float32)
+    x = np.tile(rng.standard_normal((1, H)).astype(np.float32), (T, 1))
+    _, ref_topi, _ = O.router(wr, x, K)
+    route = F.router_route(dev(wr), dev(x), K)
+    assert np.array_equal(route["topi"].cpu().numpy(), ref_topi)
+    _check_jobs(F, route, T, K, E, ref_topi, 0, E, True)
+    assert int(route["njobs"][0].item()) == K * 3 + 3
+
+
+# ------------------------------------------------------------------------------------------------ attention
+@pytest.mark.parametrize("pos0,T,tree", [(0, 1, False), (37, 5, False), (300, 5, True), (4096, 5, False), (1000, 20, True)])
+def test_attention_matches_oracle(F, O, pos0, T, tree):
+    nq, nkv, hd, nrot = 16, 2, 256, 64
+    rng = np.random.default_rng(pos0 + T)
+    rows = pos0 + T + 3
+    kc = np.zeros((rows, nkv, hd), np.uint16)
+    vc = np.zeros((rows, nkv, hd), np.uint16)
+    kc[:pos0] = (rng.standard_normal((pos0, nkv, hd))).astype(np.float16).view(np.uint16)
+    vc[:pos0] = (rng.standard_normal((pos0, nkv, hd))).astype(np.float16).view(np.uint16)
+    qg = rng.standard_normal((T, nq, 2 * hd)).astype(np.float32)
+    k = rng.standard_normal((T, nkv, hd)).astype(np.float32)
+    v = rng.standard_normal((T, nkv, hd)).astype(np.float32)
+    qn = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    kn = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    parent = depth = None
+    if tree:
+        parent = [-1] + [int(rng.integers(0, t)) for t in range(1, T)]
+        depth = [0] * T
+        for t in range(1, T):
+            depth[t] = depth[parent[t]] + 1
+    d_qg, d_k, d_kc, d_vc = dev(qg), dev(k), dev(kc.view(np.int16)), dev(vc.view(np.int16))
+    d_pos = dev(np.array([pos0], np.int32))
+    d_par = None if parent is None else dev(np.array(parent, np.int32))
+    d_dep = None if depth is None else dev(np.array(depth, np.int32))
+    F.attn_prep_append(d_qg, d_k, dev(v), dev(qn), dev(kn), d_kc, d_vc, d_pos, d_dep, nrot)
+    out = F.attn(d_qg, d_kc, d_vc, d_pos, d_par)
+    O.attn_prep_append(qg, k, v, qn, kn, kc, vc, pos0, depth, nrot)
+    ref = O.attn(qg, kc, vc, pos0, parent)
+    assert rel_err(d_qg.cpu().numpy(), qg) < 1e-5
+    # appended cache rows: f16 of values that agree to ~1e-6, so at most one f16 step apart, and almost all equal
+    got_k = d_kc.cpu().numpy().view(np.uint16)[pos0:pos0 + T].astype(np.int32)
+    assert np.abs(got_k - kc[pos0:pos0 + T].astype(np.int32)).max() <= 1
+    assert (got_k != kc[pos0:pos0 + T]).mean() < 1e-3
+    assert np.array_equal(d_vc.cpu().numpy().view(np.uint16)[pos0:pos0 + T], vc[pos0:pos0 + T])
+    assert rel_err(out.cpu().numpy(), ref) < 2e-3
+
+
+# ------------------------------------------------------------------------------------------------ DeltaNet
+def _gdn_inputs(rng, T, nk, nv, hs):
+    ch = (2 * nk + nv) * hs
+    qkvz = rng.standard_normal((T, ch + nv * hs)).astype(np.float32)
+    ab = rng.standard_normal((T, 2 * nv)).astype(np.float32)
+    convw = (0.5 * rng.standard_normal((ch, 4))).astype(np.float32)
+    dt = (0.1 * rng.standard_normal(nv)).astype(np.float32)
+    a = (-np.exp(0.3 * rng.standard_normal(nv))).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(hs)).astype(np.float32)
+    return ch, qkvz, ab, convw, dt, a, nw
+
+
+@pytest.mark.parametrize("T,tree,nk,nv", [(1, False, 2, 4), (5, False, 16, 32), (6, True, 2, 4), (20, True, 4, 8)])
+def test_gdn_core_matches_oracle(F, O, T, tree, nk, nv):
+    hs, NS, cur = 128, T + 2, 3 % (T + 2)
+    rng = np.random.default_rng(T * 10 + nv)
+    ch, qkvz, ab, convw, dt, a, nw = _gdn_inputs(rng, T, nk, nv, hs)
+    S = (0.1 * rng.standard_normal((NS, nv, hs, hs))).astype(np.float32)
+    hist = rng.standard_normal((NS, 3, ch)).astype(np.float32)
+    parent = [-1] + [int(rng.integers(0, t)) for t in range(1, T)] if tree else None
+    d_S, d_hist = dev(S), dev(hist)
+    y = F.gdn_core(dev(qkvz), dev(ab), d_hist, dev(convw), dev(dt), dev(a), dev(nw), d_S, dev(np.array([cur], np.int32)),
+                   None if parent is None else dev(np.array(parent, np.int32)), nk, nv, hs)
+    ref = O.gdn_core(qkvz, ab, hist, convw, dt, a, nw, S, cur, parent, nk, nv, hs)
+    assert rel_err(y.cpu().numpy(), ref) < 2e-3      # the reference's own bar for two steps is 2e-3 (selftest.cu:257-302)
+    assert rel_err(d_S.cpu().numpy(), S) < 1e-4
+    assert np.array_equal(d_hist.cpu().numpy(), hist)           # histories are copies: bit-exact
+    assert np.array_equal(d_S.cpu().numpy()[cur], S[cur])       # the starting slot is untouched
+
+
+def test_gdn_rollback_equals_running_only_the_kept_rows(F, O):
+    # a 5-row chain cut back to 2 rows leaves the state a 2-row window leaves
+    nk, nv, hs, T, NS = 2, 4, 128, 5, 6
+    rng = np.random.default_rng(9)
+    ch, qkvz, ab, convw, dt, a, nw = _gdn_inputs(rng, T, nk, nv, hs)
+    S0 = (0.1 * rng.standard_normal((NS, nv, hs, hs))).astype(np.float32)
+    h0 = rng.standard_normal((NS, 3, ch)).astype(np.float32)
+    args = (dev(convw), dev(dt), dev(a), dev(nw))
+    cur = dev(np.array([0], np.int32))
+    S5, H5 = dev(S0), dev(h0)
+    F.gdn_core(dev(qkvz), dev(ab), H5, *args[:4], S5, cur, None, nk, nv, hs)
+    S2, H2 = dev(S0), dev(h0)
+    F.gdn_core(dev(qkvz[:2]), dev(ab[:2]), H2, *args[:4], S2, cur, None, nk, nv, hs)
+    assert torch.equal(S5[2], S2[2]) and torch.equal(H5[2], H2[2])   # slot 1 + 1 = state after row 1
+
+
+# ------------------------------------------------------------------------------------------------ head
+def test_argmax_and_top_tokens(F, O):
+    rng = np.random.default_rng(31)
+    T, V = 5, 151936
+    logits = rng.standard_normal((T, V)).astype(np.float32)
+    logits[1, 500] = logits[1, 70000] = 9.0          # a tie: the lower index wins
+    logits[2, :] = 0.25                              # all equal
+    logits[3, 10:90] = 7.0                           # more than 64 equal candidates
+    bi, bv, err = F.argmax(dev(logits))
+    ri, rv = O.argmax(logits)
+    assert np.array_equal(bi.cpu().numpy(), ri) and np.array_equal(bv.cpu().numpy(), rv) and int(err.item()) == 0
+    ov, oi = F.top_tokens(dev(logits))
+    rv64, ri64 = O.top_tokens(logits)
+    assert np.array_equal(oi.cpu().numpy(), ri64) and np.array_equal(ov.cpu().numpy(), rv64)
+    logits[4, 123] = np.inf
+    _, _, err = F.argmax(dev(logits))
+    assert int(err.item()) == 16
+
+
+# ------------------------------------------------------------------------------------------------ drafting, acceptance
+def _edit_like_context(rng, n, vocab=5000):
+    ctx = rng.integers(0, vocab, size=n).astype(np.int32)
+    i = 300
+    while i < n:
+        if rng.random() < 0.6:
+            ln = int(rng.integers(20, 200))
+            s = int(rng.integers(0, i - ln)) if i - ln > 0 else 0
+            ln = min(ln, n - i)
+            ctx[i:i + ln] = ctx[s:s + ln]
+            i += ln
+        else:
+            i += int(rng.integers(1, 40))
+    return ctx
+
+
+def test_lookup_matches_oracle_and_reference(F, O):
+    rng = np.random.default_rng(2)
+    ctx = _edit_like_context(rng, 32768)
+    d_ctx = dev(ctx)
+    hits = 0
+    for n in list(rng.integers(4, 32768, size=60)) + [3, 4, 32768]:
+        n = int(n)
+        for lk in (15, 0, 5):
+            for d1 in (-1, int(ctx[min(n, 32767)]), 7):
+                want, wm = O.lookup(ctx[:n], lk, d1)
+                got, gm = F.lookup_draft(d_ctx, dev(np.array([n], np.int32)), lk, dev(np.array([d1], np.int32)))
+                assert got == list(want) and gm == wm
+                hits += len(got) > 0
+    assert hits > 10
+
+
+def test_accept_greedy_tree(F, O):
+    rng = np.random.default_rng(4)
+    for _ in range(50):
+        T = int(rng.integers(1, 21))
+        parent = [-1] + [int(rng.integers(0, t)) for t in range(1, T)]
+        tok = rng.integers(0, 6, size=T).astype(np.int32)
+        best = rng.integers(0, 6, size=T).astype(np.int32)
+        n, path, em = O.accept_greedy(tok, parent, best)
+        gn, gpath, gem = F.accept_greedy(dev(tok), dev(np.array(parent, np.int32)), dev(best))
+        assert (gn, gpath, gem) == (n, list(path), list(em))
+    # chain with null parent
+    tok = np.array([5, 1, 2, 3, 9], np.int32)
+    best = np.array([1, 2, 3, 4, 0], np.int32)
+    assert F.accept_greedy(dev(tok), None, dev(best)) == (4, [0, 1, 2, 3], [1, 2, 3, 4])
+
+
+def test_accept_sample_counts_match_oracle(F, O):
+    rng = np.random.default_rng(8)
+    V, T = 4096, 5
+    total = 0
+    for it in range(40):
+        logits = (rng.standard_normal((T, V)) * 3).astype(np.float32)
+        cv, ci = O.top_tokens(logits)
+        tok = rng.integers(0, V, size=T).astype(np.int32)
+        for t in range(1, T):          # make most drafts likely ones
+            tok[t] = ci[t - 1, int(rng.integers(0, 3))]
+        for s in (O.Sampling(0.7, 1.0, 0.0, 0), O.Sampling(1.0, 0.9, 0.05, 40)):
+            n, em = O.accept_sample(cv, ci, tok, s, seed=1234, seq=it, step=7)
+            fs = F.Sampling(s.temperature, s.top_p, s.min_p, s.top_k)
+            gn, _, gem = F.accept_sample(dev(cv), dev(ci), dev(tok), fs, 1234, it, dev(np.array([7], np.uint32).view(np.int32)))
+            assert gn == n and gem == list(em)       # accepted counts and tokens: bit-exact
+            total += n
+    assert total > 80   # the cases do accept drafts
+
+
+def test_philox_stream_matches_oracle(F, O):
+    # known-answer vector of Philox4x32-10 (Random123 kat_vectors: zero counter and key)
+    assert list(O.philox([0, 0, 0, 0], [0, 0])) == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    assert list(O.philox([0xFFFFFFFF] * 4, [0xFFFFFFFF] * 2)) == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
