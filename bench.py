@@ -1,0 +1,352 @@
+"""Benchmark of the speculative-decoding verify path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the full synthetic 48-layer model (hidden 2048, 512 experts top-10 + shared expert, every 4th layer
+gated attention, the rest gated DeltaNet, vocab 151,936, one MTP layer), random-init weights quantised to IQ3_S,
+a 4,096-token uniform-random context, k + 1 = 5 rows per window.  A step is one decode round: the MTP draft chain
+(4 calls), one verify window, greedy acceptance, commit.  Drafts: the sequence's own greedy continuation (computed
+before the timed region), each draft wrong with probability 0.28 (seeded), which gives the acceptance the reference
+reports for its MTP drafts (docs/SWITCHES.md:81) - the reference's `spec` test mode (engine/tools/fnx_run.cpp:8-9);
+the MTP chain is still computed and timed every round.
+
+value    decode tok/s from the device times of the round's graphs (inputs resident on the GPU)
+e2e      the same through Engine.verify / commit / draft with host token buffers: H2D of the window's tokens and
+         D2H of the acceptance result inside the timed region
+roofline the routed-expert gate|up kernel (the dominant kernel) timed live with CUDA events over all 48 layers'
+         weights; plus the whole verify step against its compulsory bytes
+N > 1:   expert-parallel ranks (512 experts split evenly, one NCCL all-reduce per layer), same token stream on every
+         rank, device-timed, max over ranks ("strong" scaling: the work is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+METRIC = "decode tok/s (MTP+lookup spec verify), verify-step us, % of HBM roofline"
+CTX, K_DRAFT, P_BAD = 4096, 4, 0.28
+E_B = 1351680          # bytes of one expert: (2*512*2048 + 2048*512) * 110 / 256
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        out = self.proc.communicate()[0]
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def model_config(F, ep_rank, ep_size, layers=48):
+    return F.flash_next_config(n_layer=layers, max_ctx=CTX + 1024, max_rows=32, ep_rank=ep_rank, ep_size=ep_size)
+
+
+def step_bytes(routed_jobs_per_step: float, ctx: int, T: int):
+    """Algorithmic bytes of one verify step: primary = active experts + attention K/V (the target's definition);
+    all = every compulsory byte (router, dense projections, DeltaNet state, head)."""
+    kv = 12 * ((ctx + T) * 2 * 256 * 2 * 2 + T * 2 * 256 * 2 * 2)
+    primary = (routed_jobs_per_step + 48) * E_B + kv
+    blk = 110 / 256
+    dense = 12 * (9216 * 2048 + 2048 * 4096) * blk + 36 * (12352 * 2048 + 2048 * 4096) * blk
+    router = 48 * 513 * 2048 * 4
+    state = 36 * (1 + T) * 32 * 128 * 128 * 4
+    head = 151936 * 2048 * blk
+    return primary, primary + dense + router + state + head
+
+
+def cpu_step_seconds(F, O, eng, cfg, steps):
+    """The CPU restatement on the host cores, on a bounded sample: one DeltaNet layer, one attention layer (each with
+    its MoE block) and the head, for a 5-row window at the bench's context; a full step is 36 x the first + 12 x the
+    second + the head."""
+    import numpy as np
+    from helpers import OracleModel
+    om = OracleModel(F, O, eng, cfg, layers=[2, 3], with_mtp=False)
+    rng = np.random.default_rng(1)
+    # the attention layer's cache: random f16 rows stand in for the 4,096-token context
+    L = om.layers[1]
+    L["kc"][:CTX] = rng.standard_normal((CTX, om.nkv, om.hd)).astype(np.float16).view(np.uint16)
+    L["vc"][:CTX] = rng.standard_normal((CTX, om.nkv, om.hd)).astype(np.float16).view(np.uint16)
+    om.pos = CTX
+    R0 = rng.standard_normal((1 + K_DRAFT, om.H)).astype(np.float32)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        R = om._gdn(om.layers[0], R0, None)
+        R = om._moe(om.layers[0], R)
+        t1 = time.perf_counter()
+        R = om._attention(om.layers[1], R, om.pos, None, None)
+        R = om._moe(om.layers[1], R)
+        t2 = time.perf_counter()
+        logits = O.iq3s_gemv(om.head, om.V, om.H, O.rmsnorm(R, om.out_norm, cfg.eps))
+        O.argmax(logits)
+        t3 = time.perf_counter()
+        ts.append(36 * (t1 - t0) + 12 * (t2 - t1) + (t3 - t2))
+    return ts
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=48, help="fewer layers for a quick functional run (not a valid bench number)")
+    ap.add_argument("--ctx", type=int, default=CTX, help="context length (the benchmark's is 4096)")
+    ap.add_argument("--verify-only", action="store_true", help="profiling aid: prefill, then warmup + steps verify windows of k+1 rows and nothing else")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3) if a.impl == "b200" else a.warmup
+
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if a.impl == "reference" and rank != 0:
+        return 0
+    import fnx_b200 as F
+    torch.cuda.set_device(local)
+    if world > 1 and a.impl == "b200":
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = model_config(F, rank if a.impl == "b200" else 0, world if a.impl == "b200" else 1, a.layers)
+    eng = F.Engine(cfg)
+    eng.init_synthetic(seed=0, sigma=0.02)
+    if world > 1 and a.impl == "b200":
+        import ctypes as C
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_char * 128)()
+            F.check(F.lib().fnx_comm_unique_id(buf))
+            uid = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
+        uid = uid.cuda()
+        dist.broadcast(uid, 0)
+        raw = bytes(uid.cpu().numpy().tobytes())
+        F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
+    hbm_peak, peak_kind = peaks()
+    workload = (f"verify step of the synthetic 48-layer Qwen3-Next-style model (IQ3_S, seed 0), ctx {CTX} uniform-random tokens (seed 1), "
+                f"k+1={1 + K_DRAFT} rows (1 committed + {K_DRAFT} drafts), greedy; drafts = own greedy continuation, each wrong with p={P_BAD}")
+
+    if a.impl == "reference":
+        import oracle as O
+        ts = cpu_step_seconds(F, O, eng, cfg, a.warmup + a.steps)[a.warmup:]
+        t = sum(ts) / len(ts)
+        cores = os.cpu_count() or 1
+        # expected tokens per round at the drafts' acceptance: 1 + p + p^2 + ...
+        exp_tok = sum((1 - P_BAD) ** j for j in range(K_DRAFT + 1))
+        v = exp_tok / t
+        sample = "per step: 1 DeltaNet layer + 1 attention layer (each with router, routed + shared experts) + head on the host cores, scaled 36x/12x/1x; MTP chain not included"
+        line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+                "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32",
+                "data": "synthetic", "config": {"workload": workload},
+                "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+                "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, cfg.vocab, size=a.ctx + 1).tolist()
+    total_rounds = a.warmup + a.steps
+    if a.verify_only:
+        eng.reset()
+        eng.prefill(prompt[:-1])
+        row = [prompt[-1]] + rng.integers(0, cfg.vocab, size=K_DRAFT).tolist()
+        ts = []
+        for _ in range(total_rounds):
+            eng.verify(row)
+            ts.append(eng.last_ms())
+        print(json.dumps({"mode": "verify-only", "layers": a.layers, "ctx": a.ctx, "verify_step_us": statistics.median(ts[a.warmup:]) * 1e3}))
+        eng.close()
+        return 0
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- the greedy continuation the drafts are taken from (not timed)
+    eng.reset()
+    eng.prefill(prompt[:-1])
+    x, want = prompt[-1], []
+    for _ in range(total_rounds * (K_DRAFT + 1) + K_DRAFT):
+        n, path, em = eng.verify([x])
+        eng.commit([0])
+        x = em[0]
+        want.append(x)
+    # ---- the decode rounds
+    eng.reset()
+    eng.prefill(prompt[:-1])
+    bad = np.random.default_rng(2).random((total_rounds, K_DRAFT)) < P_BAD
+    x, done = prompt[-1], 0
+    dev_ms, tokens, accepted, offered = 0.0, 0, 0, 0
+    c0 = None
+    clocks = Clocks(local)
+    t_ev0, t_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
+    have_kept = False
+    for r in range(total_rounds):
+        if r == a.warmup:
+            barrier()
+            c0 = eng.counters()
+            clocks.start()
+            t_ev0.record(est)
+            wall0 = time.perf_counter()
+        if have_kept:
+            eng.draft(K_DRAFT)                    # the MTP chain: computed and timed, its tokens replaced by the scripted drafts
+            if r >= a.warmup:
+                dev_ms += eng.last_ms()
+        drafts = [(want[done + j] + 1) % cfg.vocab if bad[r, j] else want[done + j] for j in range(K_DRAFT)]
+        n, path, em = eng.verify([x] + drafts)
+        if r >= a.warmup:
+            dev_ms += eng.last_ms()
+            tokens += n
+            accepted += n - 1
+            offered += K_DRAFT
+        eng.commit(path)
+        have_kept = True
+        assert em == want[done:done + n], "speculative output diverged from the greedy continuation"
+        done += n
+        x = em[-1]
+    t_ev1.record(est)
+    barrier()
+    wall = time.perf_counter() - wall0
+    clk = clocks.stop()
+    c1 = eng.counters()
+    e2e_ms = t_ev0.elapsed_time(t_ev1)
+    # max over ranks
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    launches = c1[0] - c0[0]
+    routed_jobs_per_step = (c1[1] - c0[1]) / max(1, a.steps) if world == 1 else None
+    value = tokens / (dev_ms * 1e-3)
+    e2e = tokens / (e2e_ms * 1e-3)
+
+    # ---- the verify step alone (device time of its graph), against its bytes
+    vts = []
+    for _ in range(5):
+        eng.verify([x] + want[done:done + K_DRAFT])
+        vts.append(eng.last_ms())
+    verify_ms = statistics.median(vts)
+    line = {"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32",
+            "data": "synthetic", "config": {"workload": workload, "timing": "inputs (34 GB of weights per step cycle) far larger than the 126 MB L2; CUDA events on the engine's stream",
+                                            "parallelism": f"ep{world}", "layers": a.layers},
+            "clocks": clk, "gpu_launches": int(launches),
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * (1 + K_DRAFT) + 4 * (1 + K_DRAFT) + 8, "d2h_bytes_per_step": 4 * 65 + 4 + 4 * K_DRAFT,
+                    "wall_ms_per_step": wall * 1e3 / a.steps},
+            "verify_step_us": verify_ms * 1e3, "accepted_per_offered": accepted / max(1, offered), "tokens_per_step": tokens / a.steps}
+
+    if world == 1 and rank == 0:
+        import ctypes as C
+        T = 1 + K_DRAFT
+        # routed jobs per verify step: the counters also saw the MTP calls' routers (1 layer each, few rows); take the verify-only figure
+        cA = eng.counters()
+        eng.verify([x] + want[done:done + K_DRAFT])
+        cB = eng.counters()
+        jobs_v = cB[1] - cA[1]
+        prim, allb = step_bytes(jobs_v, a.ctx + done, T)
+        line["step_roofline"] = {"bound": "hbm", "primary_bytes": prim, "all_bytes": allb, "achieved_primary_gbs": prim / (verify_ms * 1e-3) / 1e9,
+                                 "achieved_all_gbs": allb / (verify_ms * 1e-3) / 1e9, "peak": hbm_peak, "peak_kind": peak_kind,
+                                 "frac_primary_of_measured": prim / (verify_ms * 1e-3) / 1e9 / hbm_peak,
+                                 "frac_primary_of_nominal_8TBs": prim / (verify_ms * 1e-3) / 1e9 / 8000.0,
+                                 "frac_all_of_measured": allb / (verify_ms * 1e-3) / 1e9 / hbm_peak, "routed_jobs": int(jobs_v)}
+        # ---- the dominant kernel live: gate|up + SwiGLU of the routed experts, cycling over the 48 layers' weights
+        xrow = torch.randn((T, cfg.hidden), device="cuda")
+        nw = torch.ones(cfg.hidden, device="cuda")
+        gu_b = F.iq3s_bytes(2 * cfg.ffn, cfg.hidden)
+        routes, wgus, wshs = [], [], []
+        for l in range(a.layers):
+            wr = eng.tensor(f"l{l}.router", torch.float32).view(cfg.n_expert + 1, cfg.hidden)
+            routes.append(F.router_route(wr, xrow, cfg.top_k, norm_w=nw))
+            wgus.append(eng.tensor(f"l{l}.experts_gu", torch.uint8))
+            wshs.append(eng.tensor(f"l{l}.shared_gu", torch.uint8))
+        h = torch.zeros((T * cfg.top_k + T, cfg.ffn), device="cuda")
+        L = F.lib()
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def gate_up(l):
+            r = routes[l]
+            F.check(L.fnx_moe_gate_up(F.ptr(wgus[l]), gu_b, 0, F.ptr(wshs[l]), cfg.n_expert, F.ptr(r["jobs"]), F.ptr(r["njobs"]), r["njobs_max"],
+                                      F.ptr(xrow), F.ptr(nw), cfg.eps, cfg.hidden, cfg.ffn, F.ptr(h), F.ptr(r["err"]), st))
+        for l in range(a.layers):
+            gate_up(l)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        e0.record()
+        for _ in range(reps):
+            for l in range(a.layers):
+                gate_up(l)
+        e1.record()
+        torch.cuda.synchronize()
+        njobs = [int(r["njobs"][0].item()) for r in routes]
+        per_launch_s = e0.elapsed_time(e1) * 1e-3 / (reps * a.layers)
+        bytes_per_launch = sum(njobs) / len(njobs) * gu_b
+        ach = bytes_per_launch / per_launch_s / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "k_iq3s_mmv<1, gate|up>", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                            "peak_kind": peak_kind, "traffic": None, "us_per_launch": per_launch_s * 1e6, "jobs_per_launch": sum(njobs) / len(njobs),
+                            "algorithmic_bytes_per_launch": bytes_per_launch}
+        # ---- CPU restatement on the host cores, bounded sample
+        import oracle as O
+        ts = cpu_step_seconds(F, O, eng, cfg, 2)
+        exp_tok = tokens / a.steps
+        line["cpu_baseline"] = {"value": exp_tok / ts[-1], "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                "sample": "1 DeltaNet layer + 1 attention layer (each with router, routed + shared experts) + head, 5-row window, scaled 36x/12x/1x to a verify step; MTP chain not included",
+                                "verify_step_s": ts[-1]}
+    if rank == 0:
+        print(json.dumps(line))
+    eng.close()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -73,10 +73,12 @@ typedef struct {
 /* router_route (engine/src/kernels.hpp:294-296; simple form route :79): logits [T][E + 1] = Wr . xin (f32 weights,
  * row E the shared expert's gate), top-K by logit (ties: lower index), weights = softmax over the K; jobs for the
  * experts in [e_lo, e_hi) in first-pick order, then (add_shared != 0) one job of the shared expert (w = E) per 4
- * rows; *njobs = their number.  xin = rmsnorm(x) * norm_w when norm_w is not null. */
+ * rows; njobs[0] = their number (njobs[1] is the launch's block counter: zero it once, it is left at zero).
+ * xin = rmsnorm(x) * norm_w when norm_w is not null.  stats (may be null): stats[0] += routed jobs of this call,
+ * stats[1] += 1 (how many distinct experts the windows touched: the roofline's byte count). */
 int fnx_router_route(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K,
                      int e_lo, int e_hi, int add_shared, float* logits, int* topi, float* topw, fnx_job* jobs,
-                     int* njobs, unsigned* err, fnx_stream st);
+                     int* njobs, unsigned long long* stats, unsigned* err, fnx_stream st);
 /* moe_gate_up + SwiGLU (engine/src/kernels.hpp:319, :329; engine/src/moe.cuh:572-608): h[out][F] =
  * silu(Wg . xin) * (Wu . xin).  Wgu: expert e's [gate (F); up (F)] x H tile matrix at Wgu + (e - e_base) *
  * expert_stride; the shared expert (w == E) is read from Wsh. */
@@ -180,6 +182,8 @@ int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n);
 int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts);
 /* the device time of the last verify / draft graph launch in milliseconds (CUDA events on the engine's stream) */
 float fnx_engine_last_ms(const fnx_engine* e);
+/* counters since creation: [0] kernels launched through graphs, [1] routed expert jobs, [2] router calls */
+int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3);
 int fnx_engine_pos(const fnx_engine* e, int seq);
 fnx_stream fnx_engine_stream(fnx_engine* e);
 

@@ -143,7 +143,7 @@ def attn_prep_append(qg, k, v, qn, kn, kc, vc, pos0, depth=None, nrot=64, eps=1e
     nkv, hd = k.shape[1], k.shape[2]
     d = None if depth is None else i32(depth)
     lib().fnx_o_attn_prep_append(_p(qg), _p(k), _p(f32(v)), _p(f32(qn)), _p(f32(kn)), _p(kc), _p(vc), T, nq, nkv, hd,
-                                 nrot, pos0, _p(d), C.c_float(eps), C.c_float(rope_base))
+                                 int(nrot), int(pos0), _p(d), C.c_float(eps), C.c_float(rope_base))
 
 
 def attn(qg, kc, vc, pos0, parent=None):
@@ -151,7 +151,7 @@ def attn(qg, kc, vc, pos0, parent=None):
     nkv, hd = kc.shape[1], kc.shape[2]
     out = np.empty((T, nq, hd), np.float32)
     par = None if parent is None else i32(parent)
-    lib().fnx_o_attn(_p(qg), _p(kc), _p(vc), _p(out), T, nq, nkv, hd, pos0, _p(par))
+    lib().fnx_o_attn(_p(qg), _p(kc), _p(vc), _p(out), T, nq, nkv, hd, int(pos0), _p(par))
     return out
 
 
@@ -162,7 +162,7 @@ def gdn_core(qkvz, ab, hist_pool, convw, dt, a, nw, S_pool, cur, parent, nk, nv,
     y = np.empty((T, nv * hs), np.float32)
     par = None if parent is None else i32(parent)
     lib().fnx_o_gdn_core(_p(qkvz), _p(ab), _p(hist_pool), _p(f32(convw)), _p(f32(dt)), _p(f32(a)), _p(f32(nw)),
-                         _p(S_pool), cur, NS, _p(par), _p(y), nk, nv, hs, T, C.c_float(eps))
+                         _p(S_pool), int(cur), int(NS), _p(par), _p(y), nk, nv, hs, T, C.c_float(eps))
     return y
 
 

@@ -60,7 +60,7 @@ _PROTOS = {
     "fnx_iq3s_quantize": (_I, [_P, _P, _Z, _P]),
     "fnx_fill_normal": (_I, [_P, _Z, _F, _U64, _U32, _P]),
     "fnx_dense": (_I, [_P, _I, _I, _P, _I, _I, _P, _F, _P, _I, _I, _P, _P]),
-    "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
     "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
@@ -85,6 +85,7 @@ _PROTOS = {
     "fnx_engine_commit": (_I, [_P, _I, _P, _I]),
     "fnx_engine_draft": (_I, [_P, _I, _I, _P]),
     "fnx_engine_last_ms": (_F, [_P]),
+    "fnx_engine_counters": (_I, [_P, _P]),
     "fnx_engine_pos": (_I, [_P, _I]),
     "fnx_engine_stream": (_P, [_P]),
     "fnx_comm_unique_id": (_I, [_P]),
@@ -206,7 +207,7 @@ def router_route(Wr, x, K: int, norm_w=None, eps: float = 1e-6, e_lo: int = 0, e
     njobs = torch.zeros(2, dtype=torch.int32, device=dev)
     err = new_err(dev) if err is None else err
     check(lib().fnx_router_route(ptr(Wr), ptr(x), ptr(norm_w), eps, T, E, H, K, e_lo, e_hi, 1 if add_shared else 0, ptr(logits), ptr(topi),
-                                 ptr(topw), ptr(jobs), ptr(njobs), ptr(err), _stream()))
+                                 ptr(topw), ptr(jobs), ptr(njobs), None, ptr(err), _stream()))
     return dict(logits=logits, topi=topi, topw=topw, jobs=jobs, njobs=njobs, njobs_max=njobs_max, err=err)
 
 
@@ -375,6 +376,12 @@ class Engine:
         out = (C.c_int * k)()
         check(lib().fnx_engine_draft(self._h, seq, k, out))
         return list(out)
+
+    def counters(self):
+        """(kernels launched through graphs, routed expert jobs, router calls) since creation."""
+        out = (C.c_ulonglong * 3)()
+        check(lib().fnx_engine_counters(self._h, out))
+        return tuple(out)
 
     def last_ms(self) -> float:
         return lib().fnx_engine_last_ms(self._h)

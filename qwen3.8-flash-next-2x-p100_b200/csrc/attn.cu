@@ -15,6 +15,8 @@ __global__ void k_attn_prep_append(float* __restrict__ qg, int ldq, float* __res
                                    const float* __restrict__ qn, const float* __restrict__ kn, __half* __restrict__ kc,
                                    __half* __restrict__ vc, int nq, int nkv, int hd, int nrot, const int* __restrict__ pos0p,
                                    const int* __restrict__ depth, float eps, float rope_base) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float xrow[];   // hd floats
     __shared__ float red[32];
     const int t = blockIdx.y, h = blockIdx.x, i = threadIdx.x, pos0 = *pos0p;
@@ -38,7 +40,8 @@ __global__ void k_attn_prep_append(float* __restrict__ qg, int ldq, float* __res
     float y = xrow[i];
     if (i < nrot) {
         const int pr = i < nrot / 2 ? i : i - nrot / 2;
-        const float fe = powf(rope_base, -2.0f * (float) pr / (float) nrot);
+        // the unit frequency through double: the correctly rounded f32 of base^(-2 i / nrot) (engine/src/rope.hpp:33-35)
+        const float fe = (float) pow((double) rope_base, -2.0 * (double) pr / (double) nrot);
         float sn, cs;
         sincosf((float) pos * fe, &sn, &cs);
         const float x0 = xrow[pr], x1 = xrow[pr + nrot / 2];
@@ -63,6 +66,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
                                                            const __half* __restrict__ vc, float* __restrict__ acc_out,
                                                            AttPartial* __restrict__ mz_out, int T, int nq, int nkv, int hd,
                                                            const int* __restrict__ pos0p, const int* __restrict__ parent) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t smem[];
     const int s = blockIdx.x, S = gridDim.x, kvh = blockIdx.y, r0 = blockIdx.z * ATT_ROWS;
     const int nr = min(ATT_ROWS, T - r0), qpk = nq / nkv, NQ = nr * qpk;
@@ -77,9 +82,32 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
     float* ms = fs + ATT_ROWS * ATT_MAXQ;                              // running max
     float* zs = ms + ATT_ROWS * ATT_MAXQ;                              // running sum
     unsigned* see = reinterpret_cast<unsigned*>(zs + ATT_ROWS * ATT_MAXQ);   // per local row: window rows it sees
-    for (int i = tid; i < NQ * hd; i += ATT_THREADS) {
-        const int qi = i / hd, d = i % hd, r = qi / qpk, hh = qi % qpk;
-        qs[i] = qg[(size_t) (r0 + r) * ldq + (size_t) (kvh * qpk + hh) * 2 * hd + d];
+    {   // a block with no positions leaves only empty partials: the merge skips them without reading their sums
+        const int nch0 = (ctx + ATT_CH - 1) / ATT_CH;
+        if ((int) ((long long) nch0 * s / S) >= (int) ((long long) nch0 * (s + 1) / S)) {
+            if (tid < NQ) {
+                const int r = tid / qpk, hh = tid % qpk;
+                mz_out[((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s] = AttPartial{-INFINITY, 0.f};
+            }
+            return;
+        }
+    }
+    // the queries: 16 bytes per thread per load, 8 loads in flight
+    for (int i0 = tid; i0 < NQ * hd / 4; i0 += 8 * ATT_THREADS) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * ATT_THREADS;
+            if (i < NQ * hd / 4) {
+                const int qi = i / (hd / 4), d4 = i % (hd / 4), r = qi / qpk, hh = qi % qpk;
+                v[j] = *reinterpret_cast<const float4*>(qg + (size_t) (r0 + r) * ldq + (size_t) (kvh * qpk + hh) * 2 * hd + d4 * 4);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * ATT_THREADS;
+            if (i < NQ * hd / 4) reinterpret_cast<float4*>(qs)[i] = v[j];
+        }
     }
     if (tid < NQ) { ms[tid] = -INFINITY; zs[tid] = 0.f; }
     if (tid < nr) {
@@ -98,16 +126,25 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
         const int p0 = c * ATT_CH, np = min(ATT_CH, ctx - p0);
         __syncthreads();
         // K and V rows of the chunk, 16 bytes per thread per step
-        for (int i = tid; i < ATT_CH * hd / 8; i += ATT_THREADS) {
-            const int pp = i / (hd / 8), d8 = i % (hd / 8);
-            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
-            if (pp < np) {
-                const size_t g = ((size_t) (p0 + pp) * nkv + kvh) * hd + d8 * 8;
-                kv4 = *reinterpret_cast<const uint4*>(kc + g);
-                vv4 = *reinterpret_cast<const uint4*>(vc + g);
+        {
+            constexpr int NL = ATT_CH * 256 / 8 / ATT_THREADS;   // 4 K and 4 V loads per thread, all in flight (hd == 256)
+            uint4 kv4[NL], vv4[NL];
+#pragma unroll
+            for (int j = 0; j < NL; ++j) {
+                const int i = tid + j * ATT_THREADS, pp = i / (hd / 8), d8 = i % (hd / 8);
+                kv4[j] = vv4[j] = make_uint4(0, 0, 0, 0);
+                if (pp < np) {
+                    const size_t g = ((size_t) (p0 + pp) * nkv + kvh) * hd + d8 * 8;
+                    kv4[j] = *reinterpret_cast<const uint4*>(kc + g);
+                    vv4[j] = *reinterpret_cast<const uint4*>(vc + g);
+                }
             }
-            *reinterpret_cast<uint4*>(Ks + pp * KS + d8 * 8) = kv4;
-            *reinterpret_cast<uint4*>(Vs + pp * hd + d8 * 8) = vv4;
+#pragma unroll
+            for (int j = 0; j < NL; ++j) {
+                const int i = tid + j * ATT_THREADS, pp = i / (hd / 8), d8 = i % (hd / 8);
+                *reinterpret_cast<uint4*>(Ks + pp * KS + d8 * 8) = kv4[j];
+                *reinterpret_cast<uint4*>(Vs + pp * hd + d8 * 8) = vv4[j];
+            }
         }
         __syncthreads();
         // scores: warp w takes queries w, w + 8, ...; lane = position
@@ -144,11 +181,18 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
 #pragma unroll
             for (int qi = 0; qi < ATT_ROWS * ATT_MAXQ; ++qi)
                 if (qi < NQ) acc[qi] *= fs[qi];
-            for (int pp = 0; pp < ATT_CH; ++pp) {
-                const float vv = __half2float(Vs[pp * hd + d]);
+            for (int pp = 0; pp < ATT_CH; pp += 4) {
+                const float v0 = __half2float(Vs[pp * hd + d]), v1 = __half2float(Vs[(pp + 1) * hd + d]);
+                const float v2 = __half2float(Vs[(pp + 2) * hd + d]), v3 = __half2float(Vs[(pp + 3) * hd + d]);
 #pragma unroll
                 for (int qi = 0; qi < ATT_ROWS * ATT_MAXQ; ++qi)
-                    if (qi < NQ) acc[qi] = fmaf(es[qi * ATT_CH + pp], vv, acc[qi]);
+                    if (qi < NQ) {
+                        const float4 e4 = *reinterpret_cast<const float4*>(es + qi * ATT_CH + pp);
+                        acc[qi] = fmaf(e4.x, v0, acc[qi]);
+                        acc[qi] = fmaf(e4.y, v1, acc[qi]);
+                        acc[qi] = fmaf(e4.z, v2, acc[qi]);
+                        acc[qi] = fmaf(e4.w, v3, acc[qi]);
+                    }
             }
         }
     }
@@ -171,17 +215,33 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
 // merge the splits of (row, head): out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) z_s * sigmoid(gate)
 __global__ void k_attn_combine(const float* __restrict__ acc_in, const AttPartial* __restrict__ mz_in, const float* __restrict__ qg, int ldq,
                                float* __restrict__ out, int nq, int hd, int S) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float sm_m[256], sm_w[256];
     const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
     const size_t base = ((size_t) t * nq + h) * S;
+    AttPartial p = AttPartial{-INFINITY, 0.f};
+    if (i < S) p = mz_in[base + i];
+    sm_m[i] = i < S ? p.m : -INFINITY;
+    __syncthreads();
+    // block maximum of m (S <= 256 = blockDim)
     float mx = -INFINITY;
-    for (int s = 0; s < S; ++s) mx = fmaxf(mx, mz_in[base + s].m);
-    float z = 0.f, acc = 0.f;
-    for (int s = 0; s < S; ++s) {
-        const AttPartial p = mz_in[base + s];
-        if (p.m == -INFINITY) continue;
-        const float w = expf(p.m - mx);
-        z = fmaf(w, p.z, z);
-        acc = fmaf(w, acc_in[(base + s) * hd + i], acc);
+    for (int s = 0; s < S; ++s) mx = fmaxf(mx, sm_m[s]);
+    sm_w[i] = i < S && p.m != -INFINITY ? expf(p.m - mx) : 0.f;
+    __syncthreads();
+    __shared__ float sm_z[256];
+    sm_z[i] = i < S ? sm_w[i] * p.z : 0.f;
+    __syncthreads();
+    float z = 0.f;
+    for (int s = 0; s < S; ++s) z += sm_z[s];        // fixed order: deterministic
+    // the live splits' sums, 8 loads in flight, added in split order
+    float acc = 0.f;
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = s0 + j < S && sm_w[s0 + j] != 0.f ? acc_in[(base + s0 + j) * hd + i] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(s0 + j < S ? sm_w[s0 + j] : 0.f, v[j], acc);
     }
     const float gate = qg[(size_t) t * ldq + (size_t) h * 2 * hd + hd + i];
     out[((size_t) t * nq + h) * hd + i] = acc / z * sigmoidf_(gate);
@@ -202,8 +262,11 @@ extern "C" int fnx_attn_prep_append(float* qg, int ldq, float* k, int ldk, const
     FNX_REQUIRE(qg && k && v && q_norm && k_norm && kc && vc && pos0, "fnx_attn_prep_append: null pointer");
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_attn_prep_append: %d rows", T);
     FNX_REQUIRE(hd % 32 == 0 && hd <= 1024 && nrot <= hd && nrot % 2 == 0, "fnx_attn_prep_append: head dim %d, rotary %d", hd, nrot);
-    k_attn_prep_append<<<dim3(nq + 2 * nkv, T), hd, hd * sizeof(float), as_stream(st)>>>(qg, ldq, k, ldk, v, ldv, q_norm, k_norm, (__half*) kc, (__half*) vc,
+    {
+        const cudaError_t le_ = launch_k(k_attn_prep_append, dim3(dim3(nq + 2 * nkv, T)), dim3(hd), hd * sizeof(float), as_stream(st), qg, ldq, k, ldk, v, ldv, q_norm, k_norm, (__half*) kc, (__half*) vc,
                                                                                         nq, nkv, hd, nrot, pos0, depth, eps, rope_base);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_prep_append: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_attn_prep_append");
     return FNX_OK;
 }
@@ -220,6 +283,7 @@ extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc
     FNX_REQUIRE(hd == ATT_THREADS, "fnx_attn: head dim %d (this build: %d)", hd, ATT_THREADS);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQ, "fnx_attn: %d q heads over %d KV heads", nq, nkv);
     const int S = attn_splits(nkv);
+    FNX_REQUIRE(S <= 256, "fnx_attn: %d splits", S);
     float* acc = (float*) scratch;
     AttPartial* mz = (AttPartial*) (acc + (size_t) T * nq * S * hd);
     const size_t smem = (size_t) ATT_ROWS * ATT_MAXQ * hd * sizeof(float) + (size_t) ATT_CH * (hd + 8) * sizeof(__half) +
@@ -230,10 +294,16 @@ extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc
         FNX_CUDA_OK(cudaFuncSetAttribute(k_attn_part, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
         configured = true;
     }
-    k_attn_part<<<dim3(S, nkv, (T + ATT_ROWS - 1) / ATT_ROWS), ATT_THREADS, smem, as_stream(st)>>>(qg, ldq, (const __half*) kc, (const __half*) vc,
+    {
+        const cudaError_t le_ = launch_k(k_attn_part, dim3(dim3(S, nkv, (T + ATT_ROWS - 1) / ATT_ROWS)), dim3(ATT_THREADS), smem, as_stream(st), qg, ldq, (const __half*) kc, (const __half*) vc,
                                                                                                    acc, mz, T, nq, nkv, hd, pos0, parent);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_part: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_attn (partials)");
-    k_attn_combine<<<dim3(nq, T), hd, 0, as_stream(st)>>>(acc, mz, qg, ldq, out, nq, hd, S);
+    {
+        const cudaError_t le_ = launch_k(k_attn_combine, dim3(dim3(nq, T)), dim3(hd), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_attn (combine)");
     return FNX_OK;
 }

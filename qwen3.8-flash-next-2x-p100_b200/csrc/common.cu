@@ -1,6 +1,7 @@
 // Host-side plumbing shared by every entry point: the per-thread error text and device facts.
 #include "fnx_common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace fnxb {
@@ -25,6 +26,15 @@ int sm_count() {
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
     }
     return n;
+}
+
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("FNX_PDL");
+        on = v && v[0] == '1';
+    }
+    return on != 0;
 }
 
 }  // namespace fnxb

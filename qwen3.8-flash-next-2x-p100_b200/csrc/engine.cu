@@ -104,6 +104,9 @@ struct fnx_engine {
     std::map<int, std::pair<__half**, __half**>> commit_tables;   // per sequence: device tables of its K and V caches
     void* comm = nullptr;
     int proj_ld = 0;
+    unsigned long long* d_stats = nullptr;
+    unsigned long long launches = 0;
+    std::map<uint64_t, unsigned> graph_kernels;
 };
 
 namespace fnxb {
@@ -296,7 +299,7 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
     const Dims d = dims(e->c);
     const bool ep = e->c.ep_size > 1;
     FNX_TRY(fnx_router_route(L.wr, R, L.norm2, e->c.eps, T, d.E, d.H, d.K, e->e_lo, e->e_hi, 1, e->rlogits, e->topi, e->topw, e->jobs, e->njobs,
-                             e->err, e->st));
+                             e->d_stats, e->err, e->st));
     const int njobs_max = T * d.K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
     FNX_TRY(fnx_moe_gate_up(L.wgu, e->gu_bytes, e->e_lo, L.wsh_gu, d.E, e->jobs, e->njobs, njobs_max, R, L.norm2, e->c.eps, d.H, d.F, e->hbuf,
                             e->err, e->st));
@@ -391,6 +394,16 @@ static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
             return rc;
         }
         if (ce != cudaSuccess) return fail(FNX_E_CUDA, "graph capture: %s", cudaGetErrorString(ce));
+        size_t nn = 0;
+        FNX_CUDA_OK(cudaGraphGetNodes(g, nullptr, &nn));
+        std::vector<cudaGraphNode_t> nodes(nn);
+        FNX_CUDA_OK(cudaGraphGetNodes(g, nodes.data(), &nn));
+        unsigned nk = 0;
+        for (size_t i = 0; i < nn; ++i) {
+            cudaGraphNodeType ty;
+            if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) ++nk;
+        }
+        e->graph_kernels[key] = nk;
         cudaGraphExec_t x = nullptr;
         FNX_CUDA_OK(cudaGraphInstantiate(&x, g, 0));
         cudaGraphDestroy(g);
@@ -398,6 +411,7 @@ static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
     }
     FNX_CUDA_OK(cudaEventRecord(e->ev0, e->st));
     FNX_CUDA_OK(cudaGraphLaunch(it->second, e->st));
+    e->launches += e->graph_kernels[key];
     FNX_CUDA_OK(cudaEventRecord(e->ev1, e->st));
     return FNX_OK;
 }
@@ -474,6 +488,7 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_ctx, (size_t) c.n_seq * e->cache_rows, "seq.ctx"));
         FNX_TRY(dalloc(e, &e->d_ctx_n, c.n_seq, "seq.ctx_n"));
         FNX_TRY(dalloc(e, &e->err, 1, "buf.err"));
+        FNX_TRY(dalloc(e, &e->d_stats, 2, "buf.stats"));
         void* sc = nullptr;
         const size_t sb = fnx_attn_scratch_bytes(d.MAXR, d.nq, d.hd);
         FNX_TRY(dalloc(e, (uint8_t**) &sc, sb, "buf.attn_scratch"));
@@ -688,6 +703,16 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
 }
 
 extern "C" float fnx_engine_last_ms(const fnx_engine* e) { return e ? e->last_ms : 0.f; }
+extern "C" int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3) {
+    FNX_REQUIRE(e && h_out3, "fnx_engine_counters: null pointer");
+    unsigned long long st[2] = {0, 0};
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    FNX_CUDA_OK(cudaMemcpy(st, e->d_stats, sizeof st, cudaMemcpyDeviceToHost));
+    h_out3[0] = e->launches;
+    h_out3[1] = st[0];
+    h_out3[2] = st[1];
+    return FNX_OK;
+}
 extern "C" int fnx_engine_pos(const fnx_engine* e, int seq) { return e && seq >= 0 && seq < e->c.n_seq ? e->seqs[seq].pos : -1; }
 extern "C" fnx_stream fnx_engine_stream(fnx_engine* e) { return e ? (fnx_stream) e->st : nullptr; }
 

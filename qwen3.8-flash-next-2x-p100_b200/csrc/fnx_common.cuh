@@ -33,8 +33,33 @@ int fail(int code, const char* fmt, ...);
 
 inline cudaStream_t as_stream(fnx_stream s) { return (cudaStream_t) s; }
 int sm_count();
+// Programmatic dependent launch: every kernel of the window is launched so that it may start while its predecessor
+// in the stream drains.  A kernel does whatever does not depend on earlier kernels (its tables, its barriers, bulk
+// copies of weights), then pdl_wait() before it touches anything an earlier kernel wrote.  Off unless FNX_PDL=1:
+// inside the window's CUDA graph the overlap measured slower than plain stream order on B200.
+bool pdl_enabled();
+#if defined(__CUDACC__)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
 
 #if defined(__CUDACC__)
+// ---- programmatic dependent launch (no-ops when the launch carried no such dependency)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- warp helpers
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -19,23 +19,13 @@ namespace fnxb {
 
 constexpr int GDN_HS = 128, GDN_Q = 4, GDN_QC = GDN_HS / GDN_Q, GDN_THREADS = 128;
 
-// value of channel c at the k-th row before window row t on its path (k = 0: row t itself), reaching into the
-// starting history (3 rows, oldest first) past the root
-__device__ __forceinline__ float gdn_src(const float* __restrict__ qkvz, int stride, const float* __restrict__ hin, int ch,
-                                         const int* __restrict__ parent, int t, int k, int c) {
-    int a = t;
-    for (int i = 0; i < k; ++i) {
-        a = parent ? parent[a] : a - 1;
-        if (a < 0) return hin[(size_t) (2 - (k - 1 - i)) * ch + c];
-    }
-    return qkvz[(size_t) a * stride + c];
-}
-
 __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     k_gdn_core(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
                const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
                const float* __restrict__ nw, float* __restrict__ S_pool, const int* __restrict__ curp, int NS,
                const int* __restrict__ parent, float* __restrict__ y, int nk, int nv, int T, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) float sm[];
     cg::cluster_group cluster = cg::this_cluster();
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, kh = lv % nk, tid = threadIdx.x;
@@ -50,6 +40,8 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     float* ared = kred + 2 * 4 * GDN_QC;         // [T][4][QC]
     float* osum = ared + (size_t) T * 4 * GDN_QC;   // [T] this block's square sums (read by the cluster)
     float* red = osum + T;                       // [4][2 T]
+    float* xin = red + 8 * T;                    // [T + 3][2 HS + QC] conv inputs
+    int* anc = reinterpret_cast<int*>(xin + (size_t) (T + 3) * (2 * GDN_HS + GDN_QC));   // [T][3]
     const float* hin = hist_pool + (size_t) cur * hsz;
     if (tid < T) {
         const float* abt = ab + (size_t) tid * ldab;
@@ -57,15 +49,48 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
         gates[2 * tid] = expf((x > 20.0f ? x : log1pf(expf(x))) * a_[lv]);
         gates[2 * tid + 1] = 1.0f / (1.0f + expf(-abt[nv + lv]));
     }
-    // ---- conv + silu: the head's q and k channels (HS each), this block's QC v channels; histories to the slots
-    for (int e = tid; e < 2 * GDN_HS + GDN_QC; e += GDN_THREADS) {
+    // ---- the conv inputs this block needs, staged with every load in flight at once: rows 0..2 = the starting
+    // history (oldest first), row 3 + t = window row t; columns = the head's q (HS), k (HS), this block's v (QC)
+    constexpr int NC = 2 * GDN_HS + GDN_QC;
+    auto chan = [&](int e) {
+        return e < GDN_HS ? kh * GDN_HS + e : e < 2 * GDN_HS ? nk * GDN_HS + kh * GDN_HS + (e - GDN_HS) : 2 * nk * GDN_HS + lv * GDN_HS + qq * GDN_QC + (e - 2 * GDN_HS);
+    };
+    for (int i0 = tid; i0 < (T + 3) * NC; i0 += 4 * GDN_THREADS) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = i0 + j * GDN_THREADS;
+            v[j] = 0.f;
+            if (i < (T + 3) * NC) {
+                const int r = i / NC, c = chan(i % NC);
+                v[j] = r < 3 ? hin[(size_t) r * ch + c] : qkvz[(size_t) (r - 3) * stride + c];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = i0 + j * GDN_THREADS;
+            if (i < (T + 3) * NC) xin[i] = v[j];
+        }
+    }
+    // the three rows before each window row on its path, as rows of xin (past the root: the history)
+    if (tid < T) {
+        int a = tid;
+        for (int k = 1; k <= 3; ++k) {
+            if (a >= 0) a = parent ? parent[a] : a - 1;
+            else --a;                      // a = -1 - (rows past the root)
+            anc[tid * 3 + k - 1] = a >= 0 ? 3 + a : 3 + a;   // -1 -> row 2 (newest history), -2 -> row 1, -3 -> row 0
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < NC; e += GDN_THREADS) {
         const int part = e < GDN_HS ? 0 : e < 2 * GDN_HS ? 1 : 2, i = part < 2 ? e - part * GDN_HS : e - 2 * GDN_HS;
-        const int c = part == 0 ? kh * GDN_HS + i : part == 1 ? nk * GDN_HS + kh * GDN_HS + i : 2 * nk * GDN_HS + lv * GDN_HS + qq * GDN_QC + i;
-        const float w0 = convw[c * 4], w1 = convw[c * 4 + 1], w2 = convw[c * 4 + 2], w3 = convw[c * 4 + 3];
+        const int c = chan(e);
+        const float4 cw = *reinterpret_cast<const float4*>(convw + c * 4);
+        const float w0 = cw.x, w1 = cw.y, w2 = cw.z, w3 = cw.w;
         const bool writes = part == 2 || (lv < nk && qq == 0);   // one block per channel writes its history
         for (int t = 0; t < T; ++t) {
-            const float x3 = gdn_src(qkvz, stride, hin, ch, parent, t, 3, c), x2 = gdn_src(qkvz, stride, hin, ch, parent, t, 2, c);
-            const float x1 = gdn_src(qkvz, stride, hin, ch, parent, t, 1, c), x0 = qkvz[(size_t) t * stride + c];
+            const float x3 = xin[anc[t * 3 + 2] * NC + e], x2 = xin[anc[t * 3 + 1] * NC + e], x1 = xin[anc[t * 3] * NC + e];
+            const float x0 = xin[(3 + t) * NC + e];
             const float x = w0 * x3 + w1 * x2 + w2 * x1 + w3 * x0;
             const float v = x / (1.0f + expf(-x));
             if (part == 0) xq[t * GDN_HS + i] = v;
@@ -140,14 +165,19 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
         const float sq = warp_sum(o * o);
         if (lane == 0) osum[t] = sq;
     }
+    // the gate inputs z, fetched while the cluster gathers (they do not depend on it)
+    float zv[FNX_MAX_ROWS / 4];
+    for (int t = warp, j = 0; t < T; t += 4, ++j) zv[j] = qkvz[(size_t) t * stride + ch + lv * GDN_HS + col];
+    const float nwv = nw[col];
     cluster.sync();
-    for (int t = warp, j = 0; t < T; t += 4, ++j) {
-        float ms = 0.f;
-        for (int b = 0; b < GDN_Q; ++b) ms += cluster.map_shared_rank(osum, b)[t];
-        ms /= (float) GDN_HS;
-        const float z = qkvz[(size_t) t * stride + ch + lv * GDN_HS + col];
-        y[(size_t) t * nv * GDN_HS + lv * GDN_HS + col] = ov[j] * rsqrtf(ms + eps) * nw[col] / (1.0f + expf(-z));
-    }
+    // every block's T square sums into this block's shared memory, one remote read per thread
+    float* msum = red;   // [T] (red is free by now)
+    for (int i = tid; i < T * GDN_Q; i += GDN_THREADS) kred[i] = cluster.map_shared_rank(osum, i % GDN_Q)[i / GDN_Q];
+    __syncthreads();
+    if (tid < T) msum[tid] = ((kred[tid * GDN_Q] + kred[tid * GDN_Q + 1]) + (kred[tid * GDN_Q + 2] + kred[tid * GDN_Q + 3])) / (float) GDN_HS;
+    __syncthreads();
+    for (int t = warp, j = 0; t < T; t += 4, ++j)
+        y[(size_t) t * nv * GDN_HS + lv * GDN_HS + col] = ov[j] * rsqrtf(msum[t] + eps) * nwv / (1.0f + expf(-zv[j]));
     cluster.sync();   // no block may leave while a neighbour still reads its shared memory
 }
 
@@ -162,13 +192,16 @@ extern "C" int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int lda
     FNX_REQUIRE(hs == GDN_HS, "fnx_gdn_core: head dim %d (this build: %d)", hs, GDN_HS);
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && NS >= T + 1, "fnx_gdn_core: %d rows need at least %d state slots, have %d", T, T + 1, NS);
     FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_core: %d key heads, %d value heads", nk, nv);
-    const size_t smem = sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T);
+    const size_t smem = sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T + (size_t) (T + 3) * (2 * GDN_HS + GDN_QC) + 3 * T);
     static bool configured = false;
     if (!configured) {
         FNX_CUDA_OK(cudaFuncSetAttribute(k_gdn_core, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         configured = true;
     }
-    k_gdn_core<<<nv * GDN_Q, GDN_THREADS, smem, as_stream(st)>>>(qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps);
+    {
+        const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), smem, as_stream(st), qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_gdn_core");
     return FNX_OK;
 }

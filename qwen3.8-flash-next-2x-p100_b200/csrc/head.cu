@@ -18,12 +18,33 @@ __device__ __forceinline__ unsigned long long key64(float v, int i) { return ((u
 
 __global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logits, int V, int* __restrict__ best_i,
                                                  float* __restrict__ best_v, unsigned* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ unsigned long long red[32];
     const int t = blockIdx.x, tid = threadIdx.x;
     const float* l = logits + (size_t) t * V;
     unsigned long long best = 0;
     bool bad = false;
-    for (int i = tid; i < V; i += 1024) {
+    // four float4 per thread in flight; a tail of fewer than 4 values is read one by one
+    const int V4 = (((uintptr_t) l & 15) == 0) ? V / 4 : 0;
+    for (int i0 = tid; i0 < V4; i0 += 4096) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = i0 + 1024 * j < V4 ? reinterpret_cast<const float4*>(l)[i0 + 1024 * j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = i0 + 1024 * j;
+            if (i >= V4) continue;
+            const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                bad |= !isfinite(e[c]);
+                const unsigned long long k = key64(e[c], 4 * i + c);
+                best = k > best ? k : best;
+            }
+        }
+    }
+    for (int i = 4 * V4 + tid; i < V; i += 1024) {
         const float v = l[i];
         bad |= !isfinite(v);
         const unsigned long long k = key64(v, i);
@@ -50,6 +71,8 @@ __global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logit
 }
 
 __global__ void __launch_bounds__(1024) k_top_tokens(const float* __restrict__ logits, int V, float* __restrict__ out_v, int* __restrict__ out_i) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ unsigned hist[256];
     __shared__ unsigned long long prefix_s, sel[FNX_TOPK_N];
     __shared__ unsigned need_s, nsel;
@@ -101,11 +124,15 @@ __global__ void __launch_bounds__(1024) k_top_tokens(const float* __restrict__ l
 }
 
 __global__ void k_embed_rows(const __half* __restrict__ table, const int* __restrict__ tok, int H, float* __restrict__ R) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < H) R[(size_t) t * H + i] = __half2float(table[(size_t) tok[t] * H + i]);
 }
 
 __global__ void __launch_bounds__(256) k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int n, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float red[8];
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* xr = x + (size_t) r * n;
@@ -126,28 +153,40 @@ using namespace fnxb;
 
 extern "C" int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st) {
     FNX_REQUIRE(logits && best_i && err && T >= 1 && V >= 1, "fnx_argmax: bad arguments");
-    k_argmax<<<T, 1024, 0, as_stream(st)>>>(logits, V, best_i, best_v, err);
+    {
+        const cudaError_t le_ = launch_k(k_argmax, dim3(T), dim3(1024), 0, as_stream(st), logits, V, best_i, best_v, err);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_argmax: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_argmax");
     return FNX_OK;
 }
 
 extern "C" int fnx_top_tokens(const float* logits, int T, int V, float* out_v, int* out_i, fnx_stream st) {
     FNX_REQUIRE(logits && out_v && out_i && T >= 1 && V >= FNX_TOPK_N, "fnx_top_tokens: bad arguments (vocabulary of at least %d)", FNX_TOPK_N);
-    k_top_tokens<<<T, 1024, 0, as_stream(st)>>>(logits, V, out_v, out_i);
+    {
+        const cudaError_t le_ = launch_k(k_top_tokens, dim3(T), dim3(1024), 0, as_stream(st), logits, V, out_v, out_i);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_top_tokens: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_top_tokens");
     return FNX_OK;
 }
 
 extern "C" int fnx_embed_rows(const void* table_f16, const int* tok, int T, int H, float* R, fnx_stream st) {
     FNX_REQUIRE(table_f16 && tok && R && T >= 1, "fnx_embed_rows: bad arguments");
-    k_embed_rows<<<dim3((H + 255) / 256, T), 256, 0, as_stream(st)>>>((const __half*) table_f16, tok, H, R);
+    {
+        const cudaError_t le_ = launch_k(k_embed_rows, dim3(dim3((H + 255) / 256, T)), dim3(256), 0, as_stream(st), (const __half*) table_f16, tok, H, R);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_embed_rows: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_embed_rows");
     return FNX_OK;
 }
 
 extern "C" int fnx_rmsnorm(const float* x, const float* w, float* y, int rows, int n, float eps, fnx_stream st) {
     FNX_REQUIRE(x && w && y && rows >= 1 && n >= 1, "fnx_rmsnorm: bad arguments");
-    k_rmsnorm<<<rows, 256, 0, as_stream(st)>>>(x, w, y, n, eps);
+    {
+        const cudaError_t le_ = launch_k(k_rmsnorm, dim3(rows), dim3(256), 0, as_stream(st), x, w, y, n, eps);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_rmsnorm: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_rmsnorm");
     return FNX_OK;
 }

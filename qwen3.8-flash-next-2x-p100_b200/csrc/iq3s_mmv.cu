@@ -27,7 +27,7 @@ namespace fnxb {
 __device__ const uint32_t g_iq3s_grid[512] = {FNX_IQ3S_GRID_VALUES};
 
 enum { MMV_DENSE = 0, MMV_GATEUP = 1, MMV_DOWN = 2 };
-constexpr int MMV_THREADS = 256, MMV_WARPS = 8, MMV_ITEMS = 16;
+constexpr int MMV_THREADS = 512, MMV_WARPS = 16, MMV_ITEMS = 16;
 constexpr int MMV_STEP_BYTES = MMV_ITEMS * TILE_BYTES;   // 28,160
 constexpr int MMV_TABLE_BYTES = 512 * 128;
 
@@ -70,8 +70,8 @@ __host__ __device__ inline size_t mmv_smem_bytes(int K, int NG, int nstage) {
     b += (size_t) NG * (K / 32) * 32 * sizeof(uint2);       // xq
     b += (size_t) NG * (K / 256) * 8 * sizeof(float);       // xs
     b += (size_t) 2 * MMV_ITEMS * 16 * 4 * NG * sizeof(float);   // part, double buffered
-    b += 16 * sizeof(float);                                // rs
-    b += 8 * sizeof(uint64_t);                              // barriers
+    b += 32 * sizeof(float);                                // rs: square sums per (row slot, chunk)
+    b += 8 * sizeof(uint64_t);                              // barriers (one per stage, at most 8)
     return b;
 }
 
@@ -80,6 +80,14 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+// four s32 -> four saturated s8 in one word (byte 0 = a)
+__device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return r;
 }
 
 template <int I>
@@ -155,64 +163,85 @@ __device__ __forceinline__ void mmv_item(const uint8_t* tile, const uint8_t* tab
 
 // Quantises the job's activation rows into the MMA's B layout: cell (sub-block sbG, column n, thread q) = the 8
 // int8 values x[32 sbG + 8 q .. + 7] of row n (columns 0..3: level 1 of rows 0..3, columns 4..7: level 2).
+// A task = (row slot, chunk of up to 4 blocks): a warp issues all of a task's loads at once, so the whole prologue
+// costs one or two memory latencies.  With an RMS norm the row's scalar 1 / rms multiplies every value, so the
+// int8 codes are those of x * w and only the block scales take the factor, after the row's square sum is known.
 template <int NG, int MODE>
 __device__ __forceinline__ void mmv_load_x(const MmvParams& p, const MmvSmem& sm, const int* xrow, int ntok, int tid) {
     const int warp = tid >> 5, lane = tid & 31, KB = p.K / 256, nslot = 4 * NG;
-    if (MODE != MMV_DOWN && p.norm_w) {
-        for (int ts = warp; ts < ntok; ts += MMV_WARPS) {
-            const float* xr = p.x + (size_t) xrow[ts] * p.ldx;
-            float ss = 0.f;
-            for (int i = lane * 4; i < p.K; i += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(xr + i);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    const int CB = KB < 4 ? KB : 4, nchunk = KB / CB;   // blocks per chunk, chunks per row
+    const bool norm = MODE != MMV_DOWN && p.norm_w != nullptr;
+    for (int task = warp; task < nslot * nchunk; task += MMV_WARPS) {
+        const int ts = task / nchunk, ck = task % nchunk, ng = ts >> 2, n = ts & 3;
+        const bool live = ts < ntok;
+        float4 v[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (j < CB) {
+                v[j][0] = v[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live) {
+                    const float* xr = p.x + (size_t) xrow[ts] * p.ldx + (ck * CB + j) * 256 + lane * 8;
+                    v[j][0] = *reinterpret_cast<const float4*>(xr);
+                    v[j][1] = *reinterpret_cast<const float4*>(xr + 4);
+                }
             }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (j < CB) {
+                const int blk = ck * CB + j;
+                float x8[8] = {v[j][0].x, v[j][0].y, v[j][0].z, v[j][0].w, v[j][1].x, v[j][1].y, v[j][1].z, v[j][1].w};
+                if (norm) {
+                    const float* w = p.norm_w + blk * 256 + lane * 8;
+                    const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+                    const float w8[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        ss = fmaf(x8[i], x8[i], ss);
+                        x8[i] *= w8[i];
+                    }
+                }
+                float am = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(x8[i]));
+                am = warp_max(am);
+                const float d = am / 127.0f, inv = am > 0.f ? 127.0f / am : 0.f, inv2 = inv * 256.0f;
+                int a8[8], b8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    a8[i] = __float2int_rn(x8[i] * inv);                              // |a| <= 127 by construction
+                    b8[i] = __float2int_rn((x8[i] - (float) a8[i] * d) * inv2);       // |b| <= 128: saturated when packed
+                }
+                const uint32_t lo1 = pack_s8x4(a8[0], a8[1], a8[2], a8[3]), hi1 = pack_s8x4(a8[4], a8[5], a8[6], a8[7]);
+                const uint32_t lo2 = pack_s8x4(b8[0], b8[1], b8[2], b8[3]), hi2 = pack_s8x4(b8[4], b8[5], b8[6], b8[7]);
+                const int sbG = blk * 8 + (lane >> 2), q = lane & 3;
+                uint2* c1 = sm.xq + ((size_t) (ng * (p.K / 32) + sbG) * 8 + n) * 4 + q;
+                c1[0] = make_uint2(lo1, hi1);
+                c1[16] = make_uint2(lo2, hi2);   // column n + 4
+                if (lane == 0) {
+                    float* xs = sm.xs + (size_t) (ng * KB + blk) * 8;
+                    xs[n] = d;
+                    xs[n + 4] = d * (1.0f / 256.0f);
+                }
+            }
+        if (norm) {
             ss = warp_sum(ss);
-            if (lane == 0) sm.rs[ts] = rsqrtf(ss / (float) p.K + p.eps);
+            if (lane == 0) sm.rs[ts * 4 + ck] = ss;
+        }
+    }
+    __syncthreads();
+    if (norm) {
+        for (int i = tid; i < ntok * KB; i += MMV_THREADS) {
+            const int ts = i / KB, blk = i % KB, ng = ts >> 2, n = ts & 3;
+            float ss = 0.f;
+            for (int c = 0; c < nchunk; ++c) ss += sm.rs[ts * 4 + c];
+            const float r = rsqrtf(ss / (float) p.K + p.eps);
+            float* xs = sm.xs + (size_t) (ng * KB + blk) * 8;
+            xs[n] *= r;
+            xs[n + 4] *= r;
         }
         __syncthreads();
     }
-    for (int task = warp; task < nslot * KB; task += MMV_WARPS) {
-        const int ts = task / KB, blk = task % KB, ng = ts >> 2, n = ts & 3;
-        const int sbG = blk * 8 + (lane >> 2), q = lane & 3;
-        uint2* c1 = sm.xq + ((size_t) (ng * (p.K / 32) + sbG) * 8 + n) * 4 + q;
-        uint2* c2 = c1 + 16;   // column n + 4
-        float* xs = sm.xs + (size_t) (ng * KB + blk) * 8;
-        if (ts >= ntok) {
-            *c1 = make_uint2(0u, 0u);
-            *c2 = make_uint2(0u, 0u);
-            if (lane == 0) { xs[n] = 0.f; xs[n + 4] = 0.f; }
-            continue;
-        }
-        const float* xr = p.x + (size_t) xrow[ts] * p.ldx + blk * 256 + lane * 8;
-        float4 v0 = *reinterpret_cast<const float4*>(xr), v1 = *reinterpret_cast<const float4*>(xr + 4);
-        if (MODE != MMV_DOWN && p.norm_w) {
-            const float r = sm.rs[ts];
-            const float* w = p.norm_w + blk * 256 + lane * 8;
-            const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
-            v0.x *= r * w0.x; v0.y *= r * w0.y; v0.z *= r * w0.z; v0.w *= r * w0.w;
-            v1.x *= r * w1.x; v1.y *= r * w1.y; v1.z *= r * w1.z; v1.w *= r * w1.w;
-        }
-        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        float am = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
-        am = warp_max(am);
-        const float d = am / 127.0f, inv = am > 0.f ? 127.0f / am : 0.f, inv2 = inv * 256.0f;
-        uint32_t lo1 = 0, hi1 = 0, lo2 = 0, hi2 = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            int a = __float2int_rn(v[i] * inv);
-            a = max(-127, min(127, a));
-            int b = __float2int_rn((v[i] - (float) a * d) * inv2);
-            b = max(-127, min(127, b));
-            if (i < 4) { lo1 |= (uint32_t) (a & 255) << (8 * i); lo2 |= (uint32_t) (b & 255) << (8 * i); }
-            else { hi1 |= (uint32_t) (a & 255) << (8 * (i - 4)); hi2 |= (uint32_t) (b & 255) << (8 * (i - 4)); }
-        }
-        *c1 = make_uint2(lo1, hi1);
-        *c2 = make_uint2(lo2, hi2);
-        if (lane == 0) { xs[n] = d; xs[n + 4] = d * (1.0f / 256.0f); }
-    }
-    __syncthreads();
 }
 
 template <int NG, int MODE>
@@ -228,29 +257,17 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
         sm.xq = reinterpret_cast<uint2*>(b); b += (size_t) NG * (p.K / 32) * 32 * sizeof(uint2);
         sm.xs = reinterpret_cast<float*>(b); b += (size_t) NG * KB * 8 * sizeof(float);
         sm.part = reinterpret_cast<float*>(b); b += (size_t) 2 * MMV_ITEMS * 16 * 4 * NG * sizeof(float);
-        sm.rs = reinterpret_cast<float*>(b); b += 16 * sizeof(float);
+        sm.rs = reinterpret_cast<float*>(b); b += 32 * sizeof(float);
         sm.bars = reinterpret_cast<uint64_t*>(b);
     }
-    // the codebook, one copy per bank: entry e at byte e * 128 + 4 * lane
-    for (int e = tid; e < 512; e += MMV_THREADS) {
-        const uint32_t v = g_iq3s_grid[e];
-        uint4* d = reinterpret_cast<uint4*>(sm.table + e * 128);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) d[i] = make_uint4(v, v, v, v);
-    }
+    pdl_launch_dependents();
     if (tid == 0) {
         for (int i = 0; i < NST; ++i) mbar_init(&sm.bars[i], 1);
         fence_barrier_init();
     }
-    __syncthreads();
-
-    const int njobs = p.jobs ? min(*p.njobs, p.njobs_max) : 1;
     // steps of one job: gate|up walks h-tiles (TPS / 2 per step), the others row tiles (TPS per step)
     const int spj = MODE == MMV_GATEUP ? p.rows / (8 * TPS) : p.rows / (16 * TPS);
-    const long long total = (long long) njobs * spj;
-    const int s0 = (int) (total * blockIdx.x / gridDim.x), s1 = (int) (total * (blockIdx.x + 1) / gridDim.x);
-    if (s0 >= s1) return;
-
+    int njobs = 1, s0 = 0, s1 = 0;
     auto job_weights = [&](int j) -> const uint8_t* {
         if (!p.jobs) return p.W;
         const int e = p.jobs[j].w;
@@ -269,8 +286,33 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
             bulk_g2s(dst, W + (size_t) ls * MMV_STEP_BYTES, MMV_STEP_BYTES, &sm.bars[st]);
         }
     };
-    if (tid == 0)
-        for (int i = 0; i < NST && s0 + i < s1; ++i) issue(s0 + i);
+    auto plan = [&]() {
+        const long long total = (long long) njobs * spj;
+        s0 = (int) (total * blockIdx.x / gridDim.x);
+        s1 = (int) (total * (blockIdx.x + 1) / gridDim.x);
+    };
+    // a dense matrix is the same whatever ran before: its first steps are on their way before anything else
+    if (MODE == MMV_DENSE && !p.jobs) {
+        plan();
+        if (tid == 0)
+            for (int i = 0; i < NST && s0 + i < s1; ++i) issue(s0 + i);
+    }
+    // the codebook, one copy per bank: entry e at byte e * 128 + 4 * lane
+    for (int e = tid; e < 512; e += MMV_THREADS) {
+        const uint32_t v = g_iq3s_grid[e];
+        uint4* d = reinterpret_cast<uint4*>(sm.table + e * 128);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[i] = make_uint4(v, v, v, v);
+    }
+    pdl_wait();   // from here on: what earlier kernels of the stream wrote (activations, job lists)
+    __syncthreads();
+    if (!(MODE == MMV_DENSE && !p.jobs)) {
+        njobs = p.jobs ? min(*p.njobs, p.njobs_max) : 1;
+        plan();
+        if (tid == 0)
+            for (int i = 0; i < NST && s0 + i < s1; ++i) issue(s0 + i);
+    }
+    if (s0 >= s1) return;
 
     const int xq_gs = (p.K / 32) * 32, xs_gs = KB * 8;
     int cur_job = -1, ntok = 0;
@@ -301,9 +343,8 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
         }
         const uint8_t* stage = sm.stage + (size_t) st * MMV_STEP_BYTES;
         float* part = sm.part + (size_t) buf * MMV_ITEMS * 16 * 4 * NG;
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int it = warp + 8 * k, blk = it % KB;
+        {
+            const int it = warp, blk = it % KB;
             float acc[NG][4];
 #pragma unroll
             for (int ng = 0; ng < NG; ++ng)
@@ -361,10 +402,10 @@ template <int NG, int MODE>
 static int launch_mmv(const MmvParams& p0, cudaStream_t st) {
     MmvParams p = p0;
     const int KB = p.K / 256;
-    p.nstage = 3;
+    p.nstage = 4;   // as many 28 KB steps in flight as the shared memory left by the codebook and the activations holds
     size_t smem = mmv_smem_bytes(p.K, NG, p.nstage);
-    if (smem > 227 * 1024) {
-        p.nstage = 2;
+    while (smem > 227 * 1024 && p.nstage > 2) {
+        --p.nstage;
         smem = mmv_smem_bytes(p.K, NG, p.nstage);
     }
     if (smem > 227 * 1024) return fail(FNX_E_ARG, "iq3s_mmv: %d columns x %d rows need %zu bytes of shared memory", p.K, 4 * NG, smem);
@@ -374,8 +415,10 @@ static int launch_mmv(const MmvParams& p0, cudaStream_t st) {
         FNX_CUDA_OK(cudaFuncSetAttribute(k_iq3s_mmv<NG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
-    k_iq3s_mmv<NG, MODE><<<sm_count(), MMV_THREADS, smem, st>>>(p);
-    FNX_LAUNCH_OK("iq3s_mmv");
+    {
+        const cudaError_t le_ = launch_k(k_iq3s_mmv<NG, MODE>, dim3(sm_count()), dim3(MMV_THREADS), smem, st, p);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "iq3s_mmv: launch failed: %s", cudaGetErrorString(le_));
+    }
     return FNX_OK;
 }
 

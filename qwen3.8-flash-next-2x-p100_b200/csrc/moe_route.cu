@@ -8,40 +8,52 @@
 
 namespace fnxb {
 
-constexpr int RT_WARPS = 4, RT_TOK = 8, RT_MAXE = 1024;
+constexpr int RT_WARPS = 8, RT_TOK = 8, RT_MAXE = 1024;
 
 __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restrict__ Wr, const float* __restrict__ x,
                                                           const float* __restrict__ norm_w, float eps, int T, int E, int H, int K,
                                                           int e_lo, int e_hi, int add_shared, float* __restrict__ logits,
                                                           int* __restrict__ topi, float* __restrict__ topw, fnx_job* __restrict__ jobs,
-                                                          int* __restrict__ njobs, unsigned* __restrict__ err) {
-    extern __shared__ __align__(16) float xs[];   // [RT_TOK][H]
-    __shared__ float rs[RT_TOK];
+                                                          int* __restrict__ njobs, unsigned long long* __restrict__ stats, unsigned* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float xs[];   // [RT_TOK][H]: x * norm_w (the row's 1 / rms is applied to the sums)
+    __shared__ float rs[RT_TOK], ssw[RT_TOK][RT_WARPS];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = blockIdx.x * RT_WARPS + warp;
+    constexpr int NT = RT_WARPS * 32;
     for (int t0 = 0; t0 < T; t0 += RT_TOK) {
         const int nt = min(RT_TOK, T - t0);
         __syncthreads();
-        for (int t = warp; t < nt; t += RT_WARPS) {
+        // stage the rows: every thread issues its loads of a row together (H / 512 <= 8 float4 each)
+        for (int t = 0; t < nt; ++t) {
             const float* xr = x + (size_t) (t0 + t) * H;
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = tid * 4 + j * NT * 4;
+                v[j] = c < H ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             float ss = 0.f;
-            for (int i = lane * 4; i < H; i += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(xr + i);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = tid * 4 + j * NT * 4;
+                if (c >= H) continue;
+                ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+                if (norm_w) {
+                    const float4 w = *reinterpret_cast<const float4*>(norm_w + c);
+                    v[j].x *= w.x; v[j].y *= w.y; v[j].z *= w.z; v[j].w *= w.w;
+                }
+                *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v[j];
             }
             ss = warp_sum(ss);
-            if (lane == 0) rs[t] = norm_w ? rsqrtf(ss / (float) H + eps) : 1.0f;
+            if (lane == 0) ssw[t][warp] = ss;
         }
         __syncthreads();
-        for (int i = tid * 4; i < nt * H; i += RT_WARPS * 32 * 4) {
-            const int t = i / H, c = i % H;
-            float4 v = *reinterpret_cast<const float4*>(x + (size_t) (t0 + t) * H + c);
-            if (norm_w) {
-                const float4 w = *reinterpret_cast<const float4*>(norm_w + c);
-                const float r = rs[t];
-                v.x *= r * w.x; v.y *= r * w.y; v.z *= r * w.z; v.w *= r * w.w;
-            }
-            *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v;
+        if (tid < nt) {
+            float ss = 0.f;
+            for (int w = 0; w < RT_WARPS; ++w) ss += ssw[tid][w];
+            rs[tid] = norm_w ? rsqrtf(ss / (float) H + eps) : 1.0f;
         }
         __syncthreads();
         if (row <= E) {
@@ -49,22 +61,32 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
 #pragma unroll
             for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
             const float* wr = Wr + (size_t) row * H;
-            for (int i = lane * 4; i < H; i += 128) {
-                const float4 w = *reinterpret_cast<const float4*>(wr + i);
+            for (int i0 = 0; i0 < H; i0 += 1024) {   // 8 float4 of the weight row in flight per lane
+                float4 w[8];
 #pragma unroll
-                for (int t = 0; t < RT_TOK; ++t)
-                    if (t < nt) {
-                        const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + i);
-                        acc[t] = fmaf(w.x, v.x, acc[t]);
-                        acc[t] = fmaf(w.y, v.y, acc[t]);
-                        acc[t] = fmaf(w.z, v.z, acc[t]);
-                        acc[t] = fmaf(w.w, v.w, acc[t]);
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    const int i = i0 + lane * 4 + j * 128;
+                    w[j] = i < H ? *reinterpret_cast<const float4*>(wr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = i0 + lane * 4 + j * 128;
+                    if (i >= H) continue;
+#pragma unroll
+                    for (int t = 0; t < RT_TOK; ++t)
+                        if (t < nt) {
+                            const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + i);
+                            acc[t] = fmaf(w[j].x, v.x, acc[t]);
+                            acc[t] = fmaf(w[j].y, v.y, acc[t]);
+                            acc[t] = fmaf(w[j].z, v.z, acc[t]);
+                            acc[t] = fmaf(w[j].w, v.w, acc[t]);
+                        }
+                }
             }
 #pragma unroll
             for (int t = 0; t < RT_TOK; ++t)
                 if (t < nt) {
-                    const float s = warp_sum(acc[t]);
+                    const float s = warp_sum(acc[t]) * rs[t];
                     if (lane == 0) {
                         logits[(size_t) (t0 + t) * (E + 1) + row] = s;
                         if (!isfinite(s)) atomicOr(err, (unsigned) FNX_ERR_NONFINITE);
@@ -74,6 +96,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     }
     // ---- the last block to get here routes
     __shared__ bool last;
+    __shared__ int s_topi[FNX_MAX_ROWS * 32];
     __threadfence();
     __syncthreads();
     if (tid == 0) last = atomicAdd(&njobs[1], 1) == (int) gridDim.x - 1;
@@ -103,7 +126,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
             const float w = expf(bv - top);
             z += w;
             if (lane == k) mine = w;
-            if (lane == 0) topi[t * K + k] = bi;
+            if (lane == 0) { topi[t * K + k] = bi; s_topi[t * K + k] = bi; }
 #pragma unroll
             for (int j = 0; j < RT_MAXE / 32; ++j)
                 if (lane + 32 * j == bi) v[j] = -INFINITY;
@@ -111,40 +134,63 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
         if (lane < K) topw[t * K + lane] = mine / z;
     }
     __syncthreads();
-    // jobs in ascending expert order: expert e's rows in row order, 4 per job; then the shared expert's
-    __shared__ int cnt[RT_MAXE], base[RT_MAXE + 1];
-    for (int e = tid; e < E; e += RT_WARPS * 32) {
+    // jobs in ascending expert order: expert e's rows in row order, 4 per job; then the shared expert's.
+    // Thread `tid` owns experts [tid * EPT, (tid + 1) * EPT): counts, a block-wide exclusive scan, then the fill.
+    constexpr int NTH = RT_WARPS * 32, EPT = RT_MAXE / NTH;
+    __shared__ int wsum_[RT_WARPS];
+    __shared__ int routed_total;
+    int cnt_[EPT], mine = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int e = tid * EPT + j;
         int c = 0;
-        if (e >= e_lo && e < e_hi)
-            for (int i = 0; i < T * K; ++i) c += topi[i] == e;
-        cnt[e] = (c + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+        if (e < E && e >= e_lo && e < e_hi)
+            for (int i = 0; i < T * K; ++i) c += s_topi[i] == e;
+        cnt_[j] = (c + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+        mine += cnt_[j];
     }
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum_[warp] = incl;
     __syncthreads();
-    if (tid == 0) {
-        int s = 0;
-        for (int e = 0; e < E; ++e) { base[e] = s; s += cnt[e]; }
-        base[E] = s;
+    int base_ = incl - mine;
+    for (int w = 0; w < warp; ++w) base_ += wsum_[w];
+    if (tid == NTH - 1) {
+        const int s = base_ + mine;
+        routed_total = s;
         njobs[0] = s + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
         njobs[1] = 0;
+        if (stats) {
+            atomicAdd(&stats[0], (unsigned long long) s);
+            atomicAdd(&stats[1], 1ull);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int e = tid * EPT + j;
+        if (cnt_[j]) {
+            int n = 0;
+            fnx_job* jb = jobs + base_;
+            for (int i = 0; i < T * K; ++i)
+                if (s_topi[i] == e) {
+                    fnx_job& jj = jb[n / FNX_JOB_TOK];
+                    jj.w = e;
+                    jj.y[n % FNX_JOB_TOK] = i / K;
+                    jj.out[n % FNX_JOB_TOK] = i;
+                    jj.n = n % FNX_JOB_TOK + 1;
+                    ++n;
+                }
+            base_ += cnt_[j];
+        }
     }
     __syncthreads();
-    for (int e = tid; e < E; e += RT_WARPS * 32) {
-        if (!cnt[e]) continue;
-        int n = 0;
-        fnx_job* jb = jobs + base[e];
-        for (int i = 0; i < T * K; ++i)
-            if (topi[i] == e) {
-                fnx_job& j = jb[n / FNX_JOB_TOK];
-                j.w = e;
-                j.y[n % FNX_JOB_TOK] = i / K;
-                j.out[n % FNX_JOB_TOK] = i;
-                j.n = n % FNX_JOB_TOK + 1;
-                ++n;
-            }
-    }
     if (add_shared)
         for (int t = tid; t < T; t += RT_WARPS * 32) {
-            fnx_job& j = jobs[base[E] + t / FNX_JOB_TOK];
+            fnx_job& j = jobs[routed_total + t / FNX_JOB_TOK];
             j.w = E;
             j.y[t % FNX_JOB_TOK] = t;
             j.out[t % FNX_JOB_TOK] = T * K + t;
@@ -155,16 +201,32 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
 __global__ void k_combine(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
                           const float* __restrict__ logits, int T, int E, int H, int K, int e_lo, int e_hi, int add_shared,
                           float* __restrict__ out, int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= H) return;
-    float s = 0.f;
-    for (int k = 0; k < K; ++k) {
-        const int e = topi[t * K + k];
-        if (e >= e_lo && e < e_hi) s = fmaf(topw[t * K + k], part[((size_t) t * K + k) * H + i], s);
+    // the picks' weights first (0 outside the expert range), then every addend's load at once
+    float w[32], v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        w[k] = 0.f;
+        if (k < K) {
+            const int e = topi[t * K + k];
+            w[k] = e >= e_lo && e < e_hi ? topw[t * K + k] : 0.f;
+        }
     }
-    if (add_shared) s += sigmoidf_(logits[(size_t) t * (E + 1) + E]) * part[((size_t) T * K + t) * H + i];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = k < K && w[k] != 0.f ? part[((size_t) t * K + k) * H + i] : 0.f;
+    const float shv = add_shared ? part[((size_t) T * K + t) * H + i] : 0.f;
+    const float shl = add_shared ? logits[(size_t) t * (E + 1) + E] : 0.f;
     float* o = out + (size_t) t * H + i;
-    *o = accumulate ? *o + s : s;
+    const float prev = accumulate ? *o : 0.f;
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+        if (k < K) s = fmaf(w[k], v[k], s);
+    if (add_shared) s += sigmoidf_(shl) * shv;
+    *o = prev + s;
 }
 
 }  // namespace fnxb
@@ -173,7 +235,7 @@ using namespace fnxb;
 
 extern "C" int fnx_router_route(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K, int e_lo,
                                 int e_hi, int add_shared, float* logits, int* topi, float* topw, fnx_job* jobs, int* njobs,
-                                unsigned* err, fnx_stream st) {
+                                unsigned long long* stats, unsigned* err, fnx_stream st) {
     FNX_REQUIRE(Wr && x && logits && topi && topw && jobs && njobs && err, "fnx_router_route: null pointer");
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_router_route: %d rows (1..%d)", T, FNX_MAX_ROWS);
     FNX_REQUIRE(E >= K && E <= RT_MAXE && K >= 1 && K <= 32, "fnx_router_route: %d experts, top %d not supported", E, K);
@@ -186,8 +248,11 @@ extern "C" int fnx_router_route(const float* Wr, const float* x, const float* no
         configured = true;
     }
     const int blocks = (E + 1 + RT_WARPS - 1) / RT_WARPS;
-    k_router<<<blocks, RT_WARPS * 32, smem, as_stream(st)>>>(Wr, x, norm_w, eps, T, E, H, K, e_lo, e_hi, add_shared, logits, topi, topw, jobs,
-                                                            njobs, err);
+    {
+        const cudaError_t le_ = launch_k(k_router, dim3(blocks), dim3(RT_WARPS * 32), smem, as_stream(st), Wr, x, norm_w, eps, T, E, H, K, e_lo, e_hi, add_shared, logits, topi, topw, jobs,
+                                                            njobs, stats, err);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_router: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_router_route");
     return FNX_OK;
 }
@@ -196,7 +261,10 @@ extern "C" int fnx_moe_combine(const float* part, const int* topi, const float* 
                                int e_lo, int e_hi, int add_shared, float* out, int accumulate, fnx_stream st) {
     FNX_REQUIRE(part && topi && topw && logits && out, "fnx_moe_combine: null pointer");
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_moe_combine: %d rows", T);
-    k_combine<<<dim3((H + 255) / 256, T), 256, 0, as_stream(st)>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
+    {
+        const cudaError_t le_ = launch_k(k_combine, dim3(dim3((H + 255) / 256, T)), dim3(256), 0, as_stream(st), part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_combine: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_moe_combine");
     return FNX_OK;
 }

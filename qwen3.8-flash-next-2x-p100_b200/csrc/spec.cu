@@ -13,6 +13,8 @@ constexpr int LOOKUP_N = 3, LOOKUP_MIN = 3;   // engine/src/session.cpp:17-18
 
 __global__ void __launch_bounds__(1024) k_lookup(const int* __restrict__ ctx, const int* __restrict__ np, int lk, const int* __restrict__ d1p,
                                                  int* __restrict__ out, int* __restrict__ out_n) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ int red[32];
     const int n = *np, tid = threadIdx.x;
     if (lk == 0 || n <= LOOKUP_N) {
@@ -46,6 +48,8 @@ __global__ void __launch_bounds__(1024) k_lookup(const int* __restrict__ ctx, co
 // result: [0] = n, [1 .. 1 + n) path, [1 + FNX_MAX_ROWS ..) emitted tokens
 __global__ void k_accept_greedy(const int* __restrict__ tok, const int* __restrict__ parent, const int* __restrict__ best, int T,
                                 int* __restrict__ result) {
+    pdl_wait();
+    pdl_launch_dependents();
     if (threadIdx.x != 0) return;
     int cur = 0, n = 0;
     for (;;) {
@@ -79,6 +83,8 @@ __global__ void __launch_bounds__(1024) k_accept_sample(const float* __restrict_
                                                         const int* __restrict__ tok, int T, fnx_sampling sp, const int* __restrict__ q_ids,
                                                         const double* __restrict__ q_p, const int* __restrict__ q_n, uint64_t seed,
                                                         uint32_t seq, const uint32_t* __restrict__ stepp, int* __restrict__ result) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t smem[];
     DistS* dist = reinterpret_cast<DistS*>(smem);                                  // [T]
     double* ex = reinterpret_cast<double*>(smem + sizeof(DistS) * (size_t) T);     // [T][64] scratch
@@ -177,14 +183,20 @@ using namespace fnxb;
 
 extern "C" int fnx_lookup_draft(const int* ctx, const int* n, int lk, const int* d1, int* out, int* out_n, fnx_stream st) {
     FNX_REQUIRE(ctx && n && out && out_n && lk >= 0 && lk <= FNX_MAX_ROWS, "fnx_lookup_draft: bad arguments");
-    k_lookup<<<1, 1024, 0, as_stream(st)>>>(ctx, n, lk, d1, out, out_n);
+    {
+        const cudaError_t le_ = launch_k(k_lookup, dim3(1), dim3(1024), 0, as_stream(st), ctx, n, lk, d1, out, out_n);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_lookup: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_lookup_draft");
     return FNX_OK;
 }
 
 extern "C" int fnx_accept_greedy(const int* tok, const int* parent, const int* best, int T, int* result, fnx_stream st) {
     FNX_REQUIRE(tok && best && result && T >= 1 && T <= FNX_MAX_ROWS, "fnx_accept_greedy: bad arguments");
-    k_accept_greedy<<<1, 32, 0, as_stream(st)>>>(tok, parent, best, T, result);
+    {
+        const cudaError_t le_ = launch_k(k_accept_greedy, dim3(1), dim3(32), 0, as_stream(st), tok, parent, best, T, result);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_accept_greedy: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_accept_greedy");
     return FNX_OK;
 }
@@ -200,7 +212,10 @@ extern "C" int fnx_accept_sample(const float* cand_v, const int* cand_i, const i
         FNX_CUDA_OK(cudaFuncSetAttribute(k_accept_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
         configured = true;
     }
-    k_accept_sample<<<1, 1024, smem, as_stream(st)>>>(cand_v, cand_i, tok, T, s, q_ids, q_p, q_n, seed, seq, step, result);
+    {
+        const cudaError_t le_ = launch_k(k_accept_sample, dim3(1), dim3(1024), smem, as_stream(st), cand_v, cand_i, tok, T, s, q_ids, q_p, q_n, seed, seq, step, result);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_accept_sample: launch failed: %s", cudaGetErrorString(le_));
+    }
     FNX_LAUNCH_OK("fnx_accept_sample");
     return FNX_OK;
 }

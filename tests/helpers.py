@@ -26,7 +26,7 @@ class OracleModel:
     Mirrors the engine's data flow (engine.cu: enqueue_verify / enqueue_mtp): pre-norm residual blocks, the input
     projection rows laid out [q|gate per head; k; v] or [q|k|v|z|alpha|beta], ring slots for the DeltaNet state."""
 
-    def __init__(self, F, O, eng, cfg):
+    def __init__(self, F, O, eng, cfg, layers=None, with_mtp=True):
         import torch
         self.O, self.cfg = O, cfg
         c = cfg
@@ -73,8 +73,9 @@ class OracleModel:
             L["wsh_dn"] = iq(pre + "shared_dn", self.H, self.Fn)
             return L
 
-        self.layers = [layer(f"l{l}.", (l + 1) % c.attn_every == 0) for l in range(c.n_layer)]
-        self.mtp = layer("mtp.", True)
+        ids = range(c.n_layer) if layers is None else layers
+        self.layers = [layer(f"l{l}.", (l + 1) % c.attn_every == 0) for l in ids]
+        self.mtp = layer("mtp.", True) if with_mtp else None
         self.mtp_hnorm, self.mtp_enorm, self.mtp_onorm = f32("mtp.h_norm"), f32("mtp.e_norm"), f32("mtp.out_norm")
         self.out_norm = f32("out_norm")
         self.fc_hid, self.fc_emb = iq("mtp.fc_hid", self.H, self.H), iq("mtp.fc_emb", self.H, self.H)
@@ -130,6 +131,7 @@ class OracleModel:
         return O.accept_greedy(tokens, parent, self.best)
 
     def commit(self, path):
+        path = [int(v) for v in path]
         n = len(path)
         for L in self.layers:
             if L["attn"]:
@@ -139,7 +141,7 @@ class OracleModel:
                         L["vc"][self.pos + j] = L["vc"][self.pos + s]
         self.kept_rows = self.R[np.asarray(path)].copy()
         self.kept_pos0 = self.pos
-        self.cur = (self.cur + 1 + path[-1]) % self.NS
+        self.cur = int((self.cur + 1 + int(path[-1])) % self.NS)
         self.pos += n
 
     def _mtp_call(self, src, toks, pos0):
