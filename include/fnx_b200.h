@@ -60,6 +60,12 @@ int fnx_fill_normal(float* out, size_t n, float sigma, uint64_t seed, uint32_t s
 int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps,
               float* y, int ldy, int accumulate, unsigned* err, fnx_stream st);
 
+/* Tracing (FNX_PROF / k_prof_stamp, engine/src/engine.cu:1382-1529): while a device buffer of
+ * [blocks][64] u64 is registered, block b of every IQ3_S matvec launch writes %globaltimer stamps of its phases
+ * (start, set-up done, activations ready, then per step: weights landed, computed) to row b, count in word 0.
+ * Null unregisters.  Synchronises. */
+int fnx_debug_profile_buffer(void* dev_u64);
+
 /* ---------------------------------------------------------------------------------------------- MoE
  * One expert job: expert `w` applied to n activation rows (Job, engine/src/kernels.hpp:18-23, with MAXT = 4 rows;
  * an expert picked by more rows gets several jobs). */
@@ -182,6 +188,11 @@ int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n);
 int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts);
 /* the device time of the last verify / draft graph launch in milliseconds (CUDA events on the engine's stream) */
 float fnx_engine_last_ms(const fnx_engine* e);
+/* Windows of up to 8 rows on a single rank can run as ONE persistent cooperative kernel (csrc/step.cu) instead of
+ * the launch-per-operator graph: on = 1 (or FNX_STEP=1 in the environment) selects it; larger windows and
+ * expert-parallel ranks always take the launch-per-operator path.  Off by default until it is the faster of the
+ * two.  Drops the captured graphs. */
+int fnx_engine_use_step_kernel(fnx_engine* e, int on);
 /* counters since creation: [0] kernels launched through graphs, [1] routed expert jobs, [2] router calls */
 int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3);
 int fnx_engine_pos(const fnx_engine* e, int seq);

@@ -59,6 +59,7 @@ _PROTOS = {
     "fnx_iq3s_dequant_tiles": (_I, [_P, _P, _Z, _Z, _P]),
     "fnx_iq3s_quantize": (_I, [_P, _P, _Z, _P]),
     "fnx_fill_normal": (_I, [_P, _Z, _F, _U64, _U32, _P]),
+    "fnx_debug_profile_buffer": (_I, [_P]),
     "fnx_dense": (_I, [_P, _I, _I, _P, _I, _I, _P, _F, _P, _I, _I, _P, _P]),
     "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
@@ -86,6 +87,7 @@ _PROTOS = {
     "fnx_engine_draft": (_I, [_P, _I, _I, _P]),
     "fnx_engine_last_ms": (_F, [_P]),
     "fnx_engine_counters": (_I, [_P, _P]),
+    "fnx_engine_use_step_kernel": (_I, [_P, _I]),
     "fnx_engine_pos": (_I, [_P, _I]),
     "fnx_engine_stream": (_P, [_P]),
     "fnx_comm_unique_id": (_I, [_P]),
@@ -349,7 +351,7 @@ class Engine:
         class _Holder:
             pass
         h = _Holder()
-        h.__cuda_array_interface__ = {"shape": (n,), "typestr": {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1",
+        h.__cuda_array_interface__ = {"shape": (n,), "typestr": {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1", torch.int64: "<i8",
                                                                  torch.float16: "<f2"}[dtype], "data": (p, False), "version": 2}
         t = torch.as_tensor(h, device="cuda")
         return t if shape is None else t.view(shape)
@@ -376,6 +378,9 @@ class Engine:
         out = (C.c_int * k)()
         check(lib().fnx_engine_draft(self._h, seq, k, out))
         return list(out)
+
+    def use_step_kernel(self, on: bool):
+        check(lib().fnx_engine_use_step_kernel(self._h, 1 if on else 0))
 
     def counters(self):
         """(kernels launched through graphs, routed expert jobs, router calls) since creation."""

@@ -16,6 +16,7 @@
 
 #include "fnx_common.cuh"
 #include "iq3s_tile.h"
+#include "step.cuh"
 
 namespace fnxb {
 
@@ -105,6 +106,14 @@ struct fnx_engine {
     void* comm = nullptr;
     int proj_ld = 0;
     unsigned long long* d_stats = nullptr;
+    // the persistent step kernel (windows of up to 8 rows on a single rank)
+    bool use_step = false;
+    std::map<uint64_t, StepParams*> step_params;     // per graph key: device parameter block
+    std::map<int, StepLayer*> step_layers;          // per sequence: device layer table
+    unsigned* d_sync = nullptr;
+    uint8_t* d_ximg = nullptr;
+    float *d_xnorm = nullptr, *d_gdn_o = nullptr, *d_gdn_sq = nullptr;
+    unsigned long long* d_prof = nullptr;
     unsigned long long launches = 0;
     std::map<uint64_t, unsigned> graph_kernels;
 };
@@ -377,6 +386,60 @@ static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
     return fnx_argmax(e->logits, 1, d.V, e->d_draft, nullptr, e->err, e->st);
 }
 
+// the persistent step kernel's parameter block for (sequence, rows, tree): built once, outside any capture
+static bool step_ok(const fnx_engine* e, int T) {
+    const Dims d = dims(e->c);
+    return e->use_step && e->c.ep_size == 1 && T <= 8 && d.hd == 256 && d.hs == 128 && d.nq / d.nkv <= 8 && d.E <= 1024 && d.K <= 32 &&
+           (size_t) T * d.H * sizeof(float) <= 65536 && d.nq * d.hd <= 4096 && d.nv * d.hs <= 4096 && d.H <= 4096;
+}
+static int step_prepare(fnx_engine* e, uint64_t key, int seq, int T, bool tree) {
+    if (e->step_params.count(key)) return FNX_OK;
+    const Dims d = dims(e->c);
+    if (!e->step_layers.count(seq)) {
+        std::vector<StepLayer> hl(e->layers.size());
+        for (size_t l = 0; l < e->layers.size(); ++l) {
+            const LayerW& L = e->layers[l];
+            StepLayer& s = hl[l];
+            s.attn = L.attn;
+            s.in_rows = L.in_rows;
+            s.norm1 = L.norm1; s.norm2 = L.norm2; s.w_in = L.w_in; s.w_out = L.w_out;
+            s.qn = L.qn; s.kn = L.kn;
+            s.kc = L.kc ? L.kc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
+            s.vc = L.vc ? L.vc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
+            s.convw = L.convw; s.dt = L.dt; s.a = L.a; s.gnorm = L.gnorm;
+            s.S = L.S_pool ? L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs : nullptr;
+            s.hist = L.hist_pool ? L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch : nullptr;
+            s.wr = L.wr; s.wgu = L.wgu; s.wdn = L.wdn; s.wsh_gu = L.wsh_gu; s.wsh_dn = L.wsh_dn;
+        }
+        StepLayer* dl = nullptr;
+        FNX_TRY(dalloc(e, &dl, hl.size()));
+        FNX_CUDA_OK(cudaMemcpy(dl, hl.data(), sizeof(StepLayer) * hl.size(), cudaMemcpyHostToDevice));
+        e->step_layers[seq] = dl;
+    }
+    StepParams p{};
+    p.layers = e->step_layers[seq];
+    p.n_layer = (int) e->layers.size();
+    p.H = d.H; p.E = d.E; p.K = d.K; p.F = d.F; p.nq = d.nq; p.nkv = d.nkv; p.hd = d.hd; p.nrot = d.nrot; p.nk = d.nk; p.nv = d.nv; p.hs = d.hs; p.V = d.V;
+    p.T = T; p.NS = e->NS; p.proj_ld = e->proj_ld; p.tree = tree ? 1 : 0;
+    p.eps = e->c.eps; p.rope_base = e->c.rope_base;
+    p.gu_bytes = e->gu_bytes; p.dn_bytes = e->dn_bytes;
+    p.tok = e->d_tok; p.parent = e->d_parent; p.pos0 = e->d_pos + seq; p.cur = e->d_cur + seq; p.depth = e->d_depth;
+    p.embed = e->embed; p.head = e->head; p.out_norm = e->out_norm;
+    p.R = e->R; p.proj = e->proj; p.mix = e->mix; p.logits = e->logits; p.rlogits = e->rlogits; p.topw = e->topw; p.hbuf = e->hbuf; p.part = e->part;
+    p.topi = e->topi; p.jobs = e->jobs; p.njobs = e->njobs;
+    const int S = sm_count() / d.nkv > 0 ? sm_count() / d.nkv : 1;
+    p.att_acc = (float*) e->att_scratch;
+    p.att_mz = (AttPartialS*) (p.att_acc + (size_t) T * d.nq * S * d.hd);
+    p.gdn_o = e->d_gdn_o; p.gdn_sq = e->d_gdn_sq; p.ximg = e->d_ximg; p.xnorm = e->d_xnorm;
+    p.best_i = e->best_i; p.best_v = e->best_v; p.result = e->result;
+    p.sync = e->d_sync; p.stats = e->d_stats; p.err = e->err; p.prof = e->d_prof;
+    StepParams* dp = nullptr;
+    FNX_TRY(dalloc(e, (uint8_t**) &dp, sizeof(StepParams)));
+    FNX_CUDA_OK(cudaMemcpy(dp, &p, sizeof p, cudaMemcpyHostToDevice));
+    e->step_params[key] = dp;
+    return FNX_OK;
+}
+
 template <typename F>
 static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
     auto it = e->graphs.find(key);
@@ -489,6 +552,16 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_ctx_n, c.n_seq, "seq.ctx_n"));
         FNX_TRY(dalloc(e, &e->err, 1, "buf.err"));
         FNX_TRY(dalloc(e, &e->d_stats, 2, "buf.stats"));
+        FNX_TRY(dalloc(e, &e->d_sync, STEP_SYNC_WORDS, "buf.sync"));
+        FNX_TRY(dalloc(e, &e->d_ximg, 65536 + 1024, "buf.ximg"));
+        FNX_TRY(dalloc(e, &e->d_xnorm, (size_t) d.MAXR * d.H, "buf.xnorm"));
+        FNX_TRY(dalloc(e, &e->d_gdn_o, (size_t) d.MAXR * d.nv * d.hs, "buf.gdn_o"));
+        FNX_TRY(dalloc(e, &e->d_gdn_sq, (size_t) d.MAXR * d.nv * 4, "buf.gdn_sq"));
+        FNX_TRY(dalloc(e, &e->d_prof, 4096, "buf.prof"));
+        {
+            const char* v = getenv("FNX_STEP");
+            if (v && v[0] == '1') e->use_step = true;
+        }
         void* sc = nullptr;
         const size_t sb = fnx_attn_scratch_bytes(d.MAXR, d.nq, d.hd);
         FNX_TRY(dalloc(e, (uint8_t**) &sc, sb, "buf.attn_scratch"));
@@ -604,7 +677,13 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
     }
     const bool tree = h_parent != nullptr;
     const uint64_t key = ((uint64_t) 1 << 60) | ((uint64_t) seq << 20) | ((uint64_t) T << 1) | (tree ? 1 : 0);
-    FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
+    if (step_ok(e, T)) {
+        FNX_TRY(step_prepare(e, key, seq, T, tree));
+        StepParams* dp = e->step_params[key];
+        FNX_TRY(run_graph(e, key, [&]() { return step_launch(dp, T, e->d_sync, e->st); }));
+    } else {
+        FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
+    }
     s.last_T = T;
     if (h_result) {
         FNX_CUDA_OK(cudaMemcpyAsync(hs + 2 * FNX_MAX_ROWS, e->result, sizeof(int) * (1 + 2 * FNX_MAX_ROWS), cudaMemcpyDeviceToHost, e->st));
@@ -703,6 +782,18 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
 }
 
 extern "C" float fnx_engine_last_ms(const fnx_engine* e) { return e ? e->last_ms : 0.f; }
+extern "C" int fnx_engine_use_step_kernel(fnx_engine* e, int on) {
+    FNX_REQUIRE(e, "fnx_engine_use_step_kernel: null engine");
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    if ((on != 0) != e->use_step) {
+        for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+        e->graphs.clear();
+        e->graph_kernels.clear();
+        e->use_step = on != 0;
+    }
+    return FNX_OK;
+}
+
 extern "C" int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3) {
     FNX_REQUIRE(e && h_out3, "fnx_engine_counters: null pointer");
     unsigned long long st[2] = {0, 0};

@@ -26,6 +26,20 @@ namespace fnxb {
 
 __device__ const uint32_t g_iq3s_grid[512] = {FNX_IQ3S_GRID_VALUES};
 
+// Phase stamps (the reference's FNX_PROF idea, engine/src/engine.cu:1382-1529): when a buffer is registered, thread 0 of
+// every block writes %globaltimer at its phase boundaries: [block][MMV_PROF_SLOTS] u64, slot 0 = how many were written.
+constexpr int MMV_PROF_SLOTS = 64;
+__device__ unsigned long long* g_mmv_prof = nullptr;
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define MMV_STAMP()                                                                         \
+    do {                                                                                    \
+        if (prof && tid == 0 && nstamp < MMV_PROF_SLOTS - 1) prof[1 + nstamp++] = gtime(); \
+    } while (0)
+
 enum { MMV_DENSE = 0, MMV_GATEUP = 1, MMV_DOWN = 2 };
 constexpr int MMV_THREADS = 512, MMV_WARPS = 16, MMV_ITEMS = 16;
 constexpr int MMV_STEP_BYTES = MMV_ITEMS * TILE_BYTES;   // 28,160
@@ -260,6 +274,9 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
         sm.rs = reinterpret_cast<float*>(b); b += 32 * sizeof(float);
         sm.bars = reinterpret_cast<uint64_t*>(b);
     }
+    unsigned long long* prof = g_mmv_prof ? g_mmv_prof + (size_t) blockIdx.x * MMV_PROF_SLOTS : nullptr;
+    int nstamp = 0;
+    MMV_STAMP();
     pdl_launch_dependents();
     if (tid == 0) {
         for (int i = 0; i < NST; ++i) mbar_init(&sm.bars[i], 1);
@@ -306,6 +323,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     }
     pdl_wait();   // from here on: what earlier kernels of the stream wrote (activations, job lists)
     __syncthreads();
+    MMV_STAMP();
     if (!(MODE == MMV_DENSE && !p.jobs)) {
         njobs = p.jobs ? min(*p.njobs, p.njobs_max) : 1;
         plan();
@@ -336,11 +354,13 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
                 for (int i = 0; i < 4 * NG; ++i) xrow[i] = orow[i] = i;
             }
             mmv_load_x<NG, MODE>(p, sm, xrow, ntok, tid);
+            MMV_STAMP();
         }
         if (!mbar_wait_bounded(&sm.bars[st], ((s - s0) / NST) & 1)) {
             ok = false;
             break;
         }
+        MMV_STAMP();
         const uint8_t* stage = sm.stage + (size_t) st * MMV_STEP_BYTES;
         float* part = sm.part + (size_t) buf * MMV_ITEMS * 16 * 4 * NG;
         {
@@ -365,6 +385,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
             }
         }
         __syncthreads();
+        MMV_STAMP();
         if (tid == 0 && s + NST < s1) {
             fence_proxy_async();
             issue(s + NST);
@@ -391,6 +412,8 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
             }
         }
     }
+    MMV_STAMP();
+    if (prof && tid == 0) prof[0] = (unsigned long long) nstamp;
     if (!ok) {
         if (tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
         // give this CTA's copies still in flight a bounded chance to land before its shared memory is released
@@ -431,6 +454,12 @@ static int check_cols(int cols) {
 }  // namespace fnxb
 
 using namespace fnxb;
+
+extern "C" int fnx_debug_profile_buffer(void* dev_u64) {
+    unsigned long long* p = (unsigned long long*) dev_u64;
+    FNX_CUDA_OK(cudaMemcpyToSymbol(g_mmv_prof, &p, sizeof p));
+    return FNX_OK;
+}
 
 extern "C" int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps, float* y,
                          int ldy, int accumulate, unsigned* err, fnx_stream st) {

@@ -146,6 +146,32 @@ def test_tree_verify_equals_chain_verify_of_the_accepted_path(F, model):
     assert em[0] == want[4]
 
 
+def test_step_kernel_equals_operator_path(F, model):
+    """The persistent one-kernel window and the launch-per-operator graph give the same window: same routing, same
+    accepted tokens, hidden states and logits equal to rounding (both sum the K blocks in the same order)."""
+    cfg, eng, _ = model
+    rng = np.random.default_rng(11)
+    prompt = rng.integers(0, cfg.vocab, size=21).tolist()
+    outs = []
+    for on in (False, True):
+        eng.use_step_kernel(on)
+        eng.reset()
+        eng.prefill(prompt)
+        res = []
+        for toks, par in (([5, 6, 7, 8, 9], None), ([1, 2, 3, 4, 5, 6, 7], [-1, 0, 1, 0, 3, 3, 1]), ([11], None)):
+            r = eng.verify(toks, par)
+            R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:len(toks)].copy()
+            lg = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:len(toks)].copy()
+            ti = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:len(toks)].copy()
+            res.append((r, R, lg, ti))
+            eng.commit(r[1])
+        outs.append(res)
+    eng.use_step_kernel(False)
+    for (ra, Ra, la, ta), (rb, Rb, lb, tb) in zip(*outs):
+        assert ra == rb and np.array_equal(ta, tb)
+        assert rel_err(Rb, Ra) < 1e-4 and rel_err(lb, la) < 1e-4
+
+
 def test_engine_rejects_bad_calls(F, model):
     cfg, eng, _ = model
     eng.reset()
