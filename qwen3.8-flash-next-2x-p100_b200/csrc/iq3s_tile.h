@@ -121,22 +121,37 @@ FNX_HD void tile_get_block(const uint8_t* tile, int r, uint8_t* blk) {
 
 // byte offset of index i's codebook entry in the replicated table: (idx << 7), i.e. the 9-bit field moved to bits
 // 7..15.  S[0..3] = the 16-byte stream, S[4] = its 16-bit tail.
+// On the device the shifts are written as multiplies (x >> s == umulhi(x, 2^(32-s)), x << s == x * 2^s) by powers of
+// two read from constant memory, so that they stay multiplies: integer multiply-add runs on the FMA pipes, which
+// leaves the narrower integer-logic pipe to the masks and byte permutes (the decode is bound by that pipe).
+#if defined(__CUDACC__)
+__constant__ static uint32_t g_pow2[33] = {1u << 0,  1u << 1,  1u << 2,  1u << 3,  1u << 4,  1u << 5,  1u << 6,  1u << 7,  1u << 8,  1u << 9,  1u << 10,
+                                           1u << 11, 1u << 12, 1u << 13, 1u << 14, 1u << 15, 1u << 16, 1u << 17, 1u << 18, 1u << 19, 1u << 20, 1u << 21,
+                                           1u << 22, 1u << 23, 1u << 24, 1u << 25, 1u << 26, 1u << 27, 1u << 28, 1u << 29, 1u << 30, 1u << 31, 0u};
+#endif
 template <int I>
 FNX_HD uint32_t tile_field(const uint32_t (&S)[5]) {
     constexpr int o = 9 * I, j = o >> 5, r = o & 31;
     uint32_t v;
     if constexpr (r >= 7 && r + 9 <= 32) {
-        v = S[j] >> (r - 7);
-    } else if constexpr (r >= 7) {
-        {
 #if defined(__CUDA_ARCH__)
-            v = __funnelshift_r(S[j], S[j + 1], r - 7);
+        if constexpr (r == 7) v = S[j];
+        else v = __umulhi(S[j], g_pow2[32 - (r - 7)]);
 #else
-            v = (uint32_t) ((((uint64_t) S[j + 1] << 32) | S[j]) >> (r - 7));
+        v = S[j] >> (r - 7);
 #endif
-        }
+    } else if constexpr (r >= 7) {
+#if defined(__CUDA_ARCH__)
+        v = __funnelshift_r(S[j], S[j + 1], r - 7);
+#else
+        v = (uint32_t) ((((uint64_t) S[j + 1] << 32) | S[j]) >> (r - 7));
+#endif
     } else {
+#if defined(__CUDA_ARCH__)
+        v = S[j] * g_pow2[7 - r];
+#else
         v = S[j] << (7 - r);
+#endif
     }
     return v & 0xFF80u;
 }
@@ -144,12 +159,13 @@ FNX_HD uint32_t tile_field(const uint32_t (&S)[5]) {
 // byte mask (0xFF where the weight is negative) of index i's four weights from the lane's sign words
 template <int I>
 FNX_HD uint32_t tile_sign_mask(const uint32_t (&G)[2]) {
-    const uint32_t p = G[I >> 3] << (7 - (I & 7));
 #if defined(__CUDA_ARCH__)
-    uint32_t m;
+    uint32_t p = G[I >> 3], m;
+    if constexpr ((I & 7) != 7) p = G[I >> 3] * g_pow2[7 - (I & 7)];
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(p), "r"(0u), "r"(0xBA98u));
     return m;
 #else
+    const uint32_t p = G[I >> 3] << (7 - (I & 7));
     uint32_t m = 0;
     for (int b = 0; b < 4; ++b)
         if ((p >> (8 * b + 7)) & 1u) m |= 0xFFu << (8 * b);

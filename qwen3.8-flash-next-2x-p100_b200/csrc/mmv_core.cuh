@@ -38,7 +38,7 @@ __device__ __forceinline__ void core_fill_table(uint8_t* table, int tid, int nth
 }
 
 __device__ __forceinline__ void core_mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
@@ -52,10 +52,38 @@ __device__ __forceinline__ uint32_t core_pack_s8x4(int a, int b, int c, int d) {
     return r;
 }
 
+// shared-memory loads by 32-bit shared address: no 64-bit generic pointer arithmetic in the decode loop
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint16_t v;
+    asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+
 template <int I>
-__device__ __forceinline__ uint32_t core_decode(const uint32_t (&S)[5], const uint32_t (&G)[2], const uint8_t* table, uint32_t lane4) {
+__device__ __forceinline__ uint32_t core_decode(const uint32_t (&S)[5], const uint32_t (&G)[2], uint32_t table_s, uint32_t lane4) {
+    // (field & 0xFF80) | 4 lane: one logic op; the table's (uniform) shared address rides in the load's address
     const uint32_t off = tile_field<I>(S) | lane4;
-    const uint32_t mag = *reinterpret_cast<const uint32_t*>(table + off);
+    const uint32_t mag = lds_u32(table_s + off);
     return tile_apply_sign(mag, tile_sign_mask<I>(G));
 }
 
@@ -63,9 +91,9 @@ __device__ __forceinline__ uint32_t core_decode(const uint32_t (&S)[5], const ui
 // two C columns (2 q, 2 q + 1); null = an empty column.
 template <int NG>
 struct LaneX {
-    const uint2* b[NG];
-    const float* s0[NG];
-    const float* s1[NG];
+    uint32_t b[NG];     // shared addresses; 0 = an empty column
+    uint32_t s0[NG];
+    uint32_t s1[NG];
 };
 
 // lane pointers for a dense product over rows [0, T): group ng holds rows 4 ng .. 4 ng + 3
@@ -75,10 +103,10 @@ __device__ __forceinline__ LaneX<NG> lane_x_dense(const uint2* xq, const float* 
     const int g = lane >> 2, q = lane & 3, KB = K / 256;
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-        lx.b[ng] = 4 * ng + (g & 3) < T ? xq + (size_t) ng * (K / 32) * 32 + lane : nullptr;
+        lx.b[ng] = 4 * ng + (g & 3) < T ? smem_u32(xq + (size_t) ng * (K / 32) * 32 + lane) : 0u;
         const int c0 = 2 * q, c1 = 2 * q + 1;
-        lx.s0[ng] = 4 * ng + (c0 & 3) < T ? xs + (size_t) ng * KB * 8 + c0 : nullptr;
-        lx.s1[ng] = 4 * ng + (c1 & 3) < T ? xs + (size_t) ng * KB * 8 + c1 : nullptr;
+        lx.s0[ng] = 4 * ng + (c0 & 3) < T ? smem_u32(xs + (size_t) ng * KB * 8 + c0) : 0u;
+        lx.s1[ng] = 4 * ng + (c1 & 3) < T ? smem_u32(xs + (size_t) ng * KB * 8 + c1) : 0u;
     }
     return lx;
 }
@@ -87,38 +115,43 @@ __device__ __forceinline__ LaneX<NG> lane_x_dense(const uint2* xq, const float* 
 __device__ __forceinline__ LaneX<1> lane_x_job(const uint2* xq, const float* xs, int K, const int* y, int ntok, int lane) {
     LaneX<1> lx;
     const int g = lane >> 2, q = lane & 3, KB = K / 256;
-    lx.b[0] = nullptr;
+    lx.b[0] = 0u;
     if ((g & 3) < ntok) {
         const int row = y[g & 3];
-        lx.b[0] = xq + ((size_t) (row >> 2) * (K / 32) * 8 + (row & 3) + 4 * (g >> 2)) * 4 + q;
+        lx.b[0] = smem_u32(xq + ((size_t) (row >> 2) * (K / 32) * 8 + (row & 3) + 4 * (g >> 2)) * 4 + q);
     }
     const int c0 = 2 * q, c1 = 2 * q + 1;
-    lx.s0[0] = lx.s1[0] = nullptr;
+    lx.s0[0] = lx.s1[0] = 0u;
     if ((c0 & 3) < ntok) {
         const int row = y[c0 & 3];
-        lx.s0[0] = xs + (size_t) (row >> 2) * KB * 8 + (row & 3) + 4 * (c0 >> 2);
+        lx.s0[0] = smem_u32(xs + (size_t) (row >> 2) * KB * 8 + (row & 3) + 4 * (c0 >> 2));
     }
     if ((c1 & 3) < ntok) {
         const int row = y[c1 & 3];
-        lx.s1[0] = xs + (size_t) (row >> 2) * KB * 8 + (row & 3) + 4 * (c1 >> 2);
+        lx.s1[0] = smem_u32(xs + (size_t) (row >> 2) * KB * 8 + (row & 3) + 4 * (c1 >> 2));
     }
     return lx;
 }
 
 template <int NG, int SB>
 __device__ __forceinline__ void core_sub_block(const uint32_t (&S0)[5], const uint32_t (&G0)[2], const uint32_t (&S1)[5], const uint32_t (&G1)[2],
-                                               uint32_t sc0, uint32_t sc1, const uint8_t* table, uint32_t lane4, const LaneX<NG>& lx, int blk,
+                                               uint2 sc0, uint2 sc1, uint32_t table_s, uint32_t lane4, const uint32_t (&bx)[NG],
                                                int (&accI)[NG][4]) {
-    const uint32_t a0 = core_decode<2 * SB>(S0, G0, table, lane4);
-    const uint32_t a2 = core_decode<2 * SB + 1>(S0, G0, table, lane4);
-    const uint32_t a1 = core_decode<2 * SB>(S1, G1, table, lane4);
-    const uint32_t a3 = core_decode<2 * SB + 1>(S1, G1, table, lane4);
-    // 1 + 2 s from the nibble: ((word >> (4 SB - 1)) & 30) | 1
-    const int w0 = (int) ((SB ? (sc0 >> (4 * SB - 1)) : (sc0 << 1)) & 30u) | 1, w1 = (int) ((SB ? (sc1 >> (4 * SB - 1)) : (sc1 << 1)) & 30u) | 1;
+    const uint32_t a0 = core_decode<2 * SB>(S0, G0, table_s, lane4);
+    const uint32_t a2 = core_decode<2 * SB + 1>(S0, G0, table_s, lane4);
+    const uint32_t a1 = core_decode<2 * SB>(S1, G1, table_s, lane4);
+    const uint32_t a3 = core_decode<2 * SB + 1>(S1, G1, table_s, lane4);
+    // sc0 / sc1: the rows' eight scales 1 + 2 s as bytes (even sub-blocks in .x, odd in .y): one byte extract each
+    int w0, w1;
+    {
+        const uint32_t a = SB & 1 ? sc0.y : sc0.x, b = SB & 1 ? sc1.y : sc1.x;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(w0) : "r"(a), "r"(0u), "r"(0x4440u + (SB >> 1)));
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(w1) : "r"(b), "r"(0u), "r"(0x4440u + (SB >> 1)));
+    }
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
         uint2 b = make_uint2(0u, 0u);
-        if (lx.b[ng]) b = lx.b[ng][(size_t) (blk * 8 + SB) * 32];
+        if (bx[ng]) b = lds_v2(bx[ng] + SB * 256);   // bx: this lane's cells of the block's first sub-block
         int c[4];
         core_mma_s8(c, a0, a1, a2, a3, b.x, b.y);
         accI[ng][0] += w0 * c[0];
@@ -131,37 +164,43 @@ __device__ __forceinline__ void core_sub_block(const uint32_t (&S0)[5], const ui
 // One item: tile (16 rows x 256 columns, block `blk` of its rows) against the lane's activation cells; adds into
 // acc[ng][0..3] = (row g, col 2q), (row g, col 2q+1), (row g+8, col 2q), (row g+8, col 2q+1).
 template <int NG>
-__device__ __forceinline__ void core_item(const uint8_t* tile, const uint8_t* table, const LaneX<NG>& lx, int blk, int lane, float (&acc)[NG][4]) {
+__device__ __forceinline__ void core_item(uint32_t tile_s, uint32_t table_s, const LaneX<NG>& lx, int blk, int lane, float (&acc)[NG][4]) {
     const int g = lane >> 2;
     const uint32_t lane4 = (uint32_t) lane * 4u;
-    const uint4 i0 = *reinterpret_cast<const uint4*>(tile + TILE_IDX + lane * 16);
-    const uint4 i1 = *reinterpret_cast<const uint4*>(tile + TILE_IDX + 512 + lane * 16);
-    const uint2 s0 = *reinterpret_cast<const uint2*>(tile + TILE_SGN + lane * 8);
-    const uint2 s1 = *reinterpret_cast<const uint2*>(tile + TILE_SGN + 256 + lane * 8);
-    const uint32_t t0 = *reinterpret_cast<const uint16_t*>(tile + TILE_TAIL + lane * 2);
-    const uint32_t t1 = *reinterpret_cast<const uint16_t*>(tile + TILE_TAIL + 64 + lane * 2);
-    const uint32_t sc0 = *reinterpret_cast<const uint32_t*>(tile + TILE_SCL + g * 4);
-    const uint32_t sc1 = *reinterpret_cast<const uint32_t*>(tile + TILE_SCL + (g + 8) * 4);
-    const float d0 = __half2float(*reinterpret_cast<const __half*>(tile + TILE_D + g * 2));
-    const float d1 = __half2float(*reinterpret_cast<const __half*>(tile + TILE_D + (g + 8) * 2));
+    const uint4 i0 = lds_v4(tile_s + TILE_IDX + lane * 16);
+    const uint4 i1 = lds_v4(tile_s + TILE_IDX + 512 + lane * 16);
+    const uint2 s0 = lds_v2(tile_s + TILE_SGN + lane * 8);
+    const uint2 s1 = lds_v2(tile_s + TILE_SGN + 256 + lane * 8);
+    const uint32_t t0 = lds_u16(tile_s + TILE_TAIL + lane * 2);
+    const uint32_t t1 = lds_u16(tile_s + TILE_TAIL + 64 + lane * 2);
+    const uint32_t sn0 = lds_u32(tile_s + TILE_SCL + g * 4);
+    const uint32_t sn1 = lds_u32(tile_s + TILE_SCL + (g + 8) * 4);
+    // nibbles -> bytes 1 + 2 s: even sub-blocks (low nibbles) and odd ones (high nibbles)
+    const uint2 sc0 = make_uint2((sn0 & 0x0F0F0F0Fu) * 2u + 0x01010101u, ((sn0 >> 4) & 0x0F0F0F0Fu) * 2u + 0x01010101u);
+    const uint2 sc1 = make_uint2((sn1 & 0x0F0F0F0Fu) * 2u + 0x01010101u, ((sn1 >> 4) & 0x0F0F0F0Fu) * 2u + 0x01010101u);
+    const float d0 = __half2float(__ushort_as_half((unsigned short) lds_u16(tile_s + TILE_D + g * 2)));
+    const float d1 = __half2float(__ushort_as_half((unsigned short) lds_u16(tile_s + TILE_D + (g + 8) * 2)));
     const uint32_t S0[5] = {i0.x, i0.y, i0.z, i0.w, t0}, S1[5] = {i1.x, i1.y, i1.z, i1.w, t1};
     const uint32_t G0[2] = {s0.x, s0.y}, G1[2] = {s1.x, s1.y};
+    uint32_t bx[NG];
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) bx[ng] = lx.b[ng] ? lx.b[ng] + (uint32_t) blk * 2048u : 0u;
     int accI[NG][4];
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng)
 #pragma unroll
         for (int i = 0; i < 4; ++i) accI[ng][i] = 0;
-    core_sub_block<NG, 0>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 1>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 2>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 3>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 4>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 5>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 6>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
-    core_sub_block<NG, 7>(S0, G0, S1, G1, sc0, sc1, table, lane4, lx, blk, accI);
+    core_sub_block<NG, 0>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 1>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 2>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 3>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 4>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 5>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 6>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 7>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-        const float x0 = lx.s0[ng] ? lx.s0[ng][blk * 8] : 0.f, x1 = lx.s1[ng] ? lx.s1[ng][blk * 8] : 0.f;
+        const float x0 = lx.s0[ng] ? lds_f32(lx.s0[ng] + (uint32_t) blk * 32u) : 0.f, x1 = lx.s1[ng] ? lds_f32(lx.s1[ng] + (uint32_t) blk * 32u) : 0.f;
         acc[ng][0] += d0 * x0 * (float) accI[ng][0];
         acc[ng][1] += d0 * x1 * (float) accI[ng][1];
         acc[ng][2] += d1 * x0 * (float) accI[ng][2];
@@ -181,6 +220,317 @@ __device__ __forceinline__ void core_quant_cell(const float (&x8)[8], float am, 
     }
     c1 = make_uint2(core_pack_s8x4(a8[0], a8[1], a8[2], a8[3]), core_pack_s8x4(a8[4], a8[5], a8[6], a8[7]));
     c2 = make_uint2(core_pack_s8x4(b8[0], b8[1], b8[2], b8[3]), core_pack_s8x4(b8[4], b8[5], b8[6], b8[7]));
+}
+
+}  // namespace fnxb
+
+// ------------------------------------------------------------------------------------------------ rows -> image
+// Block-wide: quantises `nrows` rows (rowptr[r] null = an empty row; nrows a multiple of 4) of K values into an
+// image at (cells, scales).  With norm_w the rows are RMS-normed: the codes are those of x * w and the row's
+// 1 / rms goes into the block scales.  rs: nrows * 5 floats of shared scratch.  Ends with a block barrier.
+namespace fnxb {
+__device__ __forceinline__ void quant_rows(const float* const* rowptr, int nrows, int K, const float* norm_w, float eps, uint2* cells,
+                                           float* scales, float* rs, int tid, int nthreads) {
+    const int warp = tid >> 5, lane = tid & 31, nwarp = nthreads >> 5, KB = K / 256;
+    const int CB = KB < 4 ? KB : 4, nchunk = KB / CB;
+    for (int task = warp; task < nrows * nchunk; task += nwarp) {
+        const int t = task / nchunk, ck = task % nchunk, ng = t >> 2, n = t & 3;
+        const float* xr0 = rowptr[t];
+        float v[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (j < CB) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (xr0) {
+                    const float* xr = xr0 + (ck * CB + j) * 256 + lane * 8;
+                    a = *reinterpret_cast<const float4*>(xr);
+                    b = *reinterpret_cast<const float4*>(xr + 4);
+                }
+                v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+                v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+            }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (j < CB) {
+                const int blk = ck * CB + j, col = blk * 256 + lane * 8;
+                if (norm_w) {
+                    const float4 w0 = *reinterpret_cast<const float4*>(norm_w + col), w1 = *reinterpret_cast<const float4*>(norm_w + col + 4);
+                    const float w8[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        ss = fmaf(v[j][i], v[j][i], ss);
+                        v[j][i] *= w8[i];
+                    }
+                }
+                float am = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[j][i]));
+                am = warp_max(am);
+                uint2 c1, c2;
+                float d;
+                core_quant_cell(v[j], am, c1, c2, d);
+                const int sbG = blk * 8 + (lane >> 2), q = lane & 3;
+                uint2* cell = cells + ((size_t) (ng * (K / 32) + sbG) * 8 + n) * 4 + q;
+                cell[0] = c1;
+                cell[16] = c2;
+                if (lane == 0) {
+                    float* sc = scales + (size_t) (ng * KB + blk) * 8;
+                    sc[n] = d;
+                    sc[n + 4] = d * (1.0f / 256.0f);
+                }
+            }
+        if (norm_w) {
+            ss = warp_sum(ss);
+            if (lane == 0) rs[t * 4 + ck] = ss;
+        }
+    }
+    __syncthreads();
+    if (norm_w) {
+        for (int i = tid; i < nrows * KB; i += nthreads) {
+            const int t = i / KB, blk = i % KB;
+            float ss = 0.f;
+            for (int c = 0; c < nchunk; ++c) ss += rs[t * 4 + c];
+            const float r = rsqrtf(ss / (float) K + eps);
+            float* sc = scales + (size_t) ((t >> 2) * KB + blk) * 8;
+            sc[t & 3] *= r;
+            sc[(t & 3) + 4] *= r;
+        }
+        __syncthreads();
+    }
+}
+}  // namespace fnxb
+
+// ------------------------------------------------------------------------------------------------ streaming by warp
+// The product is a sequence of ITEMS: one 16-row x 256-column tile block against the activation cells.  A unit is a
+// 16-row tile across all of K (gate|up: the gate tile then its up tile): nbu consecutive items whose weights are one
+// contiguous run of tile blocks (two runs for gate|up).  A block's items are dealt to its warps in equal contiguous
+// shares, so every warp has the same amount of decode work whatever the number of units.  Each warp streams its
+// items through its PRIVATE ring of bulk async copies (lane 0 issues, every lane waits on the slot's mbarrier) and
+// accumulates in registers.  A unit that lies wholly inside one warp's share is finished and written by that warp;
+// a unit cut by share boundaries leaves its pieces in shared memory, and after ONE block barrier the warp that
+// holds the unit's first piece adds the others in warp order and writes it.  Nothing else in the loop is
+// block-wide: no per-step barrier, no thread that issues copies for others.
+namespace fnxb {
+
+enum { MAT_DENSE = 0, MAT_GATEUP = 1, MAT_DOWN = 2 };
+
+struct MatDesc {
+    const uint8_t* W;        // the dense matrix, or expert 0 of the experts held at W
+    size_t expert_stride;
+    int e_base;              // first expert held at W
+    const uint8_t* Wsh;      // the shared expert (job.w >= E)
+    int E;
+    const fnx_job* jobs;     // null: one dense job
+    const uint8_t* const* jobw;   // jobs mode: weight base of job (j - jobw0), in shared memory
+    int jobw0;
+    int rows, K;             // output rows per job (gate|up: F)
+    float* out;
+    int ldo, accumulate;
+};
+
+struct WarpRing {
+    uint8_t* slots;          // R x TILE_BYTES
+    uint32_t slots_s;        // their shared address
+    uint64_t* bars;          // R
+    int R;
+    unsigned issued, consumed;
+    long long t_wait, t_comp, t_issue;   // diagnostics: clock cycles spent waiting for weights, computing, issuing
+};
+
+// a piece of a unit left for the end-of-pass combine: slot [warp][0] = a piece that continues a unit begun by an
+// earlier warp, slot [warp][1] = the first piece of a unit that later warps continue
+struct PieceSlot {
+    int unit;                // -1: none, -2: the warp had no items at all
+    int b_lo, b_hi, job;
+    float v[128];            // [kind (gate|up only: 0 gate, 1 up)][group][16 lanes][4]
+};
+constexpr int PIECE_BYTES = sizeof(PieceSlot);
+
+__device__ __forceinline__ int mat_blocks_per_unit(int mode, int K) { return mode == MAT_GATEUP ? 2 * (K / 256) : K / 256; }
+
+// weight base of job j: the dense matrix, or the job's expert (from the per-pass table when there is one)
+__device__ __forceinline__ const uint8_t* mat_job_weights(const MatDesc& m, int j) {
+    if (!m.jobs) return m.W;
+    if (m.jobw) return m.jobw[j - m.jobw0];
+    const int e = m.jobs[j].w;
+    return e >= m.E ? m.Wsh : m.W + (size_t) (e - m.e_base) * m.expert_stride;
+}
+
+// the 16 x rows results of unit (job rows orow, local tile lu) from this lane's sums (threads q < 2 hold them)
+template <int NG, int MODE>
+__device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const int (&orow)[4 * NG], int ntok, int lane, const float (&gacc)[NG][4],
+                                               const float (&acc)[NG][4]) {
+    const int g = lane >> 2, q = lane & 3;
+    if (q >= 2) return;
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int tok = 4 * ng + 2 * q + (k & 1), row = lu * 16 + g + 8 * (k >> 1);
+            if (tok < ntok) {
+                float* dst = m.out + (size_t) orow[tok] * m.ldo + row;
+                const float v = MODE == MAT_GATEUP ? siluf_(gacc[ng][k]) * acc[ng][k] : acc[ng][k];
+                *dst = m.accumulate ? *dst + v : v;
+            }
+        }
+}
+
+// This warp's share of the items of units [ua, ub).  `lane_x(j, lx, ntok, orow)` sets the lane's activation pointers
+// and output rows for job j.  pieces: [nwarp][2] slots.  Returns false when a wait gave up.  The caller runs a block
+// barrier and then mat_combine().
+template <int NG, int MODE, typename LaneXFn>
+__device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint32_t table_s, WarpRing& ring, PieceSlot* pieces, int warp,
+                                          int nwarp, int lane, LaneXFn&& lane_x) {
+    const int KB = m.K / 256, nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
+    const long long N = (long long) (ub - ua) * nbu;
+    const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
+    PieceSlot* mine = pieces + warp * 2;
+    if (lane == 0) {
+        mine[0].unit = i0 < i1 ? -1 : -2;
+        mine[1].unit = -1;
+    }
+    // the issue cursor (lane 0): next item `ahead` = block ab of unit (local tile al of job aj)
+    int ahead = i0, ab = i0 % nbu, al = (ua + i0 / nbu) % upj, aj = (ua + i0 / nbu) / upj;
+    const uint8_t* aw = i0 < i1 ? mat_job_weights(m, aj) : nullptr;
+    auto issue_upto = [&](int limit) {
+        if (lane == 0) {
+            while (ahead < i1 && ahead < limit) {
+                const unsigned st = ring.issued % ring.R;
+                const uint8_t* src = MODE == MAT_GATEUP && ab >= KB ? aw + ((size_t) (upj + al) * KB + (ab - KB)) * TILE_BYTES
+                                                                   : aw + ((size_t) al * KB + ab) * TILE_BYTES;
+                fence_proxy_async();
+                mbar_expect_tx(&ring.bars[st], TILE_BYTES);
+                bulk_g2s(ring.slots + (size_t) st * TILE_BYTES, src, TILE_BYTES, &ring.bars[st]);
+                ++ring.issued;
+                ++ahead;
+                if (++ab == nbu) {
+                    ab = 0;
+                    if (++al == upj) {
+                        al = 0;
+                        ++aj;
+                        if (ahead < i1) aw = mat_job_weights(m, aj);
+                    }
+                }
+            }
+        }
+    };
+    issue_upto(i0 + ring.R);
+    int cur_job = -1, ntok = 0, b_lo = 0;
+    int orow[4 * NG];
+    LaneX<NG> lx;
+    float acc[NG][4], gacc[NG][4];
+    int b = i0 % nbu, lu = (ua + i0 / nbu) % upj, j = (ua + i0 / nbu) / upj;
+    for (int s = i0; s < i1; ++s) {
+        if (b == 0 || s == i0) {
+            b_lo = b;
+#pragma unroll
+            for (int ng = 0; ng < NG; ++ng)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[ng][k] = gacc[ng][k] = 0.f;
+            if (j != cur_job) {
+                cur_job = j;
+                lane_x(j, lx, ntok, orow);
+            }
+        }
+        const unsigned st = ring.consumed % ring.R;
+        const long long c0 = clock64();
+        if (!mbar_wait_bounded(&ring.bars[st], (ring.consumed / ring.R) & 1u, 8000000u)) return false;
+        const long long c1 = clock64();
+        ++ring.consumed;
+        const uint32_t tile_s = ring.slots_s + st * (uint32_t) TILE_BYTES;
+        if (MODE == MAT_GATEUP && b < KB) core_item<NG>(tile_s, table_s, lx, b, lane, gacc);
+        else core_item<NG>(tile_s, table_s, lx, MODE == MAT_GATEUP ? b - KB : b, lane, acc);
+        __syncwarp();
+        const long long c2 = clock64();
+        issue_upto(s + 1 + ring.R);
+        __syncwarp();
+        const long long c3 = clock64();
+        ring.t_wait += c1 - c0;
+        ring.t_comp += c2 - c1;
+        ring.t_issue += c3 - c2;
+        if (b == nbu - 1 || s == i1 - 1) {
+            // level 1 (threads q = 0, 1) + level 2 (q = 2, 3) of the same rows
+#pragma unroll
+            for (int ng = 0; ng < NG; ++ng)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    acc[ng][k] += __shfl_xor_sync(0xffffffffu, acc[ng][k], 2);
+                    if (MODE == MAT_GATEUP) gacc[ng][k] += __shfl_xor_sync(0xffffffffu, gacc[ng][k], 2);
+                }
+            if (b_lo == 0 && b == nbu - 1) {
+                mat_write_unit<NG, MODE>(m, lu, orow, ntok, lane, gacc, acc);
+            } else {
+                PieceSlot* ps = mine + (b_lo == 0 ? 1 : 0);
+                if (lane == 0) {
+                    ps->unit = j * upj + lu;
+                    ps->b_lo = b_lo;
+                    ps->b_hi = b + 1;
+                    ps->job = j;
+                }
+                if ((lane & 3) < 2) {
+                    const int l16 = (lane >> 2) * 2 + (lane & 3);
+#pragma unroll
+                    for (int ng = 0; ng < NG; ++ng)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (MODE == MAT_GATEUP) {
+                                ps->v[(ng * 16 + l16) * 4 + k] = gacc[ng][k];
+                                ps->v[((NG + ng) * 16 + l16) * 4 + k] = acc[ng][k];
+                            } else {
+                                ps->v[(ng * 16 + l16) * 4 + k] = acc[ng][k];
+                            }
+                        }
+                }
+            }
+        }
+        if (++b == nbu) {
+            b = 0;
+            if (++lu == upj) {
+                lu = 0;
+                ++j;
+            }
+        }
+    }
+    return true;
+}
+
+// after the block barrier: the warp that holds a unit's first piece adds the later warps' pieces and writes the unit
+template <int NG, int MODE, typename LaneXFn>
+__device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* pieces, int warp, int nwarp, int lane, LaneXFn&& lane_x) {
+    const PieceSlot* first = pieces + warp * 2 + 1;
+    const int u = first->unit;
+    if (u < 0) return;
+    const int nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
+    const int l16 = (lane >> 2) * 2 + (lane & 3);
+    const bool holder = (lane & 3) < 2;
+    float acc[NG][4], gacc[NG][4];
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            gacc[ng][k] = holder && MODE == MAT_GATEUP ? first->v[(ng * 16 + l16) * 4 + k] : 0.f;
+            acc[ng][k] = holder ? first->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k] : 0.f;
+        }
+    for (int ww = warp + 1; ww < nwarp; ++ww) {
+        const PieceSlot* c = pieces + ww * 2;
+        if (c->unit == -2) continue;
+        if (c->unit != u) break;
+#pragma unroll
+        for (int ng = 0; ng < NG; ++ng)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (holder) {
+                    if (MODE == MAT_GATEUP) gacc[ng][k] += c->v[(ng * 16 + l16) * 4 + k];
+                    acc[ng][k] += c->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k];
+                }
+        if (c->b_hi == nbu) break;
+    }
+    int ntok = 0;
+    int orow[4 * NG];
+    LaneX<NG> lx;
+    lane_x(first->job, lx, ntok, orow);
+    mat_write_unit<NG, MODE>(m, u % upj, orow, ntok, lane, gacc, acc);
 }
 
 }  // namespace fnxb

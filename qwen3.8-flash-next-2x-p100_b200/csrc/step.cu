@@ -378,7 +378,7 @@ __device__ void mat_phase(const Smem& sm, Flow& f, int tid, const MatWork& w, in
             for (int ng = 0; ng < NG; ++ng)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) acc[ng][k] = 0.f;
-            core_item<NG>(stage + (size_t) it * TILE_BYTES, sm.table, lx, blk, lane, acc);
+            core_item<NG>(smem_u32(stage + (size_t) it * TILE_BYTES), smem_u32(sm.table), lx, blk, lane, acc);
             const int g = lane >> 2, q = lane & 3;
 #pragma unroll
             for (int ng = 0; ng < NG; ++ng) {

@@ -94,7 +94,7 @@ def test_dense_rejects_bad_shapes(F):
     tiles = torch.zeros(F.iq3s_bytes(64, 2048), dtype=torch.uint8, device="cuda")
     x = torch.zeros((1, 2048), device="cuda")
     with pytest.raises(F.FnxError):
-        F.dense(tiles, 48, 2048, x)          # not a whole number of steps
+        F.dense(tiles, 40, 2048, x)          # not a whole number of 16-row tiles
     with pytest.raises(F.FnxError):
         F.dense(tiles, 64, 768, x[:, :768])  # unsupported column count
 
