@@ -114,9 +114,8 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     ring.slots_s = smem_u32(ring.slots);
     const uint32_t table_s = smem_u32(table);
     ring.bars = bars + warp * R;
-    ring.R = R;
-    ring.issued = ring.consumed = 0;
-    ring.t_wait = ring.t_comp = ring.t_issue = 0;
+    ring.parity = 0;
+    ring_reset(ring, R);
     const int njobs = p.jobs ? min(*p.njobs, p.njobs_max) : 1, upj = p.rows / 16;
     const long long total = (long long) njobs * upj;
     const int u0 = (int) (total * blockIdx.x / gridDim.x), u1 = (int) (total * (blockIdx.x + 1) / gridDim.x);
@@ -174,10 +173,6 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     }
     if (prof && tid == 0) {
         prof[0] = (unsigned long long) nstamp;
-        prof[40] = (unsigned long long) ring.t_wait;
-        prof[41] = (unsigned long long) ring.t_comp;
-        prof[42] = (unsigned long long) ring.t_issue;
-        prof[43] = (unsigned long long) ring.consumed;
     }
 }
 

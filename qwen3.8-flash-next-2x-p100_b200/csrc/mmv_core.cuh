@@ -332,11 +332,21 @@ struct MatDesc {
 struct WarpRing {
     uint8_t* slots;          // R x TILE_BYTES
     uint32_t slots_s;        // their shared address
-    uint64_t* bars;          // R
-    int R;
-    unsigned issued, consumed;
-    long long t_wait, t_comp, t_issue;   // diagnostics: clock cycles spent waiting for weights, computing, issuing
+    uint64_t* bars;          // one per slot (up to 8)
+    int R;                   // slots in use: may change while the ring is empty
+    unsigned in_slot, out_slot;   // next slot to fill, next slot to read
+    unsigned parity;         // bit i: the phase parity slot i's next read waits for
+    int pre;                 // items of the next mat_items() call already issued (mat_preissue)
+    // the issue cursor (lane 0): next item `ahead` = block ab of local tile al of job aj, weights aw
+    int ahead, ab, al, aj;
+    const uint8_t* aw;
 };
+
+__device__ __forceinline__ void ring_reset(WarpRing& r, int R) {
+    r.R = R;
+    r.in_slot = r.out_slot = 0;
+    r.pre = 0;
+}
 
 // a piece of a unit left for the end-of-pass combine: slot [warp][0] = a piece that continues a unit begun by an
 // earlier warp, slot [warp][1] = the first piece of a unit that later warps continue
@@ -376,6 +386,55 @@ __device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const i
         }
 }
 
+// places the warp's issue cursor at the first item of its share of units [ua, ub)
+template <int MODE>
+__device__ __forceinline__ void mat_cursor(const MatDesc& m, int ua, int ub, WarpRing& ring, int warp, int nwarp) {
+    const int nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
+    const long long N = (long long) (ub - ua) * nbu;
+    const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
+    ring.ahead = i0;
+    ring.ab = i0 % nbu;
+    ring.al = (ua + i0 / nbu) % upj;
+    ring.aj = (ua + i0 / nbu) / upj;
+    ring.aw = i0 < i1 ? mat_job_weights(m, ring.aj) : nullptr;
+}
+
+// lane 0: bulk copies for the items before min(i1, limit) that are not yet on their way
+template <int MODE>
+__device__ __forceinline__ void mat_issue_upto(const MatDesc& m, WarpRing& ring, int i1, int limit, int lane) {
+    if (lane != 0) return;
+    const int KB = m.K / 256, nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
+    while (ring.ahead < i1 && ring.ahead < limit) {
+        const unsigned st = ring.in_slot;
+        const uint8_t* src = MODE == MAT_GATEUP && ring.ab >= KB ? ring.aw + ((size_t) (upj + ring.al) * KB + (ring.ab - KB)) * TILE_BYTES
+                                                                 : ring.aw + ((size_t) ring.al * KB + ring.ab) * TILE_BYTES;
+        fence_proxy_async();
+        mbar_expect_tx(&ring.bars[st], TILE_BYTES);
+        bulk_g2s(ring.slots + (size_t) st * TILE_BYTES, src, TILE_BYTES, &ring.bars[st]);
+        ring.in_slot = st + 1 == (unsigned) ring.R ? 0u : st + 1;
+        ++ring.ahead;
+        if (++ring.ab == nbu) {
+            ring.ab = 0;
+            if (++ring.al == upj) {
+                ring.al = 0;
+                ++ring.aj;
+                if (ring.ahead < i1) ring.aw = mat_job_weights(m, ring.aj);
+            }
+        }
+    }
+}
+
+// before the barrier that precedes a matrix phase whose weights do not depend on it: the warp's first items on their way
+template <int MODE>
+__device__ __forceinline__ void mat_preissue(const MatDesc& m, int ua, int ub, WarpRing& ring, int warp, int nwarp, int lane) {
+    const int nbu = mat_blocks_per_unit(MODE, m.K);
+    const long long N = (long long) (ub - ua) * nbu;
+    const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
+    mat_cursor<MODE>(m, ua, ub, ring, warp, nwarp);
+    mat_issue_upto<MODE>(m, ring, i1, i0 + ring.R, lane);
+    ring.pre = 1;
+}
+
 // This warp's share of the items of units [ua, ub).  `lane_x(j, lx, ntok, orow)` sets the lane's activation pointers
 // and output rows for job j.  pieces: [nwarp][2] slots.  Returns false when a wait gave up.  The caller runs a block
 // barrier and then mat_combine().
@@ -390,31 +449,9 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
         mine[0].unit = i0 < i1 ? -1 : -2;
         mine[1].unit = -1;
     }
-    // the issue cursor (lane 0): next item `ahead` = block ab of unit (local tile al of job aj)
-    int ahead = i0, ab = i0 % nbu, al = (ua + i0 / nbu) % upj, aj = (ua + i0 / nbu) / upj;
-    const uint8_t* aw = i0 < i1 ? mat_job_weights(m, aj) : nullptr;
-    auto issue_upto = [&](int limit) {
-        if (lane == 0) {
-            while (ahead < i1 && ahead < limit) {
-                const unsigned st = ring.issued % ring.R;
-                const uint8_t* src = MODE == MAT_GATEUP && ab >= KB ? aw + ((size_t) (upj + al) * KB + (ab - KB)) * TILE_BYTES
-                                                                   : aw + ((size_t) al * KB + ab) * TILE_BYTES;
-                fence_proxy_async();
-                mbar_expect_tx(&ring.bars[st], TILE_BYTES);
-                bulk_g2s(ring.slots + (size_t) st * TILE_BYTES, src, TILE_BYTES, &ring.bars[st]);
-                ++ring.issued;
-                ++ahead;
-                if (++ab == nbu) {
-                    ab = 0;
-                    if (++al == upj) {
-                        al = 0;
-                        ++aj;
-                        if (ahead < i1) aw = mat_job_weights(m, aj);
-                    }
-                }
-            }
-        }
-    };
+    if (!ring.pre) mat_cursor<MODE>(m, ua, ub, ring, warp, nwarp);
+    ring.pre = 0;
+    auto issue_upto = [&](int limit) { mat_issue_upto<MODE>(m, ring, i1, limit, lane); };
     issue_upto(i0 + ring.R);
     int cur_job = -1, ntok = 0, b_lo = 0;
     int orow[4 * NG];
@@ -433,22 +470,15 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
                 lane_x(j, lx, ntok, orow);
             }
         }
-        const unsigned st = ring.consumed % ring.R;
-        const long long c0 = clock64();
-        if (!mbar_wait_bounded(&ring.bars[st], (ring.consumed / ring.R) & 1u, 8000000u)) return false;
-        const long long c1 = clock64();
-        ++ring.consumed;
+        const unsigned st = ring.out_slot;
+        if (!mbar_wait_bounded(&ring.bars[st], (ring.parity >> st) & 1u, 8000000u)) return false;
+        ring.parity ^= 1u << st;
+        ring.out_slot = st + 1 == (unsigned) ring.R ? 0u : st + 1;
         const uint32_t tile_s = ring.slots_s + st * (uint32_t) TILE_BYTES;
         if (MODE == MAT_GATEUP && b < KB) core_item<NG>(tile_s, table_s, lx, b, lane, gacc);
         else core_item<NG>(tile_s, table_s, lx, MODE == MAT_GATEUP ? b - KB : b, lane, acc);
         __syncwarp();
-        const long long c2 = clock64();
         issue_upto(s + 1 + ring.R);
-        __syncwarp();
-        const long long c3 = clock64();
-        ring.t_wait += c1 - c0;
-        ring.t_comp += c2 - c1;
-        ring.t_issue += c3 - c2;
         if (b == nbu - 1 || s == i1 - 1) {
             // level 1 (threads q = 0, 1) + level 2 (q = 2, 3) of the same rows
 #pragma unroll
