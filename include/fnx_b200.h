@@ -34,7 +34,8 @@ enum { FNX_ERR_TIMEOUT = 1, FNX_ERR_NONFINITE = 2, FNX_ERR_LOGITS = 16 };
 
 enum { FNX_TOPK_N = 64,      /* sampler candidates per row (TOPK_N, engine/src/kernels.hpp:441) */
        FNX_MAX_ROWS = 32,    /* rows (tree nodes) of one verify window */
-       FNX_JOB_TOK = 4 };    /* activation rows of one expert job */
+       FNX_JOB_TOK = 4,      /* activation rows of one expert job */
+       FNX_ATTN_STATIC_MAX_SLOTS = 16384 };   /* (row, head, split) partials fnx_attn_static's built-in scratch holds */
 
 const char* fnx_last_error(void);
 int fnx_version(void);
@@ -114,6 +115,22 @@ int fnx_attn_prep_append(float* qg, int ldq, float* k, int ldk, const float* v, 
 size_t fnx_attn_scratch_bytes(int T, int nq, int hd);
 int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
              const int* pos0, const int* parent, void* scratch, fnx_stream st);
+/* fnx_attn without caller scratch and without any allocation (no counterpart in the reference, whose attn takes the
+ * caller's buffer, engine/src/kernels.hpp:238): the split partials go to one file-scope device array of
+ * FNX_ATTN_STATIC_MAX_SLOTS x (hd floats + 8 bytes) = 16.9 MB per device, for callers that may not allocate (a
+ * memory-frozen serving process).  Same arguments, kernels and results as fnx_attn.
+ * Limit: T * nq * splits <= FNX_ATTN_STATIC_MAX_SLOTS, where splits = SM count / nkv (148 / nkv on a B200): e.g. 13
+ * rows of 16 heads over 2 KV heads; larger windows are rejected with FNX_E_ARG and a message naming the three factors.
+ * Set-up: the first call on a device resolves the array's address with cudaGetSymbolAddress (return code checked) and
+ * raises the kernel's shared-memory limit; neither belongs inside a stream capture, so call fnx_attn_static_setup()
+ * (or one plain fnx_attn_static) once per device before capturing.  After set-up a call makes two kernel launches and
+ * no other runtime call.
+ * Sharing: every call on a device uses the same array.  Nothing in it has to start at zero (each call overwrites
+ * every slot it later reads), but two calls that overlap in time (different streams or host threads, same device)
+ * race on it and give undefined results: serialise them on one stream, or use fnx_attn with separate scratch. */
+int fnx_attn_static_setup(void);
+int fnx_attn_static(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
+                    const int* pos0, const int* parent, fnx_stream st);
 
 /* ---------------------------------------------------------------------------------------------- gated DeltaNet
  * gdn_core (engine/src/kernels.hpp:97-99).  State and conv-history rings of NS slots replace snap / hsnap + the

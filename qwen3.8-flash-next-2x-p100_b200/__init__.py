@@ -68,6 +68,8 @@ _PROTOS = {
     "fnx_attn_prep_append": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P]),
     "fnx_attn_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "fnx_attn_static_setup": (_I, []),
+    "fnx_attn_static": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "fnx_gdn_core": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _P]),
     "fnx_argmax": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "fnx_top_tokens": (_I, [_P, _I, _I, _P, _P, _P]),
@@ -251,6 +253,17 @@ def attn(qg, kc, vc, pos0, parent=None, scratch=None):
     if scratch is None:
         scratch = torch.empty(lib().fnx_attn_scratch_bytes(T, nq, hd), dtype=torch.uint8, device=qg.device)
     check(lib().fnx_attn(ptr(qg), nq * hd2, ptr(kc), ptr(vc), ptr(out), T, nq, nkv, hd, ptr(pos0), ptr(parent), ptr(scratch), _stream()))
+    return out
+
+
+def attn_static(qg, kc, vc, pos0, parent=None):
+    """fnx_attn_static: attention whose split partials live in the library's built-in device array (nothing is allocated
+    by the library; `out` is the caller's)."""
+    import torch
+    T, nq, hd2 = qg.shape
+    nkv, hd = kc.shape[1], kc.shape[2]
+    out = torch.empty((T, nq, hd), dtype=torch.float32, device=qg.device)
+    check(lib().fnx_attn_static(ptr(qg), nq * hd2, ptr(kc), ptr(vc), ptr(out), T, nq, nkv, hd, ptr(pos0), ptr(parent), _stream()))
     return out
 
 

@@ -307,3 +307,66 @@ extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc
     FNX_LAUNCH_OK("fnx_attn (combine)");
     return FNX_OK;
 }
+
+// ---- allocation-free variant: the split partials live in a file-scope device array -------------------------------------------------
+
+namespace fnxb {
+
+constexpr int ATT_STATIC_SLOTS = FNX_ATTN_STATIC_MAX_SLOTS;   // (row, head, split) partials
+constexpr int ATT_STATIC_HD = ATT_THREADS;
+constexpr size_t ATT_STATIC_BYTES = (size_t) ATT_STATIC_SLOTS * (ATT_STATIC_HD * sizeof(float) + sizeof(AttPartial));
+static __device__ __align__(256) unsigned char g_attn_static_scratch[ATT_STATIC_BYTES];
+
+constexpr int ATT_STATIC_MAX_DEV = 64;
+static void* g_attn_static_ptr[ATT_STATIC_MAX_DEV];   // per device: the array's address, resolved once
+
+static int attn_static_resolve(void** out) {
+    int dev = -1;
+    FNX_CUDA_OK(cudaGetDevice(&dev));
+    FNX_REQUIRE(dev >= 0 && dev < ATT_STATIC_MAX_DEV, "fnx_attn_static: device %d", dev);
+    if (!g_attn_static_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t rc = cudaGetSymbolAddress((void**) &p, g_attn_static_scratch);
+        if (rc != cudaSuccess || !p) return fail(FNX_E_CUDA, "fnx_attn_static: cudaGetSymbolAddress: %s", cudaGetErrorString(rc));
+        FNX_CUDA_OK(cudaFuncSetAttribute(k_attn_part, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+        g_attn_static_ptr[dev] = p;
+    }
+    *out = g_attn_static_ptr[dev];
+    return FNX_OK;
+}
+
+}  // namespace fnxb
+
+extern "C" int fnx_attn_static_setup(void) {
+    void* p = nullptr;
+    return attn_static_resolve(&p);
+}
+
+extern "C" int fnx_attn_static(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd, const int* pos0,
+                               const int* parent, fnx_stream st) {
+    FNX_REQUIRE(qg && kc && vc && out && pos0, "fnx_attn_static: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_attn_static: %d rows", T);
+    FNX_REQUIRE(hd == ATT_THREADS, "fnx_attn_static: head dim %d (this build: %d)", hd, ATT_THREADS);
+    FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQ, "fnx_attn_static: %d q heads over %d KV heads", nq, nkv);
+    const int S = attn_splits(nkv);
+    FNX_REQUIRE(S <= 256, "fnx_attn_static: %d splits", S);
+    const long long slots = (long long) T * nq * S;
+    FNX_REQUIRE(slots <= ATT_STATIC_SLOTS,
+                "fnx_attn_static: %d rows x %d heads x %d splits = %lld partials exceed the built-in scratch of %d; use fnx_attn with caller scratch",
+                T, nq, S, slots, ATT_STATIC_SLOTS);
+    void* scratch = nullptr;
+    if (const int rc = attn_static_resolve(&scratch)) return rc;
+    float* acc = (float*) scratch;
+    AttPartial* mz = (AttPartial*) (acc + (size_t) slots * hd);
+    const size_t smem = (size_t) ATT_ROWS * ATT_MAXQ * hd * sizeof(float) + (size_t) ATT_CH * (hd + 8) * sizeof(__half) +
+                        (size_t) ATT_CH * hd * sizeof(__half) + (size_t) ATT_ROWS * ATT_MAXQ * (ATT_CH + 3) * sizeof(float) +
+                        ATT_ROWS * sizeof(unsigned);
+    cudaError_t le = launch_k(k_attn_part, dim3(S, nkv, (T + ATT_ROWS - 1) / ATT_ROWS), dim3(ATT_THREADS), smem, as_stream(st), qg, ldq,
+                              (const __half*) kc, (const __half*) vc, acc, mz, T, nq, nkv, hd, pos0, parent);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_part: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_attn_static (partials)");
+    le = launch_k(k_attn_combine, dim3(nq, T), dim3(hd), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_attn_static (combine)");
+    return FNX_OK;
+}
