@@ -20,7 +20,7 @@
 #include <cuda_runtime.h>
 
 #include "fnx_common.cuh"
-#include "mmv_core.cuh"
+#include "mmv_stage.cuh"
 
 namespace fnxb {
 
@@ -38,47 +38,6 @@ __device__ __forceinline__ unsigned long long gtime() {
         if (prof && tid == 0 && nstamp < MMV_PROF_SLOTS - 1) prof[1 + nstamp++] = gtime(); \
     } while (0)
 
-constexpr int MMV_THREADS = 512, MMV_WARPS = 16;
-
-struct MmvParams {
-    const uint8_t* W;
-    size_t expert_stride;
-    int e_base;
-    const uint8_t* Wsh;
-    int E;
-    const fnx_job* jobs;
-    const int* njobs;
-    int njobs_max;
-    int T;
-    const float* x;
-    int ldx;
-    const float* norm_w;
-    float eps;
-    float* out;
-    int ldo;
-    int rows;   // output rows per job (gate|up: F)
-    int K;
-    int accumulate;
-    int R;      // ring slots per warp
-    unsigned* err;
-};
-
-// jobs whose activation images a block holds at once: its range of units spans at most two jobs of gate|up and a
-// few of down; anything wider is walked in passes
-template <int MODE>
-__host__ __device__ constexpr int mmv_jmax() { return MODE == MAT_DENSE ? 1 : MODE == MAT_GATEUP ? 2 : 4; }
-
-template <int NG, int MODE>
-__host__ __device__ inline size_t mmv_image_bytes(int K) {
-    return (size_t) mmv_jmax<MODE>() * NG * ((size_t) (K / 32) * 32 * 8 + (size_t) (K / 256) * 8 * 4);
-}
-template <int NG, int MODE>
-__host__ __device__ inline size_t mmv_smem_bytes(int K, int R) {
-    constexpr int rows = mmv_jmax<MODE>() * 4 * NG;
-    return (size_t) CORE_TABLE_BYTES + (size_t) MMV_WARPS * R * (TILE_BYTES + 8) + mmv_image_bytes<NG, MODE>(K) + rows * (sizeof(float*) + 5 * sizeof(float)) +
-           (size_t) MMV_WARPS * 2 * PIECE_BYTES + 8 * sizeof(void*) + 64;
-}
-
 template <int NG, int MODE>
 __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -86,102 +45,43 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     constexpr int JMAX = mmv_jmax<MODE>(), NROW = JMAX * 4 * NG;
     const int KB = p.K / 256, R = p.R;
     uint8_t* table = smem_raw;
-    uint8_t* slots = table + CORE_TABLE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t) MMV_WARPS * R * TILE_BYTES);
-    uint2* cells = reinterpret_cast<uint2*>(bars + MMV_WARPS * R);
-    float* scales = reinterpret_cast<float*>(cells + (size_t) JMAX * NG * (p.K / 32) * 32);
-    const float** rowptr = reinterpret_cast<const float**>(scales + (size_t) JMAX * NG * KB * 8);
-    float* rs = reinterpret_cast<float*>(rowptr + NROW);
-    PieceSlot* pieces = reinterpret_cast<PieceSlot*>(rs + NROW * 5);
-    const uint8_t** jobw = reinterpret_cast<const uint8_t**>(pieces + MMV_WARPS * 2);
+    StageSmem S;
+    S.table_s = smem_u32(table);
+    S.slots = table + CORE_TABLE_BYTES;
+    S.bars = reinterpret_cast<uint64_t*>(S.slots + (size_t) MMV_WARPS * R * TILE_BYTES);
+    S.bar_stride = R;
+    S.cells = reinterpret_cast<uint2*>(S.bars + MMV_WARPS * R);
+    S.scales = reinterpret_cast<float*>(S.cells + (size_t) JMAX * NG * (p.K / 32) * 32);
+    S.rs = S.scales + (size_t) JMAX * NG * KB * 8;
+    S.pieces = reinterpret_cast<PieceSlot*>(S.rs + NROW * 16);
+    S.jobs_s = reinterpret_cast<fnx_job*>(S.pieces + MMV_WARPS * 2);
     unsigned long long* prof = g_mmv_prof ? g_mmv_prof + (size_t) blockIdx.x * MMV_PROF_SLOTS : nullptr;
     int nstamp = 0;
     MMV_STAMP();
     pdl_launch_dependents();
+    pdl_wait();   // from here on: what earlier kernels of the stream wrote (activations, job lists)
+    // the job list or the first rows are fetched while the codebook is replicated and the barriers are set up
+    StageRegs h;
+    stage_begin<NG, MODE>(p, h, tid, RowPlain());
     core_fill_table(table, tid, MMV_THREADS);
     if (lane == 0) {
-        for (int i = 0; i < R; ++i) mbar_init(&bars[warp * R + i], 1);
+        for (int i = 0; i < R; ++i) mbar_init(&S.bars[warp * R + i], 1);
         fence_barrier_init();
     }
-    pdl_wait();   // from here on: what earlier kernels of the stream wrote (activations, job lists)
     __syncthreads();
-    MMV_STAMP();
-    MatDesc m;
-    m.W = p.W; m.expert_stride = p.expert_stride; m.e_base = p.e_base; m.Wsh = p.Wsh; m.E = p.E; m.jobs = p.jobs; m.jobw = p.jobs ? jobw : nullptr; m.jobw0 = 0;
-    m.rows = p.rows; m.K = p.K; m.out = p.out; m.ldo = p.ldo; m.accumulate = p.accumulate;
     WarpRing ring;
-    ring.slots = slots + (size_t) warp * R * TILE_BYTES;
-    ring.slots_s = smem_u32(ring.slots);
-    const uint32_t table_s = smem_u32(table);
-    ring.bars = bars + warp * R;
     ring.parity = 0;
-    ring_reset(ring, R);
-    const int njobs = p.jobs ? min(*p.njobs, p.njobs_max) : 1, upj = p.rows / 16;
-    const long long total = (long long) njobs * upj;
-    const int u0 = (int) (total * blockIdx.x / gridDim.x), u1 = (int) (total * (blockIdx.x + 1) / gridDim.x);
-    bool ok = true;
-    for (int uc = u0; uc < u1;) {
-        const int j0 = uc / upj, j1 = min(j0 + JMAX, (u1 - 1) / upj + 1), ue = min(u1, j1 * upj);
-        if (tid < NROW) {
-            const int slot = tid / (4 * NG), r = tid % (4 * NG), j = j0 + slot;
-            const float* ptr = nullptr;
-            if (j < j1) {
-                if (!p.jobs) ptr = r < p.T ? p.x + (size_t) r * p.ldx : nullptr;
-                else {
-                    const fnx_job& jb = p.jobs[j];
-                    if (r < jb.n && r < 4) ptr = p.x + (size_t) (MODE == MAT_DOWN ? jb.out[r] : jb.y[r]) * p.ldx;
-                }
-            }
-            rowptr[tid] = ptr;
-        }
-        if (p.jobs && tid >= 64 && tid < 64 + JMAX) {
-            const int j = j0 + tid - 64;
-            if (j < j1) {
-                const int e = p.jobs[j].w;
-                jobw[tid - 64] = e >= p.E ? p.Wsh : p.W + (size_t) (e - p.e_base) * p.expert_stride;
-            }
-        }
-        m.jobw0 = j0;
-        __syncthreads();
-        quant_rows(rowptr, NROW, p.K, MODE == MAT_DOWN ? nullptr : p.norm_w, p.eps, cells, scales, rs, tid, MMV_THREADS);
-        MMV_STAMP();
-        auto lane_x = [&](int j, LaneX<NG>& lx, int& ntok, int (&orow)[4 * NG]) {
-            if (!p.jobs) {
-                ntok = p.T;
-#pragma unroll
-                for (int i = 0; i < 4 * NG; ++i) orow[i] = i;
-                lx = lane_x_dense<NG>(cells, scales, p.K, p.T, lane);
-            } else {
-                const fnx_job jb = p.jobs[j];
-                ntok = min(jb.n, 4);
-#pragma unroll
-                for (int i = 0; i < 4 * NG; ++i) orow[i] = jb.out[i & 3];
-                const int slot = j - j0;
-                lx = lane_x_dense<NG>(cells + (size_t) slot * NG * (p.K / 32) * 32, scales + (size_t) slot * NG * KB * 8, p.K, ntok, lane);
-            }
-        };
-        if (ok) {
-            ok = mat_items<NG, MODE>(m, uc, ue, table_s, ring, pieces, warp, MMV_WARPS, lane, lane_x);
-            if (!ok) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
-        }
-        __syncthreads();
-        MMV_STAMP();
-        if (ok) mat_combine<NG, MODE>(m, pieces, warp, MMV_WARPS, lane, lane_x);
-        __syncthreads();   // the images are rewritten by the next pass
-        MMV_STAMP();
-        uc = ue;
-    }
-    if (prof && tid == 0) {
-        prof[0] = (unsigned long long) nstamp;
-    }
+    stage_ring(ring, S, R, warp);
+    stage_run<NG, MODE>(p, S, ring, h, tid, blockIdx.x, gridDim.x, RowPlain(), [&]() { MMV_STAMP(); });
+    if (prof && tid == 0) prof[0] = (unsigned long long) nstamp;
 }
 
 template <int NG, int MODE>
 static int launch_mmv(const MmvParams& p0, cudaStream_t st) {
     MmvParams p = p0;
     p.R = 6;   // tile blocks in flight per warp: as many as the shared memory left by the codebook and the images holds
-    while (p.R > 2 && mmv_smem_bytes<NG, MODE>(p.K, p.R) > 227 * 1024) --p.R;
-    const size_t smem = mmv_smem_bytes<NG, MODE>(p.K, p.R);
+    while (p.R > 2 && mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max) > 227 * 1024) --p.R;
+    const size_t smem = mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max);
     if (smem > 227 * 1024) return fail(FNX_E_ARG, "iq3s_mmv: %d columns x %d rows need %zu bytes of shared memory", p.K, 4 * NG, smem);
     static bool configured = false;
     if (!configured) {

@@ -29,11 +29,15 @@ __host__ __device__ __forceinline__ size_t img_bytes(int rows, int K) {
 
 // the codebook, one copy per bank: entry e at byte e * 128 + 4 * lane
 __device__ __forceinline__ void core_fill_table(uint8_t* table, int tid, int nthreads) {
-    for (int e = tid; e < 512; e += nthreads) {
-        const uint32_t v = g_grid_core[e];
-        uint4* d = reinterpret_cast<uint4*>(table + e * 128);
+    // a warp writes 32 entries: each store instruction covers 4 whole entries (512 contiguous bytes: no bank conflicts)
+    const int warp = tid >> 5, lane = tid & 31, nwarp = nthreads >> 5;
+    for (int e0 = warp * 32; e0 < 512; e0 += nwarp * 32) {
+        const uint32_t mine = g_grid_core[e0 + lane];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) d[i] = make_uint4(v, v, v, v);
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t v = __shfl_sync(0xffffffffu, mine, 4 * i + (lane >> 3));
+            *reinterpret_cast<uint4*>(table + (e0 + 4 * i) * 128 + lane * 16) = make_uint4(v, v, v, v);
+        }
     }
 }
 
@@ -52,30 +56,36 @@ __device__ __forceinline__ uint32_t core_pack_s8x4(int a, int b, int c, int d) {
     return r;
 }
 
-// shared-memory loads by 32-bit shared address: no 64-bit generic pointer arithmetic in the decode loop
+// shared-memory loads by 32-bit shared address plus a compile-time offset that rides in the instruction: no 64-bit
+// generic pointer arithmetic and no address adds in the decode loop
+template <int OFF = 0>
 __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
     uint32_t v;
-    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
     return v;
 }
+template <int OFF = 0>
 __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
     uint16_t v;
-    asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    asm("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(OFF));
     return v;
 }
+template <int OFF = 0>
 __device__ __forceinline__ uint2 lds_v2(uint32_t a) {
     uint2 v;
-    asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    asm("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFF));
     return v;
 }
+template <int OFF = 0>
 __device__ __forceinline__ uint4 lds_v4(uint32_t a) {
     uint4 v;
-    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF));
     return v;
 }
+template <int OFF = 0>
 __device__ __forceinline__ float lds_f32(uint32_t a) {
     float v;
-    asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    asm("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
     return v;
 }
 
@@ -94,9 +104,11 @@ struct LaneX {
     uint32_t b[NG];     // shared addresses; 0 = an empty column
     uint32_t s0[NG];
     uint32_t s1[NG];
+    float r0[NG], r1[NG];   // factors of the two C columns' rows (1 / rms of a normed row, else 1)
 };
 
 // lane pointers for a dense product over rows [0, T): group ng holds rows 4 ng .. 4 ng + 3
+// (T >= 4 NG: every column gets its address; rows that hold nothing must then be zero cells with zero scales)
 template <int NG>
 __device__ __forceinline__ LaneX<NG> lane_x_dense(const uint2* xq, const float* xs, int K, int T, int lane) {
     LaneX<NG> lx;
@@ -107,6 +119,7 @@ __device__ __forceinline__ LaneX<NG> lane_x_dense(const uint2* xq, const float* 
         const int c0 = 2 * q, c1 = 2 * q + 1;
         lx.s0[ng] = 4 * ng + (c0 & 3) < T ? smem_u32(xs + (size_t) ng * KB * 8 + c0) : 0u;
         lx.s1[ng] = 4 * ng + (c1 & 3) < T ? smem_u32(xs + (size_t) ng * KB * 8 + c1) : 0u;
+        lx.r0[ng] = lx.r1[ng] = 1.0f;
     }
     return lx;
 }
@@ -122,6 +135,7 @@ __device__ __forceinline__ LaneX<1> lane_x_job(const uint2* xq, const float* xs,
     }
     const int c0 = 2 * q, c1 = 2 * q + 1;
     lx.s0[0] = lx.s1[0] = 0u;
+    lx.r0[0] = lx.r1[0] = 1.0f;
     if ((c0 & 3) < ntok) {
         const int row = y[c0 & 3];
         lx.s0[0] = smem_u32(xs + (size_t) (row >> 2) * KB * 8 + (row & 3) + 4 * (c0 >> 2));
@@ -133,7 +147,7 @@ __device__ __forceinline__ LaneX<1> lane_x_job(const uint2* xq, const float* xs,
     return lx;
 }
 
-template <int NG, int SB>
+template <int NG, int SB, bool CHECK>
 __device__ __forceinline__ void core_sub_block(const uint32_t (&S0)[5], const uint32_t (&G0)[2], const uint32_t (&S1)[5], const uint32_t (&G1)[2],
                                                uint2 sc0, uint2 sc1, uint32_t table_s, uint32_t lane4, const uint32_t (&bx)[NG],
                                                int (&accI)[NG][4]) {
@@ -151,7 +165,7 @@ __device__ __forceinline__ void core_sub_block(const uint32_t (&S0)[5], const ui
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
         uint2 b = make_uint2(0u, 0u);
-        if (bx[ng]) b = lds_v2(bx[ng] + SB * 256);   // bx: this lane's cells of the block's first sub-block
+        if (!CHECK || bx[ng]) b = lds_v2<SB * 256>(bx[ng]);   // bx: this lane's cells of the block's first sub-block
         int c[4];
         core_mma_s8(c, a0, a1, a2, a3, b.x, b.y);
         accI[ng][0] += w0 * c[0];
@@ -163,44 +177,51 @@ __device__ __forceinline__ void core_sub_block(const uint32_t (&S0)[5], const ui
 
 // One item: tile (16 rows x 256 columns, block `blk` of its rows) against the lane's activation cells; adds into
 // acc[ng][0..3] = (row g, col 2q), (row g, col 2q+1), (row g+8, col 2q), (row g+8, col 2q+1).
-template <int NG>
+// CHECK: a zero address in lx means an empty column; without it every address is read (empty rows are zero cells).
+template <int NG, bool CHECK = true>
 __device__ __forceinline__ void core_item(uint32_t tile_s, uint32_t table_s, const LaneX<NG>& lx, int blk, int lane, float (&acc)[NG][4]) {
     const int g = lane >> 2;
     const uint32_t lane4 = (uint32_t) lane * 4u;
-    const uint4 i0 = lds_v4(tile_s + TILE_IDX + lane * 16);
-    const uint4 i1 = lds_v4(tile_s + TILE_IDX + 512 + lane * 16);
-    const uint2 s0 = lds_v2(tile_s + TILE_SGN + lane * 8);
-    const uint2 s1 = lds_v2(tile_s + TILE_SGN + 256 + lane * 8);
-    const uint32_t t0 = lds_u16(tile_s + TILE_TAIL + lane * 2);
-    const uint32_t t1 = lds_u16(tile_s + TILE_TAIL + 64 + lane * 2);
-    const uint32_t sn0 = lds_u32(tile_s + TILE_SCL + g * 4);
-    const uint32_t sn1 = lds_u32(tile_s + TILE_SCL + (g + 8) * 4);
+    const uint32_t a16 = tile_s + lane * 16, a8 = tile_s + lane * 8, a2 = tile_s + lane * 2, ag4 = tile_s + g * 4, ag2 = tile_s + g * 2;
+    const uint4 i0 = lds_v4<TILE_IDX>(a16);
+    const uint4 i1 = lds_v4<TILE_IDX + 512>(a16);
+    const uint2 s0 = lds_v2<TILE_SGN>(a8);
+    const uint2 s1 = lds_v2<TILE_SGN + 256>(a8);
+    const uint32_t t0 = lds_u16<TILE_TAIL>(a2);
+    const uint32_t t1 = lds_u16<TILE_TAIL + 64>(a2);
+    const uint32_t sn0 = lds_u32<TILE_SCL>(ag4);
+    const uint32_t sn1 = lds_u32<TILE_SCL + 32>(ag4);
     // nibbles -> bytes 1 + 2 s: even sub-blocks (low nibbles) and odd ones (high nibbles)
     const uint2 sc0 = make_uint2((sn0 & 0x0F0F0F0Fu) * 2u + 0x01010101u, ((sn0 >> 4) & 0x0F0F0F0Fu) * 2u + 0x01010101u);
     const uint2 sc1 = make_uint2((sn1 & 0x0F0F0F0Fu) * 2u + 0x01010101u, ((sn1 >> 4) & 0x0F0F0F0Fu) * 2u + 0x01010101u);
-    const float d0 = __half2float(__ushort_as_half((unsigned short) lds_u16(tile_s + TILE_D + g * 2)));
-    const float d1 = __half2float(__ushort_as_half((unsigned short) lds_u16(tile_s + TILE_D + (g + 8) * 2)));
+    const float d0 = __half2float(__ushort_as_half((unsigned short) lds_u16<TILE_D>(ag2)));
+    const float d1 = __half2float(__ushort_as_half((unsigned short) lds_u16<TILE_D + 16>(ag2)));
     const uint32_t S0[5] = {i0.x, i0.y, i0.z, i0.w, t0}, S1[5] = {i1.x, i1.y, i1.z, i1.w, t1};
     const uint32_t G0[2] = {s0.x, s0.y}, G1[2] = {s1.x, s1.y};
     uint32_t bx[NG];
 #pragma unroll
-    for (int ng = 0; ng < NG; ++ng) bx[ng] = lx.b[ng] ? lx.b[ng] + (uint32_t) blk * 2048u : 0u;
+    for (int ng = 0; ng < NG; ++ng) bx[ng] = !CHECK || lx.b[ng] ? lx.b[ng] + (uint32_t) blk * 2048u : 0u;
     int accI[NG][4];
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng)
 #pragma unroll
         for (int i = 0; i < 4; ++i) accI[ng][i] = 0;
-    core_sub_block<NG, 0>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 1>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 2>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 3>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 4>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 5>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 6>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
-    core_sub_block<NG, 7>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 0, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 1, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 2, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 3, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 4, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 5, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 6, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
+    core_sub_block<NG, 7, CHECK>(S0, G0, S1, G1, sc0, sc1, table_s, lane4, bx, accI);
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-        const float x0 = lx.s0[ng] ? lds_f32(lx.s0[ng] + (uint32_t) blk * 32u) : 0.f, x1 = lx.s1[ng] ? lds_f32(lx.s1[ng] + (uint32_t) blk * 32u) : 0.f;
+        float x0 = !CHECK || lx.s0[ng] ? lds_f32(lx.s0[ng] + (uint32_t) blk * 32u) : 0.f;
+        float x1 = !CHECK || lx.s1[ng] ? lds_f32(lx.s1[ng] + (uint32_t) blk * 32u) : 0.f;
+        if (!CHECK) {
+            x0 *= lx.r0[ng];
+            x1 *= lx.r1[ng];
+        }
         acc[ng][0] += d0 * x0 * (float) accI[ng][0];
         acc[ng][1] += d0 * x1 * (float) accI[ng][1];
         acc[ng][2] += d1 * x0 * (float) accI[ng][2];
@@ -208,96 +229,136 @@ __device__ __forceinline__ void core_item(uint32_t tile_s, uint32_t table_s, con
     }
 }
 
-// Quantises 8 consecutive values of one lane (a cell) given the block's maximum over the warp; returns the cells
+// Quantises 8 consecutive values of one lane (a cell) given the block's maximum over the warp; returns the cells.
+// Rounding rides on the FMA pipe: adding 1.5 * 2^23 leaves round-to-nearest-even(x) in the low mantissa bits (its low
+// byte is the s8 code), so no value passes through the conversion unit.
 __device__ __forceinline__ void core_quant_cell(const float (&x8)[8], float am, uint2& c1, uint2& c2, float& d) {
-    d = am / 127.0f;
-    const float inv = am > 0.f ? 127.0f / am : 0.f, inv2 = inv * 256.0f;
-    int a8[8], b8[8];
+    constexpr float MAGIC = 12582912.0f;
+    d = am * (1.0f / 127.0f);
+    const float inv = am > 0.f ? __fdividef(127.0f, am) : 0.f, inv2 = inv * 256.0f;
+    uint32_t a8[8], b8[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        a8[i] = __float2int_rn(x8[i] * inv);
-        b8[i] = __float2int_rn((x8[i] - (float) a8[i] * d) * inv2);
+        const float ta = fmaf(x8[i], inv, MAGIC);              // |x inv| <= 127
+        const float af = ta - MAGIC;
+        const float tb = fminf(fmaf(fmaf(-af, d, x8[i]), inv2, MAGIC), MAGIC + 127.0f);   // the residue, in steps of d / 256
+        a8[i] = __float_as_uint(ta);
+        b8[i] = __float_as_uint(tb);
     }
-    c1 = make_uint2(core_pack_s8x4(a8[0], a8[1], a8[2], a8[3]), core_pack_s8x4(a8[4], a8[5], a8[6], a8[7]));
-    c2 = make_uint2(core_pack_s8x4(b8[0], b8[1], b8[2], b8[3]), core_pack_s8x4(b8[4], b8[5], b8[6], b8[7]));
+    auto pack = [](uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) {
+        uint32_t lo, hi, r;
+        asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(v0), "r"(v1));
+        asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(v2), "r"(v3));
+        asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(r) : "r"(lo), "r"(hi));
+        return r;
+    };
+    c1 = make_uint2(pack(a8[0], a8[1], a8[2], a8[3]), pack(a8[4], a8[5], a8[6], a8[7]));
+    c2 = make_uint2(pack(b8[0], b8[1], b8[2], b8[3]), pack(b8[4], b8[5], b8[6], b8[7]));
 }
 
 }  // namespace fnxb
 
 // ------------------------------------------------------------------------------------------------ rows -> image
-// Block-wide: quantises `nrows` rows (rowptr[r] null = an empty row; nrows a multiple of 4) of K values into an
-// image at (cells, scales).  With norm_w the rows are RMS-normed: the codes are those of x * w and the row's
-// 1 / rms goes into the block scales.  rs: nrows * 5 floats of shared scratch.  Ends with a block barrier.
+// A quantisation TASK is one 256-column block of one live row, done by one warp (8 values per lane); a warp works on
+// a batch of up to four tasks at once so that their loads and their warp reductions overlap.  quant_fetch() starts a
+// task's loads, quant_finish() turns a batch into image cells and scales at (cells, scales) for image rows t (group
+// t / 4, column t % 4).  With norm_w the codes are those of x * w and the block's sum of squares goes to
+// rs[t * 16 + blk]: the row's 1 / rms (quant_row_factor) multiplies the products later, it is uniform along the row.
+// Rows that hold nothing are not tasks: quant_zero_row() clears their cells and scales.
 namespace fnxb {
-__device__ __forceinline__ void quant_rows(const float* const* rowptr, int nrows, int K, const float* norm_w, float eps, uint2* cells,
-                                           float* scales, float* rs, int tid, int nthreads) {
-    const int warp = tid >> 5, lane = tid & 31, nwarp = nthreads >> 5, KB = K / 256;
-    const int CB = KB < 4 ? KB : 4, nchunk = KB / CB;
-    for (int task = warp; task < nrows * nchunk; task += nwarp) {
-        const int t = task / nchunk, ck = task % nchunk, ng = t >> 2, n = t & 3;
-        const float* xr0 = rowptr[t];
-        float v[4][8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (j < CB) {
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                if (xr0) {
-                    const float* xr = xr0 + (ck * CB + j) * 256 + lane * 8;
-                    a = *reinterpret_cast<const float4*>(xr);
-                    b = *reinterpret_cast<const float4*>(xr + 4);
-                }
-                v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
-                v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
-            }
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (j < CB) {
-                const int blk = ck * CB + j, col = blk * 256 + lane * 8;
-                if (norm_w) {
-                    const float4 w0 = *reinterpret_cast<const float4*>(norm_w + col), w1 = *reinterpret_cast<const float4*>(norm_w + col + 4);
-                    const float w8[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        ss = fmaf(v[j][i], v[j][i], ss);
-                        v[j][i] *= w8[i];
-                    }
-                }
-                float am = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[j][i]));
-                am = warp_max(am);
-                uint2 c1, c2;
-                float d;
-                core_quant_cell(v[j], am, c1, c2, d);
-                const int sbG = blk * 8 + (lane >> 2), q = lane & 3;
-                uint2* cell = cells + ((size_t) (ng * (K / 32) + sbG) * 8 + n) * 4 + q;
-                cell[0] = c1;
-                cell[16] = c2;
-                if (lane == 0) {
-                    float* sc = scales + (size_t) (ng * KB + blk) * 8;
-                    sc[n] = d;
-                    sc[n + 4] = d * (1.0f / 256.0f);
-                }
-            }
-        if (norm_w) {
-            ss = warp_sum(ss);
-            if (lane == 0) rs[t * 4 + ck] = ss;
-        }
+constexpr int QUANT_BATCH = 2;
+
+struct QuantTask {
+    const float* src;   // the block's 256 values; null: no task
+    int t, blk;
+};
+
+__device__ __forceinline__ void quant_fetch(const QuantTask& q, int lane, float (&v)[8]) {
+    if (q.src) {
+        const float4 a = *reinterpret_cast<const float4*>(q.src + lane * 8), b = *reinterpret_cast<const float4*>(q.src + lane * 8 + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     }
-    __syncthreads();
+}
+
+__device__ __forceinline__ void quant_finish(const QuantTask (&q)[QUANT_BATCH], float (&v)[QUANT_BATCH][8], int K, const float* norm_w, uint2* cells,
+                                             float* scales, float* rs, int lane) {
+    const int KB = K / 256;
+    float am[QUANT_BATCH], ss[QUANT_BATCH];
     if (norm_w) {
-        for (int i = tid; i < nrows * KB; i += nthreads) {
-            const int t = i / KB, blk = i % KB;
-            float ss = 0.f;
-            for (int c = 0; c < nchunk; ++c) ss += rs[t * 4 + c];
-            const float r = rsqrtf(ss / (float) K + eps);
-            float* sc = scales + (size_t) ((t >> 2) * KB + blk) * 8;
-            sc[t & 3] *= r;
-            sc[(t & 3) + 4] *= r;
+        float4 w[QUANT_BATCH][2];
+#pragma unroll
+        for (int j = 0; j < QUANT_BATCH; ++j)
+            if (q[j].src) {
+                w[j][0] = *reinterpret_cast<const float4*>(norm_w + q[j].blk * 256 + lane * 8);
+                w[j][1] = *reinterpret_cast<const float4*>(norm_w + q[j].blk * 256 + lane * 8 + 4);
+            }
+#pragma unroll
+        for (int j = 0; j < QUANT_BATCH; ++j) {
+            ss[j] = 0.f;
+            if (q[j].src) {
+                const float w8[8] = {w[j][0].x, w[j][0].y, w[j][0].z, w[j][0].w, w[j][1].x, w[j][1].y, w[j][1].z, w[j][1].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    ss[j] = fmaf(v[j][i], v[j][i], ss[j]);
+                    v[j][i] *= w8[i];
+                }
+            }
         }
-        __syncthreads();
     }
+#pragma unroll
+    for (int j = 0; j < QUANT_BATCH; ++j) {
+        am[j] = 0.f;
+        if (q[j].src) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) am[j] = fmaxf(am[j], fabsf(v[j][i]));
+        }
+    }
+    // the batch's maxima (and sums of squares) cross the warp together: five rounds for all of them
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < QUANT_BATCH; ++j) {
+            am[j] = fmaxf(am[j], __shfl_xor_sync(0xffffffffu, am[j], o));
+            if (norm_w) ss[j] += __shfl_xor_sync(0xffffffffu, ss[j], o);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < QUANT_BATCH; ++j)
+        if (q[j].src) {
+            const int t = q[j].t, blk = q[j].blk, ng = t >> 2, n = t & 3;
+            uint2 c1, c2;
+            float d;
+            core_quant_cell(v[j], am[j], c1, c2, d);
+            const int sbG = blk * 8 + (lane >> 2), qq = lane & 3;
+            uint2* cell = cells + ((size_t) (ng * (K / 32) + sbG) * 8 + n) * 4 + qq;
+            cell[0] = c1;
+            cell[16] = c2;
+            if (lane == 0) {
+                float* sc = scales + (size_t) (ng * KB + blk) * 8;
+                sc[n] = d;
+                sc[n + 4] = d * (1.0f / 256.0f);
+                if (norm_w) rs[t * 16 + blk] = ss[j];
+            }
+        }
+}
+
+// image row t holds nothing: zero cells, zero scales (threads idx of n cooperate)
+__device__ __forceinline__ void quant_zero_row(int t, int K, uint2* cells, float* scales, float* rs, int idx, int n_threads) {
+    const int KB = K / 256, ng = t >> 2, n = t & 3;
+    for (int i = idx; i < (K / 32) * 8; i += n_threads) {   // (sub-block, level, q)
+        const int sbG = i >> 3, lvl = (i >> 2) & 1, q = i & 3;
+        cells[((size_t) (ng * (K / 32) + sbG) * 8 + n + 4 * lvl) * 4 + q] = make_uint2(0u, 0u);
+    }
+    for (int i = idx; i < KB * 2; i += n_threads) scales[(size_t) (ng * KB + (i >> 1)) * 8 + n + 4 * (i & 1)] = 0.f;
+    for (int i = idx; i < KB; i += n_threads) rs[t * 16 + i] = 0.f;
+}
+
+// 1 / rms of image row t from the block sums (after the barrier that follows the tasks)
+__device__ __forceinline__ float quant_row_factor(const float* rs, int t, int K, float eps) {
+    float ss = 0.f;
+    for (int c = 0; c < K / 256; ++c) ss += rs[t * 16 + c];
+    return rsqrtf(ss / (float) K + eps);
 }
 }  // namespace fnxb
 
@@ -340,6 +401,7 @@ struct WarpRing {
     // the issue cursor (lane 0): next item `ahead` = block ab of local tile al of job aj, weights aw
     int ahead, ab, al, aj;
     const uint8_t* aw;
+    const uint8_t* asrc;     // the next item's tile block
 };
 
 __device__ __forceinline__ void ring_reset(WarpRing& r, int R) {
@@ -352,7 +414,8 @@ __device__ __forceinline__ void ring_reset(WarpRing& r, int R) {
 // earlier warp, slot [warp][1] = the first piece of a unit that later warps continue
 struct PieceSlot {
     int unit;                // -1: none, -2: the warp had no items at all
-    int b_lo, b_hi, job;
+    int b_lo, b_hi, job, ntok;
+    int orow[8];
     float v[128];            // [kind (gate|up only: 0 gate, 1 up)][group][16 lanes][4]
 };
 constexpr int PIECE_BYTES = sizeof(PieceSlot);
@@ -390,13 +453,16 @@ __device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const i
 template <int MODE>
 __device__ __forceinline__ void mat_cursor(const MatDesc& m, int ua, int ub, WarpRing& ring, int warp, int nwarp) {
     const int nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
-    const long long N = (long long) (ub - ua) * nbu;
+    const unsigned N = (unsigned) (ub - ua) * nbu;   // < 2^26 for any matrix here
     const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
     ring.ahead = i0;
     ring.ab = i0 % nbu;
     ring.al = (ua + i0 / nbu) % upj;
     ring.aj = (ua + i0 / nbu) / upj;
     ring.aw = i0 < i1 ? mat_job_weights(m, ring.aj) : nullptr;
+    const int KB = m.K / 256;
+    ring.asrc = MODE == MAT_GATEUP && ring.ab >= KB ? ring.aw + ((size_t) (upj + ring.al) * KB + (ring.ab - KB)) * TILE_BYTES
+                                                    : ring.aw + ((size_t) ring.al * KB + ring.ab) * TILE_BYTES;
 }
 
 // lane 0: bulk copies for the items before min(i1, limit) that are not yet on their way
@@ -406,32 +472,36 @@ __device__ __forceinline__ void mat_issue_upto(const MatDesc& m, WarpRing& ring,
     const int KB = m.K / 256, nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
     while (ring.ahead < i1 && ring.ahead < limit) {
         const unsigned st = ring.in_slot;
-        const uint8_t* src = MODE == MAT_GATEUP && ring.ab >= KB ? ring.aw + ((size_t) (upj + ring.al) * KB + (ring.ab - KB)) * TILE_BYTES
-                                                                 : ring.aw + ((size_t) ring.al * KB + ring.ab) * TILE_BYTES;
-        fence_proxy_async();
+        // the slot's previous readers are ordered before this copy by the warp barrier that precedes the call
         mbar_expect_tx(&ring.bars[st], TILE_BYTES);
-        bulk_g2s(ring.slots + (size_t) st * TILE_BYTES, src, TILE_BYTES, &ring.bars[st]);
+        bulk_g2s(ring.slots + (size_t) st * TILE_BYTES, ring.asrc, TILE_BYTES, &ring.bars[st]);
         ring.in_slot = st + 1 == (unsigned) ring.R ? 0u : st + 1;
         ++ring.ahead;
-        if (++ring.ab == nbu) {
+        ring.asrc += TILE_BYTES;   // a tile's blocks, and a matrix's tiles, follow one another
+        ++ring.ab;
+        if (MODE == MAT_GATEUP && ring.ab == KB) ring.asrc = ring.aw + (size_t) (upj + ring.al) * KB * TILE_BYTES;
+        if (ring.ab == nbu) {
             ring.ab = 0;
             if (++ring.al == upj) {
                 ring.al = 0;
                 ++ring.aj;
                 if (ring.ahead < i1) ring.aw = mat_job_weights(m, ring.aj);
             }
+            if (MODE == MAT_GATEUP || ring.al == 0) ring.asrc = ring.aw + (size_t) ring.al * KB * TILE_BYTES;
         }
     }
 }
 
 // before the barrier that precedes a matrix phase whose weights do not depend on it: the warp's first items on their way
+// (`depth` copies per warp: the copy engine takes a request every ~80 cycles per SM, and a full ring of requests from
+// every warp at once would hold the issuing lanes for microseconds)
 template <int MODE>
-__device__ __forceinline__ void mat_preissue(const MatDesc& m, int ua, int ub, WarpRing& ring, int warp, int nwarp, int lane) {
+__device__ __forceinline__ void mat_preissue(const MatDesc& m, int ua, int ub, WarpRing& ring, int warp, int nwarp, int lane, int depth) {
     const int nbu = mat_blocks_per_unit(MODE, m.K);
-    const long long N = (long long) (ub - ua) * nbu;
+    const unsigned N = (unsigned) (ub - ua) * nbu;   // < 2^26 for any matrix here
     const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
     mat_cursor<MODE>(m, ua, ub, ring, warp, nwarp);
-    mat_issue_upto<MODE>(m, ring, i1, i0 + ring.R, lane);
+    mat_issue_upto<MODE>(m, ring, i1, i0 + min(ring.R, depth), lane);
     ring.pre = 1;
 }
 
@@ -442,7 +512,7 @@ template <int NG, int MODE, typename LaneXFn>
 __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint32_t table_s, WarpRing& ring, PieceSlot* pieces, int warp,
                                           int nwarp, int lane, LaneXFn&& lane_x) {
     const int KB = m.K / 256, nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
-    const long long N = (long long) (ub - ua) * nbu;
+    const unsigned N = (unsigned) (ub - ua) * nbu;   // < 2^26 for any matrix here
     const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
     PieceSlot* mine = pieces + warp * 2;
     if (lane == 0) {
@@ -475,8 +545,8 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
         ring.parity ^= 1u << st;
         ring.out_slot = st + 1 == (unsigned) ring.R ? 0u : st + 1;
         const uint32_t tile_s = ring.slots_s + st * (uint32_t) TILE_BYTES;
-        if (MODE == MAT_GATEUP && b < KB) core_item<NG>(tile_s, table_s, lx, b, lane, gacc);
-        else core_item<NG>(tile_s, table_s, lx, MODE == MAT_GATEUP ? b - KB : b, lane, acc);
+        if (MODE == MAT_GATEUP && b < KB) core_item<NG, false>(tile_s, table_s, lx, b, lane, gacc);
+        else core_item<NG, false>(tile_s, table_s, lx, MODE == MAT_GATEUP ? b - KB : b, lane, acc);
         __syncwarp();
         issue_upto(s + 1 + ring.R);
         if (b == nbu - 1 || s == i1 - 1) {
@@ -497,6 +567,9 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
                     ps->b_lo = b_lo;
                     ps->b_hi = b + 1;
                     ps->job = j;
+                    ps->ntok = ntok;
+#pragma unroll
+                    for (int i = 0; i < 4 * NG; ++i) ps->orow[i] = orow[i];
                 }
                 if ((lane & 3) < 2) {
                     const int l16 = (lane >> 2) * 2 + (lane & 3);
@@ -526,8 +599,8 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
 }
 
 // after the block barrier: the warp that holds a unit's first piece adds the later warps' pieces and writes the unit
-template <int NG, int MODE, typename LaneXFn>
-__device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* pieces, int warp, int nwarp, int lane, LaneXFn&& lane_x) {
+template <int NG, int MODE>
+__device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* pieces, int warp, int nwarp, int lane) {
     const PieceSlot* first = pieces + warp * 2 + 1;
     const int u = first->unit;
     if (u < 0) return;
@@ -556,11 +629,10 @@ __device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* p
                 }
         if (c->b_hi == nbu) break;
     }
-    int ntok = 0;
     int orow[4 * NG];
-    LaneX<NG> lx;
-    lane_x(first->job, lx, ntok, orow);
-    mat_write_unit<NG, MODE>(m, u % upj, orow, ntok, lane, gacc, acc);
+#pragma unroll
+    for (int i = 0; i < 4 * NG; ++i) orow[i] = first->orow[i];
+    mat_write_unit<NG, MODE>(m, u % upj, orow, first->ntok, lane, gacc, acc);
 }
 
 }  // namespace fnxb
