@@ -8,8 +8,45 @@
 
 namespace fnxb {
 
-constexpr int RT_WARPS = 8, RT_TOK = 8, RT_MAXE = 1024;
+constexpr int RT_WARPS = 8, RT_TOK = 8, RT_MAXE = 1024, RT_SPLIT = 2, RT_ROWS = RT_WARPS / RT_SPLIT;
 
+// float -> unsigned key with the same order (so that warp-wide integer maxima rank logits)
+__device__ __forceinline__ unsigned rt_key(float v) {
+    const unsigned u = __float_as_uint(v);
+    return u & 0x80000000u ? ~u : u | 0x80000000u;
+}
+
+// Top K of one row's E logits by one warp: K rounds of (largest value, lowest index).  SL = slots per lane.
+template <int SL>
+__device__ __forceinline__ void rt_topk_row(const volatile float* l, int E, int K, int lane, int* topi_g, int* topi_s, float* topw_g) {
+    unsigned key[SL];
+#pragma unroll
+    for (int j = 0; j < SL; ++j) key[j] = lane + 32 * j < E ? rt_key(l[lane + 32 * j]) : 0u;
+    float top = 0.f, z = 0.f, mine = 0.f;
+    for (int k = 0; k < K; ++k) {
+        unsigned bk = 0u;
+        int bj = 0;
+#pragma unroll
+        for (int j = 0; j < SL; ++j)
+            if (key[j] > bk) { bk = key[j]; bj = j; }   // strict: the lowest slot (index) among equals
+        const unsigned wk = __reduce_max_sync(0xffffffffu, bk);
+        const int bi = __reduce_min_sync(0xffffffffu, bk == wk ? lane + 32 * bj : 0x7fffffff);
+        const unsigned u = wk & 0x80000000u ? wk & 0x7fffffffu : ~wk;
+        const float bv = __uint_as_float(u);
+        if (k == 0) top = bv;
+        const float w = expf(bv - top);
+        z += w;
+        if (lane == k) mine = w;
+        if (lane == 0) { topi_g[k] = bi; topi_s[k] = bi; }
+#pragma unroll
+        for (int j = 0; j < SL; ++j)
+            if (lane + 32 * j == bi) key[j] = 0u;
+    }
+    if (lane < K) topw_g[lane] = mine / z;
+}
+
+// Grid: ceil((E + 1) / RT_ROWS) blocks of RT_WARPS warps; a block computes RT_ROWS logit rows, RT_SPLIT warps per row
+// (each a contiguous share of the columns, summed in share order).
 __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restrict__ Wr, const float* __restrict__ x,
                                                           const float* __restrict__ norm_w, float eps, int T, int E, int H, int K,
                                                           int e_lo, int e_hi, int add_shared, float* __restrict__ logits,
@@ -18,64 +55,79 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(16) float xs[];   // [RT_TOK][H]: x * norm_w (the row's 1 / rms is applied to the sums)
-    __shared__ float rs[RT_TOK], ssw[RT_TOK][RT_WARPS];
+    __shared__ float rs[RT_TOK], ssw[RT_TOK][RT_WARPS], psum[RT_ROWS][RT_SPLIT][RT_TOK];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row = blockIdx.x * RT_WARPS + warp;
+    const int row = blockIdx.x * RT_ROWS + warp / RT_SPLIT, share = warp % RT_SPLIT;
     constexpr int NT = RT_WARPS * 32;
+    const int HS = H / RT_SPLIT, c_lo = share * HS;   // this warp's columns
+    // the warp's first weights are on their way before anything else (they depend on nothing)
+    float4 w[8];
+    if (row <= E) {
+        const float* wr = Wr + (size_t) row * H + c_lo;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = lane * 4 + j * 128;
+            w[j] = i < HS ? *reinterpret_cast<const float4*>(wr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     for (int t0 = 0; t0 < T; t0 += RT_TOK) {
         const int nt = min(RT_TOK, T - t0);
         __syncthreads();
-        // stage the rows: every thread issues its loads of a row together (H / 512 <= 8 float4 each)
-        for (int t = 0; t < nt; ++t) {
-            const float* xr = x + (size_t) (t0 + t) * H;
-            float4 v[8];
+        // stage the rows: a thread's loads of every row are issued together, two rows at a time
+        for (int tp = 0; tp < nt; tp += 2) {
+            float4 v[2][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = tid * 4 + j * NT * 4;
-                v[j] = c < H ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-            float ss = 0.f;
+            for (int r = 0; r < 2; ++r)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = tid * 4 + j * NT * 4;
-                if (c >= H) continue;
-                ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
-                if (norm_w) {
-                    const float4 w = *reinterpret_cast<const float4*>(norm_w + c);
-                    v[j].x *= w.x; v[j].y *= w.y; v[j].z *= w.z; v[j].w *= w.w;
+                for (int j = 0; j < 4; ++j) {
+                    const int c = tid * 4 + j * NT * 4;
+                    v[r][j] = tp + r < nt && c < H ? *reinterpret_cast<const float4*>(x + (size_t) (t0 + tp + r) * H + c) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v[j];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = tid * 4 + j * NT * 4;
+                    if (c >= H || tp + r >= nt) continue;
+                    ss += v[r][j].x * v[r][j].x + v[r][j].y * v[r][j].y + v[r][j].z * v[r][j].z + v[r][j].w * v[r][j].w;
+                    if (norm_w) {
+                        const float4 nw = *reinterpret_cast<const float4*>(norm_w + c);
+                        v[r][j].x *= nw.x; v[r][j].y *= nw.y; v[r][j].z *= nw.z; v[r][j].w *= nw.w;
+                    }
+                    *reinterpret_cast<float4*>(xs + (size_t) (tp + r) * H + c) = v[r][j];
+                }
+                ss = warp_sum(ss);
+                if (lane == 0 && tp + r < nt) ssw[tp + r][warp] = ss;
             }
-            ss = warp_sum(ss);
-            if (lane == 0) ssw[t][warp] = ss;
         }
         __syncthreads();
         if (tid < nt) {
             float ss = 0.f;
-            for (int w = 0; w < RT_WARPS; ++w) ss += ssw[tid][w];
+            for (int wq = 0; wq < RT_WARPS; ++wq) ss += ssw[tid][wq];
             rs[tid] = norm_w ? rsqrtf(ss / (float) H + eps) : 1.0f;
         }
-        __syncthreads();
+        float acc[RT_TOK];
+#pragma unroll
+        for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
         if (row <= E) {
-            float acc[RT_TOK];
+            const float* wr = Wr + (size_t) row * H + c_lo;
+            for (int i0 = 0; i0 < HS; i0 += 1024) {   // 8 float4 of the weight row in flight per lane
+                if (i0 > 0 || t0 > 0) {
 #pragma unroll
-            for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
-            const float* wr = Wr + (size_t) row * H;
-            for (int i0 = 0; i0 < H; i0 += 1024) {   // 8 float4 of the weight row in flight per lane
-                float4 w[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = i0 + lane * 4 + j * 128;
-                    w[j] = i < H ? *reinterpret_cast<const float4*>(wr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j = 0; j < 8; ++j) {
+                        const int i = i0 + lane * 4 + j * 128;
+                        w[j] = i < HS ? *reinterpret_cast<const float4*>(wr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int i = i0 + lane * 4 + j * 128;
-                    if (i >= H) continue;
+                    if (i >= HS) continue;
 #pragma unroll
                     for (int t = 0; t < RT_TOK; ++t)
                         if (t < nt) {
-                            const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + i);
+                            const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + c_lo + i);
                             acc[t] = fmaf(w[j].x, v.x, acc[t]);
                             acc[t] = fmaf(w[j].y, v.y, acc[t]);
                             acc[t] = fmaf(w[j].z, v.z, acc[t]);
@@ -86,52 +138,45 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
 #pragma unroll
             for (int t = 0; t < RT_TOK; ++t)
                 if (t < nt) {
-                    const float s = warp_sum(acc[t]) * rs[t];
-                    if (lane == 0) {
-                        logits[(size_t) (t0 + t) * (E + 1) + row] = s;
-                        if (!isfinite(s)) atomicOr(err, (unsigned) FNX_ERR_NONFINITE);
-                    }
+                    const float s = warp_sum(acc[t]);
+                    if (lane == 0) psum[warp / RT_SPLIT][share][t] = s;
                 }
+        }
+        __syncthreads();
+        if (tid < RT_ROWS * RT_TOK) {
+            const int r = tid / RT_TOK, t = tid % RT_TOK, grow = blockIdx.x * RT_ROWS + r;
+            if (t < nt && grow <= E) {
+                float s = 0.f;
+#pragma unroll
+                for (int q = 0; q < RT_SPLIT; ++q) s += psum[r][q][t];
+                s *= rs[t];
+                logits[(size_t) (t0 + t) * (E + 1) + grow] = s;
+                if (!isfinite(s)) atomicOr(err, (unsigned) FNX_ERR_NONFINITE);
+            }
         }
     }
     // ---- the last block to get here routes
     __shared__ bool last;
     __shared__ int s_topi[FNX_MAX_ROWS * 32];
+    __shared__ int s_cnt[RT_MAXE];
     __threadfence();
     __syncthreads();
     if (tid == 0) last = atomicAdd(&njobs[1], 1) == (int) gridDim.x - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
-    // top K per row: a warp per row, 10 rounds of (value, index) maximum, ties to the lower index
+    for (int e = tid; e < RT_MAXE; e += NT) s_cnt[e] = 0;
+    // top K per row: a warp per row, K rounds of (value, index) maximum, ties to the lower index
     for (int t = warp; t < T; t += RT_WARPS) {
         const volatile float* l = logits + (size_t) t * (E + 1);
-        float v[RT_MAXE / 32];
-#pragma unroll
-        for (int j = 0; j < RT_MAXE / 32; ++j) v[j] = lane + 32 * j < E ? l[lane + 32 * j] : -INFINITY;
-        float top = 0.f, z = 0.f, mine = 0.f;
-        for (int k = 0; k < K; ++k) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < RT_MAXE / 32; ++j)
-                if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
-#pragma unroll
-            for (int o = 16; o; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-            }
-            if (k == 0) top = bv;
-            const float w = expf(bv - top);
-            z += w;
-            if (lane == k) mine = w;
-            if (lane == 0) { topi[t * K + k] = bi; s_topi[t * K + k] = bi; }
-#pragma unroll
-            for (int j = 0; j < RT_MAXE / 32; ++j)
-                if (lane + 32 * j == bi) v[j] = -INFINITY;
-        }
-        if (lane < K) topw[t * K + lane] = mine / z;
+        if (E <= 512) rt_topk_row<16>(l, E, K, lane, topi + t * K, s_topi + t * K, topw + t * K);
+        else rt_topk_row<RT_MAXE / 32>(l, E, K, lane, topi + t * K, s_topi + t * K, topw + t * K);
+    }
+    __syncthreads();
+    // how many rows picked each expert of this rank
+    for (int i = tid; i < T * K; i += NT) {
+        const int e = s_topi[i];
+        if (e >= e_lo && e < e_hi) atomicAdd(&s_cnt[e], 1);
     }
     __syncthreads();
     // jobs in ascending expert order: expert e's rows in row order, 4 per job; then the shared expert's.
@@ -143,10 +188,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
         const int e = tid * EPT + j;
-        int c = 0;
-        if (e < E && e >= e_lo && e < e_hi)
-            for (int i = 0; i < T * K; ++i) c += s_topi[i] == e;
-        cnt_[j] = (c + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+        cnt_[j] = (s_cnt[e] + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
         mine += cnt_[j];
     }
     int incl = mine;
@@ -239,7 +281,7 @@ extern "C" int fnx_router_route(const float* Wr, const float* x, const float* no
     FNX_REQUIRE(Wr && x && logits && topi && topw && jobs && njobs && err, "fnx_router_route: null pointer");
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_router_route: %d rows (1..%d)", T, FNX_MAX_ROWS);
     FNX_REQUIRE(E >= K && E <= RT_MAXE && K >= 1 && K <= 32, "fnx_router_route: %d experts, top %d not supported", E, K);
-    FNX_REQUIRE(H % 128 == 0 && H <= 4096, "fnx_router_route: hidden %d not supported", H);
+    FNX_REQUIRE(H % 256 == 0 && H <= 4096, "fnx_router_route: hidden %d not supported", H);
     FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E, "fnx_router_route: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
     const size_t smem = (size_t) RT_TOK * H * sizeof(float);
     static bool configured = false;
@@ -247,7 +289,7 @@ extern "C" int fnx_router_route(const float* Wr, const float* x, const float* no
         FNX_CUDA_OK(cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         configured = true;
     }
-    const int blocks = (E + 1 + RT_WARPS - 1) / RT_WARPS;
+    const int blocks = (E + 1 + RT_ROWS - 1) / RT_ROWS;
     {
         const cudaError_t le_ = launch_k(k_router, dim3(blocks), dim3(RT_WARPS * 32), smem, as_stream(st), Wr, x, norm_w, eps, T, E, H, K, e_lo, e_hi, add_shared, logits, topi, topw, jobs,
                                                             njobs, stats, err);
