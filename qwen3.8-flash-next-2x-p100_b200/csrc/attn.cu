@@ -147,33 +147,49 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
             }
         }
         __syncthreads();
-        // scores: warp w takes queries w, w + 8, ...; lane = position
-        for (int qi = warp; qi < NQ; qi += ATT_THREADS / 32) {
-            const float* q = qs + qi * hd;
+        // scores: warp w takes queries w, w + 8, ... together (one read of the K row feeds all of them); lane = position
+        {
+            constexpr int NWQ = ATT_THREADS / 32, QPW = (ATT_ROWS * ATT_MAXQ + NWQ - 1) / NWQ;
             const __half* kr = Ks + lane * KS;
-            float sacc = 0.f;
+            float sacc[QPW];
+#pragma unroll
+            for (int j = 0; j < QPW; ++j) sacc[j] = 0.f;
             for (int d = 0; d < hd; d += 8) {
                 const uint4 kk = *reinterpret_cast<const uint4*>(kr + d);
-                const float4 q0 = *reinterpret_cast<const float4*>(q + d), q1 = *reinterpret_cast<const float4*>(q + d + 4);
                 const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk.x));
                 const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
                 const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk.z));
                 const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk.w));
-                sacc = fmaf(q0.x, k0.x, sacc); sacc = fmaf(q0.y, k0.y, sacc);
-                sacc = fmaf(q0.z, k1.x, sacc); sacc = fmaf(q0.w, k1.y, sacc);
-                sacc = fmaf(q1.x, k2.x, sacc); sacc = fmaf(q1.y, k2.y, sacc);
-                sacc = fmaf(q1.z, k3.x, sacc); sacc = fmaf(q1.w, k3.y, sacc);
+#pragma unroll
+                for (int j = 0; j < QPW; ++j) {
+                    const int qi = warp + j * NWQ;
+                    if (qi < NQ) {
+                        const float* q = qs + qi * hd + d;
+                        const float4 q0 = *reinterpret_cast<const float4*>(q), q1 = *reinterpret_cast<const float4*>(q + 4);
+                        float a = sacc[j];
+                        a = fmaf(q0.x, k0.x, a); a = fmaf(q0.y, k0.y, a);
+                        a = fmaf(q0.z, k1.x, a); a = fmaf(q0.w, k1.y, a);
+                        a = fmaf(q1.x, k2.x, a); a = fmaf(q1.y, k2.y, a);
+                        a = fmaf(q1.z, k3.x, a); a = fmaf(q1.w, k3.y, a);
+                        sacc[j] = a;
+                    }
+                }
             }
-            const int p = p0 + lane, r = qi / qpk;
-            const bool vis = lane < np && (p < pos0 || ((see[r] >> (p - pos0)) & 1u));
-            const float sv = vis ? sacc * scale : -INFINITY;
-            const float mo = ms[qi], mn = fmaxf(mo, warp_max(sv));
-            const float w = sv == -INFINITY ? 0.f : expf(sv - mn);
-            const float f = mo == -INFINITY ? 0.f : expf(mo - mn);
-            const float zn = zs[qi] * f + warp_sum(w);
-            es[qi * ATT_CH + lane] = w;
-            __syncwarp();
-            if (lane == 0) { ms[qi] = mn; zs[qi] = zn; fs[qi] = f; }
+#pragma unroll
+            for (int j = 0; j < QPW; ++j) {
+                const int qi = warp + j * NWQ;
+                if (qi >= NQ) continue;
+                const int p = p0 + lane, r = qi / qpk;
+                const bool vis = lane < np && (p < pos0 || ((see[r] >> (p - pos0)) & 1u));
+                const float sv = vis ? sacc[j] * scale : -INFINITY;
+                const float mo = ms[qi], mn = fmaxf(mo, warp_max(sv));
+                const float w = sv == -INFINITY ? 0.f : expf(sv - mn);
+                const float f = mo == -INFINITY ? 0.f : expf(mo - mn);
+                const float zn = zs[qi] * f + warp_sum(w);
+                es[qi * ATT_CH + lane] = w;
+                __syncwarp();
+                if (lane == 0) { ms[qi] = mn; zs[qi] = zn; fs[qi] = f; }
+            }
         }
         __syncthreads();
         // values: thread = dimension (hd == ATT_THREADS), all queries
@@ -213,38 +229,56 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
 }
 
 // merge the splits of (row, head): out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) z_s * sigmoid(gate)
-__global__ void k_attn_combine(const float* __restrict__ acc_in, const AttPartial* __restrict__ mz_in, const float* __restrict__ qg, int ldq,
-                               float* __restrict__ out, int nq, int hd, int S) {
+constexpr int ATC_G = 4;   // groups of hd threads that share the splits of one (row, head)
+
+__global__ void __launch_bounds__(ATT_THREADS * ATC_G) k_attn_combine(const float* __restrict__ acc_in, const AttPartial* __restrict__ mz_in,
+                                                                      const float* __restrict__ qg, int ldq, float* __restrict__ out, int nq, int hd,
+                                                                      int S) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float sm_m[256], sm_w[256];
-    const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
+    __shared__ float sm_m[256], sm_w[256], sm_z[256], sm_p[ATC_G][ATT_THREADS];
+    const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x % ATT_THREADS, g = threadIdx.x / ATT_THREADS;
     const size_t base = ((size_t) t * nq + h) * S;
     AttPartial p = AttPartial{-INFINITY, 0.f};
-    if (i < S) p = mz_in[base + i];
-    sm_m[i] = i < S ? p.m : -INFINITY;
+    if (g == 0) {
+        if (i < S) p = mz_in[base + i];
+        sm_m[i] = i < S ? p.m : -INFINITY;
+    }
     __syncthreads();
-    // block maximum of m (S <= 256 = blockDim)
+    // block maximum of m (S <= 256)
     float mx = -INFINITY;
     for (int s = 0; s < S; ++s) mx = fmaxf(mx, sm_m[s]);
-    sm_w[i] = i < S && p.m != -INFINITY ? expf(p.m - mx) : 0.f;
+    if (g == 0) {
+        const float w = i < S && p.m != -INFINITY ? expf(p.m - mx) : 0.f;
+        sm_w[i] = w;
+        sm_z[i] = w * p.z;
+    }
     __syncthreads();
-    __shared__ float sm_z[256];
-    sm_z[i] = i < S ? sm_w[i] * p.z : 0.f;
-    __syncthreads();
-    float z = 0.f;
-    for (int s = 0; s < S; ++s) z += sm_z[s];        // fixed order: deterministic
-    // the live splits' sums, 8 loads in flight, added in split order
+    // group g adds the live splits g, g + G, ... in order (8 loads in flight); group 0 then adds the groups in order
     float acc = 0.f;
-    for (int s0 = 0; s0 < S; s0 += 8) {
+    for (int s0 = g; s0 < S; s0 += 8 * ATC_G) {
         float v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = s0 + j < S && sm_w[s0 + j] != 0.f ? acc_in[(base + s0 + j) * hd + i] : 0.f;
+        for (int j = 0; j < 8; ++j) {
+            const int sp = s0 + j * ATC_G;
+            v[j] = sp < S && sm_w[sp] != 0.f ? acc_in[(base + sp) * hd + i] : 0.f;
+        }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc = fmaf(s0 + j < S ? sm_w[s0 + j] : 0.f, v[j], acc);
+        for (int j = 0; j < 8; ++j) {
+            const int sp = s0 + j * ATC_G;
+            acc = fmaf(sp < S ? sm_w[sp] : 0.f, v[j], acc);
+        }
     }
+    sm_p[g][i] = acc;
+    __syncthreads();
+    if (g != 0) return;
+    float z = 0.f;
+    for (int s = 0; s < S; ++s) z += sm_z[s];        // fixed order: deterministic
+    float tot = sm_p[0][i];
+#pragma unroll
+    for (int k = 1; k < ATC_G; ++k) tot += sm_p[k][i];
     const float gate = qg[(size_t) t * ldq + (size_t) h * 2 * hd + hd + i];
-    out[((size_t) t * nq + h) * hd + i] = acc / z * sigmoidf_(gate);
+    out[((size_t) t * nq + h) * hd + i] = tot / z * sigmoidf_(gate);
 }
 
 static int attn_splits(int nkv) {
@@ -301,7 +335,7 @@ extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc
     }
     FNX_LAUNCH_OK("fnx_attn (partials)");
     {
-        const cudaError_t le_ = launch_k(k_attn_combine, dim3(dim3(nq, T)), dim3(hd), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
+        const cudaError_t le_ = launch_k(k_attn_combine, dim3(dim3(nq, T)), dim3(hd * ATC_G), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_attn (combine)");
@@ -365,7 +399,7 @@ extern "C" int fnx_attn_static(const float* qg, int ldq, const void* kc, const v
                               (const __half*) kc, (const __half*) vc, acc, mz, T, nq, nkv, hd, pos0, parent);
     if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_part: launch failed: %s", cudaGetErrorString(le));
     FNX_LAUNCH_OK("fnx_attn_static (partials)");
-    le = launch_k(k_attn_combine, dim3(nq, T), dim3(hd), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
+    le = launch_k(k_attn_combine, dim3(nq, T), dim3(hd * ATC_G), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
     if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le));
     FNX_LAUNCH_OK("fnx_attn_static (combine)");
     return FNX_OK;

@@ -43,6 +43,15 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     float* xin = red + 8 * T;                    // [T + 3][2 HS + QC] conv inputs
     int* anc = reinterpret_cast<int*>(xin + (size_t) (T + 3) * (2 * GDN_HS + GDN_QC));   // [T][3]
     const float* hin = hist_pool + (size_t) cur * hsz;
+    // the starting state of the warp's key rows is on its way before anything else: row 0's parent is the root
+    const int part = warp, col = qq * GDN_QC + lane;
+    const size_t soff = (size_t) lv * GDN_HS * GDN_HS + (size_t) part * 32 * GDN_HS + col;
+    float s[32];
+    {
+        const float* src = S_pool + (size_t) cur * ssz + soff;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) s[r] = src[(size_t) r * GDN_HS];
+    }
     if (tid < T) {
         const float* abt = ab + (size_t) tid * ldab;
         const float x = abt[lv] + dt[lv];
@@ -55,10 +64,18 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     auto chan = [&](int e) {
         return e < GDN_HS ? kh * GDN_HS + e : e < 2 * GDN_HS ? nk * GDN_HS + kh * GDN_HS + (e - GDN_HS) : 2 * nk * GDN_HS + lv * GDN_HS + qq * GDN_QC + (e - 2 * GDN_HS);
     };
-    for (int i0 = tid; i0 < (T + 3) * NC; i0 += 4 * GDN_THREADS) {
-        float v[4];
+    constexpr int SB = 20;   // loads in flight per thread: a 5-row window's conv inputs in one round
+    // the conv weights of this thread's channels ride along
+    float4 cw3[3];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+    for (int k = 0; k < 3; ++k) {
+        const int e = tid + k * GDN_THREADS;
+        cw3[k] = e < NC ? *reinterpret_cast<const float4*>(convw + chan(e) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int i0 = tid; i0 < (T + 3) * NC; i0 += SB * GDN_THREADS) {
+        float v[SB];
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
             const int i = i0 + j * GDN_THREADS;
             v[j] = 0.f;
             if (i < (T + 3) * NC) {
@@ -67,7 +84,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
             }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < SB; ++j) {
             const int i = i0 + j * GDN_THREADS;
             if (i < (T + 3) * NC) xin[i] = v[j];
         }
@@ -82,10 +99,13 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
         }
     }
     __syncthreads();
-    for (int e = tid; e < NC; e += GDN_THREADS) {
+#pragma unroll
+    for (int k3 = 0; k3 < 3; ++k3) {
+        const int e = tid + k3 * GDN_THREADS;
+        if (e >= NC) continue;
         const int part = e < GDN_HS ? 0 : e < 2 * GDN_HS ? 1 : 2, i = part < 2 ? e - part * GDN_HS : e - 2 * GDN_HS;
         const int c = chan(e);
-        const float4 cw = *reinterpret_cast<const float4*>(convw + c * 4);
+        const float4 cw = cw3[k3];
         const float w0 = cw.x, w1 = cw.y, w2 = cw.z, w3 = cw.w;
         const bool writes = part == 2 || (lv < nk && qq == 0);   // one block per channel writes its history
         for (int t = 0; t < T; ++t) {
@@ -120,10 +140,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     }
     __syncthreads();
     // ---- the delta rule: warp `part` holds key rows [32 part, +32) of the block's QC value columns, lane = column
-    const int part = warp, col = qq * GDN_QC + lane;
-    const size_t soff = (size_t) lv * GDN_HS * GDN_HS + (size_t) part * 32 * GDN_HS + col;
-    float s[32];
-    int have = -2;   // the row whose result the registers hold (-1: the starting state)
+    int have = -1;   // the row whose result the registers hold (-1: the starting state)
     const float scale = rsqrtf((float) GDN_HS);
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
