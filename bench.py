@@ -36,6 +36,9 @@ sys.path.insert(0, str(ROOT / "tests"))
 METRIC = "decode tok/s (MTP+lookup spec verify), verify-step us, % of HBM roofline"
 CTX, K_DRAFT, P_BAD = 4096, 4, 0.28
 E_B = 1351680          # bytes of one expert: (2*512*2048 + 2048*512) * 110 / 256
+# DRAM bytes per expert job of the gate|up launch, from an ncu capture of one launch (dram__bytes_read.sum +
+# dram__bytes_write.sum = 42.02 MB for 46 jobs; the algorithmic figure is 901,120 bytes per job)
+NCU_TRAFFIC_PER_JOB = 42.02e6 / 46
 
 
 def peaks():
@@ -331,7 +334,8 @@ def main():
         bytes_per_launch = sum(njobs) / len(njobs) * gu_b
         ach = bytes_per_launch / per_launch_s / 1e9
         line["roofline"] = {"bound": "hbm", "kernel": "k_iq3s_mmv<1, gate|up>", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-                            "peak_kind": peak_kind, "traffic": None, "us_per_launch": per_launch_s * 1e6, "jobs_per_launch": sum(njobs) / len(njobs),
+                            "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_PER_JOB * sum(njobs) / len(njobs),
+                            "traffic_source": "ncu dram__bytes_read+write of one gate|up launch (46 jobs, 4-layer case): 42.02 MB, scaled by jobs per launch", "us_per_launch": per_launch_s * 1e6, "jobs_per_launch": sum(njobs) / len(njobs),
                             "algorithmic_bytes_per_launch": bytes_per_launch}
         # ---- CPU restatement on the host cores, bounded sample
         import oracle as O
