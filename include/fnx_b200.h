@@ -57,7 +57,7 @@ int fnx_fill_normal(float* out, size_t n, float sigma, uint64_t seed, uint32_t s
 /* ---------------------------------------------------------------------------------------------- dense GEMV
  * y[t][r] (+)= W[r] . xin[t] for t < T (T <= 8 per call), W an IQ3_S tile matrix; xin[t] = x[t], or
  * rmsnorm(x[t]) * norm_w when norm_w is not null.  Replaces q8s_gemv / mmvq / rms_norm_rows
- * (engine/src/kernels.hpp:49-52, 405-406).  rows % 32 == 0 (cols 2048), % 16 (cols 4096), % 128 (cols 512). */
+ * (engine/src/kernels.hpp:49-52, 405-406).  rows % 16 == 0; cols in {256, 512, 1024, 2048, 4096}. */
 int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps,
               float* y, int ldy, int accumulate, unsigned* err, fnx_stream st);
 
