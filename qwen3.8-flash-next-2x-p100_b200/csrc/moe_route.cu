@@ -4,6 +4,8 @@
 // and its simple form route / k_topk + k_jobs (engine/src/kernels.cu:338-398): one launch computes the router logits
 // (f32 weights, a warp per expert row, fixed summation order), and the last block to finish picks the top K per row,
 // renormalises their softmax and lists the jobs.  fnx_moe_combine replaces k_combine (engine/src/kernels.cu:412-419).
+#include <algorithm>
+
 #include "fnx_common.cuh"
 
 namespace fnxb {
@@ -24,11 +26,21 @@ __device__ __forceinline__ void rt_topk_row(const volatile float* l, int E, int 
     for (int j = 0; j < SL; ++j) key[j] = lane + 32 * j < E ? rt_key(l[lane + 32 * j]) : 0u;
     float top = 0.f, z = 0.f, mine = 0.f;
     for (int k = 0; k < K; ++k) {
-        unsigned bk = 0u;
-        int bj = 0;
+        // the lane's largest key and its slot by a pairwise tree (depth log2 SL; among equals the lower slot)
+        unsigned tk[SL];
+        int tj[SL];
 #pragma unroll
-        for (int j = 0; j < SL; ++j)
-            if (key[j] > bk) { bk = key[j]; bj = j; }   // strict: the lowest slot (index) among equals
+        for (int j = 0; j < SL; ++j) { tk[j] = key[j]; tj[j] = j; }
+#pragma unroll
+        for (int w = SL / 2; w >= 1; w >>= 1)
+#pragma unroll
+            for (int j = 0; j < w; ++j) {
+                const bool hi = tk[j + w] > tk[j];   // slots j < j + w: keep j on a tie
+                tk[j] = hi ? tk[j + w] : tk[j];
+                tj[j] = hi ? tj[j + w] : tj[j];
+            }
+        const unsigned bk = tk[0];
+        const int bj = tj[0];
         const unsigned wk = __reduce_max_sync(0xffffffffu, bk);
         const int bi = __reduce_min_sync(0xffffffffu, bk == wk ? lane + 32 * bj : 0x7fffffff);
         const unsigned u = wk & 0x80000000u ? wk & 0x7fffffffu : ~wk;
@@ -73,33 +85,32 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     for (int t0 = 0; t0 < T; t0 += RT_TOK) {
         const int nt = min(RT_TOK, T - t0);
         __syncthreads();
-        // stage the rows: a thread's loads of every row are issued together, two rows at a time
-        for (int tp = 0; tp < nt; tp += 2) {
-            float4 v[2][4];
+        // stage the rows with 16-byte async copies, all in flight at once; then, from shared memory, each thread's
+        // columns of every row: the sum of squares and the product with the norm weight
+        for (int i = tid; i < nt * (H / 4); i += NT)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + (size_t) i * 4)), "l"(x + (size_t) t0 * H + (size_t) i * 4) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        float4 nw4[4];
 #pragma unroll
-            for (int r = 0; r < 2; ++r)
+        for (int j = 0; j < 4; ++j) {
+            const int c = tid * 4 + j * NT * 4;
+            nw4[j] = norm_w && c < H ? *reinterpret_cast<const float4*>(norm_w + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            float ss = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c = tid * 4 + j * NT * 4;
-                    v[r][j] = tp + r < nt && c < H ? *reinterpret_cast<const float4*>(x + (size_t) (t0 + tp + r) * H + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                float ss = 0.f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c = tid * 4 + j * NT * 4;
-                    if (c >= H || tp + r >= nt) continue;
-                    ss += v[r][j].x * v[r][j].x + v[r][j].y * v[r][j].y + v[r][j].z * v[r][j].z + v[r][j].w * v[r][j].w;
-                    if (norm_w) {
-                        const float4 nw = *reinterpret_cast<const float4*>(norm_w + c);
-                        v[r][j].x *= nw.x; v[r][j].y *= nw.y; v[r][j].z *= nw.z; v[r][j].w *= nw.w;
-                    }
-                    *reinterpret_cast<float4*>(xs + (size_t) (tp + r) * H + c) = v[r][j];
-                }
-                ss = warp_sum(ss);
-                if (lane == 0 && tp + r < nt) ssw[tp + r][warp] = ss;
+            for (int j = 0; j < 4; ++j) {
+                const int c = tid * 4 + j * NT * 4;
+                if (c >= H) continue;
+                float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + c);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                v.x *= nw4[j].x; v.y *= nw4[j].y; v.z *= nw4[j].z; v.w *= nw4[j].w;
+                *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v;
             }
+            ss = warp_sum(ss);
+            if (lane == 0) ssw[t][warp] = ss;
         }
         __syncthreads();
         if (tid < nt) {
@@ -166,6 +177,10 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     if (!last) return;
     __threadfence();
     for (int e = tid; e < RT_MAXE; e += NT) s_cnt[e] = 0;
+    {   // the job list is built in the rows' shared memory (free by now): unused row slots stay zero
+        const int cap = (T * K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK) * (int) (sizeof(fnx_job) / 4);
+        for (int w = tid; w < cap; w += NT) reinterpret_cast<int*>(xs)[w] = 0;
+    }
     // top K per row: a warp per row, K rounds of (value, index) maximum, ties to the lower index
     for (int t = warp; t < T; t += RT_WARPS) {
         const volatile float* l = logits + (size_t) t * (E + 1);
@@ -180,10 +195,12 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     }
     __syncthreads();
     // jobs in ascending expert order: expert e's rows in row order, 4 per job; then the shared expert's.
-    // Thread `tid` owns experts [tid * EPT, (tid + 1) * EPT): counts, a block-wide exclusive scan, then the fill.
+    // Thread `tid` owns experts [tid * EPT, (tid + 1) * EPT): a block-wide exclusive scan of their job counts gives
+    // each expert's first job; then one thread per (row, pick) entry places itself, and the list is copied out.
     constexpr int NTH = RT_WARPS * 32, EPT = RT_MAXE / NTH;
     __shared__ int wsum_[RT_WARPS];
     __shared__ int routed_total;
+    __shared__ int s_base[RT_MAXE];
     int cnt_[EPT], mine = 0;
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
@@ -201,43 +218,49 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     __syncthreads();
     int base_ = incl - mine;
     for (int w = 0; w < warp; ++w) base_ += wsum_[w];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        s_base[tid * EPT + j] = base_;
+        base_ += cnt_[j];
+    }
     if (tid == NTH - 1) {
-        const int s = base_ + mine;
-        routed_total = s;
-        njobs[0] = s + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
+        routed_total = base_;
+        njobs[0] = base_ + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
         njobs[1] = 0;
         if (stats) {
-            atomicAdd(&stats[0], (unsigned long long) s);
+            atomicAdd(&stats[0], (unsigned long long) base_);
             atomicAdd(&stats[1], 1ull);
         }
     }
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        const int e = tid * EPT + j;
-        if (cnt_[j]) {
-            int n = 0;
-            fnx_job* jb = jobs + base_;
-            for (int i = 0; i < T * K; ++i)
-                if (s_topi[i] == e) {
-                    fnx_job& jj = jb[n / FNX_JOB_TOK];
-                    jj.w = e;
-                    jj.y[n % FNX_JOB_TOK] = i / K;
-                    jj.out[n % FNX_JOB_TOK] = i;
-                    jj.n = n % FNX_JOB_TOK + 1;
-                    ++n;
-                }
-            base_ += cnt_[j];
+    __syncthreads();
+    fnx_job* js = reinterpret_cast<fnx_job*>(xs);
+    const int total = routed_total + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
+    for (int i = tid; i < T * K; i += NTH) {
+        const int e = s_topi[i];
+        if (e < e_lo || e >= e_hi) continue;
+        int rank = 0;   // entries of the same expert before this one (row order)
+        for (int i2 = 0; i2 < i; ++i2) rank += s_topi[i2] == e;
+        fnx_job& jj = js[s_base[e] + rank / FNX_JOB_TOK];
+        jj.y[rank % FNX_JOB_TOK] = i / K;
+        jj.out[rank % FNX_JOB_TOK] = i;
+        if (rank % FNX_JOB_TOK == 0) {
+            jj.w = e;
+            jj.n = min(FNX_JOB_TOK, s_cnt[e] - rank);
         }
     }
-    __syncthreads();
     if (add_shared)
-        for (int t = tid; t < T; t += RT_WARPS * 32) {
-            fnx_job& j = jobs[routed_total + t / FNX_JOB_TOK];
-            j.w = E;
+        for (int t = tid; t < T; t += NTH) {
+            fnx_job& j = js[routed_total + t / FNX_JOB_TOK];
             j.y[t % FNX_JOB_TOK] = t;
             j.out[t % FNX_JOB_TOK] = T * K + t;
-            if (t % FNX_JOB_TOK == FNX_JOB_TOK - 1 || t == T - 1) j.n = t % FNX_JOB_TOK + 1;
+            if (t % FNX_JOB_TOK == 0) {
+                j.w = E;
+                j.n = min(FNX_JOB_TOK, T - t);
+            }
         }
+    __syncthreads();
+    constexpr int JW = sizeof(fnx_job) / 4;
+    for (int w = tid; w < total * JW; w += NTH) reinterpret_cast<int*>(jobs)[w] = reinterpret_cast<const int*>(js)[w];
 }
 
 __global__ void k_combine(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
@@ -283,7 +306,8 @@ extern "C" int fnx_router_route(const float* Wr, const float* x, const float* no
     FNX_REQUIRE(E >= K && E <= RT_MAXE && K >= 1 && K <= 32, "fnx_router_route: %d experts, top %d not supported", E, K);
     FNX_REQUIRE(H % 256 == 0 && H <= 4096, "fnx_router_route: hidden %d not supported", H);
     FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E, "fnx_router_route: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
-    const size_t smem = (size_t) RT_TOK * H * sizeof(float);
+    const size_t jobs_cap = (size_t) T * K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+    const size_t smem = std::max((size_t) RT_TOK * H * sizeof(float), jobs_cap * sizeof(fnx_job));
     static bool configured = false;
     if (!configured) {
         FNX_CUDA_OK(cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
