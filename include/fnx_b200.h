@@ -101,6 +101,18 @@ int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, const void* 
 int fnx_moe_combine(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
                     int K, int e_lo, int e_hi, int add_shared, float* out, int accumulate, fnx_stream st);
 
+/* Prompt-sized MoE block (moe_gate_up_mma / moe_down_mma, engine/src/kernels.hpp:328-330, with the job build of
+ * engine/src/prefill.cu:288-377): out[t] (+)= the routed experts in [e_lo, e_hi) and (add_shared) the shared expert of
+ * rmsnorm(x[t]) * norm_w, for any number of rows T, given the routing (topi, topw [T][K], logits [T][E + 1]).  The
+ * (row, pick) pairs are grouped by expert into jobs of up to 128 rows whose products run on the tensor cores
+ * (tcgen05.mma, f16 operands decoded from IQ3_S, f32 accumulators in tensor memory).  Not capture-safe: it reads the job
+ * count back.  scratch: fnx_moe_prefill_scratch_bytes(T, K, E, H, F) bytes. */
+size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F);
+int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu,
+                    const void* Wsh_dn, int e_base, int E, int K, int e_lo, int e_hi, int add_shared, const int* topi,
+                    const float* topw, const float* logits, const float* x, const float* norm_w, float eps, int T, int H,
+                    int F, float* out, int accumulate, void* scratch, unsigned* err, fnx_stream st);
+
 /* ---------------------------------------------------------------------------------------------- attention
  * attn_prep_append (engine/src/kernels.hpp:259): per-head RMS norm, NEOX rotary on the first nrot dims at position
  * *pos0 + depth[t] (depth null: t), K and V rows stored as f16 at cache row *pos0 + t.

@@ -65,6 +65,8 @@ _PROTOS = {
     "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
     "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "fnx_moe_prefill_scratch_bytes": (_Z, [_I, _I, _I, _I, _I]),
+    "fnx_moe_prefill": (_I, [_P, _Z, _P, _Z, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _P, _I, _P, _P, _P]),
     "fnx_attn_prep_append": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P]),
     "fnx_attn_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
@@ -235,6 +237,34 @@ def moe_experts(Wgu, Wdn, Wsh_gu, Wsh_dn, route, x, F: int, K: int, norm_w=None,
     check(L.fnx_moe_combine(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, e_lo, e_hi,
                             1 if add_shared else 0, ptr(out), 0, _stream()))
     return out, h, part
+
+
+def route_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
+    """Routing of any number of rows (windows of MAX_ROWS through fnx_router_route): (topi, topw, logits)."""
+    import torch
+    T = x.shape[0]
+    parts = [router_route(Wr, x[t0:t0 + MAX_ROWS].contiguous(), K, norm_w=norm_w, eps=eps) for t0 in range(0, T, MAX_ROWS)]
+    return (torch.cat([p["topi"] for p in parts]).contiguous(), torch.cat([p["topw"] for p in parts]).contiguous(),
+            torch.cat([p["logits"] for p in parts]).contiguous())
+
+
+def moe_prefill(Wgu, Wdn, Wsh_gu, Wsh_dn, topi, topw, logits, x, F: int, norm_w=None, eps: float = 1e-6, e_base: int = 0, e_lo: int = 0,
+                e_hi=None, add_shared: bool = True, out=None, accumulate: bool = False, scratch=None, err=None):
+    """fnx_moe_prefill: the MoE block of T rows with token groups per expert on the tensor cores; returns out [T][H]."""
+    import torch
+    T, H = x.shape
+    K = topi.shape[1]
+    E = logits.shape[1] - 1
+    e_hi = E if e_hi is None else e_hi
+    if out is None:
+        out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    if scratch is None:
+        scratch = torch.empty(lib().fnx_moe_prefill_scratch_bytes(T, K, E, H, F), dtype=torch.uint8, device=x.device)
+    err = new_err(x.device) if err is None else err
+    check(lib().fnx_moe_prefill(ptr(Wgu), iq3s_bytes(2 * F, H), ptr(Wdn), iq3s_bytes(H, F), ptr(Wsh_gu), ptr(Wsh_dn), e_base, E, K, e_lo, e_hi,
+                                1 if add_shared else 0, ptr(topi), ptr(topw), ptr(logits), ptr(x), ptr(norm_w), eps, T, H, F, ptr(out),
+                                1 if accumulate else 0, ptr(scratch), ptr(err), _stream()))
+    return out, err
 
 
 def attn_prep_append(qg, k, v, q_norm, k_norm, kc, vc, pos0, depth=None, nrot: int = 64, eps: float = 1e-6, rope_base: float = 1e7):

@@ -1,0 +1,460 @@
+// Prefill-sized MoE block: token groups per expert through the 5th-generation tensor cores.
+//
+// Replaces the reference's grouped expert GEMMs for prompts, moe_gate_up_mma / moe_down_mma
+// (engine/src/kernels.hpp:328-330, engine/src/moe_mma.cuh:301) and their job build k_pf_*
+// (engine/src/prefill.cu:288-377): the (token, pick) pairs are grouped by expert into jobs of up to 128 rows, and each
+// job's product runs as tcgen05.mma (kind::f16, f32 accumulators in tensor memory):
+//   A = a 128-feature slab of the expert's IQ3_S matrix, decoded by the block's warps straight from the tile layout
+//       (iq3s_tile.h) into f16 in the K-major core-matrix layout the instruction's shared-memory descriptor names;
+//   B = the job's activation rows (gathered, RMS-normed, rounded to f16), same layout;
+//   D = [128 features (lanes)] x [128 rows (columns)] in tensor memory; gate|up keeps two of them and the epilogue
+//       applies SwiGLU while it reads them back (tcgen05.ld).
+// Two shared-memory stages: the warps decode K-chunk c + 1 while the tensor core works on chunk c; a stage is reused
+// when the tcgen05.commit of its chunk has arrived on the stage's mbarrier.  Every wait is bounded.
+#include <cuda_fp16.h>
+
+#include "fnx_common.cuh"
+#include "iq3s_grid.h"
+#include "iq3s_tile.h"
+
+namespace fnxb {
+
+constexpr int PF_M = 128;         // features per block (tensor-memory lanes)
+constexpr int PF_N = 128;         // rows per job (tensor-memory columns per accumulator)
+constexpr int PF_KC = 128;        // K per stage: half a 256-column IQ3_S block
+constexpr int PF_THREADS = 256;
+constexpr int PF_TILE = PF_M * PF_KC * 2;      // bytes of one f16 operand tile (128 x 128)
+constexpr int PF_LBO = 128;                    // bytes between core matrices (8 rows x 16 bytes) along K
+constexpr int PF_SBO = (PF_KC / 8) * 128;      // ... along the rows
+
+struct PfJob {
+    int w, n, start;   // expert, rows, first entry of `order`
+};
+
+__device__ static const uint32_t g_grid_pf[512] = {FNX_IQ3S_GRID_VALUES};
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ uint64_t pf_desc(uint32_t saddr) {
+    // shared-memory matrix descriptor: start address, leading (K) and stride (row-group) byte offsets in 16-byte units,
+    // descriptor version 1, no swizzle
+    return (uint64_t) ((saddr & 0x3FFFFu) >> 4) | ((uint64_t) (PF_LBO >> 4) << 16) | ((uint64_t) (PF_SBO >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void pf_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void pf_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pf_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void pf_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void pf_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// byte offset of element (row, k) of a 128 x 128 f16 operand tile in the core-matrix layout
+__device__ __forceinline__ uint32_t pf_off(int row, int k) { return (uint32_t) ((row >> 3) * PF_SBO + (k >> 3) * PF_LBO + (row & 7) * 16 + (k & 7) * 2); }
+
+// what a lane holds of one 16 x 256 tile block: the index streams and sign words of rows g and g + 8, their scales
+struct PfRaw {
+    uint32_t S0[5], S1[5], G0[2], G1[2];
+    uint32_t sn0, sn1;
+    float d0, d1;
+};
+__device__ __forceinline__ void pf_load_raw(const uint8_t* tile, int lane, PfRaw& r) {
+    const int g = lane >> 2;
+    const uint4 i0 = *reinterpret_cast<const uint4*>(tile + TILE_IDX + lane * 16), i1 = *reinterpret_cast<const uint4*>(tile + TILE_IDX + 512 + lane * 16);
+    const uint2 s0 = *reinterpret_cast<const uint2*>(tile + TILE_SGN + lane * 8), s1 = *reinterpret_cast<const uint2*>(tile + TILE_SGN + 256 + lane * 8);
+    r.S0[0] = i0.x; r.S0[1] = i0.y; r.S0[2] = i0.z; r.S0[3] = i0.w;
+    r.S1[0] = i1.x; r.S1[1] = i1.y; r.S1[2] = i1.z; r.S1[3] = i1.w;
+    r.S0[4] = *reinterpret_cast<const uint16_t*>(tile + TILE_TAIL + lane * 2);
+    r.S1[4] = *reinterpret_cast<const uint16_t*>(tile + TILE_TAIL + 64 + lane * 2);
+    r.G0[0] = s0.x; r.G0[1] = s0.y;
+    r.G1[0] = s1.x; r.G1[1] = s1.y;
+    r.sn0 = *reinterpret_cast<const uint32_t*>(tile + TILE_SCL + g * 4);
+    r.sn1 = *reinterpret_cast<const uint32_t*>(tile + TILE_SCL + (g + 8) * 4);
+    r.d0 = __half2float(*reinterpret_cast<const __half*>(tile + TILE_D + g * 2));
+    r.d1 = __half2float(*reinterpret_cast<const __half*>(tile + TILE_D + (g + 8) * 2));
+}
+
+// eight signed codebook bytes (two lookups) times the sub-block scale -> eight f16 at (row, k .. k + 7): one core-matrix row
+__device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32_t lo4, uint32_t hi4, float f) {
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t w4 = j < 2 ? lo4 : hi4;
+        const int sh = (j & 1) * 16;
+        const __half2 v = __floats2half2_rn((float) (int8_t) ((w4 >> sh) & 0xFF) * f, (float) (int8_t) ((w4 >> (sh + 8)) & 0xFF) * f);
+        h[j] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(tileA + pf_off(row, k)) = make_uint4(h[0], h[1], h[2], h[3]);
+}
+
+template <int I>
+__device__ __forceinline__ uint32_t pf_decode(const uint32_t (&S)[5], const uint32_t (&G)[2], uint32_t table_s) {
+    uint32_t mag;
+    const uint32_t a = table_s + (tile_field<I>(S) >> 5);   // the field is (index << 7): 4 bytes per entry
+    asm("ld.shared.u32 %0, [%1];" : "=r"(mag) : "r"(a));
+    return tile_apply_sign(mag, tile_sign_mask<I>(G));
+}
+
+// sub-block SB of the lane's two rows into the operand tile (tile rows row0 + g, row0 + g + 8; columns relative to the
+// chunk).  Lane q of a row holds the sub-block's columns 8 q .. 8 q + 7: lookup 2 SB the first four, 2 SB + 1 the others
+// (the tile layout pairs them with the activation cells of 8 consecutive columns, iq3s_tile.h).
+template <int SB>
+__device__ __forceinline__ void pf_sub_block(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
+    const int g = lane >> 2, q = lane & 3, k0 = (SB & 3) * 32 + 8 * q;
+    const float f0 = r.d0 * (float) (1 + 2 * (int) ((r.sn0 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u));
+    const float f1 = r.d1 * (float) (1 + 2 * (int) ((r.sn1 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u));
+    pf_store8(tileA, row0 + g, k0, pf_decode<2 * SB>(r.S0, r.G0, table_s), pf_decode<2 * SB + 1>(r.S0, r.G0, table_s), f0);
+    pf_store8(tileA, row0 + g + 8, k0, pf_decode<2 * SB>(r.S1, r.G1, table_s), pf_decode<2 * SB + 1>(r.S1, r.G1, table_s), f1);
+}
+template <int HALF>
+__device__ __forceinline__ void pf_half_block(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
+    pf_sub_block<4 * HALF + 0>(r, tileA, row0, lane, table_s);
+    pf_sub_block<4 * HALF + 1>(r, tileA, row0, lane, table_s);
+    pf_sub_block<4 * HALF + 2>(r, tileA, row0, lane, table_s);
+    pf_sub_block<4 * HALF + 3>(r, tileA, row0, lane, table_s);
+}
+
+struct PfParams {
+    const uint8_t* W;          // experts [e_base ..): gate|up [2 F][K] or down [H][K] tile matrices
+    size_t expert_stride;
+    int e_base, E;
+    const uint8_t* Wsh;        // the shared expert (job.w == E)
+    const PfJob* jobs;
+    const int* order;          // per job entry: the pair index t * Kp + k; shared jobs: T * Kp + t
+    int TKp;                   // T * Kp: entries at or past it are shared-expert rows
+    int Kp;
+    const float* x;            // activations: gate|up: [T][K] (row = token), down: [pairs][K] (row = pair)
+    const float* norm_w;       // gate|up: RMS-norm weight (with rstd), else null
+    const float* rstd;         // [T]
+    int rows, K;               // output features per expert matrix (gate|up: F; down: H), inner dimension
+    float* out;                // [pairs][rows]
+    unsigned* err;
+};
+
+// MODE 0: out = x W^T (down).  MODE 1: out = silu(x Wg^T) * (x Wu^T) (gate|up; W = [gate (rows); up (rows)]).
+template <int MODE>
+__global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NA = MODE == 1 ? 2 : 1;                      // weight tiles per stage
+    constexpr int STAGE = (NA + 1) * PF_TILE;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t* stage0 = smem;                                    // 2 stages: [A0 | (A1) | B]
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem + 2 * STAGE);          // the codebook, 2 KB
+    int* src_s = reinterpret_cast<int*>(table + 512);          // [PF_N] activation row per job row (-1: none)
+    int* out_s = src_s + PF_N;                                 // [PF_N] output row
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [2] stage free
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+    const PfJob job = p.jobs[blockIdx.x];
+    const int ft = blockIdx.y, KB = p.K / 256, nchunk = p.K / PF_KC;
+    const uint8_t* W = job.w >= p.E ? p.Wsh : p.W + (size_t) (job.w - p.e_base) * p.expert_stride;
+    for (int i = tid; i < 512; i += PF_THREADS) table[i] = g_grid_pf[i];
+    if (tid < PF_N) {
+        int src = -1, o = 0;
+        if (tid < job.n) {
+            const int pr = p.order[job.start + tid];
+            o = pr;
+            src = MODE == 1 ? (pr >= p.TKp ? pr - p.TKp : pr / p.Kp) : pr;
+        }
+        src_s[tid] = src;
+        out_s[tid] = o;
+    }
+    if (tid == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NA * PF_N) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    const uint32_t tmem = *tmem_slot, table_s = smem_u32(table);
+    // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
+    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (PF_N >> 3) << 17) | ((uint32_t) (PF_M >> 4) << 24);
+    bool ok = true;
+    PfRaw raw[NA];
+    // the warp's 16 weight rows of the slab: tile row ft * 8 + warp (gate), and the same row of the up half
+    const int trow = ft * (PF_M / 16) + warp;
+    for (int c = 0; c < nchunk && ok; ++c) {
+        const int s = c & 1, kb = c >> 1;
+        uint8_t* A0 = stage0 + (size_t) s * STAGE;
+        uint8_t* B = A0 + NA * PF_TILE;
+        if ((c & 1) == 0) {
+            pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, raw[0]);
+            if (NA == 2) pf_load_raw(W + ((size_t) (p.rows / 16 + trow) * KB + kb) * TILE_BYTES, lane, raw[NA - 1]);
+        }
+        // the activations of this chunk: thread = (row, half of the 128 columns); 16 float4 in two rounds of 8
+        const int brow = tid >> 1, bk0 = (tid & 1) * 64;
+        const int src = src_s[brow];
+        float4 xv[8];
+        if (c >= 2) {   // the stage is free when the tensor core has finished chunk c - 2
+            ok = __syncthreads_and(mbar_wait_bounded(&bars[s], (unsigned) (((c >> 1) - 1) & 1), 20000000u)) != 0;
+            pf_fence_after();
+            if (!ok) break;
+        }
+#pragma unroll
+        for (int round = 0; round < 2; ++round) {
+            const int kk = bk0 + round * 32;
+            const float* xr = src >= 0 ? p.x + (size_t) src * p.K + c * PF_KC + kk : nullptr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xv[j] = xr ? *reinterpret_cast<const float4*>(xr + j * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float rs = 1.0f;
+            if (MODE == 1 && p.norm_w && xr) {
+                rs = p.rstd[src];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 w = *reinterpret_cast<const float4*>(p.norm_w + c * PF_KC + kk + j * 4);
+                    xv[j].x *= w.x * rs; xv[j].y *= w.y * rs; xv[j].z *= w.z * rs; xv[j].w *= w.w * rs;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const __half2 h0 = __floats2half2_rn(xv[j].x, xv[j].y), h1 = __floats2half2_rn(xv[j].z, xv[j].w);
+                const __half2 h2 = __floats2half2_rn(xv[j + 1].x, xv[j + 1].y), h3 = __floats2half2_rn(xv[j + 1].z, xv[j + 1].w);
+                *reinterpret_cast<uint4*>(B + pf_off(brow, kk + j * 4)) =
+                    make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1), *reinterpret_cast<const uint32_t*>(&h2),
+                               *reinterpret_cast<const uint32_t*>(&h3));
+            }
+        }
+        // the weights of this chunk: four sub-blocks of the warp's tile(s)
+        if ((c & 1) == 0) {
+            pf_half_block<0>(raw[0], A0, warp * 16, lane, table_s);
+            if (NA == 2) pf_half_block<0>(raw[NA - 1], A0 + PF_TILE, warp * 16, lane, table_s);
+        } else {
+            pf_half_block<1>(raw[0], A0, warp * 16, lane, table_s);
+            if (NA == 2) pf_half_block<1>(raw[NA - 1], A0 + PF_TILE, warp * 16, lane, table_s);
+        }
+        fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
+        __syncthreads();
+        if (tid == 0) {
+            pf_fence_after();
+            const uint32_t a_s = smem_u32(A0), b_s = smem_u32(B);
+#pragma unroll
+            for (int k16 = 0; k16 < PF_KC / 16; ++k16) {
+                const uint64_t bd = pf_desc(b_s + k16 * 2 * PF_LBO);
+                pf_mma(tmem, pf_desc(a_s + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
+                if (NA == 2) pf_mma(tmem + PF_N, pf_desc(a_s + PF_TILE + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
+            }
+            pf_commit(&bars[s]);
+        }
+    }
+    // all chunks issued: the last commit arrives when every earlier product has finished too
+    if (ok) ok = __syncthreads_and(mbar_wait_bounded(&bars[(nchunk - 1) & 1], (unsigned) (((nchunk - 1) >> 1) & 1), 20000000u)) != 0;
+    pf_fence_after();
+    if (!ok && tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
+    if (ok) {
+        // warp w reads lanes 32 (w % 4) .. + 31 (its features), columns 64 (w / 4) .. + 63 (job rows), 32 at a time
+        const int f = ft * PF_M + 32 * (warp & 3) + lane;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+            const int col0 = (warp >> 2) * 64 + h * 32;
+            const uint32_t ta = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) col0;
+            float g[32];
+            pf_ld32(ta, g);
+            if (MODE == 1) {
+                float u[32];
+                pf_ld32(ta + PF_N, u);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (col0 + i < job.n) p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+        }
+    }
+    pf_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NA * PF_N) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ job build
+// per expert: how many pairs picked it
+__global__ void k_pf_count(const int* __restrict__ topi, int n, int e_lo, int* __restrict__ cnt) {
+    const int e = e_lo + blockIdx.x;
+    int c = 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) c += topi[i] == e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    __shared__ int ws[32];
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int w = 0; w < (int) blockDim.x / 32; ++w) s += ws[w];
+        cnt[blockIdx.x] = s;
+    }
+}
+
+// one block: the experts' first entries and jobs (ascending expert order, then the shared expert's)
+__global__ void k_pf_plan(const int* __restrict__ cnt, int ne, int e_lo, int E, int T, int TKp, int add_shared, int* __restrict__ base, PfJob* __restrict__ jobs,
+                          int* __restrict__ njobs, int* __restrict__ order) {
+    __shared__ int s_entry, s_job;
+    if (threadIdx.x == 0) {
+        int entry = 0, nj = 0;
+        for (int e = 0; e < ne; ++e) {
+            base[e] = entry;
+            for (int o = 0; o < cnt[e]; o += PF_N) jobs[nj++] = PfJob{e_lo + e, min(PF_N, cnt[e] - o), entry + o};
+            entry += cnt[e];
+        }
+        s_entry = entry;
+        s_job = nj;
+    }
+    __syncthreads();
+    const int entry = s_entry, nj = s_job;
+    if (add_shared) {
+        for (int t = threadIdx.x; t < T; t += blockDim.x) order[entry + t] = TKp + t;
+        for (int j = threadIdx.x; j < (T + PF_N - 1) / PF_N; j += blockDim.x) jobs[nj + j] = PfJob{E, min(PF_N, T - j * PF_N), entry + j * PF_N};
+    }
+    if (threadIdx.x == 0) njobs[0] = nj + (add_shared ? (T + PF_N - 1) / PF_N : 0);
+}
+
+// per expert: its pairs in ascending order into order[base ..)
+__global__ void k_pf_fill(const int* __restrict__ topi, int n, int e_lo, const int* __restrict__ base, int* __restrict__ order) {
+    const int e = e_lo + blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x / 32;
+    __shared__ int ws[32], s_run;
+    if (tid == 0) s_run = base[blockIdx.x];
+    __syncthreads();
+    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+        const int i = i0 + tid;
+        const bool m = i < n && topi[i] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, m);
+        if (lane == 0) ws[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < nw; ++w) {
+            if (w < warp) before += ws[w];
+            total += ws[w];
+        }
+        const int run = s_run;
+        if (m) order[run + before + __popc(bal & ((1u << lane) - 1u))] = i;
+        __syncthreads();
+        if (tid == 0) s_run = run + total;
+        __syncthreads();
+    }
+}
+
+__global__ void k_pf_rstd(const float* __restrict__ x, int H, float eps, float* __restrict__ rstd) {
+    const float* xr = x + (size_t) blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    __shared__ float ws[32];
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int w = 0; w < (int) blockDim.x / 32; ++w) s += ws[w];
+        rstd[blockIdx.x] = rsqrtf(s / (float) H + eps);
+    }
+}
+
+// out[t] (+)= sum_k topw[t][k] part[t Kp + k] + sigmoid(logit[t][E]) part[T Kp + t]
+__global__ void k_pf_combine(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw, const float* __restrict__ logits,
+                             int T, int E, int H, int Kp, int e_lo, int e_hi, int add_shared, float* __restrict__ out, int accumulate) {
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    float s = 0.f;
+    for (int k = 0; k < Kp; ++k) {
+        const int e = topi[t * Kp + k];
+        if (e >= e_lo && e < e_hi) s = fmaf(topw[t * Kp + k], part[((size_t) t * Kp + k) * H + i], s);
+    }
+    if (add_shared) s += sigmoidf_(logits[(size_t) t * (E + 1) + E]) * part[((size_t) T * Kp + t) * H + i];
+    float* o = out + (size_t) t * H + i;
+    *o = accumulate ? *o + s : s;
+}
+
+constexpr size_t pf_smem(int mode) { return (size_t) 2 * ((mode == 1 ? 2 : 1) + 1) * PF_TILE + 2048 + 2 * PF_N * sizeof(int) + 64; }
+
+}  // namespace fnxb
+
+using namespace fnxb;
+
+static size_t pf_align(size_t v) { return (v + 255) & ~(size_t) 255; }
+
+extern "C" size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F) {
+    const size_t pairs = (size_t) T * K + T;
+    return pf_align(pairs * F * sizeof(float)) + pf_align(pairs * H * sizeof(float)) + pf_align(pairs * sizeof(int)) + pf_align((size_t) (E + 1) * sizeof(int)) * 2 +
+           pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob)) + pf_align((size_t) T * sizeof(float)) + 256;
+}
+
+extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu, const void* Wsh_dn, int e_base,
+                               int E, int K, int e_lo, int e_hi, int add_shared, const int* topi, const float* topw, const float* logits, const float* x,
+                               const float* norm_w, float eps, int T, int H, int F, float* out, int accumulate, void* scratch, unsigned* err, fnx_stream st_) {
+    FNX_REQUIRE(Wgu && Wdn && topi && topw && logits && x && out && scratch && err, "fnx_moe_prefill: null pointer");
+    FNX_REQUIRE(T >= 1 && K >= 1 && K <= 32, "fnx_moe_prefill: %d rows, top %d", T, K);
+    FNX_REQUIRE(H % 256 == 0 && F % 256 == 0 && F % PF_M == 0 && H % PF_M == 0, "fnx_moe_prefill: hidden %d, ffn %d (multiples of 256)", H, F);
+    FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E && (!add_shared || (Wsh_gu && Wsh_dn)), "fnx_moe_prefill: expert range [%d, %d) of %d", e_lo, e_hi, E);
+    FNX_REQUIRE((long long) T * K + T < (1ll << 30), "fnx_moe_prefill: %d rows are too many", T);
+    cudaStream_t st = as_stream(st_);
+    const size_t pairs = (size_t) T * K + T;
+    uint8_t* b = (uint8_t*) scratch;
+    float* hbuf = (float*) b; b += pf_align(pairs * F * sizeof(float));
+    float* part = (float*) b; b += pf_align(pairs * H * sizeof(float));
+    int* order = (int*) b; b += pf_align(pairs * sizeof(int));
+    int* cnt = (int*) b; b += pf_align((size_t) (E + 1) * sizeof(int));
+    int* base = (int*) b; b += pf_align((size_t) (E + 1) * sizeof(int));
+    PfJob* jobs = (PfJob*) b; b += pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob));
+    float* rstd = (float*) b; b += pf_align((size_t) T * sizeof(float));
+    int* njobs = (int*) b;
+    const int ne = e_hi - e_lo, n = T * K;
+    if (ne > 0) {
+        k_pf_count<<<ne, 256, 0, st>>>(topi, n, e_lo, cnt);
+        FNX_LAUNCH_OK("k_pf_count");
+    }
+    k_pf_plan<<<1, 256, 0, st>>>(cnt, ne, e_lo, E, T, n, add_shared, base, jobs, njobs, order);
+    FNX_LAUNCH_OK("k_pf_plan");
+    if (ne > 0) {
+        k_pf_fill<<<ne, 256, 0, st>>>(topi, n, e_lo, base, order);
+        FNX_LAUNCH_OK("k_pf_fill");
+    }
+    k_pf_rstd<<<T, 256, 0, st>>>(x, H, eps, rstd);
+    FNX_LAUNCH_OK("k_pf_rstd");
+    static bool configured = false;
+    if (!configured) {
+        FNX_CUDA_OK(cudaFuncSetAttribute(k_pf_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) pf_smem(0)));
+        FNX_CUDA_OK(cudaFuncSetAttribute(k_pf_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) pf_smem(1)));
+        configured = true;
+    }
+    // the job count is known on the device only: read it back (prefill is not captured into a graph)
+    int nj = 0;
+    FNX_CUDA_OK(cudaMemcpyAsync(&nj, njobs, sizeof(int), cudaMemcpyDeviceToHost, st));
+    FNX_CUDA_OK(cudaStreamSynchronize(st));
+    if (nj > 0) {
+        PfParams p{};
+        p.W = (const uint8_t*) Wgu; p.expert_stride = gu_stride; p.e_base = e_base; p.E = E; p.Wsh = (const uint8_t*) Wsh_gu;
+        p.jobs = jobs; p.order = order; p.TKp = n; p.Kp = K; p.x = x; p.norm_w = norm_w; p.rstd = rstd; p.rows = F; p.K = H; p.out = hbuf; p.err = err;
+        k_pf_gemm<1><<<dim3(nj, F / PF_M), PF_THREADS, pf_smem(1), st>>>(p);
+        FNX_LAUNCH_OK("k_pf_gemm (gate|up)");
+        p.W = (const uint8_t*) Wdn; p.expert_stride = dn_stride; p.Wsh = (const uint8_t*) Wsh_dn;
+        p.x = hbuf; p.norm_w = nullptr; p.rows = H; p.K = F; p.out = part;
+        k_pf_gemm<0><<<dim3(nj, H / PF_M), PF_THREADS, pf_smem(0), st>>>(p);
+        FNX_LAUNCH_OK("k_pf_gemm (down)");
+    }
+    k_pf_combine<<<dim3((H + 255) / 256, T), 256, 0, st>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
+    FNX_LAUNCH_OK("k_pf_combine");
+    return FNX_OK;
+}

@@ -184,6 +184,28 @@ def test_router_many_tokens_pick_one_expert(F, O):
     assert int(route["njobs"][0].item()) == K * 3 + 3
 
 
+@pytest.mark.parametrize("E,H,Fn,K,T", [(16, 512, 256, 4, 200), (32, 2048, 512, 10, 333)])
+def test_prefill_moe_on_tensor_cores_matches_oracle(F, O, E, H, Fn, K, T):
+    """Token groups per expert through tcgen05.mma (f16 operands, f32 accumulate): jobs of 128 rows and ragged tails,
+    experts nobody picked, the shared expert over all rows."""
+    fx = _moe_fixture(F, E, H, Fn, seed=23)
+    rng = np.random.default_rng(E + T)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    nw = (1.0 + 0.05 * rng.standard_normal(H)).astype(np.float32)
+    xn = O.rmsnorm(x, nw, 1e-6)
+    ref_out, _, ref_topi, _ = O.moe(fx["wr"].cpu().numpy(), fx["gu_g"], fx["dn_g"], fx["sh_gu_g"], fx["sh_dn_g"], xn, Fn, K)
+    topi, topw, logits = F.route_rows(fx["wr"], dev(x), K, norm_w=dev(nw))
+    assert np.array_equal(topi.cpu().numpy(), ref_topi)
+    out, err = F.moe_prefill(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], topi, topw, logits, dev(x), Fn, norm_w=dev(nw))
+    assert int(err.item()) == 0
+    # f16 operands: each product term carries 2^-11 relative rounding twice; the sums stay well inside the 1e-2 bar
+    assert rel_err(out.cpu().numpy(), ref_out) < 3e-3
+    # the decode-sized path gives the same block (first rows)
+    route = F.router_route(fx["wr"], dev(x[:5]), K, norm_w=dev(nw))
+    small, _, _ = F.moe_experts(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], route, dev(x[:5]), Fn, K, norm_w=dev(nw))
+    assert rel_err(out[:5].cpu().numpy(), small.cpu().numpy()) < 3e-3
+
+
 # ------------------------------------------------------------------------------------------------ attention
 @pytest.mark.parametrize("pos0,T,tree", [(0, 1, False), (37, 5, False), (300, 5, True), (4096, 5, False), (1000, 20, True)])
 def test_attention_matches_oracle(F, O, pos0, T, tree):
