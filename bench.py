@@ -139,6 +139,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=48, help="fewer layers for a quick functional run (not a valid bench number)")
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (the benchmark's is 4096)")
+    ap.add_argument("--prefill-moe", type=int, default=0, metavar="T",
+                    help="side measurement: the prompt-sized MoE block (tcgen05 grouped expert GEMM) of layer 0 over T random rows")
     ap.add_argument("--verify-only", action="store_true", help="profiling aid: prefill, then warmup + steps verify windows of k+1 rows and nothing else")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "b200" else a.warmup
@@ -171,6 +173,37 @@ def main():
         dist.broadcast(uid, 0)
         raw = bytes(uid.cpu().numpy().tobytes())
         F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
+    if a.prefill_moe:
+        # config 3's expert path on one layer: T rows grouped by expert, gate|up + SwiGLU + down on the tensor cores
+        T = a.prefill_moe
+        x = torch.randn((T, cfg.hidden), device="cuda")
+        nw = torch.ones(cfg.hidden, device="cuda")
+        wr = eng.tensor("l0.router", torch.float32).view(cfg.n_expert + 1, cfg.hidden)
+        topi, topw, logits = F.route_rows(wr, x, cfg.top_k, norm_w=nw)
+        wgu, wdn = eng.tensor("l0.experts_gu", torch.uint8), eng.tensor("l0.experts_dn", torch.uint8)
+        sgu, sdn = eng.tensor("l0.shared_gu", torch.uint8), eng.tensor("l0.shared_dn", torch.uint8)
+        scratch = torch.empty(F.lib().fnx_moe_prefill_scratch_bytes(T, cfg.top_k, cfg.n_expert, cfg.hidden, cfg.ffn), dtype=torch.uint8, device="cuda")
+        out = torch.zeros((T, cfg.hidden), device="cuda")
+        err = F.new_err()
+        run = lambda: F.moe_prefill(wgu, wdn, sgu, sdn, topi, topw, logits, x, cfg.ffn, norm_w=nw, out=out, scratch=scratch, err=err)
+        for _ in range(max(a.warmup, 1)):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.steps
+        pairs = T * (cfg.top_k + 1)
+        flops = pairs * 6.0 * cfg.hidden * cfg.ffn
+        pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        tf_peak = float(pk.get("bf16_tflops", 1590.0))
+        print(json.dumps({"mode": "prefill-moe", "rows": T, "ms_per_block": ms, "rows_per_s": T / ms * 1e3, "tflops": flops / ms / 1e9,
+                          "peak_tflops": tf_peak, "peak_kind": "measured" if pk else "fallback", "frac": flops / ms / 1e9 / tf_peak,
+                          "err": int(err.item()), "note": "one layer's routed + shared experts; routing given; includes the job build and one host read of the job count"}))
+        return
     hbm_peak, peak_kind = peaks()
     workload = (f"verify step of the synthetic 48-layer Qwen3-Next-style model (IQ3_S, seed 0), ctx {CTX} uniform-random tokens (seed 1), "
                 f"k+1={1 + K_DRAFT} rows (1 committed + {K_DRAFT} drafts), greedy; drafts = own greedy continuation, each wrong with p={P_BAD}")

@@ -6,7 +6,7 @@
 // job's product runs as tcgen05.mma (kind::f16, f32 accumulators in tensor memory):
 //   A = a 128-feature slab of the expert's IQ3_S matrix, decoded by the block's warps straight from the tile layout
 //       (iq3s_tile.h) into f16 in the K-major core-matrix layout the instruction's shared-memory descriptor names;
-//   B = the job's activation rows (gathered, RMS-normed, rounded to f16), same layout;
+//   B = the job's activation rows (RMS-normed and rounded to f16 once per call; gathered by 16-byte async copies), same layout;
 //   D = [128 features (lanes)] x [128 rows (columns)] in tensor memory; gate|up keeps two of them and the epilogue
 //       applies SwiGLU while it reads them back (tcgen05.ld).
 // Two shared-memory stages: the warps decode K-chunk c + 1 while the tensor core works on chunk c; a stage is reused
@@ -142,11 +142,10 @@ struct PfParams {
     const int* order;          // per job entry: the pair index t * Kp + k; shared jobs: T * Kp + t
     int TKp;                   // T * Kp: entries at or past it are shared-expert rows
     int Kp;
-    const float* x;            // activations: gate|up: [T][K] (row = token), down: [pairs][K] (row = pair)
-    const float* norm_w;       // gate|up: RMS-norm weight (with rstd), else null
-    const float* rstd;         // [T]
+    const __half* x;           // f16 activations: gate|up: [T][K] normed rows (row = token), down: [pairs][K] (row = pair)
     int rows, K;               // output features per expert matrix (gate|up: F; down: H), inner dimension
-    float* out;                // [pairs][rows]
+    float* out;                // down: [pairs][rows] f32
+    __half* outh;              // gate|up: [pairs][rows] f16 (the down product's operand)
     unsigned* err;
 };
 
@@ -193,58 +192,49 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (PF_N >> 3) << 17) | ((uint32_t) (PF_M >> 4) << 24);
     bool ok = true;
-    PfRaw raw[NA];
+    PfRaw raw[NA], nxt[NA];
     // the warp's 16 weight rows of the slab: tile row ft * 8 + warp (gate), and the same row of the up half
     const int trow = ft * (PF_M / 16) + warp;
-    for (int c = 0; c < nchunk && ok; ++c) {
+    auto load_raw = [&](int kb, PfRaw (&r)[NA]) {
+        pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r[0]);
+        if (NA == 2) pf_load_raw(W + ((size_t) (p.rows / 16 + trow) * KB + kb) * TILE_BYTES, lane, r[NA - 1]);
+    };
+    load_raw(0, raw);
+    for (int c = 0; c < nchunk; ++c) {
         const int s = c & 1, kb = c >> 1;
         uint8_t* A0 = stage0 + (size_t) s * STAGE;
         uint8_t* B = A0 + NA * PF_TILE;
-        if ((c & 1) == 0) {
-            pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, raw[0]);
-            if (NA == 2) pf_load_raw(W + ((size_t) (p.rows / 16 + trow) * KB + kb) * TILE_BYTES, lane, raw[NA - 1]);
-        }
-        // the activations of this chunk: thread = (row, half of the 128 columns); 16 float4 in two rounds of 8
-        const int brow = tid >> 1, bk0 = (tid & 1) * 64;
-        const int src = src_s[brow];
-        float4 xv[8];
         if (c >= 2) {   // the stage is free when the tensor core has finished chunk c - 2
             ok = __syncthreads_and(mbar_wait_bounded(&bars[s], (unsigned) (((c >> 1) - 1) & 1), 20000000u)) != 0;
             pf_fence_after();
             if (!ok) break;
         }
+        // the activations of this chunk: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies
 #pragma unroll
-        for (int round = 0; round < 2; ++round) {
-            const int kk = bk0 + round * 32;
-            const float* xr = src >= 0 ? p.x + (size_t) src * p.K + c * PF_KC + kk : nullptr;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) xv[j] = xr ? *reinterpret_cast<const float4*>(xr + j * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            float rs = 1.0f;
-            if (MODE == 1 && p.norm_w && xr) {
-                rs = p.rstd[src];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float4 w = *reinterpret_cast<const float4*>(p.norm_w + c * PF_KC + kk + j * 4);
-                    xv[j].x *= w.x * rs; xv[j].y *= w.y * rs; xv[j].z *= w.z * rs; xv[j].w *= w.w * rs;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-                const __half2 h0 = __floats2half2_rn(xv[j].x, xv[j].y), h1 = __floats2half2_rn(xv[j].z, xv[j].w);
-                const __half2 h2 = __floats2half2_rn(xv[j + 1].x, xv[j + 1].y), h3 = __floats2half2_rn(xv[j + 1].z, xv[j + 1].w);
-                *reinterpret_cast<uint4*>(B + pf_off(brow, kk + j * 4)) =
-                    make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1), *reinterpret_cast<const uint32_t*>(&h2),
-                               *reinterpret_cast<const uint32_t*>(&h3));
+        for (int j = 0; j < PF_N * (PF_KC / 8) / PF_THREADS; ++j) {
+            const int i = tid + j * PF_THREADS, brow = i >> 4, piece = i & 15;
+            const int src = src_s[brow];
+            uint8_t* dst = B + pf_off(brow, piece * 8);
+            if (src >= 0) {
+                const __half* g = p.x + (size_t) src * p.K + c * PF_KC + piece * 8;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(g) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
         }
-        // the weights of this chunk: four sub-blocks of the warp's tile(s)
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // the weights of this chunk: four sub-blocks of the warp's tile(s); the next block's bytes are fetched meanwhile
         if ((c & 1) == 0) {
             pf_half_block<0>(raw[0], A0, warp * 16, lane, table_s);
             if (NA == 2) pf_half_block<0>(raw[NA - 1], A0 + PF_TILE, warp * 16, lane, table_s);
+            if (kb + 1 < KB) load_raw(kb + 1, nxt);
         } else {
             pf_half_block<1>(raw[0], A0, warp * 16, lane, table_s);
             if (NA == 2) pf_half_block<1>(raw[NA - 1], A0 + PF_TILE, warp * 16, lane, table_s);
+#pragma unroll
+            for (int k = 0; k < NA; ++k) raw[k] = nxt[k];
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
         __syncthreads();
         if (tid == 0) {
@@ -280,7 +270,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
             }
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                if (col0 + i < job.n) p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+                if (col0 + i < job.n) {
+                    if (MODE == 1) p.outh[(size_t) out_s[col0 + i] * p.rows + f] = __float2half_rn(g[i]);
+                    else p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+                }
         }
     }
     pf_fence_before();
@@ -354,21 +347,33 @@ __global__ void k_pf_fill(const int* __restrict__ topi, int n, int e_lo, const i
     }
 }
 
-__global__ void k_pf_rstd(const float* __restrict__ x, int H, float eps, float* __restrict__ rstd) {
+// xh[t] = f16(x[t] * norm_w / rms(x[t]))   (norm_w null: f16(x[t]))
+__global__ void k_pf_xnorm(const float* __restrict__ x, const float* __restrict__ norm_w, int H, float eps, __half* __restrict__ xh) {
     const float* xr = x + (size_t) blockIdx.x * H;
+    __shared__ float ws[32], s_r;
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
         const float4 v = *reinterpret_cast<const float4*>(xr + i);
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = warp_sum(ss);
-    __shared__ float ws[32];
     if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x == 0) {
-        float s = 0.f;
-        for (int w = 0; w < (int) blockDim.x / 32; ++w) s += ws[w];
-        rstd[blockIdx.x] = rsqrtf(s / (float) H + eps);
+        float t = 0.f;
+        for (int w = 0; w < (int) blockDim.x / 32; ++w) t += ws[w];
+        s_r = norm_w ? rsqrtf(t / (float) H + eps) : 1.0f;
+    }
+    __syncthreads();
+    const float r = s_r;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(xr + i);
+        if (norm_w) {
+            const float4 w = *reinterpret_cast<const float4*>(norm_w + i);
+            v.x *= w.x * r; v.y *= w.y * r; v.z *= w.z * r; v.w *= w.w * r;
+        }
+        const __half2 a = __floats2half2_rn(v.x, v.y), b2 = __floats2half2_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(xh + (size_t) blockIdx.x * H + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b2));
     }
 }
 
@@ -397,8 +402,8 @@ static size_t pf_align(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 extern "C" size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F) {
     const size_t pairs = (size_t) T * K + T;
-    return pf_align(pairs * F * sizeof(float)) + pf_align(pairs * H * sizeof(float)) + pf_align(pairs * sizeof(int)) + pf_align((size_t) (E + 1) * sizeof(int)) * 2 +
-           pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob)) + pf_align((size_t) T * sizeof(float)) + 256;
+    return pf_align(pairs * F * sizeof(__half)) + pf_align(pairs * H * sizeof(float)) + pf_align(pairs * sizeof(int)) + pf_align((size_t) (E + 1) * sizeof(int)) * 2 +
+           pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob)) + pf_align((size_t) T * H * sizeof(__half)) + 256;
 }
 
 extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu, const void* Wsh_dn, int e_base,
@@ -412,13 +417,13 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     cudaStream_t st = as_stream(st_);
     const size_t pairs = (size_t) T * K + T;
     uint8_t* b = (uint8_t*) scratch;
-    float* hbuf = (float*) b; b += pf_align(pairs * F * sizeof(float));
+    __half* hbuf = (__half*) b; b += pf_align(pairs * F * sizeof(__half));
     float* part = (float*) b; b += pf_align(pairs * H * sizeof(float));
     int* order = (int*) b; b += pf_align(pairs * sizeof(int));
     int* cnt = (int*) b; b += pf_align((size_t) (E + 1) * sizeof(int));
     int* base = (int*) b; b += pf_align((size_t) (E + 1) * sizeof(int));
     PfJob* jobs = (PfJob*) b; b += pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob));
-    float* rstd = (float*) b; b += pf_align((size_t) T * sizeof(float));
+    __half* xh = (__half*) b; b += pf_align((size_t) T * H * sizeof(__half));
     int* njobs = (int*) b;
     const int ne = e_hi - e_lo, n = T * K;
     if (ne > 0) {
@@ -431,8 +436,8 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
         k_pf_fill<<<ne, 256, 0, st>>>(topi, n, e_lo, base, order);
         FNX_LAUNCH_OK("k_pf_fill");
     }
-    k_pf_rstd<<<T, 256, 0, st>>>(x, H, eps, rstd);
-    FNX_LAUNCH_OK("k_pf_rstd");
+    k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, H, eps, xh);
+    FNX_LAUNCH_OK("k_pf_xnorm");
     static bool configured = false;
     if (!configured) {
         FNX_CUDA_OK(cudaFuncSetAttribute(k_pf_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) pf_smem(0)));
@@ -446,11 +451,11 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     if (nj > 0) {
         PfParams p{};
         p.W = (const uint8_t*) Wgu; p.expert_stride = gu_stride; p.e_base = e_base; p.E = E; p.Wsh = (const uint8_t*) Wsh_gu;
-        p.jobs = jobs; p.order = order; p.TKp = n; p.Kp = K; p.x = x; p.norm_w = norm_w; p.rstd = rstd; p.rows = F; p.K = H; p.out = hbuf; p.err = err;
+        p.jobs = jobs; p.order = order; p.TKp = n; p.Kp = K; p.x = xh; p.rows = F; p.K = H; p.outh = hbuf; p.err = err;
         k_pf_gemm<1><<<dim3(nj, F / PF_M), PF_THREADS, pf_smem(1), st>>>(p);
         FNX_LAUNCH_OK("k_pf_gemm (gate|up)");
         p.W = (const uint8_t*) Wdn; p.expert_stride = dn_stride; p.Wsh = (const uint8_t*) Wsh_dn;
-        p.x = hbuf; p.norm_w = nullptr; p.rows = H; p.K = F; p.out = part;
+        p.x = hbuf; p.rows = H; p.K = F; p.out = part; p.outh = nullptr;
         k_pf_gemm<0><<<dim3(nj, H / PF_M), PF_THREADS, pf_smem(0), st>>>(p);
         FNX_LAUNCH_OK("k_pf_gemm (down)");
     }
