@@ -22,7 +22,8 @@ namespace fnxb {
 constexpr int PF_M = 128;         // features per block (tensor-memory lanes)
 constexpr int PF_N = 128;         // rows per job (tensor-memory columns per accumulator)
 constexpr int PF_KC = 128;        // K per stage: half a 256-column IQ3_S block
-constexpr int PF_THREADS = 256;
+constexpr int PF_THREADS = 512;
+constexpr int PF_REP = 16;         // copies of the codebook (entry e of copy r at word e * 16 + r): lanes l and l + 16 share one
 constexpr int PF_TILE = PF_M * PF_KC * 2;      // bytes of one f16 operand tile (128 x 128)
 constexpr int PF_LBO = 128;                    // bytes between core matrices (8 rows x 16 bytes) along K
 constexpr int PF_SBO = (PF_KC / 8) * 128;      // ... along the rows
@@ -93,14 +94,18 @@ __device__ __forceinline__ void pf_load_raw(const uint8_t* tile, int lane, PfRaw
     r.d1 = __half2float(*reinterpret_cast<const __half*>(tile + TILE_D + (g + 8) * 2));
 }
 
-// eight signed codebook bytes (two lookups) times the sub-block scale -> eight f16 at (row, k .. k + 7): one core-matrix row
-__device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32_t lo4, uint32_t hi4, float f) {
+// eight signed codebook bytes (two lookups) times the sub-block scale -> eight f16 at (row, k .. k + 7): one core-matrix
+// row.  Bytes become halves without the conversion unit: 0x6400 | (b + 128) is the f16 1024 + (b + 128), exactly.
+__device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32_t lo4, uint32_t hi4, __half2 f2) {
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
     uint32_t h[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const uint32_t w4 = j < 2 ? lo4 : hi4;
-        const int sh = (j & 1) * 16;
-        const __half2 v = __floats2half2_rn((float) (int8_t) ((w4 >> sh) & 0xFF) * f, (float) (int8_t) ((w4 >> (sh + 8)) & 0xFF) * f);
+        const uint32_t u = (j < 2 ? lo4 : hi4) ^ 0x80808080u;
+        uint32_t pair;
+        if (j & 1) asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(pair) : "r"(u), "r"(0x64646464u));
+        else asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(pair) : "r"(u), "r"(0x64646464u));
+        const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&pair), bias), f2);
         h[j] = *reinterpret_cast<const uint32_t*>(&v);
     }
     *reinterpret_cast<uint4*>(tileA + pf_off(row, k)) = make_uint4(h[0], h[1], h[2], h[3]);
@@ -109,7 +114,7 @@ __device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32
 template <int I>
 __device__ __forceinline__ uint32_t pf_decode(const uint32_t (&S)[5], const uint32_t (&G)[2], uint32_t table_s) {
     uint32_t mag;
-    const uint32_t a = table_s + (tile_field<I>(S) >> 5);   // the field is (index << 7): 4 bytes per entry
+    const uint32_t a = table_s + (tile_field<I>(S) >> 1);   // the field is (index << 7): 64 bytes per entry (PF_REP copies); table_s: the lane's copy
     asm("ld.shared.u32 %0, [%1];" : "=r"(mag) : "r"(a));
     return tile_apply_sign(mag, tile_sign_mask<I>(G));
 }
@@ -120,17 +125,28 @@ __device__ __forceinline__ uint32_t pf_decode(const uint32_t (&S)[5], const uint
 template <int SB>
 __device__ __forceinline__ void pf_sub_block(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
     const int g = lane >> 2, q = lane & 3, k0 = (SB & 3) * 32 + 8 * q;
-    const float f0 = r.d0 * (float) (1 + 2 * (int) ((r.sn0 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u));
-    const float f1 = r.d1 * (float) (1 + 2 * (int) ((r.sn1 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u));
+    const __half2 f0 = __float2half2_rn(r.d0 * (float) (1 + 2 * (int) ((r.sn0 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u)));
+    const __half2 f1 = __float2half2_rn(r.d1 * (float) (1 + 2 * (int) ((r.sn1 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u)));
     pf_store8(tileA, row0 + g, k0, pf_decode<2 * SB>(r.S0, r.G0, table_s), pf_decode<2 * SB + 1>(r.S0, r.G0, table_s), f0);
     pf_store8(tileA, row0 + g + 8, k0, pf_decode<2 * SB>(r.S1, r.G1, table_s), pf_decode<2 * SB + 1>(r.S1, r.G1, table_s), f1);
 }
-template <int HALF>
-__device__ __forceinline__ void pf_half_block(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
-    pf_sub_block<4 * HALF + 0>(r, tileA, row0, lane, table_s);
-    pf_sub_block<4 * HALF + 1>(r, tileA, row0, lane, table_s);
-    pf_sub_block<4 * HALF + 2>(r, tileA, row0, lane, table_s);
-    pf_sub_block<4 * HALF + 3>(r, tileA, row0, lane, table_s);
+// sub-blocks [4 HALF + 2 PAIR, + 2) of a tile block
+template <int HALF, int PAIR>
+__device__ __forceinline__ void pf_two_sub_blocks(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
+    pf_sub_block<4 * HALF + 2 * PAIR + 0>(r, tileA, row0, lane, table_s);
+    pf_sub_block<4 * HALF + 2 * PAIR + 1>(r, tileA, row0, lane, table_s);
+}
+// the warp's share of chunk-half HALF: gate|up (sel = which matrix): all four sub-blocks; down (sel = which pair): two
+template <int HALF, int MODE>
+__device__ __forceinline__ void pf_warp_share(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s, int sel) {
+    if (MODE == 1) {
+        pf_two_sub_blocks<HALF, 0>(r, tileA, row0, lane, table_s);
+        pf_two_sub_blocks<HALF, 1>(r, tileA, row0, lane, table_s);
+    } else if (sel == 0) {
+        pf_two_sub_blocks<HALF, 0>(r, tileA, row0, lane, table_s);
+    } else {
+        pf_two_sub_blocks<HALF, 1>(r, tileA, row0, lane, table_s);
+    }
 }
 
 struct PfParams {
@@ -157,15 +173,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     constexpr int STAGE = (NA + 1) * PF_TILE;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* stage0 = smem;                                    // 2 stages: [A0 | (A1) | B]
-    uint32_t* table = reinterpret_cast<uint32_t*>(smem + 2 * STAGE);          // the codebook, 2 KB
-    int* src_s = reinterpret_cast<int*>(table + 512);          // [PF_N] activation row per job row (-1: none)
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem + 2 * STAGE);          // the codebook, PF_REP copies
+    int* src_s = reinterpret_cast<int*>(table + 512 * PF_REP);          // [PF_N] activation row per job row (-1: none)
     int* out_s = src_s + PF_N;                                 // [PF_N] output row
     uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [2] stage free
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
     const PfJob job = p.jobs[blockIdx.x];
     const int ft = blockIdx.y, KB = p.K / 256, nchunk = p.K / PF_KC;
     const uint8_t* W = job.w >= p.E ? p.Wsh : p.W + (size_t) (job.w - p.e_base) * p.expert_stride;
-    for (int i = tid; i < 512; i += PF_THREADS) table[i] = g_grid_pf[i];
+    for (int i = tid; i < 512 * PF_REP; i += PF_THREADS) table[i] = g_grid_pf[i / PF_REP];
     if (tid < PF_N) {
         int src = -1, o = 0;
         if (tid < job.n) {
@@ -188,17 +204,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     pf_fence_before();
     __syncthreads();
     pf_fence_after();
-    const uint32_t tmem = *tmem_slot, table_s = smem_u32(table);
+    const uint32_t tmem = *tmem_slot, table_s = smem_u32(table) + (uint32_t) (lane % PF_REP) * 4u;
     // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (PF_N >> 3) << 17) | ((uint32_t) (PF_M >> 4) << 24);
     bool ok = true;
-    PfRaw raw[NA], nxt[NA];
-    // the warp's 16 weight rows of the slab: tile row ft * 8 + warp (gate), and the same row of the up half
-    const int trow = ft * (PF_M / 16) + warp;
-    auto load_raw = [&](int kb, PfRaw (&r)[NA]) {
-        pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r[0]);
-        if (NA == 2) pf_load_raw(W + ((size_t) (p.rows / 16 + trow) * KB + kb) * TILE_BYTES, lane, r[NA - 1]);
-    };
+    // 16 warps: warp w decodes tile row (w % 8) of the 128-feature slab; gate|up: of the gate (w < 8) or the up matrix
+    // (all four sub-blocks of the chunk); down: sub-block pair w / 8 of the chunk
+    PfRaw raw, nxt;
+    const int sel = warp >> 3;
+    const int trow = (MODE == 1 && sel ? p.rows / 16 : 0) + ft * (PF_M / 16) + (warp & 7);
+    const int a_off = MODE == 1 && sel ? PF_TILE : 0, row0 = (warp & 7) * 16;
+    auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
     load_raw(0, raw);
     for (int c = 0; c < nchunk; ++c) {
         const int s = c & 1, kb = c >> 1;
@@ -225,14 +241,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         asm volatile("cp.async.commit_group;" ::: "memory");
         // the weights of this chunk: four sub-blocks of the warp's tile(s); the next block's bytes are fetched meanwhile
         if ((c & 1) == 0) {
-            pf_half_block<0>(raw[0], A0, warp * 16, lane, table_s);
-            if (NA == 2) pf_half_block<0>(raw[NA - 1], A0 + PF_TILE, warp * 16, lane, table_s);
+            pf_warp_share<0, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
             if (kb + 1 < KB) load_raw(kb + 1, nxt);
         } else {
-            pf_half_block<1>(raw[0], A0, warp * 16, lane, table_s);
-            if (NA == 2) pf_half_block<1>(raw[NA - 1], A0 + PF_TILE, warp * 16, lane, table_s);
-#pragma unroll
-            for (int k = 0; k < NA; ++k) raw[k] = nxt[k];
+            pf_warp_share<1, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
+            raw = nxt;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
@@ -254,27 +267,23 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     pf_fence_after();
     if (!ok && tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
     if (ok) {
-        // warp w reads lanes 32 (w % 4) .. + 31 (its features), columns 64 (w / 4) .. + 63 (job rows), 32 at a time
-        const int f = ft * PF_M + 32 * (warp & 3) + lane;
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-            const int col0 = (warp >> 2) * 64 + h * 32;
-            const uint32_t ta = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) col0;
-            float g[32];
-            pf_ld32(ta, g);
-            if (MODE == 1) {
-                float u[32];
-                pf_ld32(ta + PF_N, u);
+        // warp w reads lanes 32 (w % 4) .. + 31 (its features), columns 32 (w / 4) .. + 31 (job rows)
+        const int f = ft * PF_M + 32 * (warp & 3) + lane, col0 = (warp >> 2) * 32;
+        const uint32_t ta = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) col0;
+        float g[32];
+        pf_ld32(ta, g);
+        if (MODE == 1) {
+            float u[32];
+            pf_ld32(ta + PF_N, u);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (col0 + i < job.n) {
-                    if (MODE == 1) p.outh[(size_t) out_s[col0 + i] * p.rows + f] = __float2half_rn(g[i]);
-                    else p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
-                }
+            for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (col0 + i < job.n) {
+                if (MODE == 1) p.outh[(size_t) out_s[col0 + i] * p.rows + f] = __float2half_rn(g[i]);
+                else p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+            }
     }
     pf_fence_before();
     __syncthreads();
@@ -392,7 +401,7 @@ __global__ void k_pf_combine(const float* __restrict__ part, const int* __restri
     *o = accumulate ? *o + s : s;
 }
 
-constexpr size_t pf_smem(int mode) { return (size_t) 2 * ((mode == 1 ? 2 : 1) + 1) * PF_TILE + 2048 + 2 * PF_N * sizeof(int) + 64; }
+constexpr size_t pf_smem(int mode) { return (size_t) 2 * ((mode == 1 ? 2 : 1) + 1) * PF_TILE + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
 
 }  // namespace fnxb
 
