@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import zlib
 import os
 import pathlib
 import statistics
@@ -173,6 +174,15 @@ def main():
         dist.broadcast(uid, 0)
         raw = bytes(uid.cpu().numpy().tobytes())
         F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
+        if os.environ.get("FNX_EP_NCCL", "0") != "1":
+            # the per-layer sum over NVLink peer memory instead of NCCL: exchange the ranks' IPC handles
+            mine = (C.c_char * 128)()
+            F.check(F.lib().fnx_engine_ep_handles(eng._h, mine))
+            hm = torch.frombuffer(bytearray(mine.raw), dtype=torch.uint8).clone().cuda()
+            allh = [torch.zeros(128, dtype=torch.uint8, device="cuda") for _ in range(world)]
+            dist.all_gather(allh, hm)
+            blob = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
+            F.check(F.lib().fnx_engine_ep_open(eng._h, blob, rank, world))
     if a.prefill_moe:
         # config 3's expert path on one layer: T rows grouped by expert, gate|up + SwiGLU + down on the tensor cores
         T = a.prefill_moe
@@ -317,7 +327,9 @@ def main():
             "clocks": clk, "gpu_launches": int(launches),
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * (1 + K_DRAFT) + 4 * (1 + K_DRAFT) + 8, "d2h_bytes_per_step": 4 * 65 + 4 + 4 * K_DRAFT,
                     "wall_ms_per_step": wall * 1e3 / a.steps},
-            "verify_step_us": verify_ms * 1e3, "accepted_per_offered": accepted / max(1, offered), "tokens_per_step": tokens / a.steps}
+            "verify_step_us": verify_ms * 1e3, "accepted_per_offered": accepted / max(1, offered), "tokens_per_step": tokens / a.steps,
+            "tokens_crc": zlib.crc32(np.asarray(want[:done], np.int64).tobytes()),
+            "ep_sum": "none" if world == 1 else ("nccl" if os.environ.get("FNX_EP_NCCL", "0") == "1" else "peer-memory")}
 
     if world == 1 and rank == 0:
         import ctypes as C

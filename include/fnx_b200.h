@@ -232,6 +232,13 @@ fnx_stream fnx_engine_stream(fnx_engine* e);
 int fnx_comm_unique_id(void* h_id128);
 int fnx_engine_comm_init(fnx_engine* e, const void* h_id128, int rank, int size);
 int fnx_allreduce(fnx_engine* e, float* x, size_t count, fnx_stream st);
+/* The same sum without NCCL, fused with the combine: every rank stores its routed addend straight into every peer's
+ * landing buffer over NVLink (plain peer stores + one release flag per peer), then adds the ranks' planes in rank order
+ * after a bounded wait (FNX_ERR_TIMEOUT).  fnx_engine_ep_handles: this rank's two CUDA IPC handles (128 bytes);
+ * exchange them between the ranks' processes by any means, then fnx_engine_ep_open(all ranks' handles, [size][128]).
+ * Replaces the reference's pinned-host sum exchange (ring_sum, engine/src/kernels.hpp:396). */
+int fnx_engine_ep_handles(fnx_engine* e, void* h_out128);
+int fnx_engine_ep_open(fnx_engine* e, const void* h_all, int rank, int size);
 
 #ifdef __cplusplus
 }

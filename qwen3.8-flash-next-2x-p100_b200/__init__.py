@@ -97,6 +97,8 @@ _PROTOS = {
     "fnx_comm_unique_id": (_I, [_P]),
     "fnx_engine_comm_init": (_I, [_P, _P, _I, _I]),
     "fnx_allreduce": (_I, [_P, _P, _Z, _P]),
+    "fnx_engine_ep_handles": (_I, [_P, _P]),
+    "fnx_engine_ep_open": (_I, [_P, _P, _I, _I]),
 }
 EXPORTS = tuple(_PROTOS)
 

@@ -106,6 +106,15 @@ struct fnx_engine {
     void* comm = nullptr;
     int proj_ld = 0;
     unsigned long long* d_stats = nullptr;
+    // expert-parallel exchange over peer memory (fnx_engine_ep_open): this rank's landing buffer [2 slots][ranks][MAXR][H]
+    // and arrival flags [2][ranks]; device arrays of every rank's buffer and flags; sequence counters of the two kernels
+    float* xbuf = nullptr;
+    unsigned* xflag = nullptr;
+    float** d_peer_x = nullptr;
+    unsigned** d_peer_flag = nullptr;
+    unsigned* d_xseq = nullptr;   // [0] sends so far, [1] receives so far, [2] send block counter, [3] receive block counter
+    std::vector<void*> ipc_opened;
+    bool ep_peers = false;
     // the persistent step kernel (windows of up to 8 rows on a single rank)
     bool use_step = false;
     std::map<uint64_t, StepParams*> step_params;     // per graph key: device parameter block
@@ -165,6 +174,78 @@ __global__ void k_add_rows(float* __restrict__ dst, const float* __restrict__ sr
     const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] += src[i];
 }
+// ---- expert-parallel sum over NVLink peer memory, fused with the combine (replaces combine + ncclAllReduce + add)
+// Send: this rank's routed addend a[t][h] = sum over its experts' picks of topw * part, stored straight into EVERY
+// rank's landing buffer (slot = sequence parity, plane = this rank); the last block to finish releases one flag per
+// peer.  Receive: waits (bounded) until every rank's flag of the slot shows the sequence, then R += the planes in rank
+// order (the same order on every rank: identical sums) + the local shared expert.  Two slots suffice: a rank sends
+// sequence n + 2 only after it has received everyone's n + 1, which they sent after reading n.
+__global__ void k_ep_send(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw, int T, int H, int K, int e_lo,
+                          int e_hi, float* const* __restrict__ peer_x, unsigned* const* __restrict__ peer_flag, int rank, int R, int maxr,
+                          unsigned* __restrict__ seqs) {
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned seq = seqs[0];
+    const int slot = (int) (seq & 1u);
+    if (i < H) {
+        float s = 0.f;
+        for (int k = 0; k < K; ++k) {
+            const int e = topi[t * K + k];
+            if (e >= e_lo && e < e_hi) s = fmaf(topw[t * K + k], part[((size_t) t * K + k) * H + i], s);
+        }
+        const size_t off = (((size_t) slot * R + rank) * maxr + t) * H + i;
+        for (int r = 0; r < R; ++r) peer_x[r][off] = s;
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ bool last;
+    if (threadIdx.x == 0) last = atomicAdd(&seqs[2], 1u) == gridDim.x * gridDim.y - 1;
+    __syncthreads();
+    if (last && threadIdx.x < R) {
+        __threadfence_system();
+        unsigned* f = peer_flag[threadIdx.x] + slot * R + rank;
+        const unsigned v = seq + 1u;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(v) : "memory");
+    }
+    if (last && threadIdx.x == 0) {
+        seqs[2] = 0;
+        seqs[0] = seq + 1u;
+    }
+}
+
+__global__ void k_ep_recv(const float* __restrict__ xbuf, const unsigned* __restrict__ xflag, const float* __restrict__ part,
+                          const float* __restrict__ logits, int T, int E, int H, int K, int R, int maxr, float* __restrict__ out,
+                          unsigned* __restrict__ seqs, unsigned* __restrict__ err) {
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned seq = seqs[1];
+    const int slot = (int) (seq & 1u);
+    __shared__ bool ok;
+    if (threadIdx.x == 0) {
+        bool all = false;
+        for (unsigned it = 0; it < 20000000u && !all; ++it) {
+            all = true;
+            for (int r = 0; r < R; ++r) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(xflag + slot * R + r) : "memory");
+                all = all && v == seq + 1u;
+            }
+        }
+        if (!all) atomicOr(err, (unsigned) FNX_ERR_TIMEOUT);
+        ok = all;
+    }
+    __syncthreads();
+    if (i < H && ok) {
+        float s = 0.f;
+        for (int r = 0; r < R; ++r) s += __ldcv(xbuf + (((size_t) slot * R + r) * maxr + t) * H + i);
+        s += sigmoidf_(logits[(size_t) t * (E + 1) + E]) * part[((size_t) T * K + t) * H + i];
+        out[(size_t) t * H + i] += s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(&seqs[3], 1u) == gridDim.x * gridDim.y - 1) {
+        seqs[3] = 0;
+        seqs[1] = seq + 1u;
+    }
+}
+
 // depth of every window row from the parent array (parent null: a chain)
 __global__ void k_depths(const int* __restrict__ parent, int* __restrict__ depth, int T) {
     const int t = threadIdx.x;
@@ -314,6 +395,15 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
                             e->err, e->st));
     FNX_TRY(fnx_moe_down(L.wdn, e->dn_bytes, e->e_lo, L.wsh_dn, d.E, e->jobs, e->njobs, njobs_max, e->hbuf, d.H, d.F, e->part, e->err, e->st));
     if (!ep) return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, d.E, 1, R, 1, e->st);
+    if (e->ep_peers) {
+        const dim3 grid((d.H + 255) / 256, T);
+        k_ep_send<<<grid, 256, 0, e->st>>>(e->part, e->topi, e->topw, T, d.H, d.K, e->e_lo, e->e_hi, e->d_peer_x, e->d_peer_flag, e->c.ep_rank,
+                                             e->c.ep_size, d.MAXR, e->d_xseq);
+        FNX_LAUNCH_OK("k_ep_send");
+        k_ep_recv<<<grid, 256, 0, e->st>>>(e->xbuf, e->xflag, e->part, e->rlogits, T, d.E, d.H, d.K, e->c.ep_size, d.MAXR, R, e->d_xseq, e->err);
+        FNX_LAUNCH_OK("k_ep_recv");
+        return FNX_OK;
+    }
     // expert parallel: this rank's routed addend, summed across ranks, then the (replicated) shared expert
     FNX_TRY(fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, e->e_lo, e->e_hi, 0, e->moe_out, 0, e->st));
     FNX_TRY(fnx_allreduce(e, e->moe_out, (size_t) T * d.H, e->st));
@@ -534,6 +624,13 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->hbuf, (size_t) d.P * d.F, "buf.h"));
         FNX_TRY(dalloc(e, &e->part, (size_t) d.P * d.H, "buf.part"));
         FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
+        if (c.ep_size > 1) {
+            FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
+            FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size, "buf.ep_flag"));
+            FNX_TRY(dalloc(e, &e->d_peer_x, (size_t) c.ep_size));
+            FNX_TRY(dalloc(e, &e->d_peer_flag, (size_t) c.ep_size));
+            FNX_TRY(dalloc(e, &e->d_xseq, 4));
+        }
         FNX_TRY(dalloc(e, &e->best_i, d.MAXR, "buf.best_i"));
         FNX_TRY(dalloc(e, &e->best_v, d.MAXR, "buf.best_v"));
         FNX_TRY(dalloc(e, &e->cand_v, (size_t) d.MAXR * FNX_TOPK_N, "buf.cand_v"));
@@ -582,6 +679,7 @@ extern "C" void fnx_engine_destroy(fnx_engine* e) {
     if (!e) return;
     if (e->st) cudaStreamSynchronize(e->st);
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+    for (void* q : e->ipc_opened) cudaIpcCloseMemHandle(q);
     if (e->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(e->comm);
     for (void* p : e->owned) cudaFree(p);
     if (e->h_stage) cudaFreeHost(e->h_stage);
@@ -824,6 +922,44 @@ extern "C" int fnx_engine_comm_init(fnx_engine* e, const void* h_id128, int rank
     memcpy(id.b, h_id128, 128);
     const int rc = n->CommInitRank(&e->comm, size, id, rank);
     if (rc) return fail(FNX_E_CUDA, "ncclCommInitRank: %s", n->GetErrorString ? n->GetErrorString(rc) : "error");
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_ep_handles(fnx_engine* e, void* h_out128) {
+    FNX_REQUIRE(e && h_out128 && e->xbuf && e->xflag, "fnx_engine_ep_handles: no expert-parallel engine");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h[2];
+    FNX_CUDA_OK(cudaIpcGetMemHandle(&h[0], e->xbuf));
+    FNX_CUDA_OK(cudaIpcGetMemHandle(&h[1], e->xflag));
+    memcpy(h_out128, h, sizeof h);
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_ep_open(fnx_engine* e, const void* h_all, int rank, int size) {
+    FNX_REQUIRE(e && h_all && rank == e->c.ep_rank && size == e->c.ep_size && e->xbuf, "fnx_engine_ep_open: rank %d of %d does not match the engine's shard", rank, size);
+    FNX_REQUIRE(!e->ep_peers, "fnx_engine_ep_open: already open");
+    std::vector<float*> px(size);
+    std::vector<unsigned*> pf(size);
+    const cudaIpcMemHandle_t* h = (const cudaIpcMemHandle_t*) h_all;
+    for (int r = 0; r < size; ++r) {
+        if (r == rank) {
+            px[r] = e->xbuf;
+            pf[r] = e->xflag;
+            continue;
+        }
+        void *a = nullptr, *b = nullptr;
+        FNX_CUDA_OK(cudaIpcOpenMemHandle(&a, h[2 * r], cudaIpcMemLazyEnablePeerAccess));
+        e->ipc_opened.push_back(a);
+        FNX_CUDA_OK(cudaIpcOpenMemHandle(&b, h[2 * r + 1], cudaIpcMemLazyEnablePeerAccess));
+        e->ipc_opened.push_back(b);
+        px[r] = (float*) a;
+        pf[r] = (unsigned*) b;
+    }
+    FNX_CUDA_OK(cudaMemcpy(e->d_peer_x, px.data(), sizeof(float*) * size, cudaMemcpyHostToDevice));
+    FNX_CUDA_OK(cudaMemcpy(e->d_peer_flag, pf.data(), sizeof(unsigned*) * size, cudaMemcpyHostToDevice));
+    e->ep_peers = true;
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);   // windows captured with the NCCL path are captured again
+    e->graphs.clear();
     return FNX_OK;
 }
 
