@@ -21,6 +21,7 @@ N > 1:   expert-parallel ranks (512 experts split evenly, one NCCL all-reduce pe
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import zlib
 import os
@@ -53,32 +54,43 @@ class Clocks:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
 
     def __init__(self, gpu_index: int):
-        self.rows, self.proc, self.idx = [], None, gpu_index
+        self.rows, self.proc, self.idx, self.t0 = [], None, gpu_index, None
 
-    def start(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    def launch(self):
+        """Starts the sampler (it needs a few hundred ms before its first line); mark() opens the timed region."""
+        q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "20", "-i", str(self.idx)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def start(self):
+        if self.proc is None:
+            self.launch()
+        self.t0 = time.time()
+
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        t1 = time.time()
+        time.sleep(0.05)
         self.proc.terminate()
         out = self.proc.communicate()[0]
         sm, mx, reasons = [], [], set()
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 6:
+            if len(f) < 7:
                 continue
             try:
-                sm.append(float(f[0])); mx.append(float(f[1]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if self.t0 is not None and not (self.t0 - 0.02 <= ts <= t1 + 0.02):
+                    continue   # outside the timed region
+                sm.append(float(f[1])); mx.append(float(f[2]))
             except ValueError:
                 continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
@@ -135,7 +147,7 @@ def cpu_step_seconds(F, O, eng, cfg, steps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=48, help="fewer layers for a quick functional run (not a valid bench number)")
@@ -272,6 +284,7 @@ def main():
     dev_ms, tokens, accepted, offered = 0.0, 0, 0, 0
     c0 = None
     clocks = Clocks(local)
+    clocks.launch()
     t_ev0, t_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
     have_kept = False

@@ -222,6 +222,14 @@ float fnx_engine_last_ms(const fnx_engine* e);
  * expert-parallel ranks always take the launch-per-operator path.  Off by default until it is the faster of the
  * two.  Drops the captured graphs. */
 int fnx_engine_use_step_kernel(fnx_engine* e, int on);
+/* Acceptance rule of the following windows: null = greedy (the default); else the sampling rule of
+ * engine/src/session.cpp:575-612 over each row's 64 best tokens with Philox uniforms addressed (seed, seq, window, slot);
+ * drafts count as fixed (q = 1), windows must be chains.  Resets the per-sequence window counters. */
+int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uint64_t seed);
+/* lookup_drafts (engine/src/session.cpp:428-447) over the sequence's own context on the device (committed tokens and
+ * the pending one; root >= 0 replaces the pending token, for a caller that starts the next window from another token):
+ * up to lk drafts into h_out, their number into h_n; d1 >= 0 keeps only a match whose first draft is d1. */
+int fnx_engine_lookup(fnx_engine* e, int seq, int lk, int d1, int root, int* h_out, int* h_n);
 /* counters since creation: [0] kernels launched through graphs, [1] routed expert jobs, [2] router calls */
 int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3);
 int fnx_engine_pos(const fnx_engine* e, int seq);

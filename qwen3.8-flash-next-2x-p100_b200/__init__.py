@@ -97,6 +97,8 @@ _PROTOS = {
     "fnx_comm_unique_id": (_I, [_P]),
     "fnx_engine_comm_init": (_I, [_P, _P, _I, _I]),
     "fnx_allreduce": (_I, [_P, _P, _Z, _P]),
+    "fnx_engine_set_sampling": (_I, [_P, _P, _U64]),
+    "fnx_engine_lookup": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "fnx_engine_ep_handles": (_I, [_P, _P]),
     "fnx_engine_ep_open": (_I, [_P, _P, _I, _I]),
 }
@@ -423,6 +425,15 @@ class Engine:
         out = (C.c_int * k)()
         check(lib().fnx_engine_draft(self._h, seq, k, out))
         return list(out)
+
+    def set_sampling(self, sampling=None, seed: int = 0):
+        """Sampling (an fnx Sampling struct) or None for greedy windows."""
+        check(lib().fnx_engine_set_sampling(self._h, C.byref(sampling) if sampling is not None else None, seed))
+
+    def lookup(self, lk: int, d1: int = -1, root: int = -1, seq: int = 0):
+        out, n = (C.c_int * MAX_ROWS)(), C.c_int()
+        check(lib().fnx_engine_lookup(self._h, seq, lk, d1, root, out, C.byref(n)))
+        return list(out[:n.value])
 
     def use_step_kernel(self, on: bool):
         check(lib().fnx_engine_use_step_kernel(self._h, 1 if on else 0))

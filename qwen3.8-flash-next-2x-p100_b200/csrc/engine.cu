@@ -66,6 +66,7 @@ struct LayerW {
 
 struct SeqState {
     int pos = 0, cur = 0;
+    uint32_t step = 0;   // windows verified under the sampling rule (the Philox step of the next one)
     int last_T = 0;              // rows of the last verify window
     int kept = 0;                // rows kept by the last commit
     int kept_pos0 = 0;           // position of the first kept row
@@ -115,6 +116,12 @@ struct fnx_engine {
     unsigned* d_xseq = nullptr;   // [0] sends so far, [1] receives so far, [2] send block counter, [3] receive block counter
     std::vector<void*> ipc_opened;
     bool ep_peers = false;
+    // stochastic acceptance (fnx_engine_set_sampling): off = greedy windows
+    bool sampling_on = false;
+    fnx_sampling sampling{};
+    uint64_t sample_seed = 0;
+    uint32_t* d_step = nullptr;   // [n_seq] windows sampled so far (the Philox step)
+    int* d_lk = nullptr;          // lookup: [0, MAX_ROWS) drafts, [MAX_ROWS, +2) count and match, +2 the first-draft filter, +3 the context length
     // the persistent step kernel (windows of up to 8 rows on a single rank)
     bool use_step = false;
     std::map<uint64_t, StepParams*> step_params;     // per graph key: device parameter block
@@ -246,6 +253,7 @@ __global__ void k_ep_recv(const float* __restrict__ xbuf, const unsigned* __rest
     }
 }
 
+__global__ void k_plus_one(int* dst, const int* src) { *dst = *src + 1; }
 // depth of every window row from the parent array (parent null: a chain)
 __global__ void k_depths(const int* __restrict__ parent, int* __restrict__ depth, int T) {
     const int t = threadIdx.x;
@@ -460,6 +468,12 @@ static int enqueue_verify(fnx_engine* e, int seq, int T, bool tree) {
         FNX_TRY(enqueue_moe(e, L, e->R, T));
     }
     FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0));
+    if (e->sampling_on) {   // the sampling rule over the rows' 64 best tokens, uniforms addressed (seed, sequence, window, slot)
+        FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
+        FNX_TRY(fnx_accept_sample(e->cand_v, e->cand_i, e->d_tok, T, e->sampling, nullptr, nullptr, nullptr, e->sample_seed, (uint32_t) seq, e->d_step + seq,
+                                  e->result, e->st));
+        return FNX_OK;
+    }
     FNX_TRY(fnx_argmax(e->logits, T, d.V, e->best_i, e->best_v, e->err, e->st));
     return fnx_accept_greedy(e->d_tok, par, e->best_i, T, e->result, e->st);
 }
@@ -643,6 +657,8 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_mtok, FNX_MAX_ROWS, "buf.mtp_tok"));
         FNX_TRY(dalloc(e, &e->d_mpos, 1, "buf.mtp_pos"));
         FNX_TRY(dalloc(e, &e->d_draft, 1, "buf.draft"));
+        FNX_TRY(dalloc(e, &e->d_step, c.n_seq, "seq.step"));
+        FNX_TRY(dalloc(e, &e->d_lk, FNX_MAX_ROWS + 4, "buf.lookup"));
         FNX_TRY(dalloc(e, &e->d_pos, c.n_seq, "seq.pos"));
         FNX_TRY(dalloc(e, &e->d_cur, c.n_seq, "seq.cur"));
         FNX_TRY(dalloc(e, &e->d_ctx, (size_t) c.n_seq * e->cache_rows, "seq.ctx"));
@@ -773,9 +789,14 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
         memcpy(hs + FNX_MAX_ROWS, h_parent, sizeof(int) * T);
         FNX_CUDA_OK(cudaMemcpyAsync(e->d_parent, hs + FNX_MAX_ROWS, sizeof(int) * T, cudaMemcpyHostToDevice, e->st));
     }
+    if (e->sampling_on) {   // the window's Philox step is a host count: a window replayed or run twice draws the same uniforms
+        hs[2 * FNX_MAX_ROWS] = (int) s.step++;
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_step + seq, hs + 2 * FNX_MAX_ROWS, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    }
     const bool tree = h_parent != nullptr;
+    FNX_REQUIRE(!(tree && e->sampling_on), "fnx_engine_verify: the sampling rule is defined on chains (parent must be null)");
     const uint64_t key = ((uint64_t) 1 << 60) | ((uint64_t) seq << 20) | ((uint64_t) T << 1) | (tree ? 1 : 0);
-    if (step_ok(e, T)) {
+    if (step_ok(e, T) && !e->sampling_on) {
         FNX_TRY(step_prepare(e, key, seq, T, tree));
         StepParams* dp = e->step_params[key];
         FNX_TRY(run_graph(e, key, [&]() { return step_launch(dp, T, e->d_sync, e->st); }));
@@ -792,6 +813,48 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
         const unsigned bits = (unsigned) hs[5 * FNX_MAX_ROWS];
         if (bits) return fail(FNX_E_STATE, "verify: device error bits 0x%x (1: a bounded wait gave up, 2: non-finite value, 16: non-finite logits)", bits);
     }
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uint64_t seed) {
+    FNX_REQUIRE(e, "fnx_engine_set_sampling: null engine");
+    FNX_REQUIRE(!s || s->temperature > 0.f, "fnx_engine_set_sampling: temperature %g (null selects greedy windows)", s ? (double) s->temperature : 0.0);
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    e->sampling_on = s != nullptr;
+    if (s) e->sampling = *s;
+    e->sample_seed = seed;
+    FNX_CUDA_OK(cudaMemset(e->d_step, 0, sizeof(uint32_t) * e->c.n_seq));
+    for (SeqState& q : e->seqs) q.step = 0;
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);   // the rule is part of the captured windows
+    e->graphs.clear();
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_lookup(fnx_engine* e, int seq, int lk, int d1, int root, int* h_out, int* h_n) {
+    FNX_REQUIRE(e && h_out && h_n && seq >= 0 && seq < e->c.n_seq && lk >= 0 && lk <= FNX_MAX_ROWS, "fnx_engine_lookup: bad arguments");
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    int* hs = e->h_stage;
+    int* out_n = e->d_lk + FNX_MAX_ROWS;
+    const int* d1p = nullptr;
+    if (d1 >= 0) {
+        hs[0] = d1;
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_lk + FNX_MAX_ROWS + 2, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
+        d1p = e->d_lk + FNX_MAX_ROWS + 2;
+    }
+    // the context holds the committed tokens followed by the pending one (the next window's first row): both count;
+    // a caller that will start the next window from another token says so (root >= 0)
+    if (root >= 0) {
+        FNX_REQUIRE(root < e->c.vocab, "fnx_engine_lookup: root token %d outside the vocabulary", root);
+        hs[1] = root;
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_ctx + (size_t) seq * e->cache_rows + e->seqs[seq].pos, hs + 1, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    }
+    k_plus_one<<<1, 1, 0, e->st>>>(e->d_lk + FNX_MAX_ROWS + 3, e->d_ctx_n + seq);
+    FNX_LAUNCH_OK("k_plus_one");
+    FNX_TRY(fnx_lookup_draft(e->d_ctx + (size_t) seq * e->cache_rows, e->d_lk + FNX_MAX_ROWS + 3, lk, d1p, e->d_lk, out_n, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(hs + 8, e->d_lk, sizeof(int) * (FNX_MAX_ROWS + 2), cudaMemcpyDeviceToHost, e->st));
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    *h_n = hs[8 + FNX_MAX_ROWS];
+    memcpy(h_out, hs + 8, sizeof(int) * (*h_n));
     return FNX_OK;
 }
 

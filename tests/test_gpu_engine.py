@@ -187,3 +187,60 @@ def test_engine_rejects_bad_calls(F, model):
     with pytest.raises(F.FnxError):
         eng.commit([0, 2, 1])
     eng.commit([0])
+
+
+def test_lookup_branch_and_draft_chain_in_one_tree_window(F, O, model):
+    """The second configuration's window: an MTP-style chain and a prompt-lookup branch share the root of one tree
+    window; the kept path is the branch that continues the greedy text, whichever it is."""
+    cfg, eng, _ = model
+    rng = np.random.default_rng(12)
+    span = rng.integers(0, cfg.vocab, size=10).tolist()
+    prompt = rng.integers(0, cfg.vocab, size=6).tolist() + span + rng.integers(0, cfg.vocab, size=5).tolist() + span[:4]
+    want = _greedy_plain(eng, prompt, 8)
+    eng.reset()
+    eng.prefill(prompt[:-1])
+    # the device drafter over the engine's own context equals the reference's host drafter on the same tokens
+    lk = eng.lookup(3, root=prompt[-1])
+    assert lk == list(O.lookup(np.array(prompt, np.int32), 3, -1)[0]) and lk == span[4:7]
+    chain = [want[0], want[1], (want[2] + 1) % cfg.vocab]         # a draft chain with one wrong token
+    toks = [prompt[-1]] + chain + lk
+    par = [-1, 0, 1, 2] + [0] + list(range(4, 4 + len(lk) - 1))
+    n, path, em = eng.verify(toks, par)
+    # greedy acceptance follows the branch whose tokens match: the chain's first two (the lookup branch is the copied span,
+    # not the model's greedy text, unless they coincide)
+    assert em[:n] == want[:n] and n >= 3 and path[:3] == [0, 1, 2]
+    eng.commit(path)
+    n2, _, em2 = eng.verify([em[-1]])
+    assert em2[0] == want[n]
+
+
+def test_engine_sampling_windows_follow_the_oracle_rule(F, O, model):
+    """Stochastic acceptance inside the engine (the fourth configuration's rule): accepted counts and emitted tokens equal
+    the oracle's rule applied to the engine's own logits, window after window (Philox step = window index)."""
+    cfg, eng, _ = model
+    rng = np.random.default_rng(13)
+    prompt = rng.integers(0, cfg.vocab, size=10).tolist()
+    s = F.Sampling(0.7, 0.95, 0.02, 40)
+    eng.reset()
+    eng.set_sampling(s, seed=77)
+    try:
+        eng.prefill(prompt[:-1])
+        # prefill windows are sampled windows too: the Philox step counts them
+        step0 = (len(prompt) - 1 + cfg.max_rows - 1) // cfg.max_rows
+        x, accepted = prompt[-1], 0
+        for w in range(6):
+            drafts = eng.draft(3)
+            toks = [x] + drafts
+            n, path, em = eng.verify(toks)
+            logits = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:len(toks)]
+            cv, ci = O.top_tokens(logits)
+            on, oem = O.accept_sample(cv, ci, np.array(toks, np.int32), O.Sampling(s.temperature, s.top_p, s.min_p, s.top_k), seed=77, seq=0,
+                                      step=step0 + w)
+            assert (n, em) == (on, list(oem)) and path == list(range(n))
+            accepted += n - 1
+            eng.commit(path)
+            x = em[-1]
+        with pytest.raises(F.FnxError):
+            eng.verify([x, 1, 2], [-1, 0, 0])          # the sampling rule is defined on chains
+    finally:
+        eng.set_sampling(None)
