@@ -86,7 +86,7 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 
-// One block: KV head kvh, split s of S (a contiguous share of the positions [0, ctx)), window rows [r0, r0 + ATT_ROWS):
+// One block: KV head kvh, split s of S (every S-th 64-position chunk of [0, ctx)), window rows [r0, r0 + ATT_ROWS):
 // their (up to 40) queries against the share, on the tensor cores (mma.sync m16n8k16, f16 x f16 -> f32):
 //   scores  = Q K^T with Q = Qhi + Qlo, two f16 halves of the f32 queries, so that only K's own f16 rounding remains;
 //   weights = exp(score - running max), rounded to f16 (their sum is taken over the rounded values);
@@ -113,8 +113,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
     float* zs = ms + ATT_MQ;
     float* fs = zs + ATT_MQ;
     unsigned* see = reinterpret_cast<unsigned*>(fs + ATT_MQ);     // per local row: window rows it sees
-    const int pa = (int) ((long long) ctx * s / S), pb = (int) ((long long) ctx * (s + 1) / S);
-    if (pa >= pb) {   // a block with no positions leaves only empty partials: the merge skips them without reading their sums
+    // Split s takes the 64-position chunks s, s + S, s + 2 S, ... in order.  Chunks are cut at absolute positions, so what a
+    // row's partial of split s sums, and in which order, depends on the row's own position only - not on the window it
+    // arrived in: a row verified alone and the same row verified among drafts give the same bits.
+    const int pa = s * ATT_SC;
+    if (pa >= ctx) {   // a block with no positions leaves only empty partials: the merge skips them without reading their sums
         if (tid < NQ) {
             const int r = tid / qpk, hh = tid % qpk;
             mz_out[((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s] = AttPartial{-INFINITY, 0.f};
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch_kv(pa, min(ATT_SC, pb - pa));
+    fetch_kv(pa, min(ATT_SC, ctx - pa));
     // the queries as f16 pairs (hi, lo); rows past NQ are zero
     for (int i0 = tid; i0 < ATT_MQ * (ATT_HD / 4); i0 += 6 * ATT_THREADS) {
         float4 v[6];
@@ -189,8 +192,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part(const float* __restri
     const uint32_t bk_off = (uint32_t) ((warp * 8 + (lane & 7)) * ATT_QS + (lane >> 3) * 8) * 2u;
     const uint32_t bv_off = (uint32_t) (((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_QS + warp * 32 + (lane >> 4) * 8) * 2u;
     const uint32_t ap_off = (uint32_t) ((lane & 15) * ATT_PS + (lane >> 4) * 8) * 2u;
-    for (int p0 = pa; p0 < pb; p0 += ATT_SC) {
-        const int np = min(ATT_SC, pb - p0);
+    for (int p0 = pa; p0 < ctx; p0 += S * ATT_SC) {
+        const int np = min(ATT_SC, ctx - p0);
         if (p0 > pa) {
             __syncthreads();   // the previous step's tiles are read
             fetch_kv(p0, np);

@@ -16,25 +16,33 @@ __device__ __forceinline__ uint32_t fkey(float v) {
 __device__ __forceinline__ float fkey_inv(uint32_t k) { return __uint_as_float(k & 0x80000000u ? k & 0x7fffffffu : ~k); }
 __device__ __forceinline__ unsigned long long key64(float v, int i) { return ((unsigned long long) fkey(v) << 32) | (uint32_t) ~i; }
 
+// Rows are scanned by ARGMAX_NB blocks each; the blocks of a row meet in a per-row slot of device memory (largest key by
+// atomicMax, an arrival counter) and the last one to arrive writes the result and clears the slot for the next call.
+// The slots are shared by every call on the device: calls must not overlap in time (the engine's are stream-ordered).
+constexpr int ARGMAX_NB = 16, ARGMAX_ROWS = 1024;
+__device__ unsigned long long g_argmax_key[ARGMAX_ROWS];
+__device__ unsigned g_argmax_cnt[ARGMAX_ROWS];
+
 __global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logits, int V, int* __restrict__ best_i,
                                                  float* __restrict__ best_v, unsigned* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ unsigned long long red[32];
-    const int t = blockIdx.x, tid = threadIdx.x;
+    const int t = blockIdx.x, tid = threadIdx.x, nb = gridDim.y;
     const float* l = logits + (size_t) t * V;
     unsigned long long best = 0;
     bool bad = false;
-    // four float4 per thread in flight; a tail of fewer than 4 values is read one by one
+    // this block's slice, in float4 units where the row allows; four float4 per thread in flight
     const int V4 = (((uintptr_t) l & 15) == 0) ? V / 4 : 0;
-    for (int i0 = tid; i0 < V4; i0 += 4096) {
+    const int a4 = (int) ((long long) V4 * blockIdx.y / nb), b4 = (int) ((long long) V4 * (blockIdx.y + 1) / nb);
+    for (int i0 = a4 + tid; i0 < b4; i0 += 4096) {
         float4 v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = i0 + 1024 * j < V4 ? reinterpret_cast<const float4*>(l)[i0 + 1024 * j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        for (int j = 0; j < 4; ++j) v[j] = i0 + 1024 * j < b4 ? reinterpret_cast<const float4*>(l)[i0 + 1024 * j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = i0 + 1024 * j;
-            if (i >= V4) continue;
+            if (i >= b4) continue;
             const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -44,12 +52,13 @@ __global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logit
             }
         }
     }
-    for (int i = 4 * V4 + tid; i < V; i += 1024) {
-        const float v = l[i];
-        bad |= !isfinite(v);
-        const unsigned long long k = key64(v, i);
-        best = k > best ? k : best;
-    }
+    if (blockIdx.y == nb - 1)   // what float4 units do not cover
+        for (int i = 4 * V4 + tid; i < V; i += 1024) {
+            const float v = l[i];
+            bad |= !isfinite(v);
+            const unsigned long long k = key64(v, i);
+            best = k > best ? k : best;
+        }
     for (int o = 16; o; o >>= 1) {
         const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
         best = ok > best ? ok : best;
@@ -64,6 +73,14 @@ __global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logit
             best = ok > best ? ok : best;
         }
         if (tid == 0) {
+            if (nb > 1) {
+                atomicMax(&g_argmax_key[t], best);
+                __threadfence();
+                if (atomicAdd(&g_argmax_cnt[t], 1u) != (unsigned) nb - 1) return;
+                __threadfence();
+                best = atomicExch(&g_argmax_key[t], 0ull);
+                g_argmax_cnt[t] = 0;
+            }
             best_i[t] = (int) ~(uint32_t) best;
             if (best_v) best_v[t] = fkey_inv((uint32_t) (best >> 32));
         }
@@ -154,7 +171,7 @@ using namespace fnxb;
 extern "C" int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st) {
     FNX_REQUIRE(logits && best_i && err && T >= 1 && V >= 1, "fnx_argmax: bad arguments");
     {
-        const cudaError_t le_ = launch_k(k_argmax, dim3(T), dim3(1024), 0, as_stream(st), logits, V, best_i, best_v, err);
+        const cudaError_t le_ = launch_k(k_argmax, dim3(T, T <= ARGMAX_ROWS && V >= 65536 ? ARGMAX_NB : 1), dim3(1024), 0, as_stream(st), logits, V, best_i, best_v, err);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_argmax: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_argmax");

@@ -178,8 +178,11 @@ __device__ __forceinline__ void core_sub_block(const uint32_t (&S0)[5], const ui
 // One item: tile (16 rows x 256 columns, block `blk` of its rows) against the lane's activation cells; adds into
 // acc[ng][0..3] = (row g, col 2q), (row g, col 2q+1), (row g+8, col 2q), (row g+8, col 2q+1).
 // CHECK: a zero address in lx means an empty column; without it every address is read (empty rows are zero cells).
-template <int NG, bool CHECK = true>
-__device__ __forceinline__ void core_item(uint32_t tile_s, uint32_t table_s, const LaneX<NG>& lx, int blk, int lane, float (&acc)[NG][4]) {
+// AccT double: the block's four products are exact in double and their sums carry ~2^-53 relative error, so that the
+// rounded result does not depend on where a row's K-sum was cut into pieces (expert modes, where the cuts move with the
+// number of jobs: a row must give the same bits whatever else is in the window).
+template <int NG, bool CHECK = true, typename AccT = float>
+__device__ __forceinline__ void core_item(uint32_t tile_s, uint32_t table_s, const LaneX<NG>& lx, int blk, int lane, AccT (&acc)[NG][4]) {
     const int g = lane >> 2;
     const uint32_t lane4 = (uint32_t) lane * 4u;
     const uint32_t a16 = tile_s + lane * 16, a8 = tile_s + lane * 8, a2 = tile_s + lane * 2, ag4 = tile_s + g * 4, ag2 = tile_s + g * 2;
@@ -222,10 +225,17 @@ __device__ __forceinline__ void core_item(uint32_t tile_s, uint32_t table_s, con
             x0 *= lx.r0[ng];
             x1 *= lx.r1[ng];
         }
-        acc[ng][0] += d0 * x0 * (float) accI[ng][0];
-        acc[ng][1] += d0 * x1 * (float) accI[ng][1];
-        acc[ng][2] += d1 * x0 * (float) accI[ng][2];
-        acc[ng][3] += d1 * x1 * (float) accI[ng][3];
+        if constexpr (sizeof(AccT) == 8) {
+            acc[ng][0] += (double) (d0 * x0) * (double) accI[ng][0];
+            acc[ng][1] += (double) (d0 * x1) * (double) accI[ng][1];
+            acc[ng][2] += (double) (d1 * x0) * (double) accI[ng][2];
+            acc[ng][3] += (double) (d1 * x1) * (double) accI[ng][3];
+        } else {
+            acc[ng][0] += d0 * x0 * (float) accI[ng][0];
+            acc[ng][1] += d0 * x1 * (float) accI[ng][1];
+            acc[ng][2] += d1 * x0 * (float) accI[ng][2];
+            acc[ng][3] += d1 * x1 * (float) accI[ng][3];
+        }
     }
 }
 
@@ -376,6 +386,17 @@ namespace fnxb {
 
 enum { MAT_DENSE = 0, MAT_GATEUP = 1, MAT_DOWN = 2 };
 
+// accumulator of a row's K-sum: the dense product is cut the same way for any number of rows (float, summed in a fixed
+// order); the expert products are cut where the job count puts the warps' shares (double, see core_item)
+template <int MODE>
+struct MatAcc {
+    using type = double;
+};
+template <>
+struct MatAcc<MAT_DENSE> {
+    using type = float;
+};
+
 struct MatDesc {
     const uint8_t* W;        // the dense matrix, or expert 0 of the experts held at W
     size_t expert_stride;
@@ -416,7 +437,7 @@ struct PieceSlot {
     int unit;                // -1: none, -2: the warp had no items at all
     int b_lo, b_hi, job, ntok;
     int orow[8];
-    float v[128];            // [kind (gate|up only: 0 gate, 1 up)][group][16 lanes][4]
+    double v[128];           // [kind (gate|up only: 0 gate, 1 up)][group][16 lanes][4]
 };
 constexpr int PIECE_BYTES = sizeof(PieceSlot);
 
@@ -431,9 +452,9 @@ __device__ __forceinline__ const uint8_t* mat_job_weights(const MatDesc& m, int 
 }
 
 // the 16 x rows results of unit (job rows orow, local tile lu) from this lane's sums (threads q < 2 hold them)
-template <int NG, int MODE>
-__device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const int (&orow)[4 * NG], int ntok, int lane, const float (&gacc)[NG][4],
-                                               const float (&acc)[NG][4]) {
+template <int NG, int MODE, typename AccT>
+__device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const int (&orow)[4 * NG], int ntok, int lane, const AccT (&gacc)[NG][4],
+                                               const AccT (&acc)[NG][4]) {
     const int g = lane >> 2, q = lane & 3;
     if (q >= 2) return;
 #pragma unroll
@@ -443,7 +464,7 @@ __device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const i
             const int tok = 4 * ng + 2 * q + (k & 1), row = lu * 16 + g + 8 * (k >> 1);
             if (tok < ntok) {
                 float* dst = m.out + (size_t) orow[tok] * m.ldo + row;
-                const float v = MODE == MAT_GATEUP ? siluf_(gacc[ng][k]) * acc[ng][k] : acc[ng][k];
+                const float v = MODE == MAT_GATEUP ? siluf_((float) gacc[ng][k]) * (float) acc[ng][k] : (float) acc[ng][k];
                 *dst = m.accumulate ? *dst + v : v;
             }
         }
@@ -526,7 +547,8 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
     int cur_job = -1, ntok = 0, b_lo = 0;
     int orow[4 * NG];
     LaneX<NG> lx;
-    float acc[NG][4], gacc[NG][4];
+    using AccT = typename MatAcc<MODE>::type;
+    AccT acc[NG][4], gacc[NG][4];
     int b = i0 % nbu, lu = (ua + i0 / nbu) % upj, j = (ua + i0 / nbu) / upj;
     for (int s = i0; s < i1; ++s) {
         if (b == 0 || s == i0) {
@@ -534,7 +556,7 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
 #pragma unroll
             for (int ng = 0; ng < NG; ++ng)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[ng][k] = gacc[ng][k] = 0.f;
+                for (int k = 0; k < 4; ++k) acc[ng][k] = gacc[ng][k] = 0;
             if (j != cur_job) {
                 cur_job = j;
                 lane_x(j, lx, ntok, orow);
@@ -545,8 +567,8 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
         ring.parity ^= 1u << st;
         ring.out_slot = st + 1 == (unsigned) ring.R ? 0u : st + 1;
         const uint32_t tile_s = ring.slots_s + st * (uint32_t) TILE_BYTES;
-        if (MODE == MAT_GATEUP && b < KB) core_item<NG, false>(tile_s, table_s, lx, b, lane, gacc);
-        else core_item<NG, false>(tile_s, table_s, lx, MODE == MAT_GATEUP ? b - KB : b, lane, acc);
+        if (MODE == MAT_GATEUP && b < KB) core_item<NG, false, AccT>(tile_s, table_s, lx, b, lane, gacc);
+        else core_item<NG, false, AccT>(tile_s, table_s, lx, MODE == MAT_GATEUP ? b - KB : b, lane, acc);
         __syncwarp();
         issue_upto(s + 1 + ring.R);
         if (b == nbu - 1 || s == i1 - 1) {
@@ -559,7 +581,7 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
                     if (MODE == MAT_GATEUP) gacc[ng][k] += __shfl_xor_sync(0xffffffffu, gacc[ng][k], 2);
                 }
             if (b_lo == 0 && b == nbu - 1) {
-                mat_write_unit<NG, MODE>(m, lu, orow, ntok, lane, gacc, acc);
+                mat_write_unit<NG, MODE, AccT>(m, lu, orow, ntok, lane, gacc, acc);
             } else {
                 PieceSlot* ps = mine + (b_lo == 0 ? 1 : 0);
                 if (lane == 0) {
@@ -607,13 +629,14 @@ __device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* p
     const int nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
     const int l16 = (lane >> 2) * 2 + (lane & 3);
     const bool holder = (lane & 3) < 2;
-    float acc[NG][4], gacc[NG][4];
+    using AccT = typename MatAcc<MODE>::type;
+    AccT acc[NG][4], gacc[NG][4];
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            gacc[ng][k] = holder && MODE == MAT_GATEUP ? first->v[(ng * 16 + l16) * 4 + k] : 0.f;
-            acc[ng][k] = holder ? first->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k] : 0.f;
+            gacc[ng][k] = holder && MODE == MAT_GATEUP ? (AccT) first->v[(ng * 16 + l16) * 4 + k] : (AccT) 0;
+            acc[ng][k] = holder ? (AccT) first->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k] : (AccT) 0;
         }
     for (int ww = warp + 1; ww < nwarp; ++ww) {
         const PieceSlot* c = pieces + ww * 2;
@@ -624,15 +647,15 @@ __device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* p
 #pragma unroll
             for (int k = 0; k < 4; ++k)
                 if (holder) {
-                    if (MODE == MAT_GATEUP) gacc[ng][k] += c->v[(ng * 16 + l16) * 4 + k];
-                    acc[ng][k] += c->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k];
+                    if (MODE == MAT_GATEUP) gacc[ng][k] += (AccT) c->v[(ng * 16 + l16) * 4 + k];
+                    acc[ng][k] += (AccT) c->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k];
                 }
         if (c->b_hi == nbu) break;
     }
     int orow[4 * NG];
 #pragma unroll
     for (int i = 0; i < 4 * NG; ++i) orow[i] = first->orow[i];
-    mat_write_unit<NG, MODE>(m, u % upj, orow, first->ntok, lane, gacc, acc);
+    mat_write_unit<NG, MODE, AccT>(m, u % upj, orow, first->ntok, lane, gacc, acc);
 }
 
 }  // namespace fnxb

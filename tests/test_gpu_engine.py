@@ -244,3 +244,24 @@ def test_engine_sampling_windows_follow_the_oracle_rule(F, O, model):
             eng.verify([x, 1, 2], [-1, 0, 0])          # the sampling rule is defined on chains
     finally:
         eng.set_sampling(None)
+
+
+def test_a_row_gives_the_same_bits_alone_and_among_drafts(F, model):
+    """Window invariance: a row's logits do not depend on the window it is verified in (attention partials are cut at
+    absolute positions, expert K-sums are accumulated in double, everything else is per row).  This is what makes
+    speculative output equal plain greedy output for any number of steps, not only up to the first near-tie."""
+    cfg, eng, _ = model
+    rng = np.random.default_rng(14)
+    prompt = rng.integers(0, cfg.vocab, size=70).tolist()
+    toks = rng.integers(0, cfg.vocab, size=5).tolist()
+    eng.reset()
+    eng.prefill(prompt)
+    eng.verify(toks)
+    together = eng.tensor("buf.logits", torch.float32).view(cfg.max_rows, cfg.vocab)[:5].clone()
+    eng.reset()
+    eng.prefill(prompt)
+    for i, t in enumerate(toks):
+        eng.verify([t])
+        eng.commit([0])
+        alone = eng.tensor("buf.logits", torch.float32).view(cfg.max_rows, cfg.vocab)[0]
+        assert torch.equal(alone, together[i]), f"row {i}"
