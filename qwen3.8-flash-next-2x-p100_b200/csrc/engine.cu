@@ -227,8 +227,11 @@ __global__ void k_ep_recv(const float* __restrict__ xbuf, const unsigned* __rest
     const int slot = (int) (seq & 1u);
     __shared__ bool ok;
     if (threadIdx.x == 0) {
+        // once a wait has given up (here or anywhere: the bit is sticky) nothing waits again: the window is lost anyway and
+        // the remaining exchanges must not each run out their limit
         bool all = false;
-        for (unsigned it = 0; it < 20000000u && !all; ++it) {
+        const bool gave_up = (*(volatile unsigned*) err & (unsigned) FNX_ERR_TIMEOUT) != 0;
+        for (unsigned it = 0; it < 2000000u && !all && !gave_up; ++it) {
             all = true;
             for (int r = 0; r < R; ++r) {
                 unsigned v;
