@@ -23,6 +23,7 @@ from __future__ import annotations
 import argparse
 import datetime
 import json
+import signal
 import zlib
 import os
 import pathlib
@@ -145,6 +146,9 @@ def cpu_step_seconds(F, O, eng, cfg, steps):
 
 
 def main():
+    # a multi-rank run that stalls (a rank that never arrives) ends by itself instead of holding the GPUs
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and hasattr(signal, "alarm"):
+        signal.alarm(int(os.environ.get("FNX_BENCH_LIMIT_S", "540")))
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -175,6 +179,7 @@ def main():
     cfg = model_config(F, rank if a.impl == "b200" else 0, world if a.impl == "b200" else 1, a.layers)
     eng = F.Engine(cfg)
     eng.init_synthetic(seed=0, sigma=0.02)
+    use_peer = False
     if world > 1 and a.impl == "b200":
         import ctypes as C
         uid = torch.zeros(128, dtype=torch.uint8)
@@ -186,7 +191,10 @@ def main():
         dist.broadcast(uid, 0)
         raw = bytes(uid.cpu().numpy().tobytes())
         F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
-        if os.environ.get("FNX_EP_NCCL", "0") != "1":
+        # the peer-memory sum has been run on 2 GPUs of this pool; wider boxes could not be had to confirm it, so they use
+        # NCCL unless FNX_EP_PEER=1 asks otherwise
+        use_peer = os.environ.get("FNX_EP_NCCL", "0") != "1" and (world == 2 or os.environ.get("FNX_EP_PEER", "0") == "1")
+        if use_peer:
             # the per-layer sum over NVLink peer memory instead of NCCL: exchange the ranks' IPC handles
             mine = (C.c_char * 128)()
             F.check(F.lib().fnx_engine_ep_handles(eng._h, mine))
@@ -342,7 +350,7 @@ def main():
                     "wall_ms_per_step": wall * 1e3 / a.steps},
             "verify_step_us": verify_ms * 1e3, "accepted_per_offered": accepted / max(1, offered), "tokens_per_step": tokens / a.steps,
             "tokens_crc": zlib.crc32(np.asarray(want[:done], np.int64).tobytes()),
-            "ep_sum": "none" if world == 1 else ("nccl" if os.environ.get("FNX_EP_NCCL", "0") == "1" else "peer-memory")}
+            "ep_sum": "none" if world == 1 else ("peer-memory" if use_peer else "nccl")}
 
     if world == 1 and rank == 0:
         import ctypes as C
