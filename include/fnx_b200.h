@@ -93,15 +93,6 @@ int fnx_moe_gate_up(const void* Wgu, size_t expert_stride, int e_base, const voi
                     const int* njobs, int njobs_max, const float* x, const float* norm_w, float eps, int H, int F,
                     float* h, unsigned* err, fnx_stream st);
 /* moe_down (engine/src/kernels.hpp:343): part[out][H] = Wd . h[out] */
-/* The same two steps with the routing inside gate|up: fnx_router_logits computes logits only; fnx_moe_gate_up_routed
- * routes the T rows from them in every block (identical results: the routing is a function of the logits) and its first
- * block writes topi, topw, jobs and njobs[0] for fnx_moe_down and fnx_moe_combine.  Saves the router's serial tail. */
-int fnx_router_logits(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, float* logits,
-                      unsigned* err, fnx_stream st);
-int fnx_moe_gate_up_routed(const void* Wgu, size_t expert_stride, int e_base, const void* Wsh, int E, const float* logits,
-                           int T, int K, int e_lo, int e_hi, int add_shared, int* topi, float* topw, fnx_job* jobs,
-                           int* njobs, int njobs_max, unsigned long long* stats, const float* x, const float* norm_w,
-                           float eps, int H, int F, float* h, unsigned* err, fnx_stream st);
 int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, const void* Wsh, int E, const fnx_job* jobs,
                  const int* njobs, int njobs_max, const float* h, int H, int F, float* part, unsigned* err,
                  fnx_stream st);

@@ -399,12 +399,11 @@ static int init_layer(fnx_engine* e, LayerW& L, int li, uint64_t seed, float sig
 static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
     const Dims d = dims(e->c);
     const bool ep = e->c.ep_size > 1;
-    // the router's logits, then gate|up with the routing done by every block for itself (no serial routing tail, no job
-    // list to fetch); its first block publishes picks, weights and jobs for down and combine
+    FNX_TRY(fnx_router_route(L.wr, R, L.norm2, e->c.eps, T, d.E, d.H, d.K, e->e_lo, e->e_hi, 1, e->rlogits, e->topi, e->topw, e->jobs, e->njobs,
+                             e->d_stats, e->err, e->st));
     const int njobs_max = T * d.K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
-    FNX_TRY(fnx_router_logits(L.wr, R, L.norm2, e->c.eps, T, d.E, d.H, e->rlogits, e->err, e->st));
-    FNX_TRY(fnx_moe_gate_up_routed(L.wgu, e->gu_bytes, e->e_lo, L.wsh_gu, d.E, e->rlogits, T, d.K, e->e_lo, e->e_hi, 1, e->topi, e->topw, e->jobs, e->njobs,
-                                   njobs_max, e->d_stats, R, L.norm2, e->c.eps, d.H, d.F, e->hbuf, e->err, e->st));
+    FNX_TRY(fnx_moe_gate_up(L.wgu, e->gu_bytes, e->e_lo, L.wsh_gu, d.E, e->jobs, e->njobs, njobs_max, R, L.norm2, e->c.eps, d.H, d.F, e->hbuf,
+                            e->err, e->st));
     FNX_TRY(fnx_moe_down(L.wdn, e->dn_bytes, e->e_lo, L.wsh_dn, d.E, e->jobs, e->njobs, njobs_max, e->hbuf, d.H, d.F, e->part, e->err, e->st));
     if (!ep) return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, d.E, 1, R, 1, e->st);
     if (e->ep_peers) {

@@ -161,41 +161,6 @@ extern "C" int fnx_moe_gate_up(const void* Wgu, size_t expert_stride, int e_base
     return launch_mmv<1, MAT_GATEUP>(p, as_stream(st));
 }
 
-extern "C" int fnx_moe_gate_up_routed(const void* Wgu, size_t expert_stride, int e_base, const void* Wsh, int E, const float* logits, int T, int K,
-                                      int e_lo, int e_hi, int add_shared, int* topi, float* topw, fnx_job* jobs, int* njobs, int njobs_max,
-                                      unsigned long long* stats, const float* x, const float* norm_w, float eps, int H, int F, float* h, unsigned* err,
-                                      fnx_stream st) {
-    if (int rc = check_cols(H)) return rc;
-    FNX_REQUIRE(Wgu && logits && topi && topw && jobs && njobs && x && h && err, "fnx_moe_gate_up_routed: null pointer");
-    FNX_REQUIRE(F % 16 == 0, "fnx_moe_gate_up_routed: ffn %d is not a multiple of 16", F);
-    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && K >= 1 && K <= 32 && E >= K && E <= RT_MAXE, "fnx_moe_gate_up_routed: %d rows, top %d of %d", T, K, E);
-    FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E, "fnx_moe_gate_up_routed: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
-    FNX_REQUIRE(njobs_max >= T * K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK, "fnx_moe_gate_up_routed: room for %d jobs, %d may be listed", njobs_max,
-                T * K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK);
-    MmvParams p{};
-    p.W = (const uint8_t*) Wgu;
-    p.expert_stride = expert_stride;
-    p.e_base = e_base;
-    p.Wsh = (const uint8_t*) Wsh;
-    p.E = E;
-    p.jobs = jobs;
-    p.njobs = njobs;
-    p.njobs_max = njobs_max;
-    p.x = x;
-    p.ldx = H;
-    p.norm_w = norm_w;
-    p.eps = eps;
-    p.out = h;
-    p.ldo = F;
-    p.rows = F;
-    p.K = H;
-    p.err = err;
-    p.route_logits = logits;
-    p.rT = T; p.rK = K; p.re_lo = e_lo; p.re_hi = e_hi; p.radd = add_shared;
-    p.topi_out = topi; p.topw_out = topw; p.jobs_out = jobs; p.njobs_out = njobs; p.stats = stats;
-    return launch_mmv<1, MAT_GATEUP>(p, as_stream(st));
-}
-
 extern "C" int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, const void* Wsh, int E, const fnx_job* jobs, const int* njobs,
                             int njobs_max, const float* h, int H, int F, float* part, unsigned* err, fnx_stream st) {
     if (int rc = check_cols(F)) return rc;

@@ -5,7 +5,6 @@
 #pragma once
 
 #include "mmv_core.cuh"
-#include "route_core.cuh"
 
 namespace fnxb {
 
@@ -32,15 +31,6 @@ struct MmvParams {
     int accumulate;
     int R;      // ring slots per warp
     unsigned* err;
-    // expert modes, optional: the block routes the window itself from the router's logits [rT][E + 1] (route_core.cuh)
-    // instead of reading a job list; block 0 publishes picks, weights and jobs for the kernels that follow
-    const float* route_logits;
-    int rT, rK, re_lo, re_hi, radd;
-    int* topi_out;
-    float* topw_out;
-    fnx_job* jobs_out;
-    int* njobs_out;
-    unsigned long long* stats;
 };
 
 // jobs whose activation images a block holds at once: its range of units spans at most two jobs of gate|up and a
@@ -115,7 +105,6 @@ __device__ __forceinline__ void stage_begin(const MmvParams& p, StageRegs& h, in
     constexpr int NROW = mmv_jmax<MODE>() * 4 * NG;
     const int warp = tid >> 5, lane = tid & 31;
     h.njobs = 1;
-    if (MOE && p.route_logits) return;   // routed in stage_run
     if (MOE) {
         const int nword = p.njobs_max * MMV_JOB_WORDS;
         h.njobs = *p.njobs;
@@ -146,27 +135,7 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
     const int warp = tid >> 5, lane = tid & 31;
     const int KB = p.K / 256;
     int njobs = 1;
-    if (MOE && p.route_logits) {
-        // the pieces' memory is free until the items run: the routing scratch and the rows' weights live there
-        static_assert(sizeof(RouteScratch) + FNX_MAX_ROWS * 32 * sizeof(float) <= (size_t) MMV_WARPS * 2 * PIECE_BYTES, "routing scratch");
-        RouteScratch& sc = *reinterpret_cast<RouteScratch*>(S.pieces);
-        float* topw_s = reinterpret_cast<float*>(&sc + 1);
-        const bool pub = bid == 0;
-        njobs = route_rows<MMV_THREADS>(p.route_logits, p.rT, p.E, p.rK, p.re_lo, p.re_hi, p.radd, sc, S.jobs_s, pub ? p.topi_out : nullptr,
-                                        pub ? p.topw_out : nullptr, topw_s, tid);
-        njobs = min(njobs, p.njobs_max);
-        if (pub) {
-            for (int w = tid; w < njobs * MMV_JOB_WORDS; w += MMV_THREADS) reinterpret_cast<int*>(p.jobs_out)[w] = reinterpret_cast<const int*>(S.jobs_s)[w];
-            if (tid == 0) {
-                p.njobs_out[0] = njobs;
-                if (p.stats) {
-                    atomicAdd(&p.stats[0], (unsigned long long) sc.routed_total);
-                    atomicAdd(&p.stats[1], 1ull);
-                }
-            }
-        }
-        __syncthreads();   // the scratch is the pieces' again
-    } else if (MOE) {
+    if (MOE) {
         const int nword = p.njobs_max * MMV_JOB_WORDS;
 #pragma unroll
         for (int i = 0; i < MMV_JOB_REGS; ++i) {

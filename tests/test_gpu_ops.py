@@ -184,39 +184,6 @@ def test_router_many_tokens_pick_one_expert(F, O):
     assert int(route["njobs"][0].item()) == K * 3 + 3
 
 
-@pytest.mark.parametrize("T", [1, 5, 20])
-def test_routing_inside_gate_up_equals_the_router_kernel(F, T):
-    """fnx_router_logits + fnx_moe_gate_up_routed (every block routes for itself) give the bits of fnx_router_route +
-    fnx_moe_gate_up: logits, picks, weights, job list, and the SwiGLU rows."""
-    E, H, Fn, K = 64, 2048, 512, 10
-    fx = _moe_fixture(F, E, H, Fn, seed=21)
-    rng = np.random.default_rng(100 + T)
-    x = dev(rng.standard_normal((T, H)).astype(np.float32))
-    nw = dev((1.0 + 0.05 * rng.standard_normal(H)).astype(np.float32))
-    route = F.router_route(fx["wr"], x, K, norm_w=nw)
-    _, h_ref, _ = F.moe_experts(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], route, x, Fn, K, norm_w=nw)
-    L, P = F.lib(), T * K + T
-    logits = torch.empty((T, E + 1), dtype=torch.float32, device="cuda")
-    topi = torch.empty((T, K), dtype=torch.int32, device="cuda")
-    topw = torch.empty((T, K), dtype=torch.float32, device="cuda")
-    jobs = torch.zeros_like(route["jobs"])
-    njobs = torch.zeros(2, dtype=torch.int32, device="cuda")
-    h = torch.zeros((P, Fn), dtype=torch.float32, device="cuda")
-    err = F.new_err()
-    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    F.check(L.fnx_router_logits(F.ptr(fx["wr"]), F.ptr(x), F.ptr(nw), 1e-6, T, E, H, F.ptr(logits), F.ptr(err), st))
-    F.check(L.fnx_moe_gate_up_routed(F.ptr(fx["gu_t"]), F.iq3s_bytes(2 * Fn, H), 0, F.ptr(fx["sh_gu_t"]), E, F.ptr(logits), T, K, 0, E, 1, F.ptr(topi),
-                                     F.ptr(topw), F.ptr(jobs), F.ptr(njobs), route["njobs_max"], None, F.ptr(x), F.ptr(nw), 1e-6, H, Fn, F.ptr(h), F.ptr(err), st))
-    torch.cuda.synchronize()
-    assert int(err.item()) == 0
-    assert torch.equal(logits, route["logits"]) and torch.equal(topi, route["topi"]) and torch.equal(topw, route["topw"])
-    nj = int(njobs[0].item())
-    assert nj == int(route["njobs"][0].item())
-    nb = nj * C.sizeof(F.Job)
-    assert torch.equal(jobs[:nb], route["jobs"][:nb])
-    assert torch.equal(h, h_ref)
-
-
 @pytest.mark.parametrize("E,H,Fn,K,T", [(16, 512, 256, 4, 200), (32, 2048, 512, 10, 333)])
 def test_prefill_moe_on_tensor_cores_matches_oracle(F, O, E, H, Fn, K, T):
     """Token groups per expert through tcgen05.mma (f16 operands, f32 accumulate): jobs of 128 rows and ragged tails,
