@@ -28,7 +28,7 @@ def vp(a):
 def ref_pins():
     O.build(ref=True)
     r = O.ref()
-    assert r is not None, "the reference pins need /root/reference"
+    assert r is not None, "the reference pins need a reference checkout (oracle/Makefile: REF)"
     rng = np.random.default_rng(100)
     d = {}
     blk = rng.integers(0, 256, size=(64, 110), dtype=np.uint8)
