@@ -98,8 +98,10 @@ class Clocks:
                 "samples": len(sm)}
 
 
-def model_config(F, ep_rank, ep_size, layers=48):
-    return F.flash_next_config(n_layer=layers, max_ctx=CTX + 1024, max_rows=32, ep_rank=ep_rank, ep_size=ep_size)
+def model_config(F, ep_rank, ep_size, layers=48, rounds=64, ctx=CTX):
+    # room for the context, every round's window of k + 1 rows, and the few single-row windows run afterwards
+    room = max(1024, (rounds + 8) * (K_DRAFT + 1) + 64)
+    return F.flash_next_config(n_layer=layers, max_ctx=ctx + (room + 255) // 256 * 256, max_rows=32, ep_rank=ep_rank, ep_size=ep_size)
 
 
 def step_bytes(routed_jobs_per_step: float, ctx: int, T: int):
@@ -176,7 +178,7 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    cfg = model_config(F, rank if a.impl == "b200" else 0, world if a.impl == "b200" else 1, a.layers)
+    cfg = model_config(F, rank if a.impl == "b200" else 0, world if a.impl == "b200" else 1, a.layers, a.warmup + a.steps, a.ctx)
     eng = F.Engine(cfg)
     eng.init_synthetic(seed=0, sigma=0.02)
     use_peer = False

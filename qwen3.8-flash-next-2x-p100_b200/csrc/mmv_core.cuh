@@ -283,36 +283,32 @@ struct QuantTask {
     int t, blk;
 };
 
-__device__ __forceinline__ void quant_fetch(const QuantTask& q, int lane, float (&v)[8]) {
+// (the block's norm weights ride with the values: one latency, not two)
+__device__ __forceinline__ void quant_fetch(const QuantTask& q, const float* norm_w, int lane, float (&v)[8], float (&w)[8]) {
     if (q.src) {
         const float4 a = *reinterpret_cast<const float4*>(q.src + lane * 8), b = *reinterpret_cast<const float4*>(q.src + lane * 8 + 4);
+        if (norm_w) {
+            const float4 c = *reinterpret_cast<const float4*>(norm_w + q.blk * 256 + lane * 8), d = *reinterpret_cast<const float4*>(norm_w + q.blk * 256 + lane * 8 + 4);
+            w[0] = c.x; w[1] = c.y; w[2] = c.z; w[3] = c.w;
+            w[4] = d.x; w[5] = d.y; w[6] = d.z; w[7] = d.w;
+        }
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     }
 }
 
-__device__ __forceinline__ void quant_finish(const QuantTask (&q)[QUANT_BATCH], float (&v)[QUANT_BATCH][8], int K, const float* norm_w, uint2* cells,
+__device__ __forceinline__ void quant_finish(const QuantTask (&q)[QUANT_BATCH], float (&v)[QUANT_BATCH][8], const float (&w)[QUANT_BATCH][8], int K, const float* norm_w, uint2* cells,
                                              float* scales, float* rs, int lane) {
     const int KB = K / 256;
     float am[QUANT_BATCH], ss[QUANT_BATCH];
-    if (norm_w) {
-        float4 w[QUANT_BATCH][2];
 #pragma unroll
-        for (int j = 0; j < QUANT_BATCH; ++j)
-            if (q[j].src) {
-                w[j][0] = *reinterpret_cast<const float4*>(norm_w + q[j].blk * 256 + lane * 8);
-                w[j][1] = *reinterpret_cast<const float4*>(norm_w + q[j].blk * 256 + lane * 8 + 4);
-            }
+    for (int j = 0; j < QUANT_BATCH; ++j) {
+        ss[j] = 0.f;
+        if (norm_w && q[j].src) {
 #pragma unroll
-        for (int j = 0; j < QUANT_BATCH; ++j) {
-            ss[j] = 0.f;
-            if (q[j].src) {
-                const float w8[8] = {w[j][0].x, w[j][0].y, w[j][0].z, w[j][0].w, w[j][1].x, w[j][1].y, w[j][1].z, w[j][1].w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    ss[j] = fmaf(v[j][i], v[j][i], ss[j]);
-                    v[j][i] *= w8[i];
-                }
+            for (int i = 0; i < 8; ++i) {
+                ss[j] = fmaf(v[j][i], v[j][i], ss[j]);
+                v[j][i] *= w[j][i];
             }
         }
     }

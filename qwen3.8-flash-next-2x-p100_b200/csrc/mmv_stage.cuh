@@ -69,6 +69,7 @@ struct StageRegs {
     int njobs;
     int jw[MMV_JOB_REGS];
     float v[QUANT_BATCH][8];
+    float w[QUANT_BATCH][8];   // their norm weights
 };
 
 // no-op transform of a fetched block (row t, block blk: 8 values per lane)
@@ -117,7 +118,7 @@ __device__ __forceinline__ void stage_begin(const MmvParams& p, StageRegs& h, in
 #pragma unroll
         for (int j = 0; j < QUANT_BATCH; ++j) {
             const QuantTask q = stage_dense_task(p, warp + j * MMV_WARPS);
-            quant_fetch(q, lane, h.v[j]);
+            quant_fetch(q, p.norm_w, lane, h.v[j], h.w[j]);
             if (q.src) post(q.t, q.blk, lane, h.v[j]);
         }
     }
@@ -193,11 +194,11 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
                     }
                 }
                 if (MOE || !first || id0 != warp) {
-                    quant_fetch(q[j], lane, h.v[j]);
+                    quant_fetch(q[j], norm_w, lane, h.v[j], h.w[j]);
                     if (!MOE && q[j].src) post(q[j].t, q[j].blk, lane, h.v[j]);
                 }
             }
-            quant_finish(q, h.v, p.K, norm_w, S.cells, S.scales, S.rs, lane);
+            quant_finish(q, h.v, h.w, p.K, norm_w, S.cells, S.scales, S.rs, lane);
         }
         {   // the rows that hold nothing
             constexpr int TPR = MMV_THREADS / NROW;   // threads per image row

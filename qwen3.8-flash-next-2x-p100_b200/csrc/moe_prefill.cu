@@ -228,7 +228,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         // the activations of this chunk: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies
 #pragma unroll
         for (int j = 0; j < PF_N * (PF_KC / 8) / PF_THREADS; ++j) {
-            const int i = tid + j * PF_THREADS, brow = i >> 4, piece = i & 15;
+            // consecutive lanes take consecutive rows of one 8-column piece: the eight 16-byte stores of a quarter warp fill one
+            // 128-byte core matrix (no bank conflicts); the global side reads half sectors, which the L2 absorbs
+            const int i = tid + j * PF_THREADS, brow = i & (PF_N - 1), piece = i / PF_N;
             const int src = src_s[brow];
             uint8_t* dst = B + pf_off(brow, piece * 8);
             if (src >= 0) {
