@@ -23,10 +23,12 @@ constexpr int PF_M = 128;         // features per block (tensor-memory lanes)
 constexpr int PF_N = 128;         // rows per job (tensor-memory columns per accumulator)
 constexpr int PF_KC = 128;        // K per stage: half a 256-column IQ3_S block
 constexpr int PF_THREADS = 512;
-constexpr int PF_REP = 16;         // copies of the codebook (entry e of copy r at word e * 16 + r): lanes l and l + 16 share one
-constexpr int PF_TILE = PF_M * PF_KC * 2;      // bytes of one f16 operand tile (128 x 128)
-constexpr int PF_LBO = 128;                    // bytes between core matrices (8 rows x 16 bytes) along K
-constexpr int PF_SBO = (PF_KC / 8) * 128;      // ... along the rows
+constexpr int PF_REP = 4;          // copies of the codebook (entry e of copy r at word e * 4 + r): lane l reads copy l % 4
+// Core matrices (8 rows x 16 bytes = 128 bytes) are laid 144 bytes apart along K: the 16-byte stores of a quarter warp of
+// the decode (two rows x four K pieces) then fall into two bank groups per row instead of one (2-way conflicts, not 4-way)
+constexpr int PF_LBO = 144;                    // bytes between core matrices along K
+constexpr int PF_SBO = (PF_KC / 8) * PF_LBO;   // ... along the rows
+constexpr int PF_TILE = (PF_M / 8) * PF_SBO;   // bytes of one f16 operand tile (128 x 128)
 
 struct PfJob {
     int w, n, start;   // expert, rows, first entry of `order`
@@ -114,7 +116,7 @@ __device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32
 template <int I>
 __device__ __forceinline__ uint32_t pf_decode(const uint32_t (&S)[5], const uint32_t (&G)[2], uint32_t table_s) {
     uint32_t mag;
-    const uint32_t a = table_s + (tile_field<I>(S) >> 1);   // the field is (index << 7): 64 bytes per entry (PF_REP copies); table_s: the lane's copy
+    const uint32_t a = table_s + (tile_field<I>(S) >> 3);   // the field is (index << 7): 16 bytes per entry (PF_REP copies); table_s: the lane's copy
     asm("ld.shared.u32 %0, [%1];" : "=r"(mag) : "r"(a));
     return tile_apply_sign(mag, tile_sign_mask<I>(G));
 }
