@@ -222,10 +222,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         const int s = c & 1, kb = c >> 1;
         uint8_t* A0 = stage0 + (size_t) s * STAGE;
         uint8_t* B = A0 + NA * PF_TILE;
-        if (c >= 2) {   // the stage is free when the tensor core has finished chunk c - 2
-            ok = __syncthreads_and(mbar_wait_bounded(&bars[s], (unsigned) (((c >> 1) - 1) & 1), 20000000u)) != 0;
+        bool gave_up = false;
+        if (c >= 2) {   // the stage is free when the tensor core has finished chunk c - 2 (a wait that gives up is reported at
+                        // the chunk's one block barrier below, where every thread takes the same exit)
+            gave_up = !mbar_wait_bounded(&bars[s], (unsigned) (((c >> 1) - 1) & 1), 20000000u);
             pf_fence_after();
-            if (!ok) break;
         }
         // the activations of this chunk: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies
 #pragma unroll
@@ -253,7 +254,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
-        __syncthreads();
+        if (__syncthreads_or(gave_up)) {
+            ok = false;
+            break;
+        }
         if (tid == 0) {
             pf_fence_after();
             const uint32_t a_s = smem_u32(A0), b_s = smem_u32(B);
@@ -440,13 +444,13 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     int* njobs = (int*) b;
     const int ne = e_hi - e_lo, n = T * K;
     if (ne > 0) {
-        k_pf_count<<<ne, 256, 0, st>>>(topi, n, e_lo, cnt);
+        k_pf_count<<<ne, 1024, 0, st>>>(topi, n, e_lo, cnt);
         FNX_LAUNCH_OK("k_pf_count");
     }
     k_pf_plan<<<1, 256, 0, st>>>(cnt, ne, e_lo, E, T, n, add_shared, base, jobs, njobs, order);
     FNX_LAUNCH_OK("k_pf_plan");
     if (ne > 0) {
-        k_pf_fill<<<ne, 256, 0, st>>>(topi, n, e_lo, base, order);
+        k_pf_fill<<<ne, 1024, 0, st>>>(topi, n, e_lo, base, order);
         FNX_LAUNCH_OK("k_pf_fill");
     }
     k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, H, eps, xh);
