@@ -104,7 +104,7 @@ int fnx_moe_combine(const float* part, const int* topi, const float* topw, const
 /* Prompt-sized MoE block (moe_gate_up_mma / moe_down_mma, engine/src/kernels.hpp:328-330, with the job build of
  * engine/src/prefill.cu:288-377): out[t] (+)= the routed experts in [e_lo, e_hi) and (add_shared) the shared expert of
  * rmsnorm(x[t]) * norm_w, for any number of rows T, given the routing (topi, topw [T][K], logits [T][E + 1]).  The
- * (row, pick) pairs are grouped by expert into jobs of up to 128 rows whose products run on the tensor cores
+ * (row, pick) pairs are grouped by expert into jobs of up to 256 rows whose products run on the tensor cores
  * (tcgen05.mma, f16 operands decoded from IQ3_S, f32 accumulators in tensor memory).  Not capture-safe: it reads the job
  * count back.  scratch: fnx_moe_prefill_scratch_bytes(T, K, E, H, F) bytes. */
 size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F);

@@ -2,14 +2,14 @@
 //
 // Replaces the reference's grouped expert GEMMs for prompts, moe_gate_up_mma / moe_down_mma
 // (engine/src/kernels.hpp:328-330, engine/src/moe_mma.cuh:301) and their job build k_pf_*
-// (engine/src/prefill.cu:288-377): the (token, pick) pairs are grouped by expert into jobs of up to 128 rows, and each
+// (engine/src/prefill.cu:288-377): the (token, pick) pairs are grouped by expert into jobs of up to 256 rows, and each
 // job's product runs as tcgen05.mma (kind::f16, f32 accumulators in tensor memory):
 //   A = a 128-feature slab of the expert's IQ3_S matrix, decoded by the block's warps straight from the tile layout
 //       (iq3s_tile.h) into f16 in the K-major core-matrix layout the instruction's shared-memory descriptor names;
 //   B = the job's activation rows (RMS-normed and rounded to f16 once per call; gathered by 16-byte async copies), same layout;
-//   D = [128 features (lanes)] x [128 rows (columns)] in tensor memory; gate|up keeps two of them and the epilogue
+//   D = [128 features (lanes)] x [256 rows (columns)] in tensor memory; gate|up keeps two of them and the epilogue
 //       applies SwiGLU while it reads them back (tcgen05.ld).
-// Two shared-memory stages: the warps decode K-chunk c + 1 while the tensor core works on chunk c; a stage is reused
+// Two shared-memory stages of 64 K columns: the warps decode K-chunk c + 1 while the tensor core works on chunk c; a stage is reused
 // when the tcgen05.commit of its chunk has arrived on the stage's mbarrier.  Every wait is bounded.
 #include <cuda_fp16.h>
 
@@ -20,15 +20,16 @@
 namespace fnxb {
 
 constexpr int PF_M = 128;         // features per block (tensor-memory lanes)
-constexpr int PF_N = 128;         // rows per job (tensor-memory columns per accumulator)
-constexpr int PF_KC = 128;        // K per stage: half a 256-column IQ3_S block
+constexpr int PF_N = 256;         // rows per job (tensor-memory columns per accumulator): a decoded weight slab serves them all
+constexpr int PF_KC = 64;         // K per stage: a quarter of a 256-column IQ3_S block (two sub-blocks)
 constexpr int PF_THREADS = 512;
 constexpr int PF_REP = 4;          // copies of the codebook (entry e of copy r at word e * 4 + r): lane l reads copy l % 4
 // Core matrices (8 rows x 16 bytes = 128 bytes) are laid 144 bytes apart along K: the 16-byte stores of a quarter warp of
 // the decode (two rows x four K pieces) then fall into two bank groups per row instead of one (2-way conflicts, not 4-way)
 constexpr int PF_LBO = 144;                    // bytes between core matrices along K
 constexpr int PF_SBO = (PF_KC / 8) * PF_LBO;   // ... along the rows
-constexpr int PF_TILE = (PF_M / 8) * PF_SBO;   // bytes of one f16 operand tile (128 x 128)
+constexpr int PF_TILE_A = (PF_M / 8) * PF_SBO; // bytes of one f16 weight tile (128 features x 64)
+constexpr int PF_TILE_B = (PF_N / 8) * PF_SBO; // ... of the activation tile (256 rows x 64)
 
 struct PfJob {
     int w, n, start;   // expert, rows, first entry of `order`
@@ -126,28 +127,22 @@ __device__ __forceinline__ uint32_t pf_decode(const uint32_t (&S)[5], const uint
 // (the tile layout pairs them with the activation cells of 8 consecutive columns, iq3s_tile.h).
 template <int SB>
 __device__ __forceinline__ void pf_sub_block(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
-    const int g = lane >> 2, q = lane & 3, k0 = (SB & 3) * 32 + 8 * q;
+    const int g = lane >> 2, q = lane & 3, k0 = (SB & 1) * 32 + 8 * q;
     const __half2 f0 = __float2half2_rn(r.d0 * (float) (1 + 2 * (int) ((r.sn0 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u)));
     const __half2 f1 = __float2half2_rn(r.d1 * (float) (1 + 2 * (int) ((r.sn1 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u)));
     pf_store8(tileA, row0 + g, k0, pf_decode<2 * SB>(r.S0, r.G0, table_s), pf_decode<2 * SB + 1>(r.S0, r.G0, table_s), f0);
     pf_store8(tileA, row0 + g + 8, k0, pf_decode<2 * SB>(r.S1, r.G1, table_s), pf_decode<2 * SB + 1>(r.S1, r.G1, table_s), f1);
 }
-// sub-blocks [4 HALF + 2 PAIR, + 2) of a tile block
-template <int HALF, int PAIR>
-__device__ __forceinline__ void pf_two_sub_blocks(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s) {
-    pf_sub_block<4 * HALF + 2 * PAIR + 0>(r, tileA, row0, lane, table_s);
-    pf_sub_block<4 * HALF + 2 * PAIR + 1>(r, tileA, row0, lane, table_s);
-}
-// the warp's share of chunk-half HALF: gate|up (sel = which matrix): all four sub-blocks; down (sel = which pair): two
-template <int HALF, int MODE>
-__device__ __forceinline__ void pf_warp_share(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s, int sel) {
+// the warp's share of quarter Q of a tile block (sub-blocks 2 Q, 2 Q + 1): gate|up: both; down (two warps per tile): one
+template <int Q, int MODE>
+__device__ __forceinline__ void pf_quarter(const PfRaw& r, uint8_t* tileA, int row0, int lane, uint32_t table_s, int sel) {
     if (MODE == 1) {
-        pf_two_sub_blocks<HALF, 0>(r, tileA, row0, lane, table_s);
-        pf_two_sub_blocks<HALF, 1>(r, tileA, row0, lane, table_s);
+        pf_sub_block<2 * Q>(r, tileA, row0, lane, table_s);
+        pf_sub_block<2 * Q + 1>(r, tileA, row0, lane, table_s);
     } else if (sel == 0) {
-        pf_two_sub_blocks<HALF, 0>(r, tileA, row0, lane, table_s);
+        pf_sub_block<2 * Q>(r, tileA, row0, lane, table_s);
     } else {
-        pf_two_sub_blocks<HALF, 1>(r, tileA, row0, lane, table_s);
+        pf_sub_block<2 * Q + 1>(r, tileA, row0, lane, table_s);
     }
 }
 
@@ -172,7 +167,7 @@ template <int MODE>
 __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NA = MODE == 1 ? 2 : 1;                      // weight tiles per stage
-    constexpr int STAGE = (NA + 1) * PF_TILE;
+    constexpr int STAGE = NA * PF_TILE_A + PF_TILE_B;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* stage0 = smem;                                    // 2 stages: [A0 | (A1) | B]
     uint32_t* table = reinterpret_cast<uint32_t*>(smem + 2 * STAGE);          // the codebook, PF_REP copies
@@ -207,7 +202,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     __syncthreads();
     pf_fence_after();
     const uint32_t tmem = *tmem_slot, table_s = smem_u32(table) + (uint32_t) (lane % PF_REP) * 4u;
-    // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
+    // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 256, M = 128
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (PF_N >> 3) << 17) | ((uint32_t) (PF_M >> 4) << 24);
     bool ok = true;
     // 16 warps: warp w decodes tile row (w % 8) of the 128-feature slab; gate|up: of the gate (w < 8) or the up matrix
@@ -215,13 +210,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     PfRaw raw, nxt;
     const int sel = warp >> 3;
     const int trow = (MODE == 1 && sel ? p.rows / 16 : 0) + ft * (PF_M / 16) + (warp & 7);
-    const int a_off = MODE == 1 && sel ? PF_TILE : 0, row0 = (warp & 7) * 16;
+    const int a_off = MODE == 1 && sel ? PF_TILE_A : 0, row0 = (warp & 7) * 16;
     auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
     load_raw(0, raw);
     for (int c = 0; c < nchunk; ++c) {
-        const int s = c & 1, kb = c >> 1;
+        const int s = c & 1, kb = c >> 2, quarter = c & 3;
         uint8_t* A0 = stage0 + (size_t) s * STAGE;
-        uint8_t* B = A0 + NA * PF_TILE;
+        uint8_t* B = A0 + NA * PF_TILE_A;
         bool gave_up = false;
         if (c >= 2) {   // the stage is free when the tensor core has finished chunk c - 2 (a wait that gives up is reported at
                         // the chunk's one block barrier below, where every thread takes the same exit)
@@ -245,12 +240,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         // the weights of this chunk: four sub-blocks of the warp's tile(s); the next block's bytes are fetched meanwhile
-        if ((c & 1) == 0) {
-            pf_warp_share<0, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
-            if (kb + 1 < KB) load_raw(kb + 1, nxt);
-        } else {
-            pf_warp_share<1, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
-            raw = nxt;
+        switch (quarter) {
+            case 0:
+                pf_quarter<0, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
+                if (kb + 1 < KB) load_raw(kb + 1, nxt);
+                break;
+            case 1: pf_quarter<1, MODE>(raw, A0 + a_off, row0, lane, table_s, sel); break;
+            case 2: pf_quarter<2, MODE>(raw, A0 + a_off, row0, lane, table_s, sel); break;
+            default:
+                pf_quarter<3, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
+                raw = nxt;
+                break;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
             for (int k16 = 0; k16 < PF_KC / 16; ++k16) {
                 const uint64_t bd = pf_desc(b_s + k16 * 2 * PF_LBO);
                 pf_mma(tmem, pf_desc(a_s + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
-                if (NA == 2) pf_mma(tmem + PF_N, pf_desc(a_s + PF_TILE + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
+                if (NA == 2) pf_mma(tmem + PF_N, pf_desc(a_s + PF_TILE_A + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
             }
             pf_commit(&bars[s]);
         }
@@ -275,23 +275,28 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     pf_fence_after();
     if (!ok && tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
     if (ok) {
-        // warp w reads lanes 32 (w % 4) .. + 31 (its features), columns 32 (w / 4) .. + 31 (job rows)
-        const int f = ft * PF_M + 32 * (warp & 3) + lane, col0 = (warp >> 2) * 32;
-        const uint32_t ta = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) col0;
-        float g[32];
-        pf_ld32(ta, g);
-        if (MODE == 1) {
-            float u[32];
-            pf_ld32(ta + PF_N, u);
+        // warp w reads lanes 32 (w % 4) .. + 31 (its features), columns 64 (w / 4) .. + 63 (job rows), 32 at a time
+        const int f = ft * PF_M + 32 * (warp & 3) + lane;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            const int col0 = (warp >> 2) * 64 + hh * 32;
+            if (col0 >= job.n) break;
+            const uint32_t ta = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) col0;
+            float g[32];
+            pf_ld32(ta, g);
+            if (MODE == 1) {
+                float u[32];
+                pf_ld32(ta + PF_N, u);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (col0 + i < job.n) {
-                if (MODE == 1) p.outh[(size_t) out_s[col0 + i] * p.rows + f] = __float2half_rn(g[i]);
-                else p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+                for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
             }
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (col0 + i < job.n) {
+                    if (MODE == 1) p.outh[(size_t) out_s[col0 + i] * p.rows + f] = __float2half_rn(g[i]);
+                    else p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+                }
+        }
     }
     pf_fence_before();
     __syncthreads();
@@ -409,7 +414,7 @@ __global__ void k_pf_combine(const float* __restrict__ part, const int* __restri
     *o = accumulate ? *o + s : s;
 }
 
-constexpr size_t pf_smem(int mode) { return (size_t) 2 * ((mode == 1 ? 2 : 1) + 1) * PF_TILE + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
+constexpr size_t pf_smem(int mode) { return (size_t) 2 * ((mode == 1 ? 2 : 1) * PF_TILE_A + PF_TILE_B) + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
 
 }  // namespace fnxb
 
