@@ -9,7 +9,7 @@
 //   B = the job's activation rows (RMS-normed and rounded to f16 once per call; gathered by 16-byte async copies), same layout;
 //   D = [128 features (lanes)] x [256 rows (columns)] in tensor memory; gate|up keeps two of them and the epilogue
 //       applies SwiGLU while it reads them back (tcgen05.ld).
-// Two shared-memory stages of 64 K columns: the warps decode K-chunk c + 1 while the tensor core works on chunk c; a stage is reused
+// Three shared-memory stages of 64 K columns: the warps decode ahead while the tensor core works on earlier chunks; a stage is reused
 // when the tcgen05.commit of its chunk has arrived on the stage's mbarrier.  Every wait is bounded.
 #include <cuda_fp16.h>
 
@@ -23,6 +23,7 @@ constexpr int PF_M = 128;         // features per block (tensor-memory lanes)
 constexpr int PF_N = 256;         // rows per job (tensor-memory columns per accumulator): a decoded weight slab serves them all
 constexpr int PF_KC = 64;         // K per stage: a quarter of a 256-column IQ3_S block (two sub-blocks)
 constexpr int PF_THREADS = 512;
+constexpr int PF_STAGES = 3;      // operand stages in shared memory: the decode runs up to two chunks ahead of the tensor core
 constexpr int PF_REP = 4;          // copies of the codebook (entry e of copy r at word e * 4 + r): lane l reads copy l % 4
 // Core matrices (8 rows x 16 bytes = 128 bytes) are laid 144 bytes apart along K: the 16-byte stores of a quarter warp of
 // the decode (two rows x four K pieces) then fall into two bank groups per row instead of one (2-way conflicts, not 4-way)
@@ -169,12 +170,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     constexpr int NA = MODE == 1 ? 2 : 1;                      // weight tiles per stage
     constexpr int STAGE = NA * PF_TILE_A + PF_TILE_B;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint8_t* stage0 = smem;                                    // 2 stages: [A0 | (A1) | B]
-    uint32_t* table = reinterpret_cast<uint32_t*>(smem + 2 * STAGE);          // the codebook, PF_REP copies
+    uint8_t* stage0 = smem;                                    // PF_STAGES stages: [A0 | (A1) | B]
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem + PF_STAGES * STAGE);          // the codebook, PF_REP copies
     int* src_s = reinterpret_cast<int*>(table + 512 * PF_REP);          // [PF_N] activation row per job row (-1: none)
     int* out_s = src_s + PF_N;                                 // [PF_N] output row
-    uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [2] stage free
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [PF_STAGES] stage free
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PF_STAGES);
     const PfJob job = p.jobs[blockIdx.x];
     const int ft = blockIdx.y, KB = p.K / 256, nchunk = p.K / PF_KC;
     const uint8_t* W = job.w >= p.E ? p.Wsh : p.W + (size_t) (job.w - p.e_base) * p.expert_stride;
@@ -190,8 +191,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         out_s[tid] = o;
     }
     if (tid == 0) {
-        mbar_init(&bars[0], 1);
-        mbar_init(&bars[1], 1);
+        for (int i = 0; i < PF_STAGES; ++i) mbar_init(&bars[i], 1);
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -214,13 +214,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
     load_raw(0, raw);
     for (int c = 0; c < nchunk; ++c) {
-        const int s = c & 1, kb = c >> 2, quarter = c & 3;
+        const int s = c % PF_STAGES, use = c / PF_STAGES, kb = c >> 2, quarter = c & 3;
         uint8_t* A0 = stage0 + (size_t) s * STAGE;
         uint8_t* B = A0 + NA * PF_TILE_A;
         bool gave_up = false;
-        if (c >= 2) {   // the stage is free when the tensor core has finished chunk c - 2 (a wait that gives up is reported at
+        if (c >= PF_STAGES) {   // the stage is free when the tensor core has finished its previous chunk (a wait that gives up is reported at
                         // the chunk's one block barrier below, where every thread takes the same exit)
-            gave_up = !mbar_wait_bounded(&bars[s], (unsigned) (((c >> 1) - 1) & 1), 20000000u);
+            gave_up = !mbar_wait_bounded(&bars[s], (unsigned) ((use - 1) & 1), 20000000u);
             pf_fence_after();
         }
         // the activations of this chunk: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         }
     }
     // all chunks issued: the last commit arrives when every earlier product has finished too
-    if (ok) ok = __syncthreads_and(mbar_wait_bounded(&bars[(nchunk - 1) & 1], (unsigned) (((nchunk - 1) >> 1) & 1), 20000000u)) != 0;
+    if (ok) ok = __syncthreads_and(mbar_wait_bounded(&bars[(nchunk - 1) % PF_STAGES], (unsigned) (((nchunk - 1) / PF_STAGES) & 1), 20000000u)) != 0;
     pf_fence_after();
     if (!ok && tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
     if (ok) {
@@ -414,7 +414,7 @@ __global__ void k_pf_combine(const float* __restrict__ part, const int* __restri
     *o = accumulate ? *o + s : s;
 }
 
-constexpr size_t pf_smem(int mode) { return (size_t) 2 * ((mode == 1 ? 2 : 1) * PF_TILE_A + PF_TILE_B) + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
+constexpr size_t pf_smem(int mode) { return (size_t) PF_STAGES * ((mode == 1 ? 2 : 1) * PF_TILE_A + PF_TILE_B) + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
 
 }  // namespace fnxb
 
