@@ -455,7 +455,7 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     k_pf_plan<<<1, 256, 0, st>>>(cnt, ne, e_lo, E, T, n, add_shared, base, jobs, njobs, order);
     FNX_LAUNCH_OK("k_pf_plan");
     if (ne > 0) {
-        k_pf_fill<<<ne, 1024, 0, st>>>(topi, n, e_lo, base, order);
+        k_pf_fill<<<ne, 256, 0, st>>>(topi, n, e_lo, base, order);
         FNX_LAUNCH_OK("k_pf_fill");
     }
     k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, H, eps, xh);
