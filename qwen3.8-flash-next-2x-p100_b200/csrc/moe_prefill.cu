@@ -213,17 +213,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     const int a_off = MODE == 1 && sel ? PF_TILE_A : 0, row0 = (warp & 7) * 16;
     auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
     load_raw(0, raw);
-    for (int c = 0; c < nchunk; ++c) {
-        const int s = c % PF_STAGES, use = c / PF_STAGES, kb = c >> 2, quarter = c & 3;
-        uint8_t* A0 = stage0 + (size_t) s * STAGE;
-        uint8_t* B = A0 + NA * PF_TILE_A;
-        bool gave_up = false;
-        if (c >= PF_STAGES) {   // the stage is free when the tensor core has finished its previous chunk (a wait that gives up is reported at
-                        // the chunk's one block barrier below, where every thread takes the same exit)
-            gave_up = !mbar_wait_bounded(&bars[s], (unsigned) ((use - 1) & 1), 20000000u);
-            pf_fence_after();
-        }
-        // the activations of this chunk: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies
+    // the activations of chunk c into its stage: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies;
+    // they run one chunk ahead of the decode, so their latency hides behind it
+    auto issue_b = [&](int c) {
+        uint8_t* B = stage0 + (size_t) (c % PF_STAGES) * STAGE + NA * PF_TILE_A;
 #pragma unroll
         for (int j = 0; j < PF_N * (PF_KC / 8) / PF_THREADS; ++j) {
             // consecutive lanes take consecutive rows of one 8-column piece: the eight 16-byte stores of a quarter warp fill one
@@ -237,6 +230,23 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
             } else {
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
+        }
+    };
+    issue_b(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int c = 0; c < nchunk; ++c) {
+        const int s = c % PF_STAGES, kb = c >> 2, quarter = c & 3;
+        uint8_t* A0 = stage0 + (size_t) s * STAGE;
+        uint8_t* B = A0 + NA * PF_TILE_A;
+        bool gave_up = false;
+        if (c + 1 < nchunk) {
+            // the next chunk's stage is free when the tensor core has finished the chunk that used it (a wait that gives up is
+            // reported at the chunk's one block barrier below, where every thread takes the same exit)
+            if (c + 1 >= PF_STAGES) {
+                gave_up = !mbar_wait_bounded(&bars[(c + 1) % PF_STAGES], (unsigned) (((c + 1) / PF_STAGES - 1) & 1), 20000000u);
+                pf_fence_after();
+            }
+            issue_b(c + 1);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         // the weights of this chunk: four sub-blocks of the warp's tile(s); the next block's bytes are fetched meanwhile
@@ -252,7 +262,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
                 raw = nxt;
                 break;
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");   // this chunk's activations are in; the next chunk's may still fly
         fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
         if (__syncthreads_or(gave_up)) {
             ok = false;
