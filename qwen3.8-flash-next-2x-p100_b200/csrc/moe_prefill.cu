@@ -412,16 +412,41 @@ __global__ void k_pf_xnorm(const float* __restrict__ x, const float* __restrict_
 // out[t] (+)= sum_k topw[t][k] part[t Kp + k] + sigmoid(logit[t][E]) part[T Kp + t]
 __global__ void k_pf_combine(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw, const float* __restrict__ logits,
                              int T, int E, int H, int Kp, int e_lo, int e_hi, int add_shared, float* __restrict__ out, int accumulate) {
-    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    // a thread owns four columns of one row; the picks' weights first, then every addend's 16-byte load in flight at once
+    const int t = blockIdx.y, i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= H) return;
-    float s = 0.f;
-    for (int k = 0; k < Kp; ++k) {
-        const int e = topi[t * Kp + k];
-        if (e >= e_lo && e < e_hi) s = fmaf(topw[t * Kp + k], part[((size_t) t * Kp + k) * H + i], s);
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < Kp; k0 += 16) {   // sixteen picks at a time (the sum stays in pick order)
+        float w[16];
+        float4 v[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            w[k] = 0.f;
+            if (k0 + k < Kp) {
+                const int e = topi[t * Kp + k0 + k];
+                w[k] = e >= e_lo && e < e_hi ? topw[t * Kp + k0 + k] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            v[k] = w[k] != 0.f ? *reinterpret_cast<const float4*>(part + ((size_t) t * Kp + k0 + k) * H + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            s.x = fmaf(w[k], v[k].x, s.x); s.y = fmaf(w[k], v[k].y, s.y);
+            s.z = fmaf(w[k], v[k].z, s.z); s.w = fmaf(w[k], v[k].w, s.w);
+        }
     }
-    if (add_shared) s += sigmoidf_(logits[(size_t) t * (E + 1) + E]) * part[((size_t) T * Kp + t) * H + i];
-    float* o = out + (size_t) t * H + i;
-    *o = accumulate ? *o + s : s;
+    if (add_shared) {
+        const float g = sigmoidf_(logits[(size_t) t * (E + 1) + E]);
+        const float4 sh = *reinterpret_cast<const float4*>(part + ((size_t) T * Kp + t) * H + i);
+        s.x += g * sh.x; s.y += g * sh.y; s.z += g * sh.z; s.w += g * sh.w;
+    }
+    float4* o = reinterpret_cast<float4*>(out + (size_t) t * H + i);
+    if (accumulate) {
+        const float4 p0 = *o;
+        s.x += p0.x; s.y += p0.y; s.z += p0.z; s.w += p0.w;
+    }
+    *o = s;
 }
 
 constexpr size_t pf_smem(int mode) { return (size_t) PF_STAGES * ((mode == 1 ? 2 : 1) * PF_TILE_A + PF_TILE_B) + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
@@ -491,7 +516,7 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
         k_pf_gemm<0><<<dim3(nj, H / PF_M), PF_THREADS, pf_smem(0), st>>>(p);
         FNX_LAUNCH_OK("k_pf_gemm (down)");
     }
-    k_pf_combine<<<dim3((H + 255) / 256, T), 256, 0, st>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
+    k_pf_combine<<<dim3((H / 4 + 255) / 256, T), 256, 0, st>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
     FNX_LAUNCH_OK("k_pf_combine");
     return FNX_OK;
 }
