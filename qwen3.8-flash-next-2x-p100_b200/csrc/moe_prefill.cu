@@ -354,25 +354,45 @@ __global__ void k_pf_plan(const int* __restrict__ cnt, int ne, int e_lo, int E, 
     if (threadIdx.x == 0) njobs[0] = nj + (add_shared ? (T + PF_N - 1) / PF_N : 0);
 }
 
-// per expert: its pairs in ascending order into order[base ..)
+// per expert: its pairs in ascending order into order[base ..): a thread looks at four consecutive pairs per step
 __global__ void k_pf_fill(const int* __restrict__ topi, int n, int e_lo, const int* __restrict__ base, int* __restrict__ order) {
     const int e = e_lo + blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x / 32;
     __shared__ int ws[32], s_run;
     if (tid == 0) s_run = base[blockIdx.x];
     __syncthreads();
-    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
-        const int i = i0 + tid;
-        const bool m = i < n && topi[i] == e;
-        const unsigned bal = __ballot_sync(0xffffffffu, m);
-        if (lane == 0) ws[warp] = __popc(bal);
+    const bool vec = (((uintptr_t) topi) & 15) == 0;
+    for (int i0 = 0; i0 < n; i0 += blockDim.x * 4) {
+        const int i = i0 + tid * 4;
+        int v[4] = {-1, -1, -1, -1};
+        if (vec && i + 3 < n) {
+            const int4 q = *reinterpret_cast<const int4*>(topi + i);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + j < n) v[j] = topi[i + j];
+        }
+        int c = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c += v[j] == e;
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
+        }
+        if (lane == 31) ws[warp] = incl;
         __syncthreads();
-        int before = 0, total = 0;
+        int before = incl - c, total = 0;
         for (int w = 0; w < nw; ++w) {
             if (w < warp) before += ws[w];
             total += ws[w];
         }
         const int run = s_run;
-        if (m) order[run + before + __popc(bal & ((1u << lane) - 1u))] = i;
+        int at = run + before;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (v[j] == e) order[at++] = i + j;
         __syncthreads();
         if (tid == 0) s_run = run + total;
         __syncthreads();
