@@ -334,19 +334,30 @@ __global__ void k_pf_count(const int* __restrict__ topi, int n, int e_lo, int* _
 // one block: the experts' first entries and jobs (ascending expert order, then the shared expert's)
 __global__ void k_pf_plan(const int* __restrict__ cnt, int ne, int e_lo, int E, int T, int TKp, int add_shared, int* __restrict__ base, PfJob* __restrict__ jobs,
                           int* __restrict__ njobs, int* __restrict__ order) {
-    __shared__ int s_entry, s_job;
+    // counts into shared memory, one thread's running sums over them (a few hundred shared-memory steps), then every thread
+    // writes its experts' jobs
+    __shared__ int s_cnt[1024], s_entry[1024], s_job[1024];
+    __shared__ int s_entries, s_jobs;
+    for (int e = threadIdx.x; e < ne; e += blockDim.x) s_cnt[e] = cnt[e];
+    __syncthreads();
     if (threadIdx.x == 0) {
         int entry = 0, nj = 0;
         for (int e = 0; e < ne; ++e) {
-            base[e] = entry;
-            for (int o = 0; o < cnt[e]; o += PF_N) jobs[nj++] = PfJob{e_lo + e, min(PF_N, cnt[e] - o), entry + o};
-            entry += cnt[e];
+            s_entry[e] = entry;
+            s_job[e] = nj;
+            entry += s_cnt[e];
+            nj += (s_cnt[e] + PF_N - 1) / PF_N;
         }
-        s_entry = entry;
-        s_job = nj;
+        s_entries = entry;
+        s_jobs = nj;
     }
     __syncthreads();
-    const int entry = s_entry, nj = s_job;
+    for (int e = threadIdx.x; e < ne; e += blockDim.x) {
+        base[e] = s_entry[e];
+        int j = s_job[e];
+        for (int o = 0; o < s_cnt[e]; o += PF_N) jobs[j++] = PfJob{e_lo + e, min(PF_N, s_cnt[e] - o), s_entry[e] + o};
+    }
+    const int entry = s_entries, nj = s_jobs;
     if (add_shared) {
         for (int t = threadIdx.x; t < T; t += blockDim.x) order[entry + t] = TKp + t;
         for (int j = threadIdx.x; j < (T + PF_N - 1) / PF_N; j += blockDim.x) jobs[nj + j] = PfJob{E, min(PF_N, T - j * PF_N), entry + j * PF_N};
@@ -488,6 +499,7 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
                                const float* norm_w, float eps, int T, int H, int F, float* out, int accumulate, void* scratch, unsigned* err, fnx_stream st_) {
     FNX_REQUIRE(Wgu && Wdn && topi && topw && logits && x && out && scratch && err, "fnx_moe_prefill: null pointer");
     FNX_REQUIRE(T >= 1 && K >= 1 && K <= 32, "fnx_moe_prefill: %d rows, top %d", T, K);
+    FNX_REQUIRE(E >= 1 && E <= 1024, "fnx_moe_prefill: %d experts (at most 1024)", E);
     FNX_REQUIRE(H % 256 == 0 && F % 256 == 0 && F % PF_M == 0 && H % PF_M == 0, "fnx_moe_prefill: hidden %d, ffn %d (multiples of 256)", H, F);
     FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E && (!add_shared || (Wsh_gu && Wsh_dn)), "fnx_moe_prefill: expert range [%d, %d) of %d", e_lo, e_hi, E);
     FNX_REQUIRE((long long) T * K + T < (1ll << 30), "fnx_moe_prefill: %d rows are too many", T);
