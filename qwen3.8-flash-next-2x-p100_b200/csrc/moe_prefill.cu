@@ -22,7 +22,8 @@ namespace fnxb {
 constexpr int PF_M = 128;         // features per block (tensor-memory lanes)
 constexpr int PF_N = 256;         // rows per job (tensor-memory columns per accumulator): a decoded weight slab serves them all
 constexpr int PF_KC = 64;         // K per stage: a quarter of a 256-column IQ3_S block (two sub-blocks)
-constexpr int PF_THREADS = 512;
+constexpr int PF_THREADS = 512;     // decode threads (16 warps)
+constexpr int PF_BLOCK = PF_THREADS + 32;   // + the warp whose lane 0 issues the tensor-core work
 constexpr int PF_STAGES = 3;      // operand stages in shared memory: the decode runs up to two chunks ahead of the tensor core
 constexpr int PF_REP = 4;          // copies of the codebook (entry e of copy r at word e * 4 + r): lane l reads copy l % 4
 // Core matrices (8 rows x 16 bytes = 128 bytes) are laid 144 bytes apart along K: the 16-byte stores of a quarter warp of
@@ -165,7 +166,7 @@ struct PfParams {
 
 // MODE 0: out = x W^T (down).  MODE 1: out = silu(x Wg^T) * (x Wu^T) (gate|up; W = [gate (rows); up (rows)]).
 template <int MODE>
-__global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
+__global__ void __launch_bounds__(PF_BLOCK, 1) k_pf_gemm(const PfParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NA = MODE == 1 ? 2 : 1;                      // weight tiles per stage
     constexpr int STAGE = NA * PF_TILE_A + PF_TILE_B;
@@ -174,12 +175,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     uint32_t* table = reinterpret_cast<uint32_t*>(smem + PF_STAGES * STAGE);          // the codebook, PF_REP copies
     int* src_s = reinterpret_cast<int*>(table + 512 * PF_REP);          // [PF_N] activation row per job row (-1: none)
     int* out_s = src_s + PF_N;                                 // [PF_N] output row
-    uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [PF_STAGES] stage free
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PF_STAGES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [PF_STAGES] stage free (the tensor core's commit)
+    uint64_t* full = bars + PF_STAGES;                            // [PF_STAGES] stage filled (one arrival per decode warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full + PF_STAGES);
     const PfJob job = p.jobs[blockIdx.x];
     const int ft = blockIdx.y, KB = p.K / 256, nchunk = p.K / PF_KC;
     const uint8_t* W = job.w >= p.E ? p.Wsh : p.W + (size_t) (job.w - p.e_base) * p.expert_stride;
-    for (int i = tid; i < 512 * PF_REP; i += PF_THREADS) table[i] = g_grid_pf[i / PF_REP];
+    for (int i = tid; i < 512 * PF_REP; i += PF_BLOCK) table[i] = g_grid_pf[i / PF_REP];
     if (tid < PF_N) {
         int src = -1, o = 0;
         if (tid < job.n) {
@@ -191,7 +193,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
         out_s[tid] = o;
     }
     if (tid == 0) {
-        for (int i = 0; i < PF_STAGES; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < PF_STAGES; ++i) {
+            mbar_init(&bars[i], 1);
+            mbar_init(&full[i], PF_THREADS / 32);
+        }
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -205,86 +210,100 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pf_gemm(const PfParams p) {
     // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 256, M = 128
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (PF_N >> 3) << 17) | ((uint32_t) (PF_M >> 4) << 24);
     bool ok = true;
-    // 16 warps: warp w decodes tile row (w % 8) of the 128-feature slab; gate|up: of the gate (w < 8) or the up matrix
-    // (all four sub-blocks of the chunk); down: sub-block pair w / 8 of the chunk
-    PfRaw raw, nxt;
-    const int sel = warp >> 3;
-    const int trow = (MODE == 1 && sel ? p.rows / 16 : 0) + ft * (PF_M / 16) + (warp & 7);
-    const int a_off = MODE == 1 && sel ? PF_TILE_A : 0, row0 = (warp & 7) * 16;
-    auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
-    load_raw(0, raw);
-    // the activations of chunk c into its stage: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies;
-    // they run one chunk ahead of the decode, so their latency hides behind it
-    auto issue_b = [&](int c) {
-        uint8_t* B = stage0 + (size_t) (c % PF_STAGES) * STAGE + NA * PF_TILE_A;
-#pragma unroll
-        for (int j = 0; j < PF_N * (PF_KC / 8) / PF_THREADS; ++j) {
-            // consecutive lanes take consecutive rows of one 8-column piece: the eight 16-byte stores of a quarter warp fill one
-            // 128-byte core matrix (no bank conflicts); the global side reads half sectors, which the L2 absorbs
-            const int i = tid + j * PF_THREADS, brow = i & (PF_N - 1), piece = i / PF_N;
-            const int src = src_s[brow];
-            uint8_t* dst = B + pf_off(brow, piece * 8);
-            if (src >= 0) {
-                const __half* g = p.x + (size_t) src * p.K + c * PF_KC + piece * 8;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(g) : "memory");
-            } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-            }
-        }
-    };
-    issue_b(0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    for (int c = 0; c < nchunk; ++c) {
-        const int s = c % PF_STAGES, kb = c >> 2, quarter = c & 3;
-        uint8_t* A0 = stage0 + (size_t) s * STAGE;
-        uint8_t* B = A0 + NA * PF_TILE_A;
-        bool gave_up = false;
-        if (c + 1 < nchunk) {
-            // the next chunk's stage is free when the tensor core has finished the chunk that used it (a wait that gives up is
-            // reported at the chunk's one block barrier below, where every thread takes the same exit)
-            if (c + 1 >= PF_STAGES) {
-                gave_up = !mbar_wait_bounded(&bars[(c + 1) % PF_STAGES], (unsigned) (((c + 1) / PF_STAGES - 1) & 1), 20000000u);
+    if (warp == PF_THREADS / 32) {
+        // the issuing warp: lane 0 waits for a stage to be filled, issues its products, and has their completion free the stage
+        if (lane == 0) {
+            for (int c = 0; c < nchunk; ++c) {
+                const int s = c % PF_STAGES;
+                if (!mbar_wait_bounded(&full[s], (unsigned) ((c / PF_STAGES) & 1), 20000000u)) {
+                    atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
+                    break;
+                }
                 pf_fence_after();
-            }
-            issue_b(c + 1);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        // the weights of this chunk: four sub-blocks of the warp's tile(s); the next block's bytes are fetched meanwhile
-        switch (quarter) {
-            case 0:
-                pf_quarter<0, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
-                if (kb + 1 < KB) load_raw(kb + 1, nxt);
-                break;
-            case 1: pf_quarter<1, MODE>(raw, A0 + a_off, row0, lane, table_s, sel); break;
-            case 2: pf_quarter<2, MODE>(raw, A0 + a_off, row0, lane, table_s, sel); break;
-            default:
-                pf_quarter<3, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
-                raw = nxt;
-                break;
-        }
-        asm volatile("cp.async.wait_group 1;" ::: "memory");   // this chunk's activations are in; the next chunk's may still fly
-        fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
-        if (__syncthreads_or(gave_up)) {
-            ok = false;
-            break;
-        }
-        if (tid == 0) {
-            pf_fence_after();
-            const uint32_t a_s = smem_u32(A0), b_s = smem_u32(B);
+                const uint32_t a_s = smem_u32(stage0 + (size_t) s * STAGE), b_s = a_s + NA * PF_TILE_A;
 #pragma unroll
-            for (int k16 = 0; k16 < PF_KC / 16; ++k16) {
-                const uint64_t bd = pf_desc(b_s + k16 * 2 * PF_LBO);
-                pf_mma(tmem, pf_desc(a_s + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
-                if (NA == 2) pf_mma(tmem + PF_N, pf_desc(a_s + PF_TILE_A + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
+                for (int k16 = 0; k16 < PF_KC / 16; ++k16) {
+                    const uint64_t bd = pf_desc(b_s + k16 * 2 * PF_LBO);
+                    pf_mma(tmem, pf_desc(a_s + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
+                    if (NA == 2) pf_mma(tmem + PF_N, pf_desc(a_s + PF_TILE_A + k16 * 2 * PF_LBO), bd, IDESC, (c | k16) != 0);
+                }
+                pf_commit(&bars[s]);
             }
-            pf_commit(&bars[s]);
+        }
+        __syncwarp();
+    } else {
+        // 16 warps: warp w decodes tile row (w % 8) of the 128-feature slab; gate|up: of the gate (w < 8) or the up matrix
+        // (all four sub-blocks of the chunk); down: sub-block pair w / 8 of the chunk
+        PfRaw raw, nxt;
+        const int sel = warp >> 3;
+        const int trow = (MODE == 1 && sel ? p.rows / 16 : 0) + ft * (PF_M / 16) + (warp & 7);
+        const int a_off = MODE == 1 && sel ? PF_TILE_A : 0, row0 = (warp & 7) * 16;
+        auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
+        load_raw(0, raw);
+        // the activations of chunk c into its stage: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies;
+        // they run one chunk ahead of the decode, so their latency hides behind it
+        auto issue_b = [&](int c) {
+            uint8_t* B = stage0 + (size_t) (c % PF_STAGES) * STAGE + NA * PF_TILE_A;
+#pragma unroll
+            for (int j = 0; j < PF_N * (PF_KC / 8) / PF_THREADS; ++j) {
+                // consecutive lanes take consecutive rows of one 8-column piece: the eight 16-byte stores of a quarter warp fill one
+                // 128-byte core matrix (no bank conflicts); the global side reads half sectors, which the L2 absorbs
+                const int i = tid + j * PF_THREADS, brow = i & (PF_N - 1), piece = i / PF_N;
+                const int src = src_s[brow];
+                uint8_t* dst = B + pf_off(brow, piece * 8);
+                if (src >= 0) {
+                    const __half* g = p.x + (size_t) src * p.K + c * PF_KC + piece * 8;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(g) : "memory");
+                } else {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        };
+        issue_b(0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        for (int c = 0; c < nchunk; ++c) {
+            const int s = c % PF_STAGES, kb = c >> 2, quarter = c & 3;
+            uint8_t* A0 = stage0 + (size_t) s * STAGE;
+            bool gave_up = false;
+            if (c + 1 < nchunk) {
+                // the next chunk's stage is free when the tensor core has finished the chunk that used it (a wait that gives up is
+                // reported at the chunk's one block barrier below, where every thread takes the same exit)
+                if (c + 1 >= PF_STAGES) {
+                    gave_up = !mbar_wait_bounded(&bars[(c + 1) % PF_STAGES], (unsigned) (((c + 1) / PF_STAGES - 1) & 1), 20000000u);
+                    pf_fence_after();
+                }
+                issue_b(c + 1);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            // the weights of this chunk: four sub-blocks of the warp's tile(s); the next block's bytes are fetched meanwhile
+            switch (quarter) {
+                case 0:
+                    pf_quarter<0, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
+                    if (kb + 1 < KB) load_raw(kb + 1, nxt);
+                    break;
+                case 1: pf_quarter<1, MODE>(raw, A0 + a_off, row0, lane, table_s, sel); break;
+                case 2: pf_quarter<2, MODE>(raw, A0 + a_off, row0, lane, table_s, sel); break;
+                default:
+                    pf_quarter<3, MODE>(raw, A0 + a_off, row0, lane, table_s, sel);
+                    raw = nxt;
+                    break;
+            }
+            asm volatile("cp.async.wait_group 1;" ::: "memory");   // this chunk's activations are in; the next chunk's may still fly
+            fence_proxy_async();   // the tiles were written through the generic proxy; the tensor core reads them through the async one
+            if (__any_sync(0xffffffffu, gave_up)) {   // no arrival: the issuing warp's wait runs out and reports it
+                ok = false;
+                break;
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[s])) : "memory");
         }
     }
     // all chunks issued: the last commit arrives when every earlier product has finished too
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (ok) ok = __syncthreads_and(mbar_wait_bounded(&bars[(nchunk - 1) % PF_STAGES], (unsigned) (((nchunk - 1) / PF_STAGES) & 1), 20000000u)) != 0;
     pf_fence_after();
     if (!ok && tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
-    if (ok) {
+    if (ok && warp < PF_THREADS / 32) {
         // warp w reads lanes 32 (w % 4) .. + 31 (its features), columns 64 (w / 4) .. + 63 (job rows), 32 at a time
         const int f = ft * PF_M + 32 * (warp & 3) + lane;
 #pragma unroll 1
@@ -541,11 +560,11 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
         PfParams p{};
         p.W = (const uint8_t*) Wgu; p.expert_stride = gu_stride; p.e_base = e_base; p.E = E; p.Wsh = (const uint8_t*) Wsh_gu;
         p.jobs = jobs; p.order = order; p.TKp = n; p.Kp = K; p.x = xh; p.rows = F; p.K = H; p.outh = hbuf; p.err = err;
-        k_pf_gemm<1><<<dim3(nj, F / PF_M), PF_THREADS, pf_smem(1), st>>>(p);
+        k_pf_gemm<1><<<dim3(nj, F / PF_M), PF_BLOCK, pf_smem(1), st>>>(p);
         FNX_LAUNCH_OK("k_pf_gemm (gate|up)");
         p.W = (const uint8_t*) Wdn; p.expert_stride = dn_stride; p.Wsh = (const uint8_t*) Wsh_dn;
         p.x = hbuf; p.rows = H; p.K = F; p.out = part; p.outh = nullptr;
-        k_pf_gemm<0><<<dim3(nj, H / PF_M), PF_THREADS, pf_smem(0), st>>>(p);
+        k_pf_gemm<0><<<dim3(nj, H / PF_M), PF_BLOCK, pf_smem(0), st>>>(p);
         FNX_LAUNCH_OK("k_pf_gemm (down)");
     }
     k_pf_combine<<<dim3((H / 4 + 255) / 256, T), 256, 0, st>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
