@@ -135,8 +135,8 @@ int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc, float* ou
  * rows of 16 heads over 2 KV heads; larger windows are rejected with FNX_E_ARG and a message naming the three factors.
  * Set-up: the first call on a device resolves the array's address with cudaGetSymbolAddress (return code checked) and
  * raises the kernel's shared-memory limit; neither belongs inside a stream capture, so call fnx_attn_static_setup()
- * (or one plain fnx_attn_static) once per device before capturing.  After set-up a call makes two kernel launches and
- * no other runtime call.
+ * (or one plain fnx_attn_static) once per device before capturing.  After set-up a call makes two kernel launches; its
+ * only other runtime calls are cudaGetDevice and cudaGetLastError, which neither allocate nor synchronise.
  * Sharing: every call on a device uses the same array.  Nothing in it has to start at zero (each call overwrites
  * every slot it later reads), but two calls that overlap in time (different streams or host threads, same device)
  * race on it and give undefined results: serialise them on one stream, or use fnx_attn with separate scratch. */
@@ -210,18 +210,28 @@ int fnx_engine_reset(fnx_engine* e, int seq);
  * through the model; leaves logits, per-row argmax and the acceptance result on the device and, when h_result is
  * not null, copies the greedy acceptance result back (synchronises).  Does not commit. */
 int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const int* h_parent, int T, int* h_result);
-/* Engine::commit: keeps the n accepted rows h_path[0..n) of the last window of `seq` */
+/* Engine::commit: keeps the n accepted rows h_path[0..n) of the last window of `seq`.  The window buffers (tokens,
+ * acceptance result, residual rows) are shared by the engine's sequences: commit (and draft) sequence A before verifying
+ * sequence B; a commit or draft for a sequence other than the one verified last returns FNX_E_STATE. */
 int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n);
 /* Engine::draft: the MTP layer on the rows kept by the last commit, then k - 1 chained single-row calls;
  * h_drafts receives k tokens */
 int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts);
 /* the device time of the last verify / draft graph launch in milliseconds (CUDA events on the engine's stream) */
 float fnx_engine_last_ms(const fnx_engine* e);
-/* Windows of up to 8 rows on a single rank can run as ONE persistent cooperative kernel (csrc/step.cu) instead of
- * the launch-per-operator graph: on = 1 (or FNX_STEP=1 in the environment) selects it; larger windows and
- * expert-parallel ranks always take the launch-per-operator path.  Off by default until it is the faster of the
- * two.  Drops the captured graphs. */
-int fnx_engine_use_step_kernel(fnx_engine* e, int on);
+/* Windows of up to 8 rows run as ONE persistent cooperative kernel (csrc/window.cu: every layer's projections,
+ * mixer, router and experts as phases of one launch, with bounded grid barriers between them) instead of the
+ * launch-per-operator graph (the reference's Engine::enqueue, engine/src/engine.cu:1760-1848); wider windows, and
+ * expert-parallel ranks whose peer exchange is not open, take the launch-per-operator path.  on = 0 (or FNX_WINDOW=0 in
+ * the environment) selects the launch-per-operator path for every window.  Drops the captured graphs. */
+int fnx_engine_use_window_kernel(fnx_engine* e, int on);
+/* Tracing of the window kernel (FNX_PROF, engine/src/engine.cu:1382-1529): on = 1 makes block 0 of the following
+ * windows write tagged %globaltimer stamps (tag << 56 | ns) at its phase boundaries; h_out (may be null, cap words)
+ * receives the last window's stamps, word 0 = their number.  Synchronises; drops the captured graphs when it switches. */
+int fnx_engine_window_profile(fnx_engine* e, int on, unsigned long long* h_out, int cap);
+/* the device error word (FNX_ERR_* bits) of the last window; synchronises.  fnx_engine_verify clears the word when it
+ * starts a window, and returns FNX_E_STATE with the bits when it copies a result back. */
+int fnx_engine_error_bits(fnx_engine* e, unsigned* h_bits);
 /* Acceptance rule of the following windows: null = greedy (the default); else the sampling rule of
  * engine/src/session.cpp:575-612 over each row's 64 best tokens with Philox uniforms addressed (seed, seq, window, slot);
  * drafts count as fixed (q = 1), windows must be chains.  Resets the per-sequence window counters. */

@@ -3,6 +3,9 @@
 #include "fnx_oracle.h"
 
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdlib.h>
 #include <string.h>
 
@@ -511,6 +514,17 @@ void fnx_o_philox4x32(const uint32_t ctr[4], const uint32_t key[2], uint32_t out
 }
 
 /* 53-bit uniform in [0, 1) from words 0 and 1 of the block at counter (slot, step, seq, 0) */
+/* the OpenMP team of the loops above: n > 0 sets it (a launcher may have exported OMP_NUM_THREADS=1); returns the size in use */
+int fnx_o_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void) n;
+    return 1;
+#endif
+}
+
 double fnx_o_uniform(uint64_t seed, uint32_t seq, uint32_t step, uint32_t slot) {
     const uint32_t ctr[4] = {slot, step, seq, 0u}, key[2] = {(uint32_t) seed, (uint32_t) (seed >> 32)};
     uint32_t o[4];

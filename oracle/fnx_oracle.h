@@ -70,6 +70,7 @@ void fnx_o_top_tokens(const float* logits, int T, int V, int n, float* out_v, in
 /* ---- drafting and acceptance ---- */
 int fnx_o_lookup(const int* ctx, int n, int lk, int d1, int* out, int* match);
 void fnx_o_philox4x32(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
+int fnx_o_threads(int n);
 double fnx_o_uniform(uint64_t seed, uint32_t seq, uint32_t step, uint32_t slot);
 typedef struct {
     float temperature, top_p, min_p;

@@ -1,0 +1,366 @@
+// Device bodies of the gated-attention kernels, shared by the stand-alone launches (attn.cu) and the persistent window
+// kernel (window.cu): per-head norm + rotary + KV append, the tree-masked split-K partial, and the merge of the splits.
+// Reference: attn_prep_append / norm_rope (engine/src/kernels.cu:1880-1910, 513-530), k_attn_part / k_attn_combine
+// (engine/src/kernels.cu:558-667, 786-803).
+#pragma once
+
+#include "fnx_common.cuh"
+
+namespace fnxb {
+
+struct SyncBlock {
+    __device__ __forceinline__ void operator()() const { __syncthreads(); }
+};
+// a named barrier of n threads (n a multiple of 32), for a group of warps inside a larger block
+struct SyncNamed {
+    int id, n;
+    __device__ __forceinline__ void operator()() const { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+};
+
+// ------------------------------------------------------------------------------------------------ prep + append
+// One (head h of nq + 2 nkv, row t) item by hd threads (i = the thread's element); xrow: hd floats, red: 32 floats of
+// shared memory; sync() is a barrier of the item's threads.
+template <typename Sync>
+__device__ __forceinline__ void attn_prep_body(float* qg, int ldq, float* k, int ldk, const float* v, int ldv, const float* qn, const float* kn,
+                                               __half* kc, __half* vc, int nq, int nkv, int hd, int nrot, int pos0, const int* depth, float eps,
+                                               float rope_base, int t, int h, int i, float* xrow, float* red, Sync sync) {
+    const int pos = pos0 + (depth ? depth[t] : t);
+    const size_t crow = (size_t) (pos0 + t) * nkv * hd;
+    if (h >= nq + nkv) {   // a V head: store only
+        const int kvh = h - nq - nkv;
+        vc[crow + (size_t) kvh * hd + i] = __float2half_rn(v[(size_t) t * ldv + (size_t) kvh * hd + i]);
+        return;
+    }
+    float* x = h < nq ? qg + (size_t) t * ldq + (size_t) h * 2 * hd : k + (size_t) t * ldk + (size_t) (h - nq) * hd;
+    const float* w = h < nq ? qn : kn;
+    const float val = x[i];
+    float ss = warp_sum(val * val);
+    if ((i & 31) == 0) red[i >> 5] = ss;
+    sync();
+    ss = 0.f;
+    for (int j = 0; j < hd / 32; ++j) ss += red[j];
+    xrow[i] = val * rsqrtf(ss / (float) hd + eps) * w[i];
+    sync();
+    float y = xrow[i];
+    if (i < nrot) {
+        const int pr = i < nrot / 2 ? i : i - nrot / 2;
+        // the unit frequency through double: the correctly rounded f32 of base^(-2 i / nrot) (engine/src/rope.hpp:33-35)
+        const float fe = (float) pow((double) rope_base, -2.0 * (double) pr / (double) nrot);
+        float sn, cs;
+        sincosf((float) pos * fe, &sn, &cs);
+        const float x0 = xrow[pr], x1 = xrow[pr + nrot / 2];
+        y = i < nrot / 2 ? x0 * cs - x1 * sn : x0 * sn + x1 * cs;
+    }
+    x[i] = y;
+    if (h >= nq) kc[crow + (size_t) (h - nq) * hd + i] = __float2half_rn(y);
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+constexpr int ATT_SC = 64;        // positions per step
+constexpr int ATT_ROWS = 5;       // window rows one block serves
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_MAXQ = 8;       // q heads per KV head
+constexpr int ATT_MQ = 48;        // the block's ATT_ROWS * ATT_MAXQ queries, padded to three 16-row MMA tiles
+constexpr int ATT_HD = 256;
+constexpr int ATT_QS = ATT_HD + 8;    // row strides (halves) of the Q, K, V tiles: 8 rows of a ldmatrix land in 8 bank groups
+constexpr int ATT_SS = ATT_SC + 4;    // score rows (floats)
+constexpr int ATT_PS = ATT_SC + 8;    // probability rows (halves)
+
+constexpr size_t attn_part_smem() {
+    return (size_t) (2 * ATT_MQ + 2 * ATT_SC) * ATT_QS * sizeof(__half) + (size_t) ATT_MQ * ATT_SS * sizeof(float) +
+           (size_t) ATT_MQ * ATT_PS * sizeof(__half) + 3 * ATT_MQ * sizeof(float) + ATT_ROWS * sizeof(unsigned);
+}
+
+struct AttPartial {   // one (row, head, split)
+    float m, z;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+
+// One block: KV head kvh, split s of S (every S-th 64-position chunk of [0, ctx)), window rows [r0, r0 + ATT_ROWS):
+// their (up to 40) queries against the share, on the tensor cores (mma.sync m16n8k16, f16 x f16 -> f32):
+//   scores  = Q K^T with Q = Qhi + Qlo, two f16 halves of the f32 queries, so that only K's own f16 rounding remains;
+//   weights = exp(score - running max), rounded to f16 (their sum is taken over the rounded values);
+//   sums   += weights V, accumulated in f32 registers across the steps of 64 positions.
+// scratch: acc [T][nq][S][hd] floats, then mz [T][nq][S]
+// (tid: the thread among the item's ATT_THREADS; smem: attn_part_smem() bytes, 16-byte aligned; sync(): their barrier)
+template <typename Sync>
+__device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const __half* kc, const __half* vc, float* acc_out, AttPartial* mz_out, int T,
+                                               int nq, int nkv, int pos0, const int* parent, int s, int S, int kvh, int r0, int tid, uint8_t* smem,
+                                               Sync sync) {
+    const int nr = min(ATT_ROWS, T - r0), qpk = nq / nkv, NQ = nr * qpk;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
+    const int ctx = pos0 + T;
+    __half* Qh = reinterpret_cast<__half*>(smem);           // [ATT_MQ][ATT_QS]
+    __half* Ql = Qh + ATT_MQ * ATT_QS;
+    __half* Ks = Ql + ATT_MQ * ATT_QS;                      // [ATT_SC][ATT_QS]
+    __half* Vs = Ks + ATT_SC * ATT_QS;
+    float* Sf = reinterpret_cast<float*>(Vs + ATT_SC * ATT_QS);   // [ATT_MQ][ATT_SS]
+    __half* Pp = reinterpret_cast<__half*>(Sf + ATT_MQ * ATT_SS); // [ATT_MQ][ATT_PS]
+    float* ms = reinterpret_cast<float*>(Pp + ATT_MQ * ATT_PS);   // running max, sum, rescale per query
+    float* zs = ms + ATT_MQ;
+    float* fs = zs + ATT_MQ;
+    unsigned* see = reinterpret_cast<unsigned*>(fs + ATT_MQ);     // per local row: window rows it sees
+    // Split s takes the 64-position chunks s, s + S, s + 2 S, ... in order.  Chunks are cut at absolute positions, so what a
+    // row's partial of split s sums, and in which order, depends on the row's own position only - not on the window it
+    // arrived in: a row verified alone and the same row verified among drafts give the same bits.
+    const int pa = s * ATT_SC;
+    if (pa >= ctx) {   // a block with no positions leaves only empty partials: the merge skips them without reading their sums
+        if (tid < NQ) {
+            const int r = tid / qpk, hh = tid % qpk;
+            mz_out[((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s] = AttPartial{-INFINITY, 0.f};
+        }
+        return;
+    }
+    // the first step's K and V rows are on their way while the queries are split
+    auto fetch_kv = [&](int p0, int np) {
+#pragma unroll
+        for (int j = 0; j < ATT_SC * (ATT_HD / 8) / ATT_THREADS; ++j) {
+            const int i = tid + j * ATT_THREADS, pp = i / (ATT_HD / 8), d8 = i % (ATT_HD / 8);
+            __half* kd = Ks + pp * ATT_QS + d8 * 8;
+            __half* vd = Vs + pp * ATT_QS + d8 * 8;
+            if (pp < np) {
+                const size_t go = ((size_t) (p0 + pp) * nkv + kvh) * ATT_HD + d8 * 8;
+                cp_async16(kd, kc + go);
+                cp_async16(vd, vc + go);
+            } else {
+                *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_kv(pa, min(ATT_SC, ctx - pa));
+    // the queries as f16 pairs (hi, lo); rows past NQ are zero
+    for (int i0 = tid; i0 < ATT_MQ * (ATT_HD / 4); i0 += 6 * ATT_THREADS) {
+        float4 v[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            const int i = i0 + j * ATT_THREADS, qi = i / (ATT_HD / 4), d4 = i % (ATT_HD / 4);
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < ATT_MQ * (ATT_HD / 4) && qi < NQ) {
+                const int r = qi / qpk, hh = qi % qpk;
+                v[j] = *reinterpret_cast<const float4*>(qg + (size_t) (r0 + r) * ldq + (size_t) (kvh * qpk + hh) * 2 * ATT_HD + d4 * 4);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            const int i = i0 + j * ATT_THREADS, qi = i / (ATT_HD / 4), d4 = i % (ATT_HD / 4);
+            if (i >= ATT_MQ * (ATT_HD / 4)) continue;
+            const float x[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            __half h[4], l[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                h[k] = __float2half_rn(x[k]);
+                l[k] = __float2half_rn(x[k] - __half2float(h[k]));
+            }
+            *reinterpret_cast<uint2*>(Qh + qi * ATT_QS + d4 * 4) = make_uint2((uint32_t) __half_as_ushort(h[0]) | ((uint32_t) __half_as_ushort(h[1]) << 16),
+                                                                                (uint32_t) __half_as_ushort(h[2]) | ((uint32_t) __half_as_ushort(h[3]) << 16));
+            *reinterpret_cast<uint2*>(Ql + qi * ATT_QS + d4 * 4) = make_uint2((uint32_t) __half_as_ushort(l[0]) | ((uint32_t) __half_as_ushort(l[1]) << 16),
+                                                                                (uint32_t) __half_as_ushort(l[2]) | ((uint32_t) __half_as_ushort(l[3]) << 16));
+        }
+    }
+    if (tid < ATT_MQ) { ms[tid] = -INFINITY; zs[tid] = 0.f; fs[tid] = 0.f; }
+    if (tid < nr) {
+        unsigned m = 0;
+        for (int a = r0 + tid; a >= 0; a = parent ? parent[a] : a - 1) m |= 1u << a;
+        see[tid] = m;
+    }
+    float acc[3][4][4];   // [query tile][8-dim tile of the warp's 32 dims][c]
+#pragma unroll
+    for (int m = 0; m < 3; ++m)
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[m][n][k] = 0.f;
+    const float scale = rsqrtf((float) ATT_HD);
+    const uint32_t qh_s = smem_u32(Qh), ql_s = smem_u32(Ql), ks_s = smem_u32(Ks), vs_s = smem_u32(Vs), pp_s = smem_u32(Pp);
+    // ldmatrix lane addresses: A tiles (16 rows x 16 columns), B tiles of K (8 positions x 32 dims), of V (16 positions x 16 dims, transposed)
+    const uint32_t a_off = (uint32_t) ((lane & 15) * ATT_QS + (lane >> 4) * 8) * 2u;
+    const uint32_t bk_off = (uint32_t) ((warp * 8 + (lane & 7)) * ATT_QS + (lane >> 3) * 8) * 2u;
+    const uint32_t bv_off = (uint32_t) (((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_QS + warp * 32 + (lane >> 4) * 8) * 2u;
+    const uint32_t ap_off = (uint32_t) ((lane & 15) * ATT_PS + (lane >> 4) * 8) * 2u;
+    for (int p0 = pa; p0 < ctx; p0 += S * ATT_SC) {
+        const int np = min(ATT_SC, ctx - p0);
+        if (p0 > pa) {
+            sync();   // the previous step's tiles are read
+            fetch_kv(p0, np);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        sync();
+        // ---- scores: warp w = positions [8 w, 8 w + 8) of the step, all 48 query rows
+        {
+            float c[3][4];
+#pragma unroll
+            for (int m = 0; m < 3; ++m)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) c[m][k] = 0.f;
+#pragma unroll 4
+            for (int k0 = 0; k0 < ATT_HD; k0 += 32) {
+                uint32_t b0, b1, b2, b3;   // (b0, b1): dims k0 .. k0 + 15, (b2, b3): k0 + 16 .. k0 + 31
+                ldsm_x4(ks_s + bk_off + k0 * 2, b0, b1, b2, b3);
+#pragma unroll
+                for (int m = 0; m < 3; ++m) {
+                    uint32_t a0, a1, a2, a3;
+                    const uint32_t ao = a_off + (uint32_t) (m * 16 * ATT_QS + k0) * 2u;
+                    ldsm_x4(qh_s + ao, a0, a1, a2, a3);
+                    mma_f16(c[m], a0, a1, a2, a3, b0, b1);
+                    ldsm_x4(ql_s + ao, a0, a1, a2, a3);
+                    mma_f16(c[m], a0, a1, a2, a3, b0, b1);
+                    ldsm_x4(qh_s + ao + 32, a0, a1, a2, a3);
+                    mma_f16(c[m], a0, a1, a2, a3, b2, b3);
+                    ldsm_x4(ql_s + ao + 32, a0, a1, a2, a3);
+                    mma_f16(c[m], a0, a1, a2, a3, b2, b3);
+                }
+            }
+            // scaled and masked into the score tile: row = query, column = position of the step
+#pragma unroll
+            for (int m = 0; m < 3; ++m)
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int qi = m * 16 + g + 8 * hrow;
+                    float2 o;
+                    float* ov = &o.x;
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int col = warp * 8 + 2 * q + k, p = p0 + col;
+                        bool vis = qi < NQ && col < np;
+                        if (vis && p >= pos0) vis = (see[qi / qpk] >> (p - pos0)) & 1u;
+                        ov[k] = vis ? c[m][2 * hrow + k] * scale : -INFINITY;
+                    }
+                    *reinterpret_cast<float2*>(Sf + qi * ATT_SS + warp * 8 + 2 * q) = o;
+                }
+        }
+        sync();
+        // ---- weights: warp w = queries w, w + 8, ...; lane = positions lane and 32 + lane
+        for (int qi = warp; qi < ATT_MQ; qi += ATT_THREADS / 32) {
+            const float v0 = Sf[qi * ATT_SS + lane], v1 = Sf[qi * ATT_SS + 32 + lane];
+            const float mo = ms[qi], mn = fmaxf(mo, warp_max(fmaxf(v0, v1)));
+            const __half w0 = __float2half_rn(v0 == -INFINITY ? 0.f : expf(v0 - mn)), w1 = __float2half_rn(v1 == -INFINITY ? 0.f : expf(v1 - mn));
+            const float f = mo == -INFINITY ? 0.f : expf(mo - mn);
+            const float zn = zs[qi] * f + warp_sum(__half2float(w0) + __half2float(w1));
+            Pp[qi * ATT_PS + lane] = w0;
+            Pp[qi * ATT_PS + 32 + lane] = w1;
+            __syncwarp();
+            if (lane == 0) { ms[qi] = mn; zs[qi] = zn; fs[qi] = f; }
+        }
+        sync();
+        // ---- sums: warp w = dims [32 w, 32 w + 32), all 48 query rows
+#pragma unroll
+        for (int m = 0; m < 3; ++m) {
+            const float fa = fs[m * 16 + g], fb = fs[m * 16 + g + 8];
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                acc[m][n][0] *= fa; acc[m][n][1] *= fa;
+                acc[m][n][2] *= fb; acc[m][n][3] *= fb;
+            }
+        }
+#pragma unroll
+        for (int k0 = 0; k0 < ATT_SC; k0 += 16) {
+            uint32_t a[3][4];
+#pragma unroll
+            for (int m = 0; m < 3; ++m) ldsm_x4(pp_s + ap_off + (uint32_t) (m * 16 * ATT_PS + k0) * 2u, a[m][0], a[m][1], a[m][2], a[m][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < 2; ++n2) {
+                uint32_t b0, b1, b2, b3;   // (b0, b1): dims 16 n2 .. + 7, (b2, b3): + 8 .. + 15
+                ldsm_x4_t(vs_s + bv_off + (uint32_t) (k0 * ATT_QS + n2 * 16) * 2u, b0, b1, b2, b3);
+#pragma unroll
+                for (int m = 0; m < 3; ++m) {
+                    mma_f16(acc[m][2 * n2], a[m][0], a[m][1], a[m][2], a[m][3], b0, b1);
+                    mma_f16(acc[m][2 * n2 + 1], a[m][0], a[m][1], a[m][2], a[m][3], b2, b3);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < 3; ++m)
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int qi = m * 16 + g + 8 * hrow;
+            if (qi < NQ) {
+                const int r = qi / qpk, hh = qi % qpk;
+                const size_t slot = ((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s;
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+                    *reinterpret_cast<float2*>(acc_out + slot * ATT_HD + warp * 32 + n * 8 + 2 * q) = make_float2(acc[m][n][2 * hrow], acc[m][n][2 * hrow + 1]);
+            }
+        }
+    if (tid < NQ) {
+        const int r = tid / qpk, hh = tid % qpk;
+        mz_out[((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s] = AttPartial{ms[tid], zs[tid]};
+    }
+}
+
+// merge the splits of (row, head): out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) z_s * sigmoid(gate)
+constexpr int ATC_G = 4;   // groups of hd threads that share the splits of one (row, head)
+
+// By PG * ATT_THREADS threads (PG = 4: one thread group per role; PG = 2: a thread group plays roles g and g + 2);
+// sm: (3 + ATC_G) * 256 floats of shared memory; sync(): the barrier of those threads.
+template <int PG, typename Sync>
+__device__ __forceinline__ void attn_combine_body(const float* acc_in, const AttPartial* mz_in, const float* qg, int ldq, float* out, int nq, int hd, int S,
+                                                  int h, int t, int tid, float* sm, Sync sync) {
+    float* sm_m = sm;
+    float* sm_w = sm + 256;
+    float* sm_z = sm + 512;
+    float (*sm_p)[ATT_THREADS] = reinterpret_cast<float (*)[ATT_THREADS]>(sm + 768);
+    const int i = tid % ATT_THREADS, g = tid / ATT_THREADS;
+    const size_t base = ((size_t) t * nq + h) * S;
+    AttPartial p = AttPartial{-INFINITY, 0.f};
+    if (g == 0) {
+        if (i < S) p = mz_in[base + i];
+        sm_m[i] = i < S ? p.m : -INFINITY;
+    }
+    sync();
+    // block maximum of m (S <= 256)
+    float mx = -INFINITY;
+    for (int s = 0; s < S; ++s) mx = fmaxf(mx, sm_m[s]);
+    if (g == 0) {
+        const float w = i < S && p.m != -INFINITY ? expf(p.m - mx) : 0.f;
+        sm_w[i] = w;
+        sm_z[i] = w * p.z;
+    }
+    sync();
+    // group g adds the live splits g, g + G, ... in order (8 loads in flight); group 0 then adds the groups in order
+    for (int gg = g; gg < ATC_G; gg += PG) {
+        float acc = 0.f;
+        for (int s0 = gg; s0 < S; s0 += 8 * ATC_G) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int sp = s0 + j * ATC_G;
+                v[j] = sp < S && sm_w[sp] != 0.f ? acc_in[(base + sp) * hd + i] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int sp = s0 + j * ATC_G;
+                acc = fmaf(sp < S ? sm_w[sp] : 0.f, v[j], acc);
+            }
+        }
+        sm_p[gg][i] = acc;
+    }
+    sync();
+    if (g != 0) return;
+    float z = 0.f;
+    for (int s = 0; s < S; ++s) z += sm_z[s];        // fixed order: deterministic
+    float tot = sm_p[0][i];
+#pragma unroll
+    for (int k = 1; k < ATC_G; ++k) tot += sm_p[k][i];
+    const float gate = qg[(size_t) t * ldq + (size_t) h * 2 * hd + hd + i];
+    out[((size_t) t * nq + h) * hd + i] = tot / z * sigmoidf_(gate);
+}
+
+
+}  // namespace fnxb

@@ -16,7 +16,7 @@
 
 #include "fnx_common.cuh"
 #include "iq3s_tile.h"
-#include "step.cuh"
+#include "window.cuh"
 
 namespace fnxb {
 
@@ -97,7 +97,8 @@ struct fnx_engine {
     float *rlogits = nullptr, *topw = nullptr, *hbuf = nullptr, *part = nullptr, *moe_out = nullptr, *best_v = nullptr, *cand_v = nullptr;
     int *topi = nullptr, *njobs = nullptr, *best_i = nullptr, *result = nullptr, *d_tok = nullptr, *d_parent = nullptr, *d_depth = nullptr;
     int *d_pos = nullptr, *d_cur = nullptr, *d_ctx = nullptr, *d_ctx_n = nullptr, *d_path = nullptr, *d_mtok = nullptr, *d_mpos = nullptr;
-    int *cand_i = nullptr, *d_draft = nullptr;
+    int *cand_i = nullptr, *d_drafts = nullptr;
+    int last_seq = -1;          // the sequence whose window the shared window buffers (tokens, result, residual rows) hold
     fnx_job* jobs = nullptr;
     unsigned* err = nullptr;
     void* att_scratch = nullptr;
@@ -122,14 +123,14 @@ struct fnx_engine {
     uint64_t sample_seed = 0;
     uint32_t* d_step = nullptr;   // [n_seq] windows sampled so far (the Philox step)
     int* d_lk = nullptr;          // lookup: [0, MAX_ROWS) drafts, [MAX_ROWS, +2) count and match, +2 the first-draft filter, +3 the context length
-    // the persistent step kernel (windows of up to 8 rows on a single rank)
-    bool use_step = false;
-    std::map<uint64_t, StepParams*> step_params;     // per graph key: device parameter block
-    std::map<int, StepLayer*> step_layers;          // per sequence: device layer table
+    // the persistent window kernel (windows of up to WIN_MAX_ROWS rows)
+    bool use_window = false;
+    std::map<uint64_t, WinParams> win_params;       // per graph key: the kernel's parameter block (passed by value)
     unsigned* d_sync = nullptr;
-    uint8_t* d_ximg = nullptr;
-    float *d_xnorm = nullptr, *d_gdn_o = nullptr, *d_gdn_sq = nullptr;
+    float *d_gdn_o = nullptr, *d_gdn_sq = nullptr;
+    unsigned long long* d_racc = nullptr;
     unsigned long long* d_prof = nullptr;
+    int prof_on = 0;
     unsigned long long launches = 0;
     std::map<uint64_t, unsigned> graph_kernels;
 };
@@ -489,64 +490,94 @@ static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
     FNX_TRY(enqueue_dense(e, e->mtp_fc_emb, d.H, d.H, e->Emb, d.H, T, e->mtp_enorm, e->Rm, d.H, 1));
     FNX_TRY(enqueue_attention(e, e->mtp, e->Rm, T, seq, nullptr, nullptr, e->d_mpos));
     FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, T));
-    FNX_TRY(fnx_dense(e->head, d.V, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, d.V, 0, e->err, e->st));
-    return fnx_argmax(e->logits, 1, d.V, e->d_draft, nullptr, e->err, e->st);
+    return fnx_dense(e->head, d.V, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, d.V, 0, e->err, e->st);
 }
 
-// the persistent step kernel's parameter block for (sequence, rows, tree): built once, outside any capture
-static bool step_ok(const fnx_engine* e, int T) {
+// whether windows of T rows run as the persistent window kernel (window.cu)
+static bool win_ok(const fnx_engine* e, int T) {
     const Dims d = dims(e->c);
-    return e->use_step && e->c.ep_size == 1 && T <= 8 && d.hd == 256 && d.hs == 128 && d.nq / d.nkv <= 8 && d.E <= 1024 && d.K <= 32 &&
-           (size_t) T * d.H * sizeof(float) <= 65536 && d.nq * d.hd <= 4096 && d.nv * d.hs <= 4096 && d.H <= 4096;
+    const bool ep_ok = e->c.ep_size == 1 || (e->ep_peers && e->c.ep_size <= 8 && sm_count() <= 256);
+    return e->use_window && ep_ok && T <= WIN_MAX_ROWS && d.hd == 256 && d.hs == 128 && d.nq / d.nkv <= 8 && d.E <= 1024 && d.K <= 16 &&
+           d.H <= 2048 && d.F <= 2048 && d.nq * d.hd <= 4096 && d.nv * d.hs <= 4096 && (d.nv * d.hs) % 256 == 0 && (d.nq * d.hd) % 256 == 0;
 }
-static int step_prepare(fnx_engine* e, uint64_t key, int seq, int T, bool tree) {
-    if (e->step_params.count(key)) return FNX_OK;
+static void win_fill_layer(const fnx_engine* e, const LayerW& L, int seq, WinLayer& s) {
     const Dims d = dims(e->c);
-    if (!e->step_layers.count(seq)) {
-        std::vector<StepLayer> hl(e->layers.size());
-        for (size_t l = 0; l < e->layers.size(); ++l) {
-            const LayerW& L = e->layers[l];
-            StepLayer& s = hl[l];
-            s.attn = L.attn;
-            s.in_rows = L.in_rows;
-            s.norm1 = L.norm1; s.norm2 = L.norm2; s.w_in = L.w_in; s.w_out = L.w_out;
-            s.qn = L.qn; s.kn = L.kn;
-            s.kc = L.kc ? L.kc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
-            s.vc = L.vc ? L.vc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
-            s.convw = L.convw; s.dt = L.dt; s.a = L.a; s.gnorm = L.gnorm;
-            s.S = L.S_pool ? L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs : nullptr;
-            s.hist = L.hist_pool ? L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch : nullptr;
-            s.wr = L.wr; s.wgu = L.wgu; s.wdn = L.wdn; s.wsh_gu = L.wsh_gu; s.wsh_dn = L.wsh_dn;
-        }
-        StepLayer* dl = nullptr;
-        FNX_TRY(dalloc(e, &dl, hl.size()));
-        FNX_CUDA_OK(cudaMemcpy(dl, hl.data(), sizeof(StepLayer) * hl.size(), cudaMemcpyHostToDevice));
-        e->step_layers[seq] = dl;
-    }
-    StepParams p{};
-    p.layers = e->step_layers[seq];
-    p.n_layer = (int) e->layers.size();
+    s.attn = L.attn;
+    s.in_rows = L.in_rows;
+    s.norm1 = L.norm1; s.norm2 = L.norm2; s.w_in = L.w_in; s.w_out = L.w_out;
+    s.qn = L.qn; s.kn = L.kn;
+    s.kc = L.kc ? L.kc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
+    s.vc = L.vc ? L.vc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
+    s.convw = L.convw; s.dt = L.dt; s.a = L.a; s.gnorm = L.gnorm;
+    s.S = L.S_pool ? L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs : nullptr;
+    s.hist = L.hist_pool ? L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch : nullptr;
+    s.wr = L.wr; s.wgu = L.wgu; s.wdn = L.wdn; s.wsh_gu = L.wsh_gu; s.wsh_dn = L.wsh_dn;
+}
+// the window kernel's parameter block for (sequence, rows, tree) or for a draft-layer call: built once, outside any capture
+static int win_prepare(fnx_engine* e, uint64_t key, int seq, int T, bool tree, bool mtp) {
+    if (e->win_params.count(key)) return FNX_OK;
+    const Dims d = dims(e->c);
+    WinParams p{};
+    p.n_layer = mtp ? 1 : (int) e->layers.size();
+    FNX_REQUIRE(p.n_layer <= WIN_MAX_LAYERS, "window kernel: %d layers (at most %d)", p.n_layer, WIN_MAX_LAYERS);
+    if (mtp) win_fill_layer(e, e->mtp, seq, p.layers[0]);
+    else
+        for (size_t l = 0; l < e->layers.size(); ++l) win_fill_layer(e, e->layers[l], seq, p.layers[l]);
     p.H = d.H; p.E = d.E; p.K = d.K; p.F = d.F; p.nq = d.nq; p.nkv = d.nkv; p.hd = d.hd; p.nrot = d.nrot; p.nk = d.nk; p.nv = d.nv; p.hs = d.hs; p.V = d.V;
     p.T = T; p.NS = e->NS; p.proj_ld = e->proj_ld; p.tree = tree ? 1 : 0;
+    p.e_lo = e->e_lo; p.e_hi = e->e_hi; p.e_base = e->e_lo;
+    p.ep_rank = e->c.ep_rank; p.ep_size = e->c.ep_size; p.maxr = d.MAXR;
     p.eps = e->c.eps; p.rope_base = e->c.rope_base;
     p.gu_bytes = e->gu_bytes; p.dn_bytes = e->dn_bytes;
-    p.tok = e->d_tok; p.parent = e->d_parent; p.pos0 = e->d_pos + seq; p.cur = e->d_cur + seq; p.depth = e->d_depth;
-    p.embed = e->embed; p.head = e->head; p.out_norm = e->out_norm;
-    p.R = e->R; p.proj = e->proj; p.mix = e->mix; p.logits = e->logits; p.rlogits = e->rlogits; p.topw = e->topw; p.hbuf = e->hbuf; p.part = e->part;
+    p.tok = mtp ? e->d_mtok : e->d_tok;
+    p.parent = e->d_parent;
+    p.pos0 = mtp ? e->d_mpos : e->d_pos + seq;
+    p.cur = e->d_cur + seq;
+    p.depth = e->d_depth;
+    p.embed = e->embed; p.head = e->head; p.out_norm = mtp ? e->mtp_onorm : e->out_norm;
+    p.head_row0 = mtp ? T - 1 : 0;
+    p.R = mtp ? e->Rm : e->R;
+    p.proj = e->proj; p.mix = e->mix; p.logits = e->logits; p.rlogits = e->rlogits; p.topw = e->topw; p.hbuf = e->hbuf;
     p.topi = e->topi; p.jobs = e->jobs; p.njobs = e->njobs;
     const int S = sm_count() / d.nkv > 0 ? sm_count() / d.nkv : 1;
     p.att_acc = (float*) e->att_scratch;
-    p.att_mz = (AttPartialS*) (p.att_acc + (size_t) T * d.nq * S * d.hd);
-    p.gdn_o = e->d_gdn_o; p.gdn_sq = e->d_gdn_sq; p.ximg = e->d_ximg; p.xnorm = e->d_xnorm;
-    p.best_i = e->best_i; p.best_v = e->best_v; p.result = e->result;
-    p.sync = e->d_sync; p.stats = e->d_stats; p.err = e->err; p.prof = e->d_prof;
-    StepParams* dp = nullptr;
-    FNX_TRY(dalloc(e, (uint8_t**) &dp, sizeof(StepParams)));
-    FNX_CUDA_OK(cudaMemcpy(dp, &p, sizeof p, cudaMemcpyHostToDevice));
-    e->step_params[key] = dp;
+    p.att_mz = (void*) (p.att_acc + (size_t) T * d.nq * S * d.hd);
+    p.gdn_o = e->d_gdn_o; p.gdn_sq = e->d_gdn_sq; p.racc = e->d_racc;
+    p.sync = e->d_sync; p.stats = e->d_stats; p.err = e->err; p.prof = e->prof_on ? e->d_prof : nullptr;
+    p.mtp = mtp ? 1 : 0;
+    {
+        const char* v = getenv("FNX_WIN_DBG");
+        p.dbg = v && v[0] == '1';
+    }
+    p.fc_hid = e->mtp_fc_hid; p.fc_emb = e->mtp_fc_emb; p.hnorm = e->mtp_hnorm; p.enorm = e->mtp_enorm;
+    p.src = e->Rsrc; p.emb = e->Emb;
+    if (e->c.ep_size > 1) {
+        std::vector<float*> px(e->c.ep_size);
+        std::vector<unsigned*> pf(e->c.ep_size);
+        FNX_CUDA_OK(cudaMemcpy(px.data(), e->d_peer_x, sizeof(float*) * e->c.ep_size, cudaMemcpyDeviceToHost));
+        FNX_CUDA_OK(cudaMemcpy(pf.data(), e->d_peer_flag, sizeof(unsigned*) * e->c.ep_size, cudaMemcpyDeviceToHost));
+        for (int r = 0; r < e->c.ep_size; ++r) {
+            p.peers.x[r] = (unsigned long long*) px[r];
+            p.peers.flag[r] = pf[r] + 2 * e->c.ep_size;   // past the launch-per-operator exchange's flags
+        }
+        p.xseq = e->d_xseq + 4;
+    }
+    e->win_params[key] = p;
     return FNX_OK;
 }
 
+// the window kernel, then acceptance over its logits
+static int enqueue_verify_window(fnx_engine* e, const WinParams& wp, int seq, int T, bool tree) {
+    const Dims d = dims(e->c);
+    FNX_TRY(win_launch(wp, e->d_sync, e->st));
+    if (e->sampling_on) {
+        FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
+        return fnx_accept_sample(e->cand_v, e->cand_i, e->d_tok, T, e->sampling, nullptr, nullptr, nullptr, e->sample_seed, (uint32_t) seq, e->d_step + seq,
+                                 e->result, e->st);
+    }
+    FNX_TRY(fnx_argmax(e->logits, T, d.V, e->best_i, e->best_v, e->err, e->st));
+    return fnx_accept_greedy(e->d_tok, tree ? e->d_parent : nullptr, e->best_i, T, e->result, e->st);
+}
 template <typename F>
 static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
     auto it = e->graphs.find(key);
@@ -642,11 +673,13 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->part, (size_t) d.P * d.H, "buf.part"));
         FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
         if (c.ep_size > 1) {
-            FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
-            FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size, "buf.ep_flag"));
+            // landing planes [2 slots][ranks][rows][H]: f32 for the launch-per-operator exchange, 64-bit fixed-point sums for
+            // the window kernel's (hence twice the floats); flags per (slot, rank) and, for the window kernel, per block
+            FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
+            FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size * (1 + 256), "buf.ep_flag"));
             FNX_TRY(dalloc(e, &e->d_peer_x, (size_t) c.ep_size));
             FNX_TRY(dalloc(e, &e->d_peer_flag, (size_t) c.ep_size));
-            FNX_TRY(dalloc(e, &e->d_xseq, 4));
+            FNX_TRY(dalloc(e, &e->d_xseq, 8));
         }
         FNX_TRY(dalloc(e, &e->best_i, d.MAXR, "buf.best_i"));
         FNX_TRY(dalloc(e, &e->best_v, d.MAXR, "buf.best_v"));
@@ -659,7 +692,7 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_path, FNX_MAX_ROWS, "buf.path"));
         FNX_TRY(dalloc(e, &e->d_mtok, FNX_MAX_ROWS, "buf.mtp_tok"));
         FNX_TRY(dalloc(e, &e->d_mpos, 1, "buf.mtp_pos"));
-        FNX_TRY(dalloc(e, &e->d_draft, 1, "buf.draft"));
+        FNX_TRY(dalloc(e, &e->d_drafts, FNX_MAX_ROWS, "buf.draft"));
         FNX_TRY(dalloc(e, &e->d_step, c.n_seq, "seq.step"));
         FNX_TRY(dalloc(e, &e->d_lk, FNX_MAX_ROWS + 4, "buf.lookup"));
         FNX_TRY(dalloc(e, &e->d_pos, c.n_seq, "seq.pos"));
@@ -668,15 +701,14 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_ctx_n, c.n_seq, "seq.ctx_n"));
         FNX_TRY(dalloc(e, &e->err, 1, "buf.err"));
         FNX_TRY(dalloc(e, &e->d_stats, 2, "buf.stats"));
-        FNX_TRY(dalloc(e, &e->d_sync, STEP_SYNC_WORDS, "buf.sync"));
-        FNX_TRY(dalloc(e, &e->d_ximg, 65536 + 1024, "buf.ximg"));
-        FNX_TRY(dalloc(e, &e->d_xnorm, (size_t) d.MAXR * d.H, "buf.xnorm"));
+        FNX_TRY(dalloc(e, &e->d_sync, WIN_SYNC_WORDS, "buf.sync"));
         FNX_TRY(dalloc(e, &e->d_gdn_o, (size_t) d.MAXR * d.nv * d.hs, "buf.gdn_o"));
         FNX_TRY(dalloc(e, &e->d_gdn_sq, (size_t) d.MAXR * d.nv * 4, "buf.gdn_sq"));
-        FNX_TRY(dalloc(e, &e->d_prof, 4096, "buf.prof"));
+        FNX_TRY(dalloc(e, &e->d_racc, (size_t) d.MAXR * d.H, "buf.racc"));
+        FNX_TRY(dalloc(e, &e->d_prof, WIN_PROF_WORDS, "buf.prof"));
         {
-            const char* v = getenv("FNX_STEP");
-            if (v && v[0] == '1') e->use_step = true;
+            const char* v = getenv("FNX_WINDOW");
+            if (v) e->use_window = v[0] == '1';
         }
         void* sc = nullptr;
         const size_t sb = fnx_attn_scratch_bytes(d.MAXR, d.nq, d.hd);
@@ -783,8 +815,13 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
         FNX_REQUIRE(h_tok[t] >= 0 && h_tok[t] < e->c.vocab, "fnx_engine_verify: token %d outside the vocabulary", h_tok[t]);
         if (h_parent) FNX_REQUIRE(h_parent[t] < t && h_parent[t] >= (t == 0 ? -1 : 0), "fnx_engine_verify: parent[%d] = %d is not an earlier row", t, h_parent[t]);
     }
+    const bool tree = h_parent != nullptr;
+    FNX_REQUIRE(!(tree && e->sampling_on), "fnx_engine_verify: the sampling rule is defined on chains (parent must be null)");
     // the previous call's use of the staging buffer is over: every call that copies results back synchronises
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    // the device error word reports THIS window: whatever an earlier window left was returned with its result (or is
+    // still readable through fnx_engine_error_bits until now)
+    FNX_CUDA_OK(cudaMemsetAsync(e->err, 0, sizeof(unsigned), e->st));
     int* hs = e->h_stage;
     memcpy(hs, h_tok, sizeof(int) * T);
     FNX_CUDA_OK(cudaMemcpyAsync(e->d_tok, hs, sizeof(int) * T, cudaMemcpyHostToDevice, e->st));
@@ -796,17 +833,16 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
         hs[2 * FNX_MAX_ROWS] = (int) s.step++;
         FNX_CUDA_OK(cudaMemcpyAsync(e->d_step + seq, hs + 2 * FNX_MAX_ROWS, sizeof(int), cudaMemcpyHostToDevice, e->st));
     }
-    const bool tree = h_parent != nullptr;
-    FNX_REQUIRE(!(tree && e->sampling_on), "fnx_engine_verify: the sampling rule is defined on chains (parent must be null)");
     const uint64_t key = ((uint64_t) 1 << 60) | ((uint64_t) seq << 20) | ((uint64_t) T << 1) | (tree ? 1 : 0);
-    if (step_ok(e, T) && !e->sampling_on) {
-        FNX_TRY(step_prepare(e, key, seq, T, tree));
-        StepParams* dp = e->step_params[key];
-        FNX_TRY(run_graph(e, key, [&]() { return step_launch(dp, T, e->d_sync, e->st); }));
+    if (win_ok(e, T)) {
+        FNX_TRY(win_prepare(e, key, seq, T, tree, false));
+        const WinParams& wp = e->win_params[key];
+        FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify_window(e, wp, seq, T, tree); }));
     } else {
         FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
     }
     s.last_T = T;
+    e->last_seq = seq;
     if (h_result) {
         FNX_CUDA_OK(cudaMemcpyAsync(hs + 2 * FNX_MAX_ROWS, e->result, sizeof(int) * (1 + 2 * FNX_MAX_ROWS), cudaMemcpyDeviceToHost, e->st));
         FNX_CUDA_OK(cudaMemcpyAsync(hs + 5 * FNX_MAX_ROWS, e->err, sizeof(unsigned), cudaMemcpyDeviceToHost, e->st));
@@ -865,6 +901,8 @@ extern "C" int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int 
     FNX_REQUIRE(e && h_path && seq >= 0 && seq < e->c.n_seq, "fnx_engine_commit: bad arguments");
     SeqState& s = e->seqs[seq];
     FNX_REQUIRE(s.last_T > 0, "fnx_engine_commit: no verified window to commit");
+    FNX_REQUIRE(seq == e->last_seq, "fnx_engine_commit: sequence %d, but the window buffers hold sequence %d's window (commit before verifying another sequence)", seq,
+                e->last_seq);
     FNX_REQUIRE(n >= 1 && n <= s.last_T && h_path[0] == 0, "fnx_engine_commit: %d rows of a window of %d (the first kept row is row 0)", n, s.last_T);
     for (int j = 1; j < n; ++j) FNX_REQUIRE(h_path[j] > h_path[j - 1] && h_path[j] < s.last_T, "fnx_engine_commit: path[%d] = %d is not increasing", j, h_path[j]);
     const Dims d = dims(e->c);
@@ -908,53 +946,90 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
     FNX_REQUIRE(e && h_drafts && seq >= 0 && seq < e->c.n_seq && k >= 1 && k < e->c.max_rows, "fnx_engine_draft: bad arguments");
     SeqState& s = e->seqs[seq];
     FNX_REQUIRE(s.kept >= 1, "fnx_engine_draft: nothing committed since the last draft");
+    FNX_REQUIRE(seq == e->last_seq, "fnx_engine_draft: sequence %d, but the window buffers hold sequence %d's last window", seq, e->last_seq);
     const Dims d = dims(e->c);
     const int n = s.kept;
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     int* hs = e->h_stage;
-    float total_ms = 0.f;
-    // first call: the kept rows of the main model (gathered by path) with the tokens the window emitted
-    k_gather_rows<<<dim3((d.H + 255) / 256, n), 256, 0, e->st>>>(e->Rsrc, e->R, e->d_path, d.H);
-    FNX_LAUNCH_OK("draft gather");
-    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->result + 1 + FNX_MAX_ROWS, sizeof(int) * n, cudaMemcpyDeviceToDevice, e->st));
     hs[0] = s.kept_pos0;
     FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
-    FNX_TRY(run_graph(e, ((uint64_t) 2 << 60) | ((uint64_t) seq << 20) | (uint64_t) n, [&]() { return enqueue_mtp(e, seq, n, e->Rsrc); }));
-    FNX_CUDA_OK(cudaMemcpyAsync(hs + 8, e->d_draft, sizeof(int), cudaMemcpyDeviceToHost, e->st));
-    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
-    float ms = 0.f;
-    FNX_CUDA_OK(cudaEventElapsedTime(&ms, e->ev0, e->ev1));
-    total_ms += ms;
-    h_drafts[0] = hs[8];
-    // the chain: each draft from the draft layer's own last row and the previous draft
-    for (int j = 1; j < k; ++j) {
-        const int src_row = j == 1 ? n - 1 : 0;
-        FNX_CUDA_OK(cudaMemcpyAsync(e->Rsrc, e->Rm + (size_t) src_row * d.H, sizeof(float) * d.H, cudaMemcpyDeviceToDevice, e->st));
-        FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->d_draft, sizeof(int), cudaMemcpyDeviceToDevice, e->st));
-        hs[0] = s.kept_pos0 + n - 1 + j;
-        FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
-        FNX_TRY(run_graph(e, ((uint64_t) 2 << 60) | ((uint64_t) seq << 20) | 1u, [&]() { return enqueue_mtp(e, seq, 1, e->Rsrc); }));
-        FNX_CUDA_OK(cudaMemcpyAsync(hs + 8, e->d_draft, sizeof(int), cudaMemcpyDeviceToHost, e->st));
-        FNX_CUDA_OK(cudaStreamSynchronize(e->st));
-        FNX_CUDA_OK(cudaEventElapsedTime(&ms, e->ev0, e->ev1));
-        total_ms += ms;
-        h_drafts[j] = hs[8];
+    // The whole chain is one graph: the first call on the kept rows of the main model (gathered by path) with the tokens
+    // the window emitted, then k - 1 single-row calls, each from the draft layer's own last row and the previous draft;
+    // tokens and positions advance on the device, the k drafts come back in one copy.
+    const bool win = win_ok(e, n);
+    const uint64_t kbase = ((uint64_t) 2 << 60) | ((uint64_t) seq << 20);
+    if (win) {
+        FNX_TRY(win_prepare(e, kbase | (uint64_t) n, seq, n, false, true));
+        FNX_TRY(win_prepare(e, kbase | 1u, seq, 1, false, true));
     }
-    e->last_ms = total_ms;
+    auto mtp_call = [&](int T, int* out) -> int {
+        if (!win) {
+            FNX_TRY(enqueue_mtp(e, seq, T, e->Rsrc));
+            return fnx_argmax(e->logits, 1, d.V, out, nullptr, e->err, e->st);
+        }
+        FNX_TRY(win_launch(e->win_params[kbase | (uint64_t) T], e->d_sync, e->st));
+        return fnx_argmax(e->logits + (size_t) (T - 1) * d.V, 1, d.V, out, nullptr, e->err, e->st);
+    };
+    auto chain = [&]() -> int {
+        k_gather_rows<<<dim3((d.H + 255) / 256, n), 256, 0, e->st>>>(e->Rsrc, e->R, e->d_path, d.H);
+        FNX_LAUNCH_OK("draft gather");
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->result + 1 + FNX_MAX_ROWS, sizeof(int) * n, cudaMemcpyDeviceToDevice, e->st));
+        FNX_TRY(mtp_call(n, e->d_drafts));
+        for (int j = 1; j < k; ++j) {
+            const int src_row = j == 1 ? n - 1 : 0;
+            FNX_CUDA_OK(cudaMemcpyAsync(e->Rsrc, e->Rm + (size_t) src_row * d.H, sizeof(float) * d.H, cudaMemcpyDeviceToDevice, e->st));
+            FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->d_drafts + (j - 1), sizeof(int), cudaMemcpyDeviceToDevice, e->st));
+            k_advance_pos<<<1, 1, 0, e->st>>>(e->d_mpos, j == 1 ? n : 1);
+            FNX_LAUNCH_OK("draft position");
+            FNX_TRY(mtp_call(1, e->d_drafts + j));
+        }
+        return FNX_OK;
+    };
+    FNX_TRY(run_graph(e, ((uint64_t) 3 << 60) | ((uint64_t) seq << 20) | ((uint64_t) k << 8) | (uint64_t) n, chain));
+    FNX_CUDA_OK(cudaMemcpyAsync(hs + 8, e->d_drafts, sizeof(int) * k, cudaMemcpyDeviceToHost, e->st));
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    FNX_CUDA_OK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+    memcpy(h_drafts, hs + 8, sizeof(int) * k);
     s.kept = 0;
     return FNX_OK;
 }
 
 extern "C" float fnx_engine_last_ms(const fnx_engine* e) { return e ? e->last_ms : 0.f; }
-extern "C" int fnx_engine_use_step_kernel(fnx_engine* e, int on) {
-    FNX_REQUIRE(e, "fnx_engine_use_step_kernel: null engine");
+extern "C" int fnx_engine_use_window_kernel(fnx_engine* e, int on) {
+    FNX_REQUIRE(e, "fnx_engine_use_window_kernel: null engine");
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
-    if ((on != 0) != e->use_step) {
+    if ((on != 0) != e->use_window) {
         for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
         e->graphs.clear();
         e->graph_kernels.clear();
-        e->use_step = on != 0;
+        e->use_window = on != 0;
     }
+    return FNX_OK;
+}
+
+// Phase stamps of the window kernel: on = 1 makes block 0 of every following window write tagged %globaltimer stamps
+// (tag in the top byte) to a device buffer; h_out (may be null) receives the last window's: word 0 = how many.
+extern "C" int fnx_engine_window_profile(fnx_engine* e, int on, unsigned long long* h_out, int cap) {
+    FNX_REQUIRE(e, "fnx_engine_window_profile: null engine");
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    if (h_out && cap > 0) {
+        const int n = cap < WIN_PROF_WORDS ? cap : WIN_PROF_WORDS;
+        FNX_CUDA_OK(cudaMemcpy(h_out, e->d_prof, sizeof(unsigned long long) * n, cudaMemcpyDeviceToHost));
+    }
+    if ((on != 0) != (e->prof_on != 0)) {
+        e->prof_on = on != 0;
+        for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+        e->graphs.clear();
+        e->graph_kernels.clear();
+        e->win_params.clear();   // the parameter blocks carry the buffer's address
+    }
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_error_bits(fnx_engine* e, unsigned* h_bits) {
+    FNX_REQUIRE(e && h_bits, "fnx_engine_error_bits: null pointer");
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    FNX_CUDA_OK(cudaMemcpy(h_bits, e->err, sizeof(unsigned), cudaMemcpyDeviceToHost));
     return FNX_OK;
 }
 

@@ -33,6 +33,8 @@ int fail(int code, const char* fmt, ...);
 
 inline cudaStream_t as_stream(fnx_stream s) { return (cudaStream_t) s; }
 int sm_count();
+// raises a kernel's dynamic shared-memory limit on the current device, once per (device, kernel)
+int set_smem_limit(const void* kernel, int bytes);
 // Programmatic dependent launch: every kernel of the window is launched so that it may start while its predecessor
 // in the stream drains.  A kernel does whatever does not depend on earlier kernels (its tables, its barriers, bulk
 // copies of weights), then pdl_wait() before it touches anything an earlier kernel wrote.  Off unless FNX_PDL=1:

@@ -210,11 +210,7 @@ extern "C" int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int lda
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && NS >= T + 1, "fnx_gdn_core: %d rows need at least %d state slots, have %d", T, T + 1, NS);
     FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_core: %d key heads, %d value heads", nk, nv);
     const size_t smem = sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T + (size_t) (T + 3) * (2 * GDN_HS + GDN_QC) + 3 * T);
-    static bool configured = false;
-    if (!configured) {
-        FNX_CUDA_OK(cudaFuncSetAttribute(k_gdn_core, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        configured = true;
-    }
+    if (int rc = set_smem_limit((const void*) k_gdn_core, 96 * 1024)) return rc;
     {
         const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), smem, as_stream(st), qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core: launch failed: %s", cudaGetErrorString(le_));

@@ -83,11 +83,7 @@ static int launch_mmv(const MmvParams& p0, cudaStream_t st) {
     while (p.R > 2 && mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max) > 227 * 1024) --p.R;
     const size_t smem = mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max);
     if (smem > 227 * 1024) return fail(FNX_E_ARG, "iq3s_mmv: %d columns x %d rows need %zu bytes of shared memory", p.K, 4 * NG, smem);
-    static bool configured = false;
-    if (!configured) {
-        FNX_CUDA_OK(cudaFuncSetAttribute(k_iq3s_mmv<NG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int rc = set_smem_limit((const void*) k_iq3s_mmv<NG, MODE>, 227 * 1024)) return rc;
     {
         const cudaError_t le_ = launch_k(k_iq3s_mmv<NG, MODE>, dim3(sm_count()), dim3(MMV_THREADS), smem, st, p);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "iq3s_mmv: launch failed: %s", cudaGetErrorString(le_));

@@ -31,6 +31,10 @@ struct MmvParams {
     int accumulate;
     int R;      // ring slots per warp
     unsigned* err;
+    // down mode, optional (MatDesc): weighted fixed-point sums instead of stored rows
+    const float* pairw;
+    unsigned long long* racc;
+    int TK, Ktop;
 };
 
 // jobs whose activation images a block holds at once: its range of units spans at most two jobs of gate|up and a
@@ -151,6 +155,7 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
     MatDesc m;
     m.W = p.W; m.expert_stride = p.expert_stride; m.e_base = p.e_base; m.Wsh = p.Wsh; m.E = p.E; m.jobs = MOE ? S.jobs_s : nullptr; m.jobw = nullptr; m.jobw0 = 0;
     m.rows = p.rows; m.K = p.K; m.out = p.out; m.ldo = p.ldo; m.accumulate = p.accumulate;
+    m.pairw = p.pairw; m.racc = p.racc; m.TK = p.TK; m.Ktop = p.Ktop;
     const int upj = p.rows / 16;
     const unsigned total = (unsigned) njobs * upj;   // < 2^24: the products below stay inside 32 bits
     const int u0 = (int) (total * bid / nblk), u1 = (int) (total * (bid + 1) / nblk);

@@ -546,12 +546,8 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     }
     k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, H, eps, xh);
     FNX_LAUNCH_OK("k_pf_xnorm");
-    static bool configured = false;
-    if (!configured) {
-        FNX_CUDA_OK(cudaFuncSetAttribute(k_pf_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) pf_smem(0)));
-        FNX_CUDA_OK(cudaFuncSetAttribute(k_pf_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) pf_smem(1)));
-        configured = true;
-    }
+    if (int rc = set_smem_limit((const void*) k_pf_gemm<0>, (int) pf_smem(0))) return rc;
+    if (int rc = set_smem_limit((const void*) k_pf_gemm<1>, (int) pf_smem(1))) return rc;
     // the job count is known on the device only: read it back (prefill is not captured into a graph)
     int nj = 0;
     FNX_CUDA_OK(cudaMemcpyAsync(&nj, njobs, sizeof(int), cudaMemcpyDeviceToHost, st));

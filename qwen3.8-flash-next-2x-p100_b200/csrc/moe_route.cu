@@ -7,55 +7,12 @@
 #include <algorithm>
 
 #include "fnx_common.cuh"
+#include "moe_route.cuh"
+#include "mmv_core.cuh"
 
 namespace fnxb {
 
-constexpr int RT_WARPS = 8, RT_TOK = 8, RT_MAXE = 1024, RT_SPLIT = 2, RT_ROWS = RT_WARPS / RT_SPLIT;
-
-// float -> unsigned key with the same order (so that warp-wide integer maxima rank logits)
-__device__ __forceinline__ unsigned rt_key(float v) {
-    const unsigned u = __float_as_uint(v);
-    return u & 0x80000000u ? ~u : u | 0x80000000u;
-}
-
-// Top K of one row's E logits by one warp: K rounds of (largest value, lowest index).  SL = slots per lane.
-template <int SL>
-__device__ __forceinline__ void rt_topk_row(const volatile float* l, int E, int K, int lane, int* topi_g, int* topi_s, float* topw_g) {
-    unsigned key[SL];
-#pragma unroll
-    for (int j = 0; j < SL; ++j) key[j] = lane + 32 * j < E ? rt_key(l[lane + 32 * j]) : 0u;
-    float top = 0.f, z = 0.f, mine = 0.f;
-    for (int k = 0; k < K; ++k) {
-        // the lane's largest key and its slot by a pairwise tree (depth log2 SL; among equals the lower slot)
-        unsigned tk[SL];
-        int tj[SL];
-#pragma unroll
-        for (int j = 0; j < SL; ++j) { tk[j] = key[j]; tj[j] = j; }
-#pragma unroll
-        for (int w = SL / 2; w >= 1; w >>= 1)
-#pragma unroll
-            for (int j = 0; j < w; ++j) {
-                const bool hi = tk[j + w] > tk[j];   // slots j < j + w: keep j on a tie
-                tk[j] = hi ? tk[j + w] : tk[j];
-                tj[j] = hi ? tj[j + w] : tj[j];
-            }
-        const unsigned bk = tk[0];
-        const int bj = tj[0];
-        const unsigned wk = __reduce_max_sync(0xffffffffu, bk);
-        const int bi = __reduce_min_sync(0xffffffffu, bk == wk ? lane + 32 * bj : 0x7fffffff);
-        const unsigned u = wk & 0x80000000u ? wk & 0x7fffffffu : ~wk;
-        const float bv = __uint_as_float(u);
-        if (k == 0) top = bv;
-        const float w = expf(bv - top);
-        z += w;
-        if (lane == k) mine = w;
-        if (lane == 0) { topi_g[k] = bi; topi_s[k] = bi; }
-#pragma unroll
-        for (int j = 0; j < SL; ++j)
-            if (lane + 32 * j == bi) key[j] = 0u;
-    }
-    if (lane < K) topw_g[lane] = mine / z;
-}
+constexpr int RT_WARPS = 8, RT_TOK = 8, RT_SPLIT = 2, RT_ROWS = RT_WARPS / RT_SPLIT;
 
 // Grid: ceil((E + 1) / RT_ROWS) blocks of RT_WARPS warps; a block computes RT_ROWS logit rows, RT_SPLIT warps per row
 // (each a contiguous share of the columns, summed in share order).
@@ -170,97 +127,38 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     __shared__ bool last;
     __shared__ int s_topi[FNX_MAX_ROWS * 32];
     __shared__ int s_cnt[RT_MAXE];
+    __shared__ int s_base[RT_MAXE];
+    __shared__ int wsum_[32];
+    __shared__ int total_[2];
     __threadfence();
     __syncthreads();
     if (tid == 0) last = atomicAdd(&njobs[1], 1) == (int) gridDim.x - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
-    for (int e = tid; e < RT_MAXE; e += NT) s_cnt[e] = 0;
-    {   // the job list is built in the rows' shared memory (free by now): unused row slots stay zero
-        const int cap = (T * K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK) * (int) (sizeof(fnx_job) / 4);
-        for (int w = tid; w < cap; w += NT) reinterpret_cast<int*>(xs)[w] = 0;
-    }
     // top K per row: a warp per row, K rounds of (value, index) maximum, ties to the lower index
     for (int t = warp; t < T; t += RT_WARPS) {
         const volatile float* l = logits + (size_t) t * (E + 1);
-        if (E <= 512) rt_topk_row<16>(l, E, K, lane, topi + t * K, s_topi + t * K, topw + t * K);
-        else rt_topk_row<RT_MAXE / 32>(l, E, K, lane, topi + t * K, s_topi + t * K, topw + t * K);
+        if (E <= 512) rt_topk_row<16>(l, E, K, lane, topi + t * K, s_topi + t * K, topw + t * K, nullptr);
+        else rt_topk_row<RT_MAXE / 32>(l, E, K, lane, topi + t * K, s_topi + t * K, topw + t * K, nullptr);
     }
     __syncthreads();
-    // how many rows picked each expert of this rank
-    for (int i = tid; i < T * K; i += NT) {
-        const int e = s_topi[i];
-        if (e >= e_lo && e < e_hi) atomicAdd(&s_cnt[e], 1);
-    }
-    __syncthreads();
-    // jobs in ascending expert order: expert e's rows in row order, 4 per job; then the shared expert's.
-    // Thread `tid` owns experts [tid * EPT, (tid + 1) * EPT): a block-wide exclusive scan of their job counts gives
-    // each expert's first job; then one thread per (row, pick) entry places itself, and the list is copied out.
-    constexpr int NTH = RT_WARPS * 32, EPT = RT_MAXE / NTH;
-    __shared__ int wsum_[RT_WARPS];
-    __shared__ int routed_total;
-    __shared__ int s_base[RT_MAXE];
-    int cnt_[EPT], mine = 0;
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        const int e = tid * EPT + j;
-        cnt_[j] = (s_cnt[e] + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
-        mine += cnt_[j];
-    }
-    int incl = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-    }
-    if (lane == 31) wsum_[warp] = incl;
-    __syncthreads();
-    int base_ = incl - mine;
-    for (int w = 0; w < warp; ++w) base_ += wsum_[w];
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        s_base[tid * EPT + j] = base_;
-        base_ += cnt_[j];
-    }
-    if (tid == NTH - 1) {
-        routed_total = base_;
-        njobs[0] = base_ + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
+    // the job list is built in the rows' shared memory (free by now) and copied out
+    RtJobSmem js;
+    js.s_topi = s_topi; js.s_cnt = s_cnt; js.s_base = s_base; js.wsum = wsum_; js.total = total_;
+    js.js = reinterpret_cast<fnx_job*>(xs);
+    rt_build_jobs<NT>(js, tid, T, E, K, e_lo, e_hi, add_shared);
+    const int total = total_[0];
+    if (tid == 0) {
+        njobs[0] = total;
         njobs[1] = 0;
         if (stats) {
-            atomicAdd(&stats[0], (unsigned long long) base_);
+            atomicAdd(&stats[0], (unsigned long long) total_[1]);
             atomicAdd(&stats[1], 1ull);
         }
     }
-    __syncthreads();
-    fnx_job* js = reinterpret_cast<fnx_job*>(xs);
-    const int total = routed_total + (add_shared ? (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0);
-    for (int i = tid; i < T * K; i += NTH) {
-        const int e = s_topi[i];
-        if (e < e_lo || e >= e_hi) continue;
-        int rank = 0;   // entries of the same expert before this one (row order)
-        for (int i2 = 0; i2 < i; ++i2) rank += s_topi[i2] == e;
-        fnx_job& jj = js[s_base[e] + rank / FNX_JOB_TOK];
-        jj.y[rank % FNX_JOB_TOK] = i / K;
-        jj.out[rank % FNX_JOB_TOK] = i;
-        if (rank % FNX_JOB_TOK == 0) {
-            jj.w = e;
-            jj.n = min(FNX_JOB_TOK, s_cnt[e] - rank);
-        }
-    }
-    if (add_shared)
-        for (int t = tid; t < T; t += NTH) {
-            fnx_job& j = js[routed_total + t / FNX_JOB_TOK];
-            j.y[t % FNX_JOB_TOK] = t;
-            j.out[t % FNX_JOB_TOK] = T * K + t;
-            if (t % FNX_JOB_TOK == 0) {
-                j.w = E;
-                j.n = min(FNX_JOB_TOK, T - t);
-            }
-        }
-    __syncthreads();
     constexpr int JW = sizeof(fnx_job) / 4;
-    for (int w = tid; w < total * JW; w += NTH) reinterpret_cast<int*>(jobs)[w] = reinterpret_cast<const int*>(js)[w];
+    for (int w = tid; w < total * JW; w += NT) reinterpret_cast<int*>(jobs)[w] = reinterpret_cast<const int*>(js.js)[w];
 }
 
 __global__ void k_combine(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
@@ -286,12 +184,14 @@ __global__ void k_combine(const float* __restrict__ part, const int* __restrict_
     const float shl = add_shared ? logits[(size_t) t * (E + 1) + E] : 0.f;
     float* o = out + (size_t) t * H + i;
     const float prev = accumulate ? *o : 0.f;
-    float s = 0.f;
+    // the addends are summed as 2^-32 fixed-point integers: the sum does not depend on their order, so this kernel, the
+    // window kernel's atomic adds and the expert-parallel ranks' partial sums all give the same bits
+    unsigned long long s = 0ull;
 #pragma unroll
     for (int k = 0; k < 32; ++k)
-        if (k < K) s = fmaf(w[k], v[k], s);
-    if (add_shared) s += sigmoidf_(shl) * shv;
-    *o = prev + s;
+        if (k < K && w[k] != 0.f) s += fix_from_float(w[k] * v[k]);
+    if (add_shared) s += fix_from_float(sigmoidf_(shl) * shv);
+    *o = prev + fix_to_float(s);
 }
 
 }  // namespace fnxb
@@ -308,11 +208,7 @@ extern "C" int fnx_router_route(const float* Wr, const float* x, const float* no
     FNX_REQUIRE(0 <= e_lo && e_lo <= e_hi && e_hi <= E, "fnx_router_route: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
     const size_t jobs_cap = (size_t) T * K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
     const size_t smem = std::max((size_t) RT_TOK * H * sizeof(float), jobs_cap * sizeof(fnx_job));
-    static bool configured = false;
-    if (!configured) {
-        FNX_CUDA_OK(cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        configured = true;
-    }
+    if (int rc = set_smem_limit((const void*) k_router, 160 * 1024)) return rc;
     const int blocks = (E + 1 + RT_ROWS - 1) / RT_ROWS;
     {
         const cudaError_t le_ = launch_k(k_router, dim3(blocks), dim3(RT_WARPS * 32), smem, as_stream(st), Wr, x, norm_w, eps, T, E, H, K, e_lo, e_hi, add_shared, logits, topi, topw, jobs,

@@ -207,11 +207,7 @@ extern "C" int fnx_accept_sample(const float* cand_v, const int* cand_i, const i
     FNX_REQUIRE(cand_v && cand_i && tok && step && result && T >= 1 && T <= FNX_MAX_ROWS, "fnx_accept_sample: bad arguments");
     FNX_REQUIRE(s.temperature > 0.f, "fnx_accept_sample: temperature %g (greedy windows use fnx_accept_greedy)", (double) s.temperature);
     const size_t smem = sizeof(DistS) * (size_t) T + sizeof(double) * FNX_TOPK_N * (size_t) T;
-    static bool configured = false;
-    if (!configured) {
-        FNX_CUDA_OK(cudaFuncSetAttribute(k_accept_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        configured = true;
-    }
+    if (int rc = set_smem_limit((const void*) k_accept_sample, 64 * 1024)) return rc;
     {
         const cudaError_t le_ = launch_k(k_accept_sample, dim3(1), dim3(1024), smem, as_stream(st), cand_v, cand_i, tok, T, s, q_ids, q_p, q_n, seed, seq, step, result);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_accept_sample: launch failed: %s", cudaGetErrorString(le_));

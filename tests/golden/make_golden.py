@@ -1,10 +1,10 @@
-"""Generates the committed golden fixtures (run in the build container, where the reference checkout exists).
+"""Generates the committed golden fixtures; needs a checkout of the reference (oracle/Makefile's REF) for ref_pins.npz.
 
     python tests/golden/make_golden.py
 
 ref_pins.npz    outputs of the REFERENCE's own host code (oracle/_ref: engine/src/tensor_convert.hpp dequantize,
-                engine/src/session.cpp make_dist / draw / lookup_drafts) on seeded inputs.  The GPU box has no
-                reference checkout; these vectors carry the pins there.
+                engine/src/session.cpp make_dist / draw / lookup_drafts) on seeded inputs: the vectors carry the
+                pins to machines without a reference checkout.
 oracle_cases.npz  small seeded operator cases with the oracle's outputs: they pin the oracle against accidental
                 change and give the GPU tests fixed inputs.
 """

@@ -146,7 +146,7 @@ def test_tree_verify_equals_chain_verify_of_the_accepted_path(F, model):
     assert em[0] == want[4]
 
 
-def test_step_kernel_equals_operator_path(F, model):
+def test_window_kernel_equals_operator_path(F, model):
     """The persistent one-kernel window and the launch-per-operator graph give the same window: same routing, same
     accepted tokens, hidden states and logits equal to rounding (both sum the K blocks in the same order)."""
     cfg, eng, _ = model
@@ -154,7 +154,7 @@ def test_step_kernel_equals_operator_path(F, model):
     prompt = rng.integers(0, cfg.vocab, size=21).tolist()
     outs = []
     for on in (False, True):
-        eng.use_step_kernel(on)
+        eng.use_window_kernel(on)
         eng.reset()
         eng.prefill(prompt)
         res = []
@@ -166,7 +166,7 @@ def test_step_kernel_equals_operator_path(F, model):
             res.append((r, R, lg, ti))
             eng.commit(r[1])
         outs.append(res)
-    eng.use_step_kernel(False)
+    eng.use_window_kernel(False)
     for (ra, Ra, la, ta), (rb, Rb, lb, tb) in zip(*outs):
         assert ra == rb and np.array_equal(ta, tb)
         assert rel_err(Rb, Ra) < 1e-4 and rel_err(lb, la) < 1e-4

@@ -171,6 +171,46 @@ def test_moe_block_matches_oracle(F, O, E, H, Fn, K, T):
     assert rel_err(acc, ref_out) < TOL_GEMV
 
 
+_CONFIG0 = {}
+
+
+def _config0_fixture(F):
+    """The first benchmark configuration's MoE block at its full size: hidden 2048, 512 routed experts of width 512
+    (N(0, 0.02) from seed 0, quantised to IQ3_S), top-10 + one shared expert; built once per session (700 MB of blocks)."""
+    if not _CONFIG0:
+        _CONFIG0.update(_moe_fixture(F, 512, 2048, 512, seed=0))
+    return _CONFIG0
+
+
+@pytest.mark.parametrize("T", [5, 20])
+def test_config0_moe_block_at_full_size(F, O, T):
+    """512 experts, top-10, 5 verify rows (seed 1) and a 20-row tree window: routing indices bit-exact, hidden states within
+    the kernels' 2e-3 (the target asks 1e-2); ~50 (T = 5) or ~170 (T = 20) jobs spread over the 148 blocks in several passes,
+    expert strides of 1.35 MB; expert-parallel shards of 2, 4 and 8 ranks add up to the whole."""
+    E, H, Fn, K = 512, 2048, 512, 10
+    fx = _config0_fixture(F)
+    x = np.random.default_rng(1).standard_normal((T, H)).astype(np.float32)
+    ref_out, ref_logits, ref_topi, ref_topw = O.moe(fx["wr"].cpu().numpy(), fx["gu_g"], fx["dn_g"], fx["sh_gu_g"], fx["sh_dn_g"], x, Fn, K)
+    srt = np.sort(ref_logits[:, :E], axis=1)
+    assert (srt[:, -K] - srt[:, -K - 1]).min() > 1e-5, "a near-tie at the top-K boundary: pick another seed"
+    route = F.router_route(fx["wr"], dev(x), K)
+    assert np.array_equal(route["topi"].cpu().numpy(), ref_topi)
+    _check_jobs(F, route, T, K, E, ref_topi, 0, E, True)
+    out, h, part = F.moe_experts(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], route, dev(x), Fn, K)
+    assert int(route["err"].item()) == 0
+    assert rel_err(out.cpu().numpy(), ref_out) < TOL_GEMV
+    gu_b, dn_b = F.iq3s_bytes(2 * Fn, H), F.iq3s_bytes(H, Fn)
+    for R in (2, 4, 8):
+        acc = np.zeros_like(ref_out)
+        for r in range(R):
+            lo, hi = r * E // R, (r + 1) * E // R
+            rt = F.router_route(fx["wr"], dev(x), K, e_lo=lo, e_hi=hi, add_shared=(r == 0))
+            o, _, _ = F.moe_experts(fx["gu_t"][lo * gu_b:hi * gu_b], fx["dn_t"][lo * dn_b:hi * dn_b], fx["sh_gu_t"], fx["sh_dn_t"], rt, dev(x), Fn, K,
+                                    e_base=lo, e_lo=lo, e_hi=hi, add_shared=(r == 0))
+            acc += o.cpu().numpy()
+        assert rel_err(acc, ref_out) < TOL_GEMV
+
+
 def test_router_many_tokens_pick_one_expert(F, O):
     # every row identical: all rows pick the same experts, so jobs split into groups of 4 rows
     E, H, K, T = 32, 1024, 4, 9
