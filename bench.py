@@ -117,34 +117,75 @@ def step_bytes(routed_jobs_per_step: float, ctx: int, T: int):
     return primary, primary + dense + router + state + head
 
 
-def cpu_step_seconds(F, O, eng, cfg, steps):
-    """The CPU restatement on the host cores, on a bounded sample: one DeltaNet layer, one attention layer (each with
-    its MoE block) and the head, for a 5-row window at the bench's context; a full step is 36 x the first + 12 x the
-    second + the head."""
+def cpu_leg(F, O, steps, threads):
+    """The CPU restatement on the host cores, on a bounded sample, and the full-size parity check that comes with it.
+
+    A four-layer engine of the benchmark model's own dimensions (three DeltaNet layers and one attention layer, random
+    init, seed 0) is mirrored by the oracle.  Parity: one 5-row window after a short prompt, engine against oracle
+    (routing indices, hidden states, logits, accepted tokens).  Timing: the oracle's DeltaNet layer and attention layer
+    (each with router, routed and shared experts) and the head on a 5-row window at the benchmark's context (the
+    attention cache filled with random f16 rows); a full 48-layer step is 36 x the first + 12 x the second + the head.
+    Returns (per-sample dicts, parity dict)."""
     import numpy as np
-    from helpers import OracleModel
-    om = OracleModel(F, O, eng, cfg, layers=[2, 3], with_mtp=False)
+    import torch
+    from helpers import OracleModel, rel_err
+    used = O.threads(threads)
+    cfg = F.flash_next_config(n_layer=4, max_ctx=CTX + 256, max_rows=8)
+    eng = F.Engine(cfg)
+    eng.init_synthetic(seed=0, sigma=0.02)
+    om = OracleModel(F, O, eng, cfg, with_mtp=False)
     rng = np.random.default_rng(1)
-    # the attention layer's cache: random f16 rows stand in for the 4,096-token context
-    L = om.layers[1]
+    # ---- parity at the benchmark's dimensions
+    prompt = rng.integers(0, cfg.vocab, size=12).tolist()
+    eng.reset()
+    eng.prefill(prompt)
+    for i in range(0, len(prompt), cfg.max_rows):
+        w = prompt[i:i + cfg.max_rows]
+        om.verify(w, None)
+        om.commit(list(range(len(w))))
+    toks = rng.integers(0, cfg.vocab, size=1 + K_DRAFT).tolist()
+    got = eng.verify(toks)
+    want = om.verify(toks, None)
+    T = len(toks)
+    R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:T]
+    logits = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:T]
+    topi = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:T]
+    parity = {"what": "4 layers of the benchmark model's dimensions (512 experts, hidden 2048, vocab 151936), 5-row window after a 12-token prompt, engine vs CPU oracle",
+              "rel_err_hidden": rel_err(R, om.R), "rel_err_logits": rel_err(logits, om.logits),
+              "routing_exact": bool(np.array_equal(topi, om.routing[-1][0])),
+              "accepted_exact": got == (want[0], list(want[1]), list(want[2]))}
+    assert parity["routing_exact"] and parity["accepted_exact"] and parity["rel_err_hidden"] < 2e-3 and parity["rel_err_logits"] < 2e-3, parity
+    eng.close()
+    # ---- timing sample
+    L = om.layers[3]
     L["kc"][:CTX] = rng.standard_normal((CTX, om.nkv, om.hd)).astype(np.float16).view(np.uint16)
     L["vc"][:CTX] = rng.standard_normal((CTX, om.nkv, om.hd)).astype(np.float16).view(np.uint16)
     om.pos = CTX
     R0 = rng.standard_normal((1 + K_DRAFT, om.H)).astype(np.float32)
-    ts = []
+    out = []
     for _ in range(steps):
         t0 = time.perf_counter()
         R = om._gdn(om.layers[0], R0, None)
         R = om._moe(om.layers[0], R)
         t1 = time.perf_counter()
-        R = om._attention(om.layers[1], R, om.pos, None, None)
-        R = om._moe(om.layers[1], R)
+        R = om._attention(om.layers[3], R, om.pos, None, None)
+        R = om._moe(om.layers[3], R)
         t2 = time.perf_counter()
-        logits = O.iq3s_gemv(om.head, om.V, om.H, O.rmsnorm(R, om.out_norm, cfg.eps))
-        O.argmax(logits)
+        lg = O.iq3s_gemv(om.head, om.V, om.H, O.rmsnorm(R, om.out_norm, cfg.eps))
+        O.argmax(lg)
         t3 = time.perf_counter()
-        ts.append(36 * (t1 - t0) + 12 * (t2 - t1) + (t3 - t2))
-    return ts
+        out.append({"sampled_s": t3 - t0, "step_s": 36 * (t1 - t0) + 12 * (t2 - t1) + (t3 - t2)})
+    return out, parity, used
+
+
+CPU_SAMPLE = ("per step: 1 DeltaNet layer + 1 attention layer (each with router, routed + shared experts) + the head of the benchmark model on the host "
+              "cores, 5-row window at ctx 4096; a verify step = 36 x the first + 12 x the second + the head (extrapolated); MTP chain not included")
+
+
+def bench_config(workload, world, layers):
+    """The `config` object of both arms' JSON lines (same keys, so that the two lines name the same workload)."""
+    return {"workload": workload, "timing": "inputs (34 GB of weights per step cycle) far larger than the 126 MB L2; CUDA events on the engine's stream",
+            "parallelism": f"ep{world}", "layers": layers}
 
 
 def main():
@@ -178,9 +219,13 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    cfg = model_config(F, rank if a.impl == "b200" else 0, world if a.impl == "b200" else 1, a.layers, a.warmup + a.steps, a.ctx)
-    eng = F.Engine(cfg)
-    eng.init_synthetic(seed=0, sigma=0.02)
+    hbm_peak, peak_kind = peaks()
+    workload = (f"verify step of the synthetic 48-layer Qwen3-Next-style model (IQ3_S, seed 0), ctx {CTX} uniform-random tokens (seed 1), "
+                f"k+1={1 + K_DRAFT} rows (1 committed + {K_DRAFT} drafts), greedy; drafts = own greedy continuation, each wrong with p={P_BAD}")
+    if a.impl != "reference":
+        cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, a.ctx)
+        eng = F.Engine(cfg)
+        eng.init_synthetic(seed=0, sigma=0.02)
     use_peer = False
     if world > 1 and a.impl == "b200":
         import ctypes as C
@@ -193,9 +238,9 @@ def main():
         dist.broadcast(uid, 0)
         raw = bytes(uid.cpu().numpy().tobytes())
         F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
-        # the peer-memory sum has been run on 2 GPUs of this pool; wider boxes could not be had to confirm it, so they use
-        # NCCL unless FNX_EP_PEER=1 asks otherwise
-        use_peer = os.environ.get("FNX_EP_NCCL", "0") != "1" and (world == 2 or os.environ.get("FNX_EP_PEER", "0") == "1")
+        # the per-layer sum goes over NVLink peer memory (fused with the combine) at every rank count; FNX_EP_NCCL=1 selects
+        # the NCCL all-reduce instead
+        use_peer = os.environ.get("FNX_EP_NCCL", "0") != "1"
         if use_peer:
             # the per-layer sum over NVLink peer memory instead of NCCL: exchange the ranks' IPC handles
             mine = (C.c_char * 128)()
@@ -236,23 +281,23 @@ def main():
                           "peak_tflops": tf_peak, "peak_kind": "measured" if pk else "fallback", "frac": flops / ms / 1e9 / tf_peak,
                           "err": int(err.item()), "note": "one layer's routed + shared experts; routing given; includes the job build and one host read of the job count"}))
         return
-    hbm_peak, peak_kind = peaks()
-    workload = (f"verify step of the synthetic 48-layer Qwen3-Next-style model (IQ3_S, seed 0), ctx {CTX} uniform-random tokens (seed 1), "
-                f"k+1={1 + K_DRAFT} rows (1 committed + {K_DRAFT} drafts), greedy; drafts = own greedy continuation, each wrong with p={P_BAD}")
-
     if a.impl == "reference":
         import oracle as O
-        ts = cpu_step_seconds(F, O, eng, cfg, a.warmup + a.steps)[a.warmup:]
-        t = sum(ts) / len(ts)
         cores = os.cpu_count() or 1
+        samples, parity, used = cpu_leg(F, O, a.warmup + a.steps, cores)
+        samples = samples[a.warmup:]
+        t_step = sum(s["step_s"] for s in samples) / len(samples)
+        t_sampled = sum(s["sampled_s"] for s in samples) / len(samples)
         # expected tokens per round at the drafts' acceptance: 1 + p + p^2 + ...
         exp_tok = sum((1 - P_BAD) ** j for j in range(K_DRAFT + 1))
-        v = exp_tok / t
-        sample = "per step: 1 DeltaNet layer + 1 attention layer (each with router, routed + shared experts) + head on the host cores, scaled 36x/12x/1x; MTP chain not included"
+        v = exp_tok / t_step
         line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
-                "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32",
-                "data": "synthetic", "config": {"workload": workload},
-                "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+                "ms_per_step": t_sampled * 1e3, "extrapolated": True, "extrapolated_step_ms": t_step * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32",
+                "data": "synthetic", "config": bench_config(workload, a.gpus, a.layers),
+                "cpu_baseline": {"value": v, "unit": "tok/s", "cores": used, "host_cores": cores, "kind": "port", "sample": CPU_SAMPLE,
+                                 "extrapolated": True, "scaling": "36 x DeltaNet layer + 12 x attention layer + 1 x head", "sampled_ms_per_step": t_sampled * 1e3},
+                "parity_full_size": parity,
                 "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return 0
@@ -345,8 +390,7 @@ def main():
     verify_ms = statistics.median(vts)
     line = {"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32",
-            "data": "synthetic", "config": {"workload": workload, "timing": "inputs (34 GB of weights per step cycle) far larger than the 126 MB L2; CUDA events on the engine's stream",
-                                            "parallelism": f"ep{world}", "layers": a.layers},
+            "data": "synthetic", "config": bench_config(workload, world, a.layers),
             "clocks": clk, "gpu_launches": int(launches),
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * (1 + K_DRAFT) + 4 * (1 + K_DRAFT) + 8, "d2h_bytes_per_step": 4 * 65 + 4 + 4 * K_DRAFT,
                     "wall_ms_per_step": wall * 1e3 / a.steps},
@@ -405,16 +449,20 @@ def main():
                             "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_PER_JOB * sum(njobs) / len(njobs),
                             "traffic_source": "ncu dram__bytes_read+write of one gate|up launch (46 jobs, 4-layer case): 42.02 MB, scaled by jobs per launch", "us_per_launch": per_launch_s * 1e6, "jobs_per_launch": sum(njobs) / len(njobs),
                             "algorithmic_bytes_per_launch": bytes_per_launch}
-        # ---- CPU restatement on the host cores, bounded sample
+        # ---- CPU restatement on the host cores, bounded sample; the full-size parity check rides along
         import oracle as O
-        ts = cpu_step_seconds(F, O, eng, cfg, 2)
+        eng.close()
+        eng = None
+        cores = os.cpu_count() or 1
+        samples, parity, used = cpu_leg(F, O, 2, cores)
         exp_tok = tokens / a.steps
-        line["cpu_baseline"] = {"value": exp_tok / ts[-1], "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
-                                "sample": "1 DeltaNet layer + 1 attention layer (each with router, routed + shared experts) + head, 5-row window, scaled 36x/12x/1x to a verify step; MTP chain not included",
-                                "verify_step_s": ts[-1]}
+        line["cpu_baseline"] = {"value": exp_tok / samples[-1]["step_s"], "unit": "tok/s", "cores": used, "host_cores": cores, "kind": "port",
+                                "sample": CPU_SAMPLE, "extrapolated": True, "verify_step_s": samples[-1]["step_s"], "sampled_s": samples[-1]["sampled_s"]}
+        line["parity_full_size"] = parity
     if rank == 0:
         print(json.dumps(line))
-    eng.close()
+    if eng is not None:
+        eng.close()
     if world > 1:
         torch.distributed.destroy_process_group()
     return 0

@@ -153,6 +153,15 @@ int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int ldab, float* h
                  const float* a, const float* nw, float* S_pool, const int* cur, int NS, const int* parent, float* y,
                  int nk, int nv, int hs, int T, float eps, fnx_stream st);
 
+/* ---------------------------------------------------------------------------------------------- commit
+ * Engine::commit at operator level (engine/src/engine_common.cu:710-754; its copies, copy_many, engine/src/kernels.hpp:429):
+ * keeps the window rows path[0..n) (device array, increasing, path[0] = 0).  The kept rows' K and V move to consecutive
+ * cache rows *pos0 .. *pos0 + n of every attention layer (k_caches / v_caches: device arrays of n_attn_layers cache
+ * pointers, rows of row_halves f16), the DeltaNet rings advance to the last kept row's slot (*cur = (*cur + 1 +
+ * path[n - 1]) % NS: the states themselves do not move), and *pos0 += n.  A chain kept as a prefix copies nothing. */
+int fnx_commit(void* const* k_caches, void* const* v_caches, int n_attn_layers, int row_halves, const int* path, int n,
+               int* pos0, int* cur, int NS, fnx_stream st);
+
 /* ---------------------------------------------------------------------------------------------- head
  * argmax (engine/src/kernels.hpp:433): per-row maximum, ties to the lower index; err bit 16 on a non-finite logit */
 int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st);
@@ -219,16 +228,6 @@ int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n);
 int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts);
 /* the device time of the last verify / draft graph launch in milliseconds (CUDA events on the engine's stream) */
 float fnx_engine_last_ms(const fnx_engine* e);
-/* Windows of up to 8 rows run as ONE persistent cooperative kernel (csrc/window.cu: every layer's projections,
- * mixer, router and experts as phases of one launch, with bounded grid barriers between them) instead of the
- * launch-per-operator graph (the reference's Engine::enqueue, engine/src/engine.cu:1760-1848); wider windows, and
- * expert-parallel ranks whose peer exchange is not open, take the launch-per-operator path.  on = 0 (or FNX_WINDOW=0 in
- * the environment) selects the launch-per-operator path for every window.  Drops the captured graphs. */
-int fnx_engine_use_window_kernel(fnx_engine* e, int on);
-/* Tracing of the window kernel (FNX_PROF, engine/src/engine.cu:1382-1529): on = 1 makes block 0 of the following
- * windows write tagged %globaltimer stamps (tag << 56 | ns) at its phase boundaries; h_out (may be null, cap words)
- * receives the last window's stamps, word 0 = their number.  Synchronises; drops the captured graphs when it switches. */
-int fnx_engine_window_profile(fnx_engine* e, int on, unsigned long long* h_out, int cap);
 /* the device error word (FNX_ERR_* bits) of the last window; synchronises.  fnx_engine_verify clears the word when it
  * starts a window, and returns FNX_E_STATE with the bits when it copies a result back. */
 int fnx_engine_error_bits(fnx_engine* e, unsigned* h_bits);

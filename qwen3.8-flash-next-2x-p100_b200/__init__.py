@@ -91,9 +91,8 @@ _PROTOS = {
     "fnx_engine_draft": (_I, [_P, _I, _I, _P]),
     "fnx_engine_last_ms": (_F, [_P]),
     "fnx_engine_counters": (_I, [_P, _P]),
-    "fnx_engine_use_window_kernel": (_I, [_P, _I]),
-    "fnx_engine_window_profile": (_I, [_P, _I, _P, _I]),
     "fnx_engine_error_bits": (_I, [_P, _P]),
+    "fnx_commit": (_I, [_P, _P, _I, _I, _P, _I, _P, _P, _I, _P]),
     "fnx_engine_pos": (_I, [_P, _I]),
     "fnx_engine_stream": (_P, [_P]),
     "fnx_comm_unique_id": (_I, [_P]),
@@ -436,19 +435,6 @@ class Engine:
         out, n = (C.c_int * MAX_ROWS)(), C.c_int()
         check(lib().fnx_engine_lookup(self._h, seq, lk, d1, root, out, C.byref(n)))
         return list(out[:n.value])
-
-    def use_window_kernel(self, on: bool):
-        check(lib().fnx_engine_use_window_kernel(self._h, 1 if on else 0))
-
-    def window_profile(self, on: bool, read: bool = False):
-        """Switches the window kernel's phase stamps on or off; read=True returns the last window's (tag, ns) stamps."""
-        import ctypes as C
-        buf = (C.c_ulonglong * 4096)() if read else None
-        check(lib().fnx_engine_window_profile(self._h, 1 if on else 0, buf, 4096 if read else 0))
-        if not read:
-            return None
-        n = int(buf[0])
-        return [(int(buf[1 + i]) >> 56, int(buf[1 + i]) & ((1 << 56) - 1)) for i in range(min(n, 4094))]
 
     def error_bits(self) -> int:
         import ctypes as C

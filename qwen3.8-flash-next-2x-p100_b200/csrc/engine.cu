@@ -16,7 +16,6 @@
 
 #include "fnx_common.cuh"
 #include "iq3s_tile.h"
-#include "window.cuh"
 
 namespace fnxb {
 
@@ -123,14 +122,6 @@ struct fnx_engine {
     uint64_t sample_seed = 0;
     uint32_t* d_step = nullptr;   // [n_seq] windows sampled so far (the Philox step)
     int* d_lk = nullptr;          // lookup: [0, MAX_ROWS) drafts, [MAX_ROWS, +2) count and match, +2 the first-draft filter, +3 the context length
-    // the persistent window kernel (windows of up to WIN_MAX_ROWS rows)
-    bool use_window = false;
-    std::map<uint64_t, WinParams> win_params;       // per graph key: the kernel's parameter block (passed by value)
-    unsigned* d_sync = nullptr;
-    float *d_gdn_o = nullptr, *d_gdn_sq = nullptr;
-    unsigned long long* d_racc = nullptr;
-    unsigned long long* d_prof = nullptr;
-    int prof_on = 0;
     unsigned long long launches = 0;
     std::map<uint64_t, unsigned> graph_kernels;
 };
@@ -287,10 +278,12 @@ __global__ void k_commit(__half* const* __restrict__ kcs, __half* const* __restr
         return;
     }
     if (threadIdx.x == 0) {
-        const int cn = *ctx_n;
-        for (int j = 0; j < n; ++j) ctx[cn + j] = tok[path[j]];
-        ctx[cn + n] = emitted[n - 1];
-        *ctx_n = cn + n;
+        if (ctx) {
+            const int cn = *ctx_n;
+            for (int j = 0; j < n; ++j) ctx[cn + j] = tok[path[j]];
+            ctx[cn + n] = emitted[n - 1];
+            *ctx_n = cn + n;
+        }
         *cur = (*cur + 1 + path[n - 1]) % NS;
     }
 }
@@ -493,91 +486,6 @@ static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
     return fnx_dense(e->head, d.V, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, d.V, 0, e->err, e->st);
 }
 
-// whether windows of T rows run as the persistent window kernel (window.cu)
-static bool win_ok(const fnx_engine* e, int T) {
-    const Dims d = dims(e->c);
-    const bool ep_ok = e->c.ep_size == 1 || (e->ep_peers && e->c.ep_size <= 8 && sm_count() <= 256);
-    return e->use_window && ep_ok && T <= WIN_MAX_ROWS && d.hd == 256 && d.hs == 128 && d.nq / d.nkv <= 8 && d.E <= 1024 && d.K <= 16 &&
-           d.H <= 2048 && d.F <= 2048 && d.nq * d.hd <= 4096 && d.nv * d.hs <= 4096 && (d.nv * d.hs) % 256 == 0 && (d.nq * d.hd) % 256 == 0;
-}
-static void win_fill_layer(const fnx_engine* e, const LayerW& L, int seq, WinLayer& s) {
-    const Dims d = dims(e->c);
-    s.attn = L.attn;
-    s.in_rows = L.in_rows;
-    s.norm1 = L.norm1; s.norm2 = L.norm2; s.w_in = L.w_in; s.w_out = L.w_out;
-    s.qn = L.qn; s.kn = L.kn;
-    s.kc = L.kc ? L.kc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
-    s.vc = L.vc ? L.vc + (size_t) seq * e->cache_rows * d.kv_rows : nullptr;
-    s.convw = L.convw; s.dt = L.dt; s.a = L.a; s.gnorm = L.gnorm;
-    s.S = L.S_pool ? L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs : nullptr;
-    s.hist = L.hist_pool ? L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch : nullptr;
-    s.wr = L.wr; s.wgu = L.wgu; s.wdn = L.wdn; s.wsh_gu = L.wsh_gu; s.wsh_dn = L.wsh_dn;
-}
-// the window kernel's parameter block for (sequence, rows, tree) or for a draft-layer call: built once, outside any capture
-static int win_prepare(fnx_engine* e, uint64_t key, int seq, int T, bool tree, bool mtp) {
-    if (e->win_params.count(key)) return FNX_OK;
-    const Dims d = dims(e->c);
-    WinParams p{};
-    p.n_layer = mtp ? 1 : (int) e->layers.size();
-    FNX_REQUIRE(p.n_layer <= WIN_MAX_LAYERS, "window kernel: %d layers (at most %d)", p.n_layer, WIN_MAX_LAYERS);
-    if (mtp) win_fill_layer(e, e->mtp, seq, p.layers[0]);
-    else
-        for (size_t l = 0; l < e->layers.size(); ++l) win_fill_layer(e, e->layers[l], seq, p.layers[l]);
-    p.H = d.H; p.E = d.E; p.K = d.K; p.F = d.F; p.nq = d.nq; p.nkv = d.nkv; p.hd = d.hd; p.nrot = d.nrot; p.nk = d.nk; p.nv = d.nv; p.hs = d.hs; p.V = d.V;
-    p.T = T; p.NS = e->NS; p.proj_ld = e->proj_ld; p.tree = tree ? 1 : 0;
-    p.e_lo = e->e_lo; p.e_hi = e->e_hi; p.e_base = e->e_lo;
-    p.ep_rank = e->c.ep_rank; p.ep_size = e->c.ep_size; p.maxr = d.MAXR;
-    p.eps = e->c.eps; p.rope_base = e->c.rope_base;
-    p.gu_bytes = e->gu_bytes; p.dn_bytes = e->dn_bytes;
-    p.tok = mtp ? e->d_mtok : e->d_tok;
-    p.parent = e->d_parent;
-    p.pos0 = mtp ? e->d_mpos : e->d_pos + seq;
-    p.cur = e->d_cur + seq;
-    p.depth = e->d_depth;
-    p.embed = e->embed; p.head = e->head; p.out_norm = mtp ? e->mtp_onorm : e->out_norm;
-    p.head_row0 = mtp ? T - 1 : 0;
-    p.R = mtp ? e->Rm : e->R;
-    p.proj = e->proj; p.mix = e->mix; p.logits = e->logits; p.rlogits = e->rlogits; p.topw = e->topw; p.hbuf = e->hbuf;
-    p.topi = e->topi; p.jobs = e->jobs; p.njobs = e->njobs;
-    const int S = sm_count() / d.nkv > 0 ? sm_count() / d.nkv : 1;
-    p.att_acc = (float*) e->att_scratch;
-    p.att_mz = (void*) (p.att_acc + (size_t) T * d.nq * S * d.hd);
-    p.gdn_o = e->d_gdn_o; p.gdn_sq = e->d_gdn_sq; p.racc = e->d_racc;
-    p.sync = e->d_sync; p.stats = e->d_stats; p.err = e->err; p.prof = e->prof_on ? e->d_prof : nullptr;
-    p.mtp = mtp ? 1 : 0;
-    {
-        const char* v = getenv("FNX_WIN_DBG");
-        p.dbg = v && v[0] == '1';
-    }
-    p.fc_hid = e->mtp_fc_hid; p.fc_emb = e->mtp_fc_emb; p.hnorm = e->mtp_hnorm; p.enorm = e->mtp_enorm;
-    p.src = e->Rsrc; p.emb = e->Emb;
-    if (e->c.ep_size > 1) {
-        std::vector<float*> px(e->c.ep_size);
-        std::vector<unsigned*> pf(e->c.ep_size);
-        FNX_CUDA_OK(cudaMemcpy(px.data(), e->d_peer_x, sizeof(float*) * e->c.ep_size, cudaMemcpyDeviceToHost));
-        FNX_CUDA_OK(cudaMemcpy(pf.data(), e->d_peer_flag, sizeof(unsigned*) * e->c.ep_size, cudaMemcpyDeviceToHost));
-        for (int r = 0; r < e->c.ep_size; ++r) {
-            p.peers.x[r] = (unsigned long long*) px[r];
-            p.peers.flag[r] = pf[r] + 2 * e->c.ep_size;   // past the launch-per-operator exchange's flags
-        }
-        p.xseq = e->d_xseq + 4;
-    }
-    e->win_params[key] = p;
-    return FNX_OK;
-}
-
-// the window kernel, then acceptance over its logits
-static int enqueue_verify_window(fnx_engine* e, const WinParams& wp, int seq, int T, bool tree) {
-    const Dims d = dims(e->c);
-    FNX_TRY(win_launch(wp, e->d_sync, e->st));
-    if (e->sampling_on) {
-        FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
-        return fnx_accept_sample(e->cand_v, e->cand_i, e->d_tok, T, e->sampling, nullptr, nullptr, nullptr, e->sample_seed, (uint32_t) seq, e->d_step + seq,
-                                 e->result, e->st);
-    }
-    FNX_TRY(fnx_argmax(e->logits, T, d.V, e->best_i, e->best_v, e->err, e->st));
-    return fnx_accept_greedy(e->d_tok, tree ? e->d_parent : nullptr, e->best_i, T, e->result, e->st);
-}
 template <typename F>
 static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
     auto it = e->graphs.find(key);
@@ -618,6 +526,18 @@ static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
 }
 
 }  // namespace fnxb
+
+extern "C" int fnx_commit(void* const* k_caches, void* const* v_caches, int n_attn_layers, int row_halves, const int* path, int n, int* pos0, int* cur,
+                          int NS, fnx_stream st) {
+    FNX_REQUIRE(path && pos0 && cur && (n_attn_layers == 0 || (k_caches && v_caches)), "fnx_commit: null pointer");
+    FNX_REQUIRE(n >= 1 && n <= FNX_MAX_ROWS && n_attn_layers >= 0 && row_halves >= 0 && NS >= 2, "fnx_commit: %d rows, %d layers, %d slots", n, n_attn_layers, NS);
+    k_commit<<<n_attn_layers + 1, 256, 0, as_stream(st)>>>((__half* const*) k_caches, (__half* const*) v_caches, n_attn_layers, row_halves, path, nullptr, nullptr, n,
+                                                             pos0, cur, NS, nullptr, nullptr);
+    FNX_LAUNCH_OK("fnx_commit");
+    k_advance_pos<<<1, 1, 0, as_stream(st)>>>(pos0, n);
+    FNX_LAUNCH_OK("fnx_commit (position)");
+    return FNX_OK;
+}
 
 extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) {
     FNX_REQUIRE(cfg && out, "fnx_engine_create: null pointer");
@@ -673,13 +593,11 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->part, (size_t) d.P * d.H, "buf.part"));
         FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
         if (c.ep_size > 1) {
-            // landing planes [2 slots][ranks][rows][H]: f32 for the launch-per-operator exchange, 64-bit fixed-point sums for
-            // the window kernel's (hence twice the floats); flags per (slot, rank) and, for the window kernel, per block
-            FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
-            FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size * (1 + 256), "buf.ep_flag"));
+            FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
+            FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size, "buf.ep_flag"));
             FNX_TRY(dalloc(e, &e->d_peer_x, (size_t) c.ep_size));
             FNX_TRY(dalloc(e, &e->d_peer_flag, (size_t) c.ep_size));
-            FNX_TRY(dalloc(e, &e->d_xseq, 8));
+            FNX_TRY(dalloc(e, &e->d_xseq, 4));
         }
         FNX_TRY(dalloc(e, &e->best_i, d.MAXR, "buf.best_i"));
         FNX_TRY(dalloc(e, &e->best_v, d.MAXR, "buf.best_v"));
@@ -701,15 +619,6 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_ctx_n, c.n_seq, "seq.ctx_n"));
         FNX_TRY(dalloc(e, &e->err, 1, "buf.err"));
         FNX_TRY(dalloc(e, &e->d_stats, 2, "buf.stats"));
-        FNX_TRY(dalloc(e, &e->d_sync, WIN_SYNC_WORDS, "buf.sync"));
-        FNX_TRY(dalloc(e, &e->d_gdn_o, (size_t) d.MAXR * d.nv * d.hs, "buf.gdn_o"));
-        FNX_TRY(dalloc(e, &e->d_gdn_sq, (size_t) d.MAXR * d.nv * 4, "buf.gdn_sq"));
-        FNX_TRY(dalloc(e, &e->d_racc, (size_t) d.MAXR * d.H, "buf.racc"));
-        FNX_TRY(dalloc(e, &e->d_prof, WIN_PROF_WORDS, "buf.prof"));
-        {
-            const char* v = getenv("FNX_WINDOW");
-            if (v) e->use_window = v[0] == '1';
-        }
         void* sc = nullptr;
         const size_t sb = fnx_attn_scratch_bytes(d.MAXR, d.nq, d.hd);
         FNX_TRY(dalloc(e, (uint8_t**) &sc, sb, "buf.attn_scratch"));
@@ -834,13 +743,7 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
         FNX_CUDA_OK(cudaMemcpyAsync(e->d_step + seq, hs + 2 * FNX_MAX_ROWS, sizeof(int), cudaMemcpyHostToDevice, e->st));
     }
     const uint64_t key = ((uint64_t) 1 << 60) | ((uint64_t) seq << 20) | ((uint64_t) T << 1) | (tree ? 1 : 0);
-    if (win_ok(e, T)) {
-        FNX_TRY(win_prepare(e, key, seq, T, tree, false));
-        const WinParams& wp = e->win_params[key];
-        FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify_window(e, wp, seq, T, tree); }));
-    } else {
-        FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
-    }
+    FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
     s.last_T = T;
     e->last_seq = seq;
     if (h_result) {
@@ -956,19 +859,9 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
     // The whole chain is one graph: the first call on the kept rows of the main model (gathered by path) with the tokens
     // the window emitted, then k - 1 single-row calls, each from the draft layer's own last row and the previous draft;
     // tokens and positions advance on the device, the k drafts come back in one copy.
-    const bool win = win_ok(e, n);
-    const uint64_t kbase = ((uint64_t) 2 << 60) | ((uint64_t) seq << 20);
-    if (win) {
-        FNX_TRY(win_prepare(e, kbase | (uint64_t) n, seq, n, false, true));
-        FNX_TRY(win_prepare(e, kbase | 1u, seq, 1, false, true));
-    }
     auto mtp_call = [&](int T, int* out) -> int {
-        if (!win) {
-            FNX_TRY(enqueue_mtp(e, seq, T, e->Rsrc));
-            return fnx_argmax(e->logits, 1, d.V, out, nullptr, e->err, e->st);
-        }
-        FNX_TRY(win_launch(e->win_params[kbase | (uint64_t) T], e->d_sync, e->st));
-        return fnx_argmax(e->logits + (size_t) (T - 1) * d.V, 1, d.V, out, nullptr, e->err, e->st);
+        FNX_TRY(enqueue_mtp(e, seq, T, e->Rsrc));
+        return fnx_argmax(e->logits, 1, d.V, out, nullptr, e->err, e->st);
     };
     auto chain = [&]() -> int {
         k_gather_rows<<<dim3((d.H + 255) / 256, n), 256, 0, e->st>>>(e->Rsrc, e->R, e->d_path, d.H);
@@ -995,37 +888,6 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
 }
 
 extern "C" float fnx_engine_last_ms(const fnx_engine* e) { return e ? e->last_ms : 0.f; }
-extern "C" int fnx_engine_use_window_kernel(fnx_engine* e, int on) {
-    FNX_REQUIRE(e, "fnx_engine_use_window_kernel: null engine");
-    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
-    if ((on != 0) != e->use_window) {
-        for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
-        e->graphs.clear();
-        e->graph_kernels.clear();
-        e->use_window = on != 0;
-    }
-    return FNX_OK;
-}
-
-// Phase stamps of the window kernel: on = 1 makes block 0 of every following window write tagged %globaltimer stamps
-// (tag in the top byte) to a device buffer; h_out (may be null) receives the last window's: word 0 = how many.
-extern "C" int fnx_engine_window_profile(fnx_engine* e, int on, unsigned long long* h_out, int cap) {
-    FNX_REQUIRE(e, "fnx_engine_window_profile: null engine");
-    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
-    if (h_out && cap > 0) {
-        const int n = cap < WIN_PROF_WORDS ? cap : WIN_PROF_WORDS;
-        FNX_CUDA_OK(cudaMemcpy(h_out, e->d_prof, sizeof(unsigned long long) * n, cudaMemcpyDeviceToHost));
-    }
-    if ((on != 0) != (e->prof_on != 0)) {
-        e->prof_on = on != 0;
-        for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
-        e->graphs.clear();
-        e->graph_kernels.clear();
-        e->win_params.clear();   // the parameter blocks carry the buffer's address
-    }
-    return FNX_OK;
-}
-
 extern "C" int fnx_engine_error_bits(fnx_engine* e, unsigned* h_bits) {
     FNX_REQUIRE(e && h_bits, "fnx_engine_error_bits: null pointer");
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));

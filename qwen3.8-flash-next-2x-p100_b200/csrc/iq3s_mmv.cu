@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     pdl_wait();   // from here on: what earlier kernels of the stream wrote (activations, job lists)
     // the job list or the first rows are fetched while the codebook is replicated and the barriers are set up
     StageRegs h;
-    stage_begin<NG, MODE>(p, h, tid, RowPlain());
+    stage_begin<NG, MODE, MMV_WARPS>(p, h, tid, RowPlain());
     core_fill_table(table, tid, MMV_THREADS);
     if (lane == 0) {
         for (int i = 0; i < R; ++i) mbar_init(&S.bars[warp * R + i], 1);
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     WarpRing ring;
     ring.parity = 0;
     stage_ring(ring, S, R, warp);
-    stage_run<NG, MODE>(p, S, ring, h, tid, blockIdx.x, gridDim.x, RowPlain(), [&]() { MMV_STAMP(); });
+    stage_run<NG, MODE, MMV_WARPS>(p, S, ring, h, tid, blockIdx.x, gridDim.x, RowPlain(), [&]() { MMV_STAMP(); });
     if (prof && tid == 0) prof[0] = (unsigned long long) nstamp;
 }
 

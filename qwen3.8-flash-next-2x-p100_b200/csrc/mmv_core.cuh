@@ -405,15 +405,10 @@ struct MatDesc {
     int rows, K;             // output rows per job (gate|up: F)
     float* out;
     int ldo, accumulate;
-    // down mode, optional: instead of storing the rows of `out`, add weight[pair] * value to the window's fixed-point
-    // sums racc[token][ldo] (pair = the job's output row; token = pair / Ktop, or pair - TK for the shared expert's rows)
-    const float* pairw;
-    unsigned long long* racc;
-    int TK, Ktop;
 };
 
-// fixed-point image of a float addend: integer sums do not depend on the order of their terms, so rows summed by
-// atomics, by a loop or across ranks give the same bits
+// fixed-point image of a float addend: integer sums do not depend on the order of their terms, so rows summed in any
+// order (a loop, several kernels, expert-parallel ranks) give the same bits
 constexpr float FIX_SCALE = 4294967296.0f;            // 2^32
 constexpr double FIX_INV = 1.0 / 4294967296.0;
 __device__ __forceinline__ unsigned long long fix_from_float(float v) { return (unsigned long long) __float2ll_rn(v * FIX_SCALE); }
@@ -472,13 +467,8 @@ __device__ __forceinline__ void mat_write_unit(const MatDesc& m, int lu, const i
             const int tok = 4 * ng + 2 * q + (k & 1), row = lu * 16 + g + 8 * (k >> 1);
             if (tok < ntok) {
                 const float v = MODE == MAT_GATEUP ? siluf_((float) gacc[ng][k]) * (float) acc[ng][k] : (float) acc[ng][k];
-                if (MODE == MAT_DOWN && m.racc) {
-                    const int pair = orow[tok], t = pair < m.TK ? pair / m.Ktop : pair - m.TK;
-                    atomicAdd(m.racc + (size_t) t * m.ldo + row, fix_from_float(m.pairw[pair] * v));
-                } else {
-                    float* dst = m.out + (size_t) orow[tok] * m.ldo + row;
-                    *dst = m.accumulate ? *dst + v : v;
-                }
+                float* dst = m.out + (size_t) orow[tok] * m.ldo + row;
+                *dst = m.accumulate ? *dst + v : v;
             }
         }
 }

@@ -31,10 +31,6 @@ struct MmvParams {
     int accumulate;
     int R;      // ring slots per warp
     unsigned* err;
-    // down mode, optional (MatDesc): weighted fixed-point sums instead of stored rows
-    const float* pairw;
-    unsigned long long* racc;
-    int TK, Ktop;
 };
 
 // jobs whose activation images a block holds at once: its range of units spans at most two jobs of gate|up and a
@@ -104,7 +100,7 @@ __device__ __forceinline__ void stage_ring(WarpRing& ring, const StageSmem& S, i
 
 // Starts the loads whose latency the caller may hide behind other work: the job list (expert modes) or the warp's
 // first rows to quantise (dense).  post(t, chunk, lane, v) may transform a fetched dense chunk of row t in place.
-template <int NG, int MODE, typename Post>
+template <int NG, int MODE, int NW = MMV_WARPS, typename Post>
 __device__ __forceinline__ void stage_begin(const MmvParams& p, StageRegs& h, int tid, Post&& post) {
     constexpr bool MOE = MODE != MAT_DENSE;
     constexpr int NROW = mmv_jmax<MODE>() * 4 * NG;
@@ -115,24 +111,24 @@ __device__ __forceinline__ void stage_begin(const MmvParams& p, StageRegs& h, in
         h.njobs = *p.njobs;
 #pragma unroll
         for (int i = 0; i < MMV_JOB_REGS; ++i) {
-            const int w = tid + i * MMV_THREADS;
+            const int w = tid + i * (NW * 32);
             h.jw[i] = w < nword ? reinterpret_cast<const int*>(p.jobs)[w] : 0;
         }
     } else {
 #pragma unroll
         for (int j = 0; j < QUANT_BATCH; ++j) {
-            const QuantTask q = stage_dense_task(p, warp + j * MMV_WARPS);
+            const QuantTask q = stage_dense_task(p, warp + j * NW);
             quant_fetch(q, p.norm_w, lane, h.v[j], h.w[j]);
             if (q.src) post(q.t, q.blk, lane, h.v[j]);
         }
     }
 }
 
-// The stage proper.  `bid` of `nblk` blocks share the matrix.  ring: the warp's ring, empty, set by stage_ring() (with
+// The stage proper.  `bid` of `nblk` blocks of NW warps share the matrix.  ring: the warp's ring, empty, set by stage_ring() (with
 // ring.pre set when mat_preissue() already ran for this block's first pass: dense stages only, whose weights do not
 // depend on what the stage waits for).  Ends with every result of the block written (no trailing barrier).
 // stamp(): a tracing hook called at the phase boundaries.
-template <int NG, int MODE, typename Post, typename Stamp>
+template <int NG, int MODE, int NW = MMV_WARPS, typename Post, typename Stamp>
 __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S, WarpRing& ring, StageRegs& h, int tid, int bid, int nblk, Post&& post,
                                           Stamp&& stamp) {
     constexpr int JMAX = mmv_jmax<MODE>(), NROW = JMAX * 4 * NG;
@@ -144,10 +140,10 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
         const int nword = p.njobs_max * MMV_JOB_WORDS;
 #pragma unroll
         for (int i = 0; i < MMV_JOB_REGS; ++i) {
-            const int w = tid + i * MMV_THREADS;
+            const int w = tid + i * (NW * 32);
             if (w < nword) reinterpret_cast<int*>(S.jobs_s)[w] = h.jw[i];
         }
-        for (int w = tid + MMV_JOB_REGS * MMV_THREADS; w < nword; w += MMV_THREADS) reinterpret_cast<int*>(S.jobs_s)[w] = reinterpret_cast<const int*>(p.jobs)[w];
+        for (int w = tid + MMV_JOB_REGS * (NW * 32); w < nword; w += (NW * 32)) reinterpret_cast<int*>(S.jobs_s)[w] = reinterpret_cast<const int*>(p.jobs)[w];
         njobs = min(h.njobs, p.njobs_max);
         __syncthreads();
     }
@@ -155,7 +151,6 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
     MatDesc m;
     m.W = p.W; m.expert_stride = p.expert_stride; m.e_base = p.e_base; m.Wsh = p.Wsh; m.E = p.E; m.jobs = MOE ? S.jobs_s : nullptr; m.jobw = nullptr; m.jobw0 = 0;
     m.rows = p.rows; m.K = p.K; m.out = p.out; m.ldo = p.ldo; m.accumulate = p.accumulate;
-    m.pairw = p.pairw; m.racc = p.racc; m.TK = p.TK; m.Ktop = p.Ktop;
     const int upj = p.rows / 16;
     const unsigned total = (unsigned) njobs * upj;   // < 2^24: the products below stay inside 32 bits
     const int u0 = (int) (total * bid / nblk), u1 = (int) (total * (bid + 1) / nblk);
@@ -164,7 +159,7 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
     for (int uc = u0; uc < u1;) {
         const int j0 = uc / upj, j1 = min(j0 + JMAX, (u1 - 1) / upj + 1), ue = min(u1, j1 * upj);
         // the pass's first tile blocks are on their way while the rows are quantised
-        if (!ring.pre) mat_preissue<MODE>(m, uc, ue, ring, warp, MMV_WARPS, lane, 2);
+        if (!ring.pre) mat_preissue<MODE>(m, uc, ue, ring, warp, NW, lane, 2);
         // live rows: the dense rows [0, T), or the rows of the pass's jobs; the others are cleared
         int nlive = MOE ? 0 : p.T, cum[JMAX + 1];
         cum[0] = 0;
@@ -177,11 +172,11 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
             nlive = cum[JMAX];
         }
         const int ntask = nlive * KB;
-        for (int id0 = warp; id0 < ntask; id0 += MMV_WARPS * QUANT_BATCH) {
+        for (int id0 = warp; id0 < ntask; id0 += NW * QUANT_BATCH) {
             QuantTask q[QUANT_BATCH];
 #pragma unroll
             for (int j = 0; j < QUANT_BATCH; ++j) {
-                const int id = id0 + j * MMV_WARPS;
+                const int id = id0 + j * NW;
                 if (!MOE) q[j] = stage_dense_task(p, id);
                 else {
                     q[j].src = nullptr;
@@ -206,7 +201,7 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
             quant_finish(q, h.v, h.w, p.K, norm_w, S.cells, S.scales, S.rs, lane);
         }
         {   // the rows that hold nothing
-            constexpr int TPR = MMV_THREADS / NROW;   // threads per image row
+            constexpr int TPR = (NW * 32) / NROW;   // threads per image row
             const int t = tid / TPR;
             bool live;
             if (!MOE) live = t < p.T;
@@ -240,12 +235,12 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
             }
         };
         if (ok) {
-            ok = mat_items<NG, MODE>(m, uc, ue, S.table_s, ring, S.pieces, warp, MMV_WARPS, lane, lane_x);
+            ok = mat_items<NG, MODE>(m, uc, ue, S.table_s, ring, S.pieces, warp, NW, lane, lane_x);
             if (!ok) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
         }
         __syncthreads();
         stamp();
-        if (ok) mat_combine<NG, MODE>(m, S.pieces, warp, MMV_WARPS, lane);
+        if (ok) mat_combine<NG, MODE>(m, S.pieces, warp, NW, lane);
         uc = ue;
         if (uc < u1) __syncthreads();   // the images and the pieces are rewritten by the next pass
         stamp();

@@ -184,8 +184,8 @@ __global__ void k_combine(const float* __restrict__ part, const int* __restrict_
     const float shl = add_shared ? logits[(size_t) t * (E + 1) + E] : 0.f;
     float* o = out + (size_t) t * H + i;
     const float prev = accumulate ? *o : 0.f;
-    // the addends are summed as 2^-32 fixed-point integers: the sum does not depend on their order, so this kernel, the
-    // window kernel's atomic adds and the expert-parallel ranks' partial sums all give the same bits
+    // the addends are summed as 2^-32 fixed-point integers: the sum does not depend on their order, so a row's result does not
+    // depend on how its picks are split over kernels or expert-parallel ranks
     unsigned long long s = 0ull;
 #pragma unroll
     for (int k = 0; k < 32; ++k)

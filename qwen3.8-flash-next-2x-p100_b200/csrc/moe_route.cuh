@@ -74,13 +74,12 @@ struct RtJobSmem {
 
 // The job list of T rows' picks, by all NTH threads of the block (every thread calls; the function synchronises the
 // block): jobs in ascending expert order, expert e's rows in row order, 4 per job; then (add_shared) the shared expert's.
-// Thread `tid` owns experts [tid * EPT, (tid + 1) * EPT): a block-wide exclusive scan of their job counts gives each
+// Thread `tid` owns experts [tid * EPT, (tid + 1) * EPT) below RT_MAXE: a block-wide exclusive scan of their job counts gives each
 // expert's first job; then one thread per (row, pick) entry places itself.  Returns the number of jobs in total[0] and
 // the routed ones in total[1] (valid after the call in every thread).
 template <int NTH>
 __device__ __forceinline__ void rt_build_jobs(const RtJobSmem& s, int tid, int T, int E, int K, int e_lo, int e_hi, int add_shared) {
-    static_assert(RT_MAXE % NTH == 0, "thread count must divide the expert limit");
-    constexpr int EPT = RT_MAXE / NTH, NW = NTH / 32;
+    constexpr int EPT = (RT_MAXE + NTH - 1) / NTH, NW = NTH / 32;
     const int warp = tid >> 5, lane = tid & 31;
     for (int e = tid; e < RT_MAXE; e += NTH) s.s_cnt[e] = 0;
     {   // unused row slots of the jobs stay zero
@@ -98,7 +97,7 @@ __device__ __forceinline__ void rt_build_jobs(const RtJobSmem& s, int tid, int T
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
         const int e = tid * EPT + j;
-        cnt_[j] = (s.s_cnt[e] + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
+        cnt_[j] = e < RT_MAXE ? (s.s_cnt[e] + FNX_JOB_TOK - 1) / FNX_JOB_TOK : 0;
         mine += cnt_[j];
     }
     int incl = mine;
@@ -113,7 +112,7 @@ __device__ __forceinline__ void rt_build_jobs(const RtJobSmem& s, int tid, int T
     for (int w = 0; w < warp; ++w) base_ += s.wsum[w];
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
-        s.s_base[tid * EPT + j] = base_;
+        if (tid * EPT + j < RT_MAXE) s.s_base[tid * EPT + j] = base_;
         base_ += cnt_[j];
     }
     if (tid == NTH - 1) {

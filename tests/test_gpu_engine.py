@@ -89,6 +89,43 @@ def test_verify_commit_draft_match_oracle(F, O, model):
     assert r1 == (r2[0], list(r2[1]), list(r2[2]))
 
 
+def test_full_size_layers_match_oracle(F, O):
+    """The benchmark model's own dimensions (hidden 2048, 512 experts top-10 of width 512, 16/2 attention heads of 256, 16/32
+    DeltaNet heads of 128, vocabulary 151,936), four layers of it (three DeltaNet, one attention): a prompt, a 5-row chain window
+    (the benchmark's window: ~50 expert jobs per layer, walked in several passes per block, expert strides of 1.35 MB) and a
+    tree window, against the oracle: the last layer's routing indices bit-exact (an earlier layer's mismatch would show in the
+    hidden states), hidden states and logits within the kernels' 2e-3 (the target asks 1e-2), accepted path and tokens equal."""
+    cfg = F.flash_next_config(n_layer=4, max_ctx=256, max_rows=8)
+    eng = F.Engine(cfg)
+    try:
+        eng.init_synthetic(seed=0, sigma=0.02)
+        om = OracleModel(F, O, eng, cfg, with_mtp=False)
+        rng = np.random.default_rng(5)
+        prompt = rng.integers(0, cfg.vocab, size=21).tolist()
+        eng.reset()
+        eng.prefill(prompt)
+        for i in range(0, len(prompt), cfg.max_rows):
+            w = prompt[i:i + cfg.max_rows]
+            om.verify(w, None)
+            om.commit(list(range(len(w))))
+        for toks, par in ((rng.integers(0, cfg.vocab, size=5).tolist(), None), (rng.integers(0, cfg.vocab, size=7).tolist(), [-1, 0, 1, 0, 3, 3, 1])):
+            T = len(toks)
+            got = eng.verify(toks, par)
+            want = om.verify(toks, par)
+            assert _routing_margin_ok(om, cfg.top_k), "pick another seed: a routing near-tie makes the comparison meaningless"
+            R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:T]
+            logits = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:T]
+            topi = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:T]
+            assert np.array_equal(topi, om.routing[-1][0])
+            assert rel_err(R, om.R) < 2e-3 and rel_err(logits, om.logits) < 2e-3
+            assert got == (want[0], list(want[1]), list(want[2]))
+            assert eng.error_bits() == 0
+            eng.commit(got[1])
+            om.commit(list(want[1]))
+    finally:
+        eng.close()
+
+
 def _greedy_plain(eng, prompt, steps):
     eng.reset()
     eng.prefill(prompt[:-1])
@@ -144,32 +181,6 @@ def test_tree_verify_equals_chain_verify_of_the_accepted_path(F, model):
     eng.commit(path)
     n, path, em = eng.verify([em[-1]])
     assert em[0] == want[4]
-
-
-def test_window_kernel_equals_operator_path(F, model):
-    """The persistent one-kernel window and the launch-per-operator graph give the same window: same routing, same
-    accepted tokens, hidden states and logits equal to rounding (both sum the K blocks in the same order)."""
-    cfg, eng, _ = model
-    rng = np.random.default_rng(11)
-    prompt = rng.integers(0, cfg.vocab, size=21).tolist()
-    outs = []
-    for on in (False, True):
-        eng.use_window_kernel(on)
-        eng.reset()
-        eng.prefill(prompt)
-        res = []
-        for toks, par in (([5, 6, 7, 8, 9], None), ([1, 2, 3, 4, 5, 6, 7], [-1, 0, 1, 0, 3, 3, 1]), ([11], None)):
-            r = eng.verify(toks, par)
-            R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:len(toks)].copy()
-            lg = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:len(toks)].copy()
-            ti = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:len(toks)].copy()
-            res.append((r, R, lg, ti))
-            eng.commit(r[1])
-        outs.append(res)
-    eng.use_window_kernel(False)
-    for (ra, Ra, la, ta), (rb, Rb, lb, tb) in zip(*outs):
-        assert ra == rb and np.array_equal(ta, tb)
-        assert rel_err(Rb, Ra) < 1e-4 and rel_err(lb, la) < 1e-4
 
 
 def test_engine_rejects_bad_calls(F, model):
