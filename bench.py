@@ -38,6 +38,8 @@ sys.path.insert(0, str(ROOT / "tests"))
 
 METRIC = "decode tok/s (MTP+lookup spec verify), verify-step us, % of HBM roofline"
 CTX, K_DRAFT, P_BAD = 4096, 4, 0.28
+C2_CTX, C2_LOOKUP = 32768, 15            # configuration 2: context and the longest lookup branch
+C4_CTX, C4_SEQS, C4_LANES = 131072, 8, 4   # configuration 4: context per sequence, sequences, lanes per window
 E_B = 1351680          # bytes of one expert: (2*512*2048 + 2048*512) * 110 / 256
 # DRAM bytes per expert job of the gate|up launch, from an ncu capture of one launch (dram__bytes_read.sum +
 # dram__bytes_write.sum = 42.02 MB for 46 jobs; the algorithmic figure is 901,120 bytes per job)
@@ -143,10 +145,14 @@ def cpu_leg(F, O, steps, threads):
         w = prompt[i:i + cfg.max_rows]
         om.verify(w, None)
         om.commit(list(range(len(w))))
-    toks = rng.integers(0, cfg.vocab, size=1 + K_DRAFT).tolist()
+    T = 1 + K_DRAFT
+    for _ in range(8):   # the first seeded window without a routing near-tie (top-K is discontinuous)
+        toks = rng.integers(0, cfg.vocab, size=T).tolist()
+        want = om.verify(toks, None)
+        gaps = [np.sort(lg[t, :-1])[::-1][cfg.top_k - 1:cfg.top_k + 1] for _, lg in om.routing for t in range(T)]
+        if min(float(g[0] - g[1]) for g in gaps) > 2e-4 * max(1.0, max(float(np.abs(lg).max()) for _, lg in om.routing)):
+            break
     got = eng.verify(toks)
-    want = om.verify(toks, None)
-    T = len(toks)
     R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:T]
     logits = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:T]
     topi = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:T]
@@ -182,6 +188,212 @@ CPU_SAMPLE = ("per step: 1 DeltaNet layer + 1 attention layer (each with router,
               "cores, 5-row window at ctx 4096; a verify step = 36 x the first + 12 x the second + the head (extrapolated); MTP chain not included")
 
 
+def _max_over_ranks(world, vals):
+    import torch
+    if world == 1:
+        return vals
+    t = torch.tensor(vals, device="cuda", dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def _barrier(world):
+    import torch
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def run_config4(a, F, eng, cfg, rank, world, local, use_peer):
+    """Configuration 4: 8 concurrent sequences, each at a 131,072-token context, MTP drafts of k = 4, the sampling rule at
+    temperature 0.7 with seeded Philox uniforms; expert-parallel over the ranks.  The sequences run as batched lanes: two
+    windows of four lanes (5 rows each) per round.  A step = one round of all 8 sequences: per window the MTP draft chain
+    over its lanes, the verify window, acceptance, commit.  The contexts are synthetic: seeded random K/V rows and DeltaNet
+    states stand in for 8 x 131,072 prefilled tokens (the values do not change the step's cost)."""
+    import numpy as np
+    import torch
+    ctx = a.ctx if a.ctx != CTX else C4_CTX
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    for l in range(a.layers):
+        attn = (l + 1) % cfg.attn_every == 0
+        if attn:
+            for nm in ("k_cache", "v_cache"):
+                t = eng.tensor(f"l{l}.{nm}", torch.float16)
+                for o in range(0, t.numel(), 1 << 28):   # in pieces of 2^28 elements
+                    t[o:o + (1 << 28)].normal_(0.0, 1.0, generator=g)
+        else:
+            eng.tensor(f"l{l}.state", torch.float32).normal_(0.0, 0.02, generator=g)
+            eng.tensor(f"l{l}.conv_hist", torch.float32).normal_(0.0, 0.5, generator=g)
+    for nm in ("k_cache", "v_cache"):
+        eng.tensor(f"mtp.{nm}", torch.float16).normal_(0.0, 1.0, generator=g)
+    for s in range(C4_SEQS):
+        eng.set_position(s, ctx)
+    samp = F.Sampling(0.7, 1.0, 0.0, 0)
+    eng.set_sampling(samp, seed=4)
+    rng = np.random.default_rng(4)
+    groups = [list(range(i, min(i + C4_LANES, C4_SEQS))) for i in range(0, C4_SEQS, C4_LANES)]
+    nxt = {s: int(rng.integers(0, cfg.vocab)) for s in range(C4_SEQS)}
+    have_kept = {s: False for s in range(C4_SEQS)}
+    clocks = Clocks(local)
+    clocks.launch()
+    est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dev_ms = verify_ms = 0.0
+    tokens = accepted = offered = 0
+    stream = []
+    c0 = None
+    for r in range(a.warmup + a.steps):
+        if r == a.warmup:
+            _barrier(world)
+            c0 = eng.counters()
+            clocks.start()
+            t0.record(est)
+            wall0 = time.perf_counter()
+        for grp in groups:
+            if have_kept[grp[0]]:
+                drafts = eng.draft_lanes(grp, K_DRAFT)
+                if r >= a.warmup:
+                    dev_ms += eng.last_ms()
+            else:
+                drafts = [rng.integers(0, cfg.vocab, size=K_DRAFT).tolist() for _ in grp]
+            res = eng.verify_lanes(grp, [[nxt[s]] + drafts[j] for j, s in enumerate(grp)])
+            if r >= a.warmup:
+                dev_ms += eng.last_ms()
+                verify_ms += eng.last_ms()
+            eng.commit_lanes(grp, [x[0] for x in res])
+            for j, s in enumerate(grp):
+                n, _, em = res[j]
+                nxt[s] = em[-1]
+                have_kept[s] = True
+                stream.extend(em)
+                if r >= a.warmup:
+                    tokens += n
+                    accepted += n - 1
+                    offered += K_DRAFT
+    t1.record(est)
+    _barrier(world)
+    wall = time.perf_counter() - wall0
+    clk = clocks.stop()
+    c1 = eng.counters()
+    dev_ms, e2e_ms = _max_over_ranks(world, [dev_ms, t0.elapsed_time(t1)])
+    T = C4_LANES * (1 + K_DRAFT)
+    jobs_per_window = (c1[1] - c0[1]) / max(1, c1[2] - c0[2]) * a.layers if c1[2] > c0[2] else 0.0
+    kv = 12 * C4_LANES * ((ctx + 5) * 2 * 256 * 2 * 2)
+    line = {"metric": METRIC, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
+            "config": {"workload": (f"configuration 4: {C4_SEQS} concurrent sequences at ctx {ctx} each (synthetic: seeded random K/V rows and DeltaNet states, seed 4), MTP k={K_DRAFT} "
+                                    f"drafts from the draft layer, sampling rule at temperature 0.7 (Philox, seed 4), batched lanes: {len(groups)} windows of {C4_LANES} lanes x "
+                                    f"{1 + K_DRAFT} rows per round; experts sharded over the ranks"),
+                       "timing": "per-step K/V reads (tens of GB) and expert weights far larger than the 126 MB L2; CUDA events on the engine's stream",
+                       "parallelism": f"ep{world}", "layers": a.layers},
+            "clocks": clk, "gpu_launches": int(c1[0] - c0[0]),
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": len(groups) * (4 * T + 4 * (2 * C4_LANES + 1) + 4 * C4_LANES * 2),
+                    "d2h_bytes_per_step": len(groups) * (4 * C4_LANES * 65 + 4 + 4 * C4_LANES * K_DRAFT), "wall_ms_per_step": wall * 1e3 / a.steps},
+            "verify_window_us": verify_ms * 1e3 / (a.steps * len(groups)), "accepted_per_offered": accepted / max(1, offered), "tokens_per_step": tokens / a.steps,
+            "tokens_crc": zlib.crc32(np.asarray(stream, np.int64).tobytes()), "ep_sum": "none" if world == 1 else ("peer-memory" if use_peer else "nccl"),
+            "window_bytes": {"kv_read": kv, "routed_jobs_per_window": jobs_per_window, "expert_bytes": (jobs_per_window + a.layers * 5) * E_B / max(1, world)}}
+    if rank == 0:
+        print(json.dumps(line))
+    eng.close()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+def edit_like_context(n, vocab, seed):
+    """Configuration 2's context: uniform-random tokens in which 60% of the positions are copies of earlier spans of
+    length 20-200 (an edit-like workload)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    out = rng.integers(0, vocab, size=n).tolist()
+    i = 256
+    while i < n:
+        if rng.random() < 0.6:
+            ln = int(rng.integers(20, 201))
+            src = int(rng.integers(0, max(1, i - ln)))
+            ln = min(ln, n - i)
+            out[i:i + ln] = out[src:src + ln]
+            i += ln
+        else:
+            i += int(rng.integers(20, 201) * 0.4 / 0.6) + 1
+    return out
+
+
+def run_config2(a, F, eng, cfg, rank, world, local, use_peer):
+    """Configuration 2: tree verification of an MTP chain of 4 plus a prompt-lookup branch of up to 15 tokens (3-gram match on
+    the GPU over the sequence's own 32,768-token edit-like context), greedy acceptance, rollback to the last accepted node.
+    A step = the MTP draft chain, the lookup, one tree window (root + chain + branch), acceptance, commit.  The text being
+    generated continues the edit-like context: the chain's drafts are the real draft layer's, the branch is what the
+    drafter finds."""
+    import numpy as np
+    import torch
+    ctx = a.ctx if a.ctx != CTX else C2_CTX
+    full = edit_like_context(ctx + 1, cfg.vocab, 2)
+    eng.reset()
+    eng.prefill(full[:-1])
+    x = full[-1]
+    clocks = Clocks(local)
+    clocks.launch()
+    est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dev_ms = verify_ms = 0.0
+    tokens = rows = lk_rows = lk_kept = 0
+    stream = []
+    have_kept = False
+    for r in range(a.warmup + a.steps):
+        if r == a.warmup:
+            _barrier(world)
+            c0 = eng.counters()
+            clocks.start()
+            t0.record(est)
+            wall0 = time.perf_counter()
+        chain = []
+        if have_kept:
+            chain = eng.draft(K_DRAFT)
+            if r >= a.warmup:
+                dev_ms += eng.last_ms()
+        lk = eng.lookup(C2_LOOKUP, root=x)
+        toks = [x] + chain + lk
+        par = [-1] + list(range(0, len(chain))) + ([0] + list(range(1 + len(chain), len(chain) + len(lk))) if lk else [])
+        n, path, em = eng.verify(toks, par)
+        if r >= a.warmup:
+            dev_ms += eng.last_ms()
+            verify_ms += eng.last_ms()
+            tokens += n
+            rows += len(toks)
+            lk_rows += len(lk)
+            lk_kept += sum(1 for p in path if p > len(chain))
+        eng.commit(path)
+        have_kept = True
+        stream.extend(em)
+        x = em[-1]
+    t1.record(est)
+    _barrier(world)
+    wall = time.perf_counter() - wall0
+    clk = clocks.stop()
+    c1 = eng.counters()
+    dev_ms, e2e_ms = _max_over_ranks(world, [dev_ms, t0.elapsed_time(t1)])
+    line = {"metric": METRIC, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
+            "config": {"workload": (f"configuration 2: tree windows (root + MTP chain of {K_DRAFT} + prompt-lookup branch of up to {C2_LOOKUP}) over a {ctx}-token edit-like context "
+                                    "(seed 2: 60% of positions copy earlier spans of 20-200 tokens), greedy acceptance, rollback to the last accepted node"),
+                       "timing": "inputs far larger than the 126 MB L2; CUDA events on the engine's stream", "parallelism": f"ep{world}", "layers": a.layers},
+            "clocks": clk, "gpu_launches": int(c1[0] - c0[0]),
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4 * 2 * 20 + 16, "d2h_bytes_per_step": 4 * 65 + 4 + 4 * K_DRAFT + 4 * 34,
+                    "wall_ms_per_step": wall * 1e3 / a.steps},
+            "verify_window_us": verify_ms * 1e3 / a.steps, "rows_per_window": rows / a.steps, "lookup_rows_per_window": lk_rows / a.steps,
+            "lookup_rows_kept_per_window": lk_kept / a.steps, "tokens_per_step": tokens / a.steps,
+            "tokens_crc": zlib.crc32(np.asarray(stream, np.int64).tobytes()), "ep_sum": "none" if world == 1 else ("peer-memory" if use_peer else "nccl"),
+            "note": "random-init weights: the model does not continue copied spans, so lookup rows are verified (and timed) but rarely kept"}
+    if rank == 0:
+        print(json.dumps(line))
+    eng.close()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
 def bench_config(workload, world, layers):
     """The `config` object of both arms' JSON lines (same keys, so that the two lines name the same workload)."""
     return {"workload": workload, "timing": "inputs (34 GB of weights per step cycle) far larger than the 126 MB L2; CUDA events on the engine's stream",
@@ -197,6 +409,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 4],
+                    help="the benchmark configuration: 1 = 5-row chain windows at ctx 4096 (the headline), 2 = tree windows of an MTP chain + a prompt-lookup "
+                         "branch over a 32,768-token edit-like context, 4 = 8 concurrent sequences at ctx 131,072 with the sampling rule (batched lanes)")
     ap.add_argument("--layers", type=int, default=48, help="fewer layers for a quick functional run (not a valid bench number)")
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (the benchmark's is 4096)")
     ap.add_argument("--prefill-moe", type=int, default=0, metavar="T",
@@ -223,7 +438,16 @@ def main():
     workload = (f"verify step of the synthetic 48-layer Qwen3-Next-style model (IQ3_S, seed 0), ctx {CTX} uniform-random tokens (seed 1), "
                 f"k+1={1 + K_DRAFT} rows (1 committed + {K_DRAFT} drafts), greedy; drafts = own greedy continuation, each wrong with p={P_BAD}")
     if a.impl != "reference":
-        cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, a.ctx)
+        if a.config == 4:
+            ctx4 = a.ctx if a.ctx != CTX else C4_CTX
+            room = (a.warmup + a.steps + 8) * (K_DRAFT + 1) + 64
+            cfg = F.flash_next_config(n_layer=a.layers, max_ctx=ctx4 + (room + 255) // 256 * 256, max_rows=C4_LANES * (1 + K_DRAFT), ep_rank=rank, ep_size=world,
+                                      n_seq=C4_SEQS)
+        elif a.config == 2:
+            ctx2 = a.ctx if a.ctx != CTX else C2_CTX
+            cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, ctx2)
+        else:
+            cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, a.ctx)
         eng = F.Engine(cfg)
         eng.init_synthetic(seed=0, sigma=0.02)
     use_peer = False
@@ -250,6 +474,10 @@ def main():
             dist.all_gather(allh, hm)
             blob = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
             F.check(F.lib().fnx_engine_ep_open(eng._h, blob, rank, world))
+    if a.config == 4:
+        return run_config4(a, F, eng, cfg, rank, world, local, use_peer)
+    if a.config == 2:
+        return run_config2(a, F, eng, cfg, rank, world, local, use_peer)
     if a.prefill_moe:
         # config 3's expert path on one layer: T rows grouped by expert, gate|up + SwiGLU + down on the tensor cores
         T = a.prefill_moe

@@ -35,6 +35,7 @@ enum { FNX_ERR_TIMEOUT = 1, FNX_ERR_NONFINITE = 2, FNX_ERR_LOGITS = 16 };
 enum { FNX_TOPK_N = 64,      /* sampler candidates per row (TOPK_N, engine/src/kernels.hpp:441) */
        FNX_MAX_ROWS = 32,    /* rows (tree nodes) of one verify window */
        FNX_JOB_TOK = 4,      /* activation rows of one expert job */
+       FNX_LANE_ROWS = 5,    /* rows of one lane of a batched window */
        FNX_ATTN_STATIC_MAX_SLOTS = 16384 };   /* (row, head, split) partials fnx_attn_static's built-in scratch holds */
 
 const char* fnx_last_error(void);
@@ -144,6 +145,18 @@ int fnx_attn_static_setup(void);
 int fnx_attn_static(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
                     const int* pos0, const int* parent, fnx_stream st);
 
+/* Batched lanes of attention (enqueue_rows, engine/src/engine.cu:1936): lane j = rows [lane_row0[j], lane_row0[j + 1]) of
+ * the window (at most FNX_LANE_ROWS rows), a chain of sequence lane_seq[j] at position pos[lane_seq[j]], reading and
+ * appending that sequence's caches at kc_base / vc_base + seq * seq_stride_rows rows.  Same kernels' bodies and results as
+ * the single-sequence calls. */
+int fnx_attn_prep_append_lanes(float* qg, int ldq, float* k, int ldk, const float* v, int ldv, const float* q_norm,
+                               const float* k_norm, void* kc_base, void* vc_base, size_t seq_stride_rows, int n_lanes,
+                               int max_lane_rows, int nq, int nkv, int hd, int nrot, const int* pos, const int* lane_seq,
+                               const int* lane_row0, float eps, float rope_base, fnx_stream st);
+int fnx_attn_lanes(const float* qg, int ldq, const void* kc_base, const void* vc_base, size_t seq_stride_rows, float* out,
+                   int T, int n_lanes, int nq, int nkv, int hd, const int* pos, const int* lane_seq, const int* lane_row0,
+                   void* scratch, fnx_stream st);
+
 /* ---------------------------------------------------------------------------------------------- gated DeltaNet
  * gdn_core (engine/src/kernels.hpp:97-99).  State and conv-history rings of NS slots replace snap / hsnap + the
  * commit copy: the window starts from slot *cur; row t starts from its parent's result and writes slot
@@ -152,6 +165,14 @@ int fnx_attn_static(const float* qg, int ldq, const void* kc, const void* vc, fl
 int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt,
                  const float* a, const float* nw, float* S_pool, const int* cur, int NS, const int* parent, float* y,
                  int nk, int nv, int hs, int T, float eps, fnx_stream st);
+
+/* Batched lanes of gdn_core (gdn_core_segs, engine/src/kernels.cu:2112-2156; GdnLanes, engine/src/kernels.hpp:103-110):
+ * lane j is a chain from slot cur[lane_seq[j]] of that sequence's rings at hist_pool + seq * hist_seq_stride floats and
+ * S_pool + seq * s_seq_stride floats. */
+int fnx_gdn_core_lanes(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, size_t hist_seq_stride,
+                       const float* convw, const float* dt, const float* a, const float* nw, float* S_pool,
+                       size_t s_seq_stride, const int* cur, int NS, const int* lane_seq, const int* lane_row0, int n_lanes,
+                       int max_lane_rows, float* y, int nk, int nv, int hs, float eps, fnx_stream st);
 
 /* ---------------------------------------------------------------------------------------------- commit
  * Engine::commit at operator level (engine/src/engine_common.cu:710-754; its copies, copy_many, engine/src/kernels.hpp:429):
@@ -189,6 +210,12 @@ typedef struct {
 int fnx_accept_sample(const float* cand_v, const int* cand_i, const int* tok, int T, fnx_sampling s, const int* q_ids,
                       const double* q_p, const int* q_n, uint64_t seed, uint32_t seq, const uint32_t* step,
                       int* result, fnx_stream st);
+/* Batched lanes of the two rules: lane j's chain is rows [lane_row0[j], lane_row0[j + 1]); result [n_lanes][1 + 2
+ * FNX_MAX_ROWS]; the sampling rule draws sequence lane_seq[j]'s uniforms at window steps[lane_seq[j]], drafts fixed. */
+int fnx_accept_greedy_lanes(const int* tok, const int* best, const int* lane_row0, int n_lanes, int* result, fnx_stream st);
+int fnx_accept_sample_lanes(const float* cand_v, const int* cand_i, const int* tok, fnx_sampling s, uint64_t seed,
+                            const int* lane_seq, const int* lane_row0, int n_lanes, int max_lane_rows,
+                            const uint32_t* steps, int* result, fnx_stream st);
 
 /* ---------------------------------------------------------------------------------------------- engine
  * The thin window scheduler: Engine::verify / commit / draft (engine/src/engine.hpp:50-229) for the synthetic
@@ -239,6 +266,22 @@ int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uint64_t seed)
  * the pending one; root >= 0 replaces the pending token, for a caller that starts the next window from another token):
  * up to lk drafts into h_out, their number into h_n; d1 >= 0 keeps only a match whose first draft is d1. */
 int fnx_engine_lookup(fnx_engine* e, int seq, int lk, int d1, int root, int* h_out, int* h_n);
+/* Batched lanes (Engine::verify_rows / commit_rows / draft_rows, engine/src/engine_common.cu:1234-1684; GdnLanes,
+ * engine/src/kernels.hpp:103-110): one window holds `rows` <= FNX_LANE_ROWS rows of each of n_lanes distinct sequences
+ * (n_lanes * rows <= max_rows), every lane a chain continuing its own sequence.  Projections, router, experts and head run
+ * over all rows at once (an expert picked by rows of several lanes is read once); attention, DeltaNet, acceptance and
+ * commit go by lane with that sequence's position, caches and state.  A lane's results are bit-identical to the same rows
+ * run through fnx_engine_verify on that sequence alone.
+ * h_tok [n_lanes][rows]; h_results [n_lanes][1 + 2 FNX_MAX_ROWS] (per lane as fnx_engine_verify's result).
+ * commit_lanes keeps the first h_keep[j] rows of lane j (chains are kept as prefixes); draft_lanes runs the MTP layer on
+ * every lane's kept rows and k - 1 chained calls of one row per lane, h_drafts [n_lanes][k]. */
+int fnx_engine_verify_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_tok, int rows, int* h_results);
+int fnx_engine_commit_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_keep);
+int fnx_engine_draft_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, int k, int* h_drafts);
+/* Places sequence `seq` at position `pos` as if that many tokens had been read, without reading them: its K/V rows and
+ * DeltaNet state keep whatever they hold (fill them through fnx_engine_tensor).  For throughput measurements at long
+ * contexts; results afterwards are a function of that memory, not of a token history. */
+int fnx_engine_set_position(fnx_engine* e, int seq, int pos);
 /* counters since creation: [0] kernels launched through graphs, [1] routed expert jobs, [2] router calls */
 int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3);
 int fnx_engine_pos(const fnx_engine* e, int seq);

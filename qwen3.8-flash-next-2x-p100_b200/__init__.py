@@ -93,6 +93,15 @@ _PROTOS = {
     "fnx_engine_counters": (_I, [_P, _P]),
     "fnx_engine_error_bits": (_I, [_P, _P]),
     "fnx_commit": (_I, [_P, _P, _I, _I, _P, _I, _P, _P, _I, _P]),
+    "fnx_engine_verify_lanes": (_I, [_P, _I, _P, _P, _I, _P]),
+    "fnx_engine_commit_lanes": (_I, [_P, _I, _P, _P]),
+    "fnx_engine_draft_lanes": (_I, [_P, _I, _P, _I, _P]),
+    "fnx_engine_set_position": (_I, [_P, _I, _I]),
+    "fnx_attn_prep_append_lanes": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _F, _P]),
+    "fnx_attn_lanes": (_I, [_P, _I, _P, _P, _Z, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "fnx_gdn_core_lanes": (_I, [_P, _I, _P, _I, _P, _Z, _P, _P, _P, _P, _P, _Z, _P, _I, _P, _P, _I, _I, _P, _I, _I, _I, _F, _P]),
+    "fnx_accept_greedy_lanes": (_I, [_P, _P, _P, _I, _P, _P]),
+    "fnx_accept_sample_lanes": (_I, [_P, _P, _P, Sampling, _U64, _P, _P, _I, _I, _P, _P, _P]),
     "fnx_engine_pos": (_I, [_P, _I]),
     "fnx_engine_stream": (_P, [_P]),
     "fnx_comm_unique_id": (_I, [_P]),
@@ -435,6 +444,39 @@ class Engine:
         out, n = (C.c_int * MAX_ROWS)(), C.c_int()
         check(lib().fnx_engine_lookup(self._h, seq, lk, d1, root, out, C.byref(n)))
         return list(out[:n.value])
+
+    def verify_lanes(self, seqs, rows_of_tokens, want_result: bool = True):
+        """One window of several sequences' rows (a chain of equal length per sequence): per lane (n, path, emitted)."""
+        import ctypes as C
+        L, T = len(seqs), len(rows_of_tokens[0])
+        assert all(len(r) == T for r in rows_of_tokens) and len(rows_of_tokens) == L
+        sq = (C.c_int * L)(*seqs)
+        tok = (C.c_int * (L * T))(*[t for r in rows_of_tokens for t in r])
+        W = 1 + 2 * MAX_ROWS
+        res = (C.c_int * (L * W))() if want_result else None
+        check(lib().fnx_engine_verify_lanes(self._h, L, sq, tok, T, res))
+        if not want_result:
+            return None
+        out = []
+        for j in range(L):
+            r = res[j * W:(j + 1) * W]
+            out.append((r[0], list(r[1:1 + r[0]]), list(r[1 + MAX_ROWS:1 + MAX_ROWS + r[0]])))
+        return out
+
+    def commit_lanes(self, seqs, keep):
+        import ctypes as C
+        L = len(seqs)
+        check(lib().fnx_engine_commit_lanes(self._h, L, (C.c_int * L)(*seqs), (C.c_int * L)(*keep)))
+
+    def draft_lanes(self, seqs, k: int):
+        import ctypes as C
+        L = len(seqs)
+        out = (C.c_int * (L * k))()
+        check(lib().fnx_engine_draft_lanes(self._h, L, (C.c_int * L)(*seqs), k, out))
+        return [list(out[j * k:(j + 1) * k]) for j in range(L)]
+
+    def set_position(self, seq: int, pos: int):
+        check(lib().fnx_engine_set_position(self._h, seq, pos))
 
     def error_bits(self) -> int:
         import ctypes as C

@@ -44,6 +44,38 @@ __global__ void __launch_bounds__(ATT_THREADS * ATC_G) k_attn_combine(const floa
     attn_combine_body<ATC_G>(acc_in, mz_in, qg, ldq, out, nq, hd, S, (int) blockIdx.x, (int) blockIdx.y, (int) threadIdx.x, sm, SyncBlock());
 }
 
+// ---- batched lanes: the rows of several sequences in one window.  Lane j holds the consecutive rows
+// [lane_row0[j], lane_row0[j + 1]) of sequence lane_seq[j]: a chain that starts at that sequence's position pos[seq] and
+// reads / appends that sequence's caches (kc_base + seq * seq_stride halves).  The bodies are the single-sequence ones
+// with their pointers moved to the lane's rows (GdnLanes / enqueue_rows, engine/src/kernels.hpp:103-110,
+// engine/src/engine.cu:1936).
+__global__ void k_attn_prep_append_lanes(float* __restrict__ qg, int ldq, float* __restrict__ k, int ldk, const float* __restrict__ v, int ldv,
+                                         const float* __restrict__ qn, const float* __restrict__ kn, __half* __restrict__ kc_base,
+                                         __half* __restrict__ vc_base, size_t seq_stride, int nq, int nkv, int hd, int nrot,
+                                         const int* __restrict__ pos, const int* __restrict__ lane_seq, const int* __restrict__ lane_row0, float eps,
+                                         float rope_base) {
+    extern __shared__ float xrow[];   // hd floats
+    __shared__ float red[32];
+    const int lane = blockIdx.z, t = blockIdx.y, row0 = lane_row0[lane];
+    if (t >= lane_row0[lane + 1] - row0) return;
+    const int seq = lane_seq[lane];
+    attn_prep_body(qg + (size_t) row0 * ldq, ldq, k + (size_t) row0 * ldk, ldk, v + (size_t) row0 * ldv, ldv, qn, kn, kc_base + seq * seq_stride,
+                   vc_base + seq * seq_stride, nq, nkv, hd, nrot, pos[seq], nullptr, eps, rope_base, t, (int) blockIdx.x, (int) threadIdx.x, xrow, red,
+                   SyncBlock());
+}
+
+// grid (splits, KV heads, lanes); a lane has at most ATT_ROWS rows
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_part_lanes(const float* __restrict__ qg, int ldq, const __half* __restrict__ kc_base,
+                                                                 const __half* __restrict__ vc_base, size_t seq_stride, float* __restrict__ acc_out,
+                                                                 AttPartial* __restrict__ mz_out, int nq, int nkv, const int* __restrict__ pos,
+                                                                 const int* __restrict__ lane_seq, const int* __restrict__ lane_row0) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = blockIdx.z, row0 = lane_row0[lane], T = lane_row0[lane + 1] - row0, seq = lane_seq[lane], S = gridDim.x;
+    if (T <= 0) return;
+    attn_part_body(qg + (size_t) row0 * ldq, ldq, kc_base + seq * seq_stride, vc_base + seq * seq_stride, acc_out + (size_t) row0 * nq * S * ATT_HD,
+                   mz_out + (size_t) row0 * nq * S, T, nq, nkv, pos[seq], nullptr, (int) blockIdx.x, S, (int) blockIdx.y, 0, (int) threadIdx.x, smem, SyncBlock());
+}
+
 static int attn_splits(int nkv) {
     const int s = sm_count() / (nkv > 0 ? nkv : 1);
     return s < 1 ? 1 : s;
@@ -157,5 +189,42 @@ extern "C" int fnx_attn_static(const float* qg, int ldq, const void* kc, const v
     le = launch_k(k_attn_combine, dim3(nq, T), dim3(hd * ATC_G), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
     if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le));
     FNX_LAUNCH_OK("fnx_attn_static (combine)");
+    return FNX_OK;
+}
+
+// ---- batched lanes (see k_attn_prep_append_lanes)
+extern "C" int fnx_attn_prep_append_lanes(float* qg, int ldq, float* k, int ldk, const float* v, int ldv, const float* q_norm, const float* k_norm,
+                                          void* kc_base, void* vc_base, size_t seq_stride_rows, int n_lanes, int max_lane_rows, int nq, int nkv, int hd,
+                                          int nrot, const int* pos, const int* lane_seq, const int* lane_row0, float eps, float rope_base, fnx_stream st) {
+    FNX_REQUIRE(qg && k && v && q_norm && k_norm && kc_base && vc_base && pos && lane_seq && lane_row0, "fnx_attn_prep_append_lanes: null pointer");
+    FNX_REQUIRE(n_lanes >= 1 && n_lanes <= FNX_MAX_ROWS && max_lane_rows >= 1 && max_lane_rows <= FNX_MAX_ROWS, "fnx_attn_prep_append_lanes: %d lanes of up to %d rows",
+                n_lanes, max_lane_rows);
+    FNX_REQUIRE(hd % 32 == 0 && hd <= 1024 && nrot <= hd && nrot % 2 == 0, "fnx_attn_prep_append_lanes: head dim %d, rotary %d", hd, nrot);
+    const cudaError_t le = launch_k(k_attn_prep_append_lanes, dim3(nq + 2 * nkv, max_lane_rows, n_lanes), dim3(hd), hd * sizeof(float), as_stream(st), qg, ldq, k, ldk,
+                                    v, ldv, q_norm, k_norm, (__half*) kc_base, (__half*) vc_base, seq_stride_rows * (size_t) nkv * hd, nq, nkv, hd, nrot, pos, lane_seq,
+                                    lane_row0, eps, rope_base);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_prep_append_lanes: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_attn_prep_append_lanes");
+    return FNX_OK;
+}
+
+extern "C" int fnx_attn_lanes(const float* qg, int ldq, const void* kc_base, const void* vc_base, size_t seq_stride_rows, float* out, int T, int n_lanes,
+                              int nq, int nkv, int hd, const int* pos, const int* lane_seq, const int* lane_row0, void* scratch, fnx_stream st) {
+    FNX_REQUIRE(qg && kc_base && vc_base && out && pos && lane_seq && lane_row0 && scratch, "fnx_attn_lanes: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && n_lanes >= 1 && n_lanes <= T, "fnx_attn_lanes: %d rows in %d lanes", T, n_lanes);
+    FNX_REQUIRE(hd == ATT_THREADS, "fnx_attn_lanes: head dim %d (this build: %d)", hd, ATT_THREADS);
+    FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQ, "fnx_attn_lanes: %d q heads over %d KV heads", nq, nkv);
+    const int S = attn_splits(nkv);
+    FNX_REQUIRE(S <= 256, "fnx_attn_lanes: %d splits", S);
+    float* acc = (float*) scratch;
+    AttPartial* mz = (AttPartial*) (acc + (size_t) T * nq * S * hd);
+    if (int rc = set_smem_limit((const void*) k_attn_part_lanes, (int) attn_part_smem())) return rc;
+    cudaError_t le = launch_k(k_attn_part_lanes, dim3(S, nkv, n_lanes), dim3(ATT_THREADS), attn_part_smem(), as_stream(st), qg, ldq, (const __half*) kc_base,
+                              (const __half*) vc_base, seq_stride_rows * (size_t) nkv * hd, acc, mz, nq, nkv, pos, lane_seq, lane_row0);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_part_lanes: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_attn_lanes (partials)");
+    le = launch_k(k_attn_combine, dim3(nq, T), dim3(hd * ATC_G), 0, as_stream(st), acc, mz, qg, ldq, out, nq, hd, S);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_attn_lanes (combine)");
     return FNX_OK;
 }

@@ -96,8 +96,15 @@ struct fnx_engine {
     float *rlogits = nullptr, *topw = nullptr, *hbuf = nullptr, *part = nullptr, *moe_out = nullptr, *best_v = nullptr, *cand_v = nullptr;
     int *topi = nullptr, *njobs = nullptr, *best_i = nullptr, *result = nullptr, *d_tok = nullptr, *d_parent = nullptr, *d_depth = nullptr;
     int *d_pos = nullptr, *d_cur = nullptr, *d_ctx = nullptr, *d_ctx_n = nullptr, *d_path = nullptr, *d_mtok = nullptr, *d_mpos = nullptr;
-    int *cand_i = nullptr, *d_drafts = nullptr;
+    int *cand_i = nullptr, *d_drafts = nullptr, *d_mpos_base = nullptr;
     int last_seq = -1;          // the sequence whose window the shared window buffers (tokens, result, residual rows) hold
+    // batched lanes: device tables of the last lane window (sequence and first row per lane, rows kept per lane), one result
+    // row per lane, the draft layer's positions per sequence and its own lane table
+    int *d_lane_seq = nullptr, *d_lane_row0 = nullptr, *d_keep = nullptr, *d_results = nullptr, *d_mpos_seq = nullptr, *d_mlane_row0 = nullptr,
+        *d_ident_row0 = nullptr, *d_ldrafts = nullptr;
+    float* Rlast = nullptr;     // the lanes' last draft-layer rows, compact, for the head
+    std::vector<int> lane_seqs; // the sequences of the last lane window, in lane order (empty: the last window was not batched)
+    int lane_T = 0;
     fnx_job* jobs = nullptr;
     unsigned* err = nullptr;
     void* att_scratch = nullptr;
@@ -486,6 +493,114 @@ static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
     return fnx_dense(e->head, d.V, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, d.V, 0, e->err, e->st);
 }
 
+// ------------------------------------------------------------------------------------------------ batched lanes
+// Several sequences' rows in one window (Engine::verify_rows / commit_rows / draft_rows, engine/src/engine_common.cu:1234-1684):
+// lane j = rows [row0[j], row0[j + 1]) of sequence lane_seq[j], a chain.  Projections, router, experts and head run over all
+// rows at once (an expert picked by rows of several lanes is read once); attention, DeltaNet, acceptance and commit go by
+// lane, each with its own sequence's position, caches and state rings.
+
+// lanes kept as prefixes of their chains: the kept tokens and the emitted one join each sequence's context, positions and
+// state slots advance
+__global__ void k_commit_lanes(const int* __restrict__ lane_seq, const int* __restrict__ lane_row0, const int* __restrict__ keep,
+                               const int* __restrict__ tok, const int* __restrict__ results, int* __restrict__ pos, int* __restrict__ cur, int NS,
+                               int* __restrict__ ctx, size_t ctx_stride, int* __restrict__ ctx_n, int L) {
+    const int lane = threadIdx.x;
+    if (lane >= L) return;
+    const int seq = lane_seq[lane], row0 = lane_row0[lane], n = keep[lane];
+    const int* res = results + (size_t) lane * (1 + 2 * FNX_MAX_ROWS);
+    int* c = ctx + (size_t) seq * ctx_stride;
+    const int cn = ctx_n[seq];
+    for (int j = 0; j < n; ++j) c[cn + j] = tok[row0 + j];
+    c[cn + n] = res[1 + FNX_MAX_ROWS + n - 1];
+    ctx_n[seq] = cn + n;
+    cur[seq] = (cur[seq] + n) % NS;
+    pos[seq] += n;
+}
+// the draft layer's first call: its rows are the lanes' kept rows (source rows and the tokens they emitted)
+__global__ void k_mtp_gather_lanes(float* __restrict__ dst, const float* __restrict__ src, int* __restrict__ mtok, const int* __restrict__ results,
+                                   const int* __restrict__ row0v, const int* __restrict__ row0m, int L, int H) {
+    const int r = blockIdx.y;   // draft-layer row
+    int lane = 0;
+    while (lane + 1 < L && r >= row0m[lane + 1]) ++lane;
+    if (r >= row0m[L]) return;
+    const int j = r - row0m[lane];
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < H) dst[(size_t) r * H + i] = src[(size_t) (row0v[lane] + j) * H + i];
+    if (i == 0) mtok[r] = results[(size_t) lane * (1 + 2 * FNX_MAX_ROWS) + 1 + FNX_MAX_ROWS + j];
+}
+// dst[lane] = src[last row of lane]
+__global__ void k_last_rows(float* __restrict__ dst, const float* __restrict__ src, const int* __restrict__ row0, int H) {
+    const int lane = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < H) dst[(size_t) lane * H + i] = src[(size_t) (row0[lane + 1] - 1) * H + i];
+}
+// the draft layer's positions advance per lane: by the rows of its first call, then by one
+__global__ void k_mtp_advance_lanes(int* __restrict__ mpos, const int* __restrict__ lane_seq, const int* __restrict__ row0m, int L, int first) {
+    const int lane = threadIdx.x;
+    if (lane < L) mpos[lane_seq[lane]] += first ? row0m[lane + 1] - row0m[lane] : 1;
+}
+__global__ void k_mtp_set_pos_lanes(int* __restrict__ mpos, const int* __restrict__ lane_seq, const int* __restrict__ base, int L) {
+    const int lane = threadIdx.x;
+    if (lane < L) mpos[lane_seq[lane]] = base[lane];
+}
+__global__ void k_scatter_drafts(int* __restrict__ out, const int* __restrict__ best, int L, int k, int j) {
+    const int lane = threadIdx.x;
+    if (lane < L) out[lane * k + j] = best[lane];
+}
+
+// mixer of one layer over the lanes' rows: R += out_proj(mixer(in_proj(rmsnorm(R))))
+static int enqueue_mixer_lanes(fnx_engine* e, const LayerW& L, float* R, int T, int n_lanes, int max_lane_rows, const int* d_lane_seq, const int* d_row0,
+                               const int* d_pos) {
+    const Dims d = dims(e->c);
+    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0));
+    if (L.attn) {
+        float* qg = e->proj;
+        float* k = e->proj + d.q_rows;
+        float* v = k + d.kv_rows;
+        FNX_TRY(fnx_attn_prep_append_lanes(qg, e->proj_ld, k, e->proj_ld, v, e->proj_ld, L.qn, L.kn, L.kc, L.vc, (size_t) e->cache_rows, n_lanes, max_lane_rows, d.nq,
+                                           d.nkv, d.hd, d.nrot, d_pos, d_lane_seq, d_row0, e->c.eps, e->c.rope_base, e->st));
+        FNX_TRY(fnx_attn_lanes(qg, e->proj_ld, L.kc, L.vc, (size_t) e->cache_rows, e->mix, T, n_lanes, d.nq, d.nkv, d.hd, d_pos, d_lane_seq, d_row0, e->att_scratch, e->st));
+        return enqueue_dense(e, L.w_out, d.H, d.nq * d.hd, e->mix, d.nq * d.hd, T, nullptr, R, d.H, 1);
+    }
+    FNX_TRY(fnx_gdn_core_lanes(e->proj, e->proj_ld, e->proj + d.gdn_ch + d.nv * d.hs, e->proj_ld, L.hist_pool, (size_t) e->NS * 3 * d.gdn_ch, L.convw, L.dt, L.a, L.gnorm,
+                               L.S_pool, (size_t) e->NS * d.nv * d.hs * d.hs, e->d_cur, e->NS, d_lane_seq, d_row0, n_lanes, max_lane_rows, e->mix, d.nk, d.nv, d.hs,
+                               e->c.eps, e->st));
+    return enqueue_dense(e, L.w_out, d.H, d.nv * d.hs, e->mix, d.nv * d.hs, T, nullptr, R, d.H, 1);
+}
+
+static int enqueue_verify_lanes(fnx_engine* e, int n_lanes, int rows) {
+    const Dims d = dims(e->c);
+    const int T = n_lanes * rows;
+    FNX_TRY(fnx_embed_rows(e->embed, e->d_tok, T, d.H, e->R, e->st));
+    for (size_t l = 0; l < e->layers.size(); ++l) {
+        const LayerW& L = e->layers[l];
+        FNX_TRY(enqueue_mixer_lanes(e, L, e->R, T, n_lanes, rows, e->d_lane_seq, e->d_lane_row0, e->d_pos));
+        FNX_TRY(enqueue_moe(e, L, e->R, T));
+    }
+    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0));
+    if (e->sampling_on) {
+        FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
+        return fnx_accept_sample_lanes(e->cand_v, e->cand_i, e->d_tok, e->sampling, e->sample_seed, e->d_lane_seq, e->d_lane_row0, n_lanes, rows, e->d_step,
+                                       e->d_results, e->st);
+    }
+    FNX_TRY(fnx_argmax(e->logits, T, d.V, e->best_i, e->best_v, e->err, e->st));
+    return fnx_accept_greedy_lanes(e->d_tok, e->best_i, e->d_lane_row0, n_lanes, e->d_results, e->st);
+}
+
+// one draft-layer call over lanes (rows per the table d_row0, Tm in all, at most max_rows per lane); the lanes' last rows go
+// through the head and their best tokens land in best_i[0 .. n_lanes)
+static int enqueue_mtp_lanes(fnx_engine* e, int n_lanes, int Tm, int max_rows, const int* d_row0, const float* src) {
+    const Dims d = dims(e->c);
+    FNX_TRY(fnx_embed_rows(e->embed, e->d_mtok, Tm, d.H, e->Emb, e->st));
+    FNX_TRY(enqueue_dense(e, e->mtp_fc_hid, d.H, d.H, src, d.H, Tm, e->mtp_hnorm, e->Rm, d.H, 0));
+    FNX_TRY(enqueue_dense(e, e->mtp_fc_emb, d.H, d.H, e->Emb, d.H, Tm, e->mtp_enorm, e->Rm, d.H, 1));
+    FNX_TRY(enqueue_mixer_lanes(e, e->mtp, e->Rm, Tm, n_lanes, max_rows, e->d_lane_seq, d_row0, e->d_mpos_seq));
+    FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, Tm));
+    k_last_rows<<<dim3((d.H + 255) / 256, n_lanes), 256, 0, e->st>>>(e->Rlast, e->Rm, d_row0, d.H);
+    FNX_LAUNCH_OK("draft last rows");
+    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->Rlast, d.H, n_lanes, e->mtp_onorm, e->logits, d.V, 0));
+    return fnx_argmax(e->logits, n_lanes, d.V, e->best_i, nullptr, e->err, e->st);
+}
+
 template <typename F>
 static int run_graph(fnx_engine* e, uint64_t key, F&& enqueue) {
     auto it = e->graphs.find(key);
@@ -610,9 +725,19 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_path, FNX_MAX_ROWS, "buf.path"));
         FNX_TRY(dalloc(e, &e->d_mtok, FNX_MAX_ROWS, "buf.mtp_tok"));
         FNX_TRY(dalloc(e, &e->d_mpos, 1, "buf.mtp_pos"));
+        FNX_TRY(dalloc(e, &e->d_mpos_base, FNX_MAX_ROWS, "buf.mtp_pos_base"));
         FNX_TRY(dalloc(e, &e->d_drafts, FNX_MAX_ROWS, "buf.draft"));
         FNX_TRY(dalloc(e, &e->d_step, c.n_seq, "seq.step"));
         FNX_TRY(dalloc(e, &e->d_lk, FNX_MAX_ROWS + 4, "buf.lookup"));
+        FNX_TRY(dalloc(e, &e->d_lane_seq, FNX_MAX_ROWS, "buf.lane_seq"));
+        FNX_TRY(dalloc(e, &e->d_lane_row0, FNX_MAX_ROWS + 1, "buf.lane_row0"));
+        FNX_TRY(dalloc(e, &e->d_mlane_row0, FNX_MAX_ROWS + 1, "buf.mtp_lane_row0"));
+        FNX_TRY(dalloc(e, &e->d_ident_row0, FNX_MAX_ROWS + 1, "buf.ident_row0"));
+        FNX_TRY(dalloc(e, &e->d_keep, FNX_MAX_ROWS, "buf.lane_keep"));
+        FNX_TRY(dalloc(e, &e->d_results, (size_t) FNX_MAX_ROWS * (1 + 2 * FNX_MAX_ROWS), "buf.lane_results"));
+        FNX_TRY(dalloc(e, &e->d_mpos_seq, c.n_seq, "seq.mtp_pos"));
+        FNX_TRY(dalloc(e, &e->d_ldrafts, (size_t) FNX_MAX_ROWS * FNX_MAX_ROWS, "buf.lane_drafts"));
+        FNX_TRY(dalloc(e, &e->Rlast, (size_t) d.MAXR * d.H, "buf.Rlast"));
         FNX_TRY(dalloc(e, &e->d_pos, c.n_seq, "seq.pos"));
         FNX_TRY(dalloc(e, &e->d_cur, c.n_seq, "seq.cur"));
         FNX_TRY(dalloc(e, &e->d_ctx, (size_t) c.n_seq * e->cache_rows, "seq.ctx"));
@@ -746,6 +871,7 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
     FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify(e, seq, T, tree); }));
     s.last_T = T;
     e->last_seq = seq;
+    e->lane_seqs.clear();
     if (h_result) {
         FNX_CUDA_OK(cudaMemcpyAsync(hs + 2 * FNX_MAX_ROWS, e->result, sizeof(int) * (1 + 2 * FNX_MAX_ROWS), cudaMemcpyDeviceToHost, e->st));
         FNX_CUDA_OK(cudaMemcpyAsync(hs + 5 * FNX_MAX_ROWS, e->err, sizeof(unsigned), cudaMemcpyDeviceToHost, e->st));
@@ -855,7 +981,7 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     int* hs = e->h_stage;
     hs[0] = s.kept_pos0;
-    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos_base, hs, sizeof(int), cudaMemcpyHostToDevice, e->st));
     // The whole chain is one graph: the first call on the kept rows of the main model (gathered by path) with the tokens
     // the window emitted, then k - 1 single-row calls, each from the draft layer's own last row and the previous draft;
     // tokens and positions advance on the device, the k drafts come back in one copy.
@@ -864,6 +990,8 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
         return fnx_argmax(e->logits, 1, d.V, out, nullptr, e->err, e->st);
     };
     auto chain = [&]() -> int {
+        // (the chain advances the position as it goes: it starts from a copy, so that running it again gives the same result)
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos, e->d_mpos_base, sizeof(int), cudaMemcpyDeviceToDevice, e->st));
         k_gather_rows<<<dim3((d.H + 255) / 256, n), 256, 0, e->st>>>(e->Rsrc, e->R, e->d_path, d.H);
         FNX_LAUNCH_OK("draft gather");
         FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->result + 1 + FNX_MAX_ROWS, sizeof(int) * n, cudaMemcpyDeviceToDevice, e->st));
@@ -974,5 +1102,146 @@ extern "C" int fnx_allreduce(fnx_engine* e, float* x, size_t count, fnx_stream s
     // ncclFloat32 = 7, ncclSum = 0
     const int rc = n->AllReduce(x, x, count, 7, 0, e->comm, as_stream(st));
     if (rc) return fail(FNX_E_CUDA, "ncclAllReduce: %s", n->GetErrorString ? n->GetErrorString(rc) : "error");
+    return FNX_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ batched lanes: API
+extern "C" int fnx_engine_verify_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_tok, int rows, int* h_results) {
+    FNX_REQUIRE(e && h_seqs && h_tok, "fnx_engine_verify_lanes: null pointer");
+    FNX_REQUIRE(n_lanes >= 1 && rows >= 1 && rows <= FNX_LANE_ROWS && n_lanes * rows <= e->c.max_rows, "fnx_engine_verify_lanes: %d lanes of %d rows (rows <= %d, %d rows in all)",
+                n_lanes, rows, FNX_LANE_ROWS, e->c.max_rows);
+    for (int j = 0; j < n_lanes; ++j) {
+        FNX_REQUIRE(h_seqs[j] >= 0 && h_seqs[j] < e->c.n_seq, "fnx_engine_verify_lanes: sequence %d", h_seqs[j]);
+        for (int i = 0; i < j; ++i) FNX_REQUIRE(h_seqs[i] != h_seqs[j], "fnx_engine_verify_lanes: sequence %d in two lanes", h_seqs[j]);
+        FNX_REQUIRE(e->seqs[h_seqs[j]].pos + rows <= e->c.max_ctx, "fnx_engine_verify_lanes: sequence %d runs past the context of %d rows", h_seqs[j], e->c.max_ctx);
+        for (int t = 0; t < rows; ++t)
+            FNX_REQUIRE(h_tok[j * rows + t] >= 0 && h_tok[j * rows + t] < e->c.vocab, "fnx_engine_verify_lanes: token %d outside the vocabulary", h_tok[j * rows + t]);
+    }
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    FNX_CUDA_OK(cudaMemsetAsync(e->err, 0, sizeof(unsigned), e->st));
+    int* hs = e->h_stage;
+    const int T = n_lanes * rows;
+    memcpy(hs, h_tok, sizeof(int) * T);
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_tok, hs, sizeof(int) * T, cudaMemcpyHostToDevice, e->st));
+    int* ht = hs + FNX_MAX_ROWS;
+    for (int j = 0; j < n_lanes; ++j) ht[j] = h_seqs[j];
+    for (int j = 0; j <= n_lanes; ++j) ht[FNX_MAX_ROWS + j] = j * rows;
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_lane_seq, ht, sizeof(int) * n_lanes, cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_lane_row0, ht + FNX_MAX_ROWS, sizeof(int) * (n_lanes + 1), cudaMemcpyHostToDevice, e->st));
+    if (e->sampling_on)
+        for (int j = 0; j < n_lanes; ++j) {
+            ht[3 * FNX_MAX_ROWS + j] = (int) e->seqs[h_seqs[j]].step++;
+            FNX_CUDA_OK(cudaMemcpyAsync(e->d_step + h_seqs[j], ht + 3 * FNX_MAX_ROWS + j, sizeof(int), cudaMemcpyHostToDevice, e->st));
+        }
+    const uint64_t key = ((uint64_t) 4 << 60) | ((uint64_t) n_lanes << 8) | (uint64_t) rows;
+    FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify_lanes(e, n_lanes, rows); }));
+    e->lane_seqs.assign(h_seqs, h_seqs + n_lanes);
+    e->lane_T = rows;
+    e->last_seq = -1;
+    for (int j = 0; j < n_lanes; ++j) e->seqs[h_seqs[j]].last_T = rows;
+    if (h_results) {
+        const size_t n = (size_t) n_lanes * (1 + 2 * FNX_MAX_ROWS);
+        std::vector<int> tmp(n + 1);
+        FNX_CUDA_OK(cudaMemcpyAsync(tmp.data(), e->d_results, sizeof(int) * n, cudaMemcpyDeviceToHost, e->st));
+        FNX_CUDA_OK(cudaMemcpyAsync(tmp.data() + n, e->err, sizeof(unsigned), cudaMemcpyDeviceToHost, e->st));
+        FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+        FNX_CUDA_OK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+        memcpy(h_results, tmp.data(), sizeof(int) * n);
+        if (tmp[n]) return fail(FNX_E_STATE, "verify_lanes: device error bits 0x%x", (unsigned) tmp[n]);
+    }
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_commit_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_keep) {
+    FNX_REQUIRE(e && h_seqs && h_keep, "fnx_engine_commit_lanes: null pointer");
+    FNX_REQUIRE(n_lanes == (int) e->lane_seqs.size() && n_lanes >= 1, "fnx_engine_commit_lanes: %d lanes, the last lane window had %d", n_lanes, (int) e->lane_seqs.size());
+    for (int j = 0; j < n_lanes; ++j) {
+        FNX_REQUIRE(h_seqs[j] == e->lane_seqs[j], "fnx_engine_commit_lanes: lane %d is sequence %d in the window, %d here", j, e->lane_seqs[j], h_seqs[j]);
+        FNX_REQUIRE(h_keep[j] >= 1 && h_keep[j] <= e->lane_T, "fnx_engine_commit_lanes: lane %d keeps %d of %d rows", j, h_keep[j], e->lane_T);
+    }
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    int* hs = e->h_stage;
+    memcpy(hs, h_keep, sizeof(int) * n_lanes);
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_keep, hs, sizeof(int) * n_lanes, cudaMemcpyHostToDevice, e->st));
+    k_commit_lanes<<<1, 32, 0, e->st>>>(e->d_lane_seq, e->d_lane_row0, e->d_keep, e->d_tok, e->d_results, e->d_pos, e->d_cur, e->NS, e->d_ctx, (size_t) e->cache_rows,
+                                        e->d_ctx_n, n_lanes);
+    FNX_LAUNCH_OK("commit lanes");
+    for (int j = 0; j < n_lanes; ++j) {
+        SeqState& s = e->seqs[h_seqs[j]];
+        s.kept = h_keep[j];
+        s.kept_pos0 = s.pos;
+        s.cur = (s.cur + h_keep[j]) % e->NS;
+        s.pos += h_keep[j];
+        s.last_T = 0;
+    }
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_draft_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, int k, int* h_drafts) {
+    FNX_REQUIRE(e && h_seqs && h_drafts && k >= 1 && k < e->c.max_rows, "fnx_engine_draft_lanes: bad arguments");
+    FNX_REQUIRE(n_lanes == (int) e->lane_seqs.size() && n_lanes >= 1, "fnx_engine_draft_lanes: %d lanes, the last lane window had %d", n_lanes, (int) e->lane_seqs.size());
+    const Dims d = dims(e->c);
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    int* hs = e->h_stage;
+    int Tm = 0, maxn = 0;
+    for (int j = 0; j < n_lanes; ++j) {
+        FNX_REQUIRE(h_seqs[j] == e->lane_seqs[j], "fnx_engine_draft_lanes: lane %d is sequence %d in the window, %d here", j, e->lane_seqs[j], h_seqs[j]);
+        const SeqState& s = e->seqs[h_seqs[j]];
+        FNX_REQUIRE(s.kept >= 1, "fnx_engine_draft_lanes: sequence %d: nothing committed since the last draft", h_seqs[j]);
+        hs[j] = Tm;
+        Tm += s.kept;
+        maxn = s.kept > maxn ? s.kept : maxn;
+        hs[FNX_MAX_ROWS + 1 + j] = s.kept_pos0;
+    }
+    hs[n_lanes] = Tm;
+    for (int j = 0; j <= n_lanes; ++j) hs[2 * FNX_MAX_ROWS + 2 + j] = j;
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mlane_row0, hs, sizeof(int) * (n_lanes + 1), cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_ident_row0, hs + 2 * FNX_MAX_ROWS + 2, sizeof(int) * (n_lanes + 1), cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_mpos_base, hs + FNX_MAX_ROWS + 1, sizeof(int) * n_lanes, cudaMemcpyHostToDevice, e->st));
+    // one graph for the whole chain: the first call on every lane's kept rows, then k - 1 calls of one row per lane
+    auto chain = [&]() -> int {
+        // (the chain advances the lanes' positions as it goes: it starts from a copy, so that running it again gives the same result)
+        k_mtp_set_pos_lanes<<<1, 32, 0, e->st>>>(e->d_mpos_seq, e->d_lane_seq, e->d_mpos_base, n_lanes);
+        FNX_LAUNCH_OK("draft positions (lanes)");
+        k_mtp_gather_lanes<<<dim3((d.H + 255) / 256, Tm), 256, 0, e->st>>>(e->Rsrc, e->R, e->d_mtok, e->d_results, e->d_lane_row0, e->d_mlane_row0, n_lanes, d.H);
+        FNX_LAUNCH_OK("draft gather (lanes)");
+        FNX_TRY(enqueue_mtp_lanes(e, n_lanes, Tm, maxn, e->d_mlane_row0, e->Rsrc));
+        k_scatter_drafts<<<1, 32, 0, e->st>>>(e->d_ldrafts, e->best_i, n_lanes, k, 0);
+        FNX_LAUNCH_OK("draft scatter");
+        for (int j = 1; j < k; ++j) {
+            // each lane's source row: its draft-layer last row (compact in Rlast), its token: the previous draft
+            FNX_CUDA_OK(cudaMemcpyAsync(e->Rsrc, e->Rlast, sizeof(float) * (size_t) n_lanes * d.H, cudaMemcpyDeviceToDevice, e->st));
+            FNX_CUDA_OK(cudaMemcpyAsync(e->d_mtok, e->best_i, sizeof(int) * n_lanes, cudaMemcpyDeviceToDevice, e->st));
+            k_mtp_advance_lanes<<<1, 32, 0, e->st>>>(e->d_mpos_seq, e->d_lane_seq, e->d_mlane_row0, n_lanes, j == 1 ? 1 : 0);
+            FNX_LAUNCH_OK("draft positions (lanes)");
+            FNX_TRY(enqueue_mtp_lanes(e, n_lanes, n_lanes, 1, e->d_ident_row0, e->Rsrc));
+            k_scatter_drafts<<<1, 32, 0, e->st>>>(e->d_ldrafts, e->best_i, n_lanes, k, j);
+            FNX_LAUNCH_OK("draft scatter");
+        }
+        return FNX_OK;
+    };
+    // the graph's shape depends on the lanes' kept counts: key on all of them
+    uint64_t key = ((uint64_t) 5 << 60) | ((uint64_t) k << 52) | ((uint64_t) n_lanes << 44);
+    for (int j = 0; j < n_lanes; ++j) key = key * 1000003ull + (uint64_t) e->seqs[h_seqs[j]].kept;
+    key |= (uint64_t) 5 << 60;
+    FNX_TRY(run_graph(e, key, chain));
+    std::vector<int> tmp((size_t) n_lanes * k);
+    FNX_CUDA_OK(cudaMemcpyAsync(tmp.data(), e->d_ldrafts, sizeof(int) * tmp.size(), cudaMemcpyDeviceToHost, e->st));
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    FNX_CUDA_OK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+    memcpy(h_drafts, tmp.data(), sizeof(int) * tmp.size());
+    for (int j = 0; j < n_lanes; ++j) e->seqs[h_seqs[j]].kept = 0;
+    return FNX_OK;
+}
+
+// A synthetic context for throughput measurements: sequence `seq` is placed at position `pos` as if that many tokens had
+// been read (its K/V rows and DeltaNet state keep whatever they hold: fill them through fnx_engine_tensor for a seeded
+// stand-in).  Results after this call are a function of that memory, not of a token history.
+extern "C" int fnx_engine_set_position(fnx_engine* e, int seq, int pos) {
+    FNX_REQUIRE(e && seq >= 0 && seq < e->c.n_seq && pos >= 0 && pos + e->c.max_rows <= e->c.max_ctx, "fnx_engine_set_position: sequence %d at %d", seq, pos);
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    e->seqs[seq].pos = pos;
+    FNX_CUDA_OK(cudaMemcpy(e->d_pos + seq, &pos, sizeof(int), cudaMemcpyHostToDevice));
+    FNX_CUDA_OK(cudaMemcpy(e->d_ctx_n + seq, &pos, sizeof(int), cudaMemcpyHostToDevice));
     return FNX_OK;
 }

@@ -19,18 +19,15 @@ namespace fnxb {
 
 constexpr int GDN_HS = 128, GDN_Q = 4, GDN_QC = GDN_HS / GDN_Q, GDN_THREADS = 128;
 
-__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
-    k_gdn_core(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
-               const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
-               const float* __restrict__ nw, float* __restrict__ S_pool, const int* __restrict__ curp, int NS,
-               const int* __restrict__ parent, float* __restrict__ y, int nk, int nv, int T, float eps) {
-    pdl_wait();
-    pdl_launch_dependents();
-    extern __shared__ __align__(16) float sm[];
+// One block of the (value head, column quarter) grid: the cluster's four blocks share a value head.
+__device__ __forceinline__ void gdn_body(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
+                                         const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
+                                         const float* __restrict__ nw, float* __restrict__ S_pool, int cur, int NS, const int* __restrict__ parent,
+                                         float* __restrict__ y, int nk, int nv, int T, float eps, float* sm) {
     cg::cluster_group cluster = cg::this_cluster();
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, kh = lv % nk, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int ch = (2 * nk + nv) * GDN_HS, cur = *curp;
+    const int ch = (2 * nk + nv) * GDN_HS;
     const size_t hsz = (size_t) 3 * ch, ssz = (size_t) nv * GDN_HS * GDN_HS;
     float* xq = sm;                              // [T][HS] q after conv, silu, norm
     float* xk = xq + (size_t) T * GDN_HS;        // [T][HS]
@@ -198,6 +195,38 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     cluster.sync();   // no block may leave while a neighbour still reads its shared memory
 }
 
+__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
+    k_gdn_core(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
+               const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
+               const float* __restrict__ nw, float* __restrict__ S_pool, const int* __restrict__ curp, int NS,
+               const int* __restrict__ parent, float* __restrict__ y, int nk, int nv, int T, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float sm[];
+    gdn_body(qkvz, stride, ab, ldab, hist_pool, convw, dt, a_, nw, S_pool, *curp, NS, parent, y, nk, nv, T, eps, sm);
+}
+
+// Batched lanes: blockIdx.y = lane j, the rows [lane_row0[j], lane_row0[j + 1]) of sequence lane_seq[j], a chain from
+// that sequence's state slot cur[seq] in its own rings (hist_pool + seq * hist_stride, S_pool + seq * s_stride)
+// (gdn_core_segs, engine/src/kernels.cu:2112-2156).  Every block of a cluster has the same lane, so all of them take
+// the same path.
+__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
+    k_gdn_core_lanes(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool, size_t hist_stride,
+                     const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_, const float* __restrict__ nw,
+                     float* __restrict__ S_pool, size_t s_stride, const int* __restrict__ cur, int NS, const int* __restrict__ lane_seq,
+                     const int* __restrict__ lane_row0, float* __restrict__ y, int nk, int nv, float eps) {
+    extern __shared__ __align__(16) float sm[];
+    const int lane = blockIdx.y, row0 = lane_row0[lane], T = lane_row0[lane + 1] - row0, seq = lane_seq[lane];
+    if (T <= 0) return;
+    gdn_body(qkvz + (size_t) row0 * stride, stride, ab + (size_t) row0 * ldab, ldab, hist_pool + seq * hist_stride, convw, dt, a_, nw, S_pool + seq * s_stride,
+             cur[seq], NS, nullptr, y + (size_t) row0 * nv * GDN_HS, nk, nv, T, eps, sm);
+}
+
+static size_t gdn_smem_bytes(int T) {
+    return sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T +
+                            (size_t) (T + 3) * (2 * GDN_HS + GDN_QC) + 3 * T);
+}
+
 }  // namespace fnxb
 
 using namespace fnxb;
@@ -209,12 +238,29 @@ extern "C" int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int lda
     FNX_REQUIRE(hs == GDN_HS, "fnx_gdn_core: head dim %d (this build: %d)", hs, GDN_HS);
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && NS >= T + 1, "fnx_gdn_core: %d rows need at least %d state slots, have %d", T, T + 1, NS);
     FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_core: %d key heads, %d value heads", nk, nv);
-    const size_t smem = sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T + (size_t) (T + 3) * (2 * GDN_HS + GDN_QC) + 3 * T);
+    const size_t smem = gdn_smem_bytes(T);
     if (int rc = set_smem_limit((const void*) k_gdn_core, 96 * 1024)) return rc;
     {
         const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), smem, as_stream(st), qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_gdn_core");
+    return FNX_OK;
+}
+
+extern "C" int fnx_gdn_core_lanes(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, size_t hist_seq_stride, const float* convw,
+                                  const float* dt, const float* a, const float* nw, float* S_pool, size_t s_seq_stride, const int* cur, int NS,
+                                  const int* lane_seq, const int* lane_row0, int n_lanes, int max_lane_rows, float* y, int nk, int nv, int hs, float eps,
+                                  fnx_stream st) {
+    FNX_REQUIRE(qkvz && ab && hist_pool && convw && dt && a && nw && S_pool && cur && lane_seq && lane_row0 && y, "fnx_gdn_core_lanes: null pointer");
+    FNX_REQUIRE(hs == GDN_HS, "fnx_gdn_core_lanes: head dim %d (this build: %d)", hs, GDN_HS);
+    FNX_REQUIRE(n_lanes >= 1 && n_lanes <= FNX_MAX_ROWS && max_lane_rows >= 1 && NS >= max_lane_rows + 1, "fnx_gdn_core_lanes: %d lanes of up to %d rows, %d state slots",
+                n_lanes, max_lane_rows, NS);
+    FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_core_lanes: %d key heads, %d value heads", nk, nv);
+    if (int rc = set_smem_limit((const void*) k_gdn_core_lanes, 96 * 1024)) return rc;
+    const cudaError_t le = launch_k(k_gdn_core_lanes, dim3(nv * GDN_Q, n_lanes), dim3(GDN_THREADS), gdn_smem_bytes(max_lane_rows), as_stream(st), qkvz, ldx, ab, ldab,
+                                    hist_pool, hist_seq_stride, convw, dt, a, nw, S_pool, s_seq_stride, cur, NS, lane_seq, lane_row0, y, nk, nv, eps);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core_lanes: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_gdn_core_lanes");
     return FNX_OK;
 }

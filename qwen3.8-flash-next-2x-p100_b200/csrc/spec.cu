@@ -46,11 +46,8 @@ __global__ void __launch_bounds__(1024) k_lookup(const int* __restrict__ ctx, co
 }
 
 // result: [0] = n, [1 .. 1 + n) path, [1 + FNX_MAX_ROWS ..) emitted tokens
-__global__ void k_accept_greedy(const int* __restrict__ tok, const int* __restrict__ parent, const int* __restrict__ best, int T,
-                                int* __restrict__ result) {
-    pdl_wait();
-    pdl_launch_dependents();
-    if (threadIdx.x != 0) return;
+__device__ __forceinline__ void accept_greedy_walk(const int* __restrict__ tok, const int* __restrict__ parent, const int* __restrict__ best, int T,
+                                                   int* __restrict__ result) {
     int cur = 0, n = 0;
     for (;;) {
         result[1 + n] = cur;
@@ -63,6 +60,21 @@ __global__ void k_accept_greedy(const int* __restrict__ tok, const int* __restri
         cur = next;
     }
     result[0] = n;
+}
+
+__global__ void k_accept_greedy(const int* __restrict__ tok, const int* __restrict__ parent, const int* __restrict__ best, int T,
+                                int* __restrict__ result) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    accept_greedy_walk(tok, parent, best, T, result);
+}
+
+// batched lanes: block j walks lane j's chain (rows [lane_row0[j], lane_row0[j + 1])) into result row j
+__global__ void k_accept_greedy_lanes(const int* __restrict__ tok, const int* __restrict__ best, const int* __restrict__ lane_row0, int* __restrict__ result) {
+    if (threadIdx.x != 0) return;
+    const int lane = blockIdx.x, row0 = lane_row0[lane];
+    accept_greedy_walk(tok + row0, nullptr, best + row0, lane_row0[lane + 1] - row0, result + (size_t) lane * (1 + 2 * FNX_MAX_ROWS));
 }
 
 struct DistS {
@@ -79,13 +91,10 @@ __device__ __forceinline__ double dist_prob(const int* ids, const double* p, int
 
 // A warp per row builds the row's distribution (make_dist): the exponentials in parallel, the sums in the
 // reference's sequential order; then thread 0 walks the chain.
-__global__ void __launch_bounds__(1024) k_accept_sample(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
-                                                        const int* __restrict__ tok, int T, fnx_sampling sp, const int* __restrict__ q_ids,
-                                                        const double* __restrict__ q_p, const int* __restrict__ q_n, uint64_t seed,
-                                                        uint32_t seq, const uint32_t* __restrict__ stepp, int* __restrict__ result) {
-    pdl_wait();
-    pdl_launch_dependents();
-    extern __shared__ __align__(16) uint8_t smem[];
+__device__ __forceinline__ void accept_sample_body(const float* __restrict__ cand_v, const int* __restrict__ cand_i, const int* __restrict__ tok, int T,
+                                                   fnx_sampling sp, const int* __restrict__ q_ids, const double* __restrict__ q_p,
+                                                   const int* __restrict__ q_n, uint64_t seed, uint32_t seq, uint32_t step, int* __restrict__ result,
+                                                   uint8_t* smem) {
     DistS* dist = reinterpret_cast<DistS*>(smem);                                  // [T]
     double* ex = reinterpret_cast<double*>(smem + sizeof(DistS) * (size_t) T);     // [T][64] scratch
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +141,6 @@ __global__ void __launch_bounds__(1024) k_accept_sample(const float* __restrict_
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
-    const uint32_t step = *stepp;
     uint32_t slot = 0;
     int n;
     double* p = ex;   // row scratch for the residual
@@ -177,6 +185,27 @@ __global__ void __launch_bounds__(1024) k_accept_sample(const float* __restrict_
     result[0] = n;
 }
 
+__global__ void __launch_bounds__(1024) k_accept_sample(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
+                                                        const int* __restrict__ tok, int T, fnx_sampling sp, const int* __restrict__ q_ids,
+                                                        const double* __restrict__ q_p, const int* __restrict__ q_n, uint64_t seed,
+                                                        uint32_t seq, const uint32_t* __restrict__ stepp, int* __restrict__ result) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) uint8_t smem[];
+    accept_sample_body(cand_v, cand_i, tok, T, sp, q_ids, q_p, q_n, seed, seq, *stepp, result, smem);
+}
+
+// batched lanes: block j applies the rule to lane j's chain with sequence lane_seq[j]'s uniforms (drafts count as fixed)
+__global__ void __launch_bounds__(1024) k_accept_sample_lanes(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
+                                                              const int* __restrict__ tok, fnx_sampling sp, uint64_t seed,
+                                                              const int* __restrict__ lane_seq, const int* __restrict__ lane_row0,
+                                                              const uint32_t* __restrict__ steps, int* __restrict__ result) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = blockIdx.x, row0 = lane_row0[lane], seq = lane_seq[lane];
+    accept_sample_body(cand_v + (size_t) row0 * FNX_TOPK_N, cand_i + (size_t) row0 * FNX_TOPK_N, tok + row0, lane_row0[lane + 1] - row0, sp, nullptr, nullptr, nullptr,
+                       seed, (uint32_t) seq, steps[seq], result + (size_t) lane * (1 + 2 * FNX_MAX_ROWS), smem);
+}
+
 }  // namespace fnxb
 
 using namespace fnxb;
@@ -213,5 +242,28 @@ extern "C" int fnx_accept_sample(const float* cand_v, const int* cand_i, const i
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_accept_sample: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_accept_sample");
+    return FNX_OK;
+}
+
+// ---- batched lanes: one result row of 1 + 2 FNX_MAX_ROWS ints per lane
+extern "C" int fnx_accept_greedy_lanes(const int* tok, const int* best, const int* lane_row0, int n_lanes, int* result, fnx_stream st) {
+    FNX_REQUIRE(tok && best && lane_row0 && result && n_lanes >= 1 && n_lanes <= FNX_MAX_ROWS, "fnx_accept_greedy_lanes: bad arguments");
+    const cudaError_t le = launch_k(k_accept_greedy_lanes, dim3(n_lanes), dim3(32), 0, as_stream(st), tok, best, lane_row0, result);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_accept_greedy_lanes: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_accept_greedy_lanes");
+    return FNX_OK;
+}
+
+extern "C" int fnx_accept_sample_lanes(const float* cand_v, const int* cand_i, const int* tok, fnx_sampling s, uint64_t seed, const int* lane_seq,
+                                       const int* lane_row0, int n_lanes, int max_lane_rows, const uint32_t* steps, int* result, fnx_stream st) {
+    FNX_REQUIRE(cand_v && cand_i && tok && lane_seq && lane_row0 && steps && result && n_lanes >= 1 && n_lanes <= FNX_MAX_ROWS && max_lane_rows >= 1 &&
+                    max_lane_rows <= FNX_MAX_ROWS,
+                "fnx_accept_sample_lanes: bad arguments");
+    FNX_REQUIRE(s.temperature > 0.f, "fnx_accept_sample_lanes: temperature %g", (double) s.temperature);
+    const size_t smem = sizeof(DistS) * (size_t) max_lane_rows + sizeof(double) * FNX_TOPK_N * (size_t) max_lane_rows;
+    if (int rc = set_smem_limit((const void*) k_accept_sample_lanes, 64 * 1024)) return rc;
+    const cudaError_t le = launch_k(k_accept_sample_lanes, dim3(n_lanes), dim3(1024), smem, as_stream(st), cand_v, cand_i, tok, s, seed, lane_seq, lane_row0, steps, result);
+    if (le != cudaSuccess) return fail(FNX_E_CUDA, "k_accept_sample_lanes: launch failed: %s", cudaGetErrorString(le));
+    FNX_LAUNCH_OK("fnx_accept_sample_lanes");
     return FNX_OK;
 }

@@ -108,11 +108,17 @@ def test_full_size_layers_match_oracle(F, O):
             w = prompt[i:i + cfg.max_rows]
             om.verify(w, None)
             om.commit(list(range(len(w))))
-        for toks, par in ((rng.integers(0, cfg.vocab, size=5).tolist(), None), (rng.integers(0, cfg.vocab, size=7).tolist(), [-1, 0, 1, 0, 3, 3, 1])):
-            T = len(toks)
+        for T, par in ((5, None), (7, [-1, 0, 1, 0, 3, 3, 1])):
+            # top-K is discontinuous: among 512 experts some window has a K-th / (K+1)-th logit pair closer than the kernels'
+            # rounding; take the first seeded window without one (a window changes no committed state, so trying one is free)
+            for _ in range(8):
+                toks = rng.integers(0, cfg.vocab, size=T).tolist()
+                want = om.verify(toks, par)
+                if _routing_margin_ok(om, cfg.top_k):
+                    break
+            else:
+                raise AssertionError("eight windows in a row with a routing near-tie")
             got = eng.verify(toks, par)
-            want = om.verify(toks, par)
-            assert _routing_margin_ok(om, cfg.top_k), "pick another seed: a routing near-tie makes the comparison meaningless"
             R = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:T]
             logits = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:T]
             topi = eng.tensor("buf.topi", torch.int32).cpu().numpy().reshape(cfg.max_rows, cfg.top_k)[:T]
@@ -276,3 +282,59 @@ def test_a_row_gives_the_same_bits_alone_and_among_drafts(F, model):
         eng.commit([0])
         alone = eng.tensor("buf.logits", torch.float32).view(cfg.max_rows, cfg.vocab)[0]
         assert torch.equal(alone, together[i]), f"row {i}"
+
+
+@pytest.mark.parametrize("sampling", [False, True])
+def test_batched_lanes_equal_single_sequence_windows(F, sampling):
+    """Three sequences of different lengths in one window (Engine::verify_rows): every lane's accepted tokens, hidden rows and
+    logits are bit-identical to the same rows run through the single-sequence window of that sequence alone, for the greedy
+    and for the sampling rule (each sequence draws its own Philox stream); so are the MTP drafts of the batched chain, and
+    so is a second window after the lanes kept different numbers of rows."""
+    cfg = small_cfg(F, n_seq=3, max_rows=16)
+    eng = F.Engine(cfg)
+    try:
+        eng.init_synthetic(seed=0, sigma=0.02)
+        rng = np.random.default_rng(21)
+        prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (9, 14, 6)]
+        rounds = [[rng.integers(0, cfg.vocab, size=4).tolist() for _ in range(3)] for _ in range(2)]
+        seqs = [0, 1, 2]
+        samp = F.Sampling(0.8, 0.95, 0.0, 40)
+
+        def begin():
+            eng.set_sampling(samp if sampling else None, seed=77)
+            for s in seqs:
+                eng.reset(s)
+                eng.prefill(prompts[s], s)
+
+        def rows_of(name, width, lo, n):
+            return eng.tensor(name, torch.float32).cpu().numpy().reshape(cfg.max_rows, width)[lo:lo + n].copy()
+
+        # ---- every sequence alone
+        begin()
+        alone = {s: [] for s in seqs}
+        for s in seqs:
+            for r in range(2):
+                res = eng.verify(rounds[r][s], None, s)
+                R, lg = rows_of("buf.R", cfg.hidden, 0, 4), rows_of("buf.logits", cfg.vocab, 0, 4)
+                eng.commit(res[1], s)
+                d = eng.draft(2, s)
+                alone[s].append((res, R, lg, d))
+        # ---- the same windows as lanes
+        begin()
+        for r in range(2):
+            got = eng.verify_lanes(seqs, [rounds[r][s] for s in seqs])
+            for j, s in enumerate(seqs):
+                res, R, lg, d = alone[s][r]
+                assert got[j] == res, (r, s, got[j], res)
+                assert np.array_equal(rows_of("buf.R", cfg.hidden, 4 * j, 4), R)
+                assert np.array_equal(rows_of("buf.logits", cfg.vocab, 4 * j, 4), lg)
+            eng.commit_lanes(seqs, [g[0] for g in got])
+            drafts = eng.draft_lanes(seqs, 2)
+            for j, s in enumerate(seqs):
+                assert drafts[j] == alone[s][r][3], (r, s, drafts[j], alone[s][r][3])
+            assert eng.error_bits() == 0
+        for s in seqs:
+            assert eng.pos(s) == len(prompts[s]) + sum(alone[s][r][0][0] for r in range(2))
+    finally:
+        eng.set_sampling(None, 0)
+        eng.close()

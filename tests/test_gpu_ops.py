@@ -422,3 +422,21 @@ def test_philox_stream_matches_oracle(F, O):
     # known-answer vector of Philox4x32-10 (Random123 kat_vectors: zero counter and key)
     assert list(O.philox([0, 0, 0, 0], [0, 0])) == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
     assert list(O.philox([0xFFFFFFFF] * 4, [0xFFFFFFFF] * 2)) == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+
+
+def test_cpp_consumer_of_the_header(F):
+    """A C++ program compiled against include/fnx_b200.h and linked with the library calls fnx_dense and fnx_router_route on
+    the GPU (tests/csrc/consumer.cpp): the header is what a consumer compiles, not only a list of names."""
+    import pathlib
+    import subprocess
+    root = pathlib.Path(__file__).resolve().parent.parent
+    pkg = next(p for p in root.iterdir() if p.is_dir() and (p / "libfnx_b200.so").exists())
+    exe = root / "tests" / "csrc" / "consumer"
+    cuda = pathlib.Path("/usr/local/cuda")
+    cmd = ["g++", "-std=c++17", "-O1", "-I", str(root / "include"), "-I", str(cuda / "include"), str(root / "tests" / "csrc" / "consumer.cpp"), "-o", str(exe),
+           "-L", str(pkg), "-lfnx_b200", "-L", str(cuda / "lib64"), "-lcudart", f"-Wl,-rpath,{pkg}", f"-Wl,-rpath,{cuda / 'lib64'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    for rows, cols in ((256, 1024), (512, 2048)):
+        r = subprocess.run([str(exe), str(rows), str(cols)], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0 and r.stdout.startswith("ok "), (r.returncode, r.stdout, r.stderr)
