@@ -39,6 +39,7 @@ sys.path.insert(0, str(ROOT / "tests"))
 METRIC = "decode tok/s (MTP+lookup spec verify), verify-step us, % of HBM roofline"
 CTX, K_DRAFT, P_BAD = 4096, 4, 0.28
 C2_CTX, C2_LOOKUP = 32768, 15            # configuration 2: context and the longest lookup branch
+C3_TOKENS = 38912                          # configuration 3: the cold prompt
 C4_CTX, C4_SEQS, C4_LANES = 131072, 8, 4   # configuration 4: context per sequence, sequences, lanes per window
 E_B = 1351680          # bytes of one expert: (2*512*2048 + 2048*512) * 110 / 256
 # DRAM bytes per expert job of the gate|up launch, from an ncu capture of one launch (dram__bytes_read.sum +
@@ -188,6 +189,35 @@ CPU_SAMPLE = ("per step: 1 DeltaNet layer + 1 attention layer (each with router,
               "cores, 5-row window at ctx 4096; a verify step = 36 x the first + 12 x the second + the head (extrapolated); MTP chain not included")
 
 
+def ep_setup(F, eng, rank, world):
+    """Expert-parallel ranks: the NCCL communicator and, unless FNX_EP_NCCL=1, the per-layer sum over NVLink peer memory
+    (fused with the combine): the ranks exchange their IPC handles.  Returns whether the peer-memory sum is in use."""
+    if world == 1:
+        return False
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    uid = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = (C.c_char * 128)()
+        F.check(F.lib().fnx_comm_unique_id(buf))
+        uid = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
+    uid = uid.cuda()
+    dist.broadcast(uid, 0)
+    raw = bytes(uid.cpu().numpy().tobytes())
+    F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
+    use_peer = os.environ.get("FNX_EP_NCCL", "0") != "1"
+    if use_peer:
+        mine = (C.c_char * 128)()
+        F.check(F.lib().fnx_engine_ep_handles(eng._h, mine))
+        hm = torch.frombuffer(bytearray(mine.raw), dtype=torch.uint8).clone().cuda()
+        allh = [torch.zeros(128, dtype=torch.uint8, device="cuda") for _ in range(world)]
+        dist.all_gather(allh, hm)
+        blob = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
+        F.check(F.lib().fnx_engine_ep_open(eng._h, blob, rank, world))
+    return use_peer
+
+
 def _max_over_ranks(world, vals):
     import torch
     if world == 1:
@@ -204,7 +234,7 @@ def _barrier(world):
     torch.cuda.synchronize()
 
 
-def run_config4(a, F, eng, cfg, rank, world, local, use_peer):
+def run_config4(a, F, eng, cfg, rank, world, local, use_peer, emit=True):
     """Configuration 4: 8 concurrent sequences, each at a 131,072-token context, MTP drafts of k = 4, the sampling rule at
     temperature 0.7 with seeded Philox uniforms; expert-parallel over the ranks.  The sequences run as batched lanes: two
     windows of four lanes (5 rows each) per round.  A step = one round of all 8 sequences: per window the MTP draft chain
@@ -234,7 +264,7 @@ def run_config4(a, F, eng, cfg, rank, world, local, use_peer):
     rng = np.random.default_rng(4)
     groups = [list(range(i, min(i + C4_LANES, C4_SEQS))) for i in range(0, C4_SEQS, C4_LANES)]
     nxt = {s: int(rng.integers(0, cfg.vocab)) for s in range(C4_SEQS)}
-    have_kept = {s: False for s in range(C4_SEQS)}
+    pending = [None] * len(groups)
     clocks = Clocks(local)
     clocks.launch()
     est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
@@ -250,22 +280,20 @@ def run_config4(a, F, eng, cfg, rank, world, local, use_peer):
             clocks.start()
             t0.record(est)
             wall0 = time.perf_counter()
-        for grp in groups:
-            if have_kept[grp[0]]:
-                drafts = eng.draft_lanes(grp, K_DRAFT)
-                if r >= a.warmup:
-                    dev_ms += eng.last_ms()
-            else:
-                drafts = [rng.integers(0, cfg.vocab, size=K_DRAFT).tolist() for _ in grp]
+        for gi, grp in enumerate(groups):
+            # (the window buffers are shared by the groups: a group's drafts for its NEXT window are taken right after its commit)
+            drafts = pending[gi] if pending[gi] is not None else [rng.integers(0, cfg.vocab, size=K_DRAFT).tolist() for _ in grp]
             res = eng.verify_lanes(grp, [[nxt[s]] + drafts[j] for j, s in enumerate(grp)])
             if r >= a.warmup:
                 dev_ms += eng.last_ms()
                 verify_ms += eng.last_ms()
             eng.commit_lanes(grp, [x[0] for x in res])
+            pending[gi] = eng.draft_lanes(grp, K_DRAFT)
+            if r >= a.warmup:
+                dev_ms += eng.last_ms()
             for j, s in enumerate(grp):
                 n, _, em = res[j]
                 nxt[s] = em[-1]
-                have_kept[s] = True
                 stream.extend(em)
                 if r >= a.warmup:
                     tokens += n
@@ -293,6 +321,56 @@ def run_config4(a, F, eng, cfg, rank, world, local, use_peer):
             "verify_window_us": verify_ms * 1e3 / (a.steps * len(groups)), "accepted_per_offered": accepted / max(1, offered), "tokens_per_step": tokens / a.steps,
             "tokens_crc": zlib.crc32(np.asarray(stream, np.int64).tobytes()), "ep_sum": "none" if world == 1 else ("peer-memory" if use_peer else "nccl"),
             "window_bytes": {"kv_read": kv, "routed_jobs_per_window": jobs_per_window, "expert_bytes": (jobs_per_window + a.layers * 5) * E_B / max(1, world)}}
+    eng.close()
+    if not emit:
+        return line
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
+    """Configuration 3: cold prefill of 38,912 uniform-random tokens (seed 3).  The engine reads a prompt through chained
+    windows of 32 rows of the decode path's kernels (every row kept); the tensor-core grouped expert GEMM
+    (fnx_moe_prefill, `--prefill-moe`) is measured on its own and is not on this path yet.  One step = the whole prompt."""
+    import numpy as np
+    import torch
+    n = a.ctx if a.ctx != CTX else C3_TOKENS
+    toks = np.random.default_rng(3).integers(0, cfg.vocab, size=n).tolist()
+    est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
+    clocks = Clocks(local)
+    clocks.launch()
+    times, walls = [], []
+    c0 = eng.counters()
+    for it in range(1 + max(1, min(a.steps, 2))):   # one warm-up pass (graph capture), then the timed passes
+        eng.reset()
+        _barrier(world)
+        if it == 1:
+            clocks.start()
+            c0 = eng.counters()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        t0.record(est)
+        eng.prefill(toks)
+        t1.record(est)
+        _barrier(world)
+        walls.append(time.perf_counter() - w0)
+        times.append(t0.elapsed_time(t1))
+    clk = clocks.stop()
+    c1 = eng.counters()
+    ms = _max_over_ranks(world, [min(times[1:])])[0]
+    wall = min(walls[1:])
+    passes = len(times) - 1
+    line = {"metric": "prefill tok/s (cold prompt)", "value": n / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": passes, "warmup": 1, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
+            "config": {"workload": f"configuration 3: cold prefill of {n} uniform-random tokens (seed 3) through chained 32-row windows of the decode kernels",
+                       "timing": "weights (34 GB per window) far larger than the 126 MB L2; CUDA events on the engine's stream", "parallelism": f"ep{world}", "layers": a.layers},
+            "clocks": clk, "gpu_launches": int((c1[0] - c0[0]) / passes),
+            "e2e": {"value": n / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * n + 4 * n, "d2h_bytes_per_step": 0, "wall_ms_per_step": wall * 1e3},
+            "windows": (n + cfg.max_rows - 1) // cfg.max_rows, "us_per_window": ms * 1e3 / ((n + cfg.max_rows - 1) // cfg.max_rows),
+            "note": "the tensor-core path for prompts (grouped expert GEMM on tcgen05) exists as a kernel and is measured by --prefill-moe; the chunked DeltaNet scan and prompt attention it needs around it are not built, so prompts take the decode kernels"}
     if rank == 0:
         print(json.dumps(line))
     eng.close()
@@ -329,10 +407,10 @@ def run_config2(a, F, eng, cfg, rank, world, local, use_peer):
     import numpy as np
     import torch
     ctx = a.ctx if a.ctx != CTX else C2_CTX
-    full = edit_like_context(ctx + 1, cfg.vocab, 2)
+    total = a.warmup + a.steps
+    full = edit_like_context(ctx + total + 1, cfg.vocab, 2)
     eng.reset()
-    eng.prefill(full[:-1])
-    x = full[-1]
+    eng.prefill(full[:ctx])
     clocks = Clocks(local)
     clocks.launch()
     est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
@@ -341,13 +419,17 @@ def run_config2(a, F, eng, cfg, rank, world, local, use_peer):
     tokens = rows = lk_rows = lk_kept = 0
     stream = []
     have_kept = False
-    for r in range(a.warmup + a.steps):
+    for r in range(total):
         if r == a.warmup:
             _barrier(world)
             c0 = eng.counters()
             clocks.start()
             t0.record(est)
             wall0 = time.perf_counter()
+        # The text being written is the edit-like text itself: each window's root is its next token (a random-init model
+        # would not continue copied spans, and then the drafter would never find a match).  The window keeps what greedy
+        # acceptance keeps of the drafts; the following root is again the text's.
+        x = full[ctx + r]
         chain = []
         if have_kept:
             chain = eng.draft(K_DRAFT)
@@ -364,10 +446,11 @@ def run_config2(a, F, eng, cfg, rank, world, local, use_peer):
             rows += len(toks)
             lk_rows += len(lk)
             lk_kept += sum(1 for p in path if p > len(chain))
-        eng.commit(path)
+        # keep the root only and go on with the text's next token: the context stays the edit-like text
+        eng.commit([0])
         have_kept = True
         stream.extend(em)
-        x = em[-1]
+        x = full[ctx + r + 1]
     t1.record(est)
     _barrier(world)
     wall = time.perf_counter() - wall0
@@ -385,7 +468,8 @@ def run_config2(a, F, eng, cfg, rank, world, local, use_peer):
             "verify_window_us": verify_ms * 1e3 / a.steps, "rows_per_window": rows / a.steps, "lookup_rows_per_window": lk_rows / a.steps,
             "lookup_rows_kept_per_window": lk_kept / a.steps, "tokens_per_step": tokens / a.steps,
             "tokens_crc": zlib.crc32(np.asarray(stream, np.int64).tobytes()), "ep_sum": "none" if world == 1 else ("peer-memory" if use_peer else "nccl"),
-            "note": "random-init weights: the model does not continue copied spans, so lookup rows are verified (and timed) but rarely kept"}
+            "note": ("each window's root is the next token of the edit-like text and only the root is kept (a random-init model does not continue copied spans): "
+                     "tokens_per_step counts what greedy acceptance accepted, the windows' cost is that of full tree windows with real lookup branches")}
     if rank == 0:
         print(json.dumps(line))
     eng.close()
@@ -409,13 +493,14 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 4],
-                    help="the benchmark configuration: 1 = 5-row chain windows at ctx 4096 (the headline), 2 = tree windows of an MTP chain + a prompt-lookup "
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
+                    help="the benchmark configuration: 1 = 5-row chain windows at ctx 4096 (the headline), 3 = cold prefill of 38,912 tokens, 2 = tree windows of an MTP chain + a prompt-lookup "
                          "branch over a 32,768-token edit-like context, 4 = 8 concurrent sequences at ctx 131,072 with the sampling rule (batched lanes)")
     ap.add_argument("--layers", type=int, default=48, help="fewer layers for a quick functional run (not a valid bench number)")
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (the benchmark's is 4096)")
     ap.add_argument("--prefill-moe", type=int, default=0, metavar="T",
                     help="side measurement: the prompt-sized MoE block (tcgen05 grouped expert GEMM) of layer 0 over T random rows")
+    ap.add_argument("--no-config4", action="store_true", help="skip the 8-sequence side measurement that follows the headline run")
     ap.add_argument("--verify-only", action="store_true", help="profiling aid: prefill, then warmup + steps verify windows of k+1 rows and nothing else")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "b200" else a.warmup
@@ -446,38 +531,19 @@ def main():
         elif a.config == 2:
             ctx2 = a.ctx if a.ctx != CTX else C2_CTX
             cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, ctx2)
+        elif a.config == 3:
+            cfg = model_config(F, rank, world, a.layers, 8, a.ctx if a.ctx != CTX else C3_TOKENS)
         else:
             cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, a.ctx)
         eng = F.Engine(cfg)
         eng.init_synthetic(seed=0, sigma=0.02)
-    use_peer = False
-    if world > 1 and a.impl == "b200":
-        import ctypes as C
-        uid = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            buf = (C.c_char * 128)()
-            F.check(F.lib().fnx_comm_unique_id(buf))
-            uid = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
-        uid = uid.cuda()
-        dist.broadcast(uid, 0)
-        raw = bytes(uid.cpu().numpy().tobytes())
-        F.check(F.lib().fnx_engine_comm_init(eng._h, raw, rank, world))
-        # the per-layer sum goes over NVLink peer memory (fused with the combine) at every rank count; FNX_EP_NCCL=1 selects
-        # the NCCL all-reduce instead
-        use_peer = os.environ.get("FNX_EP_NCCL", "0") != "1"
-        if use_peer:
-            # the per-layer sum over NVLink peer memory instead of NCCL: exchange the ranks' IPC handles
-            mine = (C.c_char * 128)()
-            F.check(F.lib().fnx_engine_ep_handles(eng._h, mine))
-            hm = torch.frombuffer(bytearray(mine.raw), dtype=torch.uint8).clone().cuda()
-            allh = [torch.zeros(128, dtype=torch.uint8, device="cuda") for _ in range(world)]
-            dist.all_gather(allh, hm)
-            blob = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
-            F.check(F.lib().fnx_engine_ep_open(eng._h, blob, rank, world))
+    use_peer = ep_setup(F, eng, rank, world) if a.impl == "b200" else False
     if a.config == 4:
         return run_config4(a, F, eng, cfg, rank, world, local, use_peer)
     if a.config == 2:
         return run_config2(a, F, eng, cfg, rank, world, local, use_peer)
+    if a.config == 3:
+        return run_config3(a, F, eng, cfg, rank, world, local, use_peer)
     if a.prefill_moe:
         # config 3's expert path on one layer: T rows grouped by expert, gate|up + SwiGLU + down on the tensor cores
         T = a.prefill_moe
@@ -507,7 +573,7 @@ def main():
         tf_peak = float(pk.get("bf16_tflops", 1590.0))
         print(json.dumps({"mode": "prefill-moe", "rows": T, "ms_per_block": ms, "rows_per_s": T / ms * 1e3, "tflops": flops / ms / 1e9,
                           "peak_tflops": tf_peak, "peak_kind": "measured" if pk else "fallback", "frac": flops / ms / 1e9 / tf_peak,
-                          "err": int(err.item()), "note": "one layer's routed + shared experts; routing given; includes the job build and one host read of the job count"}))
+                          "err": int(err.item()), "note": "one layer's routed + shared experts; routing given; includes the job build (the job count stays on the device)"}))
         return
     if a.impl == "reference":
         import oracle as O
@@ -687,10 +753,26 @@ def main():
         line["cpu_baseline"] = {"value": exp_tok / samples[-1]["step_s"], "unit": "tok/s", "cores": used, "host_cores": cores, "kind": "port",
                                 "sample": CPU_SAMPLE, "extrapolated": True, "verify_step_s": samples[-1]["step_s"], "sampled_s": samples[-1]["sampled_s"]}
         line["parity_full_size"] = parity
-    if rank == 0:
-        print(json.dumps(line))
     if eng is not None:
         eng.close()
+        eng = None
+    if a.layers == 48 and not a.no_config4:
+        # the 8-sequence workload (configuration 4, the one expert parallelism is meant for) at this rank count, beside the headline
+        import copy
+        a4 = copy.copy(a)
+        a4.steps, a4.warmup, a4.config = 6, 3, 4
+        room = (a4.warmup + a4.steps + 8) * (K_DRAFT + 1) + 64
+        cfg4 = F.flash_next_config(n_layer=48, max_ctx=C4_CTX + (room + 255) // 256 * 256, max_rows=C4_LANES * (1 + K_DRAFT), ep_rank=rank, ep_size=world, n_seq=C4_SEQS)
+        eng4 = F.Engine(cfg4)
+        eng4.init_synthetic(seed=0, sigma=0.02)
+        peer4 = ep_setup(F, eng4, rank, world)
+        l4 = run_config4(a4, F, eng4, cfg4, rank, world, local, peer4, emit=False)
+        line["config4"] = {k: l4[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup", "verify_window_us", "tokens_per_step", "accepted_per_offered", "ep_sum",
+                                             "tokens_crc", "window_bytes")}
+        line["config4"]["workload"] = l4["config"]["workload"]
+        line["config4"]["e2e"] = l4["e2e"]
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
     return 0

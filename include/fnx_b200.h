@@ -106,8 +106,8 @@ int fnx_moe_combine(const float* part, const int* topi, const float* topw, const
  * engine/src/prefill.cu:288-377): out[t] (+)= the routed experts in [e_lo, e_hi) and (add_shared) the shared expert of
  * rmsnorm(x[t]) * norm_w, for any number of rows T, given the routing (topi, topw [T][K], logits [T][E + 1]).  The
  * (row, pick) pairs are grouped by expert into jobs of up to 256 rows whose products run on the tensor cores
- * (tcgen05.mma, f16 operands decoded from IQ3_S, f32 accumulators in tensor memory).  Not capture-safe: it reads the job
- * count back.  scratch: fnx_moe_prefill_scratch_bytes(T, K, E, H, F) bytes. */
+ * (tcgen05.mma, f16 operands decoded from IQ3_S, f32 accumulators in tensor memory).  The job count stays on the device
+ * (the grids cover its largest possible value; surplus blocks leave at once).  scratch: fnx_moe_prefill_scratch_bytes(T, K, E, H, F) bytes. */
 size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F);
 int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu,
                     const void* Wsh_dn, int e_base, int E, int K, int e_lo, int e_hi, int add_shared, const int* topi,
@@ -299,6 +299,14 @@ int fnx_allreduce(fnx_engine* e, float* x, size_t count, fnx_stream st);
  * Replaces the reference's pinned-host sum exchange (ring_sum, engine/src/kernels.hpp:396). */
 int fnx_engine_ep_handles(fnx_engine* e, void* h_out128);
 int fnx_engine_ep_open(fnx_engine* e, const void* h_all, int rank, int size);
+/* polls a wait for a peer's flag makes before it gives up with FNX_ERR_TIMEOUT (default 2,000,000, about a second).
+ * Drops the captured graphs. */
+int fnx_engine_set_wait_limit(fnx_engine* e, unsigned polls);
+/* Diagnostic: maps every peer of an expert-parallel engine to this rank's own landing buffer, so that the other ranks'
+ * flags never arrive: each window's first exchange then runs out its bounded wait, the window returns FNX_E_STATE with
+ * FNX_ERR_TIMEOUT set, and the context stays usable.  Checks on one GPU, without any fault, that a missing peer cannot hang
+ * a rank (the reference's ring_sum has the same bounded wait, engine/src/kernels.hpp:373). */
+int fnx_engine_ep_open_loopback(fnx_engine* e);
 
 #ifdef __cplusplus
 }

@@ -93,6 +93,8 @@ _PROTOS = {
     "fnx_engine_counters": (_I, [_P, _P]),
     "fnx_engine_error_bits": (_I, [_P, _P]),
     "fnx_commit": (_I, [_P, _P, _I, _I, _P, _I, _P, _P, _I, _P]),
+    "fnx_engine_set_wait_limit": (_I, [_P, C.c_uint]),
+    "fnx_engine_ep_open_loopback": (_I, [_P]),
     "fnx_engine_verify_lanes": (_I, [_P, _I, _P, _P, _I, _P]),
     "fnx_engine_commit_lanes": (_I, [_P, _I, _P, _P]),
     "fnx_engine_draft_lanes": (_I, [_P, _I, _P, _I, _P]),

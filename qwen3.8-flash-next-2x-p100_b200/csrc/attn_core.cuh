@@ -67,7 +67,7 @@ constexpr int ATT_SS = ATT_SC + 4;    // score rows (floats)
 constexpr int ATT_PS = ATT_SC + 8;    // probability rows (halves)
 
 constexpr size_t attn_part_smem() {
-    return (size_t) (2 * ATT_MQ + 2 * ATT_SC) * ATT_QS * sizeof(__half) + (size_t) ATT_MQ * ATT_SS * sizeof(float) +
+    return (size_t) (2 * ATT_MQ + 4 * ATT_SC) * ATT_QS * sizeof(__half) + (size_t) ATT_MQ * ATT_SS * sizeof(float) +
            (size_t) ATT_MQ * ATT_PS * sizeof(__half) + 3 * ATT_MQ * sizeof(float) + ATT_ROWS * sizeof(unsigned);
 }
 
@@ -106,9 +106,10 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
     const int ctx = pos0 + T;
     __half* Qh = reinterpret_cast<__half*>(smem);           // [ATT_MQ][ATT_QS]
     __half* Ql = Qh + ATT_MQ * ATT_QS;
-    __half* Ks = Ql + ATT_MQ * ATT_QS;                      // [ATT_SC][ATT_QS]
+    __half* Ks = Ql + ATT_MQ * ATT_QS;                      // two buffers of [K: ATT_SC][ATT_QS], [V: ATT_SC][ATT_QS]
     __half* Vs = Ks + ATT_SC * ATT_QS;
-    float* Sf = reinterpret_cast<float*>(Vs + ATT_SC * ATT_QS);   // [ATT_MQ][ATT_SS]
+    constexpr int KVB = 2 * ATT_SC * ATT_QS;                // halves per buffer: the next step's rows land while this step is used
+    float* Sf = reinterpret_cast<float*>(Ks + 2 * KVB);     // [ATT_MQ][ATT_SS]
     __half* Pp = reinterpret_cast<__half*>(Sf + ATT_MQ * ATT_SS); // [ATT_MQ][ATT_PS]
     float* ms = reinterpret_cast<float*>(Pp + ATT_MQ * ATT_PS);   // running max, sum, rescale per query
     float* zs = ms + ATT_MQ;
@@ -126,12 +127,12 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         return;
     }
     // the first step's K and V rows are on their way while the queries are split
-    auto fetch_kv = [&](int p0, int np) {
+    auto fetch_kv = [&](int buf, int p0, int np) {
 #pragma unroll
         for (int j = 0; j < ATT_SC * (ATT_HD / 8) / ATT_THREADS; ++j) {
             const int i = tid + j * ATT_THREADS, pp = i / (ATT_HD / 8), d8 = i % (ATT_HD / 8);
-            __half* kd = Ks + pp * ATT_QS + d8 * 8;
-            __half* vd = Vs + pp * ATT_QS + d8 * 8;
+            __half* kd = Ks + buf * KVB + pp * ATT_QS + d8 * 8;
+            __half* vd = Vs + buf * KVB + pp * ATT_QS + d8 * 8;
             if (pp < np) {
                 const size_t go = ((size_t) (p0 + pp) * nkv + kvh) * ATT_HD + d8 * 8;
                 cp_async16(kd, kc + go);
@@ -143,7 +144,7 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch_kv(pa, min(ATT_SC, ctx - pa));
+    fetch_kv(0, pa, min(ATT_SC, ctx - pa));
     // the queries as f16 pairs (hi, lo); rows past NQ are zero
     for (int i0 = tid; i0 < ATT_MQ * (ATT_HD / 4); i0 += 6 * ATT_THREADS) {
         float4 v[6];
@@ -187,20 +188,22 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[m][n][k] = 0.f;
     const float scale = rsqrtf((float) ATT_HD);
-    const uint32_t qh_s = smem_u32(Qh), ql_s = smem_u32(Ql), ks_s = smem_u32(Ks), vs_s = smem_u32(Vs), pp_s = smem_u32(Pp);
+    const uint32_t qh_s = smem_u32(Qh), ql_s = smem_u32(Ql), ks0_s = smem_u32(Ks), vs0_s = smem_u32(Vs), pp_s = smem_u32(Pp);
     // ldmatrix lane addresses: A tiles (16 rows x 16 columns), B tiles of K (8 positions x 32 dims), of V (16 positions x 16 dims, transposed)
     const uint32_t a_off = (uint32_t) ((lane & 15) * ATT_QS + (lane >> 4) * 8) * 2u;
     const uint32_t bk_off = (uint32_t) ((warp * 8 + (lane & 7)) * ATT_QS + (lane >> 3) * 8) * 2u;
     const uint32_t bv_off = (uint32_t) (((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_QS + warp * 32 + (lane >> 4) * 8) * 2u;
     const uint32_t ap_off = (uint32_t) ((lane & 15) * ATT_PS + (lane >> 4) * 8) * 2u;
-    for (int p0 = pa; p0 < ctx; p0 += S * ATT_SC) {
+    int buf = 0;
+    for (int p0 = pa; p0 < ctx; p0 += S * ATT_SC, buf ^= 1) {
         const int np = min(ATT_SC, ctx - p0);
-        if (p0 > pa) {
-            sync();   // the previous step's tiles are read
-            fetch_kv(p0, np);
-        }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        sync();
+        sync();   // this step's rows have landed, and every thread is done with the previous step: its buffer is free
+        {
+            const int pn = p0 + S * ATT_SC;
+            if (pn < ctx) fetch_kv(buf ^ 1, pn, min(ATT_SC, ctx - pn));
+        }
+        const uint32_t ks_s = ks0_s + (uint32_t) (buf * KVB * 2), vs_s = vs0_s + (uint32_t) (buf * KVB * 2);
         // ---- scores: warp w = positions [8 w, 8 w + 8) of the step, all 48 query rows
         {
             float c[3][4];

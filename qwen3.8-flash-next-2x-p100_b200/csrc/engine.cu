@@ -123,6 +123,7 @@ struct fnx_engine {
     unsigned* d_xseq = nullptr;   // [0] sends so far, [1] receives so far, [2] send block counter, [3] receive block counter
     std::vector<void*> ipc_opened;
     bool ep_peers = false;
+    unsigned wait_limit = 2000000u;   // polls a peer-flag wait makes before it gives up with FNX_ERR_TIMEOUT
     // stochastic acceptance (fnx_engine_set_sampling): off = greedy windows
     bool sampling_on = false;
     fnx_sampling sampling{};
@@ -220,7 +221,7 @@ __global__ void k_ep_send(const float* __restrict__ part, const int* __restrict_
 
 __global__ void k_ep_recv(const float* __restrict__ xbuf, const unsigned* __restrict__ xflag, const float* __restrict__ part,
                           const float* __restrict__ logits, int T, int E, int H, int K, int R, int maxr, float* __restrict__ out,
-                          unsigned* __restrict__ seqs, unsigned* __restrict__ err) {
+                          unsigned* __restrict__ seqs, unsigned* __restrict__ err, unsigned wait_limit) {
     const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     const unsigned seq = seqs[1];
     const int slot = (int) (seq & 1u);
@@ -230,7 +231,7 @@ __global__ void k_ep_recv(const float* __restrict__ xbuf, const unsigned* __rest
         // the remaining exchanges must not each run out their limit
         bool all = false;
         const bool gave_up = (*(volatile unsigned*) err & (unsigned) FNX_ERR_TIMEOUT) != 0;
-        for (unsigned it = 0; it < 2000000u && !all && !gave_up; ++it) {
+        for (unsigned it = 0; it < wait_limit && !all && !gave_up; ++it) {
             all = true;
             for (int r = 0; r < R; ++r) {
                 unsigned v;
@@ -412,7 +413,7 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
         k_ep_send<<<grid, 256, 0, e->st>>>(e->part, e->topi, e->topw, T, d.H, d.K, e->e_lo, e->e_hi, e->d_peer_x, e->d_peer_flag, e->c.ep_rank,
                                              e->c.ep_size, d.MAXR, e->d_xseq);
         FNX_LAUNCH_OK("k_ep_send");
-        k_ep_recv<<<grid, 256, 0, e->st>>>(e->xbuf, e->xflag, e->part, e->rlogits, T, d.E, d.H, d.K, e->c.ep_size, d.MAXR, R, e->d_xseq, e->err);
+        k_ep_recv<<<grid, 256, 0, e->st>>>(e->xbuf, e->xflag, e->part, e->rlogits, T, d.E, d.H, d.K, e->c.ep_size, d.MAXR, R, e->d_xseq, e->err, e->wait_limit);
         FNX_LAUNCH_OK("k_ep_recv");
         return FNX_OK;
     }
@@ -1243,5 +1244,31 @@ extern "C" int fnx_engine_set_position(fnx_engine* e, int seq, int pos) {
     e->seqs[seq].pos = pos;
     FNX_CUDA_OK(cudaMemcpy(e->d_pos + seq, &pos, sizeof(int), cudaMemcpyHostToDevice));
     FNX_CUDA_OK(cudaMemcpy(e->d_ctx_n + seq, &pos, sizeof(int), cudaMemcpyHostToDevice));
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_set_wait_limit(fnx_engine* e, unsigned polls) {
+    FNX_REQUIRE(e && polls >= 1, "fnx_engine_set_wait_limit: bad arguments");
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    e->wait_limit = polls;
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);   // the limit is a launch argument of the captured windows
+    e->graphs.clear();
+    e->graph_kernels.clear();
+    return FNX_OK;
+}
+
+// Diagnostic: every peer of an expert-parallel engine is mapped to this rank's OWN landing buffer and flags.  The other
+// ranks' flags then never arrive, so each window's first exchange runs out its bounded wait, raises FNX_ERR_TIMEOUT and
+// returns with the context intact: the way to check, on one GPU and without a fault, that a missing peer cannot hang a rank.
+extern "C" int fnx_engine_ep_open_loopback(fnx_engine* e) {
+    FNX_REQUIRE(e && e->c.ep_size > 1 && e->xbuf && !e->ep_peers, "fnx_engine_ep_open_loopback: needs an expert-parallel engine whose exchange is not open");
+    std::vector<float*> px(e->c.ep_size, e->xbuf);
+    std::vector<unsigned*> pf(e->c.ep_size, e->xflag);
+    FNX_CUDA_OK(cudaMemcpy(e->d_peer_x, px.data(), sizeof(float*) * px.size(), cudaMemcpyHostToDevice));
+    FNX_CUDA_OK(cudaMemcpy(e->d_peer_flag, pf.data(), sizeof(unsigned*) * pf.size(), cudaMemcpyHostToDevice));
+    e->ep_peers = true;
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+    e->graphs.clear();
+    e->graph_kernels.clear();
     return FNX_OK;
 }

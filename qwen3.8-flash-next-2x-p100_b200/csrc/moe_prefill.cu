@@ -154,6 +154,7 @@ struct PfParams {
     int e_base, E;
     const uint8_t* Wsh;        // the shared expert (job.w == E)
     const PfJob* jobs;
+    const int* njobs;          // the launch covers the largest possible job count: blocks past *njobs leave at once
     const int* order;          // per job entry: the pair index t * Kp + k; shared jobs: T * Kp + t
     int TKp;                   // T * Kp: entries at or past it are shared-expert rows
     int Kp;
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__(PF_BLOCK, 1) k_pf_gemm(const PfParams p) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + PF_N);   // [PF_STAGES] stage free (the tensor core's commit)
     uint64_t* full = bars + PF_STAGES;                            // [PF_STAGES] stage filled (one arrival per decode warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full + PF_STAGES);
+    if ((int) blockIdx.x >= *p.njobs) return;   // (before anything is allocated or waited for)
     const PfJob job = p.jobs[blockIdx.x];
     const int ft = blockIdx.y, KB = p.K / 256, nchunk = p.K / PF_KC;
     const uint8_t* W = job.w >= p.E ? p.Wsh : p.W + (size_t) (job.w - p.e_base) * p.expert_stride;
@@ -300,7 +302,9 @@ __global__ void __launch_bounds__(PF_BLOCK, 1) k_pf_gemm(const PfParams p) {
     }
     // all chunks issued: the last commit arrives when every earlier product has finished too
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (ok) ok = __syncthreads_and(mbar_wait_bounded(&bars[(nchunk - 1) % PF_STAGES], (unsigned) (((nchunk - 1) / PF_STAGES) & 1), 20000000u)) != 0;
+    // every warp takes this barrier, whatever it saw: a warp that gave up votes "not ok" without waiting, and the block agrees on one
+    // answer before anything reads or frees the accumulators
+    ok = __syncthreads_and(ok && mbar_wait_bounded(&bars[(nchunk - 1) % PF_STAGES], (unsigned) (((nchunk - 1) / PF_STAGES) & 1), 20000000u)) != 0;
     pf_fence_after();
     if (!ok && tid == 0) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
     if (ok && warp < PF_THREADS / 32) {
@@ -548,14 +552,13 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     FNX_LAUNCH_OK("k_pf_xnorm");
     if (int rc = set_smem_limit((const void*) k_pf_gemm<0>, (int) pf_smem(0))) return rc;
     if (int rc = set_smem_limit((const void*) k_pf_gemm<1>, (int) pf_smem(1))) return rc;
-    // the job count is known on the device only: read it back (prefill is not captured into a graph)
-    int nj = 0;
-    FNX_CUDA_OK(cudaMemcpyAsync(&nj, njobs, sizeof(int), cudaMemcpyDeviceToHost, st));
-    FNX_CUDA_OK(cudaStreamSynchronize(st));
-    if (nj > 0) {
+    // the job count is known on the device only: the grids cover the largest it can be (an expert's pairs in jobs of PF_N rows:
+    // at most one ragged job per expert beyond pairs / PF_N) and the blocks past the count leave at once; nothing is read back
+    {
+        const int nj = (int) ((size_t) n / PF_N) + ne + (add_shared ? (T + PF_N - 1) / PF_N : 0);
         PfParams p{};
         p.W = (const uint8_t*) Wgu; p.expert_stride = gu_stride; p.e_base = e_base; p.E = E; p.Wsh = (const uint8_t*) Wsh_gu;
-        p.jobs = jobs; p.order = order; p.TKp = n; p.Kp = K; p.x = xh; p.rows = F; p.K = H; p.outh = hbuf; p.err = err;
+        p.jobs = jobs; p.njobs = njobs; p.order = order; p.TKp = n; p.Kp = K; p.x = xh; p.rows = F; p.K = H; p.outh = hbuf; p.err = err;
         k_pf_gemm<1><<<dim3(nj, F / PF_M), PF_BLOCK, pf_smem(1), st>>>(p);
         FNX_LAUNCH_OK("k_pf_gemm (gate|up)");
         p.W = (const uint8_t*) Wdn; p.expert_stride = dn_stride; p.Wsh = (const uint8_t*) Wsh_dn;

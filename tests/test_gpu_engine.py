@@ -338,3 +338,24 @@ def test_batched_lanes_equal_single_sequence_windows(F, sampling):
     finally:
         eng.set_sampling(None, 0)
         eng.close()
+
+
+def test_a_missing_peer_times_out_and_leaves_the_context_usable(F):
+    """An expert-parallel rank whose peer never answers: the exchange's bounded wait runs out (a flag that nothing sets), the
+    window reports FNX_ERR_TIMEOUT through the err word instead of hanging, and the same engine keeps answering calls."""
+    cfg = small_cfg(F, ep_rank=0, ep_size=2)
+    eng = F.Engine(cfg)
+    try:
+        eng.init_synthetic(seed=0, sigma=0.02)
+        F.check(F.lib().fnx_engine_ep_open_loopback(eng._h))
+        F.check(F.lib().fnx_engine_set_wait_limit(eng._h, 20000))
+        with pytest.raises(F.FnxError) as ei:
+            eng.verify([1, 2, 3])
+        assert "0x1" in str(ei.value) or "bits" in str(ei.value)
+        assert eng.error_bits() & 1
+        # the context is intact: the next call runs (and times out again, quickly: one short wait per window)
+        with pytest.raises(F.FnxError):
+            eng.verify([4, 5])
+        assert eng.pos() == 0
+    finally:
+        eng.close()
