@@ -101,10 +101,15 @@ class Clocks:
                 "samples": len(sm)}
 
 
+# the draft layer's head covers a draft vocabulary, as the reference's does (its English one holds 40,525 ids; rounded up to
+# whole 16-row tiles); the ids are synthetic: spread evenly over the vocabulary
+DRAFT_VOCAB = 40528
+
+
 def model_config(F, ep_rank, ep_size, layers=48, rounds=64, ctx=CTX):
     # room for the context, every round's window of k + 1 rows, and the few single-row windows run afterwards
     room = max(1024, (rounds + 8) * (K_DRAFT + 1) + 64)
-    return F.flash_next_config(n_layer=layers, max_ctx=ctx + (room + 255) // 256 * 256, max_rows=32, ep_rank=ep_rank, ep_size=ep_size)
+    return F.flash_next_config(n_layer=layers, max_ctx=ctx + (room + 255) // 256 * 256, max_rows=32, ep_rank=ep_rank, ep_size=ep_size, draft_vocab=DRAFT_VOCAB)
 
 
 def step_bytes(routed_jobs_per_step: float, ctx: int, T: int):
@@ -481,7 +486,7 @@ def run_config2(a, F, eng, cfg, rank, world, local, use_peer):
 def bench_config(workload, world, layers):
     """The `config` object of both arms' JSON lines (same keys, so that the two lines name the same workload)."""
     return {"workload": workload, "timing": "inputs (34 GB of weights per step cycle) far larger than the 126 MB L2; CUDA events on the engine's stream",
-            "parallelism": f"ep{world}", "layers": layers}
+            "parallelism": f"ep{world}", "layers": layers, "draft_vocab": DRAFT_VOCAB}
 
 
 def main():
@@ -527,7 +532,7 @@ def main():
             ctx4 = a.ctx if a.ctx != CTX else C4_CTX
             room = (a.warmup + a.steps + 8) * (K_DRAFT + 1) + 64
             cfg = F.flash_next_config(n_layer=a.layers, max_ctx=ctx4 + (room + 255) // 256 * 256, max_rows=C4_LANES * (1 + K_DRAFT), ep_rank=rank, ep_size=world,
-                                      n_seq=C4_SEQS)
+                                      n_seq=C4_SEQS, draft_vocab=DRAFT_VOCAB)
         elif a.config == 2:
             ctx2 = a.ctx if a.ctx != CTX else C2_CTX
             cfg = model_config(F, rank, world, a.layers, a.warmup + a.steps, ctx2)
@@ -762,7 +767,8 @@ def main():
         a4 = copy.copy(a)
         a4.steps, a4.warmup, a4.config = 6, 3, 4
         room = (a4.warmup + a4.steps + 8) * (K_DRAFT + 1) + 64
-        cfg4 = F.flash_next_config(n_layer=48, max_ctx=C4_CTX + (room + 255) // 256 * 256, max_rows=C4_LANES * (1 + K_DRAFT), ep_rank=rank, ep_size=world, n_seq=C4_SEQS)
+        cfg4 = F.flash_next_config(n_layer=48, max_ctx=C4_CTX + (room + 255) // 256 * 256, max_rows=C4_LANES * (1 + K_DRAFT), ep_rank=rank, ep_size=world, n_seq=C4_SEQS,
+                                   draft_vocab=DRAFT_VOCAB)
         eng4 = F.Engine(cfg4)
         eng4.init_synthetic(seed=0, sigma=0.02)
         peer4 = ep_setup(F, eng4, rank, world)

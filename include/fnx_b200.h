@@ -61,6 +61,13 @@ int fnx_fill_normal(float* out, size_t n, float sigma, uint64_t seed, uint32_t s
  * (engine/src/kernels.hpp:49-52, 405-406).  rows % 16 == 0; cols in {256, 512, 1024, 2048, 4096}. */
 int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps,
               float* y, int ldy, int accumulate, unsigned* err, fnx_stream st);
+/* fnx_dense over rows whose quantised image a producer already left on the device (fnx_moe_combine_image): ximg = the image of
+ * the call's T rows (fnx_dense_image_bytes(cols) bytes per 8 rows; 16-byte aligned), normed != 0 when it is the image of
+ * rmsnorm(x) * norm_w.  The blocks copy the image instead of each quantising the rows (the reference quantises a row once
+ * for all its consumers the same way: quantize_q8_1 / q8_twin, engine/src/kernels.hpp:49-52).  Same bits as fnx_dense. */
+size_t fnx_dense_image_bytes(int cols);
+int fnx_dense_image(const void* W, int rows, int cols, const void* ximg, int T, int normed, float eps, float* y, int ldy,
+                    int accumulate, unsigned* err, fnx_stream st);
 
 /* Tracing (FNX_PROF / k_prof_stamp, engine/src/engine.cu:1382-1529): while a device buffer of
  * [blocks][64] u64 is registered, block b of every IQ3_S matvec launch writes %globaltimer stamps of its phases
@@ -101,6 +108,11 @@ int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, const void* 
  * [e_lo, e_hi) of topw * part[t K + k], + sigmoid(logits[t][E]) * part[T K + t] when add_shared */
 int fnx_moe_combine(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
                     int K, int e_lo, int e_hi, int add_shared, float* out, int accumulate, fnx_stream st);
+/* fnx_moe_combine(part, ..., 0, E, 1, R, 1) that also leaves the image of rmsnorm(R[t]) * img_norm_w for fnx_dense_image
+ * (ceil(T / 8) * fnx_dense_image_bytes(H) bytes, 16-byte aligned): the rows are quantised once, by the kernel that completes
+ * them, instead of by every block of the next projection.  R gets the same bits as from fnx_moe_combine. */
+int fnx_moe_combine_image(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
+                          int K, float* R, void* img_out, const float* img_norm_w, fnx_stream st);
 
 /* Prompt-sized MoE block (moe_gate_up_mma / moe_down_mma, engine/src/kernels.hpp:328-330, with the job build of
  * engine/src/prefill.cu:288-377): out[t] (+)= the routed experts in [e_lo, e_hi) and (add_shared) the shared expert of
@@ -186,6 +198,9 @@ int fnx_commit(void* const* k_caches, void* const* v_caches, int n_attn_layers, 
 /* ---------------------------------------------------------------------------------------------- head
  * argmax (engine/src/kernels.hpp:433): per-row maximum, ties to the lower index; err bit 16 on a non-finite logit */
 int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st);
+/* the same over a reduced vocabulary: best_i[t] = map[row] (the draft vocabulary's token ids, Mtp::vocab) */
+int fnx_argmax_mapped(const float* logits, int T, int V, const int* map, int* best_i, float* best_v, unsigned* err,
+                      fnx_stream st);
 /* top_tokens (engine/src/kernels.hpp:445) without penalties: the 64 highest per row, logit descending, id ascending */
 int fnx_top_tokens(const float* logits, int T, int V, float* out_v, int* out_i, fnx_stream st);
 /* embed rows: R[t] = f16 table[tok[t]] (the reference embeds on the host, engine_common.cu:955) */
@@ -229,6 +244,10 @@ typedef struct {
     int ep_rank, ep_size;                               /* expert-parallel shard of this process */
     int n_seq;                                          /* independent sequences (lanes) held */
     float eps, rope_base;
+    int draft_vocab;                                    /* 0: the draft layer's head is the main head over the whole vocabulary;
+                                                         * else (a multiple of 16, <= vocab) the rows of the draft layer's own head
+                                                         * over a draft vocabulary (Mtp::vocab, engine/src/model.hpp:252: head row
+                                                         * -> token id; the reference ships 40,525 and 49,146 ids) */
 } fnx_model_config;
 typedef struct fnx_engine fnx_engine;
 

@@ -36,14 +36,14 @@ class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "n_layer", "hidden", "n_expert", "top_k", "ffn", "n_q_head", "n_kv_head", "head_dim", "n_rot", "gdn_k_head",
         "gdn_v_head", "gdn_head_dim", "vocab", "max_ctx", "max_rows", "attn_every", "ep_rank", "ep_size", "n_seq")] + [
-        ("eps", C.c_float), ("rope_base", C.c_float)]
+        ("eps", C.c_float), ("rope_base", C.c_float), ("draft_vocab", C.c_int)]
 
 
 def flash_next_config(**over) -> ModelConfig:
     """The synthetic Qwen3-Next-style model of the benchmark (48 layers, hidden 2048, 512 experts top-10, ffn 512)."""
     d = dict(n_layer=48, hidden=2048, n_expert=512, top_k=10, ffn=512, n_q_head=16, n_kv_head=2, head_dim=256, n_rot=64,
              gdn_k_head=16, gdn_v_head=32, gdn_head_dim=128, vocab=151936, max_ctx=8192, max_rows=8, attn_every=4,
-             ep_rank=0, ep_size=1, n_seq=1, eps=1e-6, rope_base=1e7)
+             ep_rank=0, ep_size=1, n_seq=1, eps=1e-6, rope_base=1e7, draft_vocab=0)
     d.update(over)
     return ModelConfig(**d)
 
@@ -65,8 +65,12 @@ _PROTOS = {
     "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
     "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "fnx_moe_combine_image": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "fnx_dense_image_bytes": (_Z, [_I]),
+    "fnx_dense_image": (_I, [_P, _I, _I, _P, _I, _I, _F, _P, _I, _I, _P, _P]),
     "fnx_moe_prefill_scratch_bytes": (_Z, [_I, _I, _I, _I, _I]),
     "fnx_moe_prefill": (_I, [_P, _Z, _P, _Z, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _P, _I, _P, _P, _P]),
+    "fnx_argmax_mapped": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
     "fnx_attn_prep_append": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P]),
     "fnx_attn_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
@@ -253,6 +257,30 @@ def moe_experts(Wgu, Wdn, Wsh_gu, Wsh_dn, route, x, F: int, K: int, norm_w=None,
     check(L.fnx_moe_combine(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, e_lo, e_hi,
                             1 if add_shared else 0, ptr(out), 0, _stream()))
     return out, h, part
+
+
+def moe_combine_image(part, route, T: int, E: int, H: int, K: int, R, next_norm_w):
+    """R += the weighted expert outputs (fnx_moe_combine, accumulating); returns the image of rmsnorm(R) * next_norm_w."""
+    import torch
+    L = lib()
+    img = torch.zeros(((T + 7) // 8) * L.fnx_dense_image_bytes(H), dtype=torch.uint8, device=R.device)
+    check(L.fnx_moe_combine_image(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, ptr(R), ptr(img),
+                                  ptr(next_norm_w), _stream()))
+    return img
+
+
+def dense_image(W, rows: int, cols: int, img, T: int, normed: bool = True, eps: float = 1e-6, err=None):
+    """fnx_dense over rows given as the image a producer left (T rows, in calls of 8): y [T][rows]."""
+    import torch
+    y = torch.empty((T, rows), dtype=torch.float32, device=img.device)
+    err = new_err(img.device) if err is None else err
+    L = lib()
+    stride = L.fnx_dense_image_bytes(cols)
+    for t0 in range(0, T, 8):
+        nt = min(8, T - t0)
+        check(L.fnx_dense_image(ptr(W), rows, cols, img.data_ptr() + (t0 // 8) * stride, nt, 1 if normed else 0, eps, y.data_ptr() + t0 * rows * 4,
+                                rows, 0, ptr(err), _stream()))
+    return y
 
 
 def route_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):

@@ -108,6 +108,14 @@ struct fnx_engine {
     fnx_job* jobs = nullptr;
     unsigned* err = nullptr;
     void* att_scratch = nullptr;
+    // the image of the new residual rows that the combine leaves for the next projection (single rank; one per 8 rows)
+    uint8_t* d_img = nullptr;
+    bool use_img = true;
+    // the draft layer's own head over a draft vocabulary (config draft_vocab > 0): dvn rows, row -> token id in d_dvocab;
+    // otherwise the main head and no map
+    uint8_t* mtp_head = nullptr;
+    int* d_dvocab = nullptr;
+    int dvn = 0;
     int *h_stage = nullptr;      // pinned host staging
     std::map<uint64_t, cudaGraphExec_t> graphs;
     std::map<int, std::pair<__half**, __half**>> commit_tables;   // per sequence: device tables of its K and V caches
@@ -296,6 +304,11 @@ __global__ void k_commit(__half* const* __restrict__ kcs, __half* const* __restr
     }
 }
 __global__ void k_advance_pos(int* pos, int n) { *pos += n; }
+// a synthetic draft vocabulary: dv token ids spread evenly over the vocabulary, ascending
+__global__ void k_fill_dvocab(int* map, int dv, int V) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < dv) map[r] = (int) ((long long) r * V / dv);
+}
 
 struct Dims {
     int H, E, K, F, nq, nkv, hd, nrot, nk, nv, hs, V, MAXR, q_rows, kv_rows, attn_in, gdn_ch, gdn_in, P;
@@ -398,15 +411,22 @@ static int init_layer(fnx_engine* e, LayerW& L, int li, uint64_t seed, float sig
 }
 
 // ---- one MoE block on T rows of residual R: R += experts(rmsnorm(R))
-static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
+// next_norm: the norm weights of the projection that reads R next; with them (single rank) the combine leaves that projection's
+// image of the rows in e->d_img and *img_ready is set
+static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T, const float* next_norm = nullptr, bool* img_ready = nullptr) {
     const Dims d = dims(e->c);
     const bool ep = e->c.ep_size > 1;
+    if (img_ready) *img_ready = false;
     FNX_TRY(fnx_router_route(L.wr, R, L.norm2, e->c.eps, T, d.E, d.H, d.K, e->e_lo, e->e_hi, 1, e->rlogits, e->topi, e->topw, e->jobs, e->njobs,
                              e->d_stats, e->err, e->st));
     const int njobs_max = T * d.K + (T + FNX_JOB_TOK - 1) / FNX_JOB_TOK;
     FNX_TRY(fnx_moe_gate_up(L.wgu, e->gu_bytes, e->e_lo, L.wsh_gu, d.E, e->jobs, e->njobs, njobs_max, R, L.norm2, e->c.eps, d.H, d.F, e->hbuf,
                             e->err, e->st));
     FNX_TRY(fnx_moe_down(L.wdn, e->dn_bytes, e->e_lo, L.wsh_dn, d.E, e->jobs, e->njobs, njobs_max, e->hbuf, d.H, d.F, e->part, e->err, e->st));
+    if (!ep && next_norm && e->use_img) {
+        if (img_ready) *img_ready = true;
+        return fnx_moe_combine_image(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, R, e->d_img, next_norm, e->st);
+    }
     if (!ep) return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, d.E, 1, R, 1, e->st);
     if (e->ep_peers) {
         const dim3 grid((d.H + 255) / 256, T);
@@ -426,18 +446,25 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T) {
 }
 
 // dense projection of up to MAXR rows in calls of 8
+// (img: the rows' image in e->d_img is that of x normed by norm_w: the blocks copy it instead of quantising the rows)
 static int enqueue_dense(fnx_engine* e, const uint8_t* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float* y, int ldy,
-                         int accumulate) {
+                         int accumulate, bool img = false) {
     for (int t0 = 0; t0 < T; t0 += 8) {
         const int nt = T - t0 < 8 ? T - t0 : 8;
+        if (img) {
+            FNX_TRY(fnx_dense_image(W, rows, cols, e->d_img + (size_t) (t0 / 8) * fnx_dense_image_bytes(cols), nt, norm_w != nullptr, e->c.eps,
+                                    y + (size_t) t0 * ldy, ldy, accumulate, e->err, e->st));
+            continue;
+        }
         FNX_TRY(fnx_dense(W, rows, cols, x + (size_t) t0 * ldx, ldx, nt, norm_w, e->c.eps, y + (size_t) t0 * ldy, ldy, accumulate, e->err, e->st));
     }
     return FNX_OK;
 }
 
-static int enqueue_attention(fnx_engine* e, const LayerW& L, float* R, int T, int seq, const int* d_parent, const int* d_depth, const int* d_pos) {
+static int enqueue_attention(fnx_engine* e, const LayerW& L, float* R, int T, int seq, const int* d_parent, const int* d_depth, const int* d_pos,
+                             bool img = false) {
     const Dims d = dims(e->c);
-    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0));
+    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0, img));
     __half* kc = L.kc + (size_t) seq * e->cache_rows * d.kv_rows;
     __half* vc = L.vc + (size_t) seq * e->cache_rows * d.kv_rows;
     float* qg = e->proj;
@@ -449,9 +476,9 @@ static int enqueue_attention(fnx_engine* e, const LayerW& L, float* R, int T, in
     return enqueue_dense(e, L.w_out, d.H, d.nq * d.hd, e->mix, d.nq * d.hd, T, nullptr, R, d.H, 1);
 }
 
-static int enqueue_gdn(fnx_engine* e, const LayerW& L, float* R, int T, int seq, const int* d_parent) {
+static int enqueue_gdn(fnx_engine* e, const LayerW& L, float* R, int T, int seq, const int* d_parent, bool img = false) {
     const Dims d = dims(e->c);
-    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0));
+    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0, img));
     float* S = L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs;
     float* hist = L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch;
     FNX_TRY(fnx_gdn_core(e->proj, e->proj_ld, e->proj + d.gdn_ch + d.nv * d.hs, e->proj_ld, hist, L.convw, L.dt, L.a, L.gnorm, S, e->d_cur + seq,
@@ -466,13 +493,14 @@ static int enqueue_verify(fnx_engine* e, int seq, int T, bool tree) {
     k_depths<<<1, 32, 0, e->st>>>(par, e->d_depth, T);
     FNX_LAUNCH_OK("depths");
     FNX_TRY(fnx_embed_rows(e->embed, e->d_tok, T, d.H, e->R, e->st));
+    bool img = false;   // the rows' image for the next projection is ready (left by the layer before)
     for (size_t l = 0; l < e->layers.size(); ++l) {
         const LayerW& L = e->layers[l];
-        if (L.attn) FNX_TRY(enqueue_attention(e, L, e->R, T, seq, par, e->d_depth, e->d_pos + seq));
-        else FNX_TRY(enqueue_gdn(e, L, e->R, T, seq, par));
-        FNX_TRY(enqueue_moe(e, L, e->R, T));
+        if (L.attn) FNX_TRY(enqueue_attention(e, L, e->R, T, seq, par, e->d_depth, e->d_pos + seq, img));
+        else FNX_TRY(enqueue_gdn(e, L, e->R, T, seq, par, img));
+        FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img));
     }
-    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0));
+    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0, img));
     if (e->sampling_on) {   // the sampling rule over the rows' 64 best tokens, uniforms addressed (seed, sequence, window, slot)
         FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
         FNX_TRY(fnx_accept_sample(e->cand_v, e->cand_i, e->d_tok, T, e->sampling, nullptr, nullptr, nullptr, e->sample_seed, (uint32_t) seq, e->d_step + seq,
@@ -491,7 +519,8 @@ static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
     FNX_TRY(enqueue_dense(e, e->mtp_fc_emb, d.H, d.H, e->Emb, d.H, T, e->mtp_enorm, e->Rm, d.H, 1));
     FNX_TRY(enqueue_attention(e, e->mtp, e->Rm, T, seq, nullptr, nullptr, e->d_mpos));
     FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, T));
-    return fnx_dense(e->head, d.V, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, d.V, 0, e->err, e->st);
+    return fnx_dense(e->mtp_head ? e->mtp_head : e->head, e->dvn, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, e->dvn, 0,
+                     e->err, e->st);
 }
 
 // ------------------------------------------------------------------------------------------------ batched lanes
@@ -550,9 +579,9 @@ __global__ void k_scatter_drafts(int* __restrict__ out, const int* __restrict__ 
 
 // mixer of one layer over the lanes' rows: R += out_proj(mixer(in_proj(rmsnorm(R))))
 static int enqueue_mixer_lanes(fnx_engine* e, const LayerW& L, float* R, int T, int n_lanes, int max_lane_rows, const int* d_lane_seq, const int* d_row0,
-                               const int* d_pos) {
+                               const int* d_pos, bool img = false) {
     const Dims d = dims(e->c);
-    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0));
+    FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0, img));
     if (L.attn) {
         float* qg = e->proj;
         float* k = e->proj + d.q_rows;
@@ -572,12 +601,13 @@ static int enqueue_verify_lanes(fnx_engine* e, int n_lanes, int rows) {
     const Dims d = dims(e->c);
     const int T = n_lanes * rows;
     FNX_TRY(fnx_embed_rows(e->embed, e->d_tok, T, d.H, e->R, e->st));
+    bool img = false;
     for (size_t l = 0; l < e->layers.size(); ++l) {
         const LayerW& L = e->layers[l];
-        FNX_TRY(enqueue_mixer_lanes(e, L, e->R, T, n_lanes, rows, e->d_lane_seq, e->d_lane_row0, e->d_pos));
-        FNX_TRY(enqueue_moe(e, L, e->R, T));
+        FNX_TRY(enqueue_mixer_lanes(e, L, e->R, T, n_lanes, rows, e->d_lane_seq, e->d_lane_row0, e->d_pos, img));
+        FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img));
     }
-    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0));
+    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0, img));
     if (e->sampling_on) {
         FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
         return fnx_accept_sample_lanes(e->cand_v, e->cand_i, e->d_tok, e->sampling, e->sample_seed, e->d_lane_seq, e->d_lane_row0, n_lanes, rows, e->d_step,
@@ -598,8 +628,8 @@ static int enqueue_mtp_lanes(fnx_engine* e, int n_lanes, int Tm, int max_rows, c
     FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, Tm));
     k_last_rows<<<dim3((d.H + 255) / 256, n_lanes), 256, 0, e->st>>>(e->Rlast, e->Rm, d_row0, d.H);
     FNX_LAUNCH_OK("draft last rows");
-    FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->Rlast, d.H, n_lanes, e->mtp_onorm, e->logits, d.V, 0));
-    return fnx_argmax(e->logits, n_lanes, d.V, e->best_i, nullptr, e->err, e->st);
+    FNX_TRY(enqueue_dense(e, e->mtp_head ? e->mtp_head : e->head, e->dvn, d.H, e->Rlast, d.H, n_lanes, e->mtp_onorm, e->logits, e->dvn, 0));
+    return fnx_argmax_mapped(e->logits, n_lanes, e->dvn, e->d_dvocab, e->best_i, nullptr, e->err, e->st);
 }
 
 template <typename F>
@@ -664,6 +694,8 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
                 c.ep_rank, c.ep_size, c.n_expert);
     FNX_REQUIRE(c.n_seq >= 1 && c.n_layer >= 1 && c.attn_every >= 1, "engine: bad sequence / layer counts");
     FNX_REQUIRE(c.vocab % (16 * (16 / (c.hidden / 256))) == 0, "engine: vocabulary %d is not a whole number of head tiles", c.vocab);
+    FNX_REQUIRE(c.draft_vocab >= 0 && c.draft_vocab <= c.vocab && c.draft_vocab % 16 == 0, "engine: draft vocabulary %d (0, or a multiple of 16 up to %d)",
+                c.draft_vocab, c.vocab);
     fnx_engine* e = new fnx_engine();
     e->c = c;
     const Dims d = dims(c);
@@ -690,6 +722,12 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->mtp_fc_hid, iq3s_bytes(d.H, d.H), "mtp.fc_hid"));
         FNX_TRY(dalloc(e, &e->mtp_fc_emb, iq3s_bytes(d.H, d.H), "mtp.fc_emb"));
         FNX_TRY(dalloc(e, &e->head, iq3s_bytes(d.V, d.H), "head"));
+        e->dvn = d.V;
+        if (c.draft_vocab > 0) {
+            e->dvn = c.draft_vocab;
+            FNX_TRY(dalloc(e, &e->mtp_head, iq3s_bytes(e->dvn, d.H), "mtp.head"));
+            FNX_TRY(dalloc(e, &e->d_dvocab, (size_t) e->dvn, "mtp.vocab"));
+        }
         FNX_TRY(dalloc(e, &e->embed, (size_t) d.V * d.H, "embed"));
         e->proj_ld = d.attn_in > d.gdn_in ? d.attn_in : d.gdn_in;
         const int mixw = d.nq * d.hd > d.nv * d.hs ? d.nq * d.hd : d.nv * d.hs;
@@ -708,6 +746,8 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->hbuf, (size_t) d.P * d.F, "buf.h"));
         FNX_TRY(dalloc(e, &e->part, (size_t) d.P * d.H, "buf.part"));
         FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
+        FNX_TRY(dalloc(e, &e->d_img, (size_t) ((d.MAXR + 7) / 8) * fnx_dense_image_bytes(d.H)));
+        if (const char* nf = getenv("FNX_NO_IMAGE")) e->use_img = nf[0] != '1';
         if (c.ep_size > 1) {
             FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
             FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size, "buf.ep_flag"));
@@ -795,6 +835,11 @@ extern "C" int fnx_engine_init_synthetic(fnx_engine* e, uint64_t seed, float sig
         FNX_TRY(synth_iq3s(e, e->mtp_fc_hid, d.H, d.H, sigma, seed, (61u * 16 + 0) << 12, tf, tg, tw));
         FNX_TRY(synth_iq3s(e, e->mtp_fc_emb, d.H, d.H, sigma, seed, (61u * 16 + 1) << 12, tf, tg, tw));
         FNX_TRY(synth_iq3s(e, e->head, d.V, d.H, sigma, seed, (62u * 16) << 12, tf, tg, tw));
+        if (e->mtp_head) {
+            FNX_TRY(synth_iq3s(e, e->mtp_head, e->dvn, d.H, sigma, seed, (61u * 16 + 2) << 12, tf, tg, tw));
+            k_fill_dvocab<<<(e->dvn + 255) / 256, 256, 0, e->st>>>(e->d_dvocab, e->dvn, d.V);
+            FNX_LAUNCH_OK("draft vocabulary");
+        }
         // the embedding table: N(0, 1) rounded to f16, in chunks of the staging buffer
         const size_t n = (size_t) d.V * d.H;
         uint32_t sub = 0;
@@ -988,7 +1033,7 @@ extern "C" int fnx_engine_draft(fnx_engine* e, int seq, int k, int* h_drafts) {
     // tokens and positions advance on the device, the k drafts come back in one copy.
     auto mtp_call = [&](int T, int* out) -> int {
         FNX_TRY(enqueue_mtp(e, seq, T, e->Rsrc));
-        return fnx_argmax(e->logits, 1, d.V, out, nullptr, e->err, e->st);
+        return fnx_argmax_mapped(e->logits, 1, e->dvn, e->d_dvocab, out, nullptr, e->err, e->st);
     };
     auto chain = [&]() -> int {
         // (the chain advances the position as it goes: it starts from a copy, so that running it again gives the same result)

@@ -23,7 +23,7 @@ constexpr int ARGMAX_NB = 16, ARGMAX_ROWS = 1024;
 __device__ unsigned long long g_argmax_key[ARGMAX_ROWS];
 __device__ unsigned g_argmax_cnt[ARGMAX_ROWS];
 
-__global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logits, int V, int* __restrict__ best_i,
+__global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logits, int V, const int* __restrict__ map, int* __restrict__ best_i,
                                                  float* __restrict__ best_v, unsigned* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(1024) k_argmax(const float* __restrict__ logit
                 best = atomicExch(&g_argmax_key[t], 0ull);
                 g_argmax_cnt[t] = 0;
             }
-            best_i[t] = (int) ~(uint32_t) best;
+            const int row = (int) ~(uint32_t) best;
+            best_i[t] = map ? map[row] : row;
             if (best_v) best_v[t] = fkey_inv((uint32_t) (best >> 32));
         }
     }
@@ -168,14 +169,18 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float* __restrict__ x, co
 
 using namespace fnxb;
 
-extern "C" int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st) {
+extern "C" int fnx_argmax_mapped(const float* logits, int T, int V, const int* map, int* best_i, float* best_v, unsigned* err, fnx_stream st) {
     FNX_REQUIRE(logits && best_i && err && T >= 1 && V >= 1, "fnx_argmax: bad arguments");
     {
-        const cudaError_t le_ = launch_k(k_argmax, dim3(T, T <= ARGMAX_ROWS && V >= 65536 ? ARGMAX_NB : 1), dim3(1024), 0, as_stream(st), logits, V, best_i, best_v, err);
+        const cudaError_t le_ = launch_k(k_argmax, dim3(T, T <= ARGMAX_ROWS && V >= 65536 ? ARGMAX_NB : 1), dim3(1024), 0, as_stream(st), logits, V, map, best_i, best_v, err);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_argmax: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_argmax");
     return FNX_OK;
+}
+
+extern "C" int fnx_argmax(const float* logits, int T, int V, int* best_i, float* best_v, unsigned* err, fnx_stream st) {
+    return fnx_argmax_mapped(logits, T, V, nullptr, best_i, best_v, err, st);
 }
 
 extern "C" int fnx_top_tokens(const float* logits, int T, int V, float* out_v, int* out_i, fnx_stream st) {

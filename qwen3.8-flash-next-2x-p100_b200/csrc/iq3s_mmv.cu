@@ -80,10 +80,11 @@ template <int NG, int MODE>
 static int launch_mmv(const MmvParams& p0, cudaStream_t st) {
     MmvParams p = p0;
     p.R = 6;   // tile blocks in flight per warp: as many as the shared memory left by the codebook and the images holds
-    while (p.R > 2 && mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max) > 227 * 1024) --p.R;
+    constexpr size_t LIMIT = 227 * 1024;
+    while (p.R > 2 && mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max) > LIMIT) --p.R;
     const size_t smem = mmv_smem_bytes<NG, MODE>(p.K, p.R, p.njobs_max);
-    if (smem > 227 * 1024) return fail(FNX_E_ARG, "iq3s_mmv: %d columns x %d rows need %zu bytes of shared memory", p.K, 4 * NG, smem);
-    if (int rc = set_smem_limit((const void*) k_iq3s_mmv<NG, MODE>, 227 * 1024)) return rc;
+    if (smem > LIMIT) return fail(FNX_E_ARG, "iq3s_mmv: %d columns x %d rows need %zu bytes of shared memory", p.K, 4 * NG, smem);
+    if (int rc = set_smem_limit((const void*) k_iq3s_mmv<NG, MODE>, (int) LIMIT)) return rc;
     {
         const cudaError_t le_ = launch_k(k_iq3s_mmv<NG, MODE>, dim3(sm_count()), dim3(MMV_THREADS), smem, st, p);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "iq3s_mmv: launch failed: %s", cudaGetErrorString(le_));
@@ -179,4 +180,28 @@ extern "C" int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, c
     p.K = F;
     p.err = err;
     return launch_mmv<1, MAT_DOWN>(p, as_stream(st));
+}
+
+extern "C" size_t fnx_dense_image_bytes(int cols) { return stage_image_bytes(2, cols); }
+
+extern "C" int fnx_dense_image(const void* W, int rows, int cols, const void* ximg, int T, int normed, float eps, float* y, int ldy, int accumulate,
+                               unsigned* err, fnx_stream st) {
+    if (int rc = check_cols(cols)) return rc;
+    FNX_REQUIRE(W && ximg && y && err, "fnx_dense_image: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= 8, "fnx_dense_image: %d rows per call (1..8)", T);
+    FNX_REQUIRE(rows > 0 && rows % 16 == 0, "fnx_dense_image: %d output rows, not a multiple of 16", rows);
+    FNX_REQUIRE(((uintptr_t) ximg & 15) == 0 && ((uintptr_t) W & 15) == 0, "fnx_dense_image: the image and W must be 16-byte aligned");
+    MmvParams p{};
+    p.W = (const uint8_t*) W;
+    p.T = T;
+    p.ximg = (const uint8_t*) ximg;
+    p.norm_w = normed ? (const float*) ximg : nullptr;   // only its presence matters: the image holds the normed rows' codes
+    p.eps = eps;
+    p.out = y;
+    p.ldo = ldy;
+    p.rows = rows;
+    p.K = cols;
+    p.accumulate = accumulate;
+    p.err = err;
+    return T <= 4 ? launch_mmv<1, MAT_DENSE>(p, as_stream(st)) : launch_mmv<2, MAT_DENSE>(p, as_stream(st));
 }

@@ -31,7 +31,16 @@ struct MmvParams {
     int accumulate;
     int R;      // ring slots per warp
     unsigned* err;
+    // dense: the rows' image, already built (stage_image_bytes() bytes in the layout of the block's own image): the
+    // block copies it instead of quantising x
+    const uint8_t* ximg;
 };
+
+// bytes of a dense image of NG row groups over K columns: cells, scales, block sums of squares (the order the block
+// holds them in)
+__host__ __device__ inline size_t stage_image_bytes(int NG, int K) {
+    return (size_t) NG * ((size_t) (K / 32) * 32 * 8 + (size_t) (K / 256) * 8 * 4 + 4 * 16 * 4);
+}
 
 // jobs whose activation images a block holds at once: its range of units spans at most two jobs of gate|up and a
 // few of down; anything wider is walked in passes
@@ -114,6 +123,18 @@ __device__ __forceinline__ void stage_begin(const MmvParams& p, StageRegs& h, in
             const int w = tid + i * (NW * 32);
             h.jw[i] = w < nword ? reinterpret_cast<const int*>(p.jobs)[w] : 0;
         }
+    } else if (p.ximg) {
+        // the image's first 16-byte words ride in the registers the rows would have used
+        static_assert(QUANT_BATCH == 2, "eight 16-byte words per thread");
+        const int n16 = (int) (stage_image_bytes(NG, p.K) / 16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = tid + j * (NW * 32);
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < n16) t = __ldcg(reinterpret_cast<const float4*>(p.ximg) + i);
+            float* d = j < 4 ? &h.v[j >> 1][(j & 1) * 4] : &h.w[(j - 4) >> 1][(j & 1) * 4];
+            d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+        }
     } else {
 #pragma unroll
         for (int j = 0; j < QUANT_BATCH; ++j) {
@@ -171,7 +192,19 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
             }
             nlive = cum[JMAX];
         }
-        const int ntask = nlive * KB;
+        const bool given = !MOE && p.ximg;   // the image comes ready-made
+        if (given) {
+            const int n16 = (int) (stage_image_bytes(NG, p.K) / 16);
+            float4* dst = reinterpret_cast<float4*>(S.cells);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = tid + j * (NW * 32);
+                const float* d = j < 4 ? &h.v[j >> 1][(j & 1) * 4] : &h.w[(j - 4) >> 1][(j & 1) * 4];
+                if (i < n16) dst[i] = make_float4(d[0], d[1], d[2], d[3]);
+            }
+            for (int i = tid + 8 * (NW * 32); i < n16; i += NW * 32) dst[i] = __ldcg(reinterpret_cast<const float4*>(p.ximg) + i);
+        }
+        const int ntask = given ? 0 : nlive * KB;
         for (int id0 = warp; id0 < ntask; id0 += NW * QUANT_BATCH) {
             QuantTask q[QUANT_BATCH];
 #pragma unroll
@@ -207,7 +240,7 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
             if (!MOE) live = t < p.T;
             else live = j0 + t / 4 < j1 && (t & 3) < cum[t / 4 + 1] - cum[t / 4];
             const bool used = !MOE || j0 + t / 4 < j1;
-            if (t < NROW && used && !live) quant_zero_row(t, p.K, S.cells, S.scales, S.rs, tid % TPR, TPR);
+            if (t < NROW && used && !live && !given) quant_zero_row(t, p.K, S.cells, S.scales, S.rs, tid % TPR, TPR);
         }
         first = false;
         __syncthreads();

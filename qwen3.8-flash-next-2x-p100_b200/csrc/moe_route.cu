@@ -194,6 +194,87 @@ __global__ void k_combine(const float* __restrict__ part, const int* __restrict_
     *o = prev + fix_to_float(s);
 }
 
+// k_combine that also leaves the new rows' image for the next dense product (fnx_dense_image): one warp per (256-column block,
+// row), the lane's 8 columns of every addend in flight at once; the sums and the residual update are k_combine's, the image
+// cells are those the dense kernel's own quantisation (quant_finish) makes of the same values, so the product's bits do not
+// change.  The blocks of an image's last live row also clear the rows of its last group that hold nothing.
+__global__ void __launch_bounds__(32) k_combine_image(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
+                                                      const float* __restrict__ logits, int T, int E, int H, int K, float* __restrict__ out,
+                                                      uint8_t* __restrict__ img_out, const float* __restrict__ img_norm_w, size_t img_stride) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int blk = blockIdx.x, t = blockIdx.y, lane = threadIdx.x, KB = H / 256;
+    const size_t col = (size_t) blk * 256 + lane * 8;
+    float w[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) w[k] = k < K ? topw[t * K + k] : 0.f;
+    const float shl = logits[(size_t) t * (E + 1) + E];
+    QuantTask q[QUANT_BATCH];
+    float v[QUANT_BATCH][8], nw[QUANT_BATCH][8];
+#pragma unroll
+    for (int j = 0; j < QUANT_BATCH; ++j) {
+        q[j].src = nullptr;
+        q[j].t = q[j].blk = 0;
+    }
+    q[0].src = out + (size_t) t * H + (size_t) blk * 256;
+    q[0].t = t & 7;
+    q[0].blk = blk;
+    quant_fetch(q[0], img_norm_w, lane, v[0], nw[0]);   // the old values and the norm weights
+    unsigned long long s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = 0ull;
+    // the addends in two halves of up to 16 picks, all of a half's loads in flight at once
+#pragma unroll
+    for (int k0 = 0; k0 < 32; k0 += 16) {
+        if (k0 >= K) break;
+        float4 a[16][2];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            if (k0 + k < K) {
+                const float4* src = reinterpret_cast<const float4*>(part + ((size_t) t * K + k0 + k) * H + col);
+                a[k][0] = src[0];
+                a[k][1] = src[1];
+            }
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            if (k0 + k < K) {
+                const float wk = w[k0 + k];
+                const float e8[8] = {a[k][0].x, a[k][0].y, a[k][0].z, a[k][0].w, a[k][1].x, a[k][1].y, a[k][1].z, a[k][1].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[i] += fix_from_float(wk * e8[i]);
+            }
+    }
+    {
+        const float4* src = reinterpret_cast<const float4*>(part + ((size_t) T * K + t) * H + col);
+        const float4 a0 = src[0], a1 = src[1];
+        const float g = sigmoidf_(shl);
+        const float e8[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] += fix_from_float(g * e8[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[0][i] += fix_to_float(s[i]);
+    float* dst = out + (size_t) t * H + col;
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0][0], v[0][1], v[0][2], v[0][3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(v[0][4], v[0][5], v[0][6], v[0][7]);
+    // the image of the row's group of 8
+    const int t0 = t & ~7, nt = min(8, T - t0), NG = nt <= 4 ? 1 : 2;
+    uint2* cells = reinterpret_cast<uint2*>(img_out + (size_t) (t0 / 8) * img_stride);
+    float* scales = reinterpret_cast<float*>(cells + (size_t) NG * (H / 32) * 32);
+    float* rs = scales + (size_t) NG * KB * 8;
+    quant_finish(q, v, nw, H, img_norm_w, cells, scales, rs, lane);
+    if (t == t0 + nt - 1)
+        for (int td = nt; td < 4 * NG; ++td) {
+            const int ng = td >> 2, n = td & 3;
+            for (int i = lane; i < 64; i += 32) {   // (sub-block of the column block, level, q)
+                const int sbG = blk * 8 + (i >> 3), lvl = (i >> 2) & 1, qq = i & 3;
+                cells[((size_t) (ng * (H / 32) + sbG) * 8 + n + 4 * lvl) * 4 + qq] = make_uint2(0u, 0u);
+            }
+            if (lane < 2) scales[(size_t) (ng * KB + blk) * 8 + n + 4 * lane] = 0.f;
+            if (lane == 2) rs[td * 16 + blk] = 0.f;
+        }
+}
+
 }  // namespace fnxb
 
 using namespace fnxb;
@@ -228,5 +309,20 @@ extern "C" int fnx_moe_combine(const float* part, const int* topi, const float* 
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_combine: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_moe_combine");
+    return FNX_OK;
+}
+
+extern "C" int fnx_moe_combine_image(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H, int K, float* R,
+                                     void* img_out, const float* img_norm_w, fnx_stream st) {
+    FNX_REQUIRE(part && topi && topw && logits && R && img_out && img_norm_w, "fnx_moe_combine_image: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && K >= 1 && K <= 32, "fnx_moe_combine_image: %d rows, top %d", T, K);
+    FNX_REQUIRE(H == 256 || H == 512 || H == 1024 || H == 2048 || H == 4096, "fnx_moe_combine_image: hidden %d", H);
+    FNX_REQUIRE(((uintptr_t) img_out & 15) == 0 && ((uintptr_t) R & 15) == 0 && ((uintptr_t) part & 15) == 0, "fnx_moe_combine_image: 16-byte alignment");
+    {
+        const cudaError_t le_ = launch_k(k_combine_image, dim3(H / 256, T), dim3(32), 0, as_stream(st), part, topi, topw, logits, T, E, H, K, R, (uint8_t*) img_out,
+                                         img_norm_w, fnx_dense_image_bytes(H));
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_combine_image: launch failed: %s", cudaGetErrorString(le_));
+    }
+    FNX_LAUNCH_OK("fnx_moe_combine_image");
     return FNX_OK;
 }

@@ -80,6 +80,12 @@ class OracleModel:
         self.out_norm = f32("out_norm")
         self.fc_hid, self.fc_emb = iq("mtp.fc_hid", self.H, self.H), iq("mtp.fc_emb", self.H, self.H)
         self.head = iq("head", self.V, self.H)
+        # the draft layer's own head over a draft vocabulary (head row -> token id), or the main head
+        self.dvn = int(getattr(c, "draft_vocab", 0)) or self.V
+        self.mtp_head, self.dvocab = self.head, None
+        if with_mtp and self.dvn != self.V:
+            self.mtp_head = iq("mtp.head", self.dvn, self.H)
+            self.dvocab = eng.tensor("mtp.vocab", torch.int32).cpu().numpy().copy()
         self.embed = eng.tensor("embed", torch.float16).cpu().numpy().reshape(self.V, self.H).astype(np.float32)
         self.pos, self.cur = 0, 0
         self.routing = []
@@ -151,8 +157,9 @@ class OracleModel:
             O.iq3s_gemv(self.fc_emb, self.H, self.H, O.rmsnorm(emb, self.mtp_enorm, self.cfg.eps))
         Rm = self._attention(self.mtp, Rm, pos0, None, None)
         Rm = self._moe(self.mtp, Rm)
-        logits = O.iq3s_gemv(self.head, self.V, self.H, O.rmsnorm(Rm[-1:], self.mtp_onorm, self.cfg.eps))
-        return Rm, int(O.argmax(logits)[0][0])
+        logits = O.iq3s_gemv(self.mtp_head, self.dvn, self.H, O.rmsnorm(Rm[-1:], self.mtp_onorm, self.cfg.eps))
+        row = int(O.argmax(logits)[0][0])
+        return Rm, row if self.dvocab is None else int(self.dvocab[row])
 
     def draft(self, emitted, k):
         n = len(emitted)

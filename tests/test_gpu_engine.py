@@ -89,6 +89,35 @@ def test_verify_commit_draft_match_oracle(F, O, model):
     assert r1 == (r2[0], list(r2[1]), list(r2[2]))
 
 
+def test_drafts_over_a_draft_vocabulary_match_oracle(F, O):
+    """The draft layer with its own head over a draft vocabulary (Mtp::vocab of the reference: head row -> token id): the
+    chained drafts are the oracle's, they are ids of that vocabulary, and the batched chain gives the same tokens."""
+    cfg = small_cfg(F, draft_vocab=512, n_seq=2)
+    eng = F.Engine(cfg)
+    try:
+        eng.init_synthetic(seed=3, sigma=0.02)
+        om = OracleModel(F, O, eng, cfg)
+        assert om.dvocab.shape == (512,) and np.all(np.diff(om.dvocab) > 0) and om.dvocab[-1] < cfg.vocab
+        rng = np.random.default_rng(5)
+        eng.reset()
+        toks = rng.integers(0, cfg.vocab, size=5).tolist()
+        n, path, em = eng.verify(toks)
+        on, opath, oem = om.verify(toks, None)
+        assert (n, path, em) == (on, list(opath), list(oem))
+        eng.commit(path)
+        om.commit(list(opath))
+        d = eng.draft(3)
+        assert d == om.draft(list(oem), 3)
+        assert all(t in set(om.dvocab.tolist()) for t in d)
+        # the same window on a second sequence through the batched lanes
+        res = eng.verify_lanes([1], [toks])
+        assert res[0] == (n, path, em)
+        eng.commit_lanes([1], [len(path)])
+        assert eng.draft_lanes([1], 3) == [d]
+    finally:
+        eng.close()
+
+
 def test_full_size_layers_match_oracle(F, O):
     """The benchmark model's own dimensions (hidden 2048, 512 experts top-10 of width 512, 16/2 attention heads of 256, 16/32
     DeltaNet heads of 128, vocabulary 151,936), four layers of it (three DeltaNet, one attention): a prompt, a 5-row chain window

@@ -171,6 +171,45 @@ def test_moe_block_matches_oracle(F, O, E, H, Fn, K, T):
     assert rel_err(acc, ref_out) < TOL_GEMV
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 20])
+def test_combine_that_leaves_the_image_gives_the_same_bits(F, T):
+    """fnx_moe_combine_image updates the residual like fnx_moe_combine (accumulating), bit for bit, and the image it leaves
+    feeds fnx_dense_image the bits fnx_dense computes from the rows themselves; a smaller window after a larger one leaves no
+    stale rows behind."""
+    import torch
+    E, H, Fn, K = 64, 2048, 512, 10
+    fx = _moe_fixture(F, E, H, Fn, seed=21)
+    rng = np.random.default_rng(100 + T)
+    nw = dev((1.0 + 0.05 * rng.standard_normal(H)).astype(np.float32))
+    nw2 = dev((1.0 + 0.05 * rng.standard_normal(H)).astype(np.float32))
+    Wd = fx["gu_t"]   # any tile matrix with 2048 columns serves as the next projection: expert 0's gate|up (1024 rows)
+    rows = 2 * Fn
+    L = F.lib()
+    for rep in range(2):
+        x = dev(rng.standard_normal((T, H)).astype(np.float32))
+        R0 = dev(rng.standard_normal((T, H)).astype(np.float32))
+        route = F.router_route(fx["wr"], x, K, norm_w=nw)
+        out, h, part = F.moe_experts(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], route, x, Fn, K, norm_w=nw)
+        want = R0.clone()
+        F.check(L.fnx_moe_combine(F.ptr(part), F.ptr(route["topi"]), F.ptr(route["topw"]), F.ptr(route["logits"]), T, E, H, K, 0, E, 1, F.ptr(want), 1,
+                                  None))
+        got = R0.clone()
+        img = F.moe_combine_image(part, route, T, E, H, K, got, nw2)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        y_img = F.dense_image(Wd, rows, H, img, T)
+        y_ref, _ = F.dense(Wd, rows, H, want, norm_w=nw2)
+        assert torch.equal(y_img, y_ref)
+    if T == 5:   # the image buffer held 8 rows before: the rows of the group that hold nothing now must read as zero
+        img8 = torch.full_like(img, 0x55)
+        F.check(L.fnx_moe_combine_image(F.ptr(part), F.ptr(route["topi"]), F.ptr(route["topw"]), F.ptr(route["logits"]), T, E, H, K, F.ptr(R0.clone()),
+                                        F.ptr(img8), F.ptr(nw2), None))
+        got = R0.clone()
+        F.check(L.fnx_moe_combine_image(F.ptr(part), F.ptr(route["topi"]), F.ptr(route["topw"]), F.ptr(route["logits"]), T, E, H, K, F.ptr(got), F.ptr(img8),
+                                        F.ptr(nw2), None))
+        assert torch.equal(F.dense_image(Wd, rows, H, img8, T), y_ref)
+
+
 _CONFIG0 = {}
 
 
