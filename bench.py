@@ -337,14 +337,15 @@ def run_config4(a, F, eng, cfg, rank, world, local, use_peer, emit=True):
 
 
 def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
-    """Configuration 3: cold prefill of 38,912 uniform-random tokens (seed 3).  The engine reads a prompt through chained
-    windows of 32 rows of the decode path's kernels (every row kept); the tensor-core grouped expert GEMM
-    (fnx_moe_prefill, `--prefill-moe`) is measured on its own and is not on this path yet.  One step = the whole prompt."""
+    """Configuration 3: cold prefill of 38,912 uniform-random tokens (seed 3).  One rank reads the prompt on the prompt pass
+    (fnx_engine_prompt: projections and experts on the tensor cores, chained DeltaNet windows, window attention); expert-parallel
+    ranks, and `--prompt-windows`, read it through chained 32-row windows of the decode kernels.  One step = the whole prompt."""
     import numpy as np
     import torch
     n = a.ctx if a.ctx != CTX else C3_TOKENS
     toks = np.random.default_rng(3).integers(0, cfg.vocab, size=n).tolist()
     est = torch.cuda.ExternalStream(F.lib().fnx_engine_stream(eng._h))
+    windows = world > 1 or a.prompt_windows
     clocks = Clocks(local)
     clocks.launch()
     times, walls = [], []
@@ -358,7 +359,10 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.perf_counter()
         t0.record(est)
-        eng.prefill(toks)
+        if windows:
+            eng.prefill(toks)
+        else:
+            eng.prompt(toks)
         t1.record(est)
         _barrier(world)
         walls.append(time.perf_counter() - w0)
@@ -370,12 +374,13 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
     passes = len(times) - 1
     line = {"metric": "prefill tok/s (cold prompt)", "value": n / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": passes, "warmup": 1, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
-            "config": {"workload": f"configuration 3: cold prefill of {n} uniform-random tokens (seed 3) through chained 32-row windows of the decode kernels",
+            "config": {"workload": f"configuration 3: cold prefill of {n} uniform-random tokens (seed 3) " +
+                       ("through chained 32-row windows of the decode kernels" if windows else "on the prompt pass (tensor-core projections and experts, chained DeltaNet windows, window attention)"),
                        "timing": "weights (34 GB per window) far larger than the 126 MB L2; CUDA events on the engine's stream", "parallelism": f"ep{world}", "layers": a.layers},
             "clocks": clk, "gpu_launches": int((c1[0] - c0[0]) / passes),
             "e2e": {"value": n / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * n + 4 * n, "d2h_bytes_per_step": 0, "wall_ms_per_step": wall * 1e3},
             "windows": (n + cfg.max_rows - 1) // cfg.max_rows, "us_per_window": ms * 1e3 / ((n + cfg.max_rows - 1) // cfg.max_rows),
-            "note": "the tensor-core path for prompts (grouped expert GEMM on tcgen05) exists as a kernel and is measured by --prefill-moe; the chunked DeltaNet scan and prompt attention it needs around it are not built, so prompts take the decode kernels"}
+            "path": "windows" if windows else "prompt pass"}
     if rank == 0:
         print(json.dumps(line))
     eng.close()
@@ -505,6 +510,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (the benchmark's is 4096)")
     ap.add_argument("--prefill-moe", type=int, default=0, metavar="T",
                     help="side measurement: the prompt-sized MoE block (tcgen05 grouped expert GEMM) of layer 0 over T random rows")
+    ap.add_argument("--prompt-windows", action="store_true", help="configuration 3: read the prompt through 32-row windows of the decode kernels instead of the prompt pass")
     ap.add_argument("--no-config4", action="store_true", help="skip the 8-sequence side measurement that follows the headline run")
     ap.add_argument("--verify-only", action="store_true", help="profiling aid: prefill, then warmup + steps verify windows of k+1 rows and nothing else")
     a = ap.parse_args()

@@ -121,6 +121,13 @@ int fnx_moe_combine_image(const float* part, const int* topi, const float* topw,
  * (tcgen05.mma, f16 operands decoded from IQ3_S, f32 accumulators in tensor memory).  The job count stays on the device
  * (the grids cover its largest possible value; surplus blocks leave at once).  scratch: fnx_moe_prefill_scratch_bytes(T, K, E, H, F) bytes. */
 size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F);
+/* fnx_dense for prompt-sized row counts (the prompt pass's projections, engine/src/prefill.cu; q8s_gemm / k_mmq,
+ * engine/src/kernels.hpp:56-70): y[t][r] (+)= W[r] . xin[t] for any T on the same tensor-core kernel as the prompt MoE block
+ * (weights decoded from IQ3_S to f16, activations rounded to f16 once per call, f32 accumulators in tensor memory).  x is
+ * [T][cols] contiguous; rows % 16 == 0; cols % 256 == 0; scratch: fnx_dense_prompt_scratch_bytes(T, cols) bytes. */
+size_t fnx_dense_prompt_scratch_bytes(int T, int cols);
+int fnx_dense_prompt(const void* W, int rows, int cols, const float* x, int T, const float* norm_w, float eps, float* y,
+                     int ldy, int accumulate, void* scratch, unsigned* err, fnx_stream st);
 int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu,
                     const void* Wsh_dn, int e_base, int E, int K, int e_lo, int e_hi, int add_shared, const int* topi,
                     const float* topw, const float* logits, const float* x, const float* norm_w, float eps, int T, int H,
@@ -181,6 +188,12 @@ int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int ldab, float* h
 /* Batched lanes of gdn_core (gdn_core_segs, engine/src/kernels.cu:2112-2156; GdnLanes, engine/src/kernels.hpp:103-110):
  * lane j is a chain from slot cur[lane_seq[j]] of that sequence's rings at hist_pool + seq * hist_seq_stride floats and
  * S_pool + seq * s_seq_stride floats. */
+/* the same over a prompt's T rows (any T), a chain of which every row is kept (gdn_prompt, engine/src/kernels.cu:2158): windows
+ * of min(FNX_MAX_ROWS, NS - 1) rows run back to back, each from the slot the one before left its last row's state in; only
+ * that state and history are written.  The final state is in slot (*cur + T) % NS: the caller advances *cur by T. */
+int fnx_gdn_prompt(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt,
+                   const float* a, const float* nw, float* S_pool, const int* cur, int NS, float* y, int nk, int nv, int hs,
+                   int T, float eps, fnx_stream st);
 int fnx_gdn_core_lanes(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, size_t hist_seq_stride,
                        const float* convw, const float* dt, const float* a, const float* nw, float* S_pool,
                        size_t s_seq_stride, const int* cur, int NS, const int* lane_seq, const int* lane_row0, int n_lanes,
@@ -265,6 +278,13 @@ int fnx_engine_reset(fnx_engine* e, int seq);
  * through the model; leaves logits, per-row argmax and the acceptance result on the device and, when h_result is
  * not null, copies the greedy acceptance result back (synchronises).  Does not commit. */
 int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const int* h_parent, int T, int* h_result);
+/* Engine::prefill (the prompt pass, engine/src/prefill.cu): reads n prompt tokens into sequence `seq` and leaves the engine
+ * as after verifying and keeping them (caches, states, context, the last token's logits and emitted token), but on the
+ * prompt-sized kernels: the first n - 1 tokens go chunk by chunk and layer by layer through tensor-core projections and
+ * experts, chained DeltaNet windows and window attention; the last token through a one-row window.  Activations are rounded
+ * to f16 where the window path uses two int8 levels, so the states agree with the window path to the parity tolerance, not
+ * bit for bit.  Single rank only (FNX_E_ARG on an expert-parallel engine).  Synchronises. */
+int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n);
 /* Engine::commit: keeps the n accepted rows h_path[0..n) of the last window of `seq`.  The window buffers (tokens,
  * acceptance result, residual rows) are shared by the engine's sequences: commit (and draft) sequence A before verifying
  * sequence B; a commit or draft for a sequence other than the one verified last returns FNX_E_STATE. */

@@ -69,6 +69,8 @@ _PROTOS = {
     "fnx_dense_image_bytes": (_Z, [_I]),
     "fnx_dense_image": (_I, [_P, _I, _I, _P, _I, _I, _F, _P, _I, _I, _P, _P]),
     "fnx_moe_prefill_scratch_bytes": (_Z, [_I, _I, _I, _I, _I]),
+    "fnx_dense_prompt_scratch_bytes": (_Z, [_I, _I]),
+    "fnx_dense_prompt": (_I, [_P, _I, _I, _P, _I, _P, _F, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_prefill": (_I, [_P, _Z, _P, _Z, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _P, _I, _P, _P, _P]),
     "fnx_argmax_mapped": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
     "fnx_attn_prep_append": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P]),
@@ -76,6 +78,7 @@ _PROTOS = {
     "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
     "fnx_attn_static_setup": (_I, []),
     "fnx_attn_static": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "fnx_gdn_prompt": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _P]),
     "fnx_gdn_core": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _P]),
     "fnx_argmax": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "fnx_top_tokens": (_I, [_P, _I, _I, _P, _P, _P]),
@@ -91,6 +94,7 @@ _PROTOS = {
     "fnx_engine_tensor": (_P, [_P, C.c_char_p, C.POINTER(_Z)]),
     "fnx_engine_reset": (_I, [_P, _I]),
     "fnx_engine_verify": (_I, [_P, _I, _P, _P, _I, _P]),
+    "fnx_engine_prompt": (_I, [_P, _I, _P, _I]),
     "fnx_engine_commit": (_I, [_P, _I, _P, _I]),
     "fnx_engine_draft": (_I, [_P, _I, _I, _P]),
     "fnx_engine_last_ms": (_F, [_P]),
@@ -267,6 +271,20 @@ def moe_combine_image(part, route, T: int, E: int, H: int, K: int, R, next_norm_
     check(L.fnx_moe_combine_image(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, ptr(R), ptr(img),
                                   ptr(next_norm_w), _stream()))
     return img
+
+
+def dense_prompt(W, rows: int, cols: int, x, norm_w=None, eps: float = 1e-6, out=None, accumulate: bool = False, err=None):
+    """fnx_dense for any number of rows, on the tensor cores: y [T][rows] (+)= W . x[t]."""
+    import torch
+    T = x.shape[0]
+    if out is None:
+        out = torch.zeros((T, rows), dtype=torch.float32, device=x.device)
+    err = new_err(x.device) if err is None else err
+    L = lib()
+    scratch = torch.empty(L.fnx_dense_prompt_scratch_bytes(T, cols), dtype=torch.uint8, device=x.device)
+    check(L.fnx_dense_prompt(ptr(W), rows, cols, ptr(x), T, ptr(norm_w), eps, ptr(out), out.stride(0), 1 if accumulate else 0, ptr(scratch), ptr(err),
+                             _stream()))
+    return out, err
 
 
 def dense_image(W, rows: int, cols: int, img, T: int, normed: bool = True, eps: float = 1e-6, err=None):
@@ -525,6 +543,12 @@ class Engine:
 
     def pos(self, seq: int = 0) -> int:
         return lib().fnx_engine_pos(self._h, seq)
+
+    def prompt(self, tokens, seq: int = 0):
+        """Reads a prompt on the prompt-sized kernels (fnx_engine_prompt); leaves the engine as after verify + commit."""
+        import ctypes as C
+        n = len(tokens)
+        check(lib().fnx_engine_prompt(self._h, seq, (C.c_int * n)(*tokens), n))
 
     def prefill(self, tokens, seq: int = 0):
         """Reads a prompt by running it through chained verify windows and keeping every row."""

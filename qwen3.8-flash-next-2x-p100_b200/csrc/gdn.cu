@@ -23,7 +23,8 @@ constexpr int GDN_HS = 128, GDN_Q = 4, GDN_QC = GDN_HS / GDN_Q, GDN_THREADS = 12
 __device__ __forceinline__ void gdn_body(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
                                          const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
                                          const float* __restrict__ nw, float* __restrict__ S_pool, int cur, int NS, const int* __restrict__ parent,
-                                         float* __restrict__ y, int nk, int nv, int T, float eps, float* sm) {
+                                         float* __restrict__ y, int nk, int nv, int T, float eps, float* sm, bool last_only = false) {
+    // (last_only: a prompt's window, every row of which is kept: only the last row's state and history are written)
     cg::cluster_group cluster = cg::this_cluster();
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, kh = lv % nk, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -113,7 +114,7 @@ __device__ __forceinline__ void gdn_body(const float* __restrict__ qkvz, int str
             if (part == 0) xq[t * GDN_HS + i] = v;
             else if (part == 1) xk[t * GDN_HS + i] = v;
             else vs[t * GDN_QC + i] = v;
-            if (writes) {
+            if (writes && (!last_only || t == T - 1)) {
                 float* hout = hist_pool + (size_t) ((cur + 1 + t) % NS) * hsz;
                 hout[c] = x2;
                 hout[ch + c] = x1;
@@ -160,11 +161,12 @@ __device__ __forceinline__ void gdn_body(const float* __restrict__ qkvz, int str
         const float delta = (vs[t * GDN_QC + lane] - gv * kvs) * bv;
         float at = 0.f;
         float* dst = S_pool + (size_t) ((cur + 1 + t) % NS) * ssz + soff;
+        const bool keep = !last_only || t == T - 1;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             s[r] = fmaf(kt[r], delta, gv * s[r]);
             at = fmaf(s[r], qt[r], at);
-            dst[(size_t) r * GDN_HS] = s[r];
+            if (keep) dst[(size_t) r * GDN_HS] = s[r];
         }
         ared[(t * 4 + part) * GDN_QC + lane] = at;
         have = t;
@@ -199,11 +201,11 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
     k_gdn_core(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab, float* __restrict__ hist_pool,
                const float* __restrict__ convw, const float* __restrict__ dt, const float* __restrict__ a_,
                const float* __restrict__ nw, float* __restrict__ S_pool, const int* __restrict__ curp, int NS,
-               const int* __restrict__ parent, float* __restrict__ y, int nk, int nv, int T, float eps) {
+               const int* __restrict__ parent, float* __restrict__ y, int nk, int nv, int T, float eps, int cur_off, int last_only) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(16) float sm[];
-    gdn_body(qkvz, stride, ab, ldab, hist_pool, convw, dt, a_, nw, S_pool, *curp, NS, parent, y, nk, nv, T, eps, sm);
+    gdn_body(qkvz, stride, ab, ldab, hist_pool, convw, dt, a_, nw, S_pool, (*curp + cur_off) % NS, NS, parent, y, nk, nv, T, eps, sm, last_only != 0);
 }
 
 // Batched lanes: blockIdx.y = lane j, the rows [lane_row0[j], lane_row0[j + 1]) of sequence lane_seq[j], a chain from
@@ -241,10 +243,29 @@ extern "C" int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int lda
     const size_t smem = gdn_smem_bytes(T);
     if (int rc = set_smem_limit((const void*) k_gdn_core, 96 * 1024)) return rc;
     {
-        const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), smem, as_stream(st), qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps);
+        const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), smem, as_stream(st), qkvz, ldx, ab, ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, parent, y, nk, nv, T, eps, 0, 0);
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_gdn_core");
+    return FNX_OK;
+}
+
+extern "C" int fnx_gdn_prompt(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt, const float* a,
+                              const float* nw, float* S_pool, const int* cur, int NS, float* y, int nk, int nv, int hs, int T, float eps, fnx_stream st) {
+    FNX_REQUIRE(qkvz && ab && hist_pool && convw && dt && a && nw && S_pool && cur && y, "fnx_gdn_prompt: null pointer");
+    FNX_REQUIRE(hs == GDN_HS, "fnx_gdn_prompt: head dim %d (this build: %d)", hs, GDN_HS);
+    FNX_REQUIRE(T >= 1 && NS >= 2, "fnx_gdn_prompt: %d rows, %d state slots", T, NS);
+    FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_prompt: %d key heads, %d value heads", nk, nv);
+    if (int rc = set_smem_limit((const void*) k_gdn_core, 96 * 1024)) return rc;
+    // windows of up to min(FNX_MAX_ROWS, NS - 1) rows, each starting from the slot the one before left its last row in
+    const int W = NS - 1 < FNX_MAX_ROWS ? NS - 1 : FNX_MAX_ROWS;
+    for (int t0 = 0; t0 < T; t0 += W) {
+        const int nt = T - t0 < W ? T - t0 : W;
+        const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), gdn_smem_bytes(nt), as_stream(st), qkvz + (size_t) t0 * ldx, ldx, ab + (size_t) t0 * ldab,
+                                         ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, (const int*) nullptr, y + (size_t) t0 * nv * GDN_HS, nk, nv, nt, eps, t0 % NS, 1);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core (prompt): launch failed: %s", cudaGetErrorString(le_));
+    }
+    FNX_LAUNCH_OK("fnx_gdn_prompt");
     return FNX_OK;
 }
 

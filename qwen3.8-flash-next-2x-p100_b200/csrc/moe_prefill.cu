@@ -163,6 +163,8 @@ struct PfParams {
     float* out;                // down: [pairs][rows] f32
     __half* outh;              // gate|up: [pairs][rows] f16 (the down product's operand)
     unsigned* err;
+    int ldo;                   // MODE 0: floats between output rows (0: rows)
+    int accumulate;            // MODE 0: out += the product
 };
 
 // MODE 0: out = x W^T (down).  MODE 1: out = silu(x Wg^T) * (x Wu^T) (gate|up; W = [gate (rows); up (rows)]).
@@ -240,7 +242,12 @@ __global__ void __launch_bounds__(PF_BLOCK, 1) k_pf_gemm(const PfParams p) {
         const int sel = warp >> 3;
         const int trow = (MODE == 1 && sel ? p.rows / 16 : 0) + ft * (PF_M / 16) + (warp & 7);
         const int a_off = MODE == 1 && sel ? PF_TILE_A : 0, row0 = (warp & 7) * 16;
-        auto load_raw = [&](int kb, PfRaw& r) { pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r); };
+        // (a slab past the matrix's last tile row, when the features are not a multiple of 128, decodes zero weights)
+        const bool live_row = MODE == 1 || trow < p.rows / 16;
+        auto load_raw = [&](int kb, PfRaw& r) {
+            if (live_row) pf_load_raw(W + ((size_t) trow * KB + kb) * TILE_BYTES, lane, r);
+            else r = PfRaw{};
+        };
         load_raw(0, raw);
         // the activations of chunk c into its stage: 16-byte pieces (8 columns of one row = one core-matrix row) by async copies;
         // they run one chunk ahead of the decode, so their latency hides behind it
@@ -323,11 +330,15 @@ __global__ void __launch_bounds__(PF_BLOCK, 1) k_pf_gemm(const PfParams p) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
             }
+            const int ldo = MODE == 0 && p.ldo ? p.ldo : p.rows;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                if (col0 + i < job.n) {
+                if (col0 + i < job.n && f < p.rows) {
                     if (MODE == 1) p.outh[(size_t) out_s[col0 + i] * p.rows + f] = __float2half_rn(g[i]);
-                    else p.out[(size_t) out_s[col0 + i] * p.rows + f] = g[i];
+                    else {
+                        float* o = p.out + (size_t) out_s[col0 + i] * ldo + f;
+                        *o = p.accumulate ? *o + g[i] : g[i];
+                    }
                 }
         }
     }
@@ -503,6 +514,14 @@ __global__ void k_pf_combine(const float* __restrict__ part, const int* __restri
     *o = s;
 }
 
+// the job list of a dense product over T rows: job j = rows [256 j, 256 j + 256) of "expert" 0, entries in row order
+__global__ void k_pf_dense_jobs(int T, PfJob* __restrict__ jobs, int* __restrict__ njobs, int* __restrict__ order) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, nj = (T + PF_N - 1) / PF_N;
+    if (i < T) order[i] = i;
+    if (i < nj) jobs[i] = PfJob{0, min(PF_N, T - i * PF_N), i * PF_N};
+    if (i == 0) *njobs = nj;
+}
+
 constexpr size_t pf_smem(int mode) { return (size_t) PF_STAGES * ((mode == 1 ? 2 : 1) * PF_TILE_A + PF_TILE_B) + 2048 * PF_REP + 2 * PF_N * sizeof(int) + 64; }
 
 }  // namespace fnxb
@@ -568,5 +587,35 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     }
     k_pf_combine<<<dim3((H / 4 + 255) / 256, T), 256, 0, st>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
     FNX_LAUNCH_OK("k_pf_combine");
+    return FNX_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ dense product for prompts
+extern "C" size_t fnx_dense_prompt_scratch_bytes(int T, int cols) {
+    return pf_align((size_t) T * cols * sizeof(__half)) + pf_align((size_t) T * sizeof(int)) + pf_align(((size_t) T / PF_N + 2) * sizeof(PfJob)) + 256;
+}
+
+extern "C" int fnx_dense_prompt(const void* W, int rows, int cols, const float* x, int T, const float* norm_w, float eps, float* y, int ldy, int accumulate,
+                                void* scratch, unsigned* err, fnx_stream st_) {
+    FNX_REQUIRE(W && x && y && scratch && err, "fnx_dense_prompt: null pointer");
+    FNX_REQUIRE(T >= 1 && rows >= 16 && rows % 16 == 0 && cols >= 256 && cols % 256 == 0 && ldy >= rows, "fnx_dense_prompt: %d rows x %d columns over %d rows", rows, cols, T);
+    cudaStream_t st = as_stream(st_);
+    uint8_t* b = (uint8_t*) scratch;
+    __half* xh = (__half*) b; b += pf_align((size_t) T * cols * sizeof(__half));
+    int* order = (int*) b; b += pf_align((size_t) T * sizeof(int));
+    PfJob* jobs = (PfJob*) b; b += pf_align(((size_t) T / PF_N + 2) * sizeof(PfJob));
+    int* njobs = (int*) b;
+    const int nj = (T + PF_N - 1) / PF_N;
+    k_pf_dense_jobs<<<(T + 255) / 256, 256, 0, st>>>(T, jobs, njobs, order);
+    FNX_LAUNCH_OK("k_pf_dense_jobs");
+    k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, cols, eps, xh);
+    FNX_LAUNCH_OK("k_pf_xnorm");
+    if (int rc = set_smem_limit((const void*) k_pf_gemm<0>, (int) pf_smem(0))) return rc;
+    PfParams p{};
+    p.W = (const uint8_t*) W; p.expert_stride = 0; p.e_base = 0; p.E = 1; p.Wsh = nullptr;
+    p.jobs = jobs; p.njobs = njobs; p.order = order; p.TKp = T; p.Kp = 1; p.x = xh; p.rows = rows; p.K = cols; p.out = y; p.outh = nullptr; p.err = err;
+    p.ldo = ldy; p.accumulate = accumulate;
+    k_pf_gemm<0><<<dim3(nj, (rows + PF_M - 1) / PF_M), PF_BLOCK, pf_smem(0), st>>>(p);
+    FNX_LAUNCH_OK("k_pf_gemm (dense)");
     return FNX_OK;
 }

@@ -118,6 +118,39 @@ def test_drafts_over_a_draft_vocabulary_match_oracle(F, O):
         eng.close()
 
 
+def test_prompt_pass_matches_the_window_path_and_the_oracle(F, O, model):
+    """A 75-token prompt through fnx_engine_prompt (tensor-core projections and experts, chained DeltaNet windows): positions,
+    context and emitted token equal the window path's (itself checked against the oracle above), the following window agrees
+    with it to the parity tolerance (activations are f16 in the prompt pass), and drafts and lookup still work."""
+    cfg, eng, om = model
+    rng = np.random.default_rng(11)
+    prompt = rng.integers(0, cfg.vocab, size=75).tolist()
+    eng.reset()
+    eng.prefill(prompt)
+    pos_w = eng.pos()
+    toks = rng.integers(0, cfg.vocab, size=5).tolist()
+    want = eng.verify(toks)
+    R_w = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:5].copy()
+    lg_w = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5].copy()
+    ctx_w = eng.tensor("seq.ctx", torch.int32).cpu().numpy()[:pos_w + 1].copy()
+    eng.reset()
+    eng.prompt(prompt)
+    assert eng.pos() == pos_w == 75 and eng.error_bits() == 0
+    assert np.array_equal(eng.tensor("seq.ctx", torch.int32).cpu().numpy()[:pos_w], ctx_w[:pos_w])
+    got = eng.verify(toks)
+    R_p = eng.tensor("buf.R", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.hidden)[:5]
+    lg_p = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5]
+    assert rel_err(R_p, R_w) < 5e-3 and rel_err(lg_p, lg_w) < 5e-3
+    assert got[0] >= 1 and len(got[1]) == got[0]
+    eng.commit(got[1])
+    assert len(eng.draft(2)) == 2
+    # a prompt of one token, and one that ends exactly on a window boundary
+    for n in (1, 2 * cfg.max_rows + 1):
+        eng.reset()
+        eng.prompt(prompt[:n])
+        assert eng.pos() == n and eng.error_bits() == 0
+
+
 def test_full_size_layers_match_oracle(F, O):
     """The benchmark model's own dimensions (hidden 2048, 512 experts top-10 of width 512, 16/2 attention heads of 256, 16/32
     DeltaNet heads of 128, vocabulary 151,936), four layers of it (three DeltaNet, one attention): a prompt, a 5-row chain window

@@ -90,6 +90,28 @@ def test_dense_zero_and_huge_inputs(F, O):
     assert rel_err(y.cpu().numpy(), ref) < TOL_GEMV
 
 
+@pytest.mark.parametrize("rows,cols,T", [(256, 2048, 300), (208, 1024, 70), (2048, 4096, 513)])
+def test_dense_prompt_matches_the_decode_product(F, rows, cols, T):
+    """The prompt-sized projection (tensor cores, f16 activations) against the decode kernel's product of the same rows: same
+    weights, activations rounded to f16 instead of two int8 levels; with the norm, into a strided output, accumulating; a
+    feature count that is not a multiple of the 128-feature slab (208)."""
+    import torch
+    Wt, _ = gpu_iq3s_matrix(F, rows, cols, 3, 77)
+    rng = np.random.default_rng(T)
+    x = dev(rng.standard_normal((T, cols)).astype(np.float32))
+    nw = dev((1.0 + 0.05 * rng.standard_normal(cols)).astype(np.float32))
+    want, _ = F.dense(Wt, rows, cols, x, norm_w=nw)
+    got, err = F.dense_prompt(Wt, rows, cols, x, norm_w=nw)
+    assert int(err.item()) == 0
+    assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 2e-3
+    base = dev(rng.standard_normal((T, rows + 16)).astype(np.float32))
+    acc = base.clone()
+    F.dense_prompt(Wt, rows, cols, x, out=acc[:, :rows], accumulate=True)
+    plain, _ = F.dense(Wt, rows, cols, x)
+    assert rel_err((acc[:, :rows] - base[:, :rows]).cpu().numpy(), plain.cpu().numpy()) < 2e-3
+    assert torch.equal(acc[:, rows:], base[:, rows:])
+
+
 def test_dense_rejects_bad_shapes(F):
     tiles = torch.zeros(F.iq3s_bytes(64, 2048), dtype=torch.uint8, device="cuda")
     x = torch.zeros((1, 2048), device="cuda")
