@@ -94,6 +94,10 @@ typedef struct {
 int fnx_router_route(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K,
                      int e_lo, int e_hi, int add_shared, float* logits, int* topi, float* topw, fnx_job* jobs,
                      int* njobs, unsigned long long* stats, unsigned* err, fnx_stream st);
+/* the routing of any number of rows, for prompts (the prompt pass's router, engine/src/prefill.cu): logits, top K and weights
+ * as fnx_router_route computes them, without a job list (fnx_moe_prefill groups the pairs itself) */
+int fnx_router_rows(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K, float* logits,
+                    int* topi, float* topw, unsigned* err, fnx_stream st);
 /* moe_gate_up + SwiGLU (engine/src/kernels.hpp:319, :329; engine/src/moe.cuh:572-608): h[out][F] =
  * silu(Wg . xin) * (Wu . xin).  Wgu: expert e's [gate (F); up (F)] x H tile matrix at Wgu + (e - e_base) *
  * expert_stride; the shared expert (w == E) is read from Wsh. */
@@ -147,6 +151,13 @@ int fnx_attn_prep_append(float* qg, int ldq, float* k, int ldk, const float* v, 
 size_t fnx_attn_scratch_bytes(int T, int nq, int hd);
 int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
              const int* pos0, const int* parent, void* scratch, fnx_stream st);
+/* the same for a prompt's rows (attn_prompt, engine/src/kernels.hpp:252): T rows of any number, a chain (row t sees every
+ * position up to pos0 + t), twelve rows per block over all the positions they see, no splits; the scores come from the f16-rounded
+ * queries alone (the window form adds their low halves).  fnx_attn_prep_append takes such T when depth is null.
+ * scratch: fnx_attn_prompt_scratch_bytes(T, nq, hd) bytes. */
+size_t fnx_attn_prompt_scratch_bytes(int T, int nq, int hd);
+int fnx_attn_prompt(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
+                    const int* pos0, void* scratch, fnx_stream st);
 /* fnx_attn without caller scratch and without any allocation (no counterpart in the reference, whose attn takes the
  * caller's buffer, engine/src/kernels.hpp:238): the split partials go to one file-scope device array of
  * FNX_ATTN_STATIC_MAX_SLOTS x (hd floats + 8 bytes) = 16.9 MB per device, for callers that may not allocate (a
@@ -188,12 +199,15 @@ int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int ldab, float* h
 /* Batched lanes of gdn_core (gdn_core_segs, engine/src/kernels.cu:2112-2156; GdnLanes, engine/src/kernels.hpp:103-110):
  * lane j is a chain from slot cur[lane_seq[j]] of that sequence's rings at hist_pool + seq * hist_seq_stride floats and
  * S_pool + seq * s_seq_stride floats. */
-/* the same over a prompt's T rows (any T), a chain of which every row is kept (gdn_prompt, engine/src/kernels.cu:2158): windows
- * of min(FNX_MAX_ROWS, NS - 1) rows run back to back, each from the slot the one before left its last row's state in; only
- * that state and history are written.  The final state is in slot (*cur + T) % NS: the caller advances *cur by T. */
+/* the same over a prompt's T rows (any T), a chain of which every row is kept (gdn_prompt, engine/src/kernels.cu:2158), in three
+ * launches: conv + SiLU, q / k norms and gates of every row at once; the delta rule with the state in registers from the
+ * first row to the last; the gated norm of every row at once.  Starts from state slot `cur` (a host value here) and leaves the
+ * last row's state and conv history in slot (cur + T) % NS: the caller advances its slot index by T.
+ * scratch: fnx_gdn_prompt_scratch_bytes(T, nk, nv, hs) bytes. */
+size_t fnx_gdn_prompt_scratch_bytes(int T, int nk, int nv, int hs);
 int fnx_gdn_prompt(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt,
-                   const float* a, const float* nw, float* S_pool, const int* cur, int NS, float* y, int nk, int nv, int hs,
-                   int T, float eps, fnx_stream st);
+                   const float* a, const float* nw, float* S_pool, int cur, int NS, float* y, int nk, int nv, int hs, int T,
+                   float eps, void* scratch, fnx_stream st);
 int fnx_gdn_core_lanes(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, size_t hist_seq_stride,
                        const float* convw, const float* dt, const float* a, const float* nw, float* S_pool,
                        size_t s_seq_stride, const int* cur, int NS, const int* lane_seq, const int* lane_row0, int n_lanes,

@@ -62,6 +62,7 @@ _PROTOS = {
     "fnx_debug_profile_buffer": (_I, [_P]),
     "fnx_dense": (_I, [_P, _I, _I, _P, _I, _I, _P, _F, _P, _I, _I, _P, _P]),
     "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "fnx_router_rows": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
     "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
@@ -76,9 +77,12 @@ _PROTOS = {
     "fnx_attn_prep_append": (_I, [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P]),
     "fnx_attn_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "fnx_attn_prompt_scratch_bytes": (_Z, [_I, _I, _I]),
+    "fnx_attn_prompt": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "fnx_attn_static_setup": (_I, []),
     "fnx_attn_static": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
-    "fnx_gdn_prompt": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _P]),
+    "fnx_gdn_prompt_scratch_bytes": (_Z, [_I, _I, _I, _I]),
+    "fnx_gdn_prompt": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _P, _P]),
     "fnx_gdn_core": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _P]),
     "fnx_argmax": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "fnx_top_tokens": (_I, [_P, _I, _I, _P, _P, _P]),
@@ -301,6 +305,19 @@ def dense_image(W, rows: int, cols: int, img, T: int, normed: bool = True, eps: 
     return y
 
 
+def router_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
+    """The prompt pass's router over any number of rows in one call: (topi, topw, logits)."""
+    import torch
+    T, H = x.shape
+    E = Wr.shape[0] - 1
+    logits = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
+    topi = torch.empty((T, K), dtype=torch.int32, device=x.device)
+    topw = torch.empty((T, K), dtype=torch.float32, device=x.device)
+    err = new_err(x.device)
+    check(lib().fnx_router_rows(ptr(Wr), ptr(x), ptr(norm_w), eps, T, E, H, K, ptr(logits), ptr(topi), ptr(topw), ptr(err), _stream()))
+    return topi, topw, logits
+
+
 def route_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
     """Routing of any number of rows (windows of MAX_ROWS through fnx_router_route): (topi, topw, logits)."""
     import torch
@@ -348,6 +365,18 @@ def attn(qg, kc, vc, pos0, parent=None, scratch=None):
     return out
 
 
+def attn_prompt(qg, kc, vc, pos0):
+    """Attention of a prompt's rows (a chain of any length) over the cache: fnx_attn_prompt."""
+    import torch
+    T, nq, hd2 = qg.shape
+    nkv, hd = kc.shape[1], kc.shape[2]
+    out = torch.empty((T, nq, hd), dtype=torch.float32, device=qg.device)
+    L = lib()
+    scratch = torch.empty(L.fnx_attn_prompt_scratch_bytes(T, nq, hd), dtype=torch.uint8, device=qg.device)
+    check(L.fnx_attn_prompt(ptr(qg), nq * hd2, ptr(kc), ptr(vc), ptr(out), T, nq, nkv, hd, ptr(pos0), ptr(scratch), _stream()))
+    return out
+
+
 def attn_static(qg, kc, vc, pos0, parent=None):
     """fnx_attn_static: attention whose split partials live in the library's built-in device array (nothing is allocated
     by the library; `out` is the caller's)."""
@@ -365,6 +394,19 @@ def gdn_core(qkvz, ab, hist_pool, convw, dt, a, nw, S_pool, cur, parent, nk: int
     y = torch.empty((T, nv * hs), dtype=torch.float32, device=qkvz.device)
     check(lib().fnx_gdn_core(ptr(qkvz), qkvz.stride(0), ptr(ab), ab.stride(0), ptr(hist_pool), ptr(convw), ptr(dt), ptr(a), ptr(nw), ptr(S_pool),
                              ptr(cur), S_pool.shape[0], ptr(parent), ptr(y), nk, nv, hs, T, eps, _stream()))
+    return y
+
+
+def gdn_prompt(qkvz, ab, hist_pool, convw, dt, a, nw, S_pool, cur: int, nk: int, nv: int, hs: int = 128, eps: float = 1e-6):
+    """The DeltaNet core over a prompt's rows (any number, a chain, every row kept) from state slot `cur`; the last row's
+    state and history land in slot (cur + T) % NS."""
+    import torch
+    T = qkvz.shape[0]
+    y = torch.empty((T, nv * hs), dtype=torch.float32, device=qkvz.device)
+    L = lib()
+    scratch = torch.empty(L.fnx_gdn_prompt_scratch_bytes(T, nk, nv, hs), dtype=torch.uint8, device=qkvz.device)
+    check(L.fnx_gdn_prompt(ptr(qkvz), qkvz.stride(0), ptr(ab), ab.stride(0), ptr(hist_pool), ptr(convw), ptr(dt), ptr(a), ptr(nw), ptr(S_pool), cur,
+                           S_pool.shape[0], ptr(y), nk, nv, hs, T, eps, ptr(scratch), _stream()))
     return y
 
 

@@ -76,6 +76,16 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part_lanes(const float* __
                    mz_out + (size_t) row0 * nq * S, T, nq, nkv, pos[seq], nullptr, (int) blockIdx.x, S, (int) blockIdx.y, 0, (int) threadIdx.x, smem, SyncBlock());
 }
 
+// the prompt form: grid (1, KV heads, groups of ATP_ROWS rows); every block runs over all the positions its rows see, so there is
+// one partial per (row, head) and the combine only normalises and gates it
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_part_prompt(const float* __restrict__ qg, int ldq, const __half* __restrict__ kc,
+                                                                  const __half* __restrict__ vc, float* __restrict__ acc_out,
+                                                                  AttPartial* __restrict__ mz_out, int T, int nq, int nkv, const int* __restrict__ pos0p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    attn_part_body_t<ATP_ROWS, ATP_MQ, false, true>(qg, ldq, kc, vc, acc_out, mz_out, T, nq, nkv, *pos0p, nullptr, 0, 1, (int) blockIdx.y,
+                                                    (int) blockIdx.z * ATP_ROWS, (int) threadIdx.x, smem, SyncBlock());
+}
+
 static int attn_splits(int nkv) {
     const int s = sm_count() / (nkv > 0 ? nkv : 1);
     return s < 1 ? 1 : s;
@@ -89,7 +99,7 @@ extern "C" int fnx_attn_prep_append(float* qg, int ldq, float* k, int ldk, const
                                     void* kc, void* vc, int T, int nq, int nkv, int hd, int nrot, const int* pos0, const int* depth, float eps,
                                     float rope_base, fnx_stream st) {
     FNX_REQUIRE(qg && k && v && q_norm && k_norm && kc && vc && pos0, "fnx_attn_prep_append: null pointer");
-    FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS, "fnx_attn_prep_append: %d rows", T);
+    FNX_REQUIRE(T >= 1 && (depth ? T <= FNX_MAX_ROWS : T <= 65535), "fnx_attn_prep_append: %d rows", T);
     FNX_REQUIRE(hd % 32 == 0 && hd <= 1024 && nrot <= hd && nrot % 2 == 0, "fnx_attn_prep_append: head dim %d, rotary %d", hd, nrot);
     {
         const cudaError_t le_ = launch_k(k_attn_prep_append, dim3(dim3(nq + 2 * nkv, T)), dim3(hd), hd * sizeof(float), as_stream(st), qg, ldq, k, ldk, v, ldv, q_norm, k_norm, (__half*) kc, (__half*) vc,
@@ -128,6 +138,25 @@ extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_attn_combine: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_attn (combine)");
+    return FNX_OK;
+}
+
+extern "C" size_t fnx_attn_prompt_scratch_bytes(int T, int nq, int hd) { return (size_t) T * nq * ((size_t) hd * sizeof(float) + sizeof(AttPartial)); }
+
+extern "C" int fnx_attn_prompt(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd, const int* pos0,
+                               void* scratch, fnx_stream st) {
+    FNX_REQUIRE(qg && kc && vc && out && pos0 && scratch, "fnx_attn_prompt: null pointer");
+    FNX_REQUIRE(T >= 1 && T <= 65535, "fnx_attn_prompt: %d rows", T);
+    FNX_REQUIRE(hd == ATT_THREADS, "fnx_attn_prompt: head dim %d (this build: %d)", hd, ATT_THREADS);
+    FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQ, "fnx_attn_prompt: %d q heads over %d KV heads", nq, nkv);
+    float* acc = (float*) scratch;
+    AttPartial* mz = (AttPartial*) (acc + (size_t) T * nq * hd);
+    if (int rc = set_smem_limit((const void*) k_attn_part_prompt, (int) attn_prompt_smem())) return rc;
+    k_attn_part_prompt<<<dim3(1, nkv, (T + ATP_ROWS - 1) / ATP_ROWS), ATT_THREADS, attn_prompt_smem(), as_stream(st)>>>(qg, ldq, (const __half*) kc, (const __half*) vc, acc, mz,
+                                                                                                                     T, nq, nkv, pos0);
+    FNX_LAUNCH_OK("fnx_attn_prompt (partials)");
+    k_attn_combine<<<dim3(nq, T), hd * ATC_G, 0, as_stream(st)>>>(acc, mz, qg, ldq, out, nq, hd, 1);
+    FNX_LAUNCH_OK("fnx_attn_prompt (combine)");
     return FNX_OK;
 }
 

@@ -66,10 +66,16 @@ constexpr int ATT_QS = ATT_HD + 8;    // row strides (halves) of the Q, K, V til
 constexpr int ATT_SS = ATT_SC + 4;    // score rows (floats)
 constexpr int ATT_PS = ATT_SC + 8;    // probability rows (halves)
 
-constexpr size_t attn_part_smem() {
-    return (size_t) (2 * ATT_MQ + 4 * ATT_SC) * ATT_QS * sizeof(__half) + (size_t) ATT_MQ * ATT_SS * sizeof(float) +
-           (size_t) ATT_MQ * ATT_PS * sizeof(__half) + 3 * ATT_MQ * sizeof(float) + ATT_ROWS * sizeof(unsigned);
+// shared memory of a block that serves `rows` window rows (mq = their queries padded to 16-row MMA tiles; qlo: the queries' low
+// halves are kept too)
+constexpr size_t attn_part_smem_of(int rows, int mq, bool qlo) {
+    return (size_t) ((qlo ? 2 : 1) * mq + 4 * ATT_SC) * ATT_QS * sizeof(__half) + (size_t) mq * ATT_SS * sizeof(float) +
+           (size_t) mq * ATT_PS * sizeof(__half) + 3 * mq * sizeof(float) + rows * sizeof(unsigned);
 }
+constexpr size_t attn_part_smem() { return attn_part_smem_of(ATT_ROWS, ATT_MQ, true); }
+// the prompt form: twelve rows per block (96 queries), f16 queries, rows a chain of any length
+constexpr int ATP_ROWS = 12, ATP_MQ = 96;
+constexpr size_t attn_prompt_smem() { return attn_part_smem_of(ATP_ROWS, ATP_MQ, false); }
 
 struct AttPartial {   // one (row, head, split)
     float m, z;
@@ -97,16 +103,20 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 //   sums   += weights V, accumulated in f32 registers across the steps of 64 positions.
 // scratch: acc [T][nq][S][hd] floats, then mz [T][nq][S]
 // (tid: the thread among the item's ATT_THREADS; smem: attn_part_smem() bytes, 16-byte aligned; sync(): their barrier)
-template <typename Sync>
-__device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const __half* kc, const __half* vc, float* acc_out, AttPartial* mz_out, int T,
-                                               int nq, int nkv, int pos0, const int* parent, int s, int S, int kvh, int r0, int tid, uint8_t* smem,
-                                               Sync sync) {
+// ROWS / MQ: window rows per block and their queries padded to 16-row tiles.  QLO: scores from both f16 halves of the queries
+// (the window path); without it from the rounded queries alone (the prompt pass, whose activations are f16 anyway).  CHAIN: the
+// rows are a chain of any length (row r sees every position up to its own), no ancestor bitmaps.
+template <int ROWS, int MQ, bool QLO, bool CHAIN, typename Sync>
+__device__ __forceinline__ void attn_part_body_t(const float* qg, int ldq, const __half* kc, const __half* vc, float* acc_out, AttPartial* mz_out, int T,
+                                                 int nq, int nkv, int pos0, const int* parent, int s, int S, int kvh, int r0, int tid, uint8_t* smem,
+                                                 Sync sync) {
+    constexpr int ATT_MQ = MQ, ATT_ROWS = ROWS, MT = MQ / 16;   // (shadow the window form's constants)
     const int nr = min(ATT_ROWS, T - r0), qpk = nq / nkv, NQ = nr * qpk;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
-    const int ctx = pos0 + T;
+    const int ctx = CHAIN ? pos0 + r0 + nr : pos0 + T;      // a chain's rows see nothing past the block's last row
     __half* Qh = reinterpret_cast<__half*>(smem);           // [ATT_MQ][ATT_QS]
     __half* Ql = Qh + ATT_MQ * ATT_QS;
-    __half* Ks = Ql + ATT_MQ * ATT_QS;                      // two buffers of [K: ATT_SC][ATT_QS], [V: ATT_SC][ATT_QS]
+    __half* Ks = Qh + (QLO ? 2 : 1) * ATT_MQ * ATT_QS;      // two buffers of [K: ATT_SC][ATT_QS], [V: ATT_SC][ATT_QS]
     __half* Vs = Ks + ATT_SC * ATT_QS;
     constexpr int KVB = 2 * ATT_SC * ATT_QS;                // halves per buffer: the next step's rows land while this step is used
     float* Sf = reinterpret_cast<float*>(Ks + 2 * KVB);     // [ATT_MQ][ATT_SS]
@@ -170,19 +180,20 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
             }
             *reinterpret_cast<uint2*>(Qh + qi * ATT_QS + d4 * 4) = make_uint2((uint32_t) __half_as_ushort(h[0]) | ((uint32_t) __half_as_ushort(h[1]) << 16),
                                                                                 (uint32_t) __half_as_ushort(h[2]) | ((uint32_t) __half_as_ushort(h[3]) << 16));
-            *reinterpret_cast<uint2*>(Ql + qi * ATT_QS + d4 * 4) = make_uint2((uint32_t) __half_as_ushort(l[0]) | ((uint32_t) __half_as_ushort(l[1]) << 16),
+            if (QLO)
+                *reinterpret_cast<uint2*>(Ql + qi * ATT_QS + d4 * 4) = make_uint2((uint32_t) __half_as_ushort(l[0]) | ((uint32_t) __half_as_ushort(l[1]) << 16),
                                                                                 (uint32_t) __half_as_ushort(l[2]) | ((uint32_t) __half_as_ushort(l[3]) << 16));
         }
     }
     if (tid < ATT_MQ) { ms[tid] = -INFINITY; zs[tid] = 0.f; fs[tid] = 0.f; }
-    if (tid < nr) {
+    if (!CHAIN && tid < nr) {
         unsigned m = 0;
         for (int a = r0 + tid; a >= 0; a = parent ? parent[a] : a - 1) m |= 1u << a;
         see[tid] = m;
     }
-    float acc[3][4][4];   // [query tile][8-dim tile of the warp's 32 dims][c]
+    float acc[MT][4][4];   // [query tile][8-dim tile of the warp's 32 dims][c]
 #pragma unroll
-    for (int m = 0; m < 3; ++m)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
         for (int n = 0; n < 4; ++n)
 #pragma unroll
@@ -206,9 +217,9 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         const uint32_t ks_s = ks0_s + (uint32_t) (buf * KVB * 2), vs_s = vs0_s + (uint32_t) (buf * KVB * 2);
         // ---- scores: warp w = positions [8 w, 8 w + 8) of the step, all 48 query rows
         {
-            float c[3][4];
+            float c[MT][4];
 #pragma unroll
-            for (int m = 0; m < 3; ++m)
+            for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) c[m][k] = 0.f;
 #pragma unroll 4
@@ -216,22 +227,26 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
                 uint32_t b0, b1, b2, b3;   // (b0, b1): dims k0 .. k0 + 15, (b2, b3): k0 + 16 .. k0 + 31
                 ldsm_x4(ks_s + bk_off + k0 * 2, b0, b1, b2, b3);
 #pragma unroll
-                for (int m = 0; m < 3; ++m) {
+                for (int m = 0; m < MT; ++m) {
                     uint32_t a0, a1, a2, a3;
                     const uint32_t ao = a_off + (uint32_t) (m * 16 * ATT_QS + k0) * 2u;
                     ldsm_x4(qh_s + ao, a0, a1, a2, a3);
                     mma_f16(c[m], a0, a1, a2, a3, b0, b1);
-                    ldsm_x4(ql_s + ao, a0, a1, a2, a3);
-                    mma_f16(c[m], a0, a1, a2, a3, b0, b1);
+                    if (QLO) {
+                        ldsm_x4(ql_s + ao, a0, a1, a2, a3);
+                        mma_f16(c[m], a0, a1, a2, a3, b0, b1);
+                    }
                     ldsm_x4(qh_s + ao + 32, a0, a1, a2, a3);
                     mma_f16(c[m], a0, a1, a2, a3, b2, b3);
-                    ldsm_x4(ql_s + ao + 32, a0, a1, a2, a3);
-                    mma_f16(c[m], a0, a1, a2, a3, b2, b3);
+                    if (QLO) {
+                        ldsm_x4(ql_s + ao + 32, a0, a1, a2, a3);
+                        mma_f16(c[m], a0, a1, a2, a3, b2, b3);
+                    }
                 }
             }
             // scaled and masked into the score tile: row = query, column = position of the step
 #pragma unroll
-            for (int m = 0; m < 3; ++m)
+            for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
                     const int qi = m * 16 + g + 8 * hrow;
@@ -241,7 +256,8 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
                     for (int k = 0; k < 2; ++k) {
                         const int col = warp * 8 + 2 * q + k, p = p0 + col;
                         bool vis = qi < NQ && col < np;
-                        if (vis && p >= pos0) vis = (see[qi / qpk] >> (p - pos0)) & 1u;
+                        if (CHAIN) vis = vis && p <= pos0 + r0 + qi / qpk;
+                        else if (vis && p >= pos0) vis = (see[qi / qpk] >> (p - pos0)) & 1u;
                         ov[k] = vis ? c[m][2 * hrow + k] * scale : -INFINITY;
                     }
                     *reinterpret_cast<float2*>(Sf + qi * ATT_SS + warp * 8 + 2 * q) = o;
@@ -263,7 +279,7 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         sync();
         // ---- sums: warp w = dims [32 w, 32 w + 32), all 48 query rows
 #pragma unroll
-        for (int m = 0; m < 3; ++m) {
+        for (int m = 0; m < MT; ++m) {
             const float fa = fs[m * 16 + g], fb = fs[m * 16 + g + 8];
 #pragma unroll
             for (int n = 0; n < 4; ++n) {
@@ -273,15 +289,15 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         }
 #pragma unroll
         for (int k0 = 0; k0 < ATT_SC; k0 += 16) {
-            uint32_t a[3][4];
+            uint32_t a[MT][4];
 #pragma unroll
-            for (int m = 0; m < 3; ++m) ldsm_x4(pp_s + ap_off + (uint32_t) (m * 16 * ATT_PS + k0) * 2u, a[m][0], a[m][1], a[m][2], a[m][3]);
+            for (int m = 0; m < MT; ++m) ldsm_x4(pp_s + ap_off + (uint32_t) (m * 16 * ATT_PS + k0) * 2u, a[m][0], a[m][1], a[m][2], a[m][3]);
 #pragma unroll
             for (int n2 = 0; n2 < 2; ++n2) {
                 uint32_t b0, b1, b2, b3;   // (b0, b1): dims 16 n2 .. + 7, (b2, b3): + 8 .. + 15
                 ldsm_x4_t(vs_s + bv_off + (uint32_t) (k0 * ATT_QS + n2 * 16) * 2u, b0, b1, b2, b3);
 #pragma unroll
-                for (int m = 0; m < 3; ++m) {
+                for (int m = 0; m < MT; ++m) {
                     mma_f16(acc[m][2 * n2], a[m][0], a[m][1], a[m][2], a[m][3], b0, b1);
                     mma_f16(acc[m][2 * n2 + 1], a[m][0], a[m][1], a[m][2], a[m][3], b2, b3);
                 }
@@ -289,7 +305,7 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         }
     }
 #pragma unroll
-    for (int m = 0; m < 3; ++m)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
             const int qi = m * 16 + g + 8 * hrow;
@@ -305,6 +321,14 @@ __device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const _
         const int r = tid / qpk, hh = tid % qpk;
         mz_out[((size_t) (r0 + r) * nq + kvh * qpk + hh) * S + s] = AttPartial{ms[tid], zs[tid]};
     }
+}
+
+// the window form: five rows per block, queries in two f16 halves, tree masks
+template <typename Sync>
+__device__ __forceinline__ void attn_part_body(const float* qg, int ldq, const __half* kc, const __half* vc, float* acc_out, AttPartial* mz_out, int T,
+                                               int nq, int nkv, int pos0, const int* parent, int s, int S, int kvh, int r0, int tid, uint8_t* smem,
+                                               Sync sync) {
+    attn_part_body_t<ATT_ROWS, ATT_MQ, true, false>(qg, ldq, kc, vc, acc_out, mz_out, T, nq, nkv, pos0, parent, s, S, kvh, r0, tid, smem, sync);
 }
 
 // merge the splits of (row, head): out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) z_s * sigmoid(gate)

@@ -114,8 +114,8 @@ struct fnx_engine {
     // the prompt pass (fnx_engine_prompt): buffers for a chunk of prompt_chunk rows, made at its first call
     int prompt_chunk = 4096;
     float *pR = nullptr, *pproj = nullptr, *pmix = nullptr, *plogits = nullptr, *ptopw = nullptr;
-    int *ptopi = nullptr, *d_ptok = nullptr, *d_ppos = nullptr;
-    void *p_moe_scratch = nullptr, *p_dense_scratch = nullptr;
+    int *ptopi = nullptr, *d_ptok = nullptr;
+    void *p_moe_scratch = nullptr, *p_dense_scratch = nullptr, *p_gdn_scratch = nullptr, *p_attn_scratch = nullptr;
     // the draft layer's own head over a draft vocabulary (config draft_vocab > 0): dvn rows, row -> token id in d_dvocab;
     // otherwise the main head and no map
     uint8_t* mtp_head = nullptr;
@@ -309,11 +309,7 @@ __global__ void k_commit(__half* const* __restrict__ kcs, __half* const* __restr
     }
 }
 __global__ void k_advance_pos(int* pos, int n) { *pos += n; }
-// the prompt pass: the windows' first positions; the chunk's tokens joining the context; position and state slot afterwards
-__global__ void k_prompt_positions(int* ppos, const int* pos, int W, int nwin) {
-    const int w = blockIdx.x * blockDim.x + threadIdx.x;
-    if (w < nwin) ppos[w] = *pos + w * W;
-}
+// the prompt pass: the chunk's tokens joining the context; position and state slot afterwards
 __global__ void k_prompt_context(int* ctx, const int* ctx_n, const int* tok, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) ctx[*ctx_n + i] = tok[i];
@@ -993,8 +989,8 @@ extern "C" int fnx_engine_lookup(fnx_engine* e, int seq, int lk, int d1, int roo
 
 // Engine::prefill (engine/src/prefill.cu: the prompt pass): the prompt's first n - 1 tokens go through the model a chunk at a time,
 // layer by layer, on the prompt-sized kernels - projections and experts on the tensor cores (fnx_dense_prompt, fnx_moe_prefill),
-// DeltaNet as chained windows that keep only their last state (fnx_gdn_prompt), attention and routing as windows over the
-// chunk's rows - and only caches, states and context are kept; the last token then goes through an ordinary one-row window,
+// DeltaNet as one scan with the state in registers (fnx_gdn_prompt), attention over twelve rows per block (fnx_attn_prompt), the
+// router over all rows at once (fnx_router_rows) - and only caches, states and context are kept; the last token then goes through an ordinary one-row window,
 // which leaves the engine exactly as after a verify + commit (logits, emitted token, the draft layer's source row).
 extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n) {
     FNX_REQUIRE(e && h_tok && seq >= 0 && seq < e->c.n_seq && n >= 1, "fnx_engine_prompt: bad arguments");
@@ -1003,7 +999,7 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
     FNX_REQUIRE(s.pos + n <= e->c.max_ctx, "fnx_engine_prompt: %d tokens run past the context of %d rows", n, e->c.max_ctx);
     for (int t = 0; t < n; ++t) FNX_REQUIRE(h_tok[t] >= 0 && h_tok[t] < e->c.vocab, "fnx_engine_prompt: token %d outside the vocabulary", h_tok[t]);
     const Dims d = dims(e->c);
-    const int CH = e->prompt_chunk, W = d.MAXR, fast = n - 1;
+    const int CH = e->prompt_chunk, fast = n - 1;
     if (fast > 0 && !e->pR) {
         const int mixw = d.nq * d.hd > d.nv * d.hs ? d.nq * d.hd : d.nv * d.hs;
         FNX_TRY(dalloc(e, &e->pR, (size_t) CH * d.H));
@@ -1013,55 +1009,86 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
         FNX_TRY(dalloc(e, &e->ptopw, (size_t) CH * d.K));
         FNX_TRY(dalloc(e, &e->ptopi, (size_t) CH * d.K));
         FNX_TRY(dalloc(e, &e->d_ptok, (size_t) CH));
-        FNX_TRY(dalloc(e, &e->d_ppos, (size_t) (CH + W - 1) / W));
         uint8_t* q = nullptr;
         FNX_TRY(dalloc(e, &q, fnx_moe_prefill_scratch_bytes(CH, d.K, d.E, d.H, d.F)));
         e->p_moe_scratch = q;
         const size_t ds = fnx_dense_prompt_scratch_bytes(CH, mixw > d.H ? mixw : d.H);
         FNX_TRY(dalloc(e, &q, ds));
         e->p_dense_scratch = q;
+        FNX_TRY(dalloc(e, &q, fnx_gdn_prompt_scratch_bytes(CH, d.nk, d.nv, d.hs)));
+        e->p_gdn_scratch = q;
+        FNX_TRY(dalloc(e, &q, fnx_attn_prompt_scratch_bytes(CH, d.nq, d.hd)));
+        e->p_attn_scratch = q;
     }
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     FNX_CUDA_OK(cudaMemsetAsync(e->err, 0, sizeof(unsigned), e->st));
+    // FNX_PROMPT_PHASES=1: the device time of each kind of phase, summed over the prompt, to stderr (a tracing aid)
+    const bool phases = getenv("FNX_PROMPT_PHASES") != nullptr;
+    enum { PH_INPROJ, PH_ATTN, PH_GDN, PH_OUTPROJ, PH_ROUTER, PH_MOE, PH_N };
+    static const char* const ph_name[PH_N] = {"in-proj", "attention", "deltanet", "out-proj", "router", "experts"};
+    std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> marks;
+    auto mark = [&](int ph, bool begin) {
+        if (!phases) return;
+        cudaEvent_t ev;
+        cudaEventCreate(&ev);
+        cudaEventRecord(ev, e->st);
+        if (begin) marks.push_back({ph, {ev, nullptr}});
+        else marks.back().second.second = ev;
+    };
     for (int c0 = 0; c0 < fast; c0 += CH) {
-        const int nt = fast - c0 < CH ? fast - c0 : CH, nwin = (nt + W - 1) / W;
+        const int nt = fast - c0 < CH ? fast - c0 : CH;
         FNX_CUDA_OK(cudaMemcpyAsync(e->d_ptok, h_tok + c0, sizeof(int) * nt, cudaMemcpyHostToDevice, e->st));
-        k_prompt_positions<<<(nwin + 255) / 256, 256, 0, e->st>>>(e->d_ppos, e->d_pos + seq, W, nwin);
-        FNX_LAUNCH_OK("prompt positions");
         FNX_TRY(fnx_embed_rows(e->embed, e->d_ptok, nt, d.H, e->pR, e->st));
         for (size_t l = 0; l < e->layers.size(); ++l) {
             const LayerW& L = e->layers[l];
+            mark(PH_INPROJ, true);
             FNX_TRY(fnx_dense_prompt(L.w_in, L.in_rows, d.H, e->pR, nt, L.norm1, e->c.eps, e->pproj, e->proj_ld, 0, e->p_dense_scratch, e->err, e->st));
+            mark(PH_INPROJ, false);
+            mark(L.attn ? PH_ATTN : PH_GDN, true);
             int mixw_l;
             if (L.attn) {
                 mixw_l = d.nq * d.hd;
                 __half* kc = L.kc + (size_t) seq * e->cache_rows * d.kv_rows;
                 __half* vc = L.vc + (size_t) seq * e->cache_rows * d.kv_rows;
-                for (int w = 0; w < nwin; ++w) {
-                    const int wt = nt - w * W < W ? nt - w * W : W;
-                    float* qg = e->pproj + (size_t) w * W * e->proj_ld;
-                    float* k = qg + d.q_rows;
-                    float* v = k + d.kv_rows;
-                    FNX_TRY(fnx_attn_prep_append(qg, e->proj_ld, k, e->proj_ld, v, e->proj_ld, L.qn, L.kn, kc, vc, wt, d.nq, d.nkv, d.hd, d.nrot, e->d_ppos + w, nullptr,
-                                                 e->c.eps, e->c.rope_base, e->st));
-                    FNX_TRY(fnx_attn(qg, e->proj_ld, kc, vc, e->pmix + (size_t) w * W * mixw_l, wt, d.nq, d.nkv, d.hd, e->d_ppos + w, nullptr, e->att_scratch, e->st));
-                }
+                float* qg = e->pproj;
+                float* k = qg + d.q_rows;
+                float* v = k + d.kv_rows;
+                FNX_TRY(fnx_attn_prep_append(qg, e->proj_ld, k, e->proj_ld, v, e->proj_ld, L.qn, L.kn, kc, vc, nt, d.nq, d.nkv, d.hd, d.nrot, e->d_pos + seq, nullptr,
+                                             e->c.eps, e->c.rope_base, e->st));
+                FNX_TRY(fnx_attn_prompt(qg, e->proj_ld, kc, vc, e->pmix, nt, d.nq, d.nkv, d.hd, e->d_pos + seq, e->p_attn_scratch, e->st));
             } else {
                 mixw_l = d.nv * d.hs;
                 float* S = L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs;
                 float* hist = L.hist_pool + (size_t) seq * e->NS * 3 * d.gdn_ch;
-                FNX_TRY(fnx_gdn_prompt(e->pproj, e->proj_ld, e->pproj + d.gdn_ch + d.nv * d.hs, e->proj_ld, hist, L.convw, L.dt, L.a, L.gnorm, S, e->d_cur + seq, e->NS,
-                                       e->pmix, d.nk, d.nv, d.hs, nt, e->c.eps, e->st));
+                FNX_TRY(fnx_gdn_prompt(e->pproj, e->proj_ld, e->pproj + d.gdn_ch + d.nv * d.hs, e->proj_ld, hist, L.convw, L.dt, L.a, L.gnorm, S, s.cur, e->NS, e->pmix,
+                                       d.nk, d.nv, d.hs, nt, e->c.eps, e->p_gdn_scratch, e->st));
             }
+            mark(0, false);
+            mark(PH_OUTPROJ, true);
             FNX_TRY(fnx_dense_prompt(L.w_out, d.H, mixw_l, e->pmix, nt, nullptr, e->c.eps, e->pR, d.H, 1, e->p_dense_scratch, e->err, e->st));
-            for (int w = 0; w < nwin; ++w) {
-                const int wt = nt - w * W < W ? nt - w * W : W;
-                const size_t r0 = (size_t) w * W;
-                FNX_TRY(fnx_router_route(L.wr, e->pR + r0 * d.H, L.norm2, e->c.eps, wt, d.E, d.H, d.K, 0, d.E, 1, e->plogits + r0 * (d.E + 1), e->ptopi + r0 * d.K,
-                                         e->ptopw + r0 * d.K, e->jobs, e->njobs, nullptr, e->err, e->st));
-            }
+            mark(0, false);
+            mark(PH_ROUTER, true);
+            FNX_TRY(fnx_router_rows(L.wr, e->pR, L.norm2, e->c.eps, nt, d.E, d.H, d.K, e->plogits, e->ptopi, e->ptopw, e->err, e->st));
+            mark(0, false);
+            mark(PH_MOE, true);
             FNX_TRY(fnx_moe_prefill(L.wgu, e->gu_bytes, L.wdn, e->dn_bytes, L.wsh_gu, L.wsh_dn, 0, d.E, d.K, 0, d.E, 1, e->ptopi, e->ptopw, e->plogits, e->pR, L.norm2,
                                     e->c.eps, nt, d.H, d.F, e->pR, 1, e->p_moe_scratch, e->err, e->st));
+            mark(0, false);
+        }
+        if (phases) {
+            FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+            float sum[PH_N] = {0};
+            for (auto& m : marks) {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, m.second.first, m.second.second);
+                sum[m.first] += ms;
+                cudaEventDestroy(m.second.first);
+                cudaEventDestroy(m.second.second);
+            }
+            marks.clear();
+            fprintf(stderr, "prompt chunk at %d (%d rows):", s.pos, nt);
+            for (int i = 0; i < PH_N; ++i) fprintf(stderr, " %s %.1f ms", ph_name[i], sum[i]);
+            fprintf(stderr, "\n");
         }
         k_prompt_context<<<(nt + 255) / 256, 256, 0, e->st>>>(e->d_ctx + (size_t) seq * e->cache_rows, e->d_ctx_n + seq, e->d_ptok, nt);
         FNX_LAUNCH_OK("prompt context");

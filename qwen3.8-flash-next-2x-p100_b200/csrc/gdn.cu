@@ -224,6 +224,162 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
              cur[seq], NS, nullptr, y + (size_t) row0 * nv * GDN_HS, nk, nv, T, eps, sm);
 }
 
+// ------------------------------------------------------------------------------------------------ prompts
+// A prompt's rows are a chain of which every row is kept, so the work splits by what depends on what (gdn_prompt,
+// engine/src/kernels.cu:2158): conv + SiLU, the q / k norms and the gates of every row at once (k_gdn_pre); the delta rule, the
+// only sequential part, with the state in registers from the first row to the last and the rows' q, k, v streamed through
+// shared memory (k_gdn_scan); the gated RMS norm of every row at once (k_gdn_post).  Only the last row's state and the last
+// three rows' conv inputs are written back.
+constexpr int GDP_THREADS = 256;
+
+// block = one row; thread = channels tid, tid + 256, ...  xq / xk [T][nk][HS], xv [T][nv][HS], gates [T][nv][2]
+__global__ void __launch_bounds__(GDP_THREADS) k_gdn_pre(const float* __restrict__ qkvz, int stride, const float* __restrict__ ab, int ldab,
+                                                         const float* __restrict__ hin, float* __restrict__ hout, const float* __restrict__ convw,
+                                                         const float* __restrict__ dt, const float* __restrict__ a_, float* __restrict__ xq,
+                                                         float* __restrict__ xk, float* __restrict__ xv, float* __restrict__ gates, int nk, int nv, int T) {
+    __shared__ float red[GDP_THREADS / 32];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ch = (2 * nk + nv) * GDN_HS;
+    // row t - k of the chain: a row of this call, or the history the call starts from (rows 0..2, oldest first)
+    auto xrow = [&](int r, int c) { return r >= 0 ? qkvz[(size_t) r * stride + c] : hin[(size_t) (3 + r) * ch + c]; };
+    for (int c0 = 0; c0 < ch; c0 += GDP_THREADS) {
+        const int c = c0 + tid;
+        const float4 cw = *reinterpret_cast<const float4*>(convw + (size_t) c * 4);
+        const float x3 = xrow(t - 3, c), x2 = xrow(t - 2, c), x1 = xrow(t - 1, c), x0 = xrow(t, c);
+        const float x = cw.x * x3 + cw.y * x2 + cw.z * x1 + cw.w * x0;
+        float v = x / (1.0f + expf(-x));
+        if (t == T - 1) {   // the history the next call starts from
+            hout[c] = x2;
+            hout[ch + c] = x1;
+            hout[2 * ch + c] = x0;
+        }
+        if (c < 2 * nk * GDN_HS) {
+            // q and k heads: the L2 norm over the head's 128 channels = four warps of this pass (two heads per pass)
+            const float sq = warp_sum(v * v);
+            __syncthreads();
+            if (lane == 0) red[warp] = sq;
+            __syncthreads();
+            const int w0 = warp & ~3;
+            float ssum = 0.f;
+            for (int w = 0; w < 4; ++w) ssum += red[w0 + w];
+            v *= rsqrtf(ssum + 1e-6f);
+            if (c < nk * GDN_HS) xq[(size_t) t * nk * GDN_HS + c] = v;
+            else xk[(size_t) t * nk * GDN_HS + (c - nk * GDN_HS)] = v;
+        } else {
+            xv[(size_t) t * nv * GDN_HS + (c - 2 * nk * GDN_HS)] = v;
+        }
+    }
+    if (tid < nv) {
+        const float* abt = ab + (size_t) t * ldab;
+        const float x = abt[tid] + dt[tid];
+        gates[((size_t) t * nv + tid) * 2] = expf((x > 20.0f ? x : log1pf(expf(x))) * a_[tid]);
+        gates[((size_t) t * nv + tid) * 2 + 1] = 1.0f / (1.0f + expf(-abt[nv + tid]));
+    }
+}
+
+// block = (value head, column quarter) as in the window kernel: warp `part` holds key rows [32 part, +32) of the block's 32 value
+// columns, lane = column.  Rows stream through two shared-memory tiles of GDS_ROWS rows.
+constexpr int GDS_ROWS = 16;
+__global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restrict__ xq, const float* __restrict__ xk, const float* __restrict__ xv,
+                                                          const float* __restrict__ gates, const float* __restrict__ S_in, float* __restrict__ S_out,
+                                                          float* __restrict__ o, int nk, int nv, int T) {
+    constexpr int ROWF = 2 * GDN_HS + GDN_QC + 2;   // floats of a staged row: k, q, the block's v, the two gates
+    __shared__ __align__(16) float tile[2][GDS_ROWS][ROWF + 2];
+    __shared__ float kred[2][4][GDN_QC], ared[GDS_ROWS][4][GDN_QC];
+    const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, kh = lv % nk, tid = threadIdx.x;
+    const int part = tid >> 5, lane = tid & 31, col = qq * GDN_QC + lane;
+    const size_t soff = (size_t) lv * GDN_HS * GDN_HS + (size_t) part * 32 * GDN_HS + col;
+    float s[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) s[r] = S_in[soff + (size_t) r * GDN_HS];
+    auto stage = [&](int buf, int t0) {
+        const int nr = min(GDS_ROWS, T - t0);
+        for (int i = tid; i < nr * (ROWF / 2); i += GDN_THREADS) {   // 8-byte pieces
+            const int r = i / (ROWF / 2), e = (i % (ROWF / 2)) * 2, t = t0 + r;
+            const float* src;
+            if (e < GDN_HS) src = xk + ((size_t) t * nk + kh) * GDN_HS + e;
+            else if (e < 2 * GDN_HS) src = xq + ((size_t) t * nk + kh) * GDN_HS + (e - GDN_HS);
+            else if (e < 2 * GDN_HS + GDN_QC) src = xv + ((size_t) t * nv + lv) * GDN_HS + qq * GDN_QC + (e - 2 * GDN_HS);
+            else src = gates + ((size_t) t * nv + lv) * 2;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(&tile[buf][r][e])), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const float scale = rsqrtf((float) GDN_HS);
+    stage(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < T; t0 += GDS_ROWS, buf ^= 1) {
+        const int nr = min(GDS_ROWS, T - t0);
+        if (t0 + GDS_ROWS < T) {
+            stage(buf ^ 1, t0 + GDS_ROWS);   // (its last readers passed the barrier that ended the previous tile)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int r0 = 0; r0 < nr; ++r0) {
+            const float* row = tile[buf][r0];
+            const float* kt = row + part * 32;
+            const float* qt = row + GDN_HS + part * 32;
+            const float gv = row[2 * GDN_HS + GDN_QC], bv = row[2 * GDN_HS + GDN_QC + 1];
+            float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
+#pragma unroll
+            for (int r = 0; r < 32; r += 4) {
+                k0 = fmaf(s[r], kt[r], k0);
+                k1 = fmaf(s[r + 1], kt[r + 1], k1);
+                k2 = fmaf(s[r + 2], kt[r + 2], k2);
+                k3 = fmaf(s[r + 3], kt[r + 3], k3);
+            }
+            float* kr = &kred[r0 & 1][0][0];
+            kr[part * GDN_QC + lane] = (k0 + k1) + (k2 + k3);
+            __syncthreads();
+            const float kvs = (kr[lane] + kr[GDN_QC + lane]) + (kr[2 * GDN_QC + lane] + kr[3 * GDN_QC + lane]);
+            const float delta = (row[2 * GDN_HS + lane] - gv * kvs) * bv;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int r = 0; r < 32; r += 4) {
+                s[r] = fmaf(kt[r], delta, gv * s[r]);
+                s[r + 1] = fmaf(kt[r + 1], delta, gv * s[r + 1]);
+                s[r + 2] = fmaf(kt[r + 2], delta, gv * s[r + 2]);
+                s[r + 3] = fmaf(kt[r + 3], delta, gv * s[r + 3]);
+                a0 = fmaf(s[r], qt[r], a0);
+                a1 = fmaf(s[r + 1], qt[r + 1], a1);
+                a2 = fmaf(s[r + 2], qt[r + 2], a2);
+                a3 = fmaf(s[r + 3], qt[r + 3], a3);
+            }
+            ared[r0][part][lane] = (a0 + a1) + (a2 + a3);
+        }
+        __syncthreads();   // the tile's sums are complete; its buffer may be refilled two tiles on
+        for (int i = tid; i < nr * GDN_QC; i += GDN_THREADS) {
+            const int r0 = i / GDN_QC, c = i % GDN_QC;
+            o[((size_t) (t0 + r0) * nv + lv) * GDN_HS + qq * GDN_QC + c] = ((ared[r0][0][c] + ared[r0][1][c]) + (ared[r0][2][c] + ared[r0][3][c])) * scale;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 32; ++r) S_out[soff + (size_t) r * GDN_HS] = s[r];
+}
+
+// block = one row, warp = a quarter (32 columns) of a value head at a time: y = o * rsqrt(mean(o^2) + eps) * nw * sigmoid(z)
+__global__ void __launch_bounds__(GDP_THREADS) k_gdn_post(const float* __restrict__ o, const float* __restrict__ qkvz, int stride, const float* __restrict__ nw,
+                                                          float* __restrict__ y, int nk, int nv, float eps) {
+    __shared__ float red[GDP_THREADS / 32];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ch = (2 * nk + nv) * GDN_HS;
+    for (int c0 = 0; c0 < nv * GDN_HS; c0 += GDP_THREADS) {
+        const int c = c0 + tid, col = c % GDN_HS;
+        const float ov = o[(size_t) t * nv * GDN_HS + c];
+        const float zv = qkvz[(size_t) t * stride + ch + c];
+        const float sq = warp_sum(ov * ov);
+        __syncthreads();
+        if (lane == 0) red[warp] = sq;
+        __syncthreads();
+        const int w0 = warp & ~3;
+        const float ms = ((red[w0] + red[w0 + 1]) + (red[w0 + 2] + red[w0 + 3])) / (float) GDN_HS;
+        y[(size_t) t * nv * GDN_HS + c] = ov * rsqrtf(ms + eps) * nw[col] / (1.0f + expf(-zv));
+    }
+}
+
 static size_t gdn_smem_bytes(int T) {
     return sizeof(float) * ((size_t) 2 * T * GDN_HS + (size_t) T * GDN_QC + 2 * T + 2 * 4 * GDN_QC + (size_t) T * 4 * GDN_QC + T + 8 * T +
                             (size_t) (T + 3) * (2 * GDN_HS + GDN_QC) + 3 * T);
@@ -250,22 +406,35 @@ extern "C" int fnx_gdn_core(const float* qkvz, int ldx, const float* ab, int lda
     return FNX_OK;
 }
 
+extern "C" size_t fnx_gdn_prompt_scratch_bytes(int T, int nk, int nv, int hs) {
+    return sizeof(float) * ((size_t) T * (2 * nk + 2 * nv) * hs + (size_t) T * nv * 2 + (size_t) 3 * (2 * nk + nv) * hs) + 1024;
+}
+
 extern "C" int fnx_gdn_prompt(const float* qkvz, int ldx, const float* ab, int ldab, float* hist_pool, const float* convw, const float* dt, const float* a,
-                              const float* nw, float* S_pool, const int* cur, int NS, float* y, int nk, int nv, int hs, int T, float eps, fnx_stream st) {
-    FNX_REQUIRE(qkvz && ab && hist_pool && convw && dt && a && nw && S_pool && cur && y, "fnx_gdn_prompt: null pointer");
+                              const float* nw, float* S_pool, int cur_host, int NS, float* y, int nk, int nv, int hs, int T, float eps, void* scratch,
+                              fnx_stream st) {
+    FNX_REQUIRE(qkvz && ab && hist_pool && convw && dt && a && nw && S_pool && y && scratch, "fnx_gdn_prompt: null pointer");
     FNX_REQUIRE(hs == GDN_HS, "fnx_gdn_prompt: head dim %d (this build: %d)", hs, GDN_HS);
-    FNX_REQUIRE(T >= 1 && NS >= 2, "fnx_gdn_prompt: %d rows, %d state slots", T, NS);
-    FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0, "fnx_gdn_prompt: %d key heads, %d value heads", nk, nv);
-    if (int rc = set_smem_limit((const void*) k_gdn_core, 96 * 1024)) return rc;
-    // windows of up to min(FNX_MAX_ROWS, NS - 1) rows, each starting from the slot the one before left its last row in
-    const int W = NS - 1 < FNX_MAX_ROWS ? NS - 1 : FNX_MAX_ROWS;
-    for (int t0 = 0; t0 < T; t0 += W) {
-        const int nt = T - t0 < W ? T - t0 : W;
-        const cudaError_t le_ = launch_k(k_gdn_core, dim3(nv * GDN_Q), dim3(GDN_THREADS), gdn_smem_bytes(nt), as_stream(st), qkvz + (size_t) t0 * ldx, ldx, ab + (size_t) t0 * ldab,
-                                         ldab, hist_pool, convw, dt, a, nw, S_pool, cur, NS, (const int*) nullptr, y + (size_t) t0 * nv * GDN_HS, nk, nv, nt, eps, t0 % NS, 1);
-        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_gdn_core (prompt): launch failed: %s", cudaGetErrorString(le_));
-    }
-    FNX_LAUNCH_OK("fnx_gdn_prompt");
+    FNX_REQUIRE(T >= 1 && NS >= 2 && cur_host >= 0 && cur_host < NS, "fnx_gdn_prompt: %d rows, slot %d of %d", T, cur_host, NS);
+    FNX_REQUIRE(nk >= 1 && nv >= nk && nv % nk == 0 && nv <= GDP_THREADS && ((2 * nk + nv) * GDN_HS) % GDP_THREADS == 0, "fnx_gdn_prompt: %d key heads, %d value heads", nk, nv);
+    const int ch = (2 * nk + nv) * GDN_HS, out_slot = (cur_host + T) % NS;
+    const size_t hsz = (size_t) 3 * ch, ssz = (size_t) nv * GDN_HS * GDN_HS;
+    float* xq = (float*) scratch;
+    float* xk = xq + (size_t) T * nk * GDN_HS;
+    float* xv = xk + (size_t) T * nk * GDN_HS;
+    float* o = xv + (size_t) T * nv * GDN_HS;
+    float* gates = o + (size_t) T * nv * GDN_HS;
+    cudaStream_t s = as_stream(st);
+    // the history the call starts from is read from a copy: the slot it leaves its own in may be the same one
+    float* hin = gates + (size_t) T * nv * 2;
+    FNX_CUDA_OK(cudaMemcpyAsync(hin, hist_pool + (size_t) cur_host * hsz, hsz * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    k_gdn_pre<<<T, GDP_THREADS, 0, s>>>(qkvz, ldx, ab, ldab, hin, hist_pool + (size_t) out_slot * hsz, convw, dt, a, xq, xk, xv, gates, nk,
+                                         nv, T);
+    FNX_LAUNCH_OK("k_gdn_pre");
+    k_gdn_scan<<<nv * GDN_Q, GDN_THREADS, 0, s>>>(xq, xk, xv, gates, S_pool + (size_t) cur_host * ssz, S_pool + (size_t) out_slot * ssz, o, nk, nv, T);
+    FNX_LAUNCH_OK("k_gdn_scan");
+    k_gdn_post<<<T, GDP_THREADS, 0, s>>>(o, qkvz, ldx, nw, y, nk, nv, eps);
+    FNX_LAUNCH_OK("k_gdn_post");
     return FNX_OK;
 }
 

@@ -161,6 +161,25 @@ def _check_jobs(F, route, T, K, E, topi, e_lo, e_hi, add_shared):
     assert shared_rows == (set(range(T)) if add_shared else set())
 
 
+@pytest.mark.parametrize("E,H,K,T", [(32, 1024, 4, 77), (512, 2048, 10, 300)])
+def test_router_rows_equals_the_window_router(F, E, H, K, T):
+    """The prompt pass's router over T rows in one call against fnx_router_route over windows of 32 rows: the same picks wherever
+    the K-th and (K + 1)-th logits are not a rounding apart, logits and weights to 1e-6."""
+    import torch
+    rng = np.random.default_rng(E + T)
+    wr = dev((0.02 * rng.standard_normal((E + 1, H))).astype(np.float32))
+    x = dev(rng.standard_normal((T, H)).astype(np.float32))
+    nw = dev((1.0 + 0.05 * rng.standard_normal(H)).astype(np.float32))
+    ti, tw, lg = F.router_rows(wr, x, K, norm_w=nw)
+    ri, rw, rl = F.route_rows(wr, x, K, norm_w=nw)
+    assert np.abs(lg.cpu().numpy() - rl.cpu().numpy()).max() < 1e-6
+    srt = np.sort(rl.cpu().numpy()[:, :E], axis=1)
+    clear = (srt[:, -K] - srt[:, -K - 1]) > 1e-5
+    assert clear.sum() > T // 2
+    assert np.array_equal(ti.cpu().numpy()[clear], ri.cpu().numpy()[clear])
+    assert np.abs(tw.cpu().numpy()[clear] - rw.cpu().numpy()[clear]).max() < 1e-5
+
+
 @pytest.mark.parametrize("E,H,Fn,K,T", [(32, 1024, 256, 4, 3), (64, 2048, 512, 10, 5), (64, 2048, 512, 10, 20)])
 def test_moe_block_matches_oracle(F, O, E, H, Fn, K, T):
     fx = _moe_fixture(F, E, H, Fn, seed=21)
@@ -347,6 +366,38 @@ def test_attention_matches_oracle(F, O, pos0, T, tree):
     assert rel_err(out.cpu().numpy(), ref) < 2e-3
 
 
+@pytest.mark.parametrize("pos0,T", [(0, 1), (0, 50), (333, 77), (5000, 13)])
+def test_prompt_attention_matches_windows(F, pos0, T):
+    """A prompt's rows in one call (twelve rows per block, f16 queries, no splits) against chained windows of the window form:
+    the same cache rows appended, outputs to the f16-query tolerance."""
+    nq, nkv, hd, nrot = 16, 2, 256, 64
+    rng = np.random.default_rng(pos0 * 7 + T)
+    rows = pos0 + T + 3
+    kc = np.zeros((rows, nkv, hd), np.uint16)
+    vc = np.zeros((rows, nkv, hd), np.uint16)
+    kc[:pos0] = (rng.standard_normal((pos0, nkv, hd))).astype(np.float16).view(np.uint16)
+    vc[:pos0] = (rng.standard_normal((pos0, nkv, hd))).astype(np.float16).view(np.uint16)
+    qg = rng.standard_normal((T, nq, 2 * hd)).astype(np.float32)
+    k = rng.standard_normal((T, nkv, hd)).astype(np.float32)
+    v = rng.standard_normal((T, nkv, hd)).astype(np.float32)
+    qn = dev((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32))
+    kn = dev((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32))
+    # windows of 32 rows
+    w_kc, w_vc = dev(kc.view(np.int16)), dev(vc.view(np.int16))
+    outs = []
+    for t0 in range(0, T, 32):
+        nt = min(32, T - t0)
+        q_w, pos = dev(qg[t0:t0 + nt]), dev(np.array([pos0 + t0], np.int32))
+        F.attn_prep_append(q_w, dev(k[t0:t0 + nt]), dev(v[t0:t0 + nt]), qn, kn, w_kc, w_vc, pos, None, nrot)
+        outs.append(F.attn(q_w, w_kc, w_vc, pos, None))
+    want = torch.cat(outs)
+    p_kc, p_vc, q_p, pos = dev(kc.view(np.int16)), dev(vc.view(np.int16)), dev(qg), dev(np.array([pos0], np.int32))
+    F.attn_prep_append(q_p, dev(k), dev(v), qn, kn, p_kc, p_vc, pos, None, nrot)
+    got = F.attn_prompt(q_p, p_kc, p_vc, pos)
+    assert torch.equal(p_kc[:pos0 + T], w_kc[:pos0 + T]) and torch.equal(p_vc[:pos0 + T], w_vc[:pos0 + T])
+    assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 2e-3
+
+
 # ------------------------------------------------------------------------------------------------ DeltaNet
 def _gdn_inputs(rng, T, nk, nv, hs):
     ch = (2 * nk + nv) * hs
@@ -375,6 +426,32 @@ def test_gdn_core_matches_oracle(F, O, T, tree, nk, nv):
     assert rel_err(d_S.cpu().numpy(), S) < 1e-4
     assert np.array_equal(d_hist.cpu().numpy(), hist)           # histories are copies: bit-exact
     assert np.array_equal(d_S.cpu().numpy()[cur], S[cur])       # the starting slot is untouched
+
+
+@pytest.mark.parametrize("T,NS", [(1, 4), (37, 9), (64, 33), (99, 33)])
+def test_gdn_prompt_equals_chained_windows(F, T, NS):
+    """The prompt form (conv / scan / norm in three launches, state in registers across all rows) against chained windows of
+    NS - 1 rows of the window kernel, each kept whole: outputs, the final state and the final history."""
+    nk, nv, hs, cur = 2, 4, 128, 2
+    rng = np.random.default_rng(T + NS)
+    ch, qkvz, ab, convw, dt, a, nw = _gdn_inputs(rng, T, nk, nv, hs)
+    S0 = (0.1 * rng.standard_normal((NS, nv, hs, hs))).astype(np.float32)
+    h0 = rng.standard_normal((NS, 3, ch)).astype(np.float32)
+    args = (dev(convw), dev(dt), dev(a), dev(nw))
+    Sw, Hw = dev(S0), dev(h0)
+    ys, c, W = [], cur, NS - 1
+    for t0 in range(0, T, W):
+        nt = min(W, T - t0)
+        ys.append(F.gdn_core(dev(qkvz[t0:t0 + nt]), dev(ab[t0:t0 + nt]), Hw, *args, Sw, dev(np.array([c], np.int32)), None, nk, nv, hs))
+        c = (c + nt) % NS
+    want = torch.cat(ys)
+    Sp, Hp = dev(S0), dev(h0)
+    got = F.gdn_prompt(dev(qkvz), dev(ab), Hp, *args, Sp, cur, nk, nv, hs)
+    assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 1e-4
+    out = (cur + T) % NS
+    assert out == c
+    assert rel_err(Sp[out].cpu().numpy(), Sw[out].cpu().numpy()) < 1e-4
+    assert torch.equal(Hp[out], Hw[out])
 
 
 def test_gdn_rollback_equals_running_only_the_kept_rows(F, O):
