@@ -112,7 +112,7 @@ struct fnx_engine {
     uint8_t* d_img = nullptr;
     bool use_img = true;
     // the prompt pass (fnx_engine_prompt): buffers for a chunk of prompt_chunk rows, made at its first call
-    int prompt_chunk = 4096;
+    int prompt_chunk = 16384;
     float *pR = nullptr, *pproj = nullptr, *pmix = nullptr, *plogits = nullptr, *ptopw = nullptr;
     int *ptopi = nullptr, *d_ptok = nullptr;
     void *p_moe_scratch = nullptr, *p_dense_scratch = nullptr, *p_gdn_scratch = nullptr, *p_attn_scratch = nullptr;
@@ -999,6 +999,10 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
     FNX_REQUIRE(s.pos + n <= e->c.max_ctx, "fnx_engine_prompt: %d tokens run past the context of %d rows", n, e->c.max_ctx);
     for (int t = 0; t < n; ++t) FNX_REQUIRE(h_tok[t] >= 0 && h_tok[t] < e->c.vocab, "fnx_engine_prompt: token %d outside the vocabulary", h_tok[t]);
     const Dims d = dims(e->c);
+    if (!e->pR) {   // the chunk: large enough that an expert's rows fill the 256-row tiles of the grouped product, within the context
+        if (const char* pc = getenv("FNX_PROMPT_CHUNK")) e->prompt_chunk = atoi(pc) > 0 ? atoi(pc) : e->prompt_chunk;
+        if (e->prompt_chunk > e->c.max_ctx) e->prompt_chunk = e->c.max_ctx;
+    }
     const int CH = e->prompt_chunk, fast = n - 1;
     if (fast > 0 && !e->pR) {
         const int mixw = d.nq * d.hd > d.nv * d.hs ? d.nq * d.hd : d.nv * d.hs;

@@ -161,91 +161,76 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router(const float* __restric
     for (int w = tid; w < total * JW; w += NT) reinterpret_cast<int*>(jobs)[w] = reinterpret_cast<const int*>(js.js)[w];
 }
 
-// Routing for prompt-sized row counts: the logits of any number of rows by blocks of sixteen expert rows x sixty-four window rows,
-// then the top K of every row by one warp each.  A warp holds a quarter of the columns of four expert rows in registers, so
-// that every 16-byte read of a staged activation row feeds sixteen multiply-adds (the window router's two: it is bound by the
-// shared-memory reads); the column quarters are summed in order, f32 throughout.
-constexpr int RP_WARPS = 16, RP_SPLIT = 4, RP_RPW = 4, RP_ROWS = (RP_WARPS / RP_SPLIT) * RP_RPW, RP_TOK = 8, RP_CHUNK = 64;
+// Routing for prompt-sized row counts: the logits of any number of rows, then the top K of every row by one warp each.
+// A block stages eight window rows once (normed, as k_router does) and its sixteen warps walk the expert rows, four per warp at
+// a time: a warp keeps a 512-column piece of its four weight rows in registers, so every 16-byte read of a staged row feeds
+// sixteen multiply-adds, and carries its 4 x 8 sums in registers across the row's pieces; nothing in the walk is block-wide,
+// so the warps hide one another's weight loads.  f32 throughout; the sums' order differs from k_router's, the values by rounding.
+constexpr int RP_WARPS = 16, RP_RPW = 4, RP_TOK = 8;
 
 __global__ void __launch_bounds__(RP_WARPS * 32) k_router_rows(const float* __restrict__ Wr, const float* __restrict__ x, const float* __restrict__ norm_w,
                                                                float eps, int T, int E, int H, float* __restrict__ logits, unsigned* __restrict__ err) {
     extern __shared__ __align__(16) float xs[];   // [RP_TOK][H]: x * norm_w (the row's 1 / rms is applied to the sums)
-    __shared__ float rs[RP_TOK], ssw[RP_TOK][RP_WARPS], psum[RP_ROWS][RP_SPLIT][RP_TOK];
+    __shared__ float rs[RP_TOK], ssw[RP_TOK][RP_WARPS];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int share = warp % RP_SPLIT, rg = warp / RP_SPLIT;
-    const int row0 = blockIdx.x * RP_ROWS + rg * RP_RPW;   // the warp's first expert row
     constexpr int NT = RP_WARPS * 32;
-    const int HS = H / RP_SPLIT, c_lo = share * HS;        // HS <= 1024: up to 8 float4 pieces per lane and row, 128 columns apart
-    const int t_end = min(T, ((int) blockIdx.y + 1) * RP_CHUNK);
-    // the weights stay in registers for hidden <= 2048 (four pieces per row); wider rows are re-read per piece
-    const bool resident = HS <= 512;
-    float4 w[RP_RPW][4];
-    if (resident) {
-#pragma unroll
-        for (int r = 0; r < RP_RPW; ++r)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = lane * 4 + j * 128;
-                w[r][j] = row0 + r <= E && i < HS ? *reinterpret_cast<const float4*>(Wr + (size_t) (row0 + r) * H + c_lo + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-    }
+    const int t0 = blockIdx.x * RP_TOK, nt = min(RP_TOK, T - t0);
+    for (int i = tid; i < nt * (H / 4); i += NT)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + (size_t) i * 4)), "l"(x + (size_t) t0 * H + (size_t) i * 4) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
     float4 nw4[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int c = tid * 4 + j * NT * 4;
         nw4[j] = norm_w && c < H ? *reinterpret_cast<const float4*>(norm_w + c) : make_float4(1.f, 1.f, 1.f, 1.f);
     }
-    for (int t0 = blockIdx.y * RP_CHUNK; t0 < t_end; t0 += RP_TOK) {
-        const int nt = min(RP_TOK, t_end - t0);
-        __syncthreads();
-        for (int i = tid; i < nt * (H / 4); i += NT)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + (size_t) i * 4)), "l"(x + (size_t) t0 * H + (size_t) i * 4) : "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            float ss = 0.f;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+        float ss = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int c = tid * 4 + j * NT * 4;
-                if (c >= H) continue;
-                float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + c);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                v.x *= nw4[j].x; v.y *= nw4[j].y; v.z *= nw4[j].z; v.w *= nw4[j].w;
-                *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v;
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) ssw[t][warp] = ss;
+        for (int j = 0; j < 4; ++j) {
+            const int c = tid * 4 + j * NT * 4;
+            if (c >= H) continue;
+            float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + c);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            v.x *= nw4[j].x; v.y *= nw4[j].y; v.z *= nw4[j].z; v.w *= nw4[j].w;
+            *reinterpret_cast<float4*>(xs + (size_t) t * H + c) = v;
         }
-        __syncthreads();
-        if (tid < nt) {
-            float ss = 0.f;
-            for (int wq = 0; wq < RP_WARPS; ++wq) ss += ssw[tid][wq];
-            rs[tid] = norm_w ? rsqrtf(ss / (float) H + eps) : 1.0f;
-        }
+        ss = warp_sum(ss);
+        if (lane == 0) ssw[t][warp] = ss;
+    }
+    __syncthreads();
+    if (tid < nt) {
+        float ss = 0.f;
+        for (int wq = 0; wq < RP_WARPS; ++wq) ss += ssw[tid][wq];
+        rs[tid] = norm_w ? rsqrtf(ss / (float) H + eps) : 1.0f;
+    }
+    __syncthreads();
+    bool bad = false;
+    for (int row0 = warp * RP_RPW; row0 <= E; row0 += RP_WARPS * RP_RPW) {
         float acc[RP_RPW][RP_TOK];
 #pragma unroll
         for (int r = 0; r < RP_RPW; ++r)
 #pragma unroll
             for (int t = 0; t < RP_TOK; ++t) acc[r][t] = 0.f;
-        for (int i0 = 0; i0 < HS; i0 += 512) {
-            if (!resident) {
+        for (int i0 = 0; i0 < H; i0 += 512) {
+            float4 w[RP_RPW][4];
 #pragma unroll
-                for (int r = 0; r < RP_RPW; ++r)
+            for (int r = 0; r < RP_RPW; ++r)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int i = i0 + lane * 4 + j * 128;
-                        w[r][j] = row0 + r <= E && i < HS ? *reinterpret_cast<const float4*>(Wr + (size_t) (row0 + r) * H + c_lo + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-            }
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + lane * 4 + j * 128;
+                    w[r][j] = row0 + r <= E && i < H ? *reinterpret_cast<const float4*>(Wr + (size_t) (row0 + r) * H + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int i = i0 + lane * 4 + j * 128;
-                if (i >= HS) continue;
+                if (i >= H) continue;
 #pragma unroll
                 for (int t = 0; t < RP_TOK; ++t)
                     if (t < nt) {
-                        const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + c_lo + i);
+                        const float4 v = *reinterpret_cast<const float4*>(xs + (size_t) t * H + i);
 #pragma unroll
                         for (int r = 0; r < RP_RPW; ++r) {
                             acc[r][t] = fmaf(w[r][j].x, v.x, acc[r][t]);
@@ -260,23 +245,15 @@ __global__ void __launch_bounds__(RP_WARPS * 32) k_router_rows(const float* __re
         for (int r = 0; r < RP_RPW; ++r)
 #pragma unroll
             for (int t = 0; t < RP_TOK; ++t)
-                if (t < nt) {
-                    const float s = warp_sum(acc[r][t]);
-                    if (lane == 0) psum[rg * RP_RPW + r][share][t] = s;
+                if (t < nt && row0 + r <= E) {
+                    const float s = warp_sum(acc[r][t]) * rs[t];
+                    if (lane == 0) {
+                        logits[(size_t) (t0 + t) * (E + 1) + row0 + r] = s;
+                        bad |= !isfinite(s);
+                    }
                 }
-        __syncthreads();
-        if (tid < RP_ROWS * RP_TOK) {
-            const int r = tid / RP_TOK, t = tid % RP_TOK, grow = blockIdx.x * RP_ROWS + r;
-            if (t < nt && grow <= E) {
-                float s = 0.f;
-#pragma unroll
-                for (int q = 0; q < RP_SPLIT; ++q) s += psum[r][q][t];
-                s *= rs[t];
-                logits[(size_t) (t0 + t) * (E + 1) + grow] = s;
-                if (!isfinite(s)) atomicOr(err, (unsigned) FNX_ERR_NONFINITE);
-            }
-        }
     }
+    if (bad) atomicOr(err, (unsigned) FNX_ERR_NONFINITE);
 }
 
 // one warp per row: the top K of its E logits and their renormalised softmax weights
@@ -457,12 +434,12 @@ extern "C" int fnx_moe_combine_image(const float* part, const int* topi, const f
 extern "C" int fnx_router_rows(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K, float* logits, int* topi,
                                float* topw, unsigned* err, fnx_stream st) {
     FNX_REQUIRE(Wr && x && logits && topi && topw && err, "fnx_router_rows: null pointer");
-    FNX_REQUIRE(T >= 1 && T <= 65535 * RP_CHUNK, "fnx_router_rows: %d rows", T);
+    FNX_REQUIRE(T >= 1, "fnx_router_rows: %d rows", T);
     FNX_REQUIRE(E >= K && E <= RT_MAXE && K >= 1 && K <= 32, "fnx_router_rows: %d experts, top %d not supported", E, K);
     FNX_REQUIRE(H % 256 == 0 && H <= 4096, "fnx_router_rows: hidden %d not supported", H);
     const size_t smem = (size_t) RP_TOK * H * sizeof(float);
     if (int rc = set_smem_limit((const void*) k_router_rows, 160 * 1024)) return rc;
-    k_router_rows<<<dim3((E + 1 + RP_ROWS - 1) / RP_ROWS, (T + RP_CHUNK - 1) / RP_CHUNK), RP_WARPS * 32, smem, as_stream(st)>>>(Wr, x, norm_w, eps, T, E, H, logits, err);
+    k_router_rows<<<(T + RP_TOK - 1) / RP_TOK, RP_WARPS * 32, smem, as_stream(st)>>>(Wr, x, norm_w, eps, T, E, H, logits, err);
     FNX_LAUNCH_OK("k_router_rows");
     k_topk_rows<<<(T + 7) / 8, 256, 0, as_stream(st)>>>(logits, T, E, K, topi, topw);
     FNX_LAUNCH_OK("k_topk_rows");
