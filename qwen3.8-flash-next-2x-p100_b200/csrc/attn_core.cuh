@@ -199,6 +199,15 @@ __device__ __forceinline__ void attn_part_body_t(const float* qg, int ldq, const
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[m][n][k] = 0.f;
     const float scale = rsqrtf((float) ATT_HD);
+    // the window row of each of the lane's score rows (query m * 16 + g + 8 * hrow), once: -1 = no such query
+    int qrow[MT][2];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int qi = m * 16 + g + 8 * hrow;
+            qrow[m][hrow] = qi < NQ ? qi / qpk : -1;
+        }
     const uint32_t qh_s = smem_u32(Qh), ql_s = smem_u32(Ql), ks0_s = smem_u32(Ks), vs0_s = smem_u32(Vs), pp_s = smem_u32(Pp);
     // ldmatrix lane addresses: A tiles (16 rows x 16 columns), B tiles of K (8 positions x 32 dims), of V (16 positions x 16 dims, transposed)
     const uint32_t a_off = (uint32_t) ((lane & 15) * ATT_QS + (lane >> 4) * 8) * 2u;
@@ -222,59 +231,98 @@ __device__ __forceinline__ void attn_part_body_t(const float* qg, int ldq, const
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) c[m][k] = 0.f;
-#pragma unroll 4
+#pragma unroll 2
             for (int k0 = 0; k0 < ATT_HD; k0 += 32) {
+                // every fragment of the 32 dims first, then the products: the loads' latency is paid once per 32 dims, not once
+                // per product (the asm statements keep their order)
                 uint32_t b0, b1, b2, b3;   // (b0, b1): dims k0 .. k0 + 15, (b2, b3): k0 + 16 .. k0 + 31
                 ldsm_x4(ks_s + bk_off + k0 * 2, b0, b1, b2, b3);
+                uint32_t ah[MT][2][4], al[QLO ? MT : 1][2][4];
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    uint32_t a0, a1, a2, a3;
                     const uint32_t ao = a_off + (uint32_t) (m * 16 * ATT_QS + k0) * 2u;
-                    ldsm_x4(qh_s + ao, a0, a1, a2, a3);
-                    mma_f16(c[m], a0, a1, a2, a3, b0, b1);
+                    ldsm_x4(qh_s + ao, ah[m][0][0], ah[m][0][1], ah[m][0][2], ah[m][0][3]);
+                    ldsm_x4(qh_s + ao + 32, ah[m][1][0], ah[m][1][1], ah[m][1][2], ah[m][1][3]);
                     if (QLO) {
-                        ldsm_x4(ql_s + ao, a0, a1, a2, a3);
-                        mma_f16(c[m], a0, a1, a2, a3, b0, b1);
+                        ldsm_x4(ql_s + ao, al[m][0][0], al[m][0][1], al[m][0][2], al[m][0][3]);
+                        ldsm_x4(ql_s + ao + 32, al[m][1][0], al[m][1][1], al[m][1][2], al[m][1][3]);
                     }
-                    ldsm_x4(qh_s + ao + 32, a0, a1, a2, a3);
-                    mma_f16(c[m], a0, a1, a2, a3, b2, b3);
-                    if (QLO) {
-                        ldsm_x4(ql_s + ao + 32, a0, a1, a2, a3);
-                        mma_f16(c[m], a0, a1, a2, a3, b2, b3);
-                    }
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m) mma_f16(c[m], ah[m][0][0], ah[m][0][1], ah[m][0][2], ah[m][0][3], b0, b1);
+                if (QLO) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) mma_f16(c[m], al[QLO ? m : 0][0][0], al[QLO ? m : 0][0][1], al[QLO ? m : 0][0][2], al[QLO ? m : 0][0][3], b0, b1);
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m) mma_f16(c[m], ah[m][1][0], ah[m][1][1], ah[m][1][2], ah[m][1][3], b2, b3);
+                if (QLO) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) mma_f16(c[m], al[QLO ? m : 0][1][0], al[QLO ? m : 0][1][1], al[QLO ? m : 0][1][2], al[QLO ? m : 0][1][3], b2, b3);
                 }
             }
             // scaled and masked into the score tile: row = query, column = position of the step
+            // a step that lies wholly before the window's first row is visible to every row: no masks to work out
+            const bool open_step = np == ATT_SC && p0 + ATT_SC <= pos0 + (CHAIN ? r0 : 0);
 #pragma unroll
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int qi = m * 16 + g + 8 * hrow;
+                    const int qi = m * 16 + g + 8 * hrow, qr = qrow[m][hrow];
                     float2 o;
                     float* ov = &o.x;
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const int col = warp * 8 + 2 * q + k, p = p0 + col;
-                        bool vis = qi < NQ && col < np;
-                        if (CHAIN) vis = vis && p <= pos0 + r0 + qi / qpk;
-                        else if (vis && p >= pos0) vis = (see[qi / qpk] >> (p - pos0)) & 1u;
+                        bool vis = qr >= 0;
+                        if (!open_step) {
+                            vis = vis && col < np;
+                            if (CHAIN) vis = vis && p <= pos0 + r0 + qr;
+                            else if (vis && p >= pos0) vis = (see[qr] >> (p - pos0)) & 1u;
+                        }
                         ov[k] = vis ? c[m][2 * hrow + k] * scale : -INFINITY;
                     }
                     *reinterpret_cast<float2*>(Sf + qi * ATT_SS + warp * 8 + 2 * q) = o;
                 }
         }
         sync();
-        // ---- weights: warp w = queries w, w + 8, ...; lane = positions lane and 32 + lane
-        for (int qi = warp; qi < ATT_MQ; qi += ATT_THREADS / 32) {
-            const float v0 = Sf[qi * ATT_SS + lane], v1 = Sf[qi * ATT_SS + 32 + lane];
-            const float mo = ms[qi], mn = fmaxf(mo, warp_max(fmaxf(v0, v1)));
-            const __half w0 = __float2half_rn(v0 == -INFINITY ? 0.f : expf(v0 - mn)), w1 = __float2half_rn(v1 == -INFINITY ? 0.f : expf(v1 - mn));
-            const float f = mo == -INFINITY ? 0.f : expf(mo - mn);
-            const float zn = zs[qi] * f + warp_sum(__half2float(w0) + __half2float(w1));
-            Pp[qi * ATT_PS + lane] = w0;
-            Pp[qi * ATT_PS + 32 + lane] = w1;
-            __syncwarp();
-            if (lane == 0) { ms[qi] = mn; zs[qi] = zn; fs[qi] = f; }
+        // ---- weights: warp w = queries w, w + 8, ..., four at a time: eight lanes per query, eight positions per lane
+        {
+            constexpr int RW = ATT_MQ / (ATT_THREADS / 32);
+            auto ex = [](float x) { return CHAIN ? __expf(x) : expf(x); };   // (the prompt form takes the hardware exponential)
+#pragma unroll
+            for (int j0 = 0; j0 < RW; j0 += 4) {
+                const int j = j0 + (lane >> 3), l8 = lane & 7;
+                const bool act = j < RW;
+                const int qi = warp + (ATT_THREADS / 32) * (act ? j : 0);
+                const float4 x0 = *reinterpret_cast<const float4*>(Sf + qi * ATT_SS + 8 * l8), x1 = *reinterpret_cast<const float4*>(Sf + qi * ATT_SS + 8 * l8 + 4);
+                const float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                float mx = fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), fmaxf(fmaxf(v[4], v[5]), fmaxf(v[6], v[7])));
+#pragma unroll
+                for (int o = 4; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                const float mo = ms[qi], mn = fmaxf(mo, mx);
+                __half h[8];
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    h[i] = __float2half_rn(v[i] == -INFINITY ? 0.f : ex(v[i] - mn));
+                    sum += __half2float(h[i]);
+                }
+#pragma unroll
+                for (int o = 4; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                const float f = mo == -INFINITY ? 0.f : ex(mo - mn);
+                const float zn = zs[qi] * f + sum;
+                __syncwarp();   // every lane has read the query's running values
+                if (act) {
+                    uint4 pk;
+                    pk.x = (uint32_t) __half_as_ushort(h[0]) | ((uint32_t) __half_as_ushort(h[1]) << 16);
+                    pk.y = (uint32_t) __half_as_ushort(h[2]) | ((uint32_t) __half_as_ushort(h[3]) << 16);
+                    pk.z = (uint32_t) __half_as_ushort(h[4]) | ((uint32_t) __half_as_ushort(h[5]) << 16);
+                    pk.w = (uint32_t) __half_as_ushort(h[6]) | ((uint32_t) __half_as_ushort(h[7]) << 16);
+                    *reinterpret_cast<uint4*>(Pp + qi * ATT_PS + 8 * l8) = pk;
+                    if (l8 == 0) { ms[qi] = mn; zs[qi] = zn; fs[qi] = f; }
+                }
+            }
         }
         sync();
         // ---- sums: warp w = dims [32 w, 32 w + 32), all 48 query rows
@@ -289,18 +337,18 @@ __device__ __forceinline__ void attn_part_body_t(const float* qg, int ldq, const
         }
 #pragma unroll
         for (int k0 = 0; k0 < ATT_SC; k0 += 16) {
-            uint32_t a[MT][4];
+            uint32_t a[MT][4], bv[2][4];
 #pragma unroll
             for (int m = 0; m < MT; ++m) ldsm_x4(pp_s + ap_off + (uint32_t) (m * 16 * ATT_PS + k0) * 2u, a[m][0], a[m][1], a[m][2], a[m][3]);
 #pragma unroll
-            for (int n2 = 0; n2 < 2; ++n2) {
-                uint32_t b0, b1, b2, b3;   // (b0, b1): dims 16 n2 .. + 7, (b2, b3): + 8 .. + 15
-                ldsm_x4_t(vs_s + bv_off + (uint32_t) (k0 * ATT_QS + n2 * 16) * 2u, b0, b1, b2, b3);
+            for (int n2 = 0; n2 < 2; ++n2)   // (b0, b1): dims 16 n2 .. + 7, (b2, b3): + 8 .. + 15
+                ldsm_x4_t(vs_s + bv_off + (uint32_t) (k0 * ATT_QS + n2 * 16) * 2u, bv[n2][0], bv[n2][1], bv[n2][2], bv[n2][3]);
 #pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    mma_f16(acc[m][2 * n2], a[m][0], a[m][1], a[m][2], a[m][3], b0, b1);
-                    mma_f16(acc[m][2 * n2 + 1], a[m][0], a[m][1], a[m][2], a[m][3], b2, b3);
-                }
+            for (int n2 = 0; n2 < 2; ++n2) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) mma_f16(acc[m][2 * n2], a[m][0], a[m][1], a[m][2], a[m][3], bv[n2][0], bv[n2][1]);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) mma_f16(acc[m][2 * n2 + 1], a[m][0], a[m][1], a[m][2], a[m][3], bv[n2][2], bv[n2][3]);
             }
         }
     }
