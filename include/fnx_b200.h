@@ -319,6 +319,15 @@ int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uint64_t seed)
  * the pending one; root >= 0 replaces the pending token, for a caller that starts the next window from another token):
  * up to lk drafts into h_out, their number into h_n; d1 >= 0 keeps only a match whose first draft is d1. */
 int fnx_engine_lookup(fnx_engine* e, int seq, int lk, int d1, int root, int* h_out, int* h_n);
+/* Sequence-state cache (Engine::save_state / load_state / state_bytes, engine/src/engine_common.cu:629-688): a committed
+ * sequence's DeltaNet states, conv histories, context tokens and, with kv, its cache rows [0, pos), copied to host memory the
+ * caller owns (fnx_engine_state_bytes(e, seq, kv) bytes) and put back later into the same or another sequence.  Without kv
+ * the image is a checkpoint of the same sequence: it can only be loaded while the engine still holds those rows' K/V (the
+ * tokens are compared).  Neither call may fall between a window and its commit (FNX_E_ARG); after a load the sequence stands
+ * at the saved position with no window pending (verify next; drafts need a window first).  Both synchronise. */
+size_t fnx_engine_state_bytes(fnx_engine* e, int seq, int kv);
+int fnx_engine_save_state(fnx_engine* e, int seq, int kv, void* host, size_t bytes);
+int fnx_engine_load_state(fnx_engine* e, int seq, const void* host, size_t bytes);
 /* Batched lanes (Engine::verify_rows / commit_rows / draft_rows, engine/src/engine_common.cu:1234-1684; GdnLanes,
  * engine/src/kernels.hpp:103-110): one window holds `rows` <= FNX_LANE_ROWS rows of each of n_lanes distinct sequences
  * (n_lanes * rows <= max_rows), every lane a chain continuing its own sequence.  Projections, router, experts and head run

@@ -99,6 +99,9 @@ _PROTOS = {
     "fnx_engine_reset": (_I, [_P, _I]),
     "fnx_engine_verify": (_I, [_P, _I, _P, _P, _I, _P]),
     "fnx_engine_prompt": (_I, [_P, _I, _P, _I]),
+    "fnx_engine_state_bytes": (_Z, [_P, _I, _I]),
+    "fnx_engine_save_state": (_I, [_P, _I, _I, _P, _Z]),
+    "fnx_engine_load_state": (_I, [_P, _I, _P, _Z]),
     "fnx_engine_commit": (_I, [_P, _I, _P, _I]),
     "fnx_engine_draft": (_I, [_P, _I, _I, _P]),
     "fnx_engine_last_ms": (_F, [_P]),
@@ -585,6 +588,17 @@ class Engine:
 
     def pos(self, seq: int = 0) -> int:
         return lib().fnx_engine_pos(self._h, seq)
+
+    def save_state(self, seq: int = 0, kv: bool = True):
+        """The sequence's state as a host buffer (a ctypes array) for load_state."""
+        import ctypes as C
+        n = lib().fnx_engine_state_bytes(self._h, seq, 1 if kv else 0)
+        buf = (C.c_uint8 * n)()
+        check(lib().fnx_engine_save_state(self._h, seq, 1 if kv else 0, buf, n))
+        return buf
+
+    def load_state(self, buf, seq: int = 0):
+        check(lib().fnx_engine_load_state(self._h, seq, buf, len(buf)))
 
     def prompt(self, tokens, seq: int = 0):
         """Reads a prompt on the prompt-sized kernels (fnx_engine_prompt); leaves the engine as after verify + commit."""

@@ -1435,6 +1435,111 @@ extern "C" int fnx_engine_set_position(fnx_engine* e, int seq, int pos) {
     return FNX_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ sequence-state cache
+// Engine::save_state / load_state (engine/src/engine_common.cu:629-688): a committed sequence's recurrent states, conv histories,
+// context tokens and (kv) cache rows, copied to host memory the caller owns, and put back later - into the same sequence (a
+// rewind; without kv the engine must still hold the rows' K/V) or another one.  The image holds, after a header, the context
+// tokens [0, pos] (the pending one included), then per layer in order: DeltaNet state and history of the current slot; with kv,
+// an attention layer's K rows [0, pos) then V rows; the draft layer's cache last.
+namespace fnxb {
+struct StateHeader {
+    uint32_t magic, kv;
+    int32_t pos, n_layer, hidden, nv, hs, gdn_ch, kv_rows, has_mtp;
+    uint32_t step, pad;
+    uint64_t bytes;
+};
+constexpr uint32_t STATE_MAGIC = 0x53584e46u;   // "FNXS"
+// the pieces of sequence `seq` at position pos with state slot cur, in image order: (device pointer, bytes)
+static std::vector<std::pair<char*, size_t>> state_pieces(fnx_engine* e, int seq, int pos, int cur, bool kv) {
+    const Dims d = dims(e->c);
+    std::vector<std::pair<char*, size_t>> v;
+    v.push_back({(char*) (e->d_ctx + (size_t) seq * e->cache_rows), sizeof(int) * ((size_t) pos + 1)});
+    auto layer = [&](LayerW& L) {
+        if (!L.attn) {
+            const size_t ssz = (size_t) d.nv * d.hs * d.hs, hsz = (size_t) 3 * d.gdn_ch;
+            v.push_back({(char*) (L.S_pool + ((size_t) seq * e->NS + cur) * ssz), ssz * sizeof(float)});
+            v.push_back({(char*) (L.hist_pool + ((size_t) seq * e->NS + cur) * hsz), hsz * sizeof(float)});
+        } else if (kv && pos > 0) {
+            v.push_back({(char*) (L.kc + (size_t) seq * e->cache_rows * d.kv_rows), (size_t) pos * d.kv_rows * sizeof(__half)});
+            v.push_back({(char*) (L.vc + (size_t) seq * e->cache_rows * d.kv_rows), (size_t) pos * d.kv_rows * sizeof(__half)});
+        }
+    };
+    for (LayerW& L : e->layers) layer(L);
+    layer(e->mtp);
+    return v;
+}
+}  // namespace fnxb
+
+extern "C" size_t fnx_engine_state_bytes(fnx_engine* e, int seq, int kv) {
+    if (!e || seq < 0 || seq >= e->c.n_seq) return 0;
+    size_t n = sizeof(StateHeader);
+    for (const auto& p : state_pieces(e, seq, e->seqs[seq].pos, e->seqs[seq].cur, kv != 0)) n += (p.second + 15) & ~(size_t) 15;
+    return n;
+}
+
+extern "C" int fnx_engine_save_state(fnx_engine* e, int seq, int kv, void* host, size_t bytes) {
+    FNX_REQUIRE(e && host && seq >= 0 && seq < e->c.n_seq, "fnx_engine_save_state: bad arguments");
+    SeqState& s = e->seqs[seq];
+    FNX_REQUIRE(s.last_T == 0, "fnx_engine_save_state: a window of sequence %d is not committed", seq);
+    const size_t need = fnx_engine_state_bytes(e, seq, kv);
+    FNX_REQUIRE(bytes >= need, "fnx_engine_save_state: %zu bytes given, %zu needed", bytes, need);
+    const Dims d = dims(e->c);
+    StateHeader h{};
+    h.magic = STATE_MAGIC; h.kv = kv != 0; h.pos = s.pos; h.n_layer = e->c.n_layer; h.hidden = d.H; h.nv = d.nv; h.hs = d.hs; h.gdn_ch = d.gdn_ch;
+    h.kv_rows = d.kv_rows; h.has_mtp = 1; h.step = s.step; h.bytes = need;
+    memcpy(host, &h, sizeof h);
+    char* dst = (char*) host + sizeof h;
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    for (const auto& p : state_pieces(e, seq, s.pos, s.cur, kv != 0)) {
+        FNX_CUDA_OK(cudaMemcpyAsync(dst, p.first, p.second, cudaMemcpyDeviceToHost, e->st));
+        dst += (p.second + 15) & ~(size_t) 15;
+    }
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_load_state(fnx_engine* e, int seq, const void* host, size_t bytes) {
+    FNX_REQUIRE(e && host && seq >= 0 && seq < e->c.n_seq && bytes >= sizeof(StateHeader), "fnx_engine_load_state: bad arguments");
+    SeqState& s = e->seqs[seq];
+    FNX_REQUIRE(s.last_T == 0, "fnx_engine_load_state: a window of sequence %d is not committed", seq);
+    StateHeader h;
+    memcpy(&h, host, sizeof h);
+    const Dims d = dims(e->c);
+    FNX_REQUIRE(h.magic == STATE_MAGIC && h.n_layer == e->c.n_layer && h.hidden == d.H && h.nv == d.nv && h.hs == d.hs && h.gdn_ch == d.gdn_ch &&
+                    h.kv_rows == d.kv_rows && h.bytes <= bytes,
+                "fnx_engine_load_state: a state saved with another layout");
+    FNX_REQUIRE(h.pos >= 0 && h.pos + 1 <= e->c.max_ctx, "fnx_engine_load_state: the state (%d rows) does not fit the context", h.pos);
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    const char* src = (const char*) host + sizeof h;
+    if (!h.kv) {
+        // the engine must still hold the rows' K/V: the sequence has to be a continuation of the saved one
+        FNX_REQUIRE(s.pos >= h.pos, "fnx_engine_load_state: a checkpoint without K/V at row %d, the sequence holds %d rows", h.pos, s.pos);
+        std::vector<int> have((size_t) h.pos);
+        if (h.pos > 0) FNX_CUDA_OK(cudaMemcpy(have.data(), e->d_ctx + (size_t) seq * e->cache_rows, sizeof(int) * (size_t) h.pos, cudaMemcpyDeviceToHost));
+        FNX_REQUIRE(h.pos == 0 || memcmp(have.data(), src, sizeof(int) * (size_t) h.pos) == 0,
+                    "fnx_engine_load_state: a checkpoint of another sequence (the engine does not hold its K/V)");
+    }
+    // the state goes to slot 0, which becomes the current one
+    const auto pieces = state_pieces(e, seq, h.pos, 0, h.kv != 0);
+    size_t total = sizeof h;
+    for (const auto& p : pieces) total += (p.second + 15) & ~(size_t) 15;
+    FNX_REQUIRE(total == h.bytes, "fnx_engine_load_state: a state saved with another layout (%zu bytes against %llu)", total, (unsigned long long) h.bytes);
+    for (const auto& p : pieces) {
+        FNX_CUDA_OK(cudaMemcpyAsync(p.first, src, p.second, cudaMemcpyHostToDevice, e->st));
+        src += (p.second + 15) & ~(size_t) 15;
+    }
+    const int zero = 0;
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_pos + seq, &h.pos, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_ctx_n + seq, &h.pos, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaMemcpyAsync(e->d_cur + seq, &zero, sizeof(int), cudaMemcpyHostToDevice, e->st));
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    s = SeqState{};
+    s.pos = h.pos;
+    s.cur = 0;
+    s.step = h.step;
+    return FNX_OK;
+}
+
 extern "C" int fnx_engine_set_wait_limit(fnx_engine* e, unsigned polls) {
     FNX_REQUIRE(e && polls >= 1, "fnx_engine_set_wait_limit: bad arguments");
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));

@@ -151,6 +151,61 @@ def test_prompt_pass_matches_the_window_path_and_the_oracle(F, O, model):
         assert eng.pos() == n and eng.error_bits() == 0
 
 
+def test_saved_state_brings_a_sequence_back_bit_for_bit(F):
+    """save_state / load_state: after a prompt, two more windows and a load, the same window gives the same bits again - with the
+    cache rows in the image (also into another sequence) and without them (a rewind of the same sequence); a checkpoint
+    without K/V is refused for a sequence that does not continue it, and neither call may fall between verify and commit."""
+    cfg = small_cfg(F, n_seq=2)
+    eng = F.Engine(cfg)
+    try:
+        eng.init_synthetic(seed=5, sigma=0.02)
+        rng = np.random.default_rng(21)
+        prompt = rng.integers(0, cfg.vocab, size=21).tolist()
+        wins = [rng.integers(0, cfg.vocab, size=5).tolist() for _ in range(3)]
+
+        def window(seq, toks):
+            r = eng.verify(toks, None, seq)
+            lg = eng.tensor("buf.logits", torch.float32).cpu().reshape(cfg.max_rows, cfg.vocab)[:len(toks)].clone()
+            return r, lg
+
+        eng.reset(0)
+        eng.prefill(prompt, 0)
+        full = eng.save_state(0, kv=True)
+        light = eng.save_state(0, kv=False)
+        assert len(light) < len(full)
+        r0, lg0 = window(0, wins[0])
+        with pytest.raises(F.FnxError):
+            eng.save_state(0)                      # a window is pending
+        eng.commit(r0[1], 0)
+        r1, _ = window(0, wins[1])
+        eng.commit(r1[1], 0)
+        assert eng.pos(0) > 21
+        # a rewind without K/V: the engine still holds the rows
+        eng.load_state(light, 0)
+        assert eng.pos(0) == 21
+        ra, lga = window(0, wins[0])
+        assert ra == r0 and torch.equal(lga, lg0)
+        eng.commit(ra[1], 0)
+        # the full image into the other sequence
+        eng.load_state(full, 1)
+        assert eng.pos(1) == 21
+        rb, lgb = window(1, wins[0])
+        assert rb == r0 and torch.equal(lgb, lg0)
+        eng.commit(rb[1], 1)
+        assert len(eng.draft(2, 1)) == 2
+        # sequence 1 after a reset does not continue the checkpoint: without K/V it is refused, with K/V it loads
+        eng.reset(1)
+        eng.prefill(wins[2], 1)
+        with pytest.raises(F.FnxError):
+            eng.load_state(light, 1)
+        eng.load_state(full, 1)
+        rc, lgc = window(1, wins[0])
+        assert rc == r0 and torch.equal(lgc, lg0)
+        eng.commit(rc[1], 1)
+    finally:
+        eng.close()
+
+
 def test_full_size_layers_match_oracle(F, O):
     """The benchmark model's own dimensions (hidden 2048, 512 experts top-10 of width 512, 16/2 attention heads of 256, 16/32
     DeltaNet heads of 128, vocabulary 151,936), four layers of it (three DeltaNet, one attention): a prompt, a 5-row chain window
