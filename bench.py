@@ -510,6 +510,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (the benchmark's is 4096)")
     ap.add_argument("--prefill-moe", type=int, default=0, metavar="T",
                     help="side measurement: the prompt-sized MoE block (tcgen05 grouped expert GEMM) of layer 0 over T random rows")
+    ap.add_argument("--attn-prompt", type=int, default=0, metavar="T", help="side mode: the prompt attention alone, T rows at position --ctx")
     ap.add_argument("--prompt-windows", action="store_true", help="configuration 3: read the prompt through 32-row windows of the decode kernels instead of the prompt pass")
     ap.add_argument("--no-config4", action="store_true", help="skip the 8-sequence side measurement that follows the headline run")
     ap.add_argument("--verify-only", action="store_true", help="profiling aid: prefill, then warmup + steps verify windows of k+1 rows and nothing else")
@@ -555,6 +556,27 @@ def main():
         return run_config2(a, F, eng, cfg, rank, world, local, use_peer)
     if a.config == 3:
         return run_config3(a, F, eng, cfg, rank, world, local, use_peer)
+    if a.attn_prompt:
+        # config 3's attention on its own: T prompt rows at position --ctx against a random f16 cache (a profiling aid)
+        T, pos0 = a.attn_prompt, a.ctx
+        nq, nkv, hd = cfg.n_q_head, cfg.n_kv_head, cfg.head_dim
+        kc = torch.randn((pos0 + T + 8, nkv, hd), device="cuda").half().view(torch.int16)
+        vc = torch.randn((pos0 + T + 8, nkv, hd), device="cuda").half().view(torch.int16)
+        qg = torch.randn((T, nq, 2 * hd), device="cuda")
+        pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+        for _ in range(max(a.warmup, 1)):
+            F.attn_prompt(qg, kc, vc, pos)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            F.attn_prompt(qg, kc, vc, pos)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.steps
+        print(json.dumps({"mode": "attn-prompt", "rows": T, "position": pos0, "ms": ms, "kv_gbs": (pos0 + T / 2) * nkv * hd * 4 * ((T + 11) // 12) / ms / 1e6,
+                          "note": "fnx_attn_prompt (partials + combine); kv_gbs = cache bytes the blocks read (from L2 mostly) per second"}))
+        return
     if a.prefill_moe:
         # config 3's expert path on one layer: T rows grouped by expert, gate|up + SwiGLU + down on the tensor cores
         T = a.prefill_moe

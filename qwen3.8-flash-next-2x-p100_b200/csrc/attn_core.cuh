@@ -1,5 +1,5 @@
-// Device bodies of the gated-attention kernels, shared by the stand-alone launches (attn.cu) and the persistent window
-// kernel (window.cu): per-head norm + rotary + KV append, the tree-masked split-K partial, and the merge of the splits.
+// Device bodies of the gated-attention kernels (attn.cu), shared by their single-sequence, batched-lane and prompt forms:
+// per-head norm + rotary + KV append, the tree-masked split-K partial, and the merge of the splits.
 // Reference: attn_prep_append / norm_rope (engine/src/kernels.cu:1880-1910, 513-530), k_attn_part / k_attn_combine
 // (engine/src/kernels.cu:558-667, 786-803).
 #pragma once

@@ -1,6 +1,5 @@
-// One matrix stage of a block: the shared body of the IQ3_S matrix x rows kernel (iq3s_mmv.cu) and of the matrix
-// phases of the persistent verify-step kernel (step.cu).  The block quantises the activation rows it needs into its
-// own shared-memory images, streams its share of the tile blocks through the warps' rings (mmv_core.cuh), combines
+// One matrix stage of a block: the body of the IQ3_S matrix x rows kernel (iq3s_mmv.cu).  The block quantises the
+// activation rows it needs into its own shared-memory images (or copies the image their producer left), streams its share of the tile blocks through the warps' rings (mmv_core.cuh), combines
 // the pieces of tiles cut by warp shares, and writes the results.
 #pragma once
 

@@ -1,4 +1,4 @@
-// Routing pieces shared by the stand-alone router kernel (moe_route.cu) and the persistent window kernel (window.cu):
+// Routing pieces of the router kernels (moe_route.cu), the window form and the prompt form:
 // order-preserving logit keys, the top-K of one row by one warp, and the block-wide job list builder.
 // Semantics: k_topk + k_jobs (engine/src/kernels.cu:338-398) and k_router_route (engine/src/moe.cuh:382-411).
 #pragma once
