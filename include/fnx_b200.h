@@ -179,6 +179,8 @@ int fnx_attn_static(const float* qg, int ldq, const void* kc, const void* vc, fl
  * the window (at most FNX_LANE_ROWS rows), a chain of sequence lane_seq[j] at position pos[lane_seq[j]], reading and
  * appending that sequence's caches at kc_base / vc_base + seq * seq_stride_rows rows.  Same kernels' bodies and results as
  * the single-sequence calls. */
+/* (in the lanes forms a lane whose lane_seq entry is negative is skipped: its rows are computed elsewhere, e.g. by the
+ * expert-parallel rank that holds that sequence's caches and states) */
 int fnx_attn_prep_append_lanes(float* qg, int ldq, float* k, int ldk, const float* v, int ldv, const float* q_norm,
                                const float* k_norm, void* kc_base, void* vc_base, size_t seq_stride_rows, int n_lanes,
                                int max_lane_rows, int nq, int nkv, int hd, int nrot, const int* pos, const int* lane_seq,

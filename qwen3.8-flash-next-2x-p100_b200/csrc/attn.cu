@@ -59,6 +59,7 @@ __global__ void k_attn_prep_append_lanes(float* __restrict__ qg, int ldq, float*
     const int lane = blockIdx.z, t = blockIdx.y, row0 = lane_row0[lane];
     if (t >= lane_row0[lane + 1] - row0) return;
     const int seq = lane_seq[lane];
+    if (seq < 0) return;   // another rank's lane
     attn_prep_body(qg + (size_t) row0 * ldq, ldq, k + (size_t) row0 * ldk, ldk, v + (size_t) row0 * ldv, ldv, qn, kn, kc_base + seq * seq_stride,
                    vc_base + seq * seq_stride, nq, nkv, hd, nrot, pos[seq], nullptr, eps, rope_base, t, (int) blockIdx.x, (int) threadIdx.x, xrow, red,
                    SyncBlock());
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_part_lanes(const float* __
                                                                  const int* __restrict__ lane_seq, const int* __restrict__ lane_row0) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int lane = blockIdx.z, row0 = lane_row0[lane], T = lane_row0[lane + 1] - row0, seq = lane_seq[lane], S = gridDim.x;
-    if (T <= 0) return;
+    if (T <= 0 || seq < 0) return;   // (a negative sequence: another rank's lane)
     attn_part_body(qg + (size_t) row0 * ldq, ldq, kc_base + seq * seq_stride, vc_base + seq * seq_stride, acc_out + (size_t) row0 * nq * S * ATT_HD,
                    mz_out + (size_t) row0 * nq * S, T, nq, nkv, pos[seq], nullptr, (int) blockIdx.x, S, (int) blockIdx.y, 0, (int) threadIdx.x, smem, SyncBlock());
 }

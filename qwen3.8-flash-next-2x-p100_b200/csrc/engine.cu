@@ -136,6 +136,14 @@ struct fnx_engine {
     unsigned* d_xseq = nullptr;   // [0] sends so far, [1] receives so far, [2] send block counter, [3] receive block counter
     std::vector<void*> ipc_opened;
     bool ep_peers = false;
+    // lanes windows on expert-parallel ranks: each rank runs the mixers (attention, DeltaNet) of its own sequences only
+    // (sequence % ranks == rank) and the mixers' output rows are gathered over the same peer memory: a second region of the
+    // landing buffer ([2 slots][MAXR][mixer width], after the expert planes) with its own flags ([2][ranks], after the
+    // experts') and sequence counters (d_xseq[4..7])
+    bool dp_mixers = true;
+    size_t x_off_rows = 0;        // floats before the rows region
+    int mix_width = 0;
+    int* d_lane_own = nullptr;    // the lane table the mixers see: the lane's sequence, or -1 for another rank's lane
     unsigned wait_limit = 2000000u;   // polls a peer-flag wait makes before it gives up with FNX_ERR_TIMEOUT
     // stochastic acceptance (fnx_engine_set_sampling): off = greedy windows
     bool sampling_on = false;
@@ -425,6 +433,78 @@ static int init_layer(fnx_engine* e, LayerW& L, int li, uint64_t seed, float sig
     return FNX_OK;
 }
 
+// ---- the gather of the mixers' output rows among expert-parallel ranks (lanes windows): every rank stores the rows of its
+// own lanes into every peer's rows region, the last block releases one flag per peer; the receiving kernel waits for every
+// other rank's flag (bounded) and copies their lanes' rows into the local buffer.
+__global__ void k_dp_send(const float* __restrict__ mix, int width, const int* __restrict__ lane_own, const int* __restrict__ lane_row0, int n_lanes,
+                          float* const* __restrict__ peer_x, size_t x_off, unsigned* const* __restrict__ peer_flag, int rank, int R, int maxr,
+                          unsigned* __restrict__ seqs) {
+    const int lane = blockIdx.y;
+    const unsigned seq = seqs[4];
+    const int slot = (int) (seq & 1u);
+    if (lane_own[lane] >= 0) {
+        const int r0 = lane_row0[lane], nr = lane_row0[lane + 1] - r0;
+        const size_t n4 = (size_t) nr * width / 4;
+        const float4* src = reinterpret_cast<const float4*>(mix + (size_t) r0 * width);
+        for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t) gridDim.x * blockDim.x) {
+            const float4 v = src[i];
+            for (int r = 0; r < R; ++r)
+                if (r != rank) reinterpret_cast<float4*>(peer_x[r] + x_off + ((size_t) slot * maxr + r0) * width)[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ bool last;
+    if (threadIdx.x == 0) last = atomicAdd(&seqs[6], 1u) == gridDim.x * gridDim.y - 1;
+    __syncthreads();
+    if (last && threadIdx.x < R) {
+        __threadfence_system();
+        unsigned* f = peer_flag[threadIdx.x] + 2 * R + slot * R + rank;
+        const unsigned v = seq + 1u;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(v) : "memory");
+    }
+    if (last && threadIdx.x == 0) {
+        seqs[6] = 0;
+        seqs[4] = seq + 1u;
+    }
+}
+__global__ void k_dp_recv(const float* __restrict__ xrows, const unsigned* __restrict__ xflag, float* __restrict__ mix, int width,
+                          const int* __restrict__ lane_own, const int* __restrict__ lane_row0, int n_lanes, int rank, int R, int maxr,
+                          unsigned* __restrict__ seqs, unsigned* __restrict__ err, unsigned wait_limit) {
+    const int lane = blockIdx.y;
+    const unsigned seq = seqs[5];
+    const int slot = (int) (seq & 1u);
+    __shared__ bool ok;
+    if (threadIdx.x == 0) {
+        bool all = false;
+        const bool gave_up = (*(volatile unsigned*) err & (unsigned) FNX_ERR_TIMEOUT) != 0;
+        for (unsigned it = 0; it < wait_limit && !all && !gave_up; ++it) {
+            all = true;
+            for (int r = 0; r < R; ++r) {
+                if (r == rank) continue;
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(xflag + 2 * R + slot * R + r) : "memory");
+                all = all && v == seq + 1u;
+            }
+        }
+        if (!all) atomicOr(err, (unsigned) FNX_ERR_TIMEOUT);
+        ok = all;
+    }
+    __syncthreads();
+    if (ok && lane_own[lane] < 0) {
+        const int r0 = lane_row0[lane], nr = lane_row0[lane + 1] - r0;
+        const size_t n4 = (size_t) nr * width / 4;
+        const float4* src = reinterpret_cast<const float4*>(xrows + ((size_t) slot * maxr + r0) * width);
+        float4* dst = reinterpret_cast<float4*>(mix + (size_t) r0 * width);
+        for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t) gridDim.x * blockDim.x) dst[i] = __ldcv(src + i);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(&seqs[7], 1u) == gridDim.x * gridDim.y - 1) {
+        seqs[7] = 0;
+        seqs[5] = seq + 1u;
+    }
+}
+
 // ---- one MoE block on T rows of residual R: R += experts(rmsnorm(R))
 // next_norm: the norm weights of the projection that reads R next; with them (single rank) the combine leaves that projection's
 // image of the rows in e->d_img and *img_ready is set
@@ -593,22 +673,41 @@ __global__ void k_scatter_drafts(int* __restrict__ out, const int* __restrict__ 
 }
 
 // mixer of one layer over the lanes' rows: R += out_proj(mixer(in_proj(rmsnorm(R))))
+// the gather of the mixers' rows among the ranks (every rank ran its own sequences' lanes only)
+static int enqueue_dp_gather(fnx_engine* e, int width, int n_lanes, const int* d_row0) {
+    const Dims d = dims(e->c);
+    const dim3 grid(8, n_lanes);
+    k_dp_send<<<grid, 256, 0, e->st>>>(e->mix, width, e->d_lane_own, d_row0, n_lanes, e->d_peer_x, e->x_off_rows, e->d_peer_flag, e->c.ep_rank, e->c.ep_size, d.MAXR,
+                                         e->d_xseq);
+    FNX_LAUNCH_OK("k_dp_send");
+    k_dp_recv<<<grid, 256, 0, e->st>>>(e->xbuf + e->x_off_rows, e->xflag, e->mix, width, e->d_lane_own, d_row0, n_lanes, e->c.ep_rank, e->c.ep_size, d.MAXR, e->d_xseq,
+                                         e->err, e->wait_limit);
+    FNX_LAUNCH_OK("k_dp_recv");
+    return FNX_OK;
+}
+
 static int enqueue_mixer_lanes(fnx_engine* e, const LayerW& L, float* R, int T, int n_lanes, int max_lane_rows, const int* d_lane_seq, const int* d_row0,
                                const int* d_pos, bool img = false) {
     const Dims d = dims(e->c);
+    // expert-parallel ranks with the peer-memory exchange open: every rank runs its own sequences' lanes (d_lane_own holds -1
+    // for the others', which the lane kernels skip) and the output rows are gathered before the output projection
+    const bool dp = e->c.ep_size > 1 && e->ep_peers && e->dp_mixers;
+    const int* lanes = dp ? e->d_lane_own : d_lane_seq;
     FNX_TRY(enqueue_dense(e, L.w_in, L.in_rows, d.H, R, d.H, T, L.norm1, e->proj, e->proj_ld, 0, img));
     if (L.attn) {
         float* qg = e->proj;
         float* k = e->proj + d.q_rows;
         float* v = k + d.kv_rows;
         FNX_TRY(fnx_attn_prep_append_lanes(qg, e->proj_ld, k, e->proj_ld, v, e->proj_ld, L.qn, L.kn, L.kc, L.vc, (size_t) e->cache_rows, n_lanes, max_lane_rows, d.nq,
-                                           d.nkv, d.hd, d.nrot, d_pos, d_lane_seq, d_row0, e->c.eps, e->c.rope_base, e->st));
-        FNX_TRY(fnx_attn_lanes(qg, e->proj_ld, L.kc, L.vc, (size_t) e->cache_rows, e->mix, T, n_lanes, d.nq, d.nkv, d.hd, d_pos, d_lane_seq, d_row0, e->att_scratch, e->st));
+                                           d.nkv, d.hd, d.nrot, d_pos, lanes, d_row0, e->c.eps, e->c.rope_base, e->st));
+        FNX_TRY(fnx_attn_lanes(qg, e->proj_ld, L.kc, L.vc, (size_t) e->cache_rows, e->mix, T, n_lanes, d.nq, d.nkv, d.hd, d_pos, lanes, d_row0, e->att_scratch, e->st));
+        if (dp) FNX_TRY(enqueue_dp_gather(e, d.nq * d.hd, n_lanes, d_row0));
         return enqueue_dense(e, L.w_out, d.H, d.nq * d.hd, e->mix, d.nq * d.hd, T, nullptr, R, d.H, 1);
     }
     FNX_TRY(fnx_gdn_core_lanes(e->proj, e->proj_ld, e->proj + d.gdn_ch + d.nv * d.hs, e->proj_ld, L.hist_pool, (size_t) e->NS * 3 * d.gdn_ch, L.convw, L.dt, L.a, L.gnorm,
-                               L.S_pool, (size_t) e->NS * d.nv * d.hs * d.hs, e->d_cur, e->NS, d_lane_seq, d_row0, n_lanes, max_lane_rows, e->mix, d.nk, d.nv, d.hs,
+                               L.S_pool, (size_t) e->NS * d.nv * d.hs * d.hs, e->d_cur, e->NS, lanes, d_row0, n_lanes, max_lane_rows, e->mix, d.nk, d.nv, d.hs,
                                e->c.eps, e->st));
+    if (dp) FNX_TRY(enqueue_dp_gather(e, d.nv * d.hs, n_lanes, d_row0));
     return enqueue_dense(e, L.w_out, d.H, d.nv * d.hs, e->mix, d.nv * d.hs, T, nullptr, R, d.H, 1);
 }
 
@@ -764,11 +863,14 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_img, (size_t) ((d.MAXR + 7) / 8) * fnx_dense_image_bytes(d.H)));
         if (const char* nf = getenv("FNX_NO_IMAGE")) e->use_img = nf[0] != '1';
         if (c.ep_size > 1) {
-            FNX_TRY(dalloc(e, &e->xbuf, (size_t) 2 * c.ep_size * d.MAXR * d.H, "buf.ep_x"));
-            FNX_TRY(dalloc(e, &e->xflag, (size_t) 2 * c.ep_size, "buf.ep_flag"));
+            e->mix_width = mixw;
+            e->x_off_rows = (size_t) 2 * c.ep_size * d.MAXR * d.H;
+            FNX_TRY(dalloc(e, &e->xbuf, e->x_off_rows + (size_t) 2 * d.MAXR * mixw, "buf.ep_x"));
+            FNX_TRY(dalloc(e, &e->xflag, (size_t) 4 * c.ep_size, "buf.ep_flag"));
+            if (const char* nd = getenv("FNX_NO_DP")) e->dp_mixers = nd[0] != '1';
             FNX_TRY(dalloc(e, &e->d_peer_x, (size_t) c.ep_size));
             FNX_TRY(dalloc(e, &e->d_peer_flag, (size_t) c.ep_size));
-            FNX_TRY(dalloc(e, &e->d_xseq, 4));
+            FNX_TRY(dalloc(e, &e->d_xseq, 8));
         }
         FNX_TRY(dalloc(e, &e->best_i, d.MAXR, "buf.best_i"));
         FNX_TRY(dalloc(e, &e->best_v, d.MAXR, "buf.best_v"));
@@ -786,6 +888,7 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->d_step, c.n_seq, "seq.step"));
         FNX_TRY(dalloc(e, &e->d_lk, FNX_MAX_ROWS + 4, "buf.lookup"));
         FNX_TRY(dalloc(e, &e->d_lane_seq, FNX_MAX_ROWS, "buf.lane_seq"));
+        FNX_TRY(dalloc(e, &e->d_lane_own, FNX_MAX_ROWS));
         FNX_TRY(dalloc(e, &e->d_lane_row0, FNX_MAX_ROWS + 1, "buf.lane_row0"));
         FNX_TRY(dalloc(e, &e->d_mlane_row0, FNX_MAX_ROWS + 1, "buf.mtp_lane_row0"));
         FNX_TRY(dalloc(e, &e->d_ident_row0, FNX_MAX_ROWS + 1, "buf.ident_row0"));
@@ -1316,6 +1419,11 @@ extern "C" int fnx_engine_verify_lanes(fnx_engine* e, int n_lanes, const int* h_
     for (int j = 0; j < n_lanes; ++j) ht[j] = h_seqs[j];
     for (int j = 0; j <= n_lanes; ++j) ht[FNX_MAX_ROWS + j] = j * rows;
     FNX_CUDA_OK(cudaMemcpyAsync(e->d_lane_seq, ht, sizeof(int) * n_lanes, cudaMemcpyHostToDevice, e->st));
+    {   // the table the mixers see on expert-parallel ranks: this rank's own sequences (sequence % ranks == rank)
+        int* ho = hs + 5 * FNX_MAX_ROWS;
+        for (int j = 0; j < n_lanes; ++j) ho[j] = h_seqs[j] % e->c.ep_size == e->c.ep_rank ? h_seqs[j] : -1;
+        FNX_CUDA_OK(cudaMemcpyAsync(e->d_lane_own, ho, sizeof(int) * n_lanes, cudaMemcpyHostToDevice, e->st));
+    }
     FNX_CUDA_OK(cudaMemcpyAsync(e->d_lane_row0, ht + FNX_MAX_ROWS, sizeof(int) * (n_lanes + 1), cudaMemcpyHostToDevice, e->st));
     if (e->sampling_on)
         for (int j = 0; j < n_lanes; ++j) {

@@ -219,7 +219,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS)
                      const int* __restrict__ lane_row0, float* __restrict__ y, int nk, int nv, float eps) {
     extern __shared__ __align__(16) float sm[];
     const int lane = blockIdx.y, row0 = lane_row0[lane], T = lane_row0[lane + 1] - row0, seq = lane_seq[lane];
-    if (T <= 0) return;
+    if (T <= 0 || seq < 0) return;   // (a negative sequence: another rank's lane)
     gdn_body(qkvz + (size_t) row0 * stride, stride, ab + (size_t) row0 * ldab, ldab, hist_pool + seq * hist_stride, convw, dt, a_, nw, S_pool + seq * s_stride,
              cur[seq], NS, nullptr, y + (size_t) row0 * nv * GDN_HS, nk, nv, T, eps, sm);
 }
