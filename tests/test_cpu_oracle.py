@@ -258,3 +258,45 @@ def test_expert_parallel_partial_sums_two_ranks_gloo(tmp_path):
     outs = [p.communicate(timeout=240)[0] for p in procs]
     for p, o in zip(procs, outs):
         assert p.returncode == 0, o
+
+
+# ------------------------------------------------------------------------------------------------ sequence-sharded mixers, 2 ranks on gloo
+_DP_WORKER = r"""
+import sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[3])
+import oracle as O
+rank, world = int(sys.argv[1]), 2
+dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{sys.argv[2]}", rank=rank, world_size=world)
+# a lanes window of 3 sequences x 2 rows: every rank has every row's queries, but the caches of its own sequences only
+rng = np.random.default_rng(7)
+nq, nkv, hd, rows, seqs = 4, 1, 256, 2, [0, 1, 2]
+pos = {0: 5, 1: 9, 2: 3}
+qg = rng.standard_normal((len(seqs) * rows, nq, 2 * hd)).astype(np.float32)
+caches = {s: ((rng.standard_normal((pos[s] + rows, nkv, hd))).astype(np.float16).view(np.uint16),
+              (rng.standard_normal((pos[s] + rows, nkv, hd))).astype(np.float16).view(np.uint16)) for s in seqs}
+full = np.concatenate([O.attn(qg[j * rows:(j + 1) * rows], caches[s][0], caches[s][1], pos[s], None) for j, s in enumerate(seqs)])
+# the rule of the engine's lanes windows: lane j runs on rank seq % world; the others' rows are gathered
+mine = np.zeros_like(full)
+own = [s % world == rank for s in seqs]
+for j, s in enumerate(seqs):
+    if own[j]:
+        mine[j * rows:(j + 1) * rows] = O.attn(qg[j * rows:(j + 1) * rows], caches[s][0], caches[s][1], pos[s], None)
+t = torch.from_numpy(mine.copy())
+dist.all_reduce(t)          # disjoint rows: the sum is the gather
+assert sum(own) in (1, 2) and np.array_equal(t.numpy(), full)
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_sequence_sharded_mixers_two_ranks_gloo(tmp_path):
+    """Lanes windows on expert-parallel ranks: each rank computes the attention of its own sequences' lanes (sequence % ranks
+    == rank) and the rows are gathered: the gathered rows equal the single-rank result bit for bit."""
+    script = tmp_path / "dp_worker.py"
+    script.write_text(_DP_WORKER)
+    port = 31500 + (abs(hash(str(tmp_path))) % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(port), str(ROOT)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o
