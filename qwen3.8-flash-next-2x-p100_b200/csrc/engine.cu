@@ -1148,6 +1148,7 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
         FNX_TRY(fnx_embed_rows(e->embed, e->d_ptok, nt, d.H, e->pR, e->st));
         for (size_t l = 0; l < e->layers.size(); ++l) {
             const LayerW& L = e->layers[l];
+            e->launches += 3 + (L.attn ? 3 : 3) + 3 + 2 + 7;   // this layer's kernels: projections 3 + 3, mixer 3, router 2, experts 7
             mark(PH_INPROJ, true);
             FNX_TRY(fnx_dense_prompt(L.w_in, L.in_rows, d.H, e->pR, nt, L.norm1, e->c.eps, e->pproj, e->proj_ld, 0, e->p_dense_scratch, e->err, e->st));
             mark(PH_INPROJ, false);
@@ -1201,6 +1202,7 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
         FNX_LAUNCH_OK("prompt context");
         k_prompt_advance<<<1, 1, 0, e->st>>>(e->d_pos + seq, e->d_cur + seq, e->d_ctx_n + seq, nt, e->NS);
         FNX_LAUNCH_OK("prompt advance");
+        e->launches += 3;   // embedding, context, advance
         FNX_CUDA_OK(cudaStreamSynchronize(e->st));   // the token copy's source and the chunk buffers are free again
         s.pos += nt;
         s.cur = (s.cur + nt) % e->NS;

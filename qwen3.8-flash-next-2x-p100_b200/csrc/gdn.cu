@@ -323,13 +323,21 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restric
             const float* kt = row + part * 32;
             const float* qt = row + GDN_HS + part * 32;
             const float gv = row[2 * GDN_HS + GDN_QC], bv = row[2 * GDN_HS + GDN_QC + 1];
+            // (the row's k and q for this warp's 32 key rows: eight 16-byte broadcast reads each)
+            float kv_[32], qv_[32];
+#pragma unroll
+            for (int r = 0; r < 32; r += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(kt + r), b = *reinterpret_cast<const float4*>(qt + r);
+                kv_[r] = a.x; kv_[r + 1] = a.y; kv_[r + 2] = a.z; kv_[r + 3] = a.w;
+                qv_[r] = b.x; qv_[r + 1] = b.y; qv_[r + 2] = b.z; qv_[r + 3] = b.w;
+            }
             float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
 #pragma unroll
             for (int r = 0; r < 32; r += 4) {
-                k0 = fmaf(s[r], kt[r], k0);
-                k1 = fmaf(s[r + 1], kt[r + 1], k1);
-                k2 = fmaf(s[r + 2], kt[r + 2], k2);
-                k3 = fmaf(s[r + 3], kt[r + 3], k3);
+                k0 = fmaf(s[r], kv_[r], k0);
+                k1 = fmaf(s[r + 1], kv_[r + 1], k1);
+                k2 = fmaf(s[r + 2], kv_[r + 2], k2);
+                k3 = fmaf(s[r + 3], kv_[r + 3], k3);
             }
             float* kr = &kred[r0 & 1][0][0];
             kr[part * GDN_QC + lane] = (k0 + k1) + (k2 + k3);
@@ -339,14 +347,14 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restric
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
             for (int r = 0; r < 32; r += 4) {
-                s[r] = fmaf(kt[r], delta, gv * s[r]);
-                s[r + 1] = fmaf(kt[r + 1], delta, gv * s[r + 1]);
-                s[r + 2] = fmaf(kt[r + 2], delta, gv * s[r + 2]);
-                s[r + 3] = fmaf(kt[r + 3], delta, gv * s[r + 3]);
-                a0 = fmaf(s[r], qt[r], a0);
-                a1 = fmaf(s[r + 1], qt[r + 1], a1);
-                a2 = fmaf(s[r + 2], qt[r + 2], a2);
-                a3 = fmaf(s[r + 3], qt[r + 3], a3);
+                s[r] = fmaf(kv_[r], delta, gv * s[r]);
+                s[r + 1] = fmaf(kv_[r + 1], delta, gv * s[r + 1]);
+                s[r + 2] = fmaf(kv_[r + 2], delta, gv * s[r + 2]);
+                s[r + 3] = fmaf(kv_[r + 3], delta, gv * s[r + 3]);
+                a0 = fmaf(s[r], qv_[r], a0);
+                a1 = fmaf(s[r + 1], qv_[r + 1], a1);
+                a2 = fmaf(s[r + 2], qv_[r + 2], a2);
+                a3 = fmaf(s[r + 3], qv_[r + 3], a3);
             }
             ared[r0][part][lane] = (a0 + a1) + (a2 + a3);
         }
