@@ -372,6 +372,28 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
     ms = _max_over_ranks(world, [min(times[1:])])[0]
     wall = min(walls[1:])
     passes = len(times) - 1
+    phases, roof = None, None
+    if not windows:
+        # one more pass, untimed as a whole, with the phases timed by events: the tensor-core products against the dense peak
+        eng.prompt_timing(True)
+        eng.reset()
+        eng.prompt(toks)
+        phases = eng.prompt_timing(False)
+        pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(pk.get("bf16_tflops_sustained", pk.get("bf16_tflops", 1400.0)))
+        L, H, Fn = a.layers, cfg.hidden, cfg.ffn
+        n_attn = sum(1 for l in range(L) if (l + 1) % cfg.attn_every == 0)
+        q_rows, kv_rows = cfg.n_q_head * 2 * cfg.head_dim, cfg.n_kv_head * cfg.head_dim
+        gdn_in = (2 * cfg.gdn_k_head + cfg.gdn_v_head) * cfg.gdn_head_dim + cfg.gdn_v_head * cfg.gdn_head_dim + 2 * cfg.gdn_v_head
+        fl = {"experts": 2.0 * n * (cfg.top_k + 1) * 3 * H * Fn * L,
+              "in_proj": 2.0 * n * H * (n_attn * (q_rows + 2 * kv_rows) + (L - n_attn) * gdn_in),
+              "out_proj": 2.0 * n * H * (n_attn * cfg.n_q_head * cfg.head_dim + (L - n_attn) * cfg.gdn_v_head * cfg.gdn_head_dim),
+              "attention": 4.0 * cfg.n_q_head * cfg.head_dim * (n * (n + 1) / 2.0) * n_attn}
+        tf = {k: fl[k] / (phases[k] * 1e-3) / 1e12 for k in fl if phases.get(k, 0) > 0}
+        roof = {"bound": "tensor", "kernel": "k_pf_gemm (grouped expert products, tcgen05)", "achieved": tf.get("experts"), "peak": peak, "unit": "TFLOP/s",
+                "frac": tf.get("experts", 0.0) / peak, "peak_kind": "measured (sustained)" if pk else "fallback", "traffic": None,
+                "tflops_by_phase": tf, "note": "device ms per phase from CUDA events around the phases of every layer and chunk, in an extra pass of the same prompt; "
+                "attention runs on mma.sync, the projections and experts on tcgen05"}
     line = {"metric": "prefill tok/s (cold prompt)", "value": n / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": passes, "warmup": 1, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
             "config": {"workload": f"configuration 3: cold prefill of {n} uniform-random tokens (seed 3) " +
@@ -380,7 +402,7 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
             "clocks": clk, "gpu_launches": int((c1[0] - c0[0]) / passes),
             "e2e": {"value": n / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * n + 4 * n, "d2h_bytes_per_step": 0, "wall_ms_per_step": wall * 1e3},
             "windows": (n + cfg.max_rows - 1) // cfg.max_rows, "us_per_window": ms * 1e3 / ((n + cfg.max_rows - 1) // cfg.max_rows),
-            "path": "windows" if windows else "prompt pass"}
+            "path": "windows" if windows else "prompt pass", "phases_ms": phases, "roofline": roof}
     if rank == 0:
         print(json.dumps(line))
     eng.close()

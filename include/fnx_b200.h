@@ -301,6 +301,10 @@ int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const int* h_par
  * to f16 where the window path uses two int8 levels, so the states agree with the window path to the parity tolerance, not
  * bit for bit.  Single rank only (FNX_E_ARG on an expert-parallel engine).  Synchronises. */
 int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n);
+/* Tracing of the prompt pass (the reference's FNX_PROF idea, engine/src/engine.cu:1382-1529): with on != 0 the following
+ * fnx_engine_prompt calls time their phases with events (a synchronisation per chunk); h_phase_ms6, when not null, receives the
+ * last timed prompt's device ms: input projections, attention, DeltaNet, output projections, router, experts. */
+int fnx_engine_prompt_timing(fnx_engine* e, int on, float* h_phase_ms6);
 /* Engine::commit: keeps the n accepted rows h_path[0..n) of the last window of `seq`.  The window buffers (tokens,
  * acceptance result, residual rows) are shared by the engine's sequences: commit (and draft) sequence A before verifying
  * sequence B; a commit or draft for a sequence other than the one verified last returns FNX_E_STATE. */

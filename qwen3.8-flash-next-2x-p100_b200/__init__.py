@@ -99,6 +99,7 @@ _PROTOS = {
     "fnx_engine_reset": (_I, [_P, _I]),
     "fnx_engine_verify": (_I, [_P, _I, _P, _P, _I, _P]),
     "fnx_engine_prompt": (_I, [_P, _I, _P, _I]),
+    "fnx_engine_prompt_timing": (_I, [_P, _I, _P]),
     "fnx_engine_state_bytes": (_Z, [_P, _I, _I]),
     "fnx_engine_save_state": (_I, [_P, _I, _I, _P, _Z]),
     "fnx_engine_load_state": (_I, [_P, _I, _P, _Z]),
@@ -605,6 +606,13 @@ class Engine:
         import ctypes as C
         n = len(tokens)
         check(lib().fnx_engine_prompt(self._h, seq, (C.c_int * n)(*tokens), n))
+
+    def prompt_timing(self, on: bool = True):
+        """Switches the prompt pass's phase timing; returns the last timed prompt's ms per phase (a dict)."""
+        import ctypes as C
+        ms = (C.c_float * 6)()
+        check(lib().fnx_engine_prompt_timing(self._h, 1 if on else 0, ms))
+        return dict(zip(("in_proj", "attention", "deltanet", "out_proj", "router", "experts"), [float(v) for v in ms]))
 
     def prefill(self, tokens, seq: int = 0):
         """Reads a prompt by running it through chained verify windows and keeping every row."""

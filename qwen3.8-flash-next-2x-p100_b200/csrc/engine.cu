@@ -115,6 +115,8 @@ struct fnx_engine {
     int prompt_chunk = 16384;
     float *pR = nullptr, *pproj = nullptr, *pmix = nullptr, *plogits = nullptr, *ptopw = nullptr;
     int *ptopi = nullptr, *d_ptok = nullptr;
+    bool prompt_timing = false;     // fnx_engine_prompt_timing: time the prompt pass's phases with events
+    float prompt_phase_ms[6] = {0, 0, 0, 0, 0, 0};   // the last timed prompt: in-proj, attention, DeltaNet, out-proj, router, experts
     void *p_moe_scratch = nullptr, *p_dense_scratch = nullptr, *p_gdn_scratch = nullptr, *p_attn_scratch = nullptr;
     // the draft layer's own head over a draft vocabulary (config draft_vocab > 0): dvn rows, row -> token id in d_dvocab;
     // otherwise the main head and no map
@@ -1130,7 +1132,9 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     FNX_CUDA_OK(cudaMemsetAsync(e->err, 0, sizeof(unsigned), e->st));
     // FNX_PROMPT_PHASES=1: the device time of each kind of phase, summed over the prompt, to stderr (a tracing aid)
-    const bool phases = getenv("FNX_PROMPT_PHASES") != nullptr;
+    const bool phases = getenv("FNX_PROMPT_PHASES") != nullptr || e->prompt_timing;
+    if (phases)
+        for (float& v : e->prompt_phase_ms) v = 0.f;
     enum { PH_INPROJ, PH_ATTN, PH_GDN, PH_OUTPROJ, PH_ROUTER, PH_MOE, PH_N };
     static const char* const ph_name[PH_N] = {"in-proj", "attention", "deltanet", "out-proj", "router", "experts"};
     std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> marks;
@@ -1194,9 +1198,12 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
                 cudaEventDestroy(m.second.second);
             }
             marks.clear();
-            fprintf(stderr, "prompt chunk at %d (%d rows):", s.pos, nt);
-            for (int i = 0; i < PH_N; ++i) fprintf(stderr, " %s %.1f ms", ph_name[i], sum[i]);
-            fprintf(stderr, "\n");
+            for (int i = 0; i < PH_N; ++i) e->prompt_phase_ms[i] += sum[i];
+            if (getenv("FNX_PROMPT_PHASES")) {
+                fprintf(stderr, "prompt chunk at %d (%d rows):", s.pos, nt);
+                for (int i = 0; i < PH_N; ++i) fprintf(stderr, " %s %.1f ms", ph_name[i], sum[i]);
+                fprintf(stderr, "\n");
+            }
         }
         k_prompt_context<<<(nt + 255) / 256, 256, 0, e->st>>>(e->d_ctx + (size_t) seq * e->cache_rows, e->d_ctx_n + seq, e->d_ptok, nt);
         FNX_LAUNCH_OK("prompt context");
@@ -1218,6 +1225,13 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
     const int zero = 0;
     FNX_TRY(fnx_engine_verify(e, seq, h_tok + n - 1, nullptr, 1, nullptr));
     return fnx_engine_commit(e, seq, &zero, 1);
+}
+
+extern "C" int fnx_engine_prompt_timing(fnx_engine* e, int on, float* h_phase_ms6) {
+    FNX_REQUIRE(e, "fnx_engine_prompt_timing: null engine");
+    e->prompt_timing = on != 0;
+    if (h_phase_ms6) memcpy(h_phase_ms6, e->prompt_phase_ms, sizeof e->prompt_phase_ms);
+    return FNX_OK;
 }
 
 extern "C" int fnx_engine_commit(fnx_engine* e, int seq, const int* h_path, int n) {

@@ -291,6 +291,35 @@ def test_config0_moe_block_at_full_size(F, O, T):
         assert rel_err(acc, ref_out) < TOL_GEMV
 
 
+def test_prefill_moe_at_full_size_matches_the_decode_path_and_the_oracle(F, O):
+    """The prompt-sized MoE block at the benchmark's own size (512 experts of width 512, hidden 2048, top-10) over 16,384 rows:
+    ~320 rows per expert, so most experts run two jobs (256 rows + a ragged tail).  Sampled rows against the decode kernels
+    (themselves checked against the oracle at this size) and a few against the oracle directly."""
+    import torch
+    E, H, Fn, K, T = 512, 2048, 512, 10, 16384
+    fx = _config0_fixture(F)
+    x = torch.randn((T, H), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    topi, topw, logits = F.router_rows(fx["wr"], x, K)
+    cnt = torch.bincount(topi.flatten().long(), minlength=E)
+    assert int(cnt.max().item()) > 256 and int((cnt > 256).sum().item()) > E // 2      # most experts need a second job
+    out, err = F.moe_prefill(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], topi, topw, logits, x, Fn)
+    assert int(err.item()) == 0
+    rows = torch.randperm(T, generator=torch.Generator().manual_seed(6))[:40].sort().values.cuda()
+    xs = x[rows].contiguous()
+    got = out[rows].cpu().numpy()
+    dec = []
+    for t0 in range(0, 40, 20):
+        route = F.router_route(fx["wr"], xs[t0:t0 + 20].contiguous(), K)
+        o, _, _ = F.moe_experts(fx["gu_t"], fx["dn_t"], fx["sh_gu_t"], fx["sh_dn_t"], route, xs[t0:t0 + 20].contiguous(), Fn, K)
+        assert int(route["err"].item()) == 0
+        dec.append(o)
+        # (the two routers agree on these rows, or the comparison below means nothing)
+        assert torch.equal(route["topi"].sort(dim=1).values, topi[rows[t0:t0 + 20]].sort(dim=1).values)
+    assert rel_err(got, torch.cat(dec).cpu().numpy()) < 3e-3
+    ref, _, _, _ = O.moe(fx["wr"].cpu().numpy(), fx["gu_g"], fx["dn_g"], fx["sh_gu_g"], fx["sh_dn_g"], xs[:8].cpu().numpy(), Fn, K)
+    assert rel_err(got[:8], ref) < 3e-3
+
+
 def test_router_many_tokens_pick_one_expert(F, O):
     # every row identical: all rows pick the same experts, so jobs split into groups of 4 rows
     E, H, K, T = 32, 1024, 4, 9
@@ -367,7 +396,7 @@ def test_attention_matches_oracle(F, O, pos0, T, tree):
 
 
 @pytest.mark.parametrize("pos0,T", [(0, 1), (0, 50), (333, 77), (5000, 13)])
-def test_prompt_attention_matches_windows(F, pos0, T):
+def test_prompt_attention_matches_windows(F, O, pos0, T):
     """A prompt's rows in one call (twelve rows per block, f16 queries, no splits) against chained windows of the window form:
     the same cache rows appended, outputs to the f16-query tolerance."""
     nq, nkv, hd, nrot = 16, 2, 256, 64
@@ -396,6 +425,9 @@ def test_prompt_attention_matches_windows(F, pos0, T):
     got = F.attn_prompt(q_p, p_kc, p_vc, pos)
     assert torch.equal(p_kc[:pos0 + T], w_kc[:pos0 + T]) and torch.equal(p_vc[:pos0 + T], w_vc[:pos0 + T])
     assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 2e-3
+    if T <= 20:   # and against the oracle (a chain: no parents)
+        ref = O.attn(q_p.cpu().numpy(), p_kc.cpu().numpy().view(np.uint16), p_vc.cpu().numpy().view(np.uint16), pos0, None)
+        assert rel_err(got.cpu().numpy(), ref) < 2e-3
 
 
 # ------------------------------------------------------------------------------------------------ DeltaNet
@@ -429,7 +461,7 @@ def test_gdn_core_matches_oracle(F, O, T, tree, nk, nv):
 
 
 @pytest.mark.parametrize("T,NS", [(1, 4), (37, 9), (64, 33), (99, 33)])
-def test_gdn_prompt_equals_chained_windows(F, T, NS):
+def test_gdn_prompt_equals_chained_windows(F, O, T, NS):
     """The prompt form (conv / scan / norm in three launches, state in registers across all rows) against chained windows of
     NS - 1 rows of the window kernel, each kept whole: outputs, the final state and the final history."""
     nk, nv, hs, cur = 2, 4, 128, 2
@@ -448,6 +480,11 @@ def test_gdn_prompt_equals_chained_windows(F, T, NS):
     Sp, Hp = dev(S0), dev(h0)
     got = F.gdn_prompt(dev(qkvz), dev(ab), Hp, *args, Sp, cur, nk, nv, hs)
     assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 1e-4
+    if T <= 40:   # and against the row-by-row oracle over the whole chain at once
+        So = np.concatenate([S0[cur:cur + 1], np.zeros((T + 1, nv, hs, hs), np.float32)])
+        ho = np.concatenate([h0[cur:cur + 1], np.zeros((T + 1, 3, ch), np.float32)])
+        ref = O.gdn_core(qkvz, ab, ho, convw, dt, a, nw, So, 0, None, nk, nv, hs)
+        assert rel_err(got.cpu().numpy(), ref) < 2e-3
     out = (cur + T) % NS
     assert out == c
     assert rel_err(Sp[out].cpu().numpy(), Sw[out].cpu().numpy()) < 1e-4
