@@ -112,7 +112,7 @@ struct fnx_engine {
     uint8_t* d_img = nullptr;
     bool use_img = true;
     // the prompt pass (fnx_engine_prompt): buffers for a chunk of prompt_chunk rows, made at its first call
-    int prompt_chunk = 16384;
+    int prompt_chunk = 40960;
     float *pR = nullptr, *pproj = nullptr, *pmix = nullptr, *plogits = nullptr, *ptopw = nullptr;
     int *ptopi = nullptr, *d_ptok = nullptr;
     bool prompt_timing = false;     // fnx_engine_prompt_timing: time the prompt pass's phases with events
