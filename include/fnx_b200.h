@@ -35,6 +35,7 @@ enum { FNX_ERR_TIMEOUT = 1, FNX_ERR_NONFINITE = 2, FNX_ERR_LOGITS = 16 };
 enum { FNX_TOPK_N = 64,      /* sampler candidates per row (TOPK_N, engine/src/kernels.hpp:441) */
        FNX_MAX_ROWS = 32,    /* rows (tree nodes) of one verify window */
        FNX_JOB_TOK = 4,      /* activation rows of one expert job */
+       FNX_DENSE_ROWS = 12,  /* activation rows of one fnx_dense call (three row groups of four) */
        FNX_LANE_ROWS = 5,    /* rows of one lane of a batched window */
        FNX_ATTN_STATIC_MAX_SLOTS = 16384 };   /* (row, head, split) partials fnx_attn_static's built-in scratch holds */
 
@@ -56,13 +57,15 @@ int fnx_iq3s_quantize(const float* w, void* ggml_blocks, size_t n, fnx_stream st
 int fnx_fill_normal(float* out, size_t n, float sigma, uint64_t seed, uint32_t stream_id, fnx_stream st);
 
 /* ---------------------------------------------------------------------------------------------- dense GEMV
- * y[t][r] (+)= W[r] . xin[t] for t < T (T <= 8 per call), W an IQ3_S tile matrix; xin[t] = x[t], or
+ * y[t][r] (+)= W[r] . xin[t] for t < T (T <= fnx_dense_rows(cols) per call: FNX_DENSE_ROWS up to 2048 columns, 8 beyond, where
+ * three row groups' images no longer fit the block's shared memory), W an IQ3_S tile matrix; xin[t] = x[t], or
  * rmsnorm(x[t]) * norm_w when norm_w is not null.  Replaces q8s_gemv / mmvq / rms_norm_rows
  * (engine/src/kernels.hpp:49-52, 405-406).  rows % 16 == 0; cols in {256, 512, 1024, 2048, 4096}. */
+int fnx_dense_rows(int cols);
 int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps,
               float* y, int ldy, int accumulate, unsigned* err, fnx_stream st);
 /* fnx_dense over rows whose quantised image a producer already left on the device (fnx_moe_combine_image): ximg = the image of
- * the call's T rows (fnx_dense_image_bytes(cols) bytes per 8 rows; 16-byte aligned), normed != 0 when it is the image of
+ * the call's T rows (fnx_dense_image_bytes(cols) bytes per FNX_DENSE_ROWS rows; 16-byte aligned), normed != 0 when it is the image of
  * rmsnorm(x) * norm_w.  The blocks copy the image instead of each quantising the rows (the reference quantises a row once
  * for all its consumers the same way: quantize_q8_1 / q8_twin, engine/src/kernels.hpp:49-52).  Same bits as fnx_dense. */
 size_t fnx_dense_image_bytes(int cols);
@@ -113,7 +116,7 @@ int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, const void* 
 int fnx_moe_combine(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
                     int K, int e_lo, int e_hi, int add_shared, float* out, int accumulate, fnx_stream st);
 /* fnx_moe_combine(part, ..., 0, E, 1, R, 1) that also leaves the image of rmsnorm(R[t]) * img_norm_w for fnx_dense_image
- * (ceil(T / 8) * fnx_dense_image_bytes(H) bytes, 16-byte aligned): the rows are quantised once, by the kernel that completes
+ * (ceil(T / FNX_DENSE_ROWS) * fnx_dense_image_bytes(H) bytes, 16-byte aligned: one image per FNX_DENSE_ROWS rows): the rows are quantised once, by the kernel that completes
  * them, instead of by every block of the next projection.  R gets the same bits as from fnx_moe_combine. */
 int fnx_moe_combine_image(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
                           int K, float* R, void* img_out, const float* img_norm_w, fnx_stream st);

@@ -21,6 +21,7 @@ _LIB = None
 TOPK_N = 64
 MAX_ROWS = 32
 JOB_TOK = 4
+DENSE_ROWS = 12     # rows of one fnx_dense call (FNX_DENSE_ROWS)
 IQ3S_BLOCK = 110
 
 
@@ -60,6 +61,7 @@ _PROTOS = {
     "fnx_iq3s_quantize": (_I, [_P, _P, _Z, _P]),
     "fnx_fill_normal": (_I, [_P, _Z, _F, _U64, _U32, _P]),
     "fnx_debug_profile_buffer": (_I, [_P]),
+    "fnx_dense_rows": (_I, [_I]),
     "fnx_dense": (_I, [_P, _I, _I, _P, _I, _I, _P, _F, _P, _I, _I, _P, _P]),
     "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "fnx_router_rows": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
@@ -224,8 +226,9 @@ def dense(W, rows: int, cols: int, x, norm_w=None, eps: float = 1e-6, out=None, 
     if out is None:
         out = torch.zeros((T, rows), dtype=torch.float32, device=x.device)
     err = new_err(x.device) if err is None else err
-    for t0 in range(0, T, 8):
-        nt = min(8, T - t0)
+    per = lib().fnx_dense_rows(cols)
+    for t0 in range(0, T, per):
+        nt = min(per, T - t0)
         check(lib().fnx_dense(ptr(W), rows, cols, ptr(x[t0:]), x.stride(0), nt, ptr(norm_w), eps, ptr(out[t0:]), out.stride(0),
                               1 if accumulate else 0, ptr(err), _stream()))
     return out, err
@@ -275,7 +278,7 @@ def moe_combine_image(part, route, T: int, E: int, H: int, K: int, R, next_norm_
     """R += the weighted expert outputs (fnx_moe_combine, accumulating); returns the image of rmsnorm(R) * next_norm_w."""
     import torch
     L = lib()
-    img = torch.zeros(((T + 7) // 8) * L.fnx_dense_image_bytes(H), dtype=torch.uint8, device=R.device)
+    img = torch.zeros(((T + DENSE_ROWS - 1) // DENSE_ROWS) * L.fnx_dense_image_bytes(H), dtype=torch.uint8, device=R.device)
     check(L.fnx_moe_combine_image(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, ptr(R), ptr(img),
                                   ptr(next_norm_w), _stream()))
     return img
@@ -296,15 +299,15 @@ def dense_prompt(W, rows: int, cols: int, x, norm_w=None, eps: float = 1e-6, out
 
 
 def dense_image(W, rows: int, cols: int, img, T: int, normed: bool = True, eps: float = 1e-6, err=None):
-    """fnx_dense over rows given as the image a producer left (T rows, in calls of 8): y [T][rows]."""
+    """fnx_dense over rows given as the image a producer left (T rows, in calls of DENSE_ROWS): y [T][rows]."""
     import torch
     y = torch.empty((T, rows), dtype=torch.float32, device=img.device)
     err = new_err(img.device) if err is None else err
     L = lib()
     stride = L.fnx_dense_image_bytes(cols)
-    for t0 in range(0, T, 8):
-        nt = min(8, T - t0)
-        check(L.fnx_dense_image(ptr(W), rows, cols, img.data_ptr() + (t0 // 8) * stride, nt, 1 if normed else 0, eps, y.data_ptr() + t0 * rows * 4,
+    for t0 in range(0, T, DENSE_ROWS):
+        nt = min(DENSE_ROWS, T - t0)
+        check(L.fnx_dense_image(ptr(W), rows, cols, img.data_ptr() + (t0 // DENSE_ROWS) * stride, nt, 1 if normed else 0, eps, y.data_ptr() + t0 * rows * 4,
                                 rows, 0, ptr(err), _stream()))
     return y
 

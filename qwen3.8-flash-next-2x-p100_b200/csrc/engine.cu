@@ -108,7 +108,7 @@ struct fnx_engine {
     fnx_job* jobs = nullptr;
     unsigned* err = nullptr;
     void* att_scratch = nullptr;
-    // the image of the new residual rows that the combine leaves for the next projection (single rank; one per 8 rows)
+    // the image of the new residual rows that the combine leaves for the next projection (single rank; one per FNX_DENSE_ROWS rows)
     uint8_t* d_img = nullptr;
     bool use_img = true;
     // the prompt pass (fnx_engine_prompt): buffers for a chunk of prompt_chunk rows, made at its first call
@@ -542,14 +542,15 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T, const fl
     return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, 0, 1, R, 1, e->st);
 }
 
-// dense projection of up to MAXR rows in calls of 8
+// dense projection of up to MAXR rows in calls of fnx_dense_rows(cols) rows
 // (img: the rows' image in e->d_img is that of x normed by norm_w: the blocks copy it instead of quantising the rows)
 static int enqueue_dense(fnx_engine* e, const uint8_t* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float* y, int ldy,
                          int accumulate, bool img = false) {
-    for (int t0 = 0; t0 < T; t0 += 8) {
-        const int nt = T - t0 < 8 ? T - t0 : 8;
+    const int per = img ? FNX_DENSE_ROWS : fnx_dense_rows(cols);   // (an image holds FNX_DENSE_ROWS rows: its products have <= 2048 columns)
+    for (int t0 = 0; t0 < T; t0 += per) {
+        const int nt = T - t0 < per ? T - t0 : per;
         if (img) {
-            FNX_TRY(fnx_dense_image(W, rows, cols, e->d_img + (size_t) (t0 / 8) * fnx_dense_image_bytes(cols), nt, norm_w != nullptr, e->c.eps,
+            FNX_TRY(fnx_dense_image(W, rows, cols, e->d_img + (size_t) (t0 / FNX_DENSE_ROWS) * fnx_dense_image_bytes(cols), nt, norm_w != nullptr, e->c.eps,
                                     y + (size_t) t0 * ldy, ldy, accumulate, e->err, e->st));
             continue;
         }
@@ -862,8 +863,9 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->hbuf, (size_t) d.P * d.F, "buf.h"));
         FNX_TRY(dalloc(e, &e->part, (size_t) d.P * d.H, "buf.part"));
         FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
-        FNX_TRY(dalloc(e, &e->d_img, (size_t) ((d.MAXR + 7) / 8) * fnx_dense_image_bytes(d.H)));
+        FNX_TRY(dalloc(e, &e->d_img, (size_t) ((d.MAXR + FNX_DENSE_ROWS - 1) / FNX_DENSE_ROWS) * fnx_dense_image_bytes(d.H)));
         if (const char* nf = getenv("FNX_NO_IMAGE")) e->use_img = nf[0] != '1';
+        if (d.H > 2048) e->use_img = false;   // (an image's product takes FNX_DENSE_ROWS rows a call, which wider rows do not fit)
         if (c.ep_size > 1) {
             e->mix_width = mixw;
             e->x_off_rows = (size_t) 2 * c.ep_size * d.MAXR * d.H;

@@ -53,8 +53,8 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) k_iq3s_mmv(const MmvParams p) 
     S.cells = reinterpret_cast<uint2*>(S.bars + MMV_WARPS * R);
     S.scales = reinterpret_cast<float*>(S.cells + (size_t) JMAX * NG * (p.K / 32) * 32);
     S.rs = S.scales + (size_t) JMAX * NG * KB * 8;
-    S.pieces = reinterpret_cast<PieceSlot*>(S.rs + NROW * 16);
-    S.jobs_s = reinterpret_cast<fnx_job*>(S.pieces + MMV_WARPS * 2);
+    S.pieces = S.rs + NROW * 16;
+    S.jobs_s = reinterpret_cast<fnx_job*>(reinterpret_cast<uint8_t*>(S.pieces) + (size_t) MMV_WARPS * 2 * sizeof(PieceSlotT<NG, MODE>));
     unsigned long long* prof = g_mmv_prof ? g_mmv_prof + (size_t) blockIdx.x * MMV_PROF_SLOTS : nullptr;
     int nstamp = 0;
     MMV_STAMP();
@@ -108,11 +108,13 @@ extern "C" int fnx_debug_profile_buffer(void* dev_u64) {
     return FNX_OK;
 }
 
+extern "C" int fnx_dense_rows(int cols) { return cols <= 2048 ? FNX_DENSE_ROWS : 8; }
+
 extern "C" int fnx_dense(const void* W, int rows, int cols, const float* x, int ldx, int T, const float* norm_w, float eps, float* y,
                          int ldy, int accumulate, unsigned* err, fnx_stream st) {
     if (int rc = check_cols(cols)) return rc;
     FNX_REQUIRE(W && x && y && err, "fnx_dense: null pointer");
-    FNX_REQUIRE(T >= 1 && T <= 8, "fnx_dense: %d rows per call (1..8)", T);
+    FNX_REQUIRE(T >= 1 && T <= fnx_dense_rows(cols), "fnx_dense: %d rows per call (1..%d at %d columns)", T, fnx_dense_rows(cols), cols);
     FNX_REQUIRE(rows > 0 && rows % 16 == 0, "fnx_dense: %d output rows, not a multiple of 16", rows);
     FNX_REQUIRE(ldx % 4 == 0 && ((uintptr_t) x & 15) == 0 && ((uintptr_t) W & 15) == 0, "fnx_dense: x and W must be 16-byte aligned");
     MmvParams p{};
@@ -128,7 +130,7 @@ extern "C" int fnx_dense(const void* W, int rows, int cols, const float* x, int 
     p.K = cols;
     p.accumulate = accumulate;
     p.err = err;
-    return T <= 4 ? launch_mmv<1, MAT_DENSE>(p, as_stream(st)) : launch_mmv<2, MAT_DENSE>(p, as_stream(st));
+    return T <= 4 ? launch_mmv<1, MAT_DENSE>(p, as_stream(st)) : T <= 8 ? launch_mmv<2, MAT_DENSE>(p, as_stream(st)) : launch_mmv<3, MAT_DENSE>(p, as_stream(st));
 }
 
 extern "C" int fnx_moe_gate_up(const void* Wgu, size_t expert_stride, int e_base, const void* Wsh, int E, const fnx_job* jobs,
@@ -182,13 +184,13 @@ extern "C" int fnx_moe_down(const void* Wdn, size_t expert_stride, int e_base, c
     return launch_mmv<1, MAT_DOWN>(p, as_stream(st));
 }
 
-extern "C" size_t fnx_dense_image_bytes(int cols) { return stage_image_bytes(2, cols); }
+extern "C" size_t fnx_dense_image_bytes(int cols) { return stage_image_bytes(FNX_DENSE_ROWS / 4, cols); }
 
 extern "C" int fnx_dense_image(const void* W, int rows, int cols, const void* ximg, int T, int normed, float eps, float* y, int ldy, int accumulate,
                                unsigned* err, fnx_stream st) {
     if (int rc = check_cols(cols)) return rc;
     FNX_REQUIRE(W && ximg && y && err, "fnx_dense_image: null pointer");
-    FNX_REQUIRE(T >= 1 && T <= 8, "fnx_dense_image: %d rows per call (1..8)", T);
+    FNX_REQUIRE(T >= 1 && T <= FNX_DENSE_ROWS && cols <= 2048, "fnx_dense_image: %d rows per call (1..%d), %d columns (up to 2048)", T, FNX_DENSE_ROWS, cols);
     FNX_REQUIRE(rows > 0 && rows % 16 == 0, "fnx_dense_image: %d output rows, not a multiple of 16", rows);
     FNX_REQUIRE(((uintptr_t) ximg & 15) == 0 && ((uintptr_t) W & 15) == 0, "fnx_dense_image: the image and W must be 16-byte aligned");
     MmvParams p{};
@@ -203,5 +205,5 @@ extern "C" int fnx_dense_image(const void* W, int rows, int cols, const void* xi
     p.K = cols;
     p.accumulate = accumulate;
     p.err = err;
-    return T <= 4 ? launch_mmv<1, MAT_DENSE>(p, as_stream(st)) : launch_mmv<2, MAT_DENSE>(p, as_stream(st));
+    return T <= 4 ? launch_mmv<1, MAT_DENSE>(p, as_stream(st)) : T <= 8 ? launch_mmv<2, MAT_DENSE>(p, as_stream(st)) : launch_mmv<3, MAT_DENSE>(p, as_stream(st));
 }

@@ -436,13 +436,13 @@ __device__ __forceinline__ void ring_reset(WarpRing& r, int R) {
 
 // a piece of a unit left for the end-of-pass combine: slot [warp][0] = a piece that continues a unit begun by an
 // earlier warp, slot [warp][1] = the first piece of a unit that later warps continue
-struct PieceSlot {
+template <int NG, int MODE>
+struct PieceSlotT {
     int unit;                // -1: none, -2: the warp had no items at all
     int b_lo, b_hi, job, ntok;
-    int orow[8];
-    double v[128];           // [kind (gate|up only: 0 gate, 1 up)][group][16 lanes][4]
+    int orow[4 * NG];
+    double v[(MODE == 1 ? 2 : 1) * NG * 64];   // [kind (gate|up only: 0 gate, 1 up)][group][16 lanes][4]   (MODE 1 = MAT_GATEUP)
 };
-constexpr int PIECE_BYTES = sizeof(PieceSlot);
 
 __device__ __forceinline__ int mat_blocks_per_unit(int mode, int K) { return mode == MAT_GATEUP ? 2 * (K / 256) : K / 256; }
 
@@ -533,12 +533,12 @@ __device__ __forceinline__ void mat_preissue(const MatDesc& m, int ua, int ub, W
 // and output rows for job j.  pieces: [nwarp][2] slots.  Returns false when a wait gave up.  The caller runs a block
 // barrier and then mat_combine().
 template <int NG, int MODE, typename LaneXFn>
-__device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint32_t table_s, WarpRing& ring, PieceSlot* pieces, int warp,
+__device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint32_t table_s, WarpRing& ring, PieceSlotT<NG, MODE>* pieces, int warp,
                                           int nwarp, int lane, LaneXFn&& lane_x) {
     const int KB = m.K / 256, nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
     const unsigned N = (unsigned) (ub - ua) * nbu;   // < 2^26 for any matrix here
     const int i0 = (int) (N * warp / nwarp), i1 = (int) (N * (warp + 1) / nwarp);
-    PieceSlot* mine = pieces + warp * 2;
+    PieceSlotT<NG, MODE>* mine = pieces + warp * 2;
     if (lane == 0) {
         mine[0].unit = i0 < i1 ? -1 : -2;
         mine[1].unit = -1;
@@ -586,7 +586,7 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
             if (b_lo == 0 && b == nbu - 1) {
                 mat_write_unit<NG, MODE, AccT>(m, lu, orow, ntok, lane, gacc, acc);
             } else {
-                PieceSlot* ps = mine + (b_lo == 0 ? 1 : 0);
+                PieceSlotT<NG, MODE>* ps = mine + (b_lo == 0 ? 1 : 0);
                 if (lane == 0) {
                     ps->unit = j * upj + lu;
                     ps->b_lo = b_lo;
@@ -625,8 +625,8 @@ __device__ __forceinline__ bool mat_items(const MatDesc& m, int ua, int ub, uint
 
 // after the block barrier: the warp that holds a unit's first piece adds the later warps' pieces and writes the unit
 template <int NG, int MODE>
-__device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* pieces, int warp, int nwarp, int lane) {
-    const PieceSlot* first = pieces + warp * 2 + 1;
+__device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlotT<NG, MODE>* pieces, int warp, int nwarp, int lane) {
+    const PieceSlotT<NG, MODE>* first = pieces + warp * 2 + 1;
     const int u = first->unit;
     if (u < 0) return;
     const int nbu = mat_blocks_per_unit(MODE, m.K), upj = m.rows / 16;
@@ -642,7 +642,7 @@ __device__ __forceinline__ void mat_combine(const MatDesc& m, const PieceSlot* p
             acc[ng][k] = holder ? (AccT) first->v[((MODE == MAT_GATEUP ? NG + ng : ng) * 16 + l16) * 4 + k] : (AccT) 0;
         }
     for (int ww = warp + 1; ww < nwarp; ++ww) {
-        const PieceSlot* c = pieces + ww * 2;
+        const PieceSlotT<NG, MODE>* c = pieces + ww * 2;
         if (c->unit == -2) continue;
         if (c->unit != u) break;
 #pragma unroll

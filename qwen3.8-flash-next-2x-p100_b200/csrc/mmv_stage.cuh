@@ -54,7 +54,7 @@ template <int NG, int MODE>
 __host__ __device__ inline size_t mmv_smem_bytes(int K, int R, int njobs_max) {
     constexpr int rows = mmv_jmax<MODE>() * 4 * NG;
     return (size_t) CORE_TABLE_BYTES + (size_t) MMV_WARPS * R * (TILE_BYTES + 8) + mmv_image_bytes<NG, MODE>(K) + rows * 16 * sizeof(float) +
-           (size_t) MMV_WARPS * 2 * PIECE_BYTES + (MODE == MAT_DENSE ? 0 : (size_t) njobs_max * sizeof(fnx_job)) + 64;
+           (size_t) MMV_WARPS * 2 * sizeof(PieceSlotT<NG, MODE>) + (MODE == MAT_DENSE ? 0 : (size_t) njobs_max * sizeof(fnx_job)) + 64;
 }
 
 constexpr int MMV_JOB_WORDS = sizeof(fnx_job) / 4, MMV_JOB_REGS = 3;   // job-list words a thread holds across the set-up
@@ -68,7 +68,7 @@ struct StageSmem {
     uint2* cells;           // images: jmax x NG x (K / 32) x 32 cells, then their scales and chunk sums
     float* scales;
     float* rs;
-    PieceSlot* pieces;      // MMV_WARPS x 2
+    void* pieces;           // MMV_WARPS x 2 piece slots (PieceSlotT of the stage's row groups and mode)
     fnx_job* jobs_s;        // njobs_max jobs (expert modes)
 };
 
@@ -267,12 +267,12 @@ __device__ __forceinline__ void stage_run(const MmvParams& p, const StageSmem& S
             }
         };
         if (ok) {
-            ok = mat_items<NG, MODE>(m, uc, ue, S.table_s, ring, S.pieces, warp, NW, lane, lane_x);
+            ok = mat_items<NG, MODE>(m, uc, ue, S.table_s, ring, static_cast<PieceSlotT<NG, MODE>*>(S.pieces), warp, NW, lane, lane_x);
             if (!ok) atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
         }
         __syncthreads();
         stamp();
-        if (ok) mat_combine<NG, MODE>(m, S.pieces, warp, NW, lane);
+        if (ok) mat_combine<NG, MODE>(m, static_cast<const PieceSlotT<NG, MODE>*>(S.pieces), warp, NW, lane);
         uc = ue;
         if (uc < u1) __syncthreads();   // the images and the pieces are rewritten by the next pass
         stamp();

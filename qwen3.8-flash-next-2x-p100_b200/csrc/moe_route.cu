@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(32) k_combine_image(const float* __restrict__ 
         q[j].t = q[j].blk = 0;
     }
     q[0].src = out + (size_t) t * H + (size_t) blk * 256;
-    q[0].t = t & 7;
+    q[0].t = t % FNX_DENSE_ROWS;
     q[0].blk = blk;
     quant_fetch(q[0], img_norm_w, lane, v[0], nw[0]);   // the old values and the norm weights
     unsigned long long s[8];
@@ -361,9 +361,9 @@ __global__ void __launch_bounds__(32) k_combine_image(const float* __restrict__ 
     float* dst = out + (size_t) t * H + col;
     *reinterpret_cast<float4*>(dst) = make_float4(v[0][0], v[0][1], v[0][2], v[0][3]);
     *reinterpret_cast<float4*>(dst + 4) = make_float4(v[0][4], v[0][5], v[0][6], v[0][7]);
-    // the image of the row's group of 8
-    const int t0 = t & ~7, nt = min(8, T - t0), NG = nt <= 4 ? 1 : 2;
-    uint2* cells = reinterpret_cast<uint2*>(img_out + (size_t) (t0 / 8) * img_stride);
+    // the image of the row's group of FNX_DENSE_ROWS
+    const int t0 = t - t % FNX_DENSE_ROWS, nt = min((int) FNX_DENSE_ROWS, T - t0), NG = (nt + 3) / 4;
+    uint2* cells = reinterpret_cast<uint2*>(img_out + (size_t) (t0 / FNX_DENSE_ROWS) * img_stride);
     float* scales = reinterpret_cast<float*>(cells + (size_t) NG * (H / 32) * 32);
     float* rs = scales + (size_t) NG * KB * 8;
     quant_finish(q, v, nw, H, img_norm_w, cells, scales, rs, lane);

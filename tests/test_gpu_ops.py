@@ -53,7 +53,8 @@ def test_gpu_quantiser_is_bit_identical_to_the_cpu_twin(F, O):
 
 # ------------------------------------------------------------------------------------------------ dense GEMV
 @pytest.mark.parametrize("rows,cols,T", [(64, 2048, 1), (64, 2048, 5), (128, 512, 4), (256, 512, 8), (32, 4096, 5), (256, 256, 3),
-                                         (64, 1024, 7), (9216, 2048, 5), (2048, 4096, 5), (128, 2048, 20)])
+                                         (64, 1024, 7), (9216, 2048, 5), (2048, 4096, 5), (128, 2048, 20), (256, 2048, 12), (2048, 4096, 11),
+                                         (64, 1024, 9)])
 def test_dense_matches_oracle(F, O, rows, cols, T):
     tiles, ggml = gpu_iq3s_matrix(F, rows, cols, seed=3, stream_id=rows + cols)
     rng = np.random.default_rng(rows + T)
@@ -110,6 +111,20 @@ def test_dense_prompt_matches_the_decode_product(F, rows, cols, T):
     plain, _ = F.dense(Wt, rows, cols, x)
     assert rel_err((acc[:, :rows] - base[:, :rows]).cpu().numpy(), plain.cpu().numpy()) < 2e-3
     assert torch.equal(acc[:, rows:], base[:, rows:])
+
+
+def test_dense_rows_do_not_depend_on_the_call_they_ride_in(F):
+    """A row's product is the same bits alone, among 5 rows and among 12 (one, two or three row groups per call)."""
+    import torch
+    rows, cols = 512, 2048
+    Wt, _ = gpu_iq3s_matrix(F, rows, cols, 3, 41)
+    rng = np.random.default_rng(12)
+    x = dev(rng.standard_normal((12, cols)).astype(np.float32))
+    nw = dev((1.0 + 0.05 * rng.standard_normal(cols)).astype(np.float32))
+    y12, _ = F.dense(Wt, rows, cols, x, norm_w=nw)
+    y5, _ = F.dense(Wt, rows, cols, x[:5].contiguous(), norm_w=nw)
+    y1, _ = F.dense(Wt, rows, cols, x[3:4].contiguous(), norm_w=nw)
+    assert torch.equal(y12[:5], y5) and torch.equal(y12[3:4], y1)
 
 
 def test_dense_rejects_bad_shapes(F):
