@@ -329,6 +329,8 @@ __device__ __forceinline__ void attn_part_body_t(const float* qg, int ldq, const
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             const float fa = fs[m * 16 + g], fb = fs[m * 16 + g + 8];
+            // (deep into a long context the running maxima rarely move: a tile whose factors are all 1 is left alone)
+            if (__all_sync(0xffffffffu, fa == 1.0f && fb == 1.0f)) continue;
 #pragma unroll
             for (int n = 0; n < 4; ++n) {
                 acc[m][n][0] *= fa; acc[m][n][1] *= fa;
