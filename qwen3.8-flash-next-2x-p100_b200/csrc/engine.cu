@@ -16,6 +16,7 @@
 
 #include "fnx_common.cuh"
 #include "iq3s_tile.h"
+#include "mmv_core.cuh"
 
 namespace fnxb {
 
@@ -142,6 +143,7 @@ struct fnx_engine {
     // (sequence % ranks == rank) and the mixers' output rows are gathered over the same peer memory: a second region of the
     // landing buffer ([2 slots][MAXR][mixer width], after the expert planes) with its own flags ([2][ranks], after the
     // experts') and sequence counters (d_xseq[4..7])
+    bool ep_one_kernel = true;    // the per-layer sum as one kernel (k_ep_exchange) instead of k_ep_send + k_ep_recv
     bool dp_mixers = true;
     size_t x_off_rows = 0;        // floats before the rows region
     int mix_width = 0;
@@ -435,6 +437,122 @@ static int init_layer(fnx_engine* e, LayerW& L, int li, uint64_t seed, float sig
     return FNX_OK;
 }
 
+// ---- the exchange as one kernel: one warp per (256-column block, row) computes the rank's routed addend for its 8 columns a
+// lane, stores it into every rank's plane, releases a flag of its own per peer, waits (bounded) for the same block's flag from
+// every rank, adds the planes in rank order and the local shared expert into the residual, and (img_out) leaves the new rows'
+// image for the next projection.  Against k_ep_send + k_ep_recv: no kernel boundary and no arrival counter between the sending
+// and the receiving half, and the flags are per block, so a block never waits for rows it does not read.
+// flags: xflag + flag_off, [2 slots][ranks][blocks]; seqs[8] = exchanges so far, seqs[9] = the blocks' arrival count.
+__global__ void __launch_bounds__(32) k_ep_exchange(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
+                                                    const float* __restrict__ logits, int T, int E, int H, int K, int e_lo, int e_hi,
+                                                    float* const* __restrict__ peer_x, unsigned* const* __restrict__ peer_flag, size_t flag_off,
+                                                    const float* __restrict__ xbuf, const unsigned* __restrict__ xflag, int rank, int R, int maxr,
+                                                    float* __restrict__ out, unsigned* __restrict__ seqs, unsigned* __restrict__ err,
+                                                    unsigned wait_limit, uint8_t* __restrict__ img_out, const float* __restrict__ img_norm_w,
+                                                    size_t img_stride) {
+    const int blk = blockIdx.x, t = blockIdx.y, lane = threadIdx.x, KB = H / 256;
+    const int nblk = gridDim.x * gridDim.y, bid = t * gridDim.x + blk;
+    const size_t col = (size_t) blk * 256 + lane * 8;
+    const unsigned seq = seqs[8];
+    const int slot = (int) (seq & 1u);
+    // ---- this rank's addend (the sum k_ep_send makes: fmaf over the picks of this rank's experts, in pick order)
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = 0.f;
+    for (int k = 0; k < K; ++k) {
+        const int e = topi[t * K + k];
+        if (e < e_lo || e >= e_hi) continue;
+        const float w = topw[t * K + k];
+        const float4* src = reinterpret_cast<const float4*>(part + ((size_t) t * K + k) * H + col);
+        const float4 a0 = src[0], a1 = src[1];
+        s[0] = fmaf(w, a0.x, s[0]); s[1] = fmaf(w, a0.y, s[1]); s[2] = fmaf(w, a0.z, s[2]); s[3] = fmaf(w, a0.w, s[3]);
+        s[4] = fmaf(w, a1.x, s[4]); s[5] = fmaf(w, a1.y, s[5]); s[6] = fmaf(w, a1.z, s[6]); s[7] = fmaf(w, a1.w, s[7]);
+    }
+    const size_t off = (((size_t) slot * R + rank) * maxr + t) * H + col;
+    for (int r = 0; r < R; ++r) {
+        float4* dst = reinterpret_cast<float4*>(peer_x[r] + off);
+        dst[0] = make_float4(s[0], s[1], s[2], s[3]);
+        dst[1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane < R) {
+        unsigned* f = peer_flag[lane] + flag_off + ((size_t) slot * R + rank) * nblk + bid;
+        const unsigned v = seq + 1u;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(v) : "memory");
+    }
+    // ---- every rank's slice of this block (bounded; once a wait has given up nothing waits again)
+    bool mine = true;
+    if (lane < R) {
+        const unsigned* f = xflag + flag_off + ((size_t) slot * R + lane) * nblk + bid;
+        const bool gave_up = (*(volatile unsigned*) err & (unsigned) FNX_ERR_TIMEOUT) != 0;
+        mine = false;
+        for (unsigned it = 0; it < wait_limit && !mine && !gave_up; ++it) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            mine = v == seq + 1u;
+        }
+    }
+    const bool all = __all_sync(0xffffffffu, mine);
+    if (!all && lane == 0) atomicOr(err, (unsigned) FNX_ERR_TIMEOUT);
+    if (all) {
+        QuantTask q[QUANT_BATCH];
+        float v[QUANT_BATCH][8], nw[QUANT_BATCH][8];
+#pragma unroll
+        for (int j = 0; j < QUANT_BATCH; ++j) {
+            q[j].src = nullptr;
+            q[j].t = q[j].blk = 0;
+        }
+        q[0].src = out + (size_t) t * H + (size_t) blk * 256;
+        q[0].t = t % FNX_DENSE_ROWS;
+        q[0].blk = blk;
+        quant_fetch(q[0], img_out ? img_norm_w : nullptr, lane, v[0], nw[0]);
+        float a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = 0.f;
+        for (int r = 0; r < R; ++r) {   // in rank order on every rank: identical sums everywhere
+            const float4* src = reinterpret_cast<const float4*>(xbuf + (((size_t) slot * R + r) * maxr + t) * H + col);
+            const float4 a0 = __ldcv(src), a1 = __ldcv(src + 1);
+            a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w;
+            a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+        }
+        {
+            const float4* src = reinterpret_cast<const float4*>(part + ((size_t) T * K + t) * H + col);
+            const float4 a0 = src[0], a1 = src[1];
+            const float g = sigmoidf_(logits[(size_t) t * (E + 1) + E]);
+            a[0] += g * a0.x; a[1] += g * a0.y; a[2] += g * a0.z; a[3] += g * a0.w;
+            a[4] += g * a1.x; a[5] += g * a1.y; a[6] += g * a1.z; a[7] += g * a1.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[0][i] += a[i];
+        float* dst = out + (size_t) t * H + col;
+        *reinterpret_cast<float4*>(dst) = make_float4(v[0][0], v[0][1], v[0][2], v[0][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(v[0][4], v[0][5], v[0][6], v[0][7]);
+        if (img_out) {
+            const int t0 = t - t % FNX_DENSE_ROWS, nt = min((int) FNX_DENSE_ROWS, T - t0), NG = (nt + 3) / 4;
+            uint2* cells = reinterpret_cast<uint2*>(img_out + (size_t) (t0 / FNX_DENSE_ROWS) * img_stride);
+            float* scales = reinterpret_cast<float*>(cells + (size_t) NG * (H / 32) * 32);
+            float* rs = scales + (size_t) NG * KB * 8;
+            quant_finish(q, v, nw, H, img_norm_w, cells, scales, rs, lane);
+            if (t == t0 + nt - 1)
+                for (int td = nt; td < 4 * NG; ++td) {
+                    const int ng = td >> 2, n = td & 3;
+                    for (int i = lane; i < 64; i += 32) {
+                        const int sbG = blk * 8 + (i >> 3), lvl = (i >> 2) & 1, qq = i & 3;
+                        cells[((size_t) (ng * (H / 32) + sbG) * 8 + n + 4 * lvl) * 4 + qq] = make_uint2(0u, 0u);
+                    }
+                    if (lane < 2) scales[(size_t) (ng * KB + blk) * 8 + n + 4 * lane] = 0.f;
+                    if (lane == 2) rs[td * 16 + blk] = 0.f;
+                }
+        }
+    }
+    __syncwarp();
+    if (lane == 0 && atomicAdd(&seqs[9], 1u) == (unsigned) nblk - 1u) {
+        seqs[9] = 0;
+        seqs[8] = seq + 1u;
+    }
+}
+
 // ---- the gather of the mixers' output rows among expert-parallel ranks (lanes windows): every rank stores the rows of its
 // own lanes into every peer's rows region, the last block releases one flag per peer; the receiving kernel waits for every
 // other rank's flag (bounded) and copies their lanes' rows into the local buffer.
@@ -525,6 +643,15 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T, const fl
         return fnx_moe_combine_image(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, R, e->d_img, next_norm, e->st);
     }
     if (!ep) return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, d.E, 1, R, 1, e->st);
+    if (e->ep_peers && e->ep_one_kernel && d.H % 256 == 0) {
+        const bool img = next_norm && e->use_img;
+        if (img_ready) *img_ready = img;
+        k_ep_exchange<<<dim3(d.H / 256, T), 32, 0, e->st>>>(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, e->e_lo, e->e_hi, e->d_peer_x, e->d_peer_flag,
+                                                             (size_t) 4 * e->c.ep_size, e->xbuf, e->xflag, e->c.ep_rank, e->c.ep_size, d.MAXR, R, e->d_xseq, e->err,
+                                                             e->wait_limit, img ? e->d_img : nullptr, next_norm, fnx_dense_image_bytes(d.H));
+        FNX_LAUNCH_OK("k_ep_exchange");
+        return FNX_OK;
+    }
     if (e->ep_peers) {
         const dim3 grid((d.H + 255) / 256, T);
         k_ep_send<<<grid, 256, 0, e->st>>>(e->part, e->topi, e->topw, T, d.H, d.K, e->e_lo, e->e_hi, e->d_peer_x, e->d_peer_flag, e->c.ep_rank,
@@ -870,11 +997,13 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
             e->mix_width = mixw;
             e->x_off_rows = (size_t) 2 * c.ep_size * d.MAXR * d.H;
             FNX_TRY(dalloc(e, &e->xbuf, e->x_off_rows + (size_t) 2 * d.MAXR * mixw, "buf.ep_x"));
-            FNX_TRY(dalloc(e, &e->xflag, (size_t) 4 * c.ep_size, "buf.ep_flag"));
+            // flags: [2][ranks] of the two-kernel exchange, [2][ranks] of the rows gather, [2][ranks][blocks] of the one-kernel exchange
+            FNX_TRY(dalloc(e, &e->xflag, (size_t) 4 * c.ep_size + (size_t) 2 * c.ep_size * d.MAXR * (d.H / 256 + 1), "buf.ep_flag"));
+            if (const char* n1 = getenv("FNX_EP_TWO_KERNELS")) e->ep_one_kernel = n1[0] != '1';
             if (const char* nd = getenv("FNX_NO_DP")) e->dp_mixers = nd[0] != '1';
             FNX_TRY(dalloc(e, &e->d_peer_x, (size_t) c.ep_size));
             FNX_TRY(dalloc(e, &e->d_peer_flag, (size_t) c.ep_size));
-            FNX_TRY(dalloc(e, &e->d_xseq, 8));
+            FNX_TRY(dalloc(e, &e->d_xseq, 12));
         }
         FNX_TRY(dalloc(e, &e->best_i, d.MAXR, "buf.best_i"));
         FNX_TRY(dalloc(e, &e->best_v, d.MAXR, "buf.best_v"));
