@@ -15,8 +15,11 @@ e2e      the same through Engine.verify / commit / draft with host token buffers
          D2H of the acceptance result inside the timed region
 roofline the routed-expert gate|up kernel (the dominant kernel) timed live with CUDA events over all 48 layers'
          weights; plus the whole verify step against its compulsory bytes
-N > 1:   expert-parallel ranks (512 experts split evenly, one NCCL all-reduce per layer), same token stream on every
-         rank, device-timed, max over ranks ("strong" scaling: the work is fixed).
+N > 1:   expert-parallel ranks (512 experts split evenly, one exchange per layer over NVLink peer memory, or NCCL with
+         FNX_EP_NCCL=1), same token stream on every rank, device-timed, max over ranks ("strong" scaling: the work is fixed).
+Other configurations: --config 2 (tree windows with lookup drafts), 3 (cold prefill of 38,912 tokens on the prompt pass),
+4 (8 sequences x 131,072-token contexts in batched lanes; also a sub-object of the default run).  Side modes, not bench
+lines: --prefill-moe T, --attn-prompt T, --verify-only.
 """
 from __future__ import annotations
 
@@ -398,7 +401,7 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
             "config": {"workload": f"configuration 3: cold prefill of {n} uniform-random tokens (seed 3) " +
                        ("through chained 32-row windows of the decode kernels" if windows else "on the prompt pass (tensor-core projections and experts, chained DeltaNet windows, window attention)"),
-                       "timing": "weights (34 GB per window) far larger than the 126 MB L2; CUDA events on the engine's stream", "parallelism": f"ep{world}", "layers": a.layers},
+                       "timing": "weights (17 GB) and activations far larger than the 126 MB L2; CUDA events on the engine's stream", "parallelism": f"ep{world}", "layers": a.layers},
             "clocks": clk, "gpu_launches": int((c1[0] - c0[0]) / passes),
             "e2e": {"value": n / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * n + 4 * n, "d2h_bytes_per_step": 0, "wall_ms_per_step": wall * 1e3},
             "windows": (n + cfg.max_rows - 1) // cfg.max_rows, "us_per_window": ms * 1e3 / ((n + cfg.max_rows - 1) // cfg.max_rows),

@@ -328,6 +328,18 @@ int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uint64_t seed)
  * the pending one; root >= 0 replaces the pending token, for a caller that starts the next window from another token):
  * up to lk drafts into h_out, their number into h_n; d1 >= 0 keeps only a match whose first draft is d1. */
 int fnx_engine_lookup(fnx_engine* e, int seq, int lk, int d1, int root, int* h_out, int* h_n);
+/* The lane planner (plan_rows, engine/src/batch_plan.hpp:63-132): host arithmetic.  Lane i offers up to avail[i] drafts;
+ * reach[i * (FNX_LANE_ROWS - 1) + j] is the chance that its drafts 0..j all stand (non-increasing in j); chain[i] != 0: a
+ * draft-layer chain, whose drafts after the first cost chain_ms each.  A window's rows past the lanes' first cost row_lo each
+ * up to the knee'th row of the window and row_hi past it, on top of base_ms.  drafts[i] receives the counts with the most
+ * expected tokens per ms (exact), at most max_rows - n_lanes in all and FNX_LANE_ROWS - 1 per lane; rate_out (optional) that
+ * rate.  Feed the result to fnx_engine_verify_lanes_rows (rows = 1 + drafts). */
+typedef struct {
+    double row_lo, row_hi, chain_ms;
+    int knee;
+} fnx_row_cost;
+int fnx_plan_rows(int n_lanes, const int* avail, const double* reach, const int* chain, int max_rows, double base_ms,
+                  const fnx_row_cost* cost, int* drafts, double* rate_out);
 /* Sequence-state cache (Engine::save_state / load_state / state_bytes, engine/src/engine_common.cu:629-688): a committed
  * sequence's DeltaNet states, conv histories, context tokens and, with kv, its cache rows [0, pos), copied to host memory the
  * caller owns (fnx_engine_state_bytes(e, seq, kv) bytes) and put back later into the same or another sequence.  Without kv
@@ -347,6 +359,10 @@ int fnx_engine_load_state(fnx_engine* e, int seq, const void* host, size_t bytes
  * commit_lanes keeps the first h_keep[j] rows of lane j (chains are kept as prefixes); draft_lanes runs the MTP layer on
  * every lane's kept rows and k - 1 chained calls of one row per lane, h_drafts [n_lanes][k]. */
 int fnx_engine_verify_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_tok, int rows, int* h_results);
+/* the same with each lane's own row count (h_rows[j] in 1..FNX_LANE_ROWS; h_tok holds the lanes' rows one after another): the
+ * windows a planner lays out, where a lane carries as many drafts as are worth their rows */
+int fnx_engine_verify_lanes_rows(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_rows, const int* h_tok,
+                                 int* h_results);
 int fnx_engine_commit_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_keep);
 int fnx_engine_draft_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, int k, int* h_drafts);
 /* Places sequence `seq` at position `pos` as if that many tokens had been read, without reading them: its K/V rows and

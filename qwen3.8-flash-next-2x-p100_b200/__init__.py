@@ -101,6 +101,8 @@ _PROTOS = {
     "fnx_engine_reset": (_I, [_P, _I]),
     "fnx_engine_verify": (_I, [_P, _I, _P, _P, _I, _P]),
     "fnx_engine_prompt": (_I, [_P, _I, _P, _I]),
+    "fnx_engine_verify_lanes_rows": (_I, [_P, _I, _P, _P, _P, _P]),
+    "fnx_plan_rows": (_I, [_I, _P, _P, _P, _I, C.c_double, _P, _P, _P]),
     "fnx_engine_prompt_timing": (_I, [_P, _I, _P]),
     "fnx_engine_state_bytes": (_Z, [_P, _I, _I]),
     "fnx_engine_save_state": (_I, [_P, _I, _I, _P, _Z]),
@@ -323,6 +325,28 @@ def router_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
     err = new_err(x.device)
     check(lib().fnx_router_rows(ptr(Wr), ptr(x), ptr(norm_w), eps, T, E, H, K, ptr(logits), ptr(topi), ptr(topw), ptr(err), _stream()))
     return topi, topw, logits
+
+
+class RowCost(C.Structure):
+    _fields_ = [("row_lo", C.c_double), ("row_hi", C.c_double), ("chain_ms", C.c_double), ("knee", C.c_int)]
+
+
+LANE_ROWS = 5
+
+
+def plan_rows(avail, reach, chain, max_rows: int, base_ms: float, row_lo: float, row_hi: float, chain_ms: float, knee: int):
+    """fnx_plan_rows: (drafts per lane, expected tokens per ms).  reach[i] lists lane i's reach probabilities."""
+    n = len(avail)
+    flat = []
+    for r in reach:
+        r = list(r)[:LANE_ROWS - 1]
+        flat += r + [0.0] * (LANE_ROWS - 1 - len(r))
+    out = (C.c_int * n)()
+    rate = C.c_double(0.0)
+    cost = RowCost(row_lo, row_hi, chain_ms, knee)
+    check(lib().fnx_plan_rows(n, (C.c_int * n)(*avail), (C.c_double * len(flat))(*flat), (C.c_int * n)(*[1 if c else 0 for c in chain]), max_rows, base_ms,
+                              C.byref(cost), out, C.byref(rate)))
+    return list(out), float(rate.value)
 
 
 def route_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
@@ -554,6 +578,21 @@ class Engine:
         check(lib().fnx_engine_verify_lanes(self._h, L, sq, tok, T, res))
         if not want_result:
             return None
+        out = []
+        for j in range(L):
+            r = res[j * W:(j + 1) * W]
+            out.append((r[0], list(r[1:1 + r[0]]), list(r[1 + MAX_ROWS:1 + MAX_ROWS + r[0]])))
+        return out
+
+    def verify_lanes_rows(self, seqs, rows_of_tokens):
+        """One window of several sequences' chains of their own lengths: per lane (n, path, emitted)."""
+        import ctypes as C
+        L = len(seqs)
+        rows = [len(r) for r in rows_of_tokens]
+        T = sum(rows)
+        W = 1 + 2 * MAX_ROWS
+        res = (C.c_int * (L * W))()
+        check(lib().fnx_engine_verify_lanes_rows(self._h, L, (C.c_int * L)(*seqs), (C.c_int * L)(*rows), (C.c_int * T)(*[t for r in rows_of_tokens for t in r]), res))
         out = []
         for j in range(L):
             r = res[j * W:(j + 1) * W]

@@ -15,7 +15,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "libfnx_b200.so"
-SOURCES = ["common.cu", "iq3s_prep.cu", "iq3s_mmv.cu", "moe_route.cu", "attn.cu", "gdn.cu", "moe_prefill.cu", "head.cu", "spec.cu", "engine.cu"]
+SOURCES = ["common.cu", "iq3s_prep.cu", "iq3s_mmv.cu", "moe_route.cu", "attn.cu", "gdn.cu", "moe_prefill.cu", "head.cu", "spec.cu", "lane_plan.cu", "engine.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xcompiler", "-Wall"]
 

@@ -105,7 +105,7 @@ struct fnx_engine {
         *d_ident_row0 = nullptr, *d_ldrafts = nullptr;
     float* Rlast = nullptr;     // the lanes' last draft-layer rows, compact, for the head
     std::vector<int> lane_seqs; // the sequences of the last lane window, in lane order (empty: the last window was not batched)
-    int lane_T = 0;
+    std::vector<int> lane_rows;   // rows of each lane of the last lanes window
     fnx_job* jobs = nullptr;
     unsigned* err = nullptr;
     void* att_scratch = nullptr;
@@ -841,9 +841,8 @@ static int enqueue_mixer_lanes(fnx_engine* e, const LayerW& L, float* R, int T, 
     return enqueue_dense(e, L.w_out, d.H, d.nv * d.hs, e->mix, d.nv * d.hs, T, nullptr, R, d.H, 1);
 }
 
-static int enqueue_verify_lanes(fnx_engine* e, int n_lanes, int rows) {
+static int enqueue_verify_lanes(fnx_engine* e, int n_lanes, int rows, int T) {   // rows: the longest lane's; T: rows in all
     const Dims d = dims(e->c);
-    const int T = n_lanes * rows;
     FNX_TRY(fnx_embed_rows(e->embed, e->d_tok, T, d.H, e->R, e->st));
     bool img = false;
     for (size_t l = 0; l < e->layers.size(); ++l) {
@@ -1546,25 +1545,36 @@ extern "C" int fnx_allreduce(fnx_engine* e, float* x, size_t count, fnx_stream s
 
 // ------------------------------------------------------------------------------------------------ batched lanes: API
 extern "C" int fnx_engine_verify_lanes(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_tok, int rows, int* h_results) {
-    FNX_REQUIRE(e && h_seqs && h_tok, "fnx_engine_verify_lanes: null pointer");
-    FNX_REQUIRE(n_lanes >= 1 && rows >= 1 && rows <= FNX_LANE_ROWS && n_lanes * rows <= e->c.max_rows, "fnx_engine_verify_lanes: %d lanes of %d rows (rows <= %d, %d rows in all)",
-                n_lanes, rows, FNX_LANE_ROWS, e->c.max_rows);
+    FNX_REQUIRE(n_lanes >= 1 && n_lanes <= FNX_MAX_ROWS, "fnx_engine_verify_lanes: %d lanes", n_lanes);
+    int each[FNX_MAX_ROWS];
+    for (int j = 0; j < n_lanes; ++j) each[j] = rows;
+    return fnx_engine_verify_lanes_rows(e, n_lanes, h_seqs, each, h_tok, h_results);
+}
+
+extern "C" int fnx_engine_verify_lanes_rows(fnx_engine* e, int n_lanes, const int* h_seqs, const int* h_rows, const int* h_tok, int* h_results) {
+    FNX_REQUIRE(e && h_seqs && h_rows && h_tok, "fnx_engine_verify_lanes: null pointer");
+    FNX_REQUIRE(n_lanes >= 1 && n_lanes <= FNX_MAX_ROWS, "fnx_engine_verify_lanes: %d lanes", n_lanes);
+    int T = 0, rows = 0;   // rows in all, the longest lane's
     for (int j = 0; j < n_lanes; ++j) {
+        FNX_REQUIRE(h_rows[j] >= 1 && h_rows[j] <= FNX_LANE_ROWS, "fnx_engine_verify_lanes: lane %d has %d rows (1..%d)", j, h_rows[j], FNX_LANE_ROWS);
         FNX_REQUIRE(h_seqs[j] >= 0 && h_seqs[j] < e->c.n_seq, "fnx_engine_verify_lanes: sequence %d", h_seqs[j]);
         for (int i = 0; i < j; ++i) FNX_REQUIRE(h_seqs[i] != h_seqs[j], "fnx_engine_verify_lanes: sequence %d in two lanes", h_seqs[j]);
-        FNX_REQUIRE(e->seqs[h_seqs[j]].pos + rows <= e->c.max_ctx, "fnx_engine_verify_lanes: sequence %d runs past the context of %d rows", h_seqs[j], e->c.max_ctx);
-        for (int t = 0; t < rows; ++t)
-            FNX_REQUIRE(h_tok[j * rows + t] >= 0 && h_tok[j * rows + t] < e->c.vocab, "fnx_engine_verify_lanes: token %d outside the vocabulary", h_tok[j * rows + t]);
+        FNX_REQUIRE(e->seqs[h_seqs[j]].pos + h_rows[j] <= e->c.max_ctx, "fnx_engine_verify_lanes: sequence %d runs past the context of %d rows", h_seqs[j], e->c.max_ctx);
+        for (int t = 0; t < h_rows[j]; ++t)
+            FNX_REQUIRE(h_tok[T + t] >= 0 && h_tok[T + t] < e->c.vocab, "fnx_engine_verify_lanes: token %d outside the vocabulary", h_tok[T + t]);
+        T += h_rows[j];
+        rows = h_rows[j] > rows ? h_rows[j] : rows;
     }
+    FNX_REQUIRE(T <= e->c.max_rows, "fnx_engine_verify_lanes: %d rows in all (at most %d)", T, e->c.max_rows);
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     FNX_CUDA_OK(cudaMemsetAsync(e->err, 0, sizeof(unsigned), e->st));
     int* hs = e->h_stage;
-    const int T = n_lanes * rows;
     memcpy(hs, h_tok, sizeof(int) * T);
     FNX_CUDA_OK(cudaMemcpyAsync(e->d_tok, hs, sizeof(int) * T, cudaMemcpyHostToDevice, e->st));
     int* ht = hs + FNX_MAX_ROWS;
     for (int j = 0; j < n_lanes; ++j) ht[j] = h_seqs[j];
-    for (int j = 0; j <= n_lanes; ++j) ht[FNX_MAX_ROWS + j] = j * rows;
+    ht[FNX_MAX_ROWS] = 0;
+    for (int j = 0; j < n_lanes; ++j) ht[FNX_MAX_ROWS + j + 1] = ht[FNX_MAX_ROWS + j] + h_rows[j];
     FNX_CUDA_OK(cudaMemcpyAsync(e->d_lane_seq, ht, sizeof(int) * n_lanes, cudaMemcpyHostToDevice, e->st));
     {   // the table the mixers see on expert-parallel ranks: this rank's own sequences (sequence % ranks == rank)
         int* ho = hs + 5 * FNX_MAX_ROWS;
@@ -1577,12 +1587,15 @@ extern "C" int fnx_engine_verify_lanes(fnx_engine* e, int n_lanes, const int* h_
             ht[3 * FNX_MAX_ROWS + j] = (int) e->seqs[h_seqs[j]].step++;
             FNX_CUDA_OK(cudaMemcpyAsync(e->d_step + h_seqs[j], ht + 3 * FNX_MAX_ROWS + j, sizeof(int), cudaMemcpyHostToDevice, e->st));
         }
-    const uint64_t key = ((uint64_t) 4 << 60) | ((uint64_t) n_lanes << 8) | (uint64_t) rows;
-    FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify_lanes(e, n_lanes, rows); }));
+    // one graph per layout (each lane's rows): the key is a hash of the counts under the lanes tag
+    uint64_t hsh = 1469598103934665603ull;
+    for (int j = 0; j < n_lanes; ++j) hsh = (hsh ^ (uint64_t) (h_rows[j] + 8 * j)) * 1099511628211ull;
+    const uint64_t key = ((uint64_t) 4 << 60) | ((hsh ^ (uint64_t) n_lanes) & 0x0fffffffffffffffull);
+    FNX_TRY(run_graph(e, key, [&]() { return enqueue_verify_lanes(e, n_lanes, rows, T); }));
     e->lane_seqs.assign(h_seqs, h_seqs + n_lanes);
-    e->lane_T = rows;
+    e->lane_rows.assign(h_rows, h_rows + n_lanes);
     e->last_seq = -1;
-    for (int j = 0; j < n_lanes; ++j) e->seqs[h_seqs[j]].last_T = rows;
+    for (int j = 0; j < n_lanes; ++j) e->seqs[h_seqs[j]].last_T = h_rows[j];
     if (h_results) {
         const size_t n = (size_t) n_lanes * (1 + 2 * FNX_MAX_ROWS);
         std::vector<int> tmp(n + 1);
@@ -1601,7 +1614,7 @@ extern "C" int fnx_engine_commit_lanes(fnx_engine* e, int n_lanes, const int* h_
     FNX_REQUIRE(n_lanes == (int) e->lane_seqs.size() && n_lanes >= 1, "fnx_engine_commit_lanes: %d lanes, the last lane window had %d", n_lanes, (int) e->lane_seqs.size());
     for (int j = 0; j < n_lanes; ++j) {
         FNX_REQUIRE(h_seqs[j] == e->lane_seqs[j], "fnx_engine_commit_lanes: lane %d is sequence %d in the window, %d here", j, e->lane_seqs[j], h_seqs[j]);
-        FNX_REQUIRE(h_keep[j] >= 1 && h_keep[j] <= e->lane_T, "fnx_engine_commit_lanes: lane %d keeps %d of %d rows", j, h_keep[j], e->lane_T);
+        FNX_REQUIRE(h_keep[j] >= 1 && h_keep[j] <= e->lane_rows[j], "fnx_engine_commit_lanes: lane %d keeps %d of %d rows", j, h_keep[j], e->lane_rows[j]);
     }
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     int* hs = e->h_stage;

@@ -226,6 +226,35 @@ def test_engine_argument_checks_need_no_gpu(F):
     assert L.fnx_iq3s_retile(None, None, 10, 256, None) == -1
 
 
+# ------------------------------------------------------------------------------------------------ the lane planner (host arithmetic)
+def test_lane_planner_finds_the_best_rate(F):
+    """fnx_plan_rows against an exhaustive search over every draft count: the plan's expected tokens per ms is the maximum
+    (costs with a knee inside the window, chain lanes whose later drafts cost a call each, a row budget that binds)."""
+    import itertools
+    rng = np.random.default_rng(4)
+    for case in range(40):
+        n = int(rng.integers(1, 5))
+        avail = [int(rng.integers(0, 5)) for _ in range(n)]
+        reach = [np.sort(rng.uniform(0.05, 0.95, size=4))[::-1].tolist() for _ in range(n)]
+        chain = [bool(rng.integers(0, 2)) for _ in range(n)]
+        max_rows = int(rng.integers(n, min(32, n + 9) + 1))
+        base, lo, hi, ch, knee = float(rng.uniform(2, 12)), float(rng.uniform(0.1, 1.5)), float(rng.uniform(1.5, 3.0)), float(rng.uniform(0.0, 0.8)), int(rng.integers(2, 12))
+
+        def rate(d):
+            tok, ms, rows = float(n), base, n
+            for i in range(n):
+                tok += sum(reach[i][:d[i]])
+                ms += max(0, d[i] - 1) * ch if chain[i] else 0.0
+            for t in range(n + 1, n + sum(d) + 1):
+                ms += lo if t <= knee else hi
+            return tok / ms
+
+        best = max(rate(d) for d in itertools.product(*[range(min(a, 4) + 1) for a in avail]) if sum(d) <= max_rows - n)
+        d, r = F.plan_rows(avail, reach, chain, max_rows, base, lo, hi, ch, knee)
+        assert all(0 <= d[i] <= min(avail[i], 4) for i in range(n)) and sum(d) <= max_rows - n
+        assert abs(rate(d) - best) <= 1e-12 * best and abs(r - best) <= 1e-9 * best, (case, d, rate(d), best)
+
+
 # ------------------------------------------------------------------------------------------------ expert-parallel rule, 2 ranks on gloo
 _EP_WORKER = r"""
 import sys, numpy as np, torch, torch.distributed as dist

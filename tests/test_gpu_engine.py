@@ -457,6 +457,47 @@ def test_batched_lanes_equal_single_sequence_windows(F, sampling):
         eng.close()
 
 
+def test_lanes_of_different_lengths_equal_single_sequence_windows(F):
+    """A planner's window: lanes of 5, 2 and 3 rows (fnx_engine_verify_lanes_rows).  Every lane's result and logits are
+    bit-identical to the same rows through that sequence's own window, and so are the drafts after the commit."""
+    cfg = small_cfg(F, n_seq=3, max_rows=16)
+    eng = F.Engine(cfg)
+    try:
+        eng.init_synthetic(seed=0, sigma=0.02)
+        rng = np.random.default_rng(33)
+        prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (7, 12, 5)]
+        wins = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (5, 2, 3)]
+        seqs = [0, 1, 2]
+
+        def begin():
+            for s in seqs:
+                eng.reset(s)
+                eng.prefill(prompts[s], s)
+
+        begin()
+        alone = []
+        for s in seqs:
+            res = eng.verify(wins[s], None, s)
+            lg = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:len(wins[s])].copy()
+            eng.commit(res[1], s)
+            alone.append((res, lg, eng.draft(2, s)))
+        begin()
+        got = eng.verify_lanes_rows(seqs, wins)
+        lg = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)
+        r0 = 0
+        for j, s in enumerate(seqs):
+            assert got[j] == alone[s][0]
+            assert np.array_equal(lg[r0:r0 + len(wins[s])], alone[s][1])
+            r0 += len(wins[s])
+        with pytest.raises(F.FnxError):
+            eng.commit_lanes(seqs, [5, 3, 3])          # lane 1 has two rows
+        eng.commit_lanes(seqs, [g[0] for g in got])
+        drafts = eng.draft_lanes(seqs, 2)
+        assert drafts == [a[2] for a in alone] and eng.error_bits() == 0
+    finally:
+        eng.close()
+
+
 def test_a_missing_peer_times_out_and_leaves_the_context_usable(F):
     """An expert-parallel rank whose peer never answers: the exchange's bounded wait runs out (a flag that nothing sets), the
     window reports FNX_ERR_TIMEOUT through the err word instead of hanging, and the same engine keeps answering calls."""
