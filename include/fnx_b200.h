@@ -37,6 +37,7 @@ enum { FNX_TOPK_N = 64,      /* sampler candidates per row (TOPK_N, engine/src/k
        FNX_JOB_TOK = 4,      /* activation rows of one expert job */
        FNX_DENSE_ROWS = 12,  /* activation rows of one fnx_dense call (three row groups of four) */
        FNX_LANE_ROWS = 5,    /* rows of one lane of a batched window */
+       FNX_PENALTY_CAP = 4096, /* tokens of a penalty window (Engine::PEN_CAP of the reference's sampler) */
        FNX_ATTN_STATIC_MAX_SLOTS = 16384 };   /* (row, head, split) partials fnx_attn_static's built-in scratch holds */
 
 const char* fnx_last_error(void);
@@ -235,6 +236,13 @@ int fnx_argmax_mapped(const float* logits, int T, int V, const int* map, int* be
                       fnx_stream st);
 /* top_tokens (engine/src/kernels.hpp:445) without penalties: the 64 highest per row, logit descending, id ascending */
 int fnx_top_tokens(const float* logits, int T, int V, float* out_v, int* out_i, fnx_stream st);
+/* The sampler's logit changes before the candidates are taken (the first half of k_topk_rows, engine/src/topk.cuh:30-45, with
+ * the rows' penalty windows of engine/src/session.cpp:88-98, 581-585), in place on logits [T][V]: per row the logit_bias
+ * list added (bias_tok each once), then over the row's penalty window (the last last_n tokens of ctx[0 .. *ctx_n) followed by
+ * window rows tok[0 .. row]) each token once: l = l <= 0 ? l * repeat : l / repeat, then l -= count * freq + present.
+ * last_n = 0: the bias only (ctx, ctx_n, tok may be null). */
+int fnx_logit_adjust(float* logits, int T, int V, const int* ctx, const int* ctx_n, const int* tok, int last_n, float repeat, float freq,
+                     float present, const int* bias_tok, const float* bias_val, int bias_n, fnx_stream st);
 /* embed rows: R[t] = f16 table[tok[t]] (the reference embeds on the host, engine_common.cu:955) */
 int fnx_embed_rows(const void* table_f16, const int* tok, int T, int H, float* R, fnx_stream st);
 /* rms_norm_rows (engine/src/kernels.hpp:406) */
@@ -324,6 +332,19 @@ int fnx_engine_error_bits(fnx_engine* e, unsigned* h_bits);
  * engine/src/session.cpp:575-612 over each row's 64 best tokens with Philox uniforms addressed (seed, seq, window, slot);
  * drafts count as fixed (q = 1), windows must be chains.  Resets the per-sequence window counters. */
 int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uint64_t seed);
+/* The sampler's logit changes of the following single-sequence windows (fnx_logit_adjust on every window's logits before the
+ * acceptance rule, greedy or sampling, looks at them): a request's logit_bias (host arrays, copied) and its penalties over
+ * each row's penalty window (Sampling's pen_* and bias, engine/src/session.hpp:17-26; applied as engine/src/session.cpp:566-585).
+ * null, or neither a window nor a list: none (the default).  Penalty windows need chain windows.  Batched lane windows and the
+ * draft layer's own logits are not changed.  Drops the captured graphs. */
+typedef struct {
+    float repeat, freq, present;   /* 1, 0, 0 change nothing */
+    int last_n;                    /* tokens of the penalty window, 0: no penalties */
+    const int* bias_tok;           /* logit_bias: each token once */
+    const float* bias_val;
+    int bias_n;
+} fnx_logit_rules;
+int fnx_engine_set_logit_rules(fnx_engine* e, const fnx_logit_rules* r);
 /* lookup_drafts (engine/src/session.cpp:428-447) over the sequence's own context on the device (committed tokens and
  * the pending one; root >= 0 replaces the pending token, for a caller that starts the next window from another token):
  * up to lk drafts into h_out, their number into h_n; d1 >= 0 keeps only a match whose first draft is d1. */
@@ -373,6 +394,44 @@ int fnx_engine_set_position(fnx_engine* e, int seq, int pos);
 int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3);
 int fnx_engine_pos(const fnx_engine* e, int seq);
 fnx_stream fnx_engine_stream(fnx_engine* e);
+/* the configuration the engine was made with */
+int fnx_engine_config(const fnx_engine* e, fnx_model_config* out);
+
+/* ---------------------------------------------------------------------------------------------- model files
+ * GGUF reader (fnx::Gguf, engine/src/gguf.hpp:47-95): maps a model file (and the other "-0000N-of-0000M" shards beside a
+ * first shard), indexes its tensors by name and keeps the first shard's metadata.  Host only: none of these calls
+ * touches a GPU.  Tensor data stays in the mapping (pointers are valid until fnx_gguf_close). */
+typedef struct fnx_gguf fnx_gguf;
+typedef struct {
+    const char* name;
+    uint32_t type;        /* ggml type id: 0 F32, 1 F16, 8 Q8_0, 21 IQ3_S, 26 I32, 30 BF16, ... */
+    int n_dims;
+    int64_t ne[4];        /* ne[0] = weights per row; unused extents are 1 */
+    const void* data;
+    size_t bytes;
+    int shard;
+    uint64_t offset;      /* of the data in its shard's file */
+} fnx_gguf_tensor;
+int fnx_gguf_open(const char* path, fnx_gguf** out);
+void fnx_gguf_close(fnx_gguf* g);
+int fnx_gguf_count(const fnx_gguf* g);
+int fnx_gguf_shards(const fnx_gguf* g);
+int fnx_gguf_tensor_at(const fnx_gguf* g, int i, fnx_gguf_tensor* out);
+/* these four return 1 when the tensor / key exists (and fill the output), else 0 */
+int fnx_gguf_find(const fnx_gguf* g, const char* name, fnx_gguf_tensor* out);
+int fnx_gguf_num(const fnx_gguf* g, const char* key, double* out);                 /* an integer, float or bool key */
+int fnx_gguf_str(const fnx_gguf* g, const char* key, char* buf, size_t cap);
+int fnx_gguf_int_array(const fnx_gguf* g, const char* key, int64_t* out, size_t cap, size_t* n);
+/* rows [row0, row0 + n_rows) of a tensor as f32 (fnx::conv::dequantize, engine/src/tensor_convert.hpp:143-326): F32, F16,
+ * BF16, Q8_0 and IQ3_S; FNX_E_UNAVAILABLE for other types */
+int fnx_gguf_rows_f32(const fnx_gguf_tensor* t, int64_t row0, int64_t n_rows, float* out);
+/* the architecture fields of a configuration from the file's metadata (the keys checked at engine/src/model.cpp:1481-1506)
+ * and tensor shapes; max_ctx, max_rows, n_seq, ep_rank and ep_size are the caller's and stay as they are */
+int fnx_gguf_model_config(const fnx_gguf* g, fnx_model_config* cfg);
+/* Fills an engine's weights from the file (llama.cpp's tensor names for this architecture; the load of
+ * engine/src/model.cpp:932-1097 with the expert slicing of :1063-1069).  IQ3_S tensors are re-tiled bit for bit; matrices of
+ * another type are quantised to IQ3_S on the GPU and counted in *h_converted (may be null).  Synchronises. */
+int fnx_engine_load_gguf(fnx_engine* e, const fnx_gguf* g, int* h_converted);
 
 /* ---------------------------------------------------------------------------------------------- expert-parallel sum
  * ring_sum (engine/src/kernels.hpp:396) over NCCL: in-place sum of x[count] f32 across the communicator. */

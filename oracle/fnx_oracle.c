@@ -447,6 +447,38 @@ void fnx_o_argmax(const float* logits, int T, int V, int* best_i, float* best_v)
     }
 }
 
+/* The sampler's logit changes before the candidates are taken: the logit_bias list added, then llama.cpp's penalties
+ * stage as the reference applies it (k_topk_rows, engine/src/topk.cuh:30-45: repeat multiplies a non-positive logit and
+ * divides a positive one, then frequency x count and presence once per token of the window), with row j's penalty
+ * window the last last_n tokens of the sequence followed by window rows 0..j (engine/src/session.cpp:88-98, 581-585;
+ * ctx holds the kept tokens, tok the window's rows, tok[0] the token the sequence ends in). */
+void fnx_o_logit_adjust(float* logits, int T, int V, const int* ctx, int ctx_n, const int* tok, int last_n, float repeat, float freq,
+                        float present, const int* bias_tok, const float* bias_val, int bias_n) {
+    for (int t = 0; t < T; ++t) {
+        float* l = logits + (size_t) t * V;
+        for (int i = 0; i < bias_n; ++i)
+            if (bias_tok[i] >= 0 && bias_tok[i] < V) l[bias_tok[i]] += bias_val[i];
+        if (last_n <= 0) continue;
+        const int len = ctx_n + t + 1, start = len > last_n ? len - last_n : 0;
+        for (int i = start; i < len; ++i) {
+            const int a = i < ctx_n ? ctx[i] : tok[i - ctx_n];
+            if (a < 0 || a >= V) continue;
+            int seen = 0, cnt = 0;
+            for (int j = start; j < len; ++j) {
+                const int b = j < ctx_n ? ctx[j] : tok[j - ctx_n];
+                if (b == a) {
+                    if (j < i) seen = 1;
+                    ++cnt;
+                }
+            }
+            if (seen) continue;   /* each token once */
+            float v = l[a];
+            v = v <= 0.f ? v * repeat : v / repeat;
+            l[a] = v - (float) cnt * freq - present;
+        }
+    }
+}
+
 /* The n highest logits per row, logit descending, id ascending on ties (top_tokens contract
  * engine/src/kernels.hpp:437-441; k_topk_rows engine/src/topk.cuh:17-155), without penalties or bias. */
 void fnx_o_top_tokens(const float* logits, int T, int V, int n, float* out_v, int* out_i) {

@@ -66,6 +66,8 @@ void fnx_o_gdn_core(const float* qkvz, const float* ab, float* hist_pool, const 
 /* ---- head ---- */
 void fnx_o_argmax(const float* logits, int T, int V, int* best_i, float* best_v);
 void fnx_o_top_tokens(const float* logits, int T, int V, int n, float* out_v, int* out_i);
+void fnx_o_logit_adjust(float* logits, int T, int V, const int* ctx, int ctx_n, const int* tok, int last_n, float repeat, float freq,
+                        float present, const int* bias_tok, const float* bias_val, int bias_n);
 
 /* ---- drafting and acceptance ---- */
 int fnx_o_lookup(const int* ctx, int n, int lk, int d1, int* out, int* match);

@@ -189,6 +189,18 @@ def top_tokens(logits, n=TOPN):
     return ov, oi
 
 
+def logit_adjust(logits, ctx, tok, last_n=0, repeat=1.0, freq=0.0, present=0.0, bias=()):
+    """The sampler's logit changes (bias list, then penalties over each row's window); returns a changed copy."""
+    out = f32(logits).copy()
+    T, V = out.shape
+    ctx, tok = i32(ctx), i32(tok)
+    bt = i32([b[0] for b in bias])
+    bv = f32([b[1] for b in bias])
+    lib().fnx_o_logit_adjust(_p(out), T, V, _p(ctx), ctx.size, _p(tok), int(last_n), C.c_float(repeat), C.c_float(freq), C.c_float(present),
+                             _p(bt), _p(bv), len(bias))
+    return out
+
+
 def lookup(ctx, lk, d1):
     ctx = i32(ctx)
     out = np.empty(max(lk, 1), np.int32)

@@ -133,6 +133,21 @@ _PROTOS = {
     "fnx_engine_lookup": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "fnx_engine_ep_handles": (_I, [_P, _P]),
     "fnx_engine_ep_open": (_I, [_P, _P, _I, _I]),
+    "fnx_engine_config": (_I, [_P, _P]),
+    "fnx_logit_adjust": (_I, [_P, _I, _I, _P, _P, _P, _I, _F, _F, _F, _P, _P, _I, _P]),
+    "fnx_engine_set_logit_rules": (_I, [_P, _P]),
+    "fnx_gguf_open": (_I, [C.c_char_p, _P]),
+    "fnx_gguf_close": (None, [_P]),
+    "fnx_gguf_count": (_I, [_P]),
+    "fnx_gguf_shards": (_I, [_P]),
+    "fnx_gguf_tensor_at": (_I, [_P, _I, _P]),
+    "fnx_gguf_find": (_I, [_P, C.c_char_p, _P]),
+    "fnx_gguf_num": (_I, [_P, C.c_char_p, _P]),
+    "fnx_gguf_str": (_I, [_P, C.c_char_p, _P, _Z]),
+    "fnx_gguf_int_array": (_I, [_P, C.c_char_p, _P, _Z, _P]),
+    "fnx_gguf_rows_f32": (_I, [_P, C.c_int64, C.c_int64, _P]),
+    "fnx_gguf_model_config": (_I, [_P, _P]),
+    "fnx_engine_load_gguf": (_I, [_P, _P, _P]),
 }
 EXPORTS = tuple(_PROTOS)
 
@@ -492,6 +507,94 @@ def accept_sample(cand_v, cand_i, tok, s: Sampling, seed: int, seq: int, step, q
 
 
 # ------------------------------------------------------------------------------------------------ engine
+class LogitRules(C.Structure):
+    _fields_ = [("repeat", C.c_float), ("freq", C.c_float), ("present", C.c_float), ("last_n", C.c_int), ("bias_tok", C.c_void_p),
+                ("bias_val", C.c_void_p), ("bias_n", C.c_int)]
+
+
+def logit_adjust(logits, ctx=None, ctx_n=None, tok=None, last_n: int = 0, repeat: float = 1.0, freq: float = 0.0, present: float = 0.0,
+                 bias_tok=None, bias_val=None):
+    """In place on logits [T][V]: the logit_bias list, then the penalties over each row's window (k_topk_rows' first half)."""
+    T, V = logits.shape
+    check(lib().fnx_logit_adjust(ptr(logits), T, V, ptr(ctx), ptr(ctx_n), ptr(tok), last_n, repeat, freq, present, ptr(bias_tok), ptr(bias_val),
+                                 0 if bias_tok is None else bias_tok.numel(), _stream()))
+    return logits
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("type", C.c_uint32), ("n_dims", C.c_int), ("ne", C.c_int64 * 4), ("data", C.c_void_p),
+                ("bytes", C.c_size_t), ("shard", C.c_int), ("offset", C.c_uint64)]
+
+
+class Gguf:
+    """The GGUF reader of the C ABI (fnx::Gguf, engine/src/gguf.hpp:47-95): host only, the file stays mapped until close()."""
+
+    def __init__(self, path):
+        self._h = C.c_void_p()
+        check(lib().fnx_gguf_open(str(path).encode(), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().fnx_gguf_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __len__(self):
+        return lib().fnx_gguf_count(self._h)
+
+    def shards(self) -> int:
+        return lib().fnx_gguf_shards(self._h)
+
+    def tensor_at(self, i: int) -> GgufTensor:
+        t = GgufTensor()
+        check(lib().fnx_gguf_tensor_at(self._h, i, C.byref(t)))
+        return t
+
+    def find(self, name: str):
+        t = GgufTensor()
+        return t if lib().fnx_gguf_find(self._h, name.encode(), C.byref(t)) else None
+
+    def num(self, key: str):
+        v = C.c_double()
+        return v.value if lib().fnx_gguf_num(self._h, key.encode(), C.byref(v)) else None
+
+    def str(self, key: str):
+        buf = C.create_string_buffer(4096)
+        return buf.value.decode() if lib().fnx_gguf_str(self._h, key.encode(), buf, 4096) else None
+
+    def int_array(self, key: str):
+        n = C.c_size_t()
+        if not lib().fnx_gguf_int_array(self._h, key.encode(), None, 0, C.byref(n)):
+            return None
+        out = (C.c_int64 * max(n.value, 1))()
+        lib().fnx_gguf_int_array(self._h, key.encode(), out, n.value, C.byref(n))
+        return list(out[:n.value])
+
+    def rows_f32(self, t: GgufTensor, row0: int = 0, n_rows=None):
+        import numpy as np
+        rows = t.ne[1] * t.ne[2] * t.ne[3]
+        n_rows = rows - row0 if n_rows is None else n_rows
+        out = np.empty((n_rows, t.ne[0]), dtype=np.float32)
+        check(lib().fnx_gguf_rows_f32(C.byref(t), row0, n_rows, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def raw(self, t: GgufTensor) -> bytes:
+        return C.string_at(t.data, t.bytes)
+
+    def model_config(self, **runtime) -> ModelConfig:
+        """The file's architecture with the caller's run-time fields (max_ctx, max_rows, n_seq, ep_rank, ep_size)."""
+        d = dict(max_ctx=8192, max_rows=8, ep_rank=0, ep_size=1, n_seq=1)
+        d.update(runtime)
+        cfg = ModelConfig(**d)
+        check(lib().fnx_gguf_model_config(self._h, C.byref(cfg)))
+        return cfg
+
+
 class Engine:
     """Engine::verify / commit / draft of the reference (engine/src/engine.hpp:50-229) over the C ABI."""
 
@@ -513,6 +616,17 @@ class Engine:
 
     def init_synthetic(self, seed: int = 0, sigma: float = 0.02):
         check(lib().fnx_engine_init_synthetic(self._h, seed, sigma))
+
+    def load_gguf(self, g: Gguf) -> int:
+        """Fills the weights from a GGUF file; returns how many tensors had to be quantised to IQ3_S on the way."""
+        n = C.c_int(0)
+        check(lib().fnx_engine_load_gguf(self._h, g._h, C.byref(n)))
+        return n.value
+
+    def config(self) -> ModelConfig:
+        cfg = ModelConfig()
+        check(lib().fnx_engine_config(self._h, C.byref(cfg)))
+        return cfg
 
     def device_bytes(self) -> int:
         return lib().fnx_engine_device_bytes(self._h)
@@ -560,6 +674,16 @@ class Engine:
     def set_sampling(self, sampling=None, seed: int = 0):
         """Sampling (an fnx Sampling struct) or None for greedy windows."""
         check(lib().fnx_engine_set_sampling(self._h, C.byref(sampling) if sampling is not None else None, seed))
+
+    def set_logit_rules(self, last_n: int = 0, repeat: float = 1.0, freq: float = 0.0, present: float = 0.0, bias=()):
+        """The request's penalties and logit_bias ((token, bias) pairs) for the following windows; no arguments: none."""
+        if last_n <= 0 and not bias:
+            check(lib().fnx_engine_set_logit_rules(self._h, None))
+            return
+        bt = (C.c_int * max(len(bias), 1))(*[int(b[0]) for b in bias])
+        bv = (C.c_float * max(len(bias), 1))(*[float(b[1]) for b in bias])
+        r = LogitRules(repeat, freq, present, last_n, C.cast(bt, C.c_void_p), C.cast(bv, C.c_void_p), len(bias))
+        check(lib().fnx_engine_set_logit_rules(self._h, C.byref(r)))
 
     def lookup(self, lk: int, d1: int = -1, root: int = -1, seq: int = 0):
         out, n = (C.c_int * MAX_ROWS)(), C.c_int()

@@ -2,7 +2,8 @@
 
     python <package>/build.py [--force] [--verbose]
 
-The shared library has a plain C ABI (include/fnx_b200.h) and links only the CUDA runtime.
+The shared library has a plain C ABI (include/fnx_b200.h) and links only the CUDA runtime.  Beside it, fnx_serve: the
+engine process of the line protocol (csrc/serve.cpp), a plain C++ program over that ABI.
 """
 from __future__ import annotations
 
@@ -15,7 +16,8 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "libfnx_b200.so"
-SOURCES = ["common.cu", "iq3s_prep.cu", "iq3s_mmv.cu", "moe_route.cu", "attn.cu", "gdn.cu", "moe_prefill.cu", "head.cu", "spec.cu", "lane_plan.cu", "engine.cu"]
+SERVE = HERE / "fnx_serve"
+SOURCES = ["common.cu", "iq3s_prep.cu", "iq3s_mmv.cu", "moe_route.cu", "attn.cu", "gdn.cu", "moe_prefill.cu", "head.cu", "spec.cu", "lane_plan.cu", "gguf.cu", "model_load.cu", "engine.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xcompiler", "-Wall"]
 
@@ -28,11 +30,20 @@ def _nvcc() -> str:
 
 
 def _stale() -> bool:
-    if not OUT.exists():
+    if not OUT.exists() or not SERVE.exists():
         return True
-    t = OUT.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [HERE.parent / "include" / "fnx_b200.h"]
+    t = min(OUT.stat().st_mtime, SERVE.stat().st_mtime)
+    deps = (list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cpp")) + list(CSRC.glob("*.hpp"))
+            + [HERE.parent / "include" / "fnx_b200.h"])
     return any(d.stat().st_mtime > t for d in deps)
+
+
+def _build_serve() -> None:
+    cmd = ["g++", "-O2", "-std=c++17", "-Wall", str(CSRC / "serve.cpp"), "-o", str(SERVE), "-L", str(HERE), "-lfnx_b200", "-Wl,-rpath,$ORIGIN", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("fnx_serve failed to build")
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
@@ -62,6 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if r.returncode:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link failed")
+    _build_serve()
     return OUT
 
 

@@ -10,6 +10,7 @@
 #include <dlfcn.h>
 
 #include <cstring>
+#include <cmath>
 #include <map>
 #include <string>
 #include <vector>
@@ -154,6 +155,12 @@ struct fnx_engine {
     fnx_sampling sampling{};
     uint64_t sample_seed = 0;
     uint32_t* d_step = nullptr;   // [n_seq] windows sampled so far (the Philox step)
+    // the sampler's logit changes before acceptance (fnx_engine_set_logit_rules): off = none
+    bool rules_on = false;
+    fnx_logit_rules rules{};
+    int* d_bias_tok = nullptr;
+    float* d_bias_val = nullptr;
+    int bias_cap = 0;
     int* d_lk = nullptr;          // lookup: [0, MAX_ROWS) drafts, [MAX_ROWS, +2) count and match, +2 the first-draft filter, +3 the context length
     unsigned long long launches = 0;
     std::map<uint64_t, unsigned> graph_kernels;
@@ -173,12 +180,6 @@ static int dalloc(fnx_engine* e, T** p, size_t count, const char* name = nullptr
     if (name) e->tensors[name] = {q, bytes};
     return FNX_OK;
 }
-
-#define FNX_TRY(expr)              \
-    do {                           \
-        int rc_ = (expr);          \
-        if (rc_ != FNX_OK) return rc_; \
-    } while (0)
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
@@ -726,6 +727,9 @@ static int enqueue_verify(fnx_engine* e, int seq, int T, bool tree) {
         FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img));
     }
     FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0, img));
+    if (e->rules_on)   // the request's logit_bias and penalties, before either rule looks at the logits
+        FNX_TRY(fnx_logit_adjust(e->logits, T, d.V, e->d_ctx + (size_t) seq * e->cache_rows, e->d_ctx_n + seq, e->d_tok, e->rules.last_n, e->rules.repeat,
+                                 e->rules.freq, e->rules.present, e->d_bias_tok, e->d_bias_val, e->rules.bias_n, e->st));
     if (e->sampling_on) {   // the sampling rule over the rows' 64 best tokens, uniforms addressed (seed, sequence, window, slot)
         FNX_TRY(fnx_top_tokens(e->logits, T, d.V, e->cand_v, e->cand_i, e->st));
         FNX_TRY(fnx_accept_sample(e->cand_v, e->cand_i, e->d_tok, T, e->sampling, nullptr, nullptr, nullptr, e->sample_seed, (uint32_t) seq, e->d_step + seq,
@@ -1058,6 +1062,8 @@ extern "C" void fnx_engine_destroy(fnx_engine* e) {
     for (void* q : e->ipc_opened) cudaIpcCloseMemHandle(q);
     if (e->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(e->comm);
     for (void* p : e->owned) cudaFree(p);
+    if (e->d_bias_tok) cudaFree(e->d_bias_tok);
+    if (e->d_bias_val) cudaFree(e->d_bias_val);
     if (e->h_stage) cudaFreeHost(e->h_stage);
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
@@ -1147,6 +1153,7 @@ extern "C" int fnx_engine_verify(fnx_engine* e, int seq, const int* h_tok, const
     }
     const bool tree = h_parent != nullptr;
     FNX_REQUIRE(!(tree && e->sampling_on), "fnx_engine_verify: the sampling rule is defined on chains (parent must be null)");
+    FNX_REQUIRE(!(tree && e->rules_on && e->rules.last_n > 0), "fnx_engine_verify: penalty windows are defined on chains (parent must be null)");
     // the previous call's use of the staging buffer is over: every call that copies results back synchronises
     FNX_CUDA_OK(cudaStreamSynchronize(e->st));
     // the device error word reports THIS window: whatever an earlier window left was returned with its result (or is
@@ -1190,6 +1197,42 @@ extern "C" int fnx_engine_set_sampling(fnx_engine* e, const fnx_sampling* s, uin
     FNX_CUDA_OK(cudaMemset(e->d_step, 0, sizeof(uint32_t) * e->c.n_seq));
     for (SeqState& q : e->seqs) q.step = 0;
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);   // the rule is part of the captured windows
+    e->graphs.clear();
+    return FNX_OK;
+}
+
+extern "C" int fnx_engine_set_logit_rules(fnx_engine* e, const fnx_logit_rules* r) {
+    FNX_REQUIRE(e, "fnx_engine_set_logit_rules: null engine");
+    if (r) {
+        FNX_REQUIRE(r->last_n >= 0 && r->last_n <= FNX_PENALTY_CAP, "fnx_engine_set_logit_rules: a penalty window of %d tokens (0..%d)", r->last_n, FNX_PENALTY_CAP);
+        FNX_REQUIRE(r->last_n == 0 || (r->repeat > 0.f && std::isfinite(r->repeat) && std::isfinite(r->freq) && std::isfinite(r->present)),
+                    "fnx_engine_set_logit_rules: penalties %g, %g, %g (repeat > 0, all finite)", (double) r->repeat, (double) r->freq, (double) r->present);
+        FNX_REQUIRE(r->bias_n >= 0 && (r->bias_n == 0 || (r->bias_tok && r->bias_val)), "fnx_engine_set_logit_rules: a bias list of %d entries without its arrays", r->bias_n);
+        for (int i = 0; i < r->bias_n; ++i)
+            FNX_REQUIRE(r->bias_tok[i] >= 0 && r->bias_tok[i] < e->c.vocab && std::isfinite(r->bias_val[i]), "fnx_engine_set_logit_rules: bias entry %d (token %d)", i, r->bias_tok[i]);
+    }
+    FNX_CUDA_OK(cudaStreamSynchronize(e->st));
+    e->rules_on = r != nullptr && (r->last_n > 0 || r->bias_n > 0);
+    if (e->rules_on) {
+        e->rules = *r;
+        if (r->bias_n > e->bias_cap) {   // the lists live on the device: the captured windows read them there
+            if (e->d_bias_tok) cudaFree(e->d_bias_tok);
+            if (e->d_bias_val) cudaFree(e->d_bias_val);
+            e->d_bias_tok = nullptr;
+            e->d_bias_val = nullptr;
+            e->bias_cap = 0;
+            FNX_CUDA_OK(cudaMalloc((void**) &e->d_bias_tok, sizeof(int) * (size_t) r->bias_n));
+            FNX_CUDA_OK(cudaMalloc((void**) &e->d_bias_val, sizeof(float) * (size_t) r->bias_n));
+            e->bias_cap = r->bias_n;
+        }
+        if (r->bias_n > 0) {
+            FNX_CUDA_OK(cudaMemcpy(e->d_bias_tok, r->bias_tok, sizeof(int) * (size_t) r->bias_n, cudaMemcpyHostToDevice));
+            FNX_CUDA_OK(cudaMemcpy(e->d_bias_val, r->bias_val, sizeof(float) * (size_t) r->bias_n, cudaMemcpyHostToDevice));
+        }
+        e->rules.bias_tok = nullptr;   // the caller's arrays are not kept
+        e->rules.bias_val = nullptr;
+    }
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);   // the rules are part of the captured windows
     e->graphs.clear();
     return FNX_OK;
 }
@@ -1473,6 +1516,12 @@ extern "C" int fnx_engine_counters(fnx_engine* e, unsigned long long* h_out3) {
 }
 extern "C" int fnx_engine_pos(const fnx_engine* e, int seq) { return e && seq >= 0 && seq < e->c.n_seq ? e->seqs[seq].pos : -1; }
 extern "C" fnx_stream fnx_engine_stream(fnx_engine* e) { return e ? (fnx_stream) e->st : nullptr; }
+
+extern "C" int fnx_engine_config(const fnx_engine* e, fnx_model_config* out) {
+    FNX_REQUIRE(e && out, "fnx_engine_config: null argument");
+    *out = e->c;
+    return FNX_OK;
+}
 
 extern "C" int fnx_comm_unique_id(void* h_id128) {
     FNX_REQUIRE(h_id128, "fnx_comm_unique_id: null pointer");

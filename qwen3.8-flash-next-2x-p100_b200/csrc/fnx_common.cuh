@@ -31,6 +31,12 @@ int fail(int code, const char* fmt, ...);
         if (!(cond)) return ::fnxb::fail(FNX_E_ARG, __VA_ARGS__);   \
     } while (0)
 
+#define FNX_TRY(expr)                  \
+    do {                               \
+        int rc_ = (expr);              \
+        if (rc_ != FNX_OK) return rc_; \
+    } while (0)
+
 inline cudaStream_t as_stream(fnx_stream s) { return (cudaStream_t) s; }
 int sm_count();
 // raises a kernel's dynamic shared-memory limit on the current device, once per (device, kernel)

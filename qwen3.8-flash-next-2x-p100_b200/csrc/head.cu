@@ -193,6 +193,62 @@ extern "C" int fnx_top_tokens(const float* logits, int T, int V, float* out_v, i
     return FNX_OK;
 }
 
+// ---- the sampler's logit changes (the first half of k_topk_rows, engine/src/topk.cuh:30-45): per window row, the request's
+// logit_bias added, then llama.cpp's penalties stage over the row's penalty window: each token of the window once, `repeat`
+// multiplying a non-positive logit and dividing a positive one, then frequency x count and presence taken off.
+// Row j's window is the last `last_n` tokens of (the sequence's kept tokens, then window rows 0..j): the tokens before the
+// one row j's logits choose.  One block per row; the window is staged in shared memory and each thread settles the tokens
+// whose first place in the window is its own.
+constexpr int ADJ_THREADS = 256;
+
+__global__ void __launch_bounds__(ADJ_THREADS) k_logit_adjust(float* __restrict__ logits, int V, const int* __restrict__ ctx, const int* __restrict__ ctx_n,
+                                                             const int* __restrict__ tok, int last_n, float repeat, float freq, float present,
+                                                             const int* __restrict__ bias_tok, const float* __restrict__ bias_val, int bias_n) {
+    extern __shared__ int win[];
+    pdl_wait();
+    const int row = blockIdx.x, tid = threadIdx.x;
+    float* L = logits + (size_t) row * V;
+    for (int i = tid; i < bias_n; i += ADJ_THREADS) {   // each token once in the list
+        const int t = bias_tok[i];
+        if (t >= 0 && t < V) L[t] += bias_val[i];
+    }
+    if (last_n <= 0) return;
+    const int n = *ctx_n, len = n + row + 1, start = len > last_n ? len - last_n : 0, w = len - start;
+    for (int i = tid; i < w; i += ADJ_THREADS) {
+        const int at = start + i;
+        win[i] = at < n ? ctx[at] : tok[at - n];
+    }
+    __syncthreads();   // the window staged, and a token in both lists has its bias in before its penalty
+    for (int i = tid; i < w; i += ADJ_THREADS) {
+        const int t = win[i];
+        if (t < 0 || t >= V) continue;
+        bool first = true;
+        for (int j = 0; j < i && first; ++j) first = win[j] != t;
+        if (!first) continue;
+        int cnt = 1;
+        for (int j = i + 1; j < w; ++j) cnt += win[j] == t;
+        float l = L[t];
+        l = l <= 0.f ? l * repeat : l / repeat;
+        L[t] = __fsub_rn(__fsub_rn(l, __fmul_rn((float) cnt, freq)), present);   // each step rounded, as written (no fused multiply-add)
+    }
+}
+
+extern "C" int fnx_logit_adjust(float* logits, int T, int V, const int* ctx, const int* ctx_n, const int* tok, int last_n, float repeat, float freq,
+                                float present, const int* bias_tok, const float* bias_val, int bias_n, fnx_stream st) {
+    FNX_REQUIRE(logits && T >= 1 && T <= FNX_MAX_ROWS && V >= 1, "fnx_logit_adjust: bad arguments");
+    FNX_REQUIRE(last_n >= 0 && last_n <= FNX_PENALTY_CAP, "fnx_logit_adjust: a penalty window of %d tokens (0..%d)", last_n, FNX_PENALTY_CAP);
+    FNX_REQUIRE(last_n == 0 || (ctx && ctx_n && tok), "fnx_logit_adjust: penalties need the context and the window's tokens");
+    FNX_REQUIRE(last_n == 0 || repeat > 0.f, "fnx_logit_adjust: repeat penalty %g (> 0)", (double) repeat);
+    FNX_REQUIRE(bias_n >= 0 && (bias_n == 0 || (bias_tok && bias_val)), "fnx_logit_adjust: a bias list of %d entries without its arrays", bias_n);
+    {
+        const cudaError_t le_ = launch_k(k_logit_adjust, dim3(T), dim3(ADJ_THREADS), sizeof(int) * (size_t) (last_n > 0 ? last_n : 1), as_stream(st), logits, V, ctx,
+                                         ctx_n, tok, last_n, repeat, freq, present, bias_tok, bias_val, bias_n);
+        if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_logit_adjust: launch failed: %s", cudaGetErrorString(le_));
+    }
+    FNX_LAUNCH_OK("fnx_logit_adjust");
+    return FNX_OK;
+}
+
 extern "C" int fnx_embed_rows(const void* table_f16, const int* tok, int T, int H, float* R, fnx_stream st) {
     FNX_REQUIRE(table_f16 && tok && R && T >= 1, "fnx_embed_rows: bad arguments");
     {

@@ -517,3 +517,274 @@ def test_a_missing_peer_times_out_and_leaves_the_context_usable(F):
         assert eng.pos() == 0
     finally:
         eng.close()
+
+
+def _weight_names(eng_cfg):
+    names = ["out_norm", "head", "embed", "mtp.e_norm", "mtp.h_norm", "mtp.out_norm", "mtp.fc_emb", "mtp.fc_hid"]
+    for l in list(range(eng_cfg.n_layer)) + ["mtp"]:
+        attn = l == "mtp" or (l + 1) % eng_cfg.attn_every == 0
+        pre = "mtp." if l == "mtp" else f"l{l}."
+        names += [pre + n for n in ("norm1", "norm2", "w_in", "w_out", "router", "experts_gu", "experts_dn", "shared_gu", "shared_dn")]
+        names += [pre + n for n in (("q_norm", "k_norm") if attn else ("conv_w", "dt", "a", "g_norm"))]
+    if eng_cfg.draft_vocab:
+        names += ["mtp.head", "mtp.vocab"]
+    return names
+
+
+def test_gguf_load_restores_every_weight_bit(F, tmp_path):
+    """An engine's weights written to a GGUF file under llama.cpp's names (gguf-py's writer) and loaded into a second engine:
+    every weight tensor holds the same bytes, nothing had to be quantised, and both engines emit the same tokens.  An
+    expert-parallel rank loads its own slice of the stacked expert tensors."""
+    from gguf_files import model_meta, tiny_model_tensors, write_gguf
+    cfg = small_cfg(F, draft_vocab=512)
+    a = F.Engine(cfg)
+    a.init_synthetic(seed=5, sigma=0.02)
+    # vectors that the synthetic model leaves at 1: make them distinct so that a swapped name shows
+    g0 = torch.Generator(device="cuda").manual_seed(1)
+    for n in _weight_names(cfg):
+        if n.endswith(("norm1", "norm2", "q_norm", "k_norm", "g_norm", "e_norm", "h_norm", "out_norm")):
+            t = a.tensor(n, torch.float32)
+            t.copy_(1.0 + 0.1 * torch.randn(t.shape, device="cuda", generator=g0))
+    path = tmp_path / "tiny.gguf"
+    write_gguf(path, model_meta(cfg), tiny_model_tensors(F, a, cfg))
+    g = F.Gguf(path)
+    cfg_b = g.model_config(max_ctx=cfg.max_ctx, max_rows=cfg.max_rows)
+    b = F.Engine(cfg_b)
+    assert b.load_gguf(g) == 0
+    tile_rows = 16 * (16 // (cfg.hidden // 256))
+
+    def in_rows(n):   # rows of an input projection that the file holds (the engine pads them to whole tiles; the padding stays zero)
+        attn = n.startswith("mtp.") or (int(n[1:n.index(".")]) + 1) % cfg.attn_every == 0
+        used = (cfg.n_q_head * 2 + 2 * cfg.n_kv_head) * cfg.head_dim if attn else (2 * cfg.gdn_k_head + 2 * cfg.gdn_v_head) * cfg.gdn_head_dim + 2 * cfg.gdn_v_head
+        return used, (used + tile_rows - 1) // tile_rows * tile_rows
+
+    def same(x, y, n):
+        ta, tb = x.tensor(n, torch.uint8), y.tensor(n, torch.uint8)
+        if not n.endswith("w_in"):
+            return ta.shape == tb.shape and torch.equal(ta, tb)
+        used, rows = in_rows(n)
+        ga = F.iq3s_untile(ta, rows, cfg.hidden).view(rows, -1)
+        gb = F.iq3s_untile(tb, rows, cfg.hidden).view(rows, -1)
+        return torch.equal(ga[:used], gb[:used]) and int(gb[used:].abs().max() if rows > used else 0) == 0
+
+    for n in _weight_names(cfg):
+        assert same(a, b, n), n
+    toks = np.random.default_rng(3).integers(0, cfg.vocab, size=7).tolist()
+    for e in (a, b):
+        e.reset()
+        e.prefill(toks[:4])
+    ra, rb = a.verify(toks[4:]), b.verify(toks[4:])
+    assert ra == rb
+    a.commit(ra[1]); b.commit(rb[1])
+    assert a.draft(3) == b.draft(3)
+    # rank 1 of 2: experts [16, 32) of the stacked tensors
+    cfg_c = g.model_config(max_ctx=cfg.max_ctx, max_rows=cfg.max_rows, ep_rank=1, ep_size=2)
+    c = F.Engine(cfg_c)
+    assert c.load_gguf(g) == 0
+    for n in ("l0.experts_gu", "l3.experts_dn", "mtp.experts_gu"):
+        ta, tc = a.tensor(n, torch.uint8), c.tensor(n, torch.uint8)
+        assert ta.numel() == 2 * tc.numel() and torch.equal(ta[tc.numel():], tc), n
+    assert torch.equal(a.tensor("l1.router", torch.uint8), c.tensor("l1.router", torch.uint8))
+    c.close()
+    b.close()
+    g.close()
+    # the same model with some matrices in other formats: they are quantised on the way in (counted), the rest stays bit-equal,
+    # and an architecture mismatch is refused
+    from gguf import GGMLQuantizationType as QT
+    from gguf.quants import dequantize, quantize
+    t = tiny_model_tensors(F, a, cfg)
+    H = cfg.hidden
+    wo = dequantize(t["blk.3.attn_output.weight"][0], QT.IQ3_S).reshape(H, -1)
+    t["blk.3.attn_output.weight"] = wo.astype(np.float16)
+    al = dequantize(t["blk.0.ssm_alpha.weight"][0], QT.IQ3_S).reshape(-1, H)
+    t["blk.0.ssm_alpha.weight"] = al.astype(np.float32)
+    sd = dequantize(t["blk.1.ffn_down_shexp.weight"][0], QT.IQ3_S).reshape(H, -1)
+    t["blk.1.ffn_down_shexp.weight"] = (quantize(sd, QT.Q8_0), QT.Q8_0)
+    path2 = tmp_path / "mixed.gguf"
+    write_gguf(path2, model_meta(cfg), t)
+    g = F.Gguf(path2)
+    b = F.Engine(g.model_config(max_ctx=cfg.max_ctx, max_rows=cfg.max_rows))
+    assert b.load_gguf(g) == 3
+    assert same(a, b, "l3.w_in") and same(a, b, "l0.w_out")
+    # weights that IQ3_S holds exactly come back as the same values (f16 holds them exactly too; Q8_0 to its own rounding)
+    wa = F.iq3s_dequant_tiles(a.tensor("l3.w_out", torch.uint8), H, wo.shape[1]).cpu().numpy()
+    wb = F.iq3s_dequant_tiles(b.tensor("l3.w_out", torch.uint8), H, wo.shape[1]).cpu().numpy()
+    assert np.linalg.norm(wb - wa) / np.linalg.norm(wa) < 0.1
+    wrong = F.Engine(small_cfg(F, draft_vocab=512, n_layer=8))
+    with pytest.raises(F.FnxError, match="architecture"):
+        wrong.load_gguf(g)
+    wrong.close()
+    b.close()
+    g.close()
+    a.close()
+
+
+class _Serve:
+    """fnx_serve as a child process, spoken to a line at a time"""
+
+    def __init__(self, *args):
+        import pathlib
+        import subprocess
+        exe = pathlib.Path(__file__).resolve().parents[1] / "qwen3.8-flash-next-2x-p100_b200" / "fnx_serve"
+        self.p = subprocess.Popen([str(exe), "--serve", *map(str, args)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+
+    def line(self):
+        l = self.p.stdout.readline()
+        assert l, "fnx_serve closed its output"
+        return l.rstrip("\n")
+
+    def send(self, *lines):
+        self.p.stdin.write("".join(l + "\n" for l in lines))
+        self.p.stdin.flush()
+
+    def reply(self):
+        """the lines of one request's answer: (PP lines, RESUME count, tokens, DONE fields) or the ERR line"""
+        pp, toks, resume = [], [], None
+        while True:
+            l = self.line()
+            w = l.split()
+            if w[0] == "ERR":
+                return l
+            if w[0] == "PP":
+                pp.append((int(w[1]), int(w[2])))
+            elif w[0] == "RESUME":
+                resume = int(w[1])
+            elif w[0] == "T":
+                toks.append(int(w[1]))
+            elif w[0] == "DONE":
+                return pp, resume, toks, w[1:]
+
+    def quit(self):
+        self.send("QUIT")
+        return self.p.wait(timeout=60)
+
+
+def test_serve_process_speaks_the_line_protocol(F, tmp_path):
+    """fnx_serve on a small model file: a greedy request's tokens are the plain greedy tokens of the same engine calls made from
+    Python (speculative windows change nothing), a prompt that goes on from the last one reuses it, seeded sampling repeats,
+    STOP cancels, bad lines answer ERR and the process carries on."""
+    from gguf_files import model_meta, tiny_model_tensors, write_gguf
+    cfg = small_cfg(F, max_ctx=1024)
+    a = F.Engine(cfg)
+    a.init_synthetic(seed=9, sigma=0.02)
+    path = tmp_path / "tiny.gguf"
+    meta = model_meta(cfg)
+    write_gguf(path, meta, tiny_model_tensors(F, a, cfg))
+    rng = np.random.default_rng(21)
+    prompt = rng.integers(0, cfg.vocab, size=40).tolist()
+
+    def plain(eng, prompt, n_new, fresh=True):   # one-row greedy windows
+        if fresh:
+            eng.reset()
+        if len(prompt) > 1:
+            eng.prompt(prompt[:-1])
+        x, out = prompt[-1], []
+        for _ in range(n_new):
+            n, path_, em = eng.verify([x])
+            eng.commit([0])
+            x = em[0]
+            out.append(x)
+        return out
+
+    want = plain(a, prompt, 24)
+    s = _Serve("--native", path, "--max-context", 1024, "--spec", 3, "--lookup", 6, "--prompt-chunk", 4096)
+    assert s.line().startswith("INFO engine=fnx_b200 version=")
+    assert s.line() == "READY 1024 stop"
+    csv = lambda ids: ",".join(map(str, ids))
+    s.send(f"GEN 24 {csv(prompt)}")
+    pp, resume, toks, done = s.reply()
+    assert pp == [(39, 39)] and resume == 0
+    assert toks == want
+    assert done[0] == "24" and done[1] == "40" and done[4] == "length" and int(done[6]) >= int(done[5]) >= 0 and done[7] == "0"
+    # the conversation goes on: the engine holds the prompt and all but the last generated token
+    more = prompt + want + rng.integers(0, cfg.vocab, size=9).tolist()
+    s.send(f"GEN 10 {csv(more)}")
+    pp, resume, toks2, done = s.reply()
+    assert resume == len(prompt) + len(want) - 1 and pp == [(len(more) - 1, len(more) - 1)] and done[7] == str(resume)
+    # the same from Python: the engine `a` holds prompt + want[:-1] too (its last window's token is not kept yet)
+    a.prompt(more[len(prompt) + len(want) - 1:-1])
+    x, want2 = more[-1], []
+    for _ in range(10):
+        n, path_, em = a.verify([x])
+        a.commit([0])
+        x = em[0]
+        want2.append(x)
+    assert toks2 == want2
+    # a prompt that does not go on from the engine's tokens starts over; chunks of the read are reported
+    s.send("GEN 3 " + csv(prompt[:30]))
+    pp, resume, toks3, done = s.reply()
+    assert resume == 0 and pp == [(29, 29)] and toks3 == plain(a, prompt[:30], 3)
+    # seeded sampling repeats itself, whatever ran in between
+    s.send(f"GEN 12 temperature=0.9 top_k=20 seed=77 {csv(prompt[:20])}")
+    r1 = s.reply()
+    s.send(f"GEN 5 {csv(prompt[:12])}")
+    s.reply()
+    s.send(f"GEN 12 temperature=0.9 top_k=20 seed=77 {csv(prompt[:20])}")
+    r2 = s.reply()
+    assert r1[2] == r2[2] and len(r1[2]) == 12
+    s.send(f"GEN 12 temperature=0.9 top_k=20 seed=78 {csv(prompt[:20])}")
+    assert s.reply()[2] != r1[2]
+    # STOP is for the latest request: it ends with "cancel", short of its max_new
+    s.send(f"GEN 600 {csv(prompt)}", "STOP")
+    pp, resume, toks4, done = s.reply()
+    assert done[4] == "cancel" and len(toks4) < 600
+    # refused lines leave the process serving
+    s.send("PING", "BGEN 0 5 1,2", "GEN 2000 1,2", f"GEN 2 {csv(prompt[:5])}")
+    assert s.reply() == "ERR PING: not supported by fnx_serve"
+    assert s.reply() == "ERR BGEN: fnx_serve runs without --batch"
+    assert s.reply() == "ERR GEN: prompt + max_new exceed the context"
+    assert len(s.reply()[2]) == 2
+    # logit_bias reaches greedy requests too: a large bias on one token makes it every pick; taken away, the plain tokens are back
+    s.send(f"GEN 4 logit_bias=77:90 {csv(prompt[:9])}", f"GEN 4 {csv(prompt[:9])}")
+    assert s.reply()[2] == [77, 77, 77, 77]
+    assert s.reply()[2] == plain(a, prompt[:9], 4)
+    # penalties: a presence penalty that no logit can overcome forbids every token of the window, so nothing repeats
+    s.send(f"GEN 24 temperature=0.8 seed=3 penalty_present=80 penalty_last_n=64 {csv(prompt[:9])}")
+    got = s.reply()[2]
+    assert len(got) == 24 and len(set(got)) == 24 and not set(got) & set(prompt[:9])
+    assert s.quit() == 0
+    a.close()
+    # an end-of-sequence token from the command line ends a reply with "stop"
+    s = _Serve("--native", path, "--max-context", 1024, "--spec", 3, "--lookup", 0, "--eos", want[5])
+    s.line(), s.line()
+    s.send(f"GEN 24 {csv(prompt)}")
+    pp, resume, toks, done = s.reply()
+    assert toks == want[:want.index(want[5]) + 1] and done[4] == "stop"
+    assert s.quit() == 0
+
+
+def test_logit_rules_change_the_window_rows(F, O, model):
+    """The engine's windows under a request's logit_bias and penalties: the logits left in the window buffer are the plain
+    window's logits changed by the oracle's restatement of the sampler's first stage (row j's penalty window: the kept tokens
+    and window rows 0..j), and the greedy result is their argmax."""
+    cfg, eng, om = model
+    rng = np.random.default_rng(8)
+    eng.reset()
+    eng.set_logit_rules()
+    prompt = rng.integers(0, 50, size=30).tolist()          # a small alphabet: tokens repeat inside the window
+    eng.prefill(prompt)
+    toks = rng.integers(0, 50, size=5).tolist()
+    eng.verify(toks)
+    plain = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5].copy()
+    bias = [(3, 2.5), (int(toks[1]), -1.0), (cfg.vocab - 1, 50.0)]
+    for last_n, rep, fr, pr, b in [(16, 1.3, 0.2, 0.4, bias), (64, 1.1, 0.0, 0.0, ()), (0, 1.0, 0.0, 0.0, bias), (4096, 0.8, 0.05, -0.1, bias[:1])]:
+        eng.set_logit_rules(last_n, rep, fr, pr, b)
+        n, path, em = eng.verify(toks)
+        got = eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5]
+        want = O.logit_adjust(plain, prompt, toks, last_n, rep, fr, pr, b)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (last_n, rep)
+        best = want.argmax(axis=1)
+        k = 1
+        while k < 5 and toks[k] == best[k - 1]:
+            k += 1
+        assert n == k and em == best[:k].tolist()
+    with pytest.raises(F.FnxError, match="chains"):
+        eng.set_logit_rules(8, 1.2)
+        eng.verify(toks[:3], [-1, 0, 0])
+    with pytest.raises(F.FnxError, match="penalty window"):
+        eng.set_logit_rules(5000, 1.2)
+    with pytest.raises(F.FnxError, match="bias entry"):
+        eng.set_logit_rules(0, bias=[(cfg.vocab, 1.0)])
+    eng.set_logit_rules()
+    eng.verify(toks)
+    assert np.array_equal(eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5], plain)

@@ -630,3 +630,26 @@ def test_cpp_consumer_of_the_header(F):
     for rows, cols in ((256, 1024), (512, 2048)):
         r = subprocess.run([str(exe), str(rows), str(cols)], capture_output=True, text=True, timeout=300)
         assert r.returncode == 0 and r.stdout.startswith("ok "), (r.returncode, r.stdout, r.stderr)
+
+
+def test_logit_adjust_matches_oracle(F, O):
+    """fnx_logit_adjust against the oracle's restatement, bit for bit: bias only, penalties only, both, windows shorter and longer
+    than the context, a token in both lists, tokens outside the vocabulary (image cells) skipped."""
+    rng = np.random.default_rng(5)
+    V = 3000
+    for T, n_ctx, last_n, rep, fr, pr, nb in [(1, 0, 8, 1.2, 0.1, 0.3, 0), (5, 200, 64, 1.3, 0.0, 0.0, 4), (8, 40, 4096, 0.9, 0.2, -0.5, 300), (3, 7000, 4096, 1.05, 0.01, 0.0, 1),
+                                              (6, 10, 0, 1.0, 0.0, 0.0, 17), (4, 33, 1, 2.0, 1.0, 1.0, 2)]:
+        logits = rng.standard_normal((T, V)).astype(np.float32) * 4
+        ctx = rng.integers(0, 60, size=n_ctx).astype(np.int32)
+        if n_ctx > 3:
+            ctx[1] = V + 5            # not a vocabulary token
+        tok = rng.integers(0, 60, size=T).astype(np.int32)
+        bt = rng.choice(V, size=nb, replace=False).astype(np.int32)
+        if nb:
+            bt[0] = tok[0]
+        bv = (rng.standard_normal(nb) * 3).astype(np.float32)
+        want = O.logit_adjust(logits, ctx, tok, last_n, rep, fr, pr, list(zip(bt.tolist(), bv.tolist())))
+        d = torch.from_numpy(logits).cuda()
+        F.logit_adjust(d, torch.from_numpy(np.concatenate([ctx, np.zeros(1, np.int32)])).cuda(), torch.tensor([n_ctx], dtype=torch.int32, device="cuda"),
+                       torch.from_numpy(tok).cuda(), last_n, rep, fr, pr, torch.from_numpy(bt).cuda() if nb else None, torch.from_numpy(bv).cuda() if nb else None)
+        assert np.array_equal(d.cpu().numpy().view(np.uint32), want.view(np.uint32)), (T, n_ctx, last_n)
