@@ -1,7 +1,7 @@
 // The engine process for a front end that speaks the reference's line protocol (engine/tools/sfnx.cpp:1-19): token ids
 // in, token ids out, on stdin / stdout.  The server tokenizes, applies the chat template and matches stop strings.
 //
-//   fnx_serve --serve --native MODEL.gguf [--max-context N] [--spec K] [--lookup K] [--eos ID,ID]
+//   fnx_serve --serve --native MODEL.gguf [--max-context N] [--spec K] [--lookup K] [--eos ID,ID] [--batch SLOTS]
 //
 // After loading: INFO engine=fnx_b200 ... and READY <max context> stop.  One request at a time:
 //   GEN <max_new> [key=value ...] <ids csv>
@@ -12,6 +12,12 @@
 // speculative-sampling rule over each row's 64 best tokens); penalty_repeat penalty_freq penalty_present penalty_last_n (sampled
 // requests) and logit_bias=<id>:<bias>,... (greedy ones too) change each window row's logits before the rule looks at them.
 // A prompt that extends what the engine already holds reads only its new tokens (RESUME counts the reused ones).
+// With --batch (INFO batch_slots=N): BGEN <slot> <max_new> <ids csv> reads a prompt into a free slot (each slot one of the
+// engine's sequences) between the decoding slots' windows and answers its first token as T + DONE, then BADM <slot> 1 if it
+// goes on (0 if not); the decoding slots share windows (a row each and their draft-layer drafts: the engine's batched lanes)
+// and stream BT <slot> <id> ... BDONE <slot> <produced> <finish> <ms> <drafts_accepted> <drafts_offered> <rounds>.  BSTOP <slot>
+// ends a decoding slot, or its prompt read at the next chunk.  Batched slots decode greedily; sampled requests run as GEN.
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstdio>
@@ -39,7 +45,7 @@ void say(const std::string& line) {
 
 struct Args {
     std::string gguf;
-    int max_ctx = 32768, K = 4, lookup = 15, prompt_chunk = 8192;
+    int max_ctx = 32768, K = 4, lookup = 15, prompt_chunk = 8192, batch = 1;
     std::vector<int> eos;
 };
 
@@ -63,9 +69,8 @@ Args parse_args(int argc, char** argv) {
         }
         // the reference's draft-layer files and card layout: this engine's file holds the draft layer, one GPU holds the model
         else if (k == "--mtp" || k == "--draft-vocab" || k == "--layer-split" || k == "--conversation-cache-mib") val();
-        else if (k == "--batch") {
-            if (std::stoi(val()) != 1) throw std::runtime_error("--batch: this process serves one request at a time (batched lanes are the library's fnx_engine_verify_lanes)");
-        } else throw std::runtime_error("unknown argument " + k);
+        else if (k == "--batch") a.batch = std::stoi(val());
+        else throw std::runtime_error("unknown argument " + k);
     }
     if (!serve) throw std::runtime_error("fnx_serve runs as --serve");
     if (a.gguf.empty()) throw std::runtime_error("--native is required");
@@ -73,6 +78,7 @@ Args parse_args(int argc, char** argv) {
     if (a.lookup < 0 || a.lookup > FNX_MAX_ROWS - 1) throw std::runtime_error("--lookup must be 0.." + std::to_string(FNX_MAX_ROWS - 1));
     if (a.max_ctx < 16) throw std::runtime_error("--max-context must be at least 16");
     if (a.prompt_chunk < 1) throw std::runtime_error("--prompt-chunk must be at least 1");
+    if (a.batch < 1 || a.batch > fnx_serve::MAX_SLOTS) throw std::runtime_error("--batch must be 1.." + std::to_string(fnx_serve::MAX_SLOTS));
     return a;
 }
 
@@ -92,6 +98,16 @@ struct Server {
     std::vector<int> history;   // the tokens sequence 0 holds
     bool sampling = false;      // the acceptance rule the engine is set to
     bool rules = false;         // the engine applies a request's penalties or logit_bias
+    struct Slot {
+        bool decoding = false;
+        long seq = 0;               // its request's number
+        int max_new = 0, produced = 0, rounds = 0;
+        int x = 0;                  // the next window's first row: the last token it emitted
+        std::vector<int> drafts;
+        long accepted = 0, offered = 0;
+        std::chrono::steady_clock::time_point t0;
+    };
+    std::vector<Slot> slots;
     bool dirty = false;         // a request failed half way: the engine's sequence is not `history`
 
     bool is_eos(int t) const {
@@ -222,26 +238,178 @@ struct Server {
         dirty = false;
     }
 
+    bool any_decoding() const {
+        for (const Slot& sl : slots)
+            if (sl.decoding) return true;
+        return false;
+    }
+
+    // batched slots decode greedily, without logit rules: whatever a solo request set goes
+    void plain_rule() {
+        if (sampling) ok(fnx_engine_set_sampling(e, nullptr, 0), "set_sampling");
+        if (rules) ok(fnx_engine_set_logit_rules(e, nullptr), "set_logit_rules");
+        sampling = rules = false;
+    }
+
+    void finish_slot(int i, const char* finish) {
+        Slot& sl = slots[(size_t) i];
+        char buf[160];
+        std::snprintf(buf, sizeof buf, "BDONE %d %d %s %.1f %ld %ld %d", i, sl.produced, finish, ms_since(sl.t0), sl.accepted, sl.offered, sl.rounds);
+        say(buf);
+        sl.decoding = false;
+    }
+
+    // drafts a lane may carry: the chain, as far as the window's rows go round the decoding slots
+    int lane_drafts(int lanes) const { return std::max(0, std::min({a.K, FNX_LANE_ROWS - 1, c.max_rows / std::max(lanes, 1) - 1})); }
+
+    // BGEN: the prompt into the slot's sequence, its first token through a window of that sequence alone
+    void admit(const Request& r) {
+        const int i = r.slot;
+        if (i < 0 || i >= (int) slots.size() || slots[(size_t) i].decoding)
+            throw std::runtime_error("BGEN: no such free slot " + std::to_string(i) + " (--batch " + std::to_string(slots.size()) + ")");
+        if (r.temperature != 0.f || !r.bias.empty())
+            throw std::runtime_error("BGEN: batched slots decode greedily (sampling, penalties and logit_bias run as GEN)");
+        plain_rule();
+        Slot& sl = slots[(size_t) i];
+        sl = Slot{};
+        sl.seq = r.seq;
+        if (i == 0) history.clear(), dirty = true;   // sequence 0 is also the solo requests'
+        ok(fnx_engine_reset(e, i), "reset");
+        const int n = (int) r.ids.size();
+        const auto t0 = std::chrono::steady_clock::now();
+        auto done_line = [&](int generated, int read, double decode_ms, const char* finish) {
+            char buf[256];
+            std::snprintf(buf, sizeof buf, "DONE %d %d %.1f %.1f %s 0 0 0", generated, read, ms_since(t0) - decode_ms, decode_ms, finish);
+            say(buf);
+        };
+        int at = 0;
+        bool cancelled = in.bstopped(i, r.seq);
+        while (at < n - 1 && !cancelled) {
+            const int m = std::min(a.prompt_chunk, n - 1 - at);
+            ok(fnx_engine_prompt(e, i, r.ids.data() + at, m), "prompt");
+            at += m;
+            say("PP " + std::to_string(at) + " " + std::to_string(n - 1));
+            cancelled = in.bstopped(i, r.seq);
+        }
+        say("RESUME 0");
+        if (cancelled) {
+            done_line(0, at, 0.0, "cancel");
+            say("BADM " + std::to_string(i) + " 0");
+            return;
+        }
+        const auto t1 = std::chrono::steady_clock::now();
+        int result[1 + 2 * FNX_MAX_ROWS];
+        const int x = r.ids.back();
+        ok(fnx_engine_verify(e, i, &x, nullptr, 1, result), "verify");
+        const int tok = result[1 + FNX_MAX_ROWS], keep = 0;
+        ok(fnx_engine_commit(e, i, &keep, 1), "commit");
+        say("T " + std::to_string(tok));
+        const bool more = !is_eos(tok) && r.max_new > 1;
+        // its first drafts (and the draft layer's cells for the kept row)
+        std::vector<int> chain((size_t) std::max(a.K, 1));
+        if (a.K > 0) ok(fnx_engine_draft(e, i, more ? a.K : 1, chain.data()), "draft");
+        done_line(1, n, ms_since(t1), is_eos(tok) ? "stop" : "length");
+        say("BADM " + std::to_string(i) + (more ? " 1" : " 0"));
+        if (!more) return;
+        sl.decoding = true;
+        sl.max_new = r.max_new;
+        sl.produced = 1;
+        sl.x = tok;
+        sl.drafts = a.K > 0 ? chain : std::vector<int>{};
+        sl.t0 = std::chrono::steady_clock::now();
+    }
+
+    // one window of every decoding slot: a row each and their drafts, accepted greedily per lane
+    void decode_step() {
+        std::vector<int> lanes;
+        for (int i = 0; i < (int) slots.size(); ++i) {
+            Slot& sl = slots[(size_t) i];
+            if (!sl.decoding) continue;
+            if (in.bstopped(i, sl.seq)) finish_slot(i, "cancel");
+            else if (fnx_engine_pos(e, i) + 1 > c.max_ctx) finish_slot(i, "length");
+            else lanes.push_back(i);
+        }
+        if (lanes.empty()) return;
+        plain_rule();
+        const int nl = (int) lanes.size(), kd = lane_drafts(nl);
+        std::vector<int> rows((size_t) nl), tok, results((size_t) nl * (1 + 2 * FNX_MAX_ROWS)), keep((size_t) nl);
+        for (int j = 0; j < nl; ++j) {
+            Slot& sl = slots[(size_t) lanes[(size_t) j]];
+            const int room = c.max_ctx - fnx_engine_pos(e, lanes[(size_t) j]) - 1;
+            if ((int) sl.drafts.size() > std::min(kd, room)) sl.drafts.resize((size_t) std::max(0, std::min(kd, room)));
+            rows[(size_t) j] = 1 + (int) sl.drafts.size();
+            tok.push_back(sl.x);
+            tok.insert(tok.end(), sl.drafts.begin(), sl.drafts.end());
+        }
+        ok(fnx_engine_verify_lanes_rows(e, nl, lanes.data(), rows.data(), tok.data(), results.data()), "verify_lanes");
+        std::vector<bool> done((size_t) nl, false);
+        std::vector<const char*> why((size_t) nl, "length");
+        for (int j = 0; j < nl; ++j) {
+            Slot& sl = slots[(size_t) lanes[(size_t) j]];
+            const int* res = results.data() + (size_t) j * (1 + 2 * FNX_MAX_ROWS);
+            const int n_acc = res[0];
+            const int* out = res + 1 + FNX_MAX_ROWS;
+            int used = 0;
+            for (int t = 0; t < n_acc && !done[(size_t) j]; ++t) {
+                say("BT " + std::to_string(lanes[(size_t) j]) + " " + std::to_string(out[t]));
+                ++used;
+                ++sl.produced;
+                if (is_eos(out[t])) why[(size_t) j] = "stop", done[(size_t) j] = true;
+                else if (sl.produced >= sl.max_new) why[(size_t) j] = "length", done[(size_t) j] = true;
+            }
+            keep[(size_t) j] = used;
+            sl.offered += (long) sl.drafts.size();
+            sl.accepted += used - 1;
+            ++sl.rounds;
+            sl.x = out[used - 1];
+        }
+        ok(fnx_engine_commit_lanes(e, nl, lanes.data(), keep.data()), "commit_lanes");
+        // the draft layer reads every lane's kept rows; the lanes that go on take its chain as their next drafts
+        const int kn = std::max(1, std::min(a.K, FNX_LANE_ROWS - 1));
+        std::vector<int> drafts((size_t) nl * kn);
+        if (a.K > 0) ok(fnx_engine_draft_lanes(e, nl, lanes.data(), kn, drafts.data()), "draft_lanes");
+        for (int j = 0; j < nl; ++j) {
+            Slot& sl = slots[(size_t) lanes[(size_t) j]];
+            if (done[(size_t) j]) finish_slot(lanes[(size_t) j], why[(size_t) j]);
+            else if (a.K > 0) sl.drafts.assign(drafts.begin() + (size_t) j * kn, drafts.begin() + (size_t) (j + 1) * kn);
+        }
+    }
+
     void run() {
         std::string line;
         long seq = 0;
-        while (in.next(line, seq)) {
+        for (;;) {
+            // requests first; the decoding slots' window when none is waiting
+            if (!in.next(line, seq, !any_decoding())) {
+                if (!any_decoding() && in.closed()) return;
+                try {
+                    decode_step();
+                } catch (const std::exception& ex) {   // the window failed: its slots end, the process carries on
+                    say(std::string("ERR ") + ex.what());
+                    for (int i = 0; i < (int) slots.size(); ++i)
+                        if (slots[(size_t) i].decoding) finish_slot(i, "cancel");
+                }
+                continue;
+            }
             if (line.empty()) continue;
             const std::string cmd = line.substr(0, line.find(' '));
             if (cmd == "QUIT") return;
-            if (cmd == "BGEN") {
-                say("ERR BGEN: fnx_serve runs without --batch");
-                continue;
-            }
-            if (cmd != "GEN") {
+            if (cmd != "GEN" && cmd != "BGEN") {
                 say("ERR " + cmd + ": not supported by fnx_serve");
                 continue;
             }
+            const bool batch = cmd == "BGEN";
+            if (batch && slots.size() < 2) {
+                say("ERR BGEN: fnx_serve runs without --batch");
+                continue;
+            }
             try {
-                Request r = fnx_serve::parse_gen(line, c.vocab, false, FNX_PENALTY_CAP);
+                Request r = fnx_serve::parse_gen(line, c.vocab, batch, FNX_PENALTY_CAP);
                 if ((long) r.ids.size() + r.max_new + 8 > c.max_ctx) throw std::runtime_error(cmd + ": prompt + max_new exceed the context");
                 r.seq = seq;
-                solo(r);
+                if (batch) admit(r);
+                else if (slots[0].decoding) throw std::runtime_error("GEN: slot 0 is decoding (a solo request runs on its sequence)");
+                else solo(r);
             } catch (const std::exception& ex) {
                 say(std::string("ERR ") + ex.what());
             }
@@ -267,8 +435,8 @@ int main(int argc, char** argv) {
     try {
         ok(fnx_gguf_open(a.gguf.c_str(), &g), "open");
         c.max_ctx = a.max_ctx;
-        c.max_rows = std::max(8, std::max(a.K, a.lookup) + 1);
-        c.n_seq = 1;
+        c.max_rows = std::max({8, std::max(a.K, a.lookup) + 1, std::min((int) FNX_MAX_ROWS, a.batch * (1 + std::min(a.K, FNX_LANE_ROWS - 1)))});
+        c.n_seq = a.batch;
         c.ep_rank = 0;
         c.ep_size = 1;
         ok(fnx_gguf_model_config(g, &c), "model file");
@@ -284,12 +452,14 @@ int main(int argc, char** argv) {
     }
     std::fprintf(stderr, "fnx_serve: loaded in %.1f s (%d tensors quantised to IQ3_S on the way), %.2f GiB on the GPU, context %d, chain %d, lookup %d\n",
                  ms_since(t_load) / 1e3, converted, fnx_engine_device_bytes(e) / 1073741824.0, a.max_ctx, a.K, a.lookup);
-    say("INFO engine=fnx_b200 version=" + std::to_string(fnx_version()) + " spec=" + std::to_string(a.K) + " conversation_cache_mib=0 logit_bias=1");
+    say("INFO engine=fnx_b200 version=" + std::to_string(fnx_version()) + " spec=" + std::to_string(a.K) + " conversation_cache_mib=0 logit_bias=1" +
+        (a.batch > 1 ? " batch_slots=" + std::to_string(a.batch) : ""));
     say("READY " + std::to_string(a.max_ctx) + " stop");
     Input in;
     std::thread reader([&] { in.run(std::cin); });
     reader.detach();
     Server srv{a, e, c, in};
+    srv.slots.resize((size_t) a.batch);
     try {
         srv.run();
     } catch (const std::exception& ex) {

@@ -11,6 +11,7 @@
 #include <cmath>
 #include <condition_variable>
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 #include <deque>
 #include <istream>
@@ -24,8 +25,11 @@
 
 namespace fnx_serve {
 
+constexpr int MAX_SLOTS = 8;
+
 // STOP is for the latest request line that has come in and for no other: one sent before a request's line never acts on
-// it, one sent after does however long the request waits in the queue.
+// it, one sent after does however long the request waits in the queue.  BSTOP <slot> is for that slot's latest BGEN in the
+// same way.
 struct Input {
     std::mutex mu;
     std::condition_variable cv;
@@ -33,8 +37,13 @@ struct Input {
     bool eof = false;
     long seq = 0;       // request lines so far
     long running = 0;   // the request the engine is on, 0: none
-    std::atomic<long> stop_upto{0};
+    long slot_seq[MAX_SLOTS] = {};   // the reader's own: the number of each slot's latest BGEN
+    std::atomic<long> stop_upto{0}, bstop_upto[MAX_SLOTS];
     std::atomic<bool> stop_now{false};
+
+    Input() {
+        for (auto& b : bstop_upto) b = 0;
+    }
 
     static bool is_request(const std::string& cmd) { return cmd == "GEN" || cmd == "BGEN"; }
 
@@ -48,8 +57,18 @@ struct Input {
                 if (running > 0 && running == seq) stop_now = true;
                 continue;
             }
+            int slot = -1;
+            if (std::sscanf(line.c_str(), "BSTOP %d", &slot) == 1) {
+                if (slot >= 0 && slot < MAX_SLOTS) bstop_upto[slot] = slot_seq[slot];
+                continue;
+            }
             const std::string cmd = line.substr(0, line.find(' '));
-            lines.emplace_back(line, is_request(cmd) ? ++seq : 0);
+            long n = 0;
+            if (is_request(cmd)) {
+                n = ++seq;
+                if (cmd == "BGEN" && std::sscanf(line.c_str() + 4, " %d", &slot) == 1 && slot >= 0 && slot < MAX_SLOTS) slot_seq[slot] = n;
+            }
+            lines.emplace_back(line, n);
             cv.notify_all();
         }
         std::lock_guard<std::mutex> lk(mu);
@@ -57,15 +76,19 @@ struct Input {
         cv.notify_all();
     }
 
-    // the next queued line; false at the end of the input
-    bool next(std::string& line, long& n) {
+    // the next queued line: waits for one when `wait`, else answers only if one is there; false: none (see closed())
+    bool next(std::string& line, long& n, bool wait = true) {
         std::unique_lock<std::mutex> lk(mu);
-        cv.wait(lk, [&] { return !lines.empty() || eof; });
+        if (wait) cv.wait(lk, [&] { return !lines.empty() || eof; });
         if (lines.empty()) return false;
         line = std::move(lines.front().first);
         n = lines.front().second;
         lines.pop_front();
         return true;
+    }
+    bool closed() {
+        std::lock_guard<std::mutex> lk(mu);
+        return eof && lines.empty();
     }
 
     // the engine takes up request n: true when a STOP for it is already in
@@ -80,6 +103,8 @@ struct Input {
         running = 0;
         stop_now = false;
     }
+    // a BSTOP (or, for the request decoding there, a STOP) came for slot's request n
+    bool bstopped(int slot, long n) const { return bstop_upto[slot].load() >= n || stop_upto.load() == n; }
 };
 
 struct Request {

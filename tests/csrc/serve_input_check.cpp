@@ -35,6 +35,19 @@ int main(int argc, char** argv) {
         std::istringstream second("STOP\n");
         live.run(second);
         std::printf("%d %d\n", (int) before, (int) live.stop_now.load());
+        // BSTOP <slot> is for that slot's latest BGEN line
+        Input b;
+        std::istringstream s1("BGEN 1 5 1,2\nBGEN 2 5 3\nBSTOP 1\n");
+        b.run(s1);
+        b.eof = false;
+        long n1 = 0, n2 = 0, n3 = 0;
+        b.next(line, n1);
+        b.next(line, n2);
+        const bool stop1 = b.bstopped(1, n1), stop2 = b.bstopped(2, n2);
+        std::istringstream s2("BGEN 1 5 4\n");
+        b.run(s2);
+        b.next(line, n3);
+        std::printf("%d %d %d %d\n", (int) stop1, (int) stop2, (int) b.bstopped(1, n3), (int) b.bstopped(1, n1));
         return 0;
     }
     std::string line;

@@ -68,9 +68,11 @@ def test_request_errors(check_exe, line, msg):
 
 def test_stop_is_for_the_latest_request_line(check_exe):
     r = subprocess.run([str(check_exe), "--stop"], capture_output=True, text=True, check=True)
-    a, b = r.stdout.strip().split("\n")
+    a, b = r.stdout.strip().split("\n")[:2]
     assert a.strip() == "GEN:1:stopped PING:0:runs GEN:2:runs GEN:3:stopped"
     assert b == "0 1"
+    # BSTOP <slot> is for that slot's latest BGEN: slot 1's first request is stopped, its second is not, slot 2's never was
+    assert r.stdout.strip().split("\n")[2] == "1 0 0 1"
 
 
 @pytest.mark.parametrize("args, msg", [
@@ -78,7 +80,7 @@ def test_stop_is_for_the_latest_request_line(check_exe):
     (["--serve"], "--native is required"),
     (["--serve", "--native"], "--native needs a value"),
     (["--serve", "--native", "m.gguf", "--spec", "99"], "--spec must be 0..31"),
-    (["--serve", "--native", "m.gguf", "--batch", "4"], "--batch: this process serves one request at a time"),
+    (["--serve", "--native", "m.gguf", "--batch", "9"], "--batch must be 1..8"),
     (["--serve", "--native", "m.gguf", "--colour", "red"], "unknown argument --colour"),
 ])
 def test_command_line(args, msg):

@@ -788,3 +788,81 @@ def test_logit_rules_change_the_window_rows(F, O, model):
     eng.set_logit_rules()
     eng.verify(toks)
     assert np.array_equal(eng.tensor("buf.logits", torch.float32).cpu().numpy().reshape(cfg.max_rows, cfg.vocab)[:5], plain)
+
+
+def test_serve_process_batched_slots(F, tmp_path):
+    """fnx_serve --batch: prompts read into slots, the decoding slots sharing windows (the engine's batched lanes).  Every slot's
+    tokens are the plain greedy tokens of its prompt alone; BSTOP ends one slot and leaves the others; a solo GEN runs
+    between windows when slot 0 is free."""
+    from gguf_files import model_meta, tiny_model_tensors, write_gguf
+    cfg = small_cfg(F, max_ctx=1024)
+    a = F.Engine(cfg)
+    a.init_synthetic(seed=9, sigma=0.02)
+    path = tmp_path / "tiny.gguf"
+    write_gguf(path, model_meta(cfg), tiny_model_tensors(F, a, cfg))
+    rng = np.random.default_rng(33)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (25, 40, 12)]
+
+    def plain(prompt, n_new):
+        a.reset()
+        a.prompt(prompt[:-1])
+        x, out = prompt[-1], []
+        for _ in range(n_new):
+            n, path_, em = a.verify([x])
+            a.commit([0])
+            x = em[0]
+            out.append(x)
+        return out
+
+    want = [plain(p, 20) for p in prompts]
+    csv = lambda ids: ",".join(map(str, ids))
+    s = _Serve("--native", path, "--max-context", 1024, "--spec", 3, "--lookup", 0, "--batch", 4, "--prompt-chunk", 4096)
+    assert "batch_slots=4" in s.line()
+    assert s.line() == "READY 1024 stop"
+    s.send(f"BGEN 1 20 {csv(prompts[0])}", f"BGEN 2 14 {csv(prompts[1])}", f"BGEN 3 1 {csv(prompts[2])}")
+    got, done, adm, first = {1: [], 2: [], 3: []}, {}, {}, []
+    while len(done) < 2 or len(adm) < 3:
+        w = s.line().split()
+        if w[0] == "T":
+            first.append(int(w[1]))
+        elif w[0] == "BADM":
+            adm[int(w[1])] = int(w[2])
+        elif w[0] == "BT":
+            got[int(w[1])].append(int(w[2]))
+        elif w[0] == "BDONE":
+            done[int(w[1])] = w[2:]
+        else:
+            assert w[0] in ("PP", "RESUME", "DONE"), w
+    assert adm == {1: 1, 2: 1, 3: 0}                      # max_new = 1 ends with its first token
+    assert first == [want[0][0], want[1][0], want[2][0]]
+    assert [first[0]] + got[1] == want[0] and [first[1]] + got[2] == want[1][:14]
+    assert done[1][0] == "20" and done[1][1] == "length" and done[2][0] == "14" and int(done[1][4]) >= int(done[1][3]) >= 0
+    # a slot stopped while it decodes; the other goes on to its end; a solo request in between
+    s.send(f"BGEN 0 600 {csv(prompts[0])}", f"BGEN 1 30 {csv(prompts[1])}")
+    seen = {0: [], 1: []}
+    sent_stop = False
+    done = {}
+    while len(done) < 2:
+        w = s.line().split()
+        if w[0] == "BT":
+            seen[int(w[1])].append(int(w[2]))
+            if not sent_stop and len(seen[0]) >= 3:
+                s.send("BSTOP 0")
+                sent_stop = True
+        elif w[0] == "BDONE":
+            done[int(w[1])] = w[2:]
+    assert done[0][1] == "cancel" and 3 <= int(done[0][0]) < 600 and done[1][1] == "length"
+    assert seen[0] == want[0][1:1 + len(seen[0])] or seen[0][:19] == want[0][1:20]
+    s.send(f"GEN 5 {csv(prompts[2])}")
+    l = s.line()
+    toks = []
+    while not l.startswith("DONE"):
+        if l.startswith("T "):
+            toks.append(int(l.split()[1]))
+        l = s.line()
+    assert toks == want[2][:5]
+    s.send("BGEN 7 5 1,2", "BGEN 1 5 temperature=0.5 1,2")
+    assert s.line() == "ERR BGEN: no such free slot 7 (--batch 4)"
+    assert s.line().startswith("ERR BGEN: batched slots decode greedily")
+    assert s.quit() == 0
+    a.close()
