@@ -589,18 +589,22 @@ def main():
         vc = torch.randn((pos0 + T + 8, nkv, hd), device="cuda").half().view(torch.int16)
         qg = torch.randn((T, nq, 2 * hd), device="cuda")
         pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
-        for _ in range(max(a.warmup, 1)):
-            F.attn_prompt(qg, kc, vc, pos)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(a.steps):
-            F.attn_prompt(qg, kc, vc, pos)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / a.steps
-        print(json.dumps({"mode": "attn-prompt", "rows": T, "position": pos0, "ms": ms, "kv_gbs": (pos0 + T / 2) * nkv * hd * 4 * ((T + 11) // 12) / ms / 1e6,
-                          "note": "fnx_attn_prompt (partials + combine); kv_gbs = cache bytes the blocks read (from L2 mostly) per second"}))
+        res = {}
+        for form, mma_sync, rows_per_block in (("tcgen05", False, 16), ("mma_sync", True, 12)):
+            for _ in range(max(a.warmup, 1)):
+                F.attn_prompt(qg, kc, vc, pos, mma_sync=mma_sync)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(a.steps):
+                F.attn_prompt(qg, kc, vc, pos, mma_sync=mma_sync)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / a.steps
+            flop = 4.0 * hd * nq * (pos0 * T + T * (T + 1) / 2)
+            res[form] = {"ms": ms, "tflops": flop / ms / 1e9, "kv_gbs": (pos0 + T / 2) * nkv * hd * 4 * ((T + rows_per_block - 1) // rows_per_block) / ms / 1e6}
+        print(json.dumps({"mode": "attn-prompt", "rows": T, "position": pos0, **res,
+                          "note": "fnx_attn_prompt, both forms; kv_gbs = cache bytes the blocks read (from L2 mostly) per second"}))
         return
     if a.prefill_moe:
         # config 3's expert path on one layer: T rows grouped by expert, gate|up + SwiGLU + down on the tensor cores

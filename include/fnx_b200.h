@@ -156,12 +156,14 @@ size_t fnx_attn_scratch_bytes(int T, int nq, int hd);
 int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
              const int* pos0, const int* parent, void* scratch, fnx_stream st);
 /* the same for a prompt's rows (attn_prompt, engine/src/kernels.hpp:252): T rows of any number, a chain (row t sees every
- * position up to pos0 + t), twelve rows per block over all the positions they see, no splits; the scores come from the f16-rounded
- * queries alone (the window form adds their low halves).  fnx_attn_prep_append takes such T when depth is null.
+ * position up to pos0 + t), no splits; the scores come from the f16-rounded queries alone (the window form adds their low
+ * halves).  Where a KV head serves eight query heads of 256 dims: sixteen rows per block on tcgen05.mma, scores and sums in
+ * tensor memory (a wait that gives up sets FNX_ERR_TIMEOUT in *err, which may be null); otherwise, or with use_mma_sync != 0:
+ * twelve rows per block on mma.sync.  fnx_attn_prep_append takes such T when depth is null.
  * scratch: fnx_attn_prompt_scratch_bytes(T, nq, hd) bytes. */
 size_t fnx_attn_prompt_scratch_bytes(int T, int nq, int hd);
 int fnx_attn_prompt(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd,
-                    const int* pos0, void* scratch, fnx_stream st);
+                    const int* pos0, void* scratch, unsigned* err, int use_mma_sync, fnx_stream st);
 /* fnx_attn without caller scratch and without any allocation (no counterpart in the reference, whose attn takes the
  * caller's buffer, engine/src/kernels.hpp:238): the split partials go to one file-scope device array of
  * FNX_ATTN_STATIC_MAX_SLOTS x (hd floats + 8 bytes) = 16.9 MB per device, for callers that may not allocate (a

@@ -80,7 +80,7 @@ _PROTOS = {
     "fnx_attn_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_attn": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
     "fnx_attn_prompt_scratch_bytes": (_Z, [_I, _I, _I]),
-    "fnx_attn_prompt": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "fnx_attn_prompt": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _I, _P]),
     "fnx_attn_static_setup": (_I, []),
     "fnx_attn_static": (_I, [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "fnx_gdn_prompt_scratch_bytes": (_Z, [_I, _I, _I, _I]),
@@ -411,15 +411,18 @@ def attn(qg, kc, vc, pos0, parent=None, scratch=None):
     return out
 
 
-def attn_prompt(qg, kc, vc, pos0):
-    """Attention of a prompt's rows (a chain of any length) over the cache: fnx_attn_prompt."""
+def attn_prompt(qg, kc, vc, pos0, mma_sync: bool = False, err=None):
+    """Attention of a prompt's rows (a chain of any length) over the cache: fnx_attn_prompt (mma_sync: the twelve-row form)."""
     import torch
     T, nq, hd2 = qg.shape
     nkv, hd = kc.shape[1], kc.shape[2]
     out = torch.empty((T, nq, hd), dtype=torch.float32, device=qg.device)
     L = lib()
     scratch = torch.empty(L.fnx_attn_prompt_scratch_bytes(T, nq, hd), dtype=torch.uint8, device=qg.device)
-    check(L.fnx_attn_prompt(ptr(qg), nq * hd2, ptr(kc), ptr(vc), ptr(out), T, nq, nkv, hd, ptr(pos0), ptr(scratch), _stream()))
+    err = new_err(qg.device) if err is None else err
+    check(L.fnx_attn_prompt(ptr(qg), nq * hd2, ptr(kc), ptr(vc), ptr(out), T, nq, nkv, hd, ptr(pos0), ptr(scratch), ptr(err), int(mma_sync), _stream()))
+    if int(err.item()):
+        raise FnxError(f"fnx_attn_prompt: device error bits {int(err.item()):#x}")
     return out
 
 

@@ -144,12 +144,23 @@ extern "C" int fnx_attn(const float* qg, int ldq, const void* kc, const void* vc
 
 extern "C" size_t fnx_attn_prompt_scratch_bytes(int T, int nq, int hd) { return (size_t) T * nq * ((size_t) hd * sizeof(float) + sizeof(AttPartial)); }
 
+namespace fnxb {
+bool attn_prompt_tc_fits(int nq, int nkv, int hd);
+int attn_prompt_tc_launch(const float* qg, int ldq, const __half* kc, const __half* vc, float* out, int T, int nq, int nkv, const int* pos0, unsigned* err,
+                          cudaStream_t st);
+}  // namespace fnxb
+
 extern "C" int fnx_attn_prompt(const float* qg, int ldq, const void* kc, const void* vc, float* out, int T, int nq, int nkv, int hd, const int* pos0,
-                               void* scratch, fnx_stream st) {
+                               void* scratch, unsigned* err, int use_mma_sync, fnx_stream st) {
     FNX_REQUIRE(qg && kc && vc && out && pos0 && scratch, "fnx_attn_prompt: null pointer");
     FNX_REQUIRE(T >= 1 && T <= 65535, "fnx_attn_prompt: %d rows", T);
     FNX_REQUIRE(hd == ATT_THREADS, "fnx_attn_prompt: head dim %d (this build: %d)", hd, ATT_THREADS);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQ, "fnx_attn_prompt: %d q heads over %d KV heads", nq, nkv);
+    if (!use_mma_sync && attn_prompt_tc_fits(nq, nkv, hd)) {
+        FNX_REQUIRE(ldq % 4 == 0 && ((uintptr_t) qg & 15) == 0 && ((uintptr_t) kc & 15) == 0 && ((uintptr_t) vc & 15) == 0 && ((uintptr_t) out & 15) == 0,
+                    "fnx_attn_prompt: rows and caches must be 16-byte aligned");
+        return attn_prompt_tc_launch(qg, ldq, (const __half*) kc, (const __half*) vc, out, T, nq, nkv, pos0, err, as_stream(st));
+    }
     float* acc = (float*) scratch;
     AttPartial* mz = (AttPartial*) (acc + (size_t) T * nq * hd);
     if (int rc = set_smem_limit((const void*) k_attn_part_prompt, (int) attn_prompt_smem())) return rc;

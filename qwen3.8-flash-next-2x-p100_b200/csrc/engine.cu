@@ -117,6 +117,7 @@ struct fnx_engine {
     int prompt_chunk = 40960;
     float *pR = nullptr, *pproj = nullptr, *pmix = nullptr, *plogits = nullptr, *ptopw = nullptr;
     int *ptopi = nullptr, *d_ptok = nullptr;
+    int prompt_attn_mma_sync = 0;   // FNX_ATTN_PROMPT_MMA=1: the prompt pass's attention on mma.sync (the comparison form)
     bool prompt_timing = false;     // fnx_engine_prompt_timing: time the prompt pass's phases with events
     float prompt_phase_ms[6] = {0, 0, 0, 0, 0, 0};   // the last timed prompt: in-proj, attention, DeltaNet, out-proj, router, experts
     void *p_moe_scratch = nullptr, *p_dense_scratch = nullptr, *p_gdn_scratch = nullptr, *p_attn_scratch = nullptr;
@@ -1279,6 +1280,7 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
     const Dims d = dims(e->c);
     if (!e->pR) {   // the chunk: large enough that an expert's rows fill the 256-row tiles of the grouped product, within the context
         if (const char* pc = getenv("FNX_PROMPT_CHUNK")) e->prompt_chunk = atoi(pc) > 0 ? atoi(pc) : e->prompt_chunk;
+        if (const char* pm = getenv("FNX_ATTN_PROMPT_MMA")) e->prompt_attn_mma_sync = atoi(pm) != 0;
         if (e->prompt_chunk > e->c.max_ctx) e->prompt_chunk = e->c.max_ctx;
     }
     const int CH = e->prompt_chunk, fast = n - 1;
@@ -1340,7 +1342,7 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
                 float* v = k + d.kv_rows;
                 FNX_TRY(fnx_attn_prep_append(qg, e->proj_ld, k, e->proj_ld, v, e->proj_ld, L.qn, L.kn, kc, vc, nt, d.nq, d.nkv, d.hd, d.nrot, e->d_pos + seq, nullptr,
                                              e->c.eps, e->c.rope_base, e->st));
-                FNX_TRY(fnx_attn_prompt(qg, e->proj_ld, kc, vc, e->pmix, nt, d.nq, d.nkv, d.hd, e->d_pos + seq, e->p_attn_scratch, e->st));
+                FNX_TRY(fnx_attn_prompt(qg, e->proj_ld, kc, vc, e->pmix, nt, d.nq, d.nkv, d.hd, e->d_pos + seq, e->p_attn_scratch, e->err, e->prompt_attn_mma_sync, e->st));
             } else {
                 mixw_l = d.nv * d.hs;
                 float* S = L.S_pool + (size_t) seq * e->NS * d.nv * d.hs * d.hs;

@@ -437,12 +437,14 @@ def test_prompt_attention_matches_windows(F, O, pos0, T):
     want = torch.cat(outs)
     p_kc, p_vc, q_p, pos = dev(kc.view(np.int16)), dev(vc.view(np.int16)), dev(qg), dev(np.array([pos0], np.int32))
     F.attn_prep_append(q_p, dev(k), dev(v), qn, kn, p_kc, p_vc, pos, None, nrot)
-    got = F.attn_prompt(q_p, p_kc, p_vc, pos)
     assert torch.equal(p_kc[:pos0 + T], w_kc[:pos0 + T]) and torch.equal(p_vc[:pos0 + T], w_vc[:pos0 + T])
-    assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 2e-3
-    if T <= 20:   # and against the oracle (a chain: no parents)
-        ref = O.attn(q_p.cpu().numpy(), p_kc.cpu().numpy().view(np.uint16), p_vc.cpu().numpy().view(np.uint16), pos0, None)
-        assert rel_err(got.cpu().numpy(), ref) < 2e-3
+    # both forms: sixteen rows per block on tcgen05.mma (this shape: eight query heads per KV head), twelve on mma.sync
+    for mma_sync in (False, True):
+        got = F.attn_prompt(q_p, p_kc, p_vc, pos, mma_sync=mma_sync)
+        assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 2e-3, mma_sync
+        if T <= 20:   # and against the oracle (a chain: no parents)
+            ref = O.attn(q_p.cpu().numpy(), p_kc.cpu().numpy().view(np.uint16), p_vc.cpu().numpy().view(np.uint16), pos0, None)
+            assert rel_err(got.cpu().numpy(), ref) < 2e-3, mma_sync
 
 
 # ------------------------------------------------------------------------------------------------ DeltaNet
