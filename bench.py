@@ -341,7 +341,7 @@ def run_config4(a, F, eng, cfg, rank, world, local, use_peer, emit=True):
 
 def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
     """Configuration 3: cold prefill of 38,912 uniform-random tokens (seed 3).  One rank reads the prompt on the prompt pass
-    (fnx_engine_prompt: projections and experts on the tensor cores, chained DeltaNet windows, window attention); expert-parallel
+    (fnx_engine_prompt: projections, experts and attention on the tensor cores, the DeltaNet scan); expert-parallel
     ranks, and `--prompt-windows`, read it through chained 32-row windows of the decode kernels.  One step = the whole prompt."""
     import numpy as np
     import torch
@@ -396,11 +396,11 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
         roof = {"bound": "tensor", "kernel": "k_pf_gemm (grouped expert products, tcgen05)", "achieved": tf.get("experts"), "peak": peak, "unit": "TFLOP/s",
                 "frac": tf.get("experts", 0.0) / peak, "peak_kind": "measured (sustained)" if pk else "fallback", "traffic": None,
                 "tflops_by_phase": tf, "note": "device ms per phase from CUDA events around the phases of every layer and chunk, in an extra pass of the same prompt; "
-                "attention runs on mma.sync, the projections and experts on tcgen05"}
+                "projections, experts and attention run on tcgen05.mma"}
     line = {"metric": "prefill tok/s (cold prompt)", "value": n / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": passes, "warmup": 1, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xint3->f32", "data": "synthetic",
             "config": {"workload": f"configuration 3: cold prefill of {n} uniform-random tokens (seed 3) " +
-                       ("through chained 32-row windows of the decode kernels" if windows else "on the prompt pass (tensor-core projections and experts, chained DeltaNet windows, window attention)"),
+                       ("through chained 32-row windows of the decode kernels" if windows else "on the prompt pass (projections, experts and attention on tcgen05.mma, DeltaNet as conv / scan / norm)"),
                        "timing": "weights (17 GB) and activations far larger than the 126 MB L2; CUDA events on the engine's stream", "parallelism": f"ep{world}", "layers": a.layers},
             "clocks": clk, "gpu_launches": int((c1[0] - c0[0]) / passes),
             "e2e": {"value": n / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * n + 4 * n, "d2h_bytes_per_step": 0, "wall_ms_per_step": wall * 1e3},

@@ -17,6 +17,9 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "fnx_common.cuh"
 
 namespace fnxb {
@@ -112,7 +115,7 @@ __device__ __forceinline__ void ta_fence_after() { asm volatile("tcgen05.fence::
 // row agree on the step's maximum through shared memory and keep half of the row's sum each.
 __global__ void __launch_bounds__(TA_THREADS, 1) k_attn_prompt_tc(const float* __restrict__ qg, int ldq, const __half* __restrict__ kc,
                                                                  const __half* __restrict__ vc, float* __restrict__ out, int T, int nq, int nkv,
-                                                                 const int* __restrict__ pos0p, unsigned* __restrict__ err,
+                                                                 const int* __restrict__ pos0p, unsigned* __restrict__ err, int use_tma,
                                                                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -147,7 +150,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) k_attn_prompt_tc(const float* _
         const int np = min(TA_N, ctx - p0);
         uint8_t* kd = Ks + b * TA_K_BYTES;
         uint8_t* vd = Vs + b * TA_V_BYTES;
-        if (np == TA_N) {
+        if (np == TA_N && use_tma) {
             if (tid == TA_SOFT) {
                 mbar_expect_tx(bar_ld + b, 2 * TA_K_BYTES);
 #pragma unroll
@@ -175,6 +178,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) k_attn_prompt_tc(const float* _
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const bool loader = tid >= TA_SOFT;
+    __syncthreads();   // the barriers are initialised before the first tensor copy names one
     if (loader) fetch_kv(0, 0);
     // the queries as f16: row r = head (r / 16), chunk row t0 + r % 16; rows past the chunk's end are zero
     for (int i = tid; i < TA_M * (TA_HD / 8); i += TA_THREADS) {
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) k_attn_prompt_tc(const float* _
         const int b = j & 1, p0 = j * TA_N;
         // this step's rows have landed: the boxes of a whole step on its buffer's barrier, the pieces of the context's last step
         // with their threads' copy groups
-        if (p0 + TA_N <= ctx) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_ld + b, (unsigned) ((j >> 1) & 1), TA_WAIT));
+        if (use_tma && p0 + TA_N <= ctx) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_ld + b, (unsigned) ((j >> 1) & 1), TA_WAIT));
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_proxy_async();   // what went through the generic proxy (pieces, P, Q) before the tensor core reads it through the async one
         if (__syncthreads_or(!ok)) {
@@ -358,10 +362,16 @@ static int attn_prompt_tc_map(CUtensorMap* map, const __half* base, int nkv) {
 int attn_prompt_tc_launch(const float* qg, int ldq, const __half* kc, const __half* vc, float* out, int T, int nq, int nkv, const int* pos0, unsigned* err,
                           cudaStream_t st) {
     if (int rc = set_smem_limit((const void*) k_attn_prompt_tc, TA_SMEM)) return rc;
+    // FNX_ATTN_PROMPT_NO_TMA=1: every step's tiles by 16-byte async copies (the comparison form)
+    static const int use_tma = []() { const char* v = getenv("FNX_ATTN_PROMPT_NO_TMA"); return v && atoi(v) ? 0 : 1; }();
     CUtensorMap map_k, map_v;
-    FNX_TRY(attn_prompt_tc_map(&map_k, kc, nkv));
-    FNX_TRY(attn_prompt_tc_map(&map_v, vc, nkv));
-    k_attn_prompt_tc<<<dim3((T + TA_POS - 1) / TA_POS, nkv), TA_THREADS, TA_SMEM, st>>>(qg, ldq, kc, vc, out, T, nq, nkv, pos0, err, map_k, map_v);
+    memset(&map_k, 0, sizeof map_k);
+    memset(&map_v, 0, sizeof map_v);
+    if (use_tma) {
+        FNX_TRY(attn_prompt_tc_map(&map_k, kc, nkv));
+        FNX_TRY(attn_prompt_tc_map(&map_v, vc, nkv));
+    }
+    k_attn_prompt_tc<<<dim3((T + TA_POS - 1) / TA_POS, nkv), TA_THREADS, TA_SMEM, st>>>(qg, ldq, kc, vc, out, T, nq, nkv, pos0, err, use_tma, map_k, map_v);
     FNX_LAUNCH_OK("fnx_attn_prompt (tensor-core form)");
     return FNX_OK;
 }
