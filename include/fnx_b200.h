@@ -98,10 +98,14 @@ typedef struct {
 int fnx_router_route(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K,
                      int e_lo, int e_hi, int add_shared, float* logits, int* topi, float* topw, fnx_job* jobs,
                      int* njobs, unsigned long long* stats, unsigned* err, fnx_stream st);
-/* the routing of any number of rows, for prompts (the prompt pass's router, engine/src/prefill.cu): logits, top K and weights
- * as fnx_router_route computes them, without a job list (fnx_moe_prefill groups the pairs itself) */
+/* the routing of any number of rows, for prompts (the prompt pass's router, engine/src/prefill.cu:653): logits, top K and
+ * weights as fnx_router_route computes them, without a job list (fnx_moe_prefill groups the pairs itself).  With scratch
+ * (fnx_router_rows_scratch_bytes(T, E, H) bytes) and 1,024 rows or more the logits are a tcgen05.mma product of the rows and the
+ * weights split into f16 high and low parts (three products; the tensor core's truncating f32 accumulation leaves the logits
+ * good to a few 1e-5, against ~1e-6 for the f32 walk that scratch = null keeps). */
+size_t fnx_router_rows_scratch_bytes(int T, int E, int H);
 int fnx_router_rows(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K, float* logits,
-                    int* topi, float* topw, unsigned* err, fnx_stream st);
+                    int* topi, float* topw, void* scratch, unsigned* err, fnx_stream st);
 /* moe_gate_up + SwiGLU (engine/src/kernels.hpp:319, :329; engine/src/moe.cuh:572-608): h[out][F] =
  * silu(Wg . xin) * (Wu . xin).  Wgu: expert e's [gate (F); up (F)] x H tile matrix at Wgu + (e - e_base) *
  * expert_stride; the shared expert (w == E) is read from Wsh. */
@@ -132,8 +136,9 @@ size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F);
 /* fnx_dense for prompt-sized row counts (the prompt pass's projections, engine/src/prefill.cu; q8s_gemm / k_mmq,
  * engine/src/kernels.hpp:56-70): y[t][r] (+)= W[r] . xin[t] for any T on the same tensor-core kernel as the prompt MoE block
  * (weights decoded from IQ3_S to f16, activations rounded to f16 once per call, f32 accumulators in tensor memory).  x is
- * [T][cols] contiguous; rows % 16 == 0; cols % 256 == 0; scratch: fnx_dense_prompt_scratch_bytes(T, cols) bytes. */
-size_t fnx_dense_prompt_scratch_bytes(int T, int cols);
+ * [T][cols] contiguous; rows % 16 == 0; cols % 256 == 0; scratch: fnx_dense_prompt_scratch_bytes(T, rows, cols) bytes.
+ * From 1,024 rows on the matrix is decoded to f16 once and the product takes both operands by tensor copies. */
+size_t fnx_dense_prompt_scratch_bytes(int T, int rows, int cols);
 int fnx_dense_prompt(const void* W, int rows, int cols, const float* x, int T, const float* norm_w, float eps, float* y,
                      int ldy, int accumulate, void* scratch, unsigned* err, fnx_stream st);
 int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu,

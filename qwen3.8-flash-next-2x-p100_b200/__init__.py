@@ -64,7 +64,8 @@ _PROTOS = {
     "fnx_dense_rows": (_I, [_I]),
     "fnx_dense": (_I, [_P, _I, _I, _P, _I, _I, _P, _F, _P, _I, _I, _P, _P]),
     "fnx_router_route": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "fnx_router_rows": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "fnx_router_rows": (_I, [_P, _P, _P, _F, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "fnx_router_rows_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_moe_gate_up": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P]),
     "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
@@ -72,7 +73,7 @@ _PROTOS = {
     "fnx_dense_image_bytes": (_Z, [_I]),
     "fnx_dense_image": (_I, [_P, _I, _I, _P, _I, _I, _F, _P, _I, _I, _P, _P]),
     "fnx_moe_prefill_scratch_bytes": (_Z, [_I, _I, _I, _I, _I]),
-    "fnx_dense_prompt_scratch_bytes": (_Z, [_I, _I]),
+    "fnx_dense_prompt_scratch_bytes": (_Z, [_I, _I, _I]),
     "fnx_dense_prompt": (_I, [_P, _I, _I, _P, _I, _P, _F, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_prefill": (_I, [_P, _Z, _P, _Z, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _P, _I, _P, _P, _P]),
     "fnx_argmax_mapped": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
@@ -309,7 +310,7 @@ def dense_prompt(W, rows: int, cols: int, x, norm_w=None, eps: float = 1e-6, out
         out = torch.zeros((T, rows), dtype=torch.float32, device=x.device)
     err = new_err(x.device) if err is None else err
     L = lib()
-    scratch = torch.empty(L.fnx_dense_prompt_scratch_bytes(T, cols), dtype=torch.uint8, device=x.device)
+    scratch = torch.empty(L.fnx_dense_prompt_scratch_bytes(T, rows, cols), dtype=torch.uint8, device=x.device)
     check(L.fnx_dense_prompt(ptr(W), rows, cols, ptr(x), T, ptr(norm_w), eps, ptr(out), out.stride(0), 1 if accumulate else 0, ptr(scratch), ptr(err),
                              _stream()))
     return out, err
@@ -329,8 +330,9 @@ def dense_image(W, rows: int, cols: int, img, T: int, normed: bool = True, eps: 
     return y
 
 
-def router_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
-    """The prompt pass's router over any number of rows in one call: (topi, topw, logits)."""
+def router_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6, tensor_cores: bool = True):
+    """The prompt pass's router over any number of rows in one call: (topi, topw, logits).  tensor_cores: give the call its
+    scratch, so that 1,024 rows or more go through the split-f16 product."""
     import torch
     T, H = x.shape
     E = Wr.shape[0] - 1
@@ -338,7 +340,10 @@ def router_rows(Wr, x, K: int, norm_w=None, eps: float = 1e-6):
     topi = torch.empty((T, K), dtype=torch.int32, device=x.device)
     topw = torch.empty((T, K), dtype=torch.float32, device=x.device)
     err = new_err(x.device)
-    check(lib().fnx_router_rows(ptr(Wr), ptr(x), ptr(norm_w), eps, T, E, H, K, ptr(logits), ptr(topi), ptr(topw), ptr(err), _stream()))
+    scratch = torch.empty(lib().fnx_router_rows_scratch_bytes(T, E, H), dtype=torch.uint8, device=x.device) if tensor_cores else None
+    check(lib().fnx_router_rows(ptr(Wr), ptr(x), ptr(norm_w), eps, T, E, H, K, ptr(logits), ptr(topi), ptr(topw), ptr(scratch), ptr(err), _stream()))
+    if int(err.item()):
+        raise FnxError(f"fnx_router_rows: device error bits {int(err.item()):#x}")
     return topi, topw, logits
 
 

@@ -17,7 +17,7 @@ HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "libfnx_b200.so"
 SERVE = HERE / "fnx_serve"
-SOURCES = ["common.cu", "iq3s_prep.cu", "iq3s_mmv.cu", "moe_route.cu", "attn.cu", "attn_prompt_tc.cu", "gdn.cu", "moe_prefill.cu", "head.cu", "spec.cu", "lane_plan.cu", "gguf.cu", "model_load.cu", "engine.cu"]
+SOURCES = ["common.cu", "iq3s_prep.cu", "iq3s_mmv.cu", "moe_route.cu", "attn.cu", "attn_prompt_tc.cu", "gdn.cu", "moe_prefill.cu", "gemm_tma.cu", "head.cu", "spec.cu", "lane_plan.cu", "gguf.cu", "model_load.cu", "engine.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xcompiler", "-Wall"]
 

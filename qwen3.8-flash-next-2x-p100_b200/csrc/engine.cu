@@ -120,7 +120,7 @@ struct fnx_engine {
     int prompt_attn_mma_sync = 0;   // FNX_ATTN_PROMPT_MMA=1: the prompt pass's attention on mma.sync (the comparison form)
     bool prompt_timing = false;     // fnx_engine_prompt_timing: time the prompt pass's phases with events
     float prompt_phase_ms[6] = {0, 0, 0, 0, 0, 0};   // the last timed prompt: in-proj, attention, DeltaNet, out-proj, router, experts
-    void *p_moe_scratch = nullptr, *p_dense_scratch = nullptr, *p_gdn_scratch = nullptr, *p_attn_scratch = nullptr;
+    void *p_router_scratch = nullptr, *p_moe_scratch = nullptr, *p_dense_scratch = nullptr, *p_gdn_scratch = nullptr, *p_attn_scratch = nullptr;
     // the draft layer's own head over a draft vocabulary (config draft_vocab > 0): dvn rows, row -> token id in d_dvocab;
     // otherwise the main head and no map
     uint8_t* mtp_head = nullptr;
@@ -1296,9 +1296,14 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
         uint8_t* q = nullptr;
         FNX_TRY(dalloc(e, &q, fnx_moe_prefill_scratch_bytes(CH, d.K, d.E, d.H, d.F)));
         e->p_moe_scratch = q;
-        const size_t ds = fnx_dense_prompt_scratch_bytes(CH, mixw > d.H ? mixw : d.H);
-        FNX_TRY(dalloc(e, &q, ds));
+        {   // the largest of the layers' input projections (rows x H) and output projections (H x mixer width)
+            const int in_rows = d.attn_in > d.gdn_in ? d.attn_in : d.gdn_in;
+            const size_t a = fnx_dense_prompt_scratch_bytes(CH, in_rows, d.H), b = fnx_dense_prompt_scratch_bytes(CH, d.H, mixw);
+            FNX_TRY(dalloc(e, &q, a > b ? a : b));
+        }
         e->p_dense_scratch = q;
+        FNX_TRY(dalloc(e, &q, fnx_router_rows_scratch_bytes(CH, d.E, d.H)));
+        e->p_router_scratch = q;
         FNX_TRY(dalloc(e, &q, fnx_gdn_prompt_scratch_bytes(CH, d.nk, d.nv, d.hs)));
         e->p_gdn_scratch = q;
         FNX_TRY(dalloc(e, &q, fnx_attn_prompt_scratch_bytes(CH, d.nq, d.hd)));
@@ -1355,7 +1360,7 @@ extern "C" int fnx_engine_prompt(fnx_engine* e, int seq, const int* h_tok, int n
             FNX_TRY(fnx_dense_prompt(L.w_out, d.H, mixw_l, e->pmix, nt, nullptr, e->c.eps, e->pR, d.H, 1, e->p_dense_scratch, e->err, e->st));
             mark(0, false);
             mark(PH_ROUTER, true);
-            FNX_TRY(fnx_router_rows(L.wr, e->pR, L.norm2, e->c.eps, nt, d.E, d.H, d.K, e->plogits, e->ptopi, e->ptopw, e->err, e->st));
+            FNX_TRY(fnx_router_rows(L.wr, e->pR, L.norm2, e->c.eps, nt, d.E, d.H, d.K, e->plogits, e->ptopi, e->ptopw, e->p_router_scratch, e->err, e->st));
             mark(0, false);
             mark(PH_MOE, true);
             FNX_TRY(fnx_moe_prefill(L.wgu, e->gu_bytes, L.wdn, e->dn_bytes, L.wsh_gu, L.wsh_dn, 0, d.E, d.K, 0, d.E, 1, e->ptopi, e->ptopw, e->plogits, e->pR, L.norm2,

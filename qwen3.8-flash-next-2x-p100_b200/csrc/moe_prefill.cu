@@ -13,6 +13,9 @@
 // when the tcgen05.commit of its chunk has arrived on the stage's mbarrier.  Every wait is bounded.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+#include <type_traits>
+
 #include "fnx_common.cuh"
 #include "iq3s_grid.h"
 #include "iq3s_tile.h"
@@ -101,7 +104,7 @@ __device__ __forceinline__ void pf_load_raw(const uint8_t* tile, int lane, PfRaw
 
 // eight signed codebook bytes (two lookups) times the sub-block scale -> eight f16 at (row, k .. k + 7): one core-matrix
 // row.  Bytes become halves without the conversion unit: 0x6400 | (b + 128) is the f16 1024 + (b + 128), exactly.
-__device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32_t lo4, uint32_t hi4, __half2 f2) {
+__device__ __forceinline__ uint4 pf_halves8(uint32_t lo4, uint32_t hi4, __half2 f2) {
     const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
     uint32_t h[4];
 #pragma unroll
@@ -113,7 +116,10 @@ __device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32
         const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&pair), bias), f2);
         h[j] = *reinterpret_cast<const uint32_t*>(&v);
     }
-    *reinterpret_cast<uint4*>(tileA + pf_off(row, k)) = make_uint4(h[0], h[1], h[2], h[3]);
+    return make_uint4(h[0], h[1], h[2], h[3]);
+}
+__device__ __forceinline__ void pf_store8(uint8_t* tileA, int row, int k, uint32_t lo4, uint32_t hi4, __half2 f2) {
+    *reinterpret_cast<uint4*>(tileA + pf_off(row, k)) = pf_halves8(lo4, hi4, f2);
 }
 
 template <int I>
@@ -514,6 +520,44 @@ __global__ void k_pf_combine(const float* __restrict__ part, const int* __restri
     *o = s;
 }
 
+// A tile matrix decoded once to f16, row-major [rows][K]: the values the grouped product's own decode makes (the same codebook
+// bytes, scales and half arithmetic), for the products that take their weights by tensor copies (gemm_tma.cu).  One warp per
+// 16 x 256 tile block.
+__global__ void __launch_bounds__(256) k_pf_decode_f16(const uint8_t* __restrict__ W, int rows, int K, __half* __restrict__ out) {
+    __shared__ uint32_t table[512 * PF_REP];
+    for (int i = threadIdx.x; i < 512 * PF_REP; i += blockDim.x) table[i] = g_grid_pf[i / PF_REP];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, KB = K / 256;
+    const size_t nblk = (size_t) (rows / 16) * KB;
+    const uint32_t table_s = smem_u32(table) + (uint32_t) (lane % PF_REP) * 4u;
+    const int g = lane >> 2, q = lane & 3;
+    for (size_t b = (size_t) blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5); b < nblk; b += (size_t) gridDim.x * (blockDim.x / 32)) {
+        const size_t trow = b / KB;
+        const int kb = (int) (b % KB);
+        PfRaw r;
+        pf_load_raw(W + b * TILE_BYTES, lane, r);
+        __half* o0 = out + (trow * 16 + g) * K + (size_t) kb * 256 + 8 * q;
+        __half* o1 = o0 + (size_t) 8 * K;
+        auto sub = [&](auto SBc) {
+            constexpr int SB = decltype(SBc)::value;
+            const __half2 f0 = __float2half2_rn(r.d0 * (float) (1 + 2 * (int) ((r.sn0 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u)));
+            const __half2 f1 = __float2half2_rn(r.d1 * (float) (1 + 2 * (int) ((r.sn1 >> (8 * (SB >> 1) + 4 * (SB & 1))) & 15u)));
+            *reinterpret_cast<uint4*>(o0 + SB * 32) = pf_halves8(pf_decode<2 * SB>(r.S0, r.G0, table_s), pf_decode<2 * SB + 1>(r.S0, r.G0, table_s), f0);
+            *reinterpret_cast<uint4*>(o1 + SB * 32) = pf_halves8(pf_decode<2 * SB>(r.S1, r.G1, table_s), pf_decode<2 * SB + 1>(r.S1, r.G1, table_s), f1);
+        };
+        sub(std::integral_constant<int, 0>{}); sub(std::integral_constant<int, 1>{}); sub(std::integral_constant<int, 2>{}); sub(std::integral_constant<int, 3>{});
+        sub(std::integral_constant<int, 4>{}); sub(std::integral_constant<int, 5>{}); sub(std::integral_constant<int, 6>{}); sub(std::integral_constant<int, 7>{});
+    }
+}
+
+int pf_decode_f16_launch(const void* W, int rows, int K, __half* out, cudaStream_t st) {
+    const size_t nblk = (size_t) (rows / 16) * (K / 256);
+    const unsigned blocks = (unsigned) (nblk / 8 < 148 * 8 ? (nblk + 7) / 8 : 148 * 8);
+    k_pf_decode_f16<<<blocks, 256, 0, st>>>((const uint8_t*) W, rows, K, out);
+    FNX_LAUNCH_OK("k_pf_decode_f16");
+    return FNX_OK;
+}
+
 // the job list of a dense product over T rows: job j = rows [256 j, 256 j + 256) of "expert" 0, entries in row order
 __global__ void k_pf_dense_jobs(int T, PfJob* __restrict__ jobs, int* __restrict__ njobs, int* __restrict__ order) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x, nj = (T + PF_N - 1) / PF_N;
@@ -591,8 +635,20 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
 }
 
 // ------------------------------------------------------------------------------------------------ dense product for prompts
-extern "C" size_t fnx_dense_prompt_scratch_bytes(int T, int cols) {
-    return pf_align((size_t) T * cols * sizeof(__half)) + pf_align((size_t) T * sizeof(int)) + pf_align(((size_t) T / PF_N + 2) * sizeof(PfJob)) + 256;
+namespace fnxb {
+int gemm_tma_launch(const __half* w, const __half* wl, const __half* x, const __half* xl, float* y, int ldy, int T, int rows, int K, int accumulate, float scale,
+                    unsigned* err, cudaStream_t st);
+// rows from which the product takes its weights decoded to f16 once (k_pf_decode_f16) and both operands by tensor copies
+// (gemm_tma.cu); FNX_PROMPT_GEMM=0 keeps every product on the form that decodes inside the product
+static int pf_tma_rows() {
+    static const int v = []() { const char* e = getenv("FNX_PROMPT_GEMM"); return e && atoi(e) == 0 ? 1 << 30 : 1024; }();
+    return v;
+}
+}  // namespace fnxb
+
+extern "C" size_t fnx_dense_prompt_scratch_bytes(int T, int rows, int cols) {
+    return pf_align((size_t) T * cols * sizeof(__half)) + pf_align((size_t) T * sizeof(int)) + pf_align(((size_t) T / PF_N + 2) * sizeof(PfJob)) + 256 +
+           pf_align((size_t) rows * cols * sizeof(__half));
 }
 
 extern "C" int fnx_dense_prompt(const void* W, int rows, int cols, const float* x, int T, const float* norm_w, float eps, float* y, int ldy, int accumulate,
@@ -604,12 +660,17 @@ extern "C" int fnx_dense_prompt(const void* W, int rows, int cols, const float* 
     __half* xh = (__half*) b; b += pf_align((size_t) T * cols * sizeof(__half));
     int* order = (int*) b; b += pf_align((size_t) T * sizeof(int));
     PfJob* jobs = (PfJob*) b; b += pf_align(((size_t) T / PF_N + 2) * sizeof(PfJob));
-    int* njobs = (int*) b;
+    int* njobs = (int*) b; b += 256;
+    __half* w16 = (__half*) b;
     const int nj = (T + PF_N - 1) / PF_N;
-    k_pf_dense_jobs<<<(T + 255) / 256, 256, 0, st>>>(T, jobs, njobs, order);
-    FNX_LAUNCH_OK("k_pf_dense_jobs");
     k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, cols, eps, xh);
     FNX_LAUNCH_OK("k_pf_xnorm");
+    if (T >= pf_tma_rows()) {   // the matrix to f16 once, then one product with both operands by tensor copies
+        FNX_TRY(pf_decode_f16_launch(W, rows, cols, w16, st));
+        return gemm_tma_launch(w16, nullptr, xh, nullptr, y, ldy, T, rows, cols, accumulate, 1.0f, err, st);
+    }
+    k_pf_dense_jobs<<<(T + 255) / 256, 256, 0, st>>>(T, jobs, njobs, order);
+    FNX_LAUNCH_OK("k_pf_dense_jobs");
     if (int rc = set_smem_limit((const void*) k_pf_gemm<0>, (int) pf_smem(0))) return rc;
     PfParams p{};
     p.W = (const uint8_t*) W; p.expert_stride = 0; p.e_base = 0; p.E = 1; p.Wsh = nullptr;

@@ -7,6 +7,8 @@
 #include <algorithm>
 
 #include "fnx_common.cuh"
+#include <cstdlib>
+
 #include "moe_route.cuh"
 #include "mmv_core.cuh"
 
@@ -431,16 +433,106 @@ extern "C" int fnx_moe_combine_image(const float* part, const int* topi, const f
     return FNX_OK;
 }
 
+// ---- the router over a prompt's rows as a tensor-core product (gemm_tma.cu): the normed rows and the f32 weights are split
+// into f16 high and low parts (weights times 256 first, so that their low parts stay clear of f16's subnormals); three
+// products (high x high, high x low, low x high) restore the f32 operands (the tensor core's truncating f32 accumulation leaves
+// the logits good to a few 1e-5).  The shared expert's gate row is a plain dot.
+__global__ void __launch_bounds__(256) k_router_split_x(const float* __restrict__ x, const float* __restrict__ norm_w, const float* __restrict__ w_gate, int H,
+                                                        float eps, __half* __restrict__ xh, __half* __restrict__ xl, float* __restrict__ logits, int ldl, int E) {
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* xr = x + (size_t) t * H;
+    __shared__ float ws[8], s_r;
+    float ss = 0.f;
+    for (int i = tid * 4; i < H; i += 1024) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) ws[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.f;
+        for (int w = 0; w < 8; ++w) a += ws[w];
+        s_r = norm_w ? rsqrtf(a / (float) H + eps) : 1.0f;
+    }
+    __syncthreads();
+    const float r = s_r;
+    float dot = 0.f;
+    for (int i = tid * 4; i < H; i += 1024) {
+        float4 v = *reinterpret_cast<const float4*>(xr + i);
+        if (norm_w) {
+            const float4 w = *reinterpret_cast<const float4*>(norm_w + i);
+            v.x *= w.x * r; v.y *= w.y * r; v.z *= w.z * r; v.w *= w.w * r;
+        }
+        const float4 g = *reinterpret_cast<const float4*>(w_gate + i);
+        dot = fmaf(v.x, g.x, fmaf(v.y, g.y, fmaf(v.z, g.z, fmaf(v.w, g.w, dot))));
+        const float e[4] = {v.x, v.y, v.z, v.w};
+        __half h[4], l[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            h[k] = __float2half_rn(e[k]);
+            l[k] = __float2half_rn(e[k] - __half2float(h[k]));
+        }
+        *reinterpret_cast<uint2*>(xh + (size_t) t * H + i) = make_uint2((uint32_t) __half_as_ushort(h[0]) | ((uint32_t) __half_as_ushort(h[1]) << 16),
+                                                                        (uint32_t) __half_as_ushort(h[2]) | ((uint32_t) __half_as_ushort(h[3]) << 16));
+        *reinterpret_cast<uint2*>(xl + (size_t) t * H + i) = make_uint2((uint32_t) __half_as_ushort(l[0]) | ((uint32_t) __half_as_ushort(l[1]) << 16),
+                                                                        (uint32_t) __half_as_ushort(l[2]) | ((uint32_t) __half_as_ushort(l[3]) << 16));
+    }
+    dot = warp_sum(dot);
+    __syncthreads();
+    if ((tid & 31) == 0) ws[tid >> 5] = dot;
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.f;
+        for (int w = 0; w < 8; ++w) a += ws[w];
+        logits[(size_t) t * ldl + E] = a;
+    }
+}
+
+__global__ void k_router_split_w(const float* __restrict__ w, size_t n, __half* __restrict__ wh, __half* __restrict__ wl) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = w[i] * 256.0f;
+    const __half h = __float2half_rn(v);
+    wh[i] = h;
+    wl[i] = __float2half_rn(v - __half2float(h));
+}
+
+namespace fnxb {
+int gemm_tma_launch(const __half* w, const __half* wl, const __half* x, const __half* xl, float* y, int ldy, int T, int rows, int K, int accumulate, float scale,
+                    unsigned* err, cudaStream_t st);
+static size_t rr_align(size_t v) { return (v + 255) & ~(size_t) 255; }
+}  // namespace fnxb
+
+extern "C" size_t fnx_router_rows_scratch_bytes(int T, int E, int H) {
+    return 2 * rr_align((size_t) T * H * sizeof(__half)) + 2 * rr_align((size_t) E * H * sizeof(__half));
+}
+
 extern "C" int fnx_router_rows(const float* Wr, const float* x, const float* norm_w, float eps, int T, int E, int H, int K, float* logits, int* topi,
-                               float* topw, unsigned* err, fnx_stream st) {
+                               float* topw, void* scratch, unsigned* err, fnx_stream st) {
     FNX_REQUIRE(Wr && x && logits && topi && topw && err, "fnx_router_rows: null pointer");
     FNX_REQUIRE(T >= 1, "fnx_router_rows: %d rows", T);
     FNX_REQUIRE(E >= K && E <= RT_MAXE && K >= 1 && K <= 32, "fnx_router_rows: %d experts, top %d not supported", E, K);
     FNX_REQUIRE(H % 256 == 0 && H <= 4096, "fnx_router_rows: hidden %d not supported", H);
-    const size_t smem = (size_t) RP_TOK * H * sizeof(float);
-    if (int rc = set_smem_limit((const void*) k_router_rows, 160 * 1024)) return rc;
-    k_router_rows<<<(T + RP_TOK - 1) / RP_TOK, RP_WARPS * 32, smem, as_stream(st)>>>(Wr, x, norm_w, eps, T, E, H, logits, err);
-    FNX_LAUNCH_OK("k_router_rows");
+    static const bool gemm_off = []() { const char* e = getenv("FNX_PROMPT_GEMM"); return e && atoi(e) == 0; }();
+    if (scratch && T >= 1024 && !gemm_off) {
+        uint8_t* b = (uint8_t*) scratch;
+        __half* xh = (__half*) b; b += rr_align((size_t) T * H * sizeof(__half));
+        __half* xl = (__half*) b; b += rr_align((size_t) T * H * sizeof(__half));
+        __half* wh = (__half*) b; b += rr_align((size_t) E * H * sizeof(__half));
+        __half* wl = (__half*) b;
+        k_router_split_x<<<T, 256, 0, as_stream(st)>>>(x, norm_w, Wr + (size_t) E * H, H, eps, xh, xl, logits, E + 1, E);
+        FNX_LAUNCH_OK("k_router_split_x");
+        const size_t n = (size_t) E * H;
+        k_router_split_w<<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(st)>>>(Wr, n, wh, wl);
+        FNX_LAUNCH_OK("k_router_split_w");
+        if (int rc = gemm_tma_launch(wh, wl, xh, xl, logits, E + 1, T, E, H, 0, 1.0f / 256.0f, err, as_stream(st))) return rc;
+    } else {
+        const size_t smem = (size_t) RP_TOK * H * sizeof(float);
+        if (int rc = set_smem_limit((const void*) k_router_rows, 160 * 1024)) return rc;
+        k_router_rows<<<(T + RP_TOK - 1) / RP_TOK, RP_WARPS * 32, smem, as_stream(st)>>>(Wr, x, norm_w, eps, T, E, H, logits, err);
+        FNX_LAUNCH_OK("k_router_rows");
+    }
     k_topk_rows<<<(T + 7) / 8, 256, 0, as_stream(st)>>>(logits, T, E, K, topi, topw);
     FNX_LAUNCH_OK("k_topk_rows");
     return FNX_OK;
