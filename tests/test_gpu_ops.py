@@ -201,7 +201,8 @@ def test_router_rows_equals_the_window_router(F, E, H, K, T):
         assert np.abs(lg.cpu().numpy() - ref).mean() < 1e-5
     assert np.abs(lg.cpu().numpy() - rl.cpu().numpy()).max() < (1e-4 if big else 1e-6)
     srt = np.sort(rl.cpu().numpy()[:, :E], axis=1)
-    clear = (srt[:, -K] - srt[:, -K - 1]) > (3e-4 if big else 1e-5)
+    # rows whose K + 1 highest logits lie further apart than the two routers' logits differ: there the picks agree in order too
+    clear = np.diff(srt[:, -K - 1:], axis=1).min(axis=1) > (3e-4 if big else 1e-5)
     assert clear.sum() > T // 2
     assert np.array_equal(ti.cpu().numpy()[clear], ri.cpu().numpy()[clear])
     assert np.abs(tw.cpu().numpy()[clear] - rw.cpu().numpy()[clear]).max() < (1e-4 if big else 1e-5)
