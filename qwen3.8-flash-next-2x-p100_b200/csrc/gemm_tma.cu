@@ -192,6 +192,141 @@ __global__ void __launch_bounds__(GT_THREADS, 1) k_gemm_tma(const GtParams p, co
     if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NA * GT_N) : "memory");
 }
 
+// ---- the grouped expert products of a prompt from f16 weights (every expert's matrix decoded once per layer, expert e at
+// rows [e R, (e + 1) R) of one stacked matrix) and rows laid out in job order (x_sorted / h_sorted: entry `pos` of the job
+// list's `order`), so that both operands of a job's tile are boxes of the same two tensors.  A job is up to 256 consecutive
+// entries of one expert; the rows of a tile past the job's end are computed and dropped.
+//   MODE 1: gate|up with SwiGLU: accumulator 0 = 128 gate features, accumulator 1 = the same up features; h = silu(g) u as f16
+//           into h_sorted [pos][F].
+//   MODE 0: down: 256 features; part[pair][f] f32 at the pair index order[pos].
+struct GtJob {
+    int w, n, start;   // expert (E: the shared expert), rows, first entry of `order`
+};
+struct GtJobParams {
+    const GtJob* jobs;
+    const int* njobs;
+    const int* order;
+    int R;             // feature rows of one expert in the stacked weight matrix (gate|up: 2 F; down: H)
+    int F;             // MODE 1: the ffn width (gate rows [0, F), up rows [F, 2 F))
+    int K;
+    __half* h_sorted;  // MODE 1
+    float* part;       // MODE 0
+    int H;             // MODE 0: floats per row of part
+    unsigned* err;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(GT_THREADS, 1) k_gemm_tma_jobs(const GtJobParams p, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x) {
+    using Sh = GtShape<2, 1>;
+    constexpr int STAGES = Sh::STAGES, NA = 2;
+    const int j = blockIdx.y;
+    if (j >= *p.njobs) return;
+    const GtJob job = p.jobs[j];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Sh::STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* done = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nk = p.K / GT_KC;
+    // the two weight boxes of the block: gate and up rows of the same 128 features, or 256 consecutive features
+    const int f0 = MODE == 1 ? blockIdx.x * GT_M : blockIdx.x * NA * GT_M;
+    const int wrow0 = job.w * p.R + f0, wrow1 = MODE == 1 ? wrow0 + p.F : wrow0 + GT_M;
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(done, 1);
+        fence_barrier_init();
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NA * GT_N) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    auto a_of = [&](int s, int a) { return smem + s * Sh::STAGE + a * GT_A_BYTES; };
+    auto b_of = [&](int s) { return smem + s * Sh::STAGE + NA * GT_A_BYTES; };
+    if (tid == 0) {
+        for (int kb = 0; kb < nk; ++kb) {
+            const int s = kb % STAGES;
+            if (kb >= STAGES && !mbar_wait_bounded(&empty[s], (unsigned) ((kb / STAGES - 1) & 1), GT_WAIT)) {
+                atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
+                break;
+            }
+            mbar_expect_tx(&full[s], (unsigned) Sh::STAGE);
+            gt_tma_2d(smem_u32(a_of(s, 0)), &map_w, kb * GT_KC, wrow0, &full[s]);
+            gt_tma_2d(smem_u32(a_of(s, 1)), &map_w, kb * GT_KC, wrow1, &full[s]);
+            gt_tma_2d(smem_u32(b_of(s)), &map_x, kb * GT_KC, job.start, &full[s]);
+        }
+    } else if (tid == 32) {
+        constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (GT_N >> 3) << 17) | ((uint32_t) (GT_M >> 4) << 24);
+        bool ok = true;
+        for (int kb = 0; kb < nk && ok; ++kb) {
+            const int s = kb % STAGES;
+            ok = mbar_wait_bounded(&full[s], (unsigned) ((kb / STAGES) & 1), GT_WAIT);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int k16 = 0; k16 < GT_KC / 16; ++k16) {
+                const uint64_t bd = gt_desc(smem_u32(b_of(s)) + k16 * 32);
+#pragma unroll
+                for (int a = 0; a < NA; ++a) gt_mma(tmem + a * GT_N, gt_desc(smem_u32(a_of(s, a)) + k16 * 32), bd, IDESC, (kb | k16) != 0);
+            }
+            gt_commit(&empty[s]);
+        }
+        if (ok) gt_commit(done);
+        else atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
+    } else if (warp >= 2) {
+        const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(done, 0u, GT_WAIT));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int lg = warp & 3;
+            const uint32_t lane_base = (uint32_t) (32 * lg) << 16;
+            if (MODE == 1) {
+                const int f = f0 + 32 * lg + lane;
+#pragma unroll 1
+                for (int c = 0; c < GT_N / 32; ++c) {
+                    if (c * 32 >= job.n) break;
+                    float g[32], u[32];
+                    gt_ld32(tmem + lane_base + (uint32_t) (c * 32), g);
+                    gt_ld32(tmem + lane_base + (uint32_t) (GT_N + c * 32), u);
+                    __half* o = p.h_sorted + (size_t) (job.start + c * 32) * p.F + f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i < job.n) o[(size_t) i * p.F] = __float2half_rn(siluf_(g[i]) * u[i]);
+                }
+            } else {
+#pragma unroll 1
+                for (int a = 0; a < NA; ++a) {
+                    const int f = f0 + a * GT_M + 32 * lg + lane;
+#pragma unroll 1
+                    for (int c = 0; c < GT_N / 32; ++c) {
+                        if (c * 32 >= job.n) break;
+                        float v[32];
+                        gt_ld32(tmem + lane_base + (uint32_t) (a * GT_N + c * 32), v);
+                        const int my = c * 32 + lane < job.n ? p.order[job.start + c * 32 + lane] : 0;   // the chunk's pair indices, one per lane
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int pair = __shfl_sync(0xffffffffu, my, i);
+                            if (c * 32 + i < job.n) __stcs(p.part + (size_t) pair * p.H + f, v[i]);
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicOr(p.err, (unsigned) FNX_ERR_TIMEOUT);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NA * GT_N) : "memory");
+}
+
 // an f16 matrix [rows][K] as a rank-2 tensor for boxes of 64 columns x box_rows rows with the 128-byte swizzle
 static int gt_map(CUtensorMap* map, const __half* base, int rows, int K, int box_rows) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -237,6 +372,29 @@ int gemm_tma_launch(const __half* w, const __half* wl, const __half* x, const __
         k_gemm_tma<2, 1><<<dim3((rows + 2 * GT_M - 1) / (2 * GT_M), (T + GT_N - 1) / GT_N), GT_THREADS, Sh::SMEM, st>>>(p, mw, mx, mwl, mxl);
     }
     FNX_LAUNCH_OK("k_gemm_tma");
+    return FNX_OK;
+}
+
+// the two grouped products of a layer's experts: h_sorted = silu(gate) up over x_sorted, then part = down over h_sorted.
+// gu16 [(experts + 1)][2 F][H], dn16 [(experts + 1)][H][F] (the last slot: the shared expert); entries = rows of x_sorted.
+int gemm_tma_experts(const __half* gu16, const __half* dn16, int slots, const __half* x_sorted, __half* h_sorted, float* part, const void* jobs, const int* njobs,
+                     const int* order, int max_jobs, int entries, int H, int F, unsigned* err, cudaStream_t st) {
+    using Sh = GtShape<2, 1>;
+    if (int rc = set_smem_limit((const void*) k_gemm_tma_jobs<1>, Sh::SMEM)) return rc;
+    if (int rc = set_smem_limit((const void*) k_gemm_tma_jobs<0>, Sh::SMEM)) return rc;
+    CUtensorMap mw, mx;
+    GtJobParams p{};
+    p.jobs = (const GtJob*) jobs; p.njobs = njobs; p.order = order; p.err = err;
+    FNX_TRY(gt_map(&mw, gu16, slots * 2 * F, H, GT_M));
+    FNX_TRY(gt_map(&mx, x_sorted, entries, H, GT_N));
+    p.R = 2 * F; p.F = F; p.K = H; p.h_sorted = h_sorted;
+    k_gemm_tma_jobs<1><<<dim3(F / GT_M, max_jobs), GT_THREADS, Sh::SMEM, st>>>(p, mw, mx);
+    FNX_LAUNCH_OK("k_gemm_tma_jobs (gate|up)");
+    FNX_TRY(gt_map(&mw, dn16, slots * H, F, GT_M));
+    FNX_TRY(gt_map(&mx, h_sorted, entries, F, GT_N));
+    p.R = H; p.K = F; p.part = part; p.H = H; p.h_sorted = nullptr;
+    k_gemm_tma_jobs<0><<<dim3(H / (2 * GT_M), max_jobs), GT_THREADS, Sh::SMEM, st>>>(p, mw, mx);
+    FNX_LAUNCH_OK("k_gemm_tma_jobs (down)");
     return FNX_OK;
 }
 

@@ -574,10 +574,33 @@ using namespace fnxb;
 
 static size_t pf_align(size_t v) { return (v + 255) & ~(size_t) 255; }
 
+// the rows of the job list's entries, in entry order: x_sorted[pos] = xh[token of order[pos]] (a routed pair t K + k: token t; a
+// shared-expert entry n + t: token t), so that a job's rows are consecutive for the tensor copies
+__global__ void __launch_bounds__(256) k_pf_gather_rows(const __half* __restrict__ xh, const int* __restrict__ order, int n, int Kp, int H, __half* __restrict__ xs) {
+    const int pos = blockIdx.x, pair = order[pos], t = pair < n ? pair / Kp : pair - n;
+    const uint4* src = reinterpret_cast<const uint4*>(xh + (size_t) t * H);
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t) pos * H);
+    for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = src[i];
+}
+
+namespace fnxb {
+int gemm_tma_experts(const __half* gu16, const __half* dn16, int slots, const __half* x_sorted, __half* h_sorted, float* part, const void* jobs, const int* njobs,
+                     const int* order, int max_jobs, int entries, int H, int F, unsigned* err, cudaStream_t st);
+static bool pf_gemm_off() {
+    static const bool v = []() { const char* e = getenv("FNX_PROMPT_GEMM"); return e && atoi(e) == 0; }();
+    return v;
+}
+// bytes of the f16 copies the tensor-copy form of the experts keeps: the rows in job order, every expert's two matrices
+static size_t pf_staged_bytes(size_t pairs, int E, int H, int F) {
+    return pf_align(pairs * H * sizeof(__half)) + pf_align((size_t) (E + 1) * 2 * F * H * sizeof(__half)) + pf_align((size_t) (E + 1) * H * F * sizeof(__half));
+}
+}  // namespace fnxb
+
 extern "C" size_t fnx_moe_prefill_scratch_bytes(int T, int K, int E, int H, int F) {
     const size_t pairs = (size_t) T * K + T;
     return pf_align(pairs * F * sizeof(__half)) + pf_align(pairs * H * sizeof(float)) + pf_align(pairs * sizeof(int)) + pf_align((size_t) (E + 1) * sizeof(int)) * 2 +
-           pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob)) + pf_align((size_t) T * H * sizeof(__half)) + 256;
+           pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob)) + pf_align((size_t) T * H * sizeof(__half)) + 256 +
+           (T >= 1024 ? pf_staged_bytes(pairs, E, H, F) : 0);
 }
 
 extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wdn, size_t dn_stride, const void* Wsh_gu, const void* Wsh_dn, int e_base,
@@ -599,7 +622,7 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     int* base = (int*) b; b += pf_align((size_t) (E + 1) * sizeof(int));
     PfJob* jobs = (PfJob*) b; b += pf_align((pairs / PF_N + E + 2 + (size_t) T / PF_N) * sizeof(PfJob));
     __half* xh = (__half*) b; b += pf_align((size_t) T * H * sizeof(__half));
-    int* njobs = (int*) b;
+    int* njobs = (int*) b; b += 256;
     const int ne = e_hi - e_lo, n = T * K;
     if (ne > 0) {
         k_pf_count<<<ne, 1024, 0, st>>>(topi, n, e_lo, cnt);
@@ -613,6 +636,25 @@ extern "C" int fnx_moe_prefill(const void* Wgu, size_t gu_stride, const void* Wd
     }
     k_pf_xnorm<<<T, 256, 0, st>>>(x, norm_w, H, eps, xh);
     FNX_LAUNCH_OK("k_pf_xnorm");
+    // From 1,024 rows on, with every expert on this rank and stacked without gaps: the experts' matrices decoded to f16 once, the
+    // rows copied into job order, and the two grouped products with both operands by tensor copies (gemm_tma.cu).
+    if (T >= 1024 && !pf_gemm_off() && e_base == 0 && e_lo == 0 && e_hi == E && add_shared && gu_stride == fnx_iq3s_bytes((size_t) 2 * F, (size_t) H) &&
+        dn_stride == fnx_iq3s_bytes((size_t) H, (size_t) F)) {
+        __half* xs = (__half*) b; b += pf_align(pairs * H * sizeof(__half));
+        __half* gu16 = (__half*) b; b += pf_align((size_t) (E + 1) * 2 * F * H * sizeof(__half));
+        __half* dn16 = (__half*) b;
+        FNX_TRY(pf_decode_f16_launch(Wgu, E * 2 * F, H, gu16, st));
+        FNX_TRY(pf_decode_f16_launch(Wsh_gu, 2 * F, H, gu16 + (size_t) E * 2 * F * H, st));
+        FNX_TRY(pf_decode_f16_launch(Wdn, E * H, F, dn16, st));
+        FNX_TRY(pf_decode_f16_launch(Wsh_dn, H, F, dn16 + (size_t) E * H * F, st));
+        k_pf_gather_rows<<<(unsigned) pairs, 256, 0, st>>>(xh, order, n, K, H, xs);
+        FNX_LAUNCH_OK("k_pf_gather_rows");
+        const int nj = (int) ((size_t) n / PF_N) + ne + (T + PF_N - 1) / PF_N;
+        FNX_TRY(gemm_tma_experts(gu16, dn16, E + 1, xs, hbuf, part, jobs, njobs, order, nj, (int) pairs, H, F, err, st));
+        k_pf_combine<<<dim3((H / 4 + 255) / 256, T), 256, 0, st>>>(part, topi, topw, logits, T, E, H, K, e_lo, e_hi, add_shared, out, accumulate);
+        FNX_LAUNCH_OK("k_pf_combine");
+        return FNX_OK;
+    }
     if (int rc = set_smem_limit((const void*) k_pf_gemm<0>, (int) pf_smem(0))) return rc;
     if (int rc = set_smem_limit((const void*) k_pf_gemm<1>, (int) pf_smem(1))) return rc;
     // the job count is known on the device only: the grids cover the largest it can be (an expert's pairs in jobs of PF_N rows:

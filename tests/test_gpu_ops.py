@@ -361,10 +361,11 @@ def test_router_many_tokens_pick_one_expert(F, O):
     assert int(route["njobs"][0].item()) == K * 3 + 3
 
 
-@pytest.mark.parametrize("E,H,Fn,K,T", [(16, 512, 256, 4, 200), (32, 2048, 512, 10, 333)])
+@pytest.mark.parametrize("E,H,Fn,K,T", [(16, 512, 256, 4, 200), (32, 2048, 512, 10, 333), (16, 512, 256, 4, 1300), (32, 2048, 512, 10, 1100)])
 def test_prefill_moe_on_tensor_cores_matches_oracle(F, O, E, H, Fn, K, T):
     """Token groups per expert through tcgen05.mma (f16 operands, f32 accumulate): jobs of 128 rows and ragged tails,
-    experts nobody picked, the shared expert over all rows."""
+    experts nobody picked, the shared expert over all rows.  From 1,024 rows on the experts' matrices are decoded to f16 once and
+    the grouped products take both operands by tensor copies (rows copied into job order)."""
     fx = _moe_fixture(F, E, H, Fn, seed=23)
     rng = np.random.default_rng(E + T)
     x = rng.standard_normal((T, H)).astype(np.float32)
