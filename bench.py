@@ -393,7 +393,7 @@ def run_config3(a, F, eng, cfg, rank, world, local, use_peer):
               "out_proj": 2.0 * n * H * (n_attn * cfg.n_q_head * cfg.head_dim + (L - n_attn) * cfg.gdn_v_head * cfg.gdn_head_dim),
               "attention": 4.0 * cfg.n_q_head * cfg.head_dim * (n * (n + 1) / 2.0) * n_attn}
         tf = {k: fl[k] / (phases[k] * 1e-3) / 1e12 for k in fl if phases.get(k, 0) > 0}
-        roof = {"bound": "tensor", "kernel": "k_pf_gemm (grouped expert products, tcgen05)", "achieved": tf.get("experts"), "peak": peak, "unit": "TFLOP/s",
+        roof = {"bound": "tensor", "kernel": "k_gemm_tma_jobs (grouped expert products on tcgen05.mma, operands by tensor copies; the phase also decodes the experts to f16, copies the rows into job order and combines)", "achieved": tf.get("experts"), "peak": peak, "unit": "TFLOP/s",
                 "frac": tf.get("experts", 0.0) / peak, "peak_kind": "measured (sustained)" if pk else "fallback", "traffic": None,
                 "tflops_by_phase": tf, "note": "device ms per phase from CUDA events around the phases of every layer and chunk, in an extra pass of the same prompt; "
                 "projections, experts and attention run on tcgen05.mma"}
