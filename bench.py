@@ -525,7 +525,7 @@ def main():
         signal.alarm(int(os.environ.get("FNX_BENCH_LIMIT_S", "540")))
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 50; configuration 2: 300, so that the timed text runs through several copied spans and gaps)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
@@ -540,6 +540,8 @@ def main():
     ap.add_argument("--no-config4", action="store_true", help="skip the 8-sequence side measurement that follows the headline run")
     ap.add_argument("--verify-only", action="store_true", help="profiling aid: prefill, then warmup + steps verify windows of k+1 rows and nothing else")
     a = ap.parse_args()
+    if a.steps is None:
+        a.steps = 300 if a.config == 2 else 50
     a.warmup = max(a.warmup, 3) if a.impl == "b200" else a.warmup
 
     import numpy as np
