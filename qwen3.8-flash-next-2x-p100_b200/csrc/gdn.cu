@@ -279,6 +279,26 @@ __global__ void __launch_bounds__(GDP_THREADS) k_gdn_pre(const float* __restrict
 
 // block = (value head, column quarter) as in the window kernel: warp `part` holds key rows [32 part, +32) of the block's 32 value
 // columns, lane = column.  Rows stream through two shared-memory tiles of GDS_ROWS rows.
+// two f32 in a 64-bit register and the packed multiply-add on them (fma.rn.f32x2: each half rounded as the scalar fmaf is, so the
+// scan's products are those of its scalar form, at half the arithmetic instructions: the scan is bound by instruction issue, with
+// one warp per scheduler)
+__device__ __forceinline__ uint64_t f2_pack(float x, float y) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t r, float& x, float& y) { asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(r)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 constexpr int GDS_ROWS = 16;
 __global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restrict__ xq, const float* __restrict__ xk, const float* __restrict__ xv,
                                                           const float* __restrict__ gates, const float* __restrict__ S_in, float* __restrict__ S_out,
@@ -289,9 +309,9 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restric
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, kh = lv % nk, tid = threadIdx.x;
     const int part = tid >> 5, lane = tid & 31, col = qq * GDN_QC + lane;
     const size_t soff = (size_t) lv * GDN_HS * GDN_HS + (size_t) part * 32 * GDN_HS + col;
-    float s[32];
+    uint64_t s[16];   // the thread's 32 state values, in pairs (rows 2 i, 2 i + 1)
 #pragma unroll
-    for (int r = 0; r < 32; ++r) s[r] = S_in[soff + (size_t) r * GDN_HS];
+    for (int r = 0; r < 32; r += 2) s[r / 2] = f2_pack(S_in[soff + (size_t) r * GDN_HS], S_in[soff + (size_t) (r + 1) * GDN_HS]);
     auto stage = [&](int buf, int t0) {
         const int nr = min(GDS_ROWS, T - t0);
         for (int i = tid; i < nr * (ROWF / 2); i += GDN_THREADS) {   // 8-byte pieces
@@ -323,40 +343,49 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restric
             const float* kt = row + part * 32;
             const float* qt = row + GDN_HS + part * 32;
             const float gv = row[2 * GDN_HS + GDN_QC], bv = row[2 * GDN_HS + GDN_QC + 1];
-            // (the row's k and q for this warp's 32 key rows: eight 16-byte broadcast reads each)
-            float kv_[32], qv_[32];
+            // (the row's k and q for this warp's 32 key rows: eight 16-byte broadcast reads each, as pairs)
+            uint64_t kp[16], qp[16];
 #pragma unroll
             for (int r = 0; r < 32; r += 4) {
-                const float4 a = *reinterpret_cast<const float4*>(kt + r), b = *reinterpret_cast<const float4*>(qt + r);
-                kv_[r] = a.x; kv_[r + 1] = a.y; kv_[r + 2] = a.z; kv_[r + 3] = a.w;
-                qv_[r] = b.x; qv_[r + 1] = b.y; qv_[r + 2] = b.z; qv_[r + 3] = b.w;
+                const ulonglong2 a = *reinterpret_cast<const ulonglong2*>(kt + r), b = *reinterpret_cast<const ulonglong2*>(qt + r);
+                kp[r / 2] = a.x; kp[r / 2 + 1] = a.y;
+                qp[r / 2] = b.x; qp[r / 2 + 1] = b.y;
             }
-            float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
+            // eight running sums in four pairs (row r of the 32 goes to sum r % 8): four independent chains of packed products
+            uint64_t kacc[4];
 #pragma unroll
-            for (int r = 0; r < 32; r += 4) {
-                k0 = fmaf(s[r], kv_[r], k0);
-                k1 = fmaf(s[r + 1], kv_[r + 1], k1);
-                k2 = fmaf(s[r + 2], kv_[r + 2], k2);
-                k3 = fmaf(s[r + 3], kv_[r + 3], k3);
-            }
+            for (int i = 0; i < 4; ++i) kacc[i] = f2_pack(0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < 16; r += 4)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) kacc[i] = f2_fma(s[r + i], kp[r + i], kacc[i]);
+            float k0, k1, k2, k3, k4, k5, k6, k7;
+            f2_unpack(kacc[0], k0, k1);
+            f2_unpack(kacc[1], k2, k3);
+            f2_unpack(kacc[2], k4, k5);
+            f2_unpack(kacc[3], k6, k7);
             float* kr = &kred[r0 & 1][0][0];
-            kr[part * GDN_QC + lane] = (k0 + k1) + (k2 + k3);
+            kr[part * GDN_QC + lane] = ((k0 + k1) + (k2 + k3)) + ((k4 + k5) + (k6 + k7));
             __syncthreads();
             const float kvs = (kr[lane] + kr[GDN_QC + lane]) + (kr[2 * GDN_QC + lane] + kr[3 * GDN_QC + lane]);
             const float delta = (row[2 * GDN_HS + lane] - gv * kvs) * bv;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            const uint64_t d2 = f2_pack(delta, delta), g2 = f2_pack(gv, gv);
+            uint64_t aacc[4];
 #pragma unroll
-            for (int r = 0; r < 32; r += 4) {
-                s[r] = fmaf(kv_[r], delta, gv * s[r]);
-                s[r + 1] = fmaf(kv_[r + 1], delta, gv * s[r + 1]);
-                s[r + 2] = fmaf(kv_[r + 2], delta, gv * s[r + 2]);
-                s[r + 3] = fmaf(kv_[r + 3], delta, gv * s[r + 3]);
-                a0 = fmaf(s[r], qv_[r], a0);
-                a1 = fmaf(s[r + 1], qv_[r + 1], a1);
-                a2 = fmaf(s[r + 2], qv_[r + 2], a2);
-                a3 = fmaf(s[r + 3], qv_[r + 3], a3);
-            }
-            ared[r0][part][lane] = (a0 + a1) + (a2 + a3);
+            for (int i = 0; i < 4; ++i) aacc[i] = f2_pack(0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < 16; r += 4)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s[r + i] = f2_fma(kp[r + i], d2, f2_mul(g2, s[r + i]));
+                    aacc[i] = f2_fma(s[r + i], qp[r + i], aacc[i]);
+                }
+            float a0, a1, a2, a3, a4, a5, a6, a7;
+            f2_unpack(aacc[0], a0, a1);
+            f2_unpack(aacc[1], a2, a3);
+            f2_unpack(aacc[2], a4, a5);
+            f2_unpack(aacc[3], a6, a7);
+            ared[r0][part][lane] = ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
         }
         __syncthreads();   // the tile's sums are complete; its buffer may be refilled two tiles on
         for (int i = tid; i < nr * GDN_QC; i += GDN_THREADS) {
@@ -365,7 +394,12 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_scan(const float* __restric
         }
     }
 #pragma unroll
-    for (int r = 0; r < 32; ++r) S_out[soff + (size_t) r * GDN_HS] = s[r];
+    for (int r = 0; r < 32; r += 2) {
+        float x, y;
+        f2_unpack(s[r / 2], x, y);
+        S_out[soff + (size_t) r * GDN_HS] = x;
+        S_out[soff + (size_t) (r + 1) * GDN_HS] = y;
+    }
 }
 
 // block = one row, warp = a quarter (32 columns) of a value head at a time: y = o * rsqrt(mean(o^2) + eps) * nw * sigmoid(z)
