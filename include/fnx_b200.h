@@ -11,7 +11,9 @@
  *   - activations are f32 rows; quantised weights are GGML IQ3_S, re-tiled once by fnx_iq3s_retile();
  *   - window scalars (first position, state slot) live in device memory so that captured graphs replay;
  *   - no entry point synchronises, allocates or reads results back: all are stream-capture safe, except where
- *     a comment says otherwise (fnx_engine_* set-up calls, fnx_comm_*);
+ *     a comment says otherwise (fnx_engine_* set-up calls, fnx_engine_load_gguf, fnx_comm_*; fnx_gguf_* is host code);
+ *     the prompt-sized products (fnx_dense_prompt, fnx_router_rows, fnx_moe_prefill, fnx_attn_prompt) encode their
+ *     tensor maps on the host at each call and pass them by value: no device allocation, capture safe;
  *   - return value: 0 on success, a negative FNX_E_* code otherwise, with text from fnx_last_error();
  *     device-side conditions are OR-ed into the `err` word (FNX_ERR_* bits, the reference's bit values,
  *     engine/src/kernels.hpp:373-375), which the caller reads back with the window's results.
