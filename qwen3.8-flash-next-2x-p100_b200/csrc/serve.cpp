@@ -2,6 +2,7 @@
 // in, token ids out, on stdin / stdout.  The server tokenizes, applies the chat template and matches stop strings.
 //
 //   fnx_serve --serve --native MODEL.gguf [--max-context N] [--spec K] [--lookup K] [--eos ID,ID] [--batch SLOTS]
+//             [--conversation-cache-mib M]
 //
 // After loading: INFO engine=fnx_b200 ... and READY <max context> stop.  One request at a time:
 //   GEN <max_new> [key=value ...] <ids csv>
@@ -11,7 +12,9 @@
 // QUIT (or the end of the input) ends the process.  Keys: temperature top_p top_k min_p seed (sampling: the engine's
 // speculative-sampling rule over each row's 64 best tokens); penalty_repeat penalty_freq penalty_present penalty_last_n (sampled
 // requests) and logit_bias=<id>:<bias>,... (greedy ones too) change each window row's logits before the rule looks at them.
-// A prompt that extends what the engine already holds reads only its new tokens (RESUME counts the reused ones).
+// A prompt that extends what the engine already holds reads only its new tokens (RESUME counts the reused ones).  With
+// --conversation-cache-mib M a conversation that another one displaces is parked in host memory (the engine's sequence state:
+// K/V rows, DeltaNet states, context) and comes back when a later prompt goes on from it; the least recently used go first.
 // With --batch (INFO batch_slots=N): BGEN <slot> <max_new> <ids csv> reads a prompt into a free slot (each slot one of the
 // engine's sequences) between the decoding slots' windows and answers its first token as T + DONE, then BADM <slot> 1 if it
 // goes on (0 if not); the decoding slots share windows (a row each and their draft-layer drafts: the engine's batched lanes)
@@ -46,6 +49,7 @@ void say(const std::string& line) {
 struct Args {
     std::string gguf;
     int max_ctx = 32768, K = 4, lookup = 15, prompt_chunk = 8192, batch = 1;
+    long cache_mib = 0;   // parked conversations in host memory (0: none)
     std::vector<int> eos;
 };
 
@@ -68,7 +72,8 @@ Args parse_args(int argc, char** argv) {
             for (const std::string& t : fnx_serve::split_commas(val())) a.eos.push_back(fnx_serve::field_int("--eos", "id", t));
         }
         // the reference's draft-layer files and card layout: this engine's file holds the draft layer, one GPU holds the model
-        else if (k == "--mtp" || k == "--draft-vocab" || k == "--layer-split" || k == "--conversation-cache-mib") val();
+        else if (k == "--conversation-cache-mib") a.cache_mib = std::stol(val());
+        else if (k == "--mtp" || k == "--draft-vocab" || k == "--layer-split") val();
         else if (k == "--batch") a.batch = std::stoi(val());
         else throw std::runtime_error("unknown argument " + k);
     }
@@ -78,6 +83,7 @@ Args parse_args(int argc, char** argv) {
     if (a.lookup < 0 || a.lookup > FNX_MAX_ROWS - 1) throw std::runtime_error("--lookup must be 0.." + std::to_string(FNX_MAX_ROWS - 1));
     if (a.max_ctx < 16) throw std::runtime_error("--max-context must be at least 16");
     if (a.prompt_chunk < 1) throw std::runtime_error("--prompt-chunk must be at least 1");
+    if (a.cache_mib < 0) throw std::runtime_error("--conversation-cache-mib must be >= 0");
     if (a.batch < 1 || a.batch > fnx_serve::MAX_SLOTS) throw std::runtime_error("--batch must be 1.." + std::to_string(fnx_serve::MAX_SLOTS));
     return a;
 }
@@ -98,6 +104,14 @@ struct Server {
     std::vector<int> history;   // the tokens sequence 0 holds
     bool sampling = false;      // the acceptance rule the engine is set to
     bool rules = false;         // the engine applies a request's penalties or logit_bias
+    struct Parked {
+        std::vector<int> tokens;       // the conversation's kept tokens
+        std::vector<uint8_t> state;    // fnx_engine_save_state's image, K/V rows included
+        long used = 0;
+    };
+    std::vector<Parked> parked;
+    size_t parked_bytes = 0;
+    long clock = 0;
     struct Slot {
         bool decoding = false;
         long seq = 0;               // its request's number
@@ -148,6 +162,44 @@ struct Server {
         rules = true;
     }
 
+    // the live conversation of sequence 0 to host memory, if the cache has (or can make) room for it
+    void park_live() {
+        const size_t budget = (size_t) a.cache_mib << 20;
+        if (dirty || history.empty() || budget == 0) return;
+        const size_t need = fnx_engine_state_bytes(e, 0, 1);
+        if (need == 0 || need > budget) return;
+        while (parked_bytes + need > budget && !parked.empty()) {   // the least recently used go first
+            size_t lru = 0;
+            for (size_t i = 1; i < parked.size(); ++i)
+                if (parked[i].used < parked[lru].used) lru = i;
+            parked_bytes -= parked[lru].state.size();
+            parked.erase(parked.begin() + (long) lru);
+        }
+        Parked p;
+        p.tokens = history;
+        p.state.resize(need);
+        p.used = ++clock;
+        ok(fnx_engine_save_state(e, 0, 1, p.state.data(), need), "save_state");
+        parked_bytes += need;
+        parked.push_back(std::move(p));
+    }
+
+    // the longest parked conversation that the prompt (all but its last token) goes on from: back into sequence 0
+    size_t unpark_for(const std::vector<int>& ids) {
+        int best = -1;
+        for (size_t i = 0; i < parked.size(); ++i) {
+            const std::vector<int>& t = parked[i].tokens;
+            if (t.size() <= ids.size() - 1 && std::equal(t.begin(), t.end(), ids.begin()) && (best < 0 || t.size() > parked[(size_t) best].tokens.size())) best = (int) i;
+        }
+        if (best < 0) return 0;
+        Parked& p = parked[(size_t) best];
+        ok(fnx_engine_load_state(e, 0, p.state.data(), p.state.size()), "load_state");
+        history = p.tokens;
+        parked_bytes -= p.state.size();
+        parked.erase(parked.begin() + best);
+        return history.size();
+    }
+
     void solo(const Request& r) {
         const bool stopped = in.begin(r.seq);
         struct End {
@@ -159,8 +211,11 @@ struct Server {
         size_t reused = 0;
         if (!dirty && history.size() <= (size_t) n - 1 && std::equal(history.begin(), history.end(), r.ids.begin())) reused = history.size();
         else {
-            ok(fnx_engine_reset(e, 0), "reset");
+            park_live();   // another conversation takes the sequence: this one waits in host memory
             history.clear();
+            if (dirty) ok(fnx_engine_reset(e, 0), "reset");   // (a request that failed half way may have left a window open)
+            reused = unpark_for(r.ids);
+            if (reused == 0) ok(fnx_engine_reset(e, 0), "reset");
         }
         dirty = true;
         set_rule(r);
@@ -452,7 +507,7 @@ int main(int argc, char** argv) {
     }
     std::fprintf(stderr, "fnx_serve: loaded in %.1f s (%d tensors quantised to IQ3_S on the way), %.2f GiB on the GPU, context %d, chain %d, lookup %d\n",
                  ms_since(t_load) / 1e3, converted, fnx_engine_device_bytes(e) / 1073741824.0, a.max_ctx, a.K, a.lookup);
-    say("INFO engine=fnx_b200 version=" + std::to_string(fnx_version()) + " spec=" + std::to_string(a.K) + " conversation_cache_mib=0 logit_bias=1" +
+    say("INFO engine=fnx_b200 version=" + std::to_string(fnx_version()) + " spec=" + std::to_string(a.K) + " conversation_cache_mib=" + std::to_string(a.cache_mib) + " logit_bias=1" +
         (a.batch > 1 ? " batch_slots=" + std::to_string(a.batch) : ""));
     say("READY " + std::to_string(a.max_ctx) + " stop");
     Input in;

@@ -866,3 +866,51 @@ def test_serve_process_batched_slots(F, tmp_path):
     assert s.line().startswith("ERR BGEN: batched slots decode greedily")
     assert s.quit() == 0
     a.close()
+
+
+def test_serve_process_parks_and_resumes_conversations(F, tmp_path):
+    """fnx_serve --conversation-cache-mib: a conversation displaced by another one waits in host memory (the engine's sequence
+    state) and comes back when a later prompt goes on from it: RESUME counts its tokens and the reply is the one the
+    conversation would have got had it never left the engine."""
+    from gguf_files import model_meta, tiny_model_tensors, write_gguf
+    cfg = small_cfg(F, max_ctx=1024)
+    a = F.Engine(cfg)
+    a.init_synthetic(seed=9, sigma=0.02)
+    path = tmp_path / "tiny.gguf"
+    write_gguf(path, model_meta(cfg), tiny_model_tensors(F, a, cfg))
+    rng = np.random.default_rng(44)
+    pa, pb = rng.integers(0, cfg.vocab, size=30).tolist(), rng.integers(0, cfg.vocab, size=22).tolist()
+    csv = lambda ids: ",".join(map(str, ids))
+
+    def plain_more(prompt_new, n_new):   # on engine `a`, which holds the conversation so far
+        if len(prompt_new) > 1:
+            a.prompt(prompt_new[:-1])
+        x, out = prompt_new[-1], []
+        for _ in range(n_new):
+            n, path_, em = a.verify([x])
+            a.commit([0])
+            x = em[0]
+            out.append(x)
+        return out
+
+    s = _Serve("--native", path, "--max-context", 1024, "--spec", 3, "--lookup", 4, "--prompt-chunk", 4096, "--conversation-cache-mib", 64)
+    assert "conversation_cache_mib=64" in s.line()
+    s.line()
+    s.send(f"GEN 8 {csv(pa)}")
+    _, resume, ta, _ = s.reply()
+    a.reset()
+    assert resume == 0 and ta == plain_more(pa, 8)
+    s.send(f"GEN 6 {csv(pb)}")                       # another conversation: A is parked
+    _, resume, tb, _ = s.reply()
+    assert resume == 0 and len(tb) == 6
+    more = pa + ta + rng.integers(0, cfg.vocab, size=5).tolist()
+    s.send(f"GEN 7 {csv(more)}")                     # A goes on: its state comes back from host memory (B is parked in turn)
+    _, resume, ta2, done = s.reply()
+    assert resume == len(pa) + len(ta) - 1 and done[7] == str(resume)
+    assert ta2 == plain_more(more[len(pa) + len(ta) - 1:], 7)
+    moreb = pb + tb + [int(rng.integers(0, cfg.vocab))]
+    s.send(f"GEN 3 {csv(moreb)}")                    # and B likewise
+    _, resume, tb2, _ = s.reply()
+    assert resume == len(pb) + len(tb) - 1 and len(tb2) == 3
+    assert s.quit() == 0
+    a.close()
