@@ -127,12 +127,6 @@ int fnx_moe_combine(const float* part, const int* topi, const float* topw, const
  * them, instead of by every block of the next projection.  R gets the same bits as from fnx_moe_combine. */
 int fnx_moe_combine_image(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
                           int K, float* R, void* img_out, const float* img_norm_w, fnx_stream st);
-/* fnx_moe_combine_image that also asks L2, before it waits for the launches ahead of it, for next_w_bytes bytes at next_w
- * (16-byte aligned; the weights of the product that consumes the image), so that they arrive while the down products
- * still run.  next_w may be null.  The results do not change. */
-int fnx_moe_combine_image_ahead(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H,
-                                int K, float* R, void* img_out, const float* img_norm_w, const void* next_w, size_t next_w_bytes,
-                                fnx_stream st);
 
 /* Prompt-sized MoE block (moe_gate_up_mma / moe_down_mma, engine/src/kernels.hpp:328-330, with the job build of
  * engine/src/prefill.cu:288-377): out[t] (+)= the routed experts in [e_lo, e_hi) and (add_shared) the shared expert of

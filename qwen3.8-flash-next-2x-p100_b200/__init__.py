@@ -70,7 +70,6 @@ _PROTOS = {
     "fnx_moe_down": (_I, [_P, _Z, _I, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P]),
     "fnx_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
     "fnx_moe_combine_image": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
-    "fnx_moe_combine_image_ahead": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "fnx_dense_image_bytes": (_Z, [_I]),
     "fnx_dense_image": (_I, [_P, _I, _I, _P, _I, _I, _F, _P, _I, _I, _P, _P]),
     "fnx_moe_prefill_scratch_bytes": (_Z, [_I, _I, _I, _I, _I]),
@@ -293,18 +292,13 @@ def moe_experts(Wgu, Wdn, Wsh_gu, Wsh_dn, route, x, F: int, K: int, norm_w=None,
     return out, h, part
 
 
-def moe_combine_image(part, route, T: int, E: int, H: int, K: int, R, next_norm_w, next_w=None):
-    """R += the weighted expert outputs (fnx_moe_combine, accumulating); returns the image of rmsnorm(R) * next_norm_w.
-    next_w: the weights of the product that will consume the image; the kernel asks L2 for them (no result changes)."""
+def moe_combine_image(part, route, T: int, E: int, H: int, K: int, R, next_norm_w):
+    """R += the weighted expert outputs (fnx_moe_combine, accumulating); returns the image of rmsnorm(R) * next_norm_w."""
     import torch
     L = lib()
     img = torch.zeros(((T + DENSE_ROWS - 1) // DENSE_ROWS) * L.fnx_dense_image_bytes(H), dtype=torch.uint8, device=R.device)
-    if next_w is None:
-        check(L.fnx_moe_combine_image(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, ptr(R), ptr(img),
-                                      ptr(next_norm_w), _stream()))
-    else:
-        check(L.fnx_moe_combine_image_ahead(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, ptr(R), ptr(img),
-                                            ptr(next_norm_w), ptr(next_w), next_w.numel() * next_w.element_size(), _stream()))
+    check(L.fnx_moe_combine_image(ptr(part), ptr(route["topi"]), ptr(route["topw"]), ptr(route["logits"]), T, E, H, K, ptr(R), ptr(img),
+                                  ptr(next_norm_w), _stream()))
     return img
 
 

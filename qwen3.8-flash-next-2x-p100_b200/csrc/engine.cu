@@ -113,7 +113,6 @@ struct fnx_engine {
     // the image of the new residual rows that the combine leaves for the next projection (single rank; one per FNX_DENSE_ROWS rows)
     uint8_t* d_img = nullptr;
     bool use_img = true;
-    bool weights_ahead = true;   // the kernel that completes a layer's rows asks L2 for the next layer's first weights
     // the prompt pass (fnx_engine_prompt): buffers for a chunk of prompt_chunk rows, made at its first call
     int prompt_chunk = 40960;
     float *pR = nullptr, *pproj = nullptr, *pmix = nullptr, *plogits = nullptr, *ptopw = nullptr;
@@ -631,8 +630,7 @@ __global__ void k_dp_recv(const float* __restrict__ xrows, const unsigned* __res
 // ---- one MoE block on T rows of residual R: R += experts(rmsnorm(R))
 // next_norm: the norm weights of the projection that reads R next; with them (single rank) the combine leaves that projection's
 // image of the rows in e->d_img and *img_ready is set
-static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T, const float* next_norm = nullptr, bool* img_ready = nullptr,
-                       const LayerW* next = nullptr) {
+static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T, const float* next_norm = nullptr, bool* img_ready = nullptr) {
     const Dims d = dims(e->c);
     const bool ep = e->c.ep_size > 1;
     if (img_ready) *img_ready = false;
@@ -644,9 +642,7 @@ static int enqueue_moe(fnx_engine* e, const LayerW& L, float* R, int T, const fl
     FNX_TRY(fnx_moe_down(L.wdn, e->dn_bytes, e->e_lo, L.wsh_dn, d.E, e->jobs, e->njobs, njobs_max, e->hbuf, d.H, d.F, e->part, e->err, e->st));
     if (!ep && next_norm && e->use_img) {
         if (img_ready) *img_ready = true;
-        const bool ahead = next && e->weights_ahead;
-        return fnx_moe_combine_image_ahead(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, R, e->d_img, next_norm, ahead ? next->w_in : nullptr,
-                                           ahead ? iq3s_bytes(next->in_rows, d.H) : 0, e->st);
+        return fnx_moe_combine_image(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, R, e->d_img, next_norm, e->st);
     }
     if (!ep) return fnx_moe_combine(e->part, e->topi, e->topw, e->rlogits, T, d.E, d.H, d.K, 0, d.E, 1, R, 1, e->st);
     if (e->ep_peers && e->ep_one_kernel && d.H % 256 == 0) {
@@ -729,8 +725,7 @@ static int enqueue_verify(fnx_engine* e, int seq, int T, bool tree) {
         const LayerW& L = e->layers[l];
         if (L.attn) FNX_TRY(enqueue_attention(e, L, e->R, T, seq, par, e->d_depth, e->d_pos + seq, img));
         else FNX_TRY(enqueue_gdn(e, L, e->R, T, seq, par, img));
-        FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img,
-                            l + 1 < e->layers.size() ? &e->layers[l + 1] : nullptr));
+        FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img));
     }
     FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0, img));
     if (e->rules_on)   // the request's logit_bias and penalties, before either rule looks at the logits
@@ -858,8 +853,7 @@ static int enqueue_verify_lanes(fnx_engine* e, int n_lanes, int rows, int T) {  
     for (size_t l = 0; l < e->layers.size(); ++l) {
         const LayerW& L = e->layers[l];
         FNX_TRY(enqueue_mixer_lanes(e, L, e->R, T, n_lanes, rows, e->d_lane_seq, e->d_lane_row0, e->d_pos, img));
-        FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img,
-                            l + 1 < e->layers.size() ? &e->layers[l + 1] : nullptr));
+        FNX_TRY(enqueue_moe(e, L, e->R, T, l + 1 < e->layers.size() ? e->layers[l + 1].norm1 : e->out_norm, &img));
     }
     FNX_TRY(enqueue_dense(e, e->head, d.V, d.H, e->R, d.H, T, e->out_norm, e->logits, d.V, 0, img));
     if (e->sampling_on) {
@@ -1002,7 +996,6 @@ extern "C" int fnx_engine_create(const fnx_model_config* cfg, fnx_engine** out) 
         FNX_TRY(dalloc(e, &e->moe_out, (size_t) d.MAXR * d.H, "buf.moe_out"));
         FNX_TRY(dalloc(e, &e->d_img, (size_t) ((d.MAXR + FNX_DENSE_ROWS - 1) / FNX_DENSE_ROWS) * fnx_dense_image_bytes(d.H)));
         if (const char* nf = getenv("FNX_NO_IMAGE")) e->use_img = nf[0] != '1';
-        if (const char* nf = getenv("FNX_NO_WEIGHTS_AHEAD")) e->weights_ahead = nf[0] != '1';
         if (d.H > 2048) e->use_img = false;   // (an image's product takes FNX_DENSE_ROWS rows a call, which wider rows do not fit)
         if (c.ep_size > 1) {
             e->mix_width = mixw;

@@ -306,17 +306,7 @@ __global__ void k_combine(const float* __restrict__ part, const int* __restrict_
 // change.  The blocks of an image's last live row also clear the rows of its last group that hold nothing.
 __global__ void __launch_bounds__(32) k_combine_image(const float* __restrict__ part, const int* __restrict__ topi, const float* __restrict__ topw,
                                                       const float* __restrict__ logits, int T, int E, int H, int K, float* __restrict__ out,
-                                                      uint8_t* __restrict__ img_out, const float* __restrict__ img_norm_w, size_t img_stride,
-                                                      const uint8_t* __restrict__ pf, unsigned long long pf_bytes) {
-    // the next product's weights do not depend on anything before this kernel: ask L2 for them before waiting, each thread
-    // its own run of 4 KiB pieces, so that they arrive while the down products still run
-    if (pf) {
-        const unsigned long long nthr = (unsigned long long) gridDim.x * gridDim.y * 32, me = ((unsigned long long) blockIdx.y * gridDim.x + blockIdx.x) * 32 + threadIdx.x;
-        for (unsigned long long o = me * 4096ull; o < pf_bytes; o += nthr * 4096ull) {
-            const unsigned n = (unsigned) (pf_bytes - o < 4096ull ? (pf_bytes - o) & ~15ull : 4096ull);
-            if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf + o), "r"(n) : "memory");
-        }
-    }
+                                                      uint8_t* __restrict__ img_out, const float* __restrict__ img_norm_w, size_t img_stride) {
     pdl_wait();
     pdl_launch_dependents();
     const int blk = blockIdx.x, t = blockIdx.y, lane = threadIdx.x, KB = H / 256;
@@ -430,19 +420,13 @@ extern "C" int fnx_moe_combine(const float* part, const int* topi, const float* 
 
 extern "C" int fnx_moe_combine_image(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H, int K, float* R,
                                      void* img_out, const float* img_norm_w, fnx_stream st) {
-    return fnx_moe_combine_image_ahead(part, topi, topw, logits, T, E, H, K, R, img_out, img_norm_w, nullptr, 0, st);
-}
-
-extern "C" int fnx_moe_combine_image_ahead(const float* part, const int* topi, const float* topw, const float* logits, int T, int E, int H, int K, float* R,
-                                           void* img_out, const float* img_norm_w, const void* next_w, size_t next_w_bytes, fnx_stream st) {
     FNX_REQUIRE(part && topi && topw && logits && R && img_out && img_norm_w, "fnx_moe_combine_image: null pointer");
-    FNX_REQUIRE(((uintptr_t) next_w & 15) == 0, "fnx_moe_combine_image: the weights to ask for start off a 16-byte boundary");
     FNX_REQUIRE(T >= 1 && T <= FNX_MAX_ROWS && K >= 1 && K <= 32, "fnx_moe_combine_image: %d rows, top %d", T, K);
     FNX_REQUIRE(H == 256 || H == 512 || H == 1024 || H == 2048 || H == 4096, "fnx_moe_combine_image: hidden %d", H);
     FNX_REQUIRE(((uintptr_t) img_out & 15) == 0 && ((uintptr_t) R & 15) == 0 && ((uintptr_t) part & 15) == 0, "fnx_moe_combine_image: 16-byte alignment");
     {
         const cudaError_t le_ = launch_k(k_combine_image, dim3(H / 256, T), dim3(32), 0, as_stream(st), part, topi, topw, logits, T, E, H, K, R, (uint8_t*) img_out,
-                                         img_norm_w, fnx_dense_image_bytes(H), (const uint8_t*) next_w, (unsigned long long) (next_w ? next_w_bytes : 0));
+                                         img_norm_w, fnx_dense_image_bytes(H));
         if (le_ != cudaSuccess) return fail(FNX_E_CUDA, "k_combine_image: launch failed: %s", cudaGetErrorString(le_));
     }
     FNX_LAUNCH_OK("fnx_moe_combine_image");

@@ -263,8 +263,7 @@ def test_combine_that_leaves_the_image_gives_the_same_bits(F, T):
         F.check(L.fnx_moe_combine(F.ptr(part), F.ptr(route["topi"]), F.ptr(route["topw"]), F.ptr(route["logits"]), T, E, H, K, 0, E, 1, F.ptr(want), 1,
                                   None))
         got = R0.clone()
-        # the second pass also asks L2 for the next product's weights (a size that is no multiple of 4 KiB): same bits
-        img = F.moe_combine_image(part, route, T, E, H, K, got, nw2, next_w=Wd.view(torch.uint8).reshape(-1)[: Wd.numel() * Wd.element_size() - 48] if rep else None)
+        img = F.moe_combine_image(part, route, T, E, H, K, got, nw2)
         torch.cuda.synchronize()
         assert torch.equal(got, want)
         y_img = F.dense_image(Wd, rows, H, img, T)
