@@ -254,6 +254,14 @@ int fnx_logit_adjust(float* logits, int T, int V, const int* ctx, const int* ctx
                      float present, const int* bias_tok, const float* bias_val, int bias_n, fnx_stream st);
 /* embed rows: R[t] = f16 table[tok[t]] (the reference embeds on the host, engine_common.cu:955) */
 int fnx_embed_rows(const void* table_f16, const int* tok, int T, int H, float* R, fnx_stream st);
+/* The draft (MTP) layer's input rows, the one step of mtp_enqueue that no other layer has (engine/src/engine.cu:2103-2113):
+ * R[t] = fc_hid . (rmsnorm(h[t]) * hnorm) + fc_emb . (rmsnorm(table[tok[t]]) * enorm), t < T; fc_hid and fc_emb H x H IQ3_S tile
+ * matrices, h the main model's rows ahead of its output norm (row stride ldh), tok the tokens that follow them, emb [T][H]
+ * scratch that receives the embedding rows.  The rest of a draft call is the attention block (fnx_dense, fnx_attn_prep_append,
+ * fnx_attn), the MoE block (fnx_router_route, fnx_moe_gate_up, fnx_moe_down, fnx_moe_combine) and the head (fnx_dense,
+ * fnx_argmax) on R, as for any layer; fnx_engine_draft is that composition.  Capture-safe; allocates nothing. */
+int fnx_mtp_input(const void* fc_hid, const void* fc_emb, const void* table_f16, const float* hnorm, const float* enorm, float eps,
+                  const float* h, int ldh, const int* tok, int T, int H, float* emb, float* R, unsigned* err, fnx_stream st);
 /* rms_norm_rows (engine/src/kernels.hpp:406) */
 int fnx_rmsnorm(const float* x, const float* w, float* y, int rows, int n, float eps, fnx_stream st);
 

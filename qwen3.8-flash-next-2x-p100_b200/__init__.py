@@ -90,6 +90,7 @@ _PROTOS = {
     "fnx_argmax": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "fnx_top_tokens": (_I, [_P, _I, _I, _P, _P, _P]),
     "fnx_embed_rows": (_I, [_P, _P, _I, _I, _P, _P]),
+    "fnx_mtp_input": (_I, [_P, _P, _P, _P, _P, _F, _P, _I, _P, _I, _I, _P, _P, _P, _P]),
     "fnx_rmsnorm": (_I, [_P, _P, _P, _I, _I, _F, _P]),
     "fnx_lookup_draft": (_I, [_P, _P, _I, _P, _P, _P, _P]),
     "fnx_accept_greedy": (_I, [_P, _P, _P, _I, _P, _P]),
@@ -250,6 +251,19 @@ def dense(W, rows: int, cols: int, x, norm_w=None, eps: float = 1e-6, out=None, 
         check(lib().fnx_dense(ptr(W), rows, cols, ptr(x[t0:]), x.stride(0), nt, ptr(norm_w), eps, ptr(out[t0:]), out.stride(0),
                               1 if accumulate else 0, ptr(err), _stream()))
     return out, err
+
+
+def mtp_input(fc_hid, fc_emb, table_f16, hnorm, enorm, h, tok, eps: float = 1e-6, err=None):
+    """The draft layer's input rows: fc_hid . rmsnorm(h) * hnorm + fc_emb . rmsnorm(table[tok]) * enorm
+    (mtp_enqueue, engine/src/engine.cu:2103-2113).  Returns (R, emb, err)."""
+    import torch
+    T, H = h.shape
+    R = torch.empty((T, H), dtype=torch.float32, device=h.device)
+    emb = torch.empty((T, H), dtype=torch.float32, device=h.device)
+    err = new_err(h.device) if err is None else err
+    check(lib().fnx_mtp_input(ptr(fc_hid), ptr(fc_emb), ptr(table_f16), ptr(hnorm), ptr(enorm), eps, ptr(h), h.stride(0), ptr(tok), T, H, ptr(emb),
+                              ptr(R), ptr(err), _stream()))
+    return R, emb, err
 
 
 def router_route(Wr, x, K: int, norm_w=None, eps: float = 1e-6, e_lo: int = 0, e_hi=None, add_shared: bool = True, err=None):

@@ -744,9 +744,7 @@ static int enqueue_verify(fnx_engine* e, int seq, int T, bool tree) {
 // one MTP call on T rows: Rm = fc_hid(rms(src)) + fc_emb(rms(emb(tok))), the draft block, the head on the last row
 static int enqueue_mtp(fnx_engine* e, int seq, int T, const float* src) {
     const Dims d = dims(e->c);
-    FNX_TRY(fnx_embed_rows(e->embed, e->d_mtok, T, d.H, e->Emb, e->st));
-    FNX_TRY(enqueue_dense(e, e->mtp_fc_hid, d.H, d.H, src, d.H, T, e->mtp_hnorm, e->Rm, d.H, 0));
-    FNX_TRY(enqueue_dense(e, e->mtp_fc_emb, d.H, d.H, e->Emb, d.H, T, e->mtp_enorm, e->Rm, d.H, 1));
+    FNX_TRY(fnx_mtp_input(e->mtp_fc_hid, e->mtp_fc_emb, e->embed, e->mtp_hnorm, e->mtp_enorm, e->c.eps, src, d.H, e->d_mtok, T, d.H, e->Emb, e->Rm, e->err, e->st));
     FNX_TRY(enqueue_attention(e, e->mtp, e->Rm, T, seq, nullptr, nullptr, e->d_mpos));
     FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, T));
     return fnx_dense(e->mtp_head ? e->mtp_head : e->head, e->dvn, d.H, e->Rm + (size_t) (T - 1) * d.H, d.H, 1, e->mtp_onorm, e->c.eps, e->logits, e->dvn, 0,
@@ -869,9 +867,7 @@ static int enqueue_verify_lanes(fnx_engine* e, int n_lanes, int rows, int T) {  
 // through the head and their best tokens land in best_i[0 .. n_lanes)
 static int enqueue_mtp_lanes(fnx_engine* e, int n_lanes, int Tm, int max_rows, const int* d_row0, const float* src) {
     const Dims d = dims(e->c);
-    FNX_TRY(fnx_embed_rows(e->embed, e->d_mtok, Tm, d.H, e->Emb, e->st));
-    FNX_TRY(enqueue_dense(e, e->mtp_fc_hid, d.H, d.H, src, d.H, Tm, e->mtp_hnorm, e->Rm, d.H, 0));
-    FNX_TRY(enqueue_dense(e, e->mtp_fc_emb, d.H, d.H, e->Emb, d.H, Tm, e->mtp_enorm, e->Rm, d.H, 1));
+    FNX_TRY(fnx_mtp_input(e->mtp_fc_hid, e->mtp_fc_emb, e->embed, e->mtp_hnorm, e->mtp_enorm, e->c.eps, src, d.H, e->d_mtok, Tm, d.H, e->Emb, e->Rm, e->err, e->st));
     FNX_TRY(enqueue_mixer_lanes(e, e->mtp, e->Rm, Tm, n_lanes, max_rows, e->d_lane_seq, d_row0, e->d_mpos_seq));
     FNX_TRY(enqueue_moe(e, e->mtp, e->Rm, Tm));
     k_last_rows<<<dim3((d.H + 255) / 256, n_lanes), 256, 0, e->st>>>(e->Rlast, e->Rm, d_row0, d.H);

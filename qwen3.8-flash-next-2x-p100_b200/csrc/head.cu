@@ -259,6 +259,25 @@ extern "C" int fnx_embed_rows(const void* table_f16, const int* tok, int T, int 
     return FNX_OK;
 }
 
+// The draft layer's input rows (the step of mtp_enqueue that no other layer has, engine/src/engine.cu:2103-2113):
+// R[t] = fc_hid . rmsnorm(h[t]) * hnorm  +  fc_emb . rmsnorm(table[tok[t]]) * enorm.  The embedding rows pass through emb.
+extern "C" int fnx_mtp_input(const void* fc_hid, const void* fc_emb, const void* table_f16, const float* hnorm, const float* enorm, float eps,
+                             const float* h, int ldh, const int* tok, int T, int H, float* emb, float* R, unsigned* err, fnx_stream st) {
+    FNX_REQUIRE(fc_hid && fc_emb && table_f16 && hnorm && enorm && h && tok && emb && R, "fnx_mtp_input: null pointer");
+    FNX_REQUIRE(T >= 1 && ldh >= H, "fnx_mtp_input: %d rows, row stride %d for %d columns", T, ldh, H);
+    FNX_TRY(fnx_embed_rows(table_f16, tok, T, H, emb, st));
+    const int per = fnx_dense_rows(H);
+    for (int t0 = 0; t0 < T; t0 += per) {
+        const int nt = T - t0 < per ? T - t0 : per;
+        FNX_TRY(fnx_dense(fc_hid, H, H, h + (size_t) t0 * ldh, ldh, nt, hnorm, eps, R + (size_t) t0 * H, H, 0, err, st));
+    }
+    for (int t0 = 0; t0 < T; t0 += per) {
+        const int nt = T - t0 < per ? T - t0 : per;
+        FNX_TRY(fnx_dense(fc_emb, H, H, emb + (size_t) t0 * H, H, nt, enorm, eps, R + (size_t) t0 * H, H, 1, err, st));
+    }
+    return FNX_OK;
+}
+
 extern "C" int fnx_rmsnorm(const float* x, const float* w, float* y, int rows, int n, float eps, fnx_stream st) {
     FNX_REQUIRE(x && w && y && rows >= 1 && n >= 1, "fnx_rmsnorm: bad arguments");
     {

@@ -80,6 +80,32 @@ def test_dense_with_norm_accumulate_and_strides(F, O):
     assert np.array_equal(out[:, rows:].cpu().numpy(), base[:, rows:])   # nothing written past the rows
 
 
+@pytest.mark.parametrize("T", [1, 5, 20])
+def test_mtp_input_matches_oracle(F, O, T):
+    """The draft layer's input rows against the oracle's composition, and bit-equal to the two dense calls they stand for
+    (20 rows: more than one call of the dense form)."""
+    import torch
+    H, V = 2048, 300
+    hid_t, hid_g = gpu_iq3s_matrix(F, H, H, seed=8, stream_id=1)
+    emb_t, emb_g = gpu_iq3s_matrix(F, H, H, seed=8, stream_id=2)
+    rng = np.random.default_rng(40 + T)
+    table = (rng.standard_normal((V, H)) * 0.5).astype(np.float16)
+    hn = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    en = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    h = (rng.standard_normal((T, H + 32)) * 2.0).astype(np.float32)   # rows with a stride
+    tok = rng.integers(0, V, T).astype(np.int32)
+    hd = dev(h)[:, :H]
+    R, emb, err = F.mtp_input(hid_t, emb_t, dev(table), dev(hn), dev(en), hd, dev(tok))
+    assert int(err.item()) == 0
+    e32 = table[tok].astype(np.float32)
+    assert np.array_equal(emb.cpu().numpy(), e32)
+    ref = O.iq3s_gemv(hid_g, H, H, O.rmsnorm(h[:, :H], hn, 1e-6)) + O.iq3s_gemv(emb_g, H, H, O.rmsnorm(e32, en, 1e-6))
+    assert rel_err(R.cpu().numpy(), ref) < TOL_GEMV
+    two, _ = F.dense(hid_t, H, H, hd, norm_w=dev(hn))
+    F.dense(emb_t, H, H, dev(e32), norm_w=dev(en), out=two, accumulate=True)
+    assert torch.equal(R, two)
+
+
 def test_dense_zero_and_huge_inputs(F, O):
     rows, cols = 64, 2048
     tiles, ggml = gpu_iq3s_matrix(F, rows, cols, seed=6, stream_id=5)
