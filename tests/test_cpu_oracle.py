@@ -218,6 +218,20 @@ def test_c_abi_exports_every_declared_symbol(F):
     assert L.fnx_iq3s_bytes(16, 256) == 1760 and F.iq3s_bytes(2048, 512) == 450560
 
 
+def test_header_is_plain_c(tmp_path):
+    """The header is what a cgo / ctypes / JNI binding includes: it has to compile as C, not only as C++."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "includes_header.c"
+    src.write_text('#include "fnx_b200.h"\nint main(void) { return fnx_iq3s_bytes(16, 256) == 1760 ? 0 : 1; }\n')
+    r = subprocess.run([cc, "-std=c11", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{ROOT / 'include'}", str(src)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_engine_argument_checks_need_no_gpu(F):
     L = F.lib()
     assert L.fnx_dense(None, 64, 2048, None, 2048, 1, None, 1e-6, None, 64, 0, None, None) == -1
