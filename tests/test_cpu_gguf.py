@@ -124,3 +124,46 @@ def test_damaged_files_are_refused(F, sample, tmp_path):
             F.Gguf(p)
     with pytest.raises(F.FnxError, match="cannot open"):
         F.Gguf(tmp_path / "absent.gguf")
+
+
+def _hand_written_gguf(version: int, align: int, tensors: dict, extra_meta=()):
+    """A container written field by field from the format's description (no writer library): header, metadata with
+    `general.alignment`, tensor records with offsets rounded up to the alignment, padded data."""
+    import struct
+
+    def s(x: str) -> bytes:
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    kv = [s("general.architecture") + struct.pack("<I", 8) + s("qwen3next"), s("general.alignment") + struct.pack("<II", 4, align)]
+    kv += list(extra_meta)
+    recs, blobs, off = [], [], 0
+    for name, arr in tensors.items():
+        ty = {np.dtype(np.float32): 0, np.dtype(np.float16): 1}[arr.dtype]
+        recs.append(s(name) + struct.pack("<I", arr.ndim) + b"".join(struct.pack("<Q", d) for d in reversed(arr.shape)) + struct.pack("<IQ", ty, off))
+        raw = arr.tobytes()
+        raw += b"\0" * (-len(raw) % align)
+        blobs.append(raw)
+        off += len(raw)
+    head = b"GGUF" + struct.pack("<IQQ", version, len(tensors), len(kv)) + b"".join(kv) + b"".join(recs)
+    head += b"\0" * (-len(head) % align)
+    return head + b"".join(blobs)
+
+
+@pytest.mark.parametrize("version,align", [(3, 32), (3, 64), (2, 32), (3, 4096)])
+def test_alignment_key_and_version_2(F, tmp_path, version, align):
+    import struct
+    rng = np.random.default_rng(align + version)
+    tensors = {"a": rng.standard_normal((3, 5)).astype(np.float32), "b": rng.standard_normal((7, 2)).astype(np.float16),
+               "c": rng.standard_normal((1, 33)).astype(np.float32)}
+    name = "general.name".encode()
+    extra = [struct.pack("<Q", len(name)) + name + struct.pack("<I", 8) + struct.pack("<Q", 4) + b"hand"]
+    p = tmp_path / "hand.gguf"
+    p.write_bytes(_hand_written_gguf(version, align, tensors, extra))
+    g = F.Gguf(p)
+    assert len(g) == 3 and g.str("general.name") == "hand" and g.num("general.alignment") == align
+    for k, want in tensors.items():
+        t = g.find(k)
+        assert t is not None and t.n_dims == want.ndim and tuple(t.ne[: want.ndim]) == tuple(reversed(want.shape))
+        assert np.array_equal(g.rows_f32(t), want.astype(np.float32))
+    g.close()
